@@ -1,0 +1,226 @@
+/*
+ * insconv_b200.h -- C ABI of the B200 (sm_100a) sparse-convolution hot path.
+ *
+ * This is the boundary a host language binds to.  Every entry point takes plain
+ * pointers and sizes; nothing here mentions torch.  Unless a parameter is marked
+ * HOST, every data pointer is a device pointer on the current CUDA device, and
+ * `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *
+ * Every function returns 0 on success and a negative SCN_E_* code otherwise;
+ * scn_last_error() then returns a thread-local, human readable message.  No
+ * entry point aborts the process, and there is no CPU fallback: without a
+ * usable CUDA device every compute call fails with SCN_E_CUDA.
+ *
+ * Each declaration cites the interface of the reference implementation
+ * (THU-luvision/INS-Conv, paths relative to sparseconvnet/SCN/) that it replaces.
+ *
+ * Conventions shared with the reference:
+ *   - spatial sizes, filter sizes and strides are int64[3] HOST arrays;
+ *   - feature matrices are row-major fp32 [rows, planes] with a row stride given
+ *     in elements (stride == planes for contiguous tensors);
+ *   - convolution weights are [volume, n_in, n_out] fp32, volume 27 (3x3x3
+ *     submanifold, offset index (dx+1)*9 + (dy+1)*3 + (dz+1)) or 8 (2x2x2 / stride
+ *     2, offset index (x&1)*4 + (y&1)*2 + (z&1));
+ *   - "no bias" is a NULL pointer;
+ *   - a site's row index is the rank of its packed key (batch, z, y, x) among the
+ *     active sites of its scale, so row i is the i-th smallest key.
+ */
+#ifndef INSCONV_B200_H_
+#define INSCONV_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define SCN_API __attribute__((visibility("default")))
+#else
+#define SCN_API
+#endif
+
+#define SCN_OK 0
+#define SCN_E_INVALID (-1)   /* bad argument (size, mode, null pointer, range)          */
+#define SCN_E_CUDA (-2)      /* a CUDA runtime call failed; message has the CUDA error  */
+#define SCN_E_RANGE (-3)     /* coordinate / batch index outside the representable key  */
+#define SCN_E_CAPACITY (-4)  /* scene bounding box or table larger than the build limit */
+#define SCN_E_STATE (-5)     /* metadata has no grid / rulebook for the requested size  */
+#define SCN_E_UNSUPPORTED (-6) /* feature of the reference outside the hot path         */
+
+/* arithmetic used by the gather-GEMM kernels */
+#define SCN_PREC_FP32 0      /* fp32 FFMA, fp32 accumulate (bit-for-bit deterministic)  */
+#define SCN_PREC_TF32 1      /* tcgen05 kind::tf32 tensor cores, fp32 accumulate in TMEM */
+
+/* Largest coordinate and batch index a key can hold. */
+#define SCN_MAX_COORD 65534
+#define SCN_MAX_BATCH 32766
+
+typedef struct scn_metadata scn_metadata; /* opaque; replaces Metadata<3> (Metadata/Metadata.h:218-386) */
+
+SCN_API const char *scn_last_error(void);
+/* Library / build identification, e.g. "insconv_b200 sm_100a". */
+SCN_API const char *scn_version(void);
+/* Number of kernel launches issued by this library since load (all threads). */
+SCN_API uint64_t scn_launch_count(void);
+/* 32: width of a rulebook entry.  Replaces n_rulebook_bits (pybind.cpp:304). */
+SCN_API int scn_n_rulebook_bits(void);
+
+/* ---------------------------------------------------------------------------
+ * Metadata: per-scale grids, rulebook caches, pre-exist maps.
+ * Replaces class Metadata<3> and its pybind surface (pybind.cpp:13-33).
+ * ------------------------------------------------------------------------- */
+SCN_API int scn_metadata_create(scn_metadata **out);
+SCN_API void scn_metadata_destroy(scn_metadata *m);
+/* Metadata::clear (Metadata/Metadata.cpp:68-90). */
+SCN_API int scn_metadata_clear(scn_metadata *m, void *stream);
+/* Metadata::getNActive (Metadata/Metadata.h). Returns -1 when the scale is unknown. */
+SCN_API int64_t scn_metadata_n_active(scn_metadata *m, const int64_t size[3]);
+/* Metadata::getSpatialLocations (Metadata/Metadata.cpp:793-821): writes [n_active,4]
+ * int64 rows (x,y,z,batch) in site order to `out` (HOST pointer). */
+SCN_API int scn_metadata_spatial_locations(scn_metadata *m, const int64_t size[3], int64_t *out_host, void *stream);
+/* Device pointers to a scale's site coordinates, SoA int32 [4][n] = x.., y.., z.., batch..
+ * (the reference's _d_hash_points, CUDA/CUDPPWrapper.hpp:736-1010, plus the batch column). */
+SCN_API int scn_metadata_site_coords(scn_metadata *m, const int64_t size[3], const int32_t **coords, int64_t *n);
+/* Copies the scale's open-addressing table to HOST arrays of `capacity` entries
+ * (capacity from a first call with keys == NULL).  Empty slots have key ~0.
+ * Key layout: batch<<48 | z<<32 | y<<16 | x.  This is the observable content of the
+ * reference's Multival_Point_Hashtable (CUDA/CUDPPWrapper.hpp:736-1010): key -> row. */
+SCN_API int scn_metadata_hash_dump(scn_metadata *m, const int64_t size[3], uint64_t *keys_host, int32_t *rows_host,
+                           int64_t *capacity, void *stream);
+/* Looks up `n` coordinates (device int32 SoA [4][n]) in the scale's table; rows[i] = site
+ * row or -1.  Replaces Multival_Point_Hashtable::retrieve (CUDA/CUDPPWrapper.hpp:900-1010). */
+SCN_API int scn_metadata_query(scn_metadata *m, const int64_t size[3], const int32_t *coords_soa, int64_t n,
+                       int32_t *rows, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * InputLayer / OutputLayer.
+ * ------------------------------------------------------------------------- */
+/* Builds the finest grid from input points.  Replaces Metadata::inputLayer ->
+ * inputLayerRulesSimple (Metadata/Metadata.cpp:442-463, Metadata/IOLayersRules.h:135-203)
+ * and HashInputPointClouds / InsertAndCompactPointCloud (CUDA/CUDPPWrapper.hpp:668-796).
+ * coords: int64 [n_in, ncols] rows (x,y,z[,batch]), ncols 3 or 4; HOST memory when
+ * coords_on_host != 0, else device memory.  mode: 3 = sum, 4 = mean (the only modes
+ * the reference's GPU grid accepts, IOLayersRules.h:141).  *n_active receives the
+ * number of unique sites.  Synchronises `stream` (sizes must reach the host). */
+SCN_API int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t *coords, int coords_on_host,
+                          int64_t n_in, int ncols, int64_t batch_size, int mode, void *stream,
+                          int64_t *n_active);
+/* out[site] = sum or mean of the features of its points, added in ascending point index.
+ * Replaces cuda_InputLayer_updateOutput / InputLayer_fp_ (CUDA/IOLayers.cpp:34-96,
+ * CUDA/IOLayers.cu:18-45).  in [n_in, planes], out [n_active, planes]. */
+SCN_API int scn_input_layer_forward(scn_metadata *m, const float *in, float *out, int64_t planes, void *stream);
+/* out[point] = in[site of point].  Replaces cuda_OutputLayer_updateOutput / InputLayer_bp_
+ * (CUDA/IOLayers.cpp:123-145, CUDA/IOLayers.cu:48-76).  in [n_active, planes], out [n_in, planes]. */
+SCN_API int scn_output_layer_forward(scn_metadata *m, const float *in, float *out, int64_t planes, void *stream);
+/* Number of input points of the last scn_input_layer_build (rules[0][2], IOLayersRules.h:11-16). */
+SCN_API int64_t scn_input_layer_n_points(scn_metadata *m);
+/* The InputLayer rulebook in the reference's padded layout (CUDA/IOLayers.cu:7-12):
+ * header HOST int32[4] = {mode, maxActive, nIn, nOut}; rows HOST int32 [nOut, 1+maxActive]
+ * = {count, point indices ascending..., zero padding}.  Call with rows == NULL to get the header. */
+SCN_API int scn_input_layer_rules(scn_metadata *m, int32_t header_host[4], int32_t *rows_host, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Rulebooks (sorted rule pairs), for inspection and parity checks.
+ * ------------------------------------------------------------------------- */
+/* Submanifold 3x3x3 rulebook of a scale.  Replaces Metadata::getSubmanifoldRuleBook ->
+ * SubmanifoldBuildObject (Metadata/Metadata.cpp:521-541, CUDA/SubmanifoldRules_cuda.cpp:38-228).
+ * counts_host: HOST int64[27] pairs per offset.  pairs_host (may be NULL): HOST int32
+ * [sum(counts), 2] rows (input_row, output_row), offsets concatenated in order, each offset
+ * ascending in output_row. */
+SCN_API int scn_ssc_rulebook(scn_metadata *m, const int64_t size[3], int64_t counts_host[27], int32_t *pairs_host,
+                     void *stream);
+/* Size-2 stride-2 rulebook between in_size and out_size = in_size/2, building the coarse grid
+ * when needed.  Replaces Metadata::getRuleBook -> Convolution_InputSgToRulesAndOutputSg_FastDownSampleMode
+ * (Metadata/Metadata.cpp:669-697, Metadata/ConvolutionRules.h:344-380).  counts_host: HOST int64[8];
+ * pairs_host (may be NULL): HOST int32 [n_fine, 2] rows (fine_row, coarse_row), each offset ascending
+ * in fine_row. */
+SCN_API int scn_conv_rulebook(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3],
+                      int64_t counts_host[8], int32_t *pairs_host, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Feature ops.  *flops receives the multiply-add count the reference returns
+ * (pairs * n_in * n_out); may be NULL.
+ * ------------------------------------------------------------------------- */
+/* Replaces cuda_SubmanifoldConvolution_updateOutput (CUDA/Convolution.cpp:152-218).
+ * in [n, n_in], out [n, n_out] over the sites of `size`. */
+SCN_API int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
+                    int64_t out_stride, const float *weight, const float *bias, int64_t n_in, int64_t n_out,
+                    int precision, void *stream, double *flops);
+/* Makes sure the coarse grid and rulebook for in_size -> out_size exist and returns the coarse site
+ * count (callers size the output with it).  Part of Metadata::getRuleBook (Metadata/Metadata.cpp:669-697). */
+SCN_API int scn_conv_prepare(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], void *stream,
+                     int64_t *n_active_out);
+/* Replaces cuda_Convolution_updateOutput (CUDA/Convolution.cpp:51-81); filter 2, stride 2. */
+SCN_API int scn_conv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
+                     int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
+                     int64_t n_in, int64_t n_out, int precision, void *stream, double *flops);
+/* Replaces cuda_Deconvolution_updateOutput (CUDA/Deconvolution.cpp:28-58): in lives on the coarse
+ * scale in_size, out on the fine scale out_size = 2*in_size. */
+SCN_API int scn_deconv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
+                       int64_t in_stride, float *out, int64_t out_stride, const float *weight,
+                       const float *bias, int64_t n_in, int64_t n_out, int precision, void *stream,
+                       double *flops);
+/* y = leaky(x * gamma/sqrt(var+eps) + beta - mean*gamma/sqrt(var+eps)); gamma/beta may be NULL.
+ * Replaces cuda_BatchNormalization_updateOutput, test mode (CUDA/BatchNormalization.cpp:39-61,
+ * CUDA/BatchNormalization.cu:78-107). */
+SCN_API int scn_bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
+                   int64_t planes, const float *running_mean, const float *running_var, const float *gamma,
+                   const float *beta, double eps, double leakiness, void *stream);
+/* out = in * weight (+ bias), weight [n_in, n_out].  Replaces cuda_NetworkInNetwork_updateOutput
+ * (CUDA/NetworkInNetwork.cpp:9-25). */
+SCN_API int scn_nin_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
+                    const float *weight, const float *bias, int64_t n_in, int64_t n_out, int precision,
+                    void *stream, double *flops);
+
+/* ---------------------------------------------------------------------------
+ * Incremental ("Incre_*") path.  `m` holds only the sites touched by the new
+ * points of this frame; `pre` is the metadata of the last full frame and the
+ * pre_* matrices are the features saved on that frame.
+ * ------------------------------------------------------------------------- */
+/* pre_exist[row of m] = row in pre or -1, cached per scale.  Replaces Metadata::getPreExistMaps
+ * (Metadata/Metadata.cpp:609-626).  *map receives a device pointer owned by m. */
+SCN_API int scn_incre_pre_exist(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const int32_t **map,
+                        int64_t *n, void *stream);
+/* Residual of the voxel means after merging the new points into the saved frame.  Replaces
+ * cuda_Incre_InputLayer_updateOutput / InputLayer_inc_fp_ (CUDA/IOLayers.cpp:290-337,
+ * CUDA/IOLayers.cu:82-106).  Call scn_input_layer_build(m, ...) first. */
+SCN_API int scn_incre_input_layer_forward(scn_metadata *m, scn_metadata *pre, const float *in, float *out,
+                                  const float *pre_out, int64_t planes, void *stream);
+/* out[point] = in[site] + pre_in[pre site] when the site existed.  Replaces
+ * cuda_Incre_OutputLayer_updateOutput / InputLayer_inc_bp_ (CUDA/IOLayers.cpp:339-368,
+ * CUDA/IOLayers.cu:123-142). */
+SCN_API int scn_incre_output_layer_forward(scn_metadata *m, scn_metadata *pre, const float *in, float *out,
+                                   const float *pre_in, int64_t planes, void *stream);
+/* Replaces cuda_Incre_SubmanifoldConvolution_updateOutput (CUDA/Convolution.cpp:221-303): the
+ * submanifold convolution of the residual over m, plus, for sites of m absent from pre, the saved
+ * features of their neighbours in pre (IncreSubmanifoldBuildObject, CUDA/SubmanifoldRules_cuda.cpp:233-472). */
+SCN_API int scn_incre_ssc_forward(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const float *in,
+                          int64_t in_stride, float *out, int64_t out_stride, const float *weight,
+                          const float *bias, const float *pre_in, int64_t pre_in_stride, int64_t n_in,
+                          int64_t n_out, int precision, void *stream, double *flops);
+/* The rule pairs (pre_row_of_neighbour, row_in_m) of the second term above, in the layout of
+ * scn_ssc_rulebook.  Replaces Metadata::getIncreSubmanifoldRuleBook (Metadata/Metadata.cpp:543-565). */
+SCN_API int scn_incre_ssc_rulebook(scn_metadata *m, scn_metadata *pre, const int64_t size[3], int64_t counts_host[27],
+                           int32_t *pairs_host, void *stream);
+/* Replaces cuda_Incre_Deconvolution_updateOutput (CUDA/Deconvolution.cpp:61-96,
+ * CUDA/Deconvolution.cu:82-155): input row = residual (+ saved row when the coarse site existed
+ * and the fine output site is new). */
+SCN_API int scn_incre_deconv_forward(scn_metadata *m, scn_metadata *pre, const int64_t in_size[3],
+                             const int64_t out_size[3], const float *in, int64_t in_stride, float *out,
+                             int64_t out_stride, const float *weight, const float *bias, const float *pre_in,
+                             int64_t pre_in_stride, int64_t n_in, int64_t n_out, int precision, void *stream,
+                             double *flops);
+/* Existing site: y = leaky(w*(x + pre_in) + b) - pre_out; new site: plain BN.  Replaces
+ * cuda_Incre_BatchNormalization_updateOutput (CUDA/BatchNormalization.cpp:63-91,
+ * CUDA/BatchNormalization.cu:112-150). */
+SCN_API int scn_incre_bn_forward(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const float *in,
+                         int64_t in_stride, float *out, int64_t out_stride, int64_t planes,
+                         const float *running_mean, const float *running_var, const float *gamma,
+                         const float *beta, double eps, double leakiness, const float *pre_out,
+                         const float *pre_in, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INSCONV_B200_H_ */

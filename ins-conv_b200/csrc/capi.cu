@@ -1,0 +1,515 @@
+// C ABI (include/insconv_b200.h) and the Metadata object behind it: per-scale grids, cached
+// rulebook maps and pre-exist maps.  Host orchestration only; kernels live in grid_build.cu,
+// feature_ops.cu and gather_gemm_tc.cu.
+//
+// Mirrors the roles of the reference's Metadata<3> (sparseconvnet/SCN/Metadata/Metadata.h:218-386,
+// Metadata.cpp:442-463, 521-626, 669-697, 793-821) and of the cuda_* host functions in
+// sparseconvnet/SCN/CUDA/{Convolution,Deconvolution,BatchNormalization,IOLayers,NetworkInNetwork}.cpp.
+#include "internal.h"
+#include <array>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <vector>
+#include <string.h>
+
+namespace scn {
+
+// ---- errors -----------------------------------------------------------------------------------
+static thread_local std::string t_error;
+void set_error(const std::string &msg) { t_error = msg; }
+int fail(int code, const std::string &msg) {
+  t_error = msg;
+  return code;
+}
+std::atomic<uint64_t> g_launches{0};
+
+// ---- device memory ----------------------------------------------------------------------------
+// cudaMallocAsync on the device's default pool; the pool keeps freed blocks (release threshold
+// raised once per device) so steady-state frames do not reach the driver allocator.
+static std::mutex g_pool_mutex;
+static bool g_pool_ready[64] = {false};
+int dev_alloc(void **p, size_t bytes, cudaStream_t s) {
+  *p = nullptr;
+  if (bytes == 0) bytes = 16;
+  int dev = 0;
+  SCN_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !g_pool_ready[dev]) {
+    std::lock_guard<std::mutex> lock(g_pool_mutex);
+    if (!g_pool_ready[dev]) {
+      cudaMemPool_t pool;
+      SCN_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+      uint64_t keep = ~0ull;
+      SCN_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+      g_pool_ready[dev] = true;
+    }
+  }
+  SCN_CUDA(cudaMallocAsync(p, bytes, s));
+  return SCN_OK;
+}
+void dev_free(void *p, cudaStream_t s) {
+  if (p) cudaFreeAsync(p, s);
+}
+
+// ---- metadata ---------------------------------------------------------------------------------
+typedef std::array<int64_t, 3> Size3;
+static Size3 to_size(const int64_t *p) { return Size3{p[0], p[1], p[2]}; }
+
+struct IncreMaps {  // per scale, relative to one saved metadata
+  const void *pre = nullptr;
+  int32_t *pre_exist = nullptr;  // [n]
+  int32_t *nbr2 = nullptr;       // [27][n] rows of pre feeding new sites
+  int64_t nbr2_count[27] = {0};
+  int64_t nbr2_total = 0;
+  int32_t *up2 = nullptr;        // [8][n_fine], stored on the coarse scale
+};
+
+}  // namespace scn
+
+struct scn_metadata {
+  std::map<scn::Size3, std::unique_ptr<scn::Grid>> grids;
+  std::map<scn::Size3, scn::IncreMaps> incre;
+  scn::Size3 input_size{{0, 0, 0}};
+  bool has_input = false;
+  int mode = 0;
+  int64_t batch_size = 0;
+  cudaStream_t last_stream = nullptr;
+
+  scn::Grid *find(const int64_t *size) {
+    auto it = grids.find(scn::to_size(size));
+    return it == grids.end() ? nullptr : it->second.get();
+  }
+  void clear(cudaStream_t s) {
+    for (auto &kv : grids) scn::grid_free(*kv.second, s);
+    grids.clear();
+    for (auto &kv : incre) {
+      scn::dev_free(kv.second.pre_exist, s);
+      scn::dev_free(kv.second.nbr2, s);
+      scn::dev_free(kv.second.up2, s);
+    }
+    incre.clear();
+    has_input = false;
+  }
+};
+
+namespace scn {
+
+static int need_grid(scn_metadata *m, const int64_t *size, Grid **g) {
+  if (!m || !size) return fail(SCN_E_INVALID, "null metadata or size");
+  *g = m->find(size);
+  if (!*g) {
+    char buf[128];
+    snprintf(buf, sizeof buf, "metadata has no grid at spatial size (%lld,%lld,%lld)", (long long)size[0],
+             (long long)size[1], (long long)size[2]);
+    return fail(SCN_E_STATE, buf);
+  }
+  return SCN_OK;
+}
+
+// coarse grid of in_size -> out_size (filter 2, stride 2), built on first use
+static int need_coarse(scn_metadata *m, const int64_t *in_size, const int64_t *out_size, Grid **fine, Grid **coarse,
+                       cudaStream_t s) {
+  SCN_TRY(need_grid(m, in_size, fine));
+  for (int d = 0; d < 3; ++d)
+    if (out_size[d] * 2 != in_size[d])
+      return fail(SCN_E_UNSUPPORTED, "only filter size 2 / stride 2 convolutions are supported (input = 2 * output)");
+  *coarse = m->find(out_size);
+  if (!*coarse) {
+    std::unique_ptr<Grid> g(new Grid());
+    SCN_TRY(grid_build(*g, nullptr, 0, (*fine)->coords, 1, (*fine)->n, false, s));
+    *coarse = g.get();
+    m->grids[to_size(out_size)] = std::move(g);
+  }
+  if ((*coarse)->n_src != (*fine)->n) return fail(SCN_E_STATE, "coarse grid was not built from this fine grid");
+  SCN_TRY(grid_build_conv(**coarse, **fine, s));
+  return SCN_OK;
+}
+
+static int need_incre(scn_metadata *m, scn_metadata *pre, const int64_t *size, Grid **g, Grid **pg, IncreMaps **im,
+                      cudaStream_t s) {
+  if (!pre) return fail(SCN_E_INVALID, "null saved metadata");
+  SCN_TRY(need_grid(m, size, g));
+  SCN_TRY(need_grid(pre, size, pg));
+  IncreMaps &x = m->incre[to_size(size)];
+  if (x.pre != pre || !x.pre_exist) {
+    dev_free(x.pre_exist, s);
+    dev_free(x.nbr2, s);
+    dev_free(x.up2, s);
+    x = IncreMaps();
+    x.pre = pre;
+    SCN_TRY(dev_alloc_t(&x.pre_exist, (size_t)(*g)->n, s));
+    SCN_TRY(grid_query(**pg, (*g)->coords, (*g)->n, (*g)->n, x.pre_exist, s));
+  }
+  *im = &x;
+  return SCN_OK;
+}
+
+static int check_feat(const void *in, const void *out, const void *w, int64_t n_in, int64_t n_out) {
+  if (!in || !out || !w) return fail(SCN_E_INVALID, "null feature or weight pointer");
+  if (n_in <= 0 || n_out <= 0) return fail(SCN_E_INVALID, "plane counts must be positive");
+  return SCN_OK;
+}
+
+}  // namespace scn
+
+using namespace scn;
+
+extern "C" {
+
+const char *scn_last_error(void) { return t_error.c_str(); }
+const char *scn_version(void) { return "insconv_b200 0.1 (sm_100a)"; }
+uint64_t scn_launch_count(void) { return g_launches.load(); }
+int scn_n_rulebook_bits(void) { return 32; }
+
+int scn_metadata_create(scn_metadata **out) {
+  if (!out) return fail(SCN_E_INVALID, "null output pointer");
+  *out = new scn_metadata();
+  return SCN_OK;
+}
+void scn_metadata_destroy(scn_metadata *m) {
+  if (!m) return;
+  m->clear(m->last_stream);
+  delete m;
+}
+int scn_metadata_clear(scn_metadata *m, void *stream) {
+  if (!m) return fail(SCN_E_INVALID, "null metadata");
+  m->clear((cudaStream_t)stream);
+  return SCN_OK;
+}
+int64_t scn_metadata_n_active(scn_metadata *m, const int64_t size[3]) {
+  if (!m || !size) return -1;
+  Grid *g = m->find(size);
+  return g ? g->n : -1;
+}
+int scn_metadata_spatial_locations(scn_metadata *m, const int64_t size[3], int64_t *out_host, void *stream) {
+  Grid *g;
+  SCN_TRY(need_grid(m, size, &g));
+  if (!out_host && g->n) return fail(SCN_E_INVALID, "null output");
+  return grid_locations(*g, out_host, (cudaStream_t)stream);
+}
+int scn_metadata_site_coords(scn_metadata *m, const int64_t size[3], const int32_t **coords, int64_t *n) {
+  Grid *g;
+  SCN_TRY(need_grid(m, size, &g));
+  if (coords) *coords = g->coords;
+  if (n) *n = g->n;
+  return SCN_OK;
+}
+int scn_metadata_hash_dump(scn_metadata *m, const int64_t size[3], uint64_t *keys_host, int32_t *rows_host,
+                           int64_t *capacity, void *stream) {
+  Grid *g;
+  SCN_TRY(need_grid(m, size, &g));
+  const int64_t cap = g->table ? (int64_t)g->mask + 1 : 0;
+  if (capacity) *capacity = cap;
+  if (!keys_host || !rows_host || cap == 0) return SCN_OK;
+  std::vector<Slot> h((size_t)cap);
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_CUDA(cudaMemcpyAsync(h.data(), g->table, (size_t)cap * sizeof(Slot), cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  for (int64_t i = 0; i < cap; ++i) {
+    keys_host[i] = h[i].key;
+    rows_host[i] = h[i].key == kEmptyKey ? -1 : h[i].row;
+  }
+  return SCN_OK;
+}
+int scn_metadata_query(scn_metadata *m, const int64_t size[3], const int32_t *coords_soa, int64_t n, int32_t *rows,
+                       void *stream) {
+  Grid *g;
+  SCN_TRY(need_grid(m, size, &g));
+  if (n < 0 || (n && (!coords_soa || !rows))) return fail(SCN_E_INVALID, "bad query arguments");
+  return grid_query(*g, coords_soa, n, n, rows, (cudaStream_t)stream);
+}
+
+// ---- input / output layer ----------------------------------------------------------------------
+int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t *coords, int coords_on_host,
+                          int64_t n_in, int ncols, int64_t batch_size, int mode, void *stream, int64_t *n_active) {
+  if (!m || !size) return fail(SCN_E_INVALID, "null metadata or size");
+  if (mode != 3 && mode != 4) return fail(SCN_E_UNSUPPORTED, "InputLayer mode must be 3 (sum) or 4 (mean)");
+  if (ncols != 3 && ncols != 4) return fail(SCN_E_INVALID, "coords must have 3 or 4 columns");
+  if (n_in < 0 || (n_in && !coords)) return fail(SCN_E_INVALID, "bad coords");
+  cudaStream_t s = (cudaStream_t)stream;
+  m->last_stream = s;
+  m->clear(s);
+  std::unique_ptr<Grid> g(new Grid());
+  const int64_t *dev_coords = coords;
+  int64_t *staged = nullptr;
+  if (coords_on_host && n_in) {
+    SCN_TRY(dev_alloc_t(&staged, (size_t)n_in * ncols, s));
+    SCN_CUDA(cudaMemcpyAsync(staged, coords, (size_t)n_in * ncols * 8, cudaMemcpyHostToDevice, s));
+    dev_coords = staged;
+  }
+  int r = grid_build(*g, dev_coords, ncols, nullptr, 0, n_in, true, s);
+  dev_free(staged, s);
+  if (r != SCN_OK) {
+    grid_free(*g, s);
+    return r;
+  }
+  if (n_active) *n_active = g->n;
+  m->grids[to_size(size)] = std::move(g);
+  m->input_size = to_size(size);
+  m->has_input = true;
+  m->mode = mode;
+  m->batch_size = batch_size;
+  return SCN_OK;
+}
+
+static int input_grid(scn_metadata *m, Grid **g) {
+  if (!m || !m->has_input) return fail(SCN_E_STATE, "metadata has no input layer");
+  *g = m->find(m->input_size.data());
+  return *g ? SCN_OK : fail(SCN_E_STATE, "metadata has no input layer");
+}
+
+int scn_input_layer_forward(scn_metadata *m, const float *in, float *out, int64_t planes, void *stream) {
+  Grid *g;
+  SCN_TRY(input_grid(m, &g));
+  if (g->n && (!in || !out)) return fail(SCN_E_INVALID, "null features");
+  return input_forward(*g, in, out, planes, m->mode == 4, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+}
+int scn_output_layer_forward(scn_metadata *m, const float *in, float *out, int64_t planes, void *stream) {
+  Grid *g;
+  SCN_TRY(input_grid(m, &g));
+  if (g->n && (!in || !out)) return fail(SCN_E_INVALID, "null features");
+  return output_forward(*g, in, out, planes, nullptr, nullptr, (cudaStream_t)stream);
+}
+int64_t scn_input_layer_n_points(scn_metadata *m) {
+  Grid *g;
+  if (input_grid(m, &g) != SCN_OK) return -1;
+  return g->n_src;
+}
+int scn_input_layer_rules(scn_metadata *m, int32_t header_host[4], int32_t *rows_host, void *stream) {
+  Grid *g;
+  SCN_TRY(input_grid(m, &g));
+  cudaStream_t s = (cudaStream_t)stream;
+  const int32_t max_active = g->n ? g->max_active : 0;
+  if (header_host) {
+    header_host[0] = m->mode;
+    header_host[1] = max_active;
+    header_host[2] = (int32_t)g->n_src;
+    header_host[3] = (int32_t)g->n;
+  }
+  if (!rows_host || g->n == 0) return SCN_OK;
+  std::vector<int32_t> off((size_t)g->n + 1), item((size_t)g->n_src);
+  if (g->csr_off) {
+    SCN_CUDA(cudaMemcpyAsync(off.data(), g->csr_off, off.size() * 4, cudaMemcpyDeviceToHost, s));
+  } else {
+    for (size_t i = 0; i < off.size(); ++i) off[i] = (int32_t)i;
+  }
+  SCN_CUDA(cudaMemcpyAsync(item.data(), g->csr_item, item.size() * 4, cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  const int64_t w = 1 + max_active;
+  memset(rows_host, 0, (size_t)(g->n * w) * 4);
+  for (int64_t r = 0; r < g->n; ++r) {
+    int32_t *row = rows_host + r * w;
+    row[0] = off[r + 1] - off[r];
+    for (int32_t j = off[r]; j < off[r + 1]; ++j) row[1 + j - off[r]] = item[j];
+  }
+  return SCN_OK;
+}
+
+// ---- rulebooks ---------------------------------------------------------------------------------
+int scn_ssc_rulebook(scn_metadata *m, const int64_t size[3], int64_t counts_host[27], int32_t *pairs_host,
+                     void *stream) {
+  Grid *g;
+  SCN_TRY(need_grid(m, size, &g));
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(grid_build_ssc(*g, s));
+  if (counts_host)
+    for (int k = 0; k < 27; ++k) counts_host[k] = g->nbr_count[k];
+  if (pairs_host) SCN_TRY(map_to_pairs(g->nbr, 27, g->n, 0, g->nbr_total, pairs_host, s));
+  return SCN_OK;
+}
+int scn_conv_rulebook(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], int64_t counts_host[8],
+                      int32_t *pairs_host, void *stream) {
+  Grid *fine, *coarse;
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(need_coarse(m, in_size, out_size, &fine, &coarse, s));
+  if (counts_host)
+    for (int k = 0; k < 8; ++k) counts_host[k] = coarse->child_count[k];
+  // fine_up[k][f] = coarse row: pair (fine, coarse), ascending fine inside an offset
+  if (pairs_host) SCN_TRY(map_to_pairs(coarse->fine_up, 8, fine->n, 1, fine->n, pairs_host, s));
+  return SCN_OK;
+}
+
+// ---- feature ops -------------------------------------------------------------------------------
+int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
+                    int64_t out_stride, const float *weight, const float *bias, int64_t n_in, int64_t n_out,
+                    int precision, void *stream, double *flops) {
+  Grid *g;
+  SCN_TRY(need_grid(m, size, &g));
+  if (flops) *flops = 0;
+  if (g->n == 0) return SCN_OK;
+  SCN_TRY(check_feat(in, out, weight, n_in, n_out));
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(grid_build_ssc(*g, s));
+  SCN_TRY(gather_gemm(in, in_stride, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, 0, precision, s));
+  if (flops) *flops = (double)g->nbr_total * (double)n_in * (double)n_out;
+  return SCN_OK;
+}
+int scn_conv_prepare(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], void *stream,
+                     int64_t *n_active_out) {
+  Grid *fine, *coarse;
+  SCN_TRY(need_coarse(m, in_size, out_size, &fine, &coarse, (cudaStream_t)stream));
+  if (n_active_out) *n_active_out = coarse->n;
+  return SCN_OK;
+}
+int scn_conv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
+                     int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
+                     int64_t n_in, int64_t n_out, int precision, void *stream, double *flops) {
+  Grid *fine, *coarse;
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(need_coarse(m, in_size, out_size, &fine, &coarse, s));
+  if (flops) *flops = 0;
+  if (coarse->n == 0) return SCN_OK;
+  SCN_TRY(check_feat(in, out, weight, n_in, n_out));
+  SCN_TRY(gather_gemm(in, in_stride, coarse->child, 8, coarse->n, weight, bias, out, out_stride, n_in, n_out, 0,
+                      precision, s));
+  if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
+  return SCN_OK;
+}
+int scn_deconv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
+                       int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
+                       int64_t n_in, int64_t n_out, int precision, void *stream, double *flops) {
+  Grid *fine, *coarse;
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(need_coarse(m, out_size, in_size, &fine, &coarse, s));
+  if (flops) *flops = 0;
+  if (fine->n == 0) return SCN_OK;
+  SCN_TRY(check_feat(in, out, weight, n_in, n_out));
+  SCN_TRY(gather_gemm(in, in_stride, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, 0,
+                      precision, s));
+  if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
+  return SCN_OK;
+}
+int scn_bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,
+                   const float *running_mean, const float *running_var, const float *gamma, const float *beta,
+                   double eps, double leakiness, void *stream) {
+  if (rows < 0 || planes < 0) return fail(SCN_E_INVALID, "negative size");
+  if (rows && planes && (!in || !out || !running_mean || !running_var)) return fail(SCN_E_INVALID, "null pointer");
+  return bn_forward(in, in_stride, out, out_stride, rows, planes, running_mean, running_var, gamma, beta, (float)eps,
+                    (float)leakiness, nullptr, nullptr, nullptr, (cudaStream_t)stream);
+}
+int scn_nin_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
+                    const float *weight, const float *bias, int64_t n_in, int64_t n_out, int precision, void *stream,
+                    double *flops) {
+  if (flops) *flops = (double)rows * (double)n_in * (double)n_out;
+  if (rows == 0) return SCN_OK;
+  SCN_TRY(check_feat(in, out, weight, n_in, n_out));
+  return gather_gemm(in, in_stride, nullptr, 1, rows, weight, bias, out, out_stride, n_in, n_out, 0, precision,
+                     (cudaStream_t)stream);
+}
+
+// ---- incremental path --------------------------------------------------------------------------
+int scn_incre_pre_exist(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const int32_t **map, int64_t *n,
+                        void *stream) {
+  Grid *g, *pg;
+  IncreMaps *im;
+  SCN_TRY(need_incre(m, pre, size, &g, &pg, &im, (cudaStream_t)stream));
+  if (map) *map = im->pre_exist;
+  if (n) *n = g->n;
+  return SCN_OK;
+}
+int scn_incre_input_layer_forward(scn_metadata *m, scn_metadata *pre, const float *in, float *out,
+                                  const float *pre_out, int64_t planes, void *stream) {
+  Grid *g0;
+  SCN_TRY(input_grid(m, &g0));
+  Grid *g, *pg;
+  IncreMaps *im;
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(need_incre(m, pre, m->input_size.data(), &g, &pg, &im, s));
+  if (g->n && (!in || !out || !pre_out)) return fail(SCN_E_INVALID, "null features");
+  return input_forward(*g, in, out, planes, m->mode == 4, im->pre_exist, pg, pre_out, s);
+}
+int scn_incre_output_layer_forward(scn_metadata *m, scn_metadata *pre, const float *in, float *out,
+                                   const float *pre_in, int64_t planes, void *stream) {
+  Grid *g0;
+  SCN_TRY(input_grid(m, &g0));
+  Grid *g, *pg;
+  IncreMaps *im;
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(need_incre(m, pre, m->input_size.data(), &g, &pg, &im, s));
+  if (g->n && (!in || !out || !pre_in)) return fail(SCN_E_INVALID, "null features");
+  return output_forward(*g, in, out, planes, im->pre_exist, pre_in, s);
+}
+
+static int need_nbr2(Grid *g, Grid *pg, IncreMaps *im, cudaStream_t s) {
+  if (im->nbr2 || g->n == 0) return SCN_OK;
+  SCN_TRY(dev_alloc_t(&im->nbr2, (size_t)g->n * 27, s));
+  SCN_TRY(build_incre_nbr(*g, *pg, im->pre_exist, im->nbr2, im->nbr2_count, s));
+  im->nbr2_total = 0;
+  for (int k = 0; k < 27; ++k) im->nbr2_total += im->nbr2_count[k];
+  return SCN_OK;
+}
+
+int scn_incre_ssc_forward(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const float *in,
+                          int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
+                          const float *pre_in, int64_t pre_in_stride, int64_t n_in, int64_t n_out, int precision,
+                          void *stream, double *flops) {
+  Grid *g, *pg;
+  IncreMaps *im;
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(need_incre(m, pre, size, &g, &pg, &im, s));
+  if (flops) *flops = 0;
+  if (g->n == 0) return SCN_OK;
+  SCN_TRY(check_feat(in, out, weight, n_in, n_out));
+  if (!pre_in) return fail(SCN_E_INVALID, "null saved features");
+  SCN_TRY(grid_build_ssc(*g, s));
+  SCN_TRY(need_nbr2(g, pg, im, s));
+  SCN_TRY(gather_gemm(in, in_stride, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, 0, precision, s));
+  if (im->nbr2_total)
+    SCN_TRY(gather_gemm(pre_in, pre_in_stride, im->nbr2, 27, g->n, weight, nullptr, out, out_stride, n_in, n_out, 1,
+                        precision, s));
+  if (flops) *flops = (double)(g->nbr_total + im->nbr2_total) * (double)n_in * (double)n_out;
+  return SCN_OK;
+}
+int scn_incre_ssc_rulebook(scn_metadata *m, scn_metadata *pre, const int64_t size[3], int64_t counts_host[27],
+                           int32_t *pairs_host, void *stream) {
+  Grid *g, *pg;
+  IncreMaps *im;
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(need_incre(m, pre, size, &g, &pg, &im, s));
+  SCN_TRY(need_nbr2(g, pg, im, s));
+  if (counts_host)
+    for (int k = 0; k < 27; ++k) counts_host[k] = im->nbr2_count[k];
+  if (pairs_host && g->n) SCN_TRY(map_to_pairs(im->nbr2, 27, g->n, 0, im->nbr2_total, pairs_host, s));
+  return SCN_OK;
+}
+int scn_incre_deconv_forward(scn_metadata *m, scn_metadata *pre, const int64_t in_size[3], const int64_t out_size[3],
+                             const float *in, int64_t in_stride, float *out, int64_t out_stride, const float *weight,
+                             const float *bias, const float *pre_in, int64_t pre_in_stride, int64_t n_in,
+                             int64_t n_out, int precision, void *stream, double *flops) {
+  Grid *fine, *coarse;
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(need_coarse(m, out_size, in_size, &fine, &coarse, s));
+  if (flops) *flops = 0;
+  if (fine->n == 0) return SCN_OK;
+  SCN_TRY(check_feat(in, out, weight, n_in, n_out));
+  if (!pre_in) return fail(SCN_E_INVALID, "null saved features");
+  Grid *g1, *pg1, *g2, *pg2;
+  IncreMaps *im_c, *im_f;
+  SCN_TRY(need_incre(m, pre, in_size, &g1, &pg1, &im_c, s));
+  SCN_TRY(need_incre(m, pre, out_size, &g2, &pg2, &im_f, s));
+  if (!im_c->up2) {
+    SCN_TRY(dev_alloc_t(&im_c->up2, (size_t)fine->n * 8, s));
+    SCN_TRY(build_incre_up(*coarse, im_c->pre_exist, im_f->pre_exist, im_c->up2, s));
+  }
+  SCN_TRY(gather_gemm(in, in_stride, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, 0,
+                      precision, s));
+  SCN_TRY(gather_gemm(pre_in, pre_in_stride, im_c->up2, 8, fine->n, weight, nullptr, out, out_stride, n_in, n_out, 1,
+                      precision, s));
+  if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
+  return SCN_OK;
+}
+int scn_incre_bn_forward(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const float *in, int64_t in_stride,
+                         float *out, int64_t out_stride, int64_t planes, const float *running_mean,
+                         const float *running_var, const float *gamma, const float *beta, double eps,
+                         double leakiness, const float *pre_out, const float *pre_in, void *stream) {
+  Grid *g, *pg;
+  IncreMaps *im;
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(need_incre(m, pre, size, &g, &pg, &im, s));
+  if (g->n == 0) return SCN_OK;
+  if (!in || !out || !running_mean || !running_var || !pre_out || !pre_in) return fail(SCN_E_INVALID, "null pointer");
+  return bn_forward(in, in_stride, out, out_stride, g->n, planes, running_mean, running_var, gamma, beta, (float)eps,
+                    (float)leakiness, im->pre_exist, pre_out, pre_in, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,317 @@
+// Feature kernels: output-stationary gather-GEMM (fp32 FFMA path), BatchNorm + leaky ReLU,
+// InputLayer / OutputLayer reductions, and their incremental variants.
+//
+// Every convolution of the hot path is one launch of the same kernel:
+//     out[o] = init(o) + sum_k  in[ map[k][o] ] * W[k]
+// with map = the 27-offset neighbour map (submanifold), the 8-slot child map (stride-2
+// convolution), the 8-slot parent map (deconvolution) or no map at all (1x1 NetworkInNetwork).
+// A CTA owns a tile of consecutive output rows, loops over the offsets and channel chunks, and
+// writes each output row exactly once: no atomics, no read-modify-write of the output, and the
+// summation order is fixed, so results are deterministic.  Consecutive rows are consecutive in key
+// order (x fastest), so the rows a tile gathers overlap heavily and are served from L2.
+//
+// Reference arithmetic restated here (paths relative to sparseconvnet/SCN/):
+//   conv / deconv           CPU/Convolution.cpp:36-72, CPU/Deconvolution.cpp:8-44, CUDA/Convolution.cu:81-223
+//   BatchNorm test mode     CUDA/BatchNormalization.cu:78-107, incremental :112-150
+//   Input / Output layer    CUDA/IOLayers.cu:18-62, incremental :82-142
+//   NetworkInNetwork        CUDA/NetworkInNetwork.cpp:9-25
+#include "internal.h"
+
+namespace scn {
+
+static inline unsigned blocks_for(long long n, int t) { return (unsigned)((n + t - 1) / t); }
+static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// ---------------------------------------------------------------------------------------------
+// gather-GEMM, fp32
+// ---------------------------------------------------------------------------------------------
+constexpr int kBK = 16;  // input channels staged per step
+
+template <int TM, int TN, int RM, int RN>
+__global__ void __launch_bounds__((TM / RM) * (TN / RN))
+k_gather_gemm_f32(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K,
+                  long long n_out, const float *__restrict__ W, const float *__restrict__ bias,
+                  float *__restrict__ out, long long out_stride, int Cin, int Cout, int accumulate, int vecA,
+                  int vecB) {
+  constexpr int NT = (TM / RM) * (TN / RN);
+  constexpr int CG = TN / RN;  // threads along the output channels
+  static_assert(RM % 4 == 0 && RN == 4, "register tile is read as float4");
+  __shared__ __align__(16) float As[kBK][TM + 4];
+  __shared__ __align__(16) float Bs[kBK][TN];
+  __shared__ int s_idx[TM];
+  const int tid = threadIdx.x, tx = tid % CG, ty = tid / CG;
+  const long long row0 = (long long)blockIdx.x * TM;
+  const int n0 = blockIdx.y * TN;
+  float acc[RM][RN];
+#pragma unroll
+  for (int i = 0; i < RM; ++i)
+#pragma unroll
+    for (int j = 0; j < RN; ++j) acc[i][j] = 0.f;
+
+  for (int k = 0; k < K; ++k) {
+    int any_local = 0;
+    for (int r = tid; r < TM; r += NT) {
+      const long long row = row0 + r;
+      int v = -1;
+      if (row < n_out) v = map ? __ldg(map + (long long)k * n_out + row) : (int)row;
+      s_idx[r] = v;
+      any_local |= (v >= 0);
+    }
+    if (!__syncthreads_or(any_local)) continue;  // no row of this tile has a neighbour at offset k
+    const float *Wk = W + (long long)k * Cin * Cout;
+    for (int c0 = 0; c0 < Cin; c0 += kBK) {
+      // gathered rows, transposed to channel-major in shared memory
+      for (int idx = tid; idx < TM * (kBK / 4); idx += NT) {
+        const int r = idx / (kBK / 4), ch = idx % (kBK / 4);
+        const int src = s_idx[r];
+        const int c = c0 + ch * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (src >= 0 && c < Cin) {
+          const float *p = in + (long long)src * in_stride + c;
+          if (vecA && c + 3 < Cin) {
+            v = __ldg(reinterpret_cast<const float4 *>(p));
+          } else {
+            v.x = __ldg(p);
+            if (c + 1 < Cin) v.y = __ldg(p + 1);
+            if (c + 2 < Cin) v.z = __ldg(p + 2);
+            if (c + 3 < Cin) v.w = __ldg(p + 3);
+          }
+        }
+        As[ch * 4 + 0][r] = v.x;
+        As[ch * 4 + 1][r] = v.y;
+        As[ch * 4 + 2][r] = v.z;
+        As[ch * 4 + 3][r] = v.w;
+      }
+      // weight slab chunk [kBK][TN]
+      for (int idx = tid; idx < kBK * (TN / 4); idx += NT) {
+        const int kk = idx / (TN / 4), cn = (idx % (TN / 4)) * 4;
+        const int ci = c0 + kk, co = n0 + cn;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ci < Cin && co < Cout) {
+          const float *p = Wk + (long long)ci * Cout + co;
+          if (vecB && co + 3 < Cout) {
+            v = __ldg(reinterpret_cast<const float4 *>(p));
+          } else {
+            v.x = __ldg(p);
+            if (co + 1 < Cout) v.y = __ldg(p + 1);
+            if (co + 2 < Cout) v.z = __ldg(p + 2);
+            if (co + 3 < Cout) v.w = __ldg(p + 3);
+          }
+        }
+        *reinterpret_cast<float4 *>(&Bs[kk][cn]) = v;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int kk = 0; kk < kBK; ++kk) {
+        float a[RM];
+#pragma unroll
+        for (int q = 0; q < RM / 4; ++q) {
+          const float4 t = *reinterpret_cast<const float4 *>(&As[kk][ty * RM + q * 4]);
+          a[q * 4 + 0] = t.x; a[q * 4 + 1] = t.y; a[q * 4 + 2] = t.z; a[q * 4 + 3] = t.w;
+        }
+        const float4 b = *reinterpret_cast<const float4 *>(&Bs[kk][tx * RN]);
+#pragma unroll
+        for (int i = 0; i < RM; ++i) {
+          acc[i][0] = fmaf(a[i], b.x, acc[i][0]);
+          acc[i][1] = fmaf(a[i], b.y, acc[i][1]);
+          acc[i][2] = fmaf(a[i], b.z, acc[i][2]);
+          acc[i][3] = fmaf(a[i], b.w, acc[i][3]);
+        }
+      }
+      __syncthreads();
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RM; ++i) {
+    const long long row = row0 + ty * RM + i;
+    if (row >= n_out) continue;
+#pragma unroll
+    for (int j = 0; j < RN; ++j) {
+      const int co = n0 + tx * RN + j;
+      if (co >= Cout) continue;
+      float v = acc[i][j];
+      float *o = out + row * out_stride + co;
+      if (accumulate) v += *o;
+      else if (bias) v += __ldg(bias + co);
+      *o = v;
+    }
+  }
+}
+
+int gather_gemm_tf32(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *W,
+                     const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate,
+                     cudaStream_t s, bool *handled);
+
+int gather_gemm(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *W,
+                const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate,
+                int precision, cudaStream_t s) {
+  if (n_out == 0) return SCN_OK;
+  if (Cin <= 0 || Cout <= 0 || Cin > 65536 || Cout > 65536) return fail(SCN_E_INVALID, "bad plane count");
+  if (precision != SCN_PREC_FP32 && precision != SCN_PREC_TF32) return fail(SCN_E_INVALID, "unknown precision");
+  if (precision == SCN_PREC_TF32) {
+    bool handled = false;
+    SCN_TRY(gather_gemm_tf32(in, in_stride, map, K, n_out, W, bias, out, out_stride, Cin, Cout, accumulate, s,
+                             &handled));
+    if (handled) return SCN_OK;
+    // shapes the tensor-core kernel does not tile (n_in not a multiple of 8, ...) use the fp32 kernel,
+    // which is at least as accurate.
+  }
+  const int vecA = aligned16(in) && (in_stride % 4 == 0);
+  const int vecB = aligned16(W) && (Cout % 4 == 0);
+  if (Cout <= 16) {
+    dim3 grid(blocks_for(n_out, 128), 1);
+    k_gather_gemm_f32<128, 16, 4, 4><<<grid, 128, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
+                                                        (int)Cin, (int)Cout, accumulate, vecA, vecB);
+  } else if (Cout <= 32) {
+    dim3 grid(blocks_for(n_out, 64), 1);
+    k_gather_gemm_f32<64, 32, 4, 4><<<grid, 128, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
+                                                       (int)Cin, (int)Cout, accumulate, vecA, vecB);
+  } else {
+    dim3 grid(blocks_for(n_out, 64), blocks_for(Cout, 64));
+    k_gather_gemm_f32<64, 64, 8, 4><<<grid, 128, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
+                                                       (int)Cin, (int)Cout, accumulate, vecA, vecB);
+  }
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// BatchNorm (running statistics) + leaky ReLU; optional incremental form
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float leaky(float v, float leak) { return v > 0.f ? v : v * leak; }
+
+template <int VEC>
+__global__ void k_bn(const float *__restrict__ in, long long in_stride, float *__restrict__ out, long long out_stride,
+                     long long rows, int C, const float *__restrict__ mean, const float *__restrict__ var,
+                     const float *__restrict__ gamma, const float *__restrict__ beta, float eps, float leak,
+                     const int32_t *__restrict__ pre_exist, const float *__restrict__ pre_out,
+                     const float *__restrict__ pre_in) {
+  extern __shared__ float sm[];  // scale[C], shift[C]
+  float *sw = sm, *sb = sm + C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float w = (1.0f / sqrtf(var[c] + eps)) * (gamma ? gamma[c] : 1.f);
+    sw[c] = w;
+    sb[c] = (beta ? beta[c] : 0.f) - mean[c] * w;
+  }
+  __syncthreads();
+  const int cv = C / VEC;
+  const long long total = rows * cv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / cv;
+    const int c = (int)(i % cv) * VEC;
+    const int pe = pre_exist ? pre_exist[row] : -1;
+    if (VEC == 4) {
+      float4 x = *reinterpret_cast<const float4 *>(in + row * in_stride + c);
+      float4 y;
+      float xs[4] = {x.x, x.y, x.z, x.w}, ys[4];
+      float pi[4] = {0, 0, 0, 0}, po[4] = {0, 0, 0, 0};
+      if (pe >= 0) {
+        float4 a = *reinterpret_cast<const float4 *>(pre_in + (long long)pe * C + c);
+        float4 b = *reinterpret_cast<const float4 *>(pre_out + (long long)pe * C + c);
+        pi[0] = a.x; pi[1] = a.y; pi[2] = a.z; pi[3] = a.w;
+        po[0] = b.x; po[1] = b.y; po[2] = b.z; po[3] = b.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float w = sw[c + j];
+        const float o = w * xs[j] + sb[c + j];
+        ys[j] = (pe >= 0) ? leaky(o + pi[j] * w, leak) - po[j] : leaky(o, leak);
+      }
+      y.x = ys[0]; y.y = ys[1]; y.z = ys[2]; y.w = ys[3];
+      *reinterpret_cast<float4 *>(out + row * out_stride + c) = y;
+    } else {
+      const float w = sw[c];
+      const float o = w * in[row * in_stride + c] + sb[c];
+      float y;
+      if (pe >= 0) y = leaky(o + pre_in[(long long)pe * C + c] * w, leak) - pre_out[(long long)pe * C + c];
+      else y = leaky(o, leak);
+      out[row * out_stride + c] = y;
+    }
+  }
+}
+
+int bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,
+               const float *mean, const float *var, const float *gamma, const float *beta, float eps, float leak,
+               const int32_t *pre_exist, const float *pre_out, const float *pre_in, cudaStream_t s) {
+  if (rows == 0 || planes == 0) return SCN_OK;
+  if (planes > 4096) return fail(SCN_E_INVALID, "BatchNorm over more than 4096 planes");
+  const bool vec = planes % 4 == 0 && in_stride % 4 == 0 && out_stride % 4 == 0 && aligned16(in) && aligned16(out) &&
+                   (!pre_exist || (aligned16(pre_in) && aligned16(pre_out)));
+  const long long work = rows * (vec ? planes / 4 : planes);
+  unsigned blocks = blocks_for(work, 256);
+  if (blocks > 148u * 16u) blocks = 148u * 16u;
+  const size_t smem = (size_t)planes * 2 * sizeof(float);
+  if (vec)
+    k_bn<4><<<blocks, 256, smem, s>>>(in, in_stride, out, out_stride, rows, (int)planes, mean, var, gamma, beta, eps,
+                                     leak, pre_exist, pre_out, pre_in);
+  else
+    k_bn<1><<<blocks, 256, smem, s>>>(in, in_stride, out, out_stride, rows, (int)planes, mean, var, gamma, beta, eps,
+                                     leak, pre_exist, pre_out, pre_in);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// InputLayer / OutputLayer
+// ---------------------------------------------------------------------------------------------
+// One thread per (site, plane).  Points of a site are added in ascending point index, the order of the
+// reference's rule rows.  With pre_exist: residual of the voxel mean against the saved frame.
+__global__ void k_input_fwd(const float *__restrict__ in, float *__restrict__ out, long long n, int planes,
+                            const int32_t *__restrict__ off, const int32_t *__restrict__ item, int average,
+                            const int32_t *__restrict__ pre_exist, const int32_t *__restrict__ pre_off,
+                            const float *__restrict__ pre_out) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n * planes) return;
+  const long long r = i / planes;
+  const int c = (int)(i % planes);
+  const int b = off ? off[r] : (int)r, e = off ? off[r + 1] : (int)r + 1;
+  const int cnt = e - b;
+  int pe = -1, pre_cnt = 0;
+  if (pre_exist) {
+    pe = pre_exist[r];
+    if (pe >= 0) pre_cnt = pre_off ? pre_off[pe + 1] - pre_off[pe] : 1;
+  }
+  const float mult = (average && cnt > 0) ? 1.0f / (float)(cnt + pre_cnt) : 1.0f;
+  float acc = 0.f;
+  for (int j = b; j < e; ++j) acc += mult * in[(long long)item[j] * planes + c];
+  if (pe >= 0) acc = acc + pre_out[(long long)pe * planes + c] * ((float)pre_cnt * mult - 1.0f);
+  out[i] = acc;
+}
+
+__global__ void k_output_fwd(const float *__restrict__ in, float *__restrict__ out, long long n_pts, int planes,
+                             const int32_t *__restrict__ src_row, const int32_t *__restrict__ pre_exist,
+                             const float *__restrict__ pre_in) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pts * planes) return;
+  const long long p = i / planes;
+  const int c = (int)(i % planes);
+  const int r = src_row[p];
+  float v = in[(long long)r * planes + c];
+  if (pre_exist) {
+    const int pe = pre_exist[r];
+    if (pe >= 0) v += pre_in[(long long)pe * planes + c];
+  }
+  out[i] = v;
+}
+
+int input_forward(const Grid &g, const float *in, float *out, int64_t planes, int average, const int32_t *pre_exist,
+                  const Grid *pre, const float *pre_out, cudaStream_t s) {
+  if (g.n == 0 || planes == 0) return SCN_OK;
+  if (!g.csr_item) return fail(SCN_E_STATE, "grid has no input rules");
+  k_input_fwd<<<blocks_for(g.n * planes, 256), 256, 0, s>>>(in, out, g.n, (int)planes, g.csr_off, g.csr_item, average,
+                                                          pre_exist, pre ? pre->csr_off : nullptr, pre_out);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+int output_forward(const Grid &g, const float *in, float *out, int64_t planes, const int32_t *pre_exist,
+                   const float *pre_in, cudaStream_t s) {
+  if (g.n_src == 0 || planes == 0) return SCN_OK;
+  k_output_fwd<<<blocks_for(g.n_src * planes, 256), 256, 0, s>>>(in, out, g.n_src, (int)planes, g.src_row, pre_exist,
+                                                               pre_in);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+}  // namespace scn

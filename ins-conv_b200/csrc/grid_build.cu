@@ -1,0 +1,675 @@
+// Grid (voxel hash) and rulebook construction kernels.
+//
+// A grid is built from source rows (input points, or the sites of the next finer scale) in four
+// device passes, none of which sorts:
+//   1. pack      coordinates -> 64-bit keys, bounding box of the scene          (reads coords once)
+//   2. mark      one bit per occupied cell in a bitmap laid out in key order    (atomicOr, L2 resident)
+//   3. rank      exclusive prefix sum of the bitmap word popcounts
+//   4. assign    row = prefix[word] + popcount(bits below): the rank of the key among the unique
+//                keys, which is the reference's site numbering; the first point to reach a site
+//                writes its coordinates and inserts key -> row into the open-addressing table.
+// The table (linear probing, 16-byte slots, load factor <= 0.5) is what every later lookup uses:
+// neighbour queries of the 3x3x3 rulebook, pre-exist maps and incremental rulebooks.
+//
+// Reference behaviour restated here (paths relative to sparseconvnet/SCN/):
+//   key order / site numbering   CUDA/CUDPPWrapper.cu:72-119, extra/cudpp/src/cudpp_hash/hash_multivalue.cpp:45-110
+//   site coords, point -> site   CUDA/CUDPPWrapper.cu:212-231
+//   input rules                  CUDA/CUDPPWrapper.cu:53-64, Metadata/IOLayersRules.h:135-203
+//   3x3x3 offsets and pairs      CUDA/SubmanifoldRules_cuda.cu:45-114
+//   2x2x2 stride-2 pairs         CUDA/SubmanifoldRules_cuda.cu:744-780, Metadata/ConvolutionRules.h:344-380
+#include "internal.h"
+#include <vector>
+#include <limits.h>
+
+namespace scn {
+
+// ---------------------------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ __forceinline__ unsigned long long pack_key(int x, int y, int z, int b) {
+  return ((unsigned long long)(unsigned)b << 48) | ((unsigned long long)(unsigned)z << 32) |
+         ((unsigned long long)(unsigned)y << 16) | (unsigned long long)(unsigned)x;
+}
+__device__ __forceinline__ void unpack_key(unsigned long long k, int &x, int &y, int &z, int &b) {
+  x = (int)(k & 0xFFFF);
+  y = (int)((k >> 16) & 0xFFFF);
+  z = (int)((k >> 32) & 0xFFFF);
+  b = (int)(k >> 48);
+}
+// murmur3 finaliser: spreads the low-entropy packed coordinates over the table.
+__device__ __forceinline__ uint32_t hash_key(unsigned long long k) {
+  k ^= k >> 33;
+  k *= 0xff51afd7ed558ccdULL;
+  k ^= k >> 33;
+  k *= 0xc4ceb9fe1a85ec53ULL;
+  k ^= k >> 33;
+  return (uint32_t)k;
+}
+__device__ __forceinline__ bool coord_ok(long long x, long long y, long long z, long long b) {
+  return x >= 0 && y >= 0 && z >= 0 && b >= 0 && x <= SCN_MAX_COORD && y <= SCN_MAX_COORD &&
+         z <= SCN_MAX_COORD && b <= SCN_MAX_BATCH;
+}
+__device__ __forceinline__ int table_find(const Slot *__restrict__ t, uint32_t mask, unsigned long long key) {
+  uint32_t h = hash_key(key) & mask;
+  for (uint32_t probe = 0; probe <= mask; ++probe) {  // bounded: at most one sweep of the table
+    const ulonglong2 s = __ldg(reinterpret_cast<const ulonglong2 *>(t + h));
+    if (s.x == key) return (int)(uint32_t)(s.y & 0xFFFFFFFFull);
+    if (s.x == kEmptyKey) return -1;
+    h = (h + 1) & mask;
+  }
+  return -1;
+}
+__device__ __forceinline__ bool table_insert(Slot *t, uint32_t mask, unsigned long long key, int row) {
+  uint32_t h = hash_key(key) & mask;
+  for (uint32_t probe = 0; probe <= mask; ++probe) {
+    unsigned long long old = atomicCAS(&t[h].key, kEmptyKey, key);
+    if (old == kEmptyKey || old == key) {
+      t[h].row = row;
+      return true;
+    }
+    h = (h + 1) & mask;
+  }
+  return false;
+}
+__device__ __forceinline__ unsigned long long box_pos(const Box &bx, int x, int y, int z, int b) {
+  return (((unsigned long long)(unsigned)(b - bx.o[3]) * bx.e[2] + (unsigned)(z - bx.o[2])) * bx.e[1] +
+          (unsigned)(y - bx.o[1])) * bx.e[0] + (unsigned)(x - bx.o[0]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// pass 1: keys + bounding box
+// ---------------------------------------------------------------------------------------------
+__global__ void k_init_info(BuildInfo *info) {
+  if (threadIdx.x < 4) {
+    info->mn[threadIdx.x] = INT_MAX;
+    info->mx[threadIdx.x] = INT_MIN;
+  }
+  if (threadIdx.x == 0) {
+    info->err = 0;
+    info->n_unique = 0;
+    info->max_active = 0;
+    info->pad = 0;
+  }
+}
+
+__device__ __forceinline__ void reduce_box(int x, int y, int z, int b, bool valid, BuildInfo *info) {
+  int mn[4] = {valid ? x : INT_MAX, valid ? y : INT_MAX, valid ? z : INT_MAX, valid ? b : INT_MAX};
+  int mx[4] = {valid ? x : INT_MIN, valid ? y : INT_MIN, valid ? z : INT_MIN, valid ? b : INT_MIN};
+#pragma unroll
+  for (int d = 0; d < 4; ++d) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mn[d] = min(mn[d], __shfl_xor_sync(0xffffffffu, mn[d], o));
+      mx[d] = max(mx[d], __shfl_xor_sync(0xffffffffu, mx[d], o));
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+    for (int d = 0; d < 4; ++d) {
+      if (mn[d] != INT_MAX) atomicMin(&info->mn[d], mn[d]);
+      if (mx[d] != INT_MIN) atomicMax(&info->mx[d], mx[d]);
+    }
+  }
+}
+
+// int64 AoS rows (x,y,z[,b]) -> keys.  One thread per point; blocks are multiples of 32 threads and
+// every lane of a warp reaches reduce_box (the tail is padded with invalid lanes).
+__global__ void k_pack_keys_i64(const long long *__restrict__ coords, int ncols, int vec, long long n,
+                                unsigned long long *__restrict__ keys, BuildInfo *info) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  bool valid = i < n;
+  long long x = 0, y = 0, z = 0, b = 0;
+  if (valid) {
+    if (vec) {  // ncols == 4 and 16-byte aligned base: two 16-byte loads per point
+      const longlong2 *p = reinterpret_cast<const longlong2 *>(coords + 4 * i);
+      longlong2 a = __ldg(p), c = __ldg(p + 1);
+      x = a.x; y = a.y; z = c.x; b = c.y;
+    } else {
+      const long long *p = coords + (long long)ncols * i;
+      x = p[0]; y = p[1]; z = p[2];
+      b = ncols > 3 ? p[3] : 0;
+    }
+    if (!coord_ok(x, y, z, b)) {
+      atomicOr(&info->err, 1u);
+      valid = false;
+      keys[i] = 0;
+    } else {
+      keys[i] = pack_key((int)x, (int)y, (int)z, (int)b);
+    }
+  }
+  reduce_box((int)x, (int)y, (int)z, (int)b, valid, info);
+}
+
+// int32 SoA coordinates of a finer grid, shifted right (downsampling by 2^shift).
+__global__ void k_pack_keys_soa(const int32_t *__restrict__ c, long long n, int shift,
+                                unsigned long long *__restrict__ keys, BuildInfo *info) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  bool valid = i < n;
+  int x = 0, y = 0, z = 0, b = 0;
+  if (valid) {
+    x = c[i] >> shift;
+    y = c[n + i] >> shift;
+    z = c[2 * n + i] >> shift;
+    b = c[3 * n + i];
+    keys[i] = pack_key(x, y, z, b);
+  }
+  reduce_box(x, y, z, b, valid, info);
+}
+
+// ---------------------------------------------------------------------------------------------
+// pass 2: occupancy bitmap in key order
+// ---------------------------------------------------------------------------------------------
+__global__ void k_mark(const unsigned long long *__restrict__ keys, long long n, Box bx,
+                       unsigned long long *bitmap) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int x, y, z, b;
+  unpack_key(keys[i], x, y, z, b);
+  unsigned long long p = box_pos(bx, x, y, z, b);
+  unsigned long long bit = 1ull << (p & 63);
+  unsigned long long *w = bitmap + (p >> 6);
+  // most cells hold one point, but duplicates and neighbours share words: skip the atomic when the
+  // bit is already visible.
+  if ((*(volatile unsigned long long *)w & bit) == 0) atomicOr(w, bit);
+}
+
+// ---------------------------------------------------------------------------------------------
+// generic two-level exclusive scan: 256 threads x 8 consecutive items per block
+// ---------------------------------------------------------------------------------------------
+constexpr int kScanThreads = 256;
+constexpr int kScanItems = 8;
+constexpr int kScanChunk = kScanThreads * kScanItems;
+
+// exclusive scan of one value per thread over the block; *total = block sum (same in all threads)
+__device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t *total) {
+  __shared__ uint32_t warp_sum[kScanThreads / 32 + 1];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  uint32_t incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  __syncthreads();  // protects warp_sum against the previous use
+  if (lane == 31) warp_sum[wid] = incl;
+  __syncthreads();
+  if (wid == 0) {
+    uint32_t w = lane < kScanThreads / 32 ? warp_sum[lane] : 0;
+    uint32_t wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      uint32_t t = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += t;
+    }
+    if (lane < kScanThreads / 32) warp_sum[lane] = wi - w;  // exclusive warp offsets
+    if (lane == kScanThreads / 32 - 1) warp_sum[kScanThreads / 32] = wi;
+  }
+  __syncthreads();
+  *total = warp_sum[kScanThreads / 32];
+  return warp_sum[wid] + incl - v;
+}
+
+template <class F>
+__global__ void k_scan_sums(F f, long long n, uint32_t *__restrict__ block_sums) {
+  long long base = (long long)blockIdx.x * kScanChunk + (long long)threadIdx.x * kScanItems;
+  uint32_t s = 0;
+#pragma unroll
+  for (int j = 0; j < kScanItems; ++j)
+    if (base + j < n) s += f(base + j);
+  uint32_t total;
+  block_exclusive_scan(s, &total);
+  if (threadIdx.x == 0) block_sums[blockIdx.x] = total;
+}
+
+// single block: in-place exclusive scan of the block sums, total to *total
+__global__ void k_scan_top(uint32_t *block_sums, long long nb, uint32_t *total_out) {
+  uint32_t carry = 0;
+  for (long long base = 0; base < nb; base += kScanThreads) {
+    long long i = base + threadIdx.x;
+    uint32_t v = i < nb ? block_sums[i] : 0;
+    uint32_t total;
+    uint32_t ex = block_exclusive_scan(v, &total);
+    if (i < nb) block_sums[i] = carry + ex;
+    carry += total;
+  }
+  if (threadIdx.x == 0 && total_out) *total_out = carry;
+}
+
+// second sweep: each thread knows the exclusive prefix of its first item and hands every item to g
+template <class F, class G>
+__global__ void k_scan_emit(F f, G g, long long n, const uint32_t *__restrict__ block_offsets) {
+  long long base = (long long)blockIdx.x * kScanChunk + (long long)threadIdx.x * kScanItems;
+  uint32_t v[kScanItems];
+  uint32_t s = 0;
+#pragma unroll
+  for (int j = 0; j < kScanItems; ++j) {
+    v[j] = (base + j < n) ? f(base + j) : 0;
+    s += v[j];
+  }
+  uint32_t total;
+  uint32_t ex = block_exclusive_scan(s, &total) + block_offsets[blockIdx.x];
+#pragma unroll
+  for (int j = 0; j < kScanItems; ++j) {
+    if (base + j < n) g(base + j, ex, v[j]);
+    ex += v[j];
+  }
+}
+
+template <class F, class G>
+static int scan_emit(F f, G g, long long n, uint32_t *total_dev, cudaStream_t s) {
+  if (n <= 0) {
+    if (total_dev) SCN_CUDA(cudaMemsetAsync(total_dev, 0, sizeof(uint32_t), s));
+    return SCN_OK;
+  }
+  long long nb = (n + kScanChunk - 1) / kScanChunk;
+  uint32_t *sums = nullptr;
+  SCN_TRY(dev_alloc_t(&sums, (size_t)nb, s));
+  k_scan_sums<<<(unsigned)nb, kScanThreads, 0, s>>>(f, n, sums);
+  SCN_LAUNCHED();
+  k_scan_top<<<1, kScanThreads, 0, s>>>(sums, nb, total_dev);
+  SCN_LAUNCHED();
+  k_scan_emit<<<(unsigned)nb, kScanThreads, 0, s>>>(f, g, n, sums);
+  SCN_LAUNCHED();
+  dev_free(sums, s);
+  return SCN_OK;
+}
+
+struct PopcWords {
+  const unsigned long long *w;
+  __device__ uint32_t operator()(long long i) const { return (uint32_t)__popcll(w[i]); }
+};
+struct U32Values {
+  const uint32_t *v;
+  __device__ uint32_t operator()(long long i) const { return v[i]; }
+};
+struct NonNegFlags {
+  const int32_t *v;
+  __device__ uint32_t operator()(long long i) const { return v[i] >= 0 ? 1u : 0u; }
+};
+struct StorePrefix {
+  uint32_t *out;
+  __device__ void operator()(long long i, uint32_t ex, uint32_t) const { out[i] = ex; }
+};
+// writes off[i] and, for the last element, off[n] = total
+struct StoreOffsets {
+  int32_t *off;
+  long long n;
+  __device__ void operator()(long long i, uint32_t ex, uint32_t v) const {
+    off[i] = (int32_t)ex;
+    if (i == n - 1) off[n] = (int32_t)(ex + v);
+  }
+};
+// ordered compaction of a [K][n] map into pairs
+struct EmitPairs {
+  const int32_t *map;
+  int32_t *pairs;
+  long long n;
+  int swap;
+  __device__ void operator()(long long i, uint32_t ex, uint32_t v) const {
+    if (!v) return;
+    int32_t a = map[i], b = (int32_t)(i % n);
+    pairs[2ll * ex] = swap ? b : a;
+    pairs[2ll * ex + 1] = swap ? a : b;
+  }
+};
+
+// ---------------------------------------------------------------------------------------------
+// pass 4: rank -> rows, coordinates, table
+// ---------------------------------------------------------------------------------------------
+__global__ void k_assign(const unsigned long long *__restrict__ keys, long long n_src, Box bx,
+                         const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
+                         long long n, int32_t *__restrict__ src_row, int32_t *coords, uint32_t *cnt, Slot *table,
+                         uint32_t mask, BuildInfo *info) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_src) return;
+  const unsigned long long key = keys[i];
+  int x, y, z, b;
+  unpack_key(key, x, y, z, b);
+  const unsigned long long p = box_pos(bx, x, y, z, b);
+  const unsigned long long w = bitmap[p >> 6];
+  const uint32_t row = prefix[p >> 6] + (uint32_t)__popcll(w & ((1ull << (p & 63)) - 1ull));
+  src_row[i] = (int32_t)row;
+  if (atomicAdd(&cnt[row], 1u) == 0u) {  // first point of the site
+    coords[row] = x;
+    coords[n + row] = y;
+    coords[2 * n + row] = z;
+    coords[3 * n + row] = b;
+    if (!table_insert(table, mask, key, (int)row)) atomicOr(&info->err, 2u);
+  }
+}
+
+// sources of each site (CSR), ascending source index inside a site
+__global__ void k_csr_identity(const int32_t *__restrict__ src_row, long long n_src, int32_t *item) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_src) item[src_row[i]] = (int32_t)i;
+}
+__global__ void k_csr_fill(const int32_t *__restrict__ src_row, long long n_src, const int32_t *__restrict__ off,
+                           uint32_t *cursor, int32_t *item) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_src) return;
+  int r = src_row[i];
+  uint32_t p = atomicAdd(&cursor[r], 1u);
+  item[off[r] + (int)p] = (int32_t)i;
+}
+__global__ void k_csr_sort(const int32_t *__restrict__ off, long long n, int32_t *item, BuildInfo *info) {
+  long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  unsigned int c = 0;
+  if (r < n) {
+    const int b = off[r], e = off[r + 1];
+    c = (unsigned)(e - b);
+    for (int i = b + 1; i < e; ++i) {  // insertion sort: segments are a handful of points
+      int v = item[i], j = i - 1;
+      while (j >= b && item[j] > v) {
+        item[j + 1] = item[j];
+        --j;
+      }
+      item[j + 1] = v;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) c = max(c, __shfl_xor_sync(0xffffffffu, c, o));
+  if ((threadIdx.x & 31) == 0 && c) atomicMax(&info->max_active, c);
+}
+
+// ---------------------------------------------------------------------------------------------
+// lookups and rulebook maps
+// ---------------------------------------------------------------------------------------------
+__global__ void k_query(const int32_t *__restrict__ c, long long stride, long long n, const Slot *__restrict__ table,
+                        uint32_t mask, int32_t *__restrict__ rows) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int x = c[i], y = c[stride + i], z = c[2 * stride + i], b = c[3 * stride + i];
+  rows[i] = coord_ok(x, y, z, b) ? table_find(table, mask, pack_key(x, y, z, b)) : -1;
+}
+
+// 3x3x3 neighbour map.  blockIdx.y = offset k = (dx+1)*9 + (dy+1)*3 + (dz+1); the input site of
+// offset k for output o is o + (dx,dy,dz).  When `absent` is given only sites with absent[o] < 0 are
+// looked up (incremental rulebook against the saved grid), the others get -1.
+__global__ void k_ssc_nbr(const int32_t *__restrict__ c, long long n, const Slot *__restrict__ table, uint32_t mask,
+                          const int32_t *__restrict__ absent, int self_ok, int32_t *__restrict__ nbr,
+                          unsigned long long *counts) {
+  const int k = blockIdx.y;
+  const int dx = k / 9 - 1, dy = (k / 3) % 3 - 1, dz = k % 3 - 1;
+  long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  int r = -1;
+  if (o < n && (absent == nullptr || absent[o] < 0)) {
+    if (k == 13 && self_ok) {
+      r = (int)o;
+    } else {
+      int x = c[o] + dx, y = c[n + o] + dy, z = c[2 * n + o] + dz, b = c[3 * n + o];
+      if (coord_ok(x, y, z, b)) r = table_find(table, mask, pack_key(x, y, z, b));
+    }
+  }
+  if (o < n) nbr[(long long)k * n + o] = r;
+  int cnt = __syncthreads_count(r >= 0);
+  if (threadIdx.x == 0 && cnt) atomicAdd(&counts[k], (unsigned long long)cnt);
+}
+
+// 2x2x2 / stride 2: offset of a fine site inside its coarse cell k = (x&1)*4 + (y&1)*2 + (z&1)
+__global__ void k_conv_maps(const int32_t *__restrict__ fc, long long nf, const int32_t *__restrict__ parent,
+                            long long nc, int32_t *child, int32_t *up, unsigned long long *counts) {
+  long long f = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  __shared__ unsigned int hist[8];
+  if (threadIdx.x < 8) hist[threadIdx.x] = 0;
+  __syncthreads();
+  if (f < nf) {
+    int k = ((fc[f] & 1) << 2) | ((fc[nf + f] & 1) << 1) | (fc[2 * nf + f] & 1);
+    int p = parent[f];
+    child[(long long)k * nc + p] = (int32_t)f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) up[(long long)j * nf + f] = (j == k) ? p : -1;
+    atomicAdd(&hist[k], 1u);
+  }
+  __syncthreads();
+  if (threadIdx.x < 8 && hist[threadIdx.x]) atomicAdd(&counts[threadIdx.x], (unsigned long long)hist[threadIdx.x]);
+}
+
+// incremental deconvolution: the saved coarse row feeds a fine output only when the coarse site
+// existed in the saved frame and the fine site did not.
+__global__ void k_incre_up(const int32_t *__restrict__ up, long long nf, const int32_t *__restrict__ pe_coarse,
+                           const int32_t *__restrict__ pe_fine, int32_t *__restrict__ up2) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 8 * nf) return;
+  long long f = i % nf;
+  int p = up[i];
+  int v = -1;
+  if (p >= 0 && pe_fine[f] < 0) v = pe_coarse[p];
+  up2[i] = v;
+}
+
+__global__ void k_locations(const int32_t *__restrict__ c, long long n, long long *__restrict__ out) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  out[4 * i] = c[i];
+  out[4 * i + 1] = c[n + i];
+  out[4 * i + 2] = c[2 * n + i];
+  out[4 * i + 3] = c[3 * n + i];
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+static inline unsigned blocks_for(long long n, int t) { return (unsigned)((n + t - 1) / t); }
+
+int grid_free(Grid &g, cudaStream_t s) {
+  dev_free(g.coords, s);
+  dev_free(g.table, s);
+  dev_free(g.src_row, s);
+  dev_free(g.csr_off, s);
+  dev_free(g.csr_item, s);
+  dev_free(g.nbr, s);
+  dev_free(g.child, s);
+  dev_free(g.fine_up, s);
+  g = Grid();
+  return SCN_OK;
+}
+
+// Bitmaps above this many bits (4 GiB of words plus 2 GiB of prefixes) are refused.
+static const unsigned long long kMaxBoxBits = 1ull << 35;
+
+int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift, int64_t n_src,
+               bool want_csr, cudaStream_t s) {
+  grid_free(g, s);
+  g.n_src = n_src;
+  if (n_src == 0) return SCN_OK;
+  if (n_src > 0x7FFFFFF0ll) return fail(SCN_E_CAPACITY, "more than 2^31 source rows");
+  const int T = 256;
+  BuildInfo *info_d = nullptr;
+  unsigned long long *keys = nullptr;
+  SCN_TRY(dev_alloc_t(&info_d, 1, s));
+  SCN_TRY(dev_alloc_t(&keys, (size_t)n_src, s));
+  k_init_info<<<1, 32, 0, s>>>(info_d);
+  SCN_LAUNCHED();
+  if (coords64) {
+    int vec = (ncols == 4 && (reinterpret_cast<uintptr_t>(coords64) & 15) == 0) ? 1 : 0;
+    k_pack_keys_i64<<<blocks_for(n_src, T), T, 0, s>>>(reinterpret_cast<const long long *>(coords64), ncols, vec,
+                                                      n_src, keys, info_d);
+  } else {
+    k_pack_keys_soa<<<blocks_for(n_src, T), T, 0, s>>>(coords_soa, n_src, shift, keys, info_d);
+  }
+  SCN_LAUNCHED();
+  BuildInfo info;
+  SCN_CUDA(cudaMemcpyAsync(&info, info_d, sizeof(info), cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  if (info.err & 1u) {
+    dev_free(info_d, s);
+    dev_free(keys, s);
+    return fail(SCN_E_RANGE, "coordinate outside [0, 65534] or batch index outside [0, 32766]");
+  }
+  Box bx;
+  unsigned long long bits = 1;
+  for (int d = 0; d < 4; ++d) {
+    bx.o[d] = info.mn[d];
+    bx.e[d] = (unsigned)(info.mx[d] - info.mn[d] + 1);
+    bits *= bx.e[d];
+    if (bits > kMaxBoxBits) {
+      dev_free(info_d, s);
+      dev_free(keys, s);
+      return fail(SCN_E_CAPACITY, "scene bounding box larger than 2^35 cells");
+    }
+  }
+  const long long nwords = (long long)((bits + 63) >> 6);
+  unsigned long long *bitmap = nullptr;
+  uint32_t *prefix = nullptr;
+  SCN_TRY(dev_alloc_t(&bitmap, (size_t)nwords, s));
+  SCN_TRY(dev_alloc_t(&prefix, (size_t)nwords, s));
+  SCN_CUDA(cudaMemsetAsync(bitmap, 0, (size_t)nwords * 8, s));
+  k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap);
+  SCN_LAUNCHED();
+  SCN_TRY(scan_emit(PopcWords{bitmap}, StorePrefix{prefix}, nwords, &info_d->n_unique, s));
+  SCN_CUDA(cudaMemcpyAsync(&info.n_unique, &info_d->n_unique, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  const int64_t n = info.n_unique;
+  g.n = n;
+  uint64_t cap = 16;
+  while (cap < (uint64_t)n * 2) cap <<= 1;
+  g.mask = (uint32_t)(cap - 1);
+  uint32_t *cnt = nullptr;
+  SCN_TRY(dev_alloc_t(&g.coords, (size_t)n * 4, s));
+  SCN_TRY(dev_alloc_t(&g.table, (size_t)cap, s));
+  SCN_TRY(dev_alloc_t(&g.src_row, (size_t)n_src, s));
+  SCN_TRY(dev_alloc_t(&cnt, (size_t)n, s));
+  SCN_CUDA(cudaMemsetAsync(g.table, 0xFF, (size_t)cap * sizeof(Slot), s));
+  SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n * 4, s));
+  k_assign<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, cnt,
+                                             g.table, g.mask, info_d);
+  SCN_LAUNCHED();
+  g.max_active = 1;
+  bool need_info = false;
+  if (want_csr) {
+    SCN_TRY(dev_alloc_t(&g.csr_item, (size_t)n_src, s));
+    if (n == n_src) {
+      k_csr_identity<<<blocks_for(n_src, T), T, 0, s>>>(g.src_row, n_src, g.csr_item);
+      SCN_LAUNCHED();
+    } else {
+      SCN_TRY(dev_alloc_t(&g.csr_off, (size_t)n + 1, s));
+      SCN_TRY(scan_emit(U32Values{cnt}, StoreOffsets{g.csr_off, (long long)n}, n, nullptr, s));
+      SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n * 4, s));
+      k_csr_fill<<<blocks_for(n_src, T), T, 0, s>>>(g.src_row, n_src, g.csr_off, cnt, g.csr_item);
+      SCN_LAUNCHED();
+      k_csr_sort<<<blocks_for(n, T), T, 0, s>>>(g.csr_off, n, g.csr_item, info_d);
+      SCN_LAUNCHED();
+      need_info = true;
+    }
+  }
+  // the error word (table overflow) always comes back; max_active with it when duplicates exist
+  SCN_CUDA(cudaMemcpyAsync(&info, info_d, sizeof(info), cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  if (need_info) g.max_active = (int32_t)info.max_active;
+  dev_free(cnt, s);
+  dev_free(prefix, s);
+  dev_free(bitmap, s);
+  dev_free(keys, s);
+  dev_free(info_d, s);
+  if (info.err & 2u) return fail(SCN_E_CAPACITY, "hash table overflow");
+  return SCN_OK;
+}
+
+int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_stride, int32_t *rows,
+               cudaStream_t s) {
+  if (n == 0) return SCN_OK;
+  if (g.n == 0) {
+    SCN_CUDA(cudaMemsetAsync(rows, 0xFF, (size_t)n * 4, s));
+    return SCN_OK;
+  }
+  k_query<<<blocks_for(n, 256), 256, 0, s>>>(coords_soa, soa_stride, n, g.table, g.mask, rows);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+static int nbr_common(const Grid &g, const Grid &lookup, const int32_t *absent, int self_ok, int32_t *nbr,
+                      int64_t *counts_host, cudaStream_t s) {
+  unsigned long long *counts_d = nullptr;
+  SCN_TRY(dev_alloc_t(&counts_d, 27, s));
+  SCN_CUDA(cudaMemsetAsync(counts_d, 0, 27 * 8, s));
+  dim3 grid(blocks_for(g.n, 256), 27);
+  k_ssc_nbr<<<grid, 256, 0, s>>>(g.coords, g.n, lookup.table, lookup.mask, absent, self_ok, nbr, counts_d);
+  SCN_LAUNCHED();
+  unsigned long long h[27];
+  SCN_CUDA(cudaMemcpyAsync(h, counts_d, sizeof(h), cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  dev_free(counts_d, s);
+  for (int k = 0; k < 27; ++k) counts_host[k] = (int64_t)h[k];
+  return SCN_OK;
+}
+
+int grid_build_ssc(Grid &g, cudaStream_t s) {
+  if (g.nbr || g.n == 0) return SCN_OK;
+  SCN_TRY(dev_alloc_t(&g.nbr, (size_t)g.n * 27, s));
+  SCN_TRY(nbr_common(g, g, nullptr, 1, g.nbr, g.nbr_count, s));
+  g.nbr_total = 0;
+  for (int k = 0; k < 27; ++k) g.nbr_total += g.nbr_count[k];
+  return SCN_OK;
+}
+
+int build_incre_nbr(const Grid &g, const Grid &pre, const int32_t *pre_exist, int32_t *nbr2, int64_t *counts_host,
+                    cudaStream_t s) {
+  if (g.n == 0) return SCN_OK;
+  if (pre.n == 0) {
+    SCN_CUDA(cudaMemsetAsync(nbr2, 0xFF, (size_t)g.n * 27 * 4, s));
+    for (int k = 0; k < 27; ++k) counts_host[k] = 0;
+    return SCN_OK;
+  }
+  return nbr_common(g, pre, pre_exist, 0, nbr2, counts_host, s);
+}
+
+int grid_build_conv(Grid &coarse, const Grid &fine, cudaStream_t s) {
+  if (coarse.child || coarse.n == 0) return SCN_OK;
+  unsigned long long *counts_d = nullptr;
+  SCN_TRY(dev_alloc_t(&counts_d, 8, s));
+  SCN_CUDA(cudaMemsetAsync(counts_d, 0, 8 * 8, s));
+  SCN_TRY(dev_alloc_t(&coarse.child, (size_t)coarse.n * 8, s));
+  SCN_TRY(dev_alloc_t(&coarse.fine_up, (size_t)fine.n * 8, s));
+  SCN_CUDA(cudaMemsetAsync(coarse.child, 0xFF, (size_t)coarse.n * 8 * 4, s));
+  k_conv_maps<<<blocks_for(fine.n, 256), 256, 0, s>>>(fine.coords, fine.n, coarse.src_row, coarse.n, coarse.child,
+                                                     coarse.fine_up, counts_d);
+  SCN_LAUNCHED();
+  unsigned long long h[8];
+  SCN_CUDA(cudaMemcpyAsync(h, counts_d, sizeof(h), cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  dev_free(counts_d, s);
+  for (int k = 0; k < 8; ++k) coarse.child_count[k] = (int64_t)h[k];
+  return SCN_OK;
+}
+
+int build_incre_up(const Grid &coarse, const int32_t *pe_coarse, const int32_t *pe_fine, int32_t *up2,
+                   cudaStream_t s) {
+  const long long nf = coarse.n_src;
+  if (nf == 0) return SCN_OK;
+  k_incre_up<<<blocks_for(8 * nf, 256), 256, 0, s>>>(coarse.fine_up, nf, pe_coarse, pe_fine, up2);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+int map_to_pairs(const int32_t *map, int K, int64_t n, int swap, int64_t expected_pairs, int32_t *pairs_host,
+                 cudaStream_t s) {
+  if (n == 0 || expected_pairs == 0) return SCN_OK;
+  const long long total_items = (long long)K * n;
+  int32_t *pairs_d = nullptr;
+  uint32_t *total_d = nullptr;
+  SCN_TRY(dev_alloc_t(&pairs_d, (size_t)expected_pairs * 2, s));
+  SCN_TRY(dev_alloc_t(&total_d, 1, s));
+  SCN_TRY(scan_emit(NonNegFlags{map}, EmitPairs{map, pairs_d, (long long)n, swap}, total_items, total_d, s));
+  uint32_t total = 0;
+  SCN_CUDA(cudaMemcpyAsync(&total, total_d, 4, cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaMemcpyAsync(pairs_host, pairs_d, (size_t)expected_pairs * 8, cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  dev_free(pairs_d, s);
+  dev_free(total_d, s);
+  if ((int64_t)total != expected_pairs) return fail(SCN_E_STATE, "rulebook pair count changed under the caller");
+  return SCN_OK;
+}
+
+int grid_locations(const Grid &g, int64_t *out_host, cudaStream_t s) {
+  if (g.n == 0) return SCN_OK;
+  long long *tmp = nullptr;
+  SCN_TRY(dev_alloc_t(&tmp, (size_t)g.n * 4, s));
+  k_locations<<<blocks_for(g.n, 256), 256, 0, s>>>(g.coords, g.n, tmp);
+  SCN_LAUNCHED();
+  SCN_CUDA(cudaMemcpyAsync(out_host, tmp, (size_t)g.n * 32, cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  dev_free(tmp, s);
+  return SCN_OK;
+}
+
+}  // namespace scn

@@ -1,0 +1,128 @@
+// Internal declarations shared by the translation units of libinsconv_b200.so.
+// Nothing in this file is part of the C ABI (see include/insconv_b200.h).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+#include <atomic>
+#include "insconv_b200.h"
+
+namespace scn {
+
+// ---- error plumbing ---------------------------------------------------------
+void set_error(const std::string &msg);
+int fail(int code, const std::string &msg);
+#define SCN_CUDA(expr)                                                                              \
+  do {                                                                                              \
+    cudaError_t e_ = (expr);                                                                        \
+    if (e_ != cudaSuccess)                                                                          \
+      return ::scn::fail(SCN_E_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e_));           \
+  } while (0)
+#define SCN_TRY(expr)                                                                               \
+  do {                                                                                              \
+    int r_ = (expr);                                                                                \
+    if (r_ != SCN_OK) return r_;                                                                    \
+  } while (0)
+
+extern std::atomic<uint64_t> g_launches;
+// Counts a launch and checks for a launch-configuration error.
+#define SCN_LAUNCHED()                                                                              \
+  do {                                                                                              \
+    ::scn::g_launches.fetch_add(1, std::memory_order_relaxed);                                      \
+    SCN_CUDA(cudaGetLastError());                                                                   \
+  } while (0)
+
+// ---- device memory: stream-ordered pool --------------------------------------
+int dev_alloc(void **p, size_t bytes, cudaStream_t s);
+void dev_free(void *p, cudaStream_t s);
+template <typename T> int dev_alloc_t(T **p, size_t count, cudaStream_t s) {
+  return dev_alloc(reinterpret_cast<void **>(p), count * sizeof(T), s);
+}
+
+// ---- key / table layout -----------------------------------------------------
+// key = batch<<48 | z<<32 | y<<16 | x : ascending key order is batch-major, then z, y, x,
+// the order the reference's packed key (z<<21 | y<<10 | x per batch grid) induces.
+struct Slot {
+  unsigned long long key;  // ~0 = empty
+  int row;                 // site row
+  int count;               // number of source points that fell in the site
+};
+static_assert(sizeof(Slot) == 16, "slot must be one 16-byte vector");
+static const unsigned long long kEmptyKey = ~0ull;
+
+// Written by the build kernels, read back by the host once per build.
+struct BuildInfo {
+  int mn[4];  // bounding box minimum  x,y,z,batch
+  int mx[4];  // bounding box maximum
+  unsigned int err;         // bit0: coordinate out of key range, bit1: table overflow
+  unsigned int n_unique;    // sites found
+  unsigned int max_active;  // most source points in one site
+  unsigned int pad;
+};
+
+// Bounding box in key order used to rank keys: pos = ((b*ez + z)*ey + y)*ex + x (box-relative).
+struct Box {
+  int o[4];            // origin x,y,z,b
+  unsigned int e[4];   // extents
+};
+
+// One scale of a scene.
+struct Grid {
+  int64_t n = 0;           // active sites
+  int32_t *coords = nullptr;  // SoA [4][n]: x, y, z, batch
+  Slot *table = nullptr;
+  uint32_t mask = 0;       // capacity - 1
+  // relation to the source rows this grid was built from (input points, or the sites of the
+  // next finer scale):
+  int64_t n_src = 0;
+  int32_t *src_row = nullptr;   // [n_src] source -> site row
+  int32_t *csr_off = nullptr;   // [n+1]  (nullptr when every site has exactly one source: off[i] = i)
+  int32_t *csr_item = nullptr;  // [n_src] sources of each site, ascending
+  int32_t max_active = 0;
+  // submanifold 3x3x3 neighbour map: nbr[k*n + o] = input row of offset k for output o, or -1
+  int32_t *nbr = nullptr;
+  int64_t nbr_count[27] = {0};
+  int64_t nbr_total = 0;
+  // size-2/stride-2 relation to the next finer grid (valid on grids built by downsampling):
+  int32_t *child = nullptr;      // [8][n]: fine row of offset k, or -1
+  int32_t *fine_up = nullptr;    // [8][n_src]: up[k*n_src+f] = coarse row if offset(f)==k else -1
+  int64_t child_count[8] = {0};
+};
+
+int grid_free(Grid &g, cudaStream_t s);
+
+// Builds g from source points.  Exactly one of coords64 / coords_soa is given:
+//   coords64  : int64 [n_src, ncols] rows (x,y,z[,b]) on the device
+//   coords_soa: int32 SoA [4][n_src] on the device, shifted right by `shift` bits (downsampling)
+int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift,
+               int64_t n_src, bool want_csr, cudaStream_t s);
+int grid_build_ssc(Grid &g, cudaStream_t s);               // fills nbr / nbr_count
+int grid_build_conv(Grid &coarse, const Grid &fine, cudaStream_t s);  // fills child / fine_up
+int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_stride, int32_t *rows,
+               cudaStream_t s);
+// ordered compaction of a [K][n] map (entries >= 0) into `expected_pairs` pairs, k-major and ascending
+// in the column inside each k.  swap = 0: pair (value, column); swap = 1: pair (column, value).
+int map_to_pairs(const int32_t *map, int K, int64_t n, int swap, int64_t expected_pairs, int32_t *pairs_host,
+                 cudaStream_t s);
+int grid_locations(const Grid &g, int64_t *out_host, cudaStream_t s);
+// incremental helpers
+int build_incre_nbr(const Grid &g, const Grid &pre, const int32_t *pre_exist, int32_t *nbr2,
+                    int64_t *counts_host, cudaStream_t s);
+int build_incre_up(const Grid &coarse, const int32_t *pe_coarse, const int32_t *pe_fine, int32_t *up2,
+                   cudaStream_t s);
+
+// ---- feature kernels --------------------------------------------------------
+// out[o] = (accumulate ? out[o] : bias) + sum_k in[map[k*n_out + o]] * W[k]   (map == nullptr: identity, K = 1)
+int gather_gemm(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *W,
+                const float *bias, float *out, int64_t out_stride, int64_t n_in, int64_t n_planes_out,
+                int accumulate, int precision, cudaStream_t s);
+int bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,
+               const float *mean, const float *var, const float *gamma, const float *beta, float eps,
+               float leak, const int32_t *pre_exist, const float *pre_out, const float *pre_in,
+               cudaStream_t s);
+int input_forward(const Grid &g, const float *in, float *out, int64_t planes, int average,
+                  const int32_t *pre_exist, const Grid *pre, const float *pre_out, cudaStream_t s);
+int output_forward(const Grid &g, const float *in, float *out, int64_t planes, const int32_t *pre_exist,
+                   const float *pre_in, cudaStream_t s);
+
+}  // namespace scn

@@ -1,0 +1,144 @@
+"""Grid (voxel hash), InputLayer rules and rulebooks through the C ABI vs the CPU oracle: bit exact."""
+import numpy as np
+import pytest
+import torch
+
+from insconv import cabi, synth
+from oracle import scn_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _build(coords, size, cuda, mode=4, on_device=True):
+    m = cabi.Metadata()
+    t = torch.from_numpy(np.ascontiguousarray(coords, dtype=np.int64))
+    n = m.input_layer_build(size, t.to(cuda) if on_device else t, mode=mode)
+    return m, n
+
+
+def _check_grid(m, n, g, size):
+    assert n == g.n
+    loc = m.spatial_locations(size)
+    np.testing.assert_array_equal(loc, g.coords)
+    keys, rows = m.hash_dump(size)
+    filled = keys != np.uint64(0xFFFFFFFFFFFFFFFF)
+    assert int(filled.sum()) == g.n
+    assert dict(zip(keys[filled].tolist(), rows[filled].tolist())) == g.hash_contents()
+    hdr, rrows = m.input_rules()
+    ohdr, orows = O.input_rules(g, int(hdr[0]))
+    np.testing.assert_array_equal(hdr, ohdr)
+    np.testing.assert_array_equal(rrows, orows)
+
+
+def _check_rules(got, want):
+    assert len(got) == len(want)
+    for k, (a, b) in enumerate(zip(got, want)):
+        np.testing.assert_array_equal(a, b, err_msg="offset %d" % k)
+
+
+def test_tiny_hand_checkable(cuda):
+    # three voxels in a row along x plus one isolated voxel
+    c = np.array([[5, 5, 5], [6, 5, 5], [7, 5, 5], [20, 20, 20]])
+    m, n = _build(c, 64, cuda)
+    g = O.Grid(c)
+    _check_grid(m, n, g, 64)
+    rules = m.ssc_rulebook(64)
+    _check_rules(rules, O.ssc_rules(g))
+    # centre offset holds every site once; +x / -x offsets hold the two chain links
+    assert rules[13].tolist() == [[0, 0], [1, 1], [2, 2], [3, 3]]
+    assert rules[22].tolist() == [[1, 0], [2, 1]]  # dx=+1: input is the +x neighbour
+    assert rules[4].tolist() == [[0, 1], [1, 2]]   # dx=-1
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+@pytest.mark.parametrize("on_device", [True, False])
+def test_boxes_and_spheres(cuda, seed, on_device):
+    c = synth.boxes_and_spheres(seed)
+    rng = np.random.RandomState(seed)
+    c = c[rng.permutation(c.shape[0])]
+    m, n = _build(c, 128, cuda, on_device=on_device)
+    g = O.Grid(c)
+    _check_grid(m, n, g, 128)
+    _check_rules(m.ssc_rulebook(128), O.ssc_rules(g))
+    coarse, crules = O.conv2_rules(g)
+    _check_rules(m.conv_rulebook(128, 64), crules)
+    assert m.n_active(64) == coarse.n
+    np.testing.assert_array_equal(m.spatial_locations(64), coarse.coords)
+    _check_rules(m.ssc_rulebook(64), O.ssc_rules(coarse))
+
+
+def test_duplicates_and_batches(cuda):
+    rng = np.random.RandomState(3)
+    c = rng.randint(1, 40, size=(20000, 3))
+    b = np.sort(rng.randint(0, 3, size=(20000, 1)), 0)
+    cb = np.concatenate([c, b], 1)
+    for mode in (3, 4):
+        m, n = _build(cb, 64, cuda, mode=mode)
+        g = O.Grid(cb)
+        assert g.n < cb.shape[0]
+        _check_grid(m, n, g, 64)
+        _check_rules(m.ssc_rulebook(64), O.ssc_rules(g))
+        _, crules = O.conv2_rules(g)
+        _check_rules(m.conv_rulebook(64, 32), crules)
+
+
+def test_permutation_invariance(cuda):
+    c = synth.boxes_and_spheres(2)
+    m1, _ = _build(c, 128, cuda)
+    m2, _ = _build(c[np.random.RandomState(0).permutation(c.shape[0])], 128, cuda)
+    np.testing.assert_array_equal(m1.spatial_locations(128), m2.spatial_locations(128))
+    _check_rules(m1.ssc_rulebook(128), m2.ssc_rulebook(128))
+
+
+@pytest.mark.parametrize("pts", [
+    [[0, 0, 0], [1, 0, 0], [0, 1, 1]],                                  # low faces of the key range
+    [[65534, 65534, 65534], [65533, 65534, 65534], [65534, 65533, 65533]],  # high faces
+    [[1023, 2047, 1023], [1024, 2047, 1023], [1024, 2048, 1024]],       # beyond the reference's 10/11/10-bit key
+])
+def test_border_and_wide_coordinates(cuda, pts):
+    # neighbours outside the key range must miss, not alias
+    c = np.array(pts)
+    m, n = _build(c, 65536, cuda)
+    g = O.Grid(c)
+    _check_grid(m, n, g, 65536)
+    _check_rules(m.ssc_rulebook(65536), O.ssc_rules(g))
+
+
+def test_empty_and_single(cuda):
+    m, n = _build(np.zeros((0, 3), np.int64), 32, cuda)
+    assert n == 0 and m.n_active(32) == 0
+    assert sum(len(r) for r in m.ssc_rulebook(32)) == 0
+    m, n = _build(np.array([[3, 4, 5]]), 32, cuda)
+    assert n == 1
+    r = m.ssc_rulebook(32)
+    assert [len(x) for x in r] == [0] * 13 + [1] + [0] * 13
+
+
+def test_errors_are_reported_not_fatal(cuda):
+    m = cabi.Metadata()
+    with pytest.raises(cabi.ScnError) as e:
+        m.input_layer_build(64, torch.tensor([[1, 2, 70000]], device=cuda), mode=4)
+    assert e.value.code == -3
+    with pytest.raises(cabi.ScnError):
+        m.input_layer_build(64, torch.tensor([[1, 2, 3]], device=cuda), mode=1)
+    with pytest.raises(cabi.ScnError):
+        m.ssc_rulebook(64)  # no grid
+    # a scene whose bounding box exceeds the build limit is refused with a clear error
+    with pytest.raises(cabi.ScnError) as e:
+        m.input_layer_build(65536, torch.tensor([[0, 0, 0], [60000, 60000, 60000]], device=cuda), mode=4)
+    assert e.value.code == -4
+    # the device is still usable afterwards
+    n = m.input_layer_build(64, torch.tensor([[1, 2, 3]], device=cuda), mode=4)
+    assert n == 1
+
+
+def test_query(cuda):
+    c = synth.boxes_and_spheres(0)
+    m, _ = _build(c, 128, cuda)
+    g = O.Grid(c)
+    rng = np.random.RandomState(0)
+    q = np.concatenate([c[rng.randint(0, c.shape[0], 5000)], rng.randint(0, 128, size=(5000, 3))], 0)
+    q4 = np.concatenate([q, np.zeros((q.shape[0], 1), np.int64)], 1)
+    soa = torch.from_numpy(np.ascontiguousarray(q4.T.astype(np.int32))).to(cuda)
+    rows = m.query(128, soa).cpu().numpy()
+    np.testing.assert_array_equal(rows, g.lookup(q4))
