@@ -1,0 +1,372 @@
+// The torch extension module `sparseconvnet.SCN`: the operator surface the sparseconvnet Python
+// modules call, for dimension 3, forwarding to the C ABI of libinsconv_b200.so.
+//
+// It mirrors the hot-path subset of the reference's pybind module (sparseconvnet/SCN/pybind.cpp:13-33,
+// 73-78, 97-102, 153-157, 173-189, 219-257, 304; prototypes in sparseconvnet/SCN/sparseconvnet.h):
+// same function names, argument order and conventions -- sizes are CPU LongTensors, outputs arrive
+// empty and are resized here, "no bias" is an empty tensor, convolutions return the multiply-add
+// count.  Differences by design: errors raise Python exceptions instead of exiting the process, work
+// is queued on torch's current CUDA stream, feature tensors must be CUDA fp32 (there is no CPU path),
+// and the backward entry points exist only to fail with a clear message (inference only).
+#include <torch/extension.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "insconv_b200.h"
+
+namespace {
+
+int g_precision = SCN_PREC_FP32;
+
+void check(int status, const char *what) {
+  if (status != SCN_OK)
+    throw std::runtime_error(std::string(what) + ": " + scn_last_error() + " (status " + std::to_string(status) + ")");
+}
+
+void *stream_of(const at::Tensor &t) { return (void *)c10::cuda::getCurrentCUDAStream(t.device().index()).stream(); }
+
+void need_cuda_f32(const at::Tensor &t, const char *name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor (this build has no CPU path)");
+  TORCH_CHECK(t.scalar_type() == at::kFloat, name, " must be float32");
+}
+
+struct Size3 {
+  int64_t v[3];
+  explicit Size3(const at::Tensor &t) {
+    TORCH_CHECK(t.numel() == 3, "only dimension 3 is supported; got a size of ", t.numel(), " elements");
+    auto c = t.to(at::kCPU, at::kLong).contiguous();
+    for (int i = 0; i < 3; ++i) v[i] = c.data_ptr<int64_t>()[i];
+  }
+};
+
+const float *opt_ptr(const at::Tensor &t) { return t.numel() ? t.data_ptr<float>() : nullptr; }
+
+void expect_filter(const at::Tensor &filt, int64_t want, const char *what) {
+  auto c = filt.to(at::kCPU, at::kLong);
+  for (int64_t i = 0; i < c.numel(); ++i)
+    TORCH_CHECK(c.data_ptr<int64_t>()[i] == want, what, ": only filter size / stride ", want, " is supported");
+}
+
+class Metadata3 {
+ public:
+  Metadata3() { check(scn_metadata_create(&h_), "Metadata"); }
+  ~Metadata3() { scn_metadata_destroy(h_); }
+  Metadata3(const Metadata3 &) = delete;
+  Metadata3 &operator=(const Metadata3 &) = delete;
+  scn_metadata *h() const { return h_; }
+
+  void clear() { check(scn_metadata_clear(h_, nullptr), "Metadata.clear"); }
+  at::Tensor getSpatialLocations(at::Tensor spatialSize) {
+    Size3 s(spatialSize);
+    int64_t n = scn_metadata_n_active(h_, s.v);
+    TORCH_CHECK(n >= 0, "Metadata has no grid at this spatial size");
+    auto out = at::empty({n, 4}, at::TensorOptions().dtype(at::kLong).device(at::kCPU));
+    check(scn_metadata_spatial_locations(h_, s.v, out.data_ptr<int64_t>(), (void *)c10::cuda::getCurrentCUDAStream().stream()),
+          "getSpatialLocations");
+    return out;
+  }
+  int64_t getNActive(at::Tensor spatialSize) {
+    Size3 s(spatialSize);
+    return scn_metadata_n_active(h_, s.v);
+  }
+
+ private:
+  scn_metadata *h_ = nullptr;
+};
+
+// ---- full-frame ops ------------------------------------------------------------------------------
+double SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filterSize, Metadata3 &m,
+                                           at::Tensor input_features, at::Tensor output_features, at::Tensor weight,
+                                           at::Tensor bias, int dilated_rate) {
+  need_cuda_f32(input_features, "input_features");
+  need_cuda_f32(weight, "weight");
+  TORCH_CHECK(dilated_rate == 1, "dilated submanifold convolutions are outside the hot path");
+  TORCH_CHECK(weight.dim() == 3 && weight.size(0) == 27, "weight must be [27, nIn, nOut]");
+  expect_filter(filterSize, 3, "SubmanifoldConvolution");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  Size3 s(inputSize);
+  auto in = input_features.contiguous();
+  auto w = weight.contiguous();
+  const int64_t n = scn_metadata_n_active(m.h(), s.v);
+  TORCH_CHECK(n >= 0, "Metadata has no grid at this spatial size");
+  TORCH_CHECK(in.size(0) == n && in.size(1) == w.size(1), "input_features must be [nActive, nIn]");
+  output_features.resize_({n, w.size(2)});
+  double flops = 0;
+  check(scn_ssc_forward(m.h(), s.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(), w.size(2),
+                        w.data_ptr<float>(), opt_ptr(bias), w.size(1), w.size(2), g_precision, stream_of(in), &flops),
+        "SubmanifoldConvolution_updateOutput");
+  return flops;
+}
+
+double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
+                                at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
+                                at::Tensor output_features, at::Tensor weight, at::Tensor bias) {
+  need_cuda_f32(input_features, "input_features");
+  need_cuda_f32(weight, "weight");
+  expect_filter(filterSize, 2, "Convolution");
+  expect_filter(filterStride, 2, "Convolution");
+  TORCH_CHECK(weight.dim() == 3 && weight.size(0) == 8, "weight must be [8, nIn, nOut]");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  Size3 si(inputSize), so(outputSize);
+  auto in = input_features.contiguous();
+  auto w = weight.contiguous();
+  int64_t n = 0;
+  check(scn_conv_prepare(m.h(), si.v, so.v, stream_of(in), &n), "Convolution_updateOutput");
+  output_features.resize_({n, w.size(2)});
+  double flops = 0;
+  check(scn_conv_forward(m.h(), si.v, so.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(),
+                         w.size(2), w.data_ptr<float>(), opt_ptr(bias), w.size(1), w.size(2), g_precision,
+                         stream_of(in), &flops),
+        "Convolution_updateOutput");
+  return flops;
+}
+
+double Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
+                                  at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
+                                  at::Tensor output_features, at::Tensor weight, at::Tensor bias) {
+  need_cuda_f32(input_features, "input_features");
+  need_cuda_f32(weight, "weight");
+  expect_filter(filterSize, 2, "Deconvolution");
+  expect_filter(filterStride, 2, "Deconvolution");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  Size3 si(inputSize), so(outputSize);
+  auto in = input_features.contiguous();
+  auto w = weight.contiguous();
+  const int64_t n = scn_metadata_n_active(m.h(), so.v);
+  TORCH_CHECK(n >= 0, "Deconvolution: Metadata has no grid at the output spatial size");
+  output_features.resize_({n, w.size(2)});
+  double flops = 0;
+  check(scn_deconv_forward(m.h(), si.v, so.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(),
+                           w.size(2), w.data_ptr<float>(), opt_ptr(bias), w.size(1), w.size(2), g_precision,
+                           stream_of(in), &flops),
+        "Deconvolution_updateOutput");
+  return flops;
+}
+
+void BatchNormalization_updateOutput(at::Tensor input_features, at::Tensor output_features, at::Tensor saveMean,
+                                     at::Tensor saveInvStd, at::Tensor runningMean, at::Tensor runningVar,
+                                     at::Tensor weight, at::Tensor bias, double eps, double momentum, bool train,
+                                     double leakiness) {
+  need_cuda_f32(input_features, "input_features");
+  TORCH_CHECK(!train, "BatchNormalization: only inference (running statistics) is on the hot path; call model.eval()");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  auto in = input_features.contiguous();
+  output_features.resize_as_(in);
+  if (in.numel() == 0) return;
+  check(scn_bn_forward(in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(), in.size(1), in.size(0),
+                       in.size(1), runningMean.data_ptr<float>(), runningVar.data_ptr<float>(), opt_ptr(weight),
+                       opt_ptr(bias), eps, leakiness, stream_of(in)),
+        "BatchNormalization_updateOutput");
+}
+
+double NetworkInNetwork_updateOutput(at::Tensor input_features, at::Tensor output_features, at::Tensor weight,
+                                     at::Tensor bias) {
+  need_cuda_f32(input_features, "input_features");
+  need_cuda_f32(weight, "weight");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  auto in = input_features.contiguous();
+  auto w = weight.contiguous();
+  output_features.resize_({in.size(0), w.size(1)});
+  double flops = 0;
+  check(scn_nin_forward(in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(), w.size(1), in.size(0),
+                        w.data_ptr<float>(), opt_ptr(bias), w.size(0), w.size(1), g_precision, stream_of(in), &flops),
+        "NetworkInNetwork_updateOutput");
+  return flops;
+}
+
+// coords may be a CPU or a CUDA LongTensor [N,3] or [N,4]; a CUDA tensor is used in place (no bounce
+// through the host).
+void build_input(Metadata3 &m, at::Tensor spatialSize, at::Tensor input_coords, const at::Tensor &feats,
+                 long batchSize, long mode) {
+  TORCH_CHECK(input_coords.dim() == 2 && (input_coords.size(1) == 3 || input_coords.size(1) == 4),
+              "coords must be N x 3 or N x 4");
+  Size3 s(spatialSize);
+  auto c = input_coords.to(at::kLong).contiguous();
+  TORCH_CHECK(c.size(0) == feats.size(0), "coords and features disagree on the number of points");
+  int64_t n = 0;
+  check(scn_input_layer_build(m.h(), s.v, c.data_ptr<int64_t>(), c.is_cuda() ? 0 : 1, c.size(0), (int)c.size(1),
+                              batchSize, (int)mode, stream_of(feats), &n),
+        "InputLayer_updateOutput");
+}
+
+void InputLayer_updateOutput(Metadata3 &m, at::Tensor spatialSize, at::Tensor input_coords, at::Tensor input_features,
+                             at::Tensor output_features, long batchSize, long mode) {
+  need_cuda_f32(input_features, "input_features");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  auto in = input_features.contiguous();
+  build_input(m, spatialSize, input_coords, in, batchSize, mode);
+  Size3 s(spatialSize);
+  output_features.resize_({scn_metadata_n_active(m.h(), s.v), in.size(1)});
+  check(scn_input_layer_forward(m.h(), in.data_ptr<float>(), output_features.data_ptr<float>(), in.size(1),
+                                stream_of(in)),
+        "InputLayer_updateOutput");
+}
+
+void OutputLayer_updateOutput(Metadata3 &m, at::Tensor input_features, at::Tensor output_features) {
+  need_cuda_f32(input_features, "input_features");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  auto in = input_features.contiguous();
+  const int64_t n = scn_input_layer_n_points(m.h());
+  TORCH_CHECK(n >= 0, "OutputLayer: Metadata has no input layer");
+  output_features.resize_({n, in.size(1)});
+  check(scn_output_layer_forward(m.h(), in.data_ptr<float>(), output_features.data_ptr<float>(), in.size(1),
+                                 stream_of(in)),
+        "OutputLayer_updateOutput");
+}
+
+// ---- incremental ops -----------------------------------------------------------------------------
+double Incre_SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filterSize, Metadata3 &m,
+                                                 at::Tensor input_features, at::Tensor output_features,
+                                                 at::Tensor weight, at::Tensor bias, Metadata3 &pre_m,
+                                                 at::Tensor pre_input_feats) {
+  need_cuda_f32(input_features, "input_features");
+  need_cuda_f32(pre_input_feats, "pre_input_feats");
+  expect_filter(filterSize, 3, "SubmanifoldConvolution");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  Size3 s(inputSize);
+  auto in = input_features.contiguous();
+  auto pre = pre_input_feats.contiguous();
+  auto w = weight.contiguous();
+  const int64_t n = scn_metadata_n_active(m.h(), s.v);
+  TORCH_CHECK(n >= 0, "Metadata has no grid at this spatial size");
+  output_features.resize_({n, w.size(2)});
+  double flops = 0;
+  check(scn_incre_ssc_forward(m.h(), pre_m.h(), s.v, in.data_ptr<float>(), in.size(1),
+                              output_features.data_ptr<float>(), w.size(2), w.data_ptr<float>(), opt_ptr(bias),
+                              pre.data_ptr<float>(), pre.size(1), w.size(1), w.size(2), g_precision, stream_of(in),
+                              &flops),
+        "Incre_SubmanifoldConvolution_updateOutput");
+  return flops;
+}
+
+double Incre_Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
+                                      at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
+                                      at::Tensor output_features, at::Tensor weight, at::Tensor bias) {
+  // a 2/2 convolution has no overlap between cells: the residual of the output is the convolution of
+  // the residual (reference: CUDA/Convolution.cpp:83-113)
+  return Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features, output_features,
+                                  weight, bias);
+}
+
+double Incre_Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
+                                        at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
+                                        at::Tensor output_features, at::Tensor weight, at::Tensor bias,
+                                        Metadata3 &pre_m, at::Tensor pre_input_feats) {
+  need_cuda_f32(input_features, "input_features");
+  need_cuda_f32(pre_input_feats, "pre_input_feats");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  Size3 si(inputSize), so(outputSize);
+  auto in = input_features.contiguous();
+  auto pre = pre_input_feats.contiguous();
+  auto w = weight.contiguous();
+  const int64_t n = scn_metadata_n_active(m.h(), so.v);
+  TORCH_CHECK(n >= 0, "Deconvolution: Metadata has no grid at the output spatial size");
+  output_features.resize_({n, w.size(2)});
+  double flops = 0;
+  check(scn_incre_deconv_forward(m.h(), pre_m.h(), si.v, so.v, in.data_ptr<float>(), in.size(1),
+                                 output_features.data_ptr<float>(), w.size(2), w.data_ptr<float>(), opt_ptr(bias),
+                                 pre.data_ptr<float>(), pre.size(1), w.size(1), w.size(2), g_precision, stream_of(in),
+                                 &flops),
+        "Incre_Deconvolution_updateOutput");
+  return flops;
+}
+
+void Incre_BatchNormalization_updateOutput(at::Tensor input_features, at::Tensor output_features, at::Tensor saveMean,
+                                           at::Tensor saveInvStd, at::Tensor runningMean, at::Tensor runningVar,
+                                           at::Tensor weight, at::Tensor bias, double eps, double momentum, bool train,
+                                           double leakiness, Metadata3 &m, Metadata3 &pre_m,
+                                           at::Tensor pre_output_feats, at::Tensor pre_input_feats,
+                                           at::Tensor spatialSize) {
+  need_cuda_f32(input_features, "input_features");
+  TORCH_CHECK(!train, "BatchNormalization: only inference (running statistics) is on the hot path; call model.eval()");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  Size3 s(spatialSize);
+  auto in = input_features.contiguous();
+  auto po = pre_output_feats.contiguous();
+  auto pi = pre_input_feats.contiguous();
+  output_features.resize_as_(in);
+  if (in.numel() == 0) return;
+  check(scn_incre_bn_forward(m.h(), pre_m.h(), s.v, in.data_ptr<float>(), in.size(1),
+                             output_features.data_ptr<float>(), in.size(1), in.size(1), runningMean.data_ptr<float>(),
+                             runningVar.data_ptr<float>(), opt_ptr(weight), opt_ptr(bias), eps, leakiness,
+                             po.data_ptr<float>(), pi.data_ptr<float>(), stream_of(in)),
+        "Incre_BatchNormalization_updateOutput");
+}
+
+void Incre_InputLayer_updateOutput(Metadata3 &m, at::Tensor spatialSize, at::Tensor input_coords,
+                                   at::Tensor input_features, at::Tensor output_features, long batchSize, long mode,
+                                   Metadata3 &pre_m, at::Tensor pre_output_feats) {
+  need_cuda_f32(input_features, "input_features");
+  need_cuda_f32(pre_output_feats, "pre_output_feats");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  auto in = input_features.contiguous();
+  auto po = pre_output_feats.contiguous();
+  build_input(m, spatialSize, input_coords, in, batchSize, mode);
+  Size3 s(spatialSize);
+  output_features.resize_({scn_metadata_n_active(m.h(), s.v), in.size(1)});
+  check(scn_incre_input_layer_forward(m.h(), pre_m.h(), in.data_ptr<float>(), output_features.data_ptr<float>(),
+                                      po.data_ptr<float>(), in.size(1), stream_of(in)),
+        "Incre_InputLayer_updateOutput");
+}
+
+void Incre_OutputLayer_updateOutput(Metadata3 &m, at::Tensor input_features, at::Tensor output_features,
+                                    Metadata3 &pre_m, at::Tensor pre_input_feats) {
+  need_cuda_f32(input_features, "input_features");
+  need_cuda_f32(pre_input_feats, "pre_input_feats");
+  c10::cuda::CUDAGuard guard(input_features.device());
+  auto in = input_features.contiguous();
+  auto pi = pre_input_feats.contiguous();
+  const int64_t n = scn_input_layer_n_points(m.h());
+  TORCH_CHECK(n >= 0, "OutputLayer: Metadata has no input layer");
+  output_features.resize_({n, in.size(1)});
+  check(scn_incre_output_layer_forward(m.h(), pre_m.h(), in.data_ptr<float>(), output_features.data_ptr<float>(),
+                                       pi.data_ptr<float>(), in.size(1), stream_of(in)),
+        "Incre_OutputLayer_updateOutput");
+}
+
+void set_precision(const std::string &p) {
+  if (p == "fp32") g_precision = SCN_PREC_FP32;
+  else if (p == "tf32") g_precision = SCN_PREC_TF32;
+  else throw std::runtime_error("precision must be 'fp32' or 'tf32'");
+}
+std::string get_precision() { return g_precision == SCN_PREC_TF32 ? "tf32" : "fp32"; }
+
+void no_backward(pybind11::args, pybind11::kwargs) {
+  throw std::runtime_error("this build of sparseconvnet.SCN is inference only: backward passes are not part of the hot path");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
+  mod.doc() = "B200 sparse-convolution operators behind the sparseconvnet.SCN interface (dimension 3)";
+  pybind11::class_<Metadata3>(mod, "Metadata_3")
+      .def(pybind11::init<>())
+      .def("clear", &Metadata3::clear)
+      .def("getSpatialLocations", &Metadata3::getSpatialLocations)
+      .def("getNActive", &Metadata3::getNActive);
+  mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput);
+  mod.def("Convolution_updateOutput", &Convolution_updateOutput);
+  mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput);
+  mod.def("BatchNormalization_updateOutput", &BatchNormalization_updateOutput);
+  mod.def("NetworkInNetwork_updateOutput", &NetworkInNetwork_updateOutput);
+  mod.def("InputLayer_updateOutput", &InputLayer_updateOutput);
+  mod.def("OutputLayer_updateOutput", &OutputLayer_updateOutput);
+  mod.def("Incre_SubmanifoldConvolution_updateOutput", &Incre_SubmanifoldConvolution_updateOutput);
+  mod.def("Incre_Convolution_updateOutput", &Incre_Convolution_updateOutput);
+  mod.def("Incre_Deconvolution_updateOutput", &Incre_Deconvolution_updateOutput);
+  mod.def("Incre_BatchNormalization_updateOutput", &Incre_BatchNormalization_updateOutput);
+  mod.def("Incre_InputLayer_updateOutput", &Incre_InputLayer_updateOutput);
+  mod.def("Incre_OutputLayer_updateOutput", &Incre_OutputLayer_updateOutput);
+  mod.def("n_rulebook_bits", []() { return scn_n_rulebook_bits(); });
+  mod.def("set_precision", &set_precision, "arithmetic of the convolution kernels: 'fp32' or 'tf32'");
+  mod.def("get_precision", &get_precision);
+  mod.def("launch_count", []() { return scn_launch_count(); });
+  for (const char *name :
+       {"SubmanifoldConvolution_backward", "Convolution_backward", "Deconvolution_backward",
+        "BatchNormalization_backward", "NetworkInNetwork_updateGradInput", "NetworkInNetwork_accGradParameters",
+        "InputLayer_updateGradInput", "OutputLayer_updateGradInput"})
+    mod.def(name, &no_backward);
+}

@@ -1,0 +1,64 @@
+"""Graph glue: Sequential, ConcatTable, AddTable, JoinTable, Identity
+(reference: sparseconvnet/sequential.py:9-25, tables.py:13-55, identity.py:10-15)."""
+import torch
+
+from .tensor import SparseConvNetTensor
+
+
+class _Container(torch.nn.Sequential):
+    def add(self, module):
+        self._modules[str(len(self._modules))] = module
+        return self
+
+
+class Sequential(_Container):
+    def forward(self, input, increment=False):
+        for module in self:
+            input = module(input, increment)
+        return input
+
+    def input_spatial_size(self, out_size):
+        for module in reversed(list(self)):
+            out_size = module.input_spatial_size(out_size)
+        return out_size
+
+
+class ConcatTable(_Container):
+    """Feeds the same input to every child and returns the list of results."""
+
+    def forward(self, input, increment=False):
+        return [module(input, increment) for module in self]
+
+    def input_spatial_size(self, out_size):
+        return self._modules["0"].input_spatial_size(out_size)
+
+
+class AddTable(_Container):
+    """Sums the features of a list of tensors living on the same sites."""
+
+    def forward(self, input, increment=False):
+        feats = input[0].features
+        for t in input[1:]:
+            feats = feats + t.features
+        return input[0].like(feats)
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+
+class JoinTable(_Container):
+    """Concatenates the feature planes of a list of tensors living on the same sites."""
+
+    def forward(self, input, increment=False):
+        return input[0].like(torch.cat([t.features for t in input], 1))
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+
+class Identity(torch.nn.Module):
+    def forward(self, input, increment=False):
+        return input
+
+    def input_spatial_size(self, out_size):
+        return out_size

@@ -1,0 +1,273 @@
+"""The operator modules of the UNet inference path.
+
+Each module mirrors the constructor arguments, parameter shapes, initialisation and forward contract
+of its reference counterpart:
+  SubmanifoldConvolution  sparseconvnet/submanifoldConvolution.py:18-81
+  Convolution             sparseconvnet/convolution.py:13-84
+  Deconvolution           sparseconvnet/deconvolution.py:13-106
+  BatchNormalization      sparseconvnet/batchNormalization.py:13-110
+  NetworkInNetwork        sparseconvnet/networkInNetwork.py:57-88
+  InputLayer/OutputLayer  sparseconvnet/ioLayers.py:15-117
+`forward(input, increment=False)`: a full frame (increment False) computes on every site and keeps what
+the next incremental frames need (`save_meta`, `save_input_feats`, `save_output`, `save_input`); an
+incremental frame computes residuals on the sites touched by the new points only.  The modules are
+inference only: outputs carry no autograd history.
+"""
+import torch
+from torch.nn import Module, Parameter
+
+import sparseconvnet
+from . import SCN
+from .metadata import Metadata
+from .tensor import SparseConvNetTensor
+from .utils import toLongTensor, optionalTensor
+
+
+def _count(madds, out):
+    sparseconvnet.forward_pass_multiplyAdd_count += madds
+    sparseconvnet.forward_pass_hidden_states += out.nelement()
+
+
+def _size_repr(name, n_in, n_out, size, stride=None):
+    s = "%s %d->%d C%s" % (name, n_in, n_out, "x".join(str(int(v)) for v in size) if size.max() != size.min() else int(size[0]))
+    if stride is not None:
+        s += "/%s" % ("x".join(str(int(v)) for v in stride) if stride.max() != stride.min() else int(stride[0]))
+    return s
+
+
+class SubmanifoldConvolution(Module):
+    def __init__(self, dimension, nIn, nOut, filter_size, bias, dilated_rate=1):
+        Module.__init__(self)
+        self.dimension, self.nIn, self.nOut = dimension, nIn, nOut
+        self.filter_size = toLongTensor(dimension, filter_size)
+        self.filter_volume = int(self.filter_size.prod().item())
+        self.dilated_rate = dilated_rate
+        std = (2.0 / nIn / self.filter_volume) ** 0.5
+        self.weight = Parameter(torch.empty(self.filter_volume, nIn, nOut).normal_(0, std))
+        if bias:
+            self.bias = Parameter(torch.zeros(nOut))
+
+    @torch.no_grad()
+    def forward(self, input, increment=False):
+        assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, self.nOut, input)
+        out = input.features.new_empty(0)
+        if not increment:
+            madds = SCN.SubmanifoldConvolution_updateOutput(
+                input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
+                optionalTensor(self, "bias"), self.dilated_rate)
+            self.save_meta = input.metadata
+            self.save_input_feats = input.features
+        else:
+            madds = SCN.Incre_SubmanifoldConvolution_updateOutput(
+                input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
+                optionalTensor(self, "bias"), self.save_meta, self.save_input_feats)
+        _count(madds, out)
+        return input.like(out)
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+    def __repr__(self):
+        return _size_repr("SubmanifoldConvolution", self.nIn, self.nOut, self.filter_size)
+
+
+ValidConvolution = SubmanifoldConvolution
+
+
+class _Strided(Module):
+    def __init__(self, dimension, nIn, nOut, filter_size, filter_stride, bias):
+        Module.__init__(self)
+        self.dimension, self.nIn, self.nOut = dimension, nIn, nOut
+        self.filter_size = toLongTensor(dimension, filter_size)
+        self.filter_stride = toLongTensor(dimension, filter_stride)
+        self.filter_volume = int(self.filter_size.prod().item())
+        std = (2.0 / nIn / self.filter_volume) ** 0.5
+        self.weight = Parameter(torch.empty(self.filter_volume, nIn, nOut).normal_(0, std))
+        if bias:
+            self.bias = Parameter(torch.zeros(nOut))
+
+
+class Convolution(_Strided):
+    @torch.no_grad()
+    def forward(self, input, increment=False):
+        assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
+        out_size = torch.div(input.spatial_size - self.filter_size, self.filter_stride, rounding_mode="floor") + 1
+        assert ((out_size - 1) * self.filter_stride + self.filter_size == input.spatial_size).all(), \
+            (input.spatial_size, out_size, self.filter_size, self.filter_stride)
+        out = input.features.new_empty(0)
+        op = SCN.Incre_Convolution_updateOutput if increment else SCN.Convolution_updateOutput
+        madds = op(input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
+                   out, self.weight, optionalTensor(self, "bias"))
+        _count(madds, out)
+        return input.like(out, out_size)
+
+    def input_spatial_size(self, out_size):
+        return (out_size - 1) * self.filter_stride + self.filter_size
+
+    def __repr__(self):
+        return _size_repr("Convolution", self.nIn, self.nOut, self.filter_size, self.filter_stride)
+
+
+class Deconvolution(_Strided):
+    @torch.no_grad()
+    def forward(self, input, increment=False):
+        assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
+        out_size = (input.spatial_size - 1) * self.filter_stride + self.filter_size
+        out = input.features.new_empty(0)
+        if not increment:
+            madds = SCN.Deconvolution_updateOutput(
+                input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
+                out, self.weight, optionalTensor(self, "bias"))
+            self.save_meta = input.metadata
+            self.save_input_feats = input.features
+        else:
+            madds = SCN.Incre_Deconvolution_updateOutput(
+                input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
+                out, self.weight, optionalTensor(self, "bias"), self.save_meta, self.save_input_feats)
+        _count(madds, out)
+        return input.like(out, out_size)
+
+    def input_spatial_size(self, out_size):
+        in_size = torch.div(out_size - self.filter_size, self.filter_stride, rounding_mode="floor") + 1
+        assert ((in_size - 1) * self.filter_stride + self.filter_size == out_size).all()
+        return in_size
+
+    def __repr__(self):
+        return _size_repr("Deconvolution", self.nIn, self.nOut, self.filter_size, self.filter_stride)
+
+
+class BatchNormalization(Module):
+    """leakiness: 0 = ReLU, (0,1) = leaky ReLU, 1 = no activation, applied in the same kernel."""
+
+    def __init__(self, nPlanes, eps=1e-4, momentum=0.9, affine=True, leakiness=1):
+        Module.__init__(self)
+        self.nPlanes, self.eps, self.momentum, self.affine, self.leakiness = nPlanes, eps, momentum, affine, leakiness
+        self.register_buffer("running_mean", torch.zeros(nPlanes))
+        self.register_buffer("running_var", torch.ones(nPlanes))
+        if affine:
+            self.weight = Parameter(torch.ones(nPlanes))
+            self.bias = Parameter(torch.zeros(nPlanes))
+
+    @torch.no_grad()
+    def forward(self, input, increment=False):
+        assert input.features.nelement() == 0 or input.features.size(1) == self.nPlanes, \
+            (self.nPlanes, input.features.shape)
+        out = input.features.new_empty(0)
+        scratch = input.features.new_empty(0)
+        if not increment:
+            SCN.BatchNormalization_updateOutput(
+                input.features, out, scratch, scratch, self.running_mean, self.running_var,
+                optionalTensor(self, "weight"), optionalTensor(self, "bias"), self.eps, self.momentum, self.training,
+                self.leakiness)
+            self.save_output = input.like(out)
+            self.save_input = input.like(input.features)
+        else:
+            SCN.Incre_BatchNormalization_updateOutput(
+                input.features, out, scratch, scratch, self.running_mean, self.running_var,
+                optionalTensor(self, "weight"), optionalTensor(self, "bias"), self.eps, self.momentum, self.training,
+                self.leakiness, input.metadata, self.save_output.metadata, self.save_output.features,
+                self.save_input.features, input.spatial_size)
+        return input.like(out)
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+    def __repr__(self):
+        return "%s(%d,eps=%g,momentum=%g,affine=%s,leakiness=%g)" % (
+            type(self).__name__, self.nPlanes, self.eps, self.momentum, self.affine, self.leakiness)
+
+
+class BatchNormReLU(BatchNormalization):
+    def __init__(self, nPlanes, eps=1e-4, momentum=0.9):
+        BatchNormalization.__init__(self, nPlanes, eps, momentum, True, 0)
+
+
+class BatchNormLeakyReLU(BatchNormalization):
+    def __init__(self, nPlanes, eps=1e-4, momentum=0.9, leakiness=0.333):
+        BatchNormalization.__init__(self, nPlanes, eps, momentum, True, leakiness)
+
+
+class NetworkInNetwork(Module):
+    """1x1 convolution; linear, so the incremental frame applies it to the residual rows as is."""
+
+    def __init__(self, nIn, nOut, bias):
+        Module.__init__(self)
+        self.nIn, self.nOut = nIn, nOut
+        self.weight = Parameter(torch.empty(nIn, nOut).normal_(0, (2.0 / nIn) ** 0.5))
+        if bias:
+            self.bias = Parameter(torch.zeros(nOut))
+
+    @torch.no_grad()
+    def forward(self, input, increment=False):
+        assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, input.features.shape)
+        out = input.features.new_empty(0)
+        madds = SCN.NetworkInNetwork_updateOutput(input.features, out, self.weight, optionalTensor(self, "bias"))
+        _count(madds, out)
+        return input.like(out)
+
+    def input_spatial_size(self, out_size):
+        return out_size
+
+    def __repr__(self):
+        return "NetworkInNetwork%d->%d" % (self.nIn, self.nOut)
+
+
+class InputLayer(Module):
+    """(coords, features[, batch_size]) -> SparseConvNetTensor.
+
+    coords: LongTensor N x 3 (one sample) or N x 4 (last column = batch index), on the CPU or on the GPU
+    (a CUDA tensor is hashed in place, without a trip through the host).  mode 3 sums and mode 4 averages
+    the features of points that share a voxel; other modes are not part of the GPU grid path.
+    """
+
+    def __init__(self, dimension, spatial_size, mode=3, normal_guide_scale=10240):
+        Module.__init__(self)
+        self.dimension = dimension
+        self.spatial_size = toLongTensor(dimension, spatial_size)
+        self.mode = mode
+        self.normal_guide_scale = normal_guide_scale
+        self.device = None
+
+    def to(self, device):
+        self.device = device
+        return self
+
+    @torch.no_grad()
+    def forward(self, input, increment=False):
+        assert len(input) >= 2, len(input)
+        coords, feats = input[0], input[1]
+        batch_size = int(input[2]) if len(input) > 2 else 0
+        if not feats.is_cuda:
+            feats = feats.to(self.device if self.device else "cuda")
+        feats = feats.float()
+        output = SparseConvNetTensor(metadata=Metadata(self.dimension), spatial_size=self.spatial_size)
+        out = feats.new_empty(0)
+        if not increment:
+            SCN.InputLayer_updateOutput(output.metadata, self.spatial_size, coords, feats, out, batch_size, self.mode)
+            output.features = out
+            self.save_output = output
+        else:
+            SCN.Incre_InputLayer_updateOutput(output.metadata, self.spatial_size, coords, feats, out, batch_size,
+                                              self.mode, self.save_output.metadata, self.save_output.features)
+            output.features = out
+        return output
+
+
+class OutputLayer(Module):
+    """SparseConvNetTensor -> N x planes tensor, one row per input point of the InputLayer."""
+
+    def __init__(self, dimension):
+        Module.__init__(self)
+        self.dimension = dimension
+
+    @torch.no_grad()
+    def forward(self, input, increment=False):
+        out = input.features.new_empty(0)
+        if not increment:
+            SCN.OutputLayer_updateOutput(input.metadata, input.features, out)
+            self.save_input_feats = input.features
+            self.save_meta = input.metadata
+        else:
+            SCN.Incre_OutputLayer_updateOutput(input.metadata, input.features, out, self.save_meta,
+                                               self.save_input_feats)
+        return out

@@ -1,0 +1,29 @@
+"""Small helpers shared by the modules (reference: sparseconvnet/utils.py:13-28)."""
+import torch
+
+from . import SCN
+
+
+def toLongTensor(dimension, x):
+    """int, list/tuple or LongTensor -> CPU LongTensor of `dimension` entries."""
+    if isinstance(x, torch.Tensor):
+        return x.to(dtype=torch.int64, device="cpu")
+    if isinstance(x, (list, tuple)):
+        assert len(x) == dimension
+        return torch.tensor(list(x), dtype=torch.int64)
+    return torch.full((dimension,), int(x), dtype=torch.int64)
+
+
+def optionalTensor(module, name):
+    """The named attribute, or an empty tensor ('no bias' convention of the operator interface)."""
+    t = getattr(module, name, None)
+    return t if t is not None else torch.empty(0)
+
+
+def set_precision(p):
+    """'fp32' (default, bit-for-bit deterministic FFMA) or 'tf32' (tcgen05 tensor cores)."""
+    SCN.set_precision(p)
+
+
+def get_precision():
+    return SCN.get_precision()

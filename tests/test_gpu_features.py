@@ -1,0 +1,136 @@
+"""Feature kernels through the C ABI vs the CPU oracle.
+
+Tolerances (stated by the north star of this build): fp32 outputs within 1e-4 relative; the metric used
+is max|a-b| / max(|b|_max, 1e-6) per tensor plus an element-wise allclose with rtol = atol = 1e-4.
+"""
+import numpy as np
+import pytest
+import torch
+
+from insconv import cabi, synth
+from oracle import scn_oracle as O
+
+pytestmark = pytest.mark.gpu
+FP32_TOL = 1e-4
+
+
+def close(got, want, tol=FP32_TOL):
+    got = got.detach().cpu()
+    want = torch.as_tensor(want)
+    assert got.shape == want.shape, (got.shape, want.shape)
+    if want.numel() == 0:
+        return
+    scale = max(float(want.abs().max()), 1e-6)
+    err = float((got - want).abs().max()) / scale
+    assert err <= tol, "relative error %.3g > %.1g" % (err, tol)
+    assert torch.allclose(got, want, rtol=tol, atol=tol * scale)
+
+
+def _scene(cuda, seed=0, size=128):
+    c = synth.boxes_and_spheres(seed, grid=size)
+    m = cabi.Metadata()
+    n = m.input_layer_build(size, torch.from_numpy(c).to(cuda), mode=4)
+    g = O.Grid(c)
+    assert n == g.n
+    return m, g
+
+
+@pytest.mark.parametrize("n_in,n_out,bias", [(16, 16, False), (3, 32, False), (32, 32, True), (64, 32, False),
+                                             (32, 64, True), (96, 96, False), (5, 7, True), (224, 224, False)])
+def test_ssc_forward(cuda, n_in, n_out, bias):
+    m, g = _scene(cuda, 0)
+    rng = np.random.RandomState(n_in * 1000 + n_out)
+    x = rng.randn(g.n, n_in).astype(np.float32)
+    w = synth.kaiming_uniform(rng, 27, n_in, n_out)
+    b = rng.randn(n_out).astype(np.float32) if bias else None
+    rules = O.ssc_rules(g)
+    want = O.conv_forward(x, w, rules, g.n, b)
+    got, flops = m.ssc_forward(128, torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda),
+                               torch.from_numpy(b).to(cuda) if bias else None)
+    close(got, want)
+    assert flops == O.rule_flops(rules, n_in, n_out)
+
+
+@pytest.mark.parametrize("n_in,n_out", [(32, 64), (16, 16), (3, 5), (96, 128)])
+def test_conv_deconv_forward(cuda, n_in, n_out):
+    m, g = _scene(cuda, 1)
+    rng = np.random.RandomState(7)
+    coarse, rules = O.conv2_rules(g)
+    x = rng.randn(g.n, n_in).astype(np.float32)
+    w = synth.kaiming_uniform(rng, 8, n_in, n_out)
+    b = rng.randn(n_out).astype(np.float32)
+    want = O.conv_forward(x, w, rules, coarse.n, b)
+    got, flops = m.conv_forward(128, 64, torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda),
+                                torch.from_numpy(b).to(cuda))
+    close(got, want)
+    assert flops == O.rule_flops(rules, n_in, n_out)
+    # deconvolution back to the fine scale with the same rulebook, pair reversed
+    wd = synth.kaiming_uniform(rng, 8, n_out, n_in)
+    y = rng.randn(coarse.n, n_out).astype(np.float32)
+    want = O.conv_forward(y, wd, rules, g.n, None, reverse=True)
+    got, _ = m.deconv_forward(64, 128, torch.from_numpy(y).to(cuda), torch.from_numpy(wd).to(cuda))
+    close(got, want)
+
+
+@pytest.mark.parametrize("planes,leak", [(32, 0.0), (3, 0.333), (224, 0.0), (17, 1.0)])
+def test_bn_forward(cuda, planes, leak):
+    rng = np.random.RandomState(planes)
+    x = rng.randn(5003, planes).astype(np.float32)
+    mean = rng.randn(planes).astype(np.float32)
+    var = rng.uniform(0.5, 2.0, planes).astype(np.float32)
+    gamma = rng.randn(planes).astype(np.float32)
+    beta = rng.randn(planes).astype(np.float32)
+    want = O.bn_forward(x, mean, var, gamma, beta, 1e-4, leak)
+    t = lambda a: torch.from_numpy(a).to(cuda)
+    got = cabi.bn_forward(t(x), t(mean), t(var), t(gamma), t(beta), 1e-4, leak)
+    close(got, want, 1e-5)
+    got = cabi.bn_forward(t(x), t(mean), t(var), None, None, 1e-4, leak)
+    close(got, O.bn_forward(x, mean, var, None, None, 1e-4, leak), 1e-5)
+
+
+@pytest.mark.parametrize("n_in,n_out,bias", [(64, 32, False), (6, 3, True), (448, 224, False)])
+def test_nin_forward(cuda, n_in, n_out, bias):
+    rng = np.random.RandomState(n_in)
+    x = rng.randn(4099, n_in).astype(np.float32)
+    w = (rng.randn(n_in, n_out) * np.sqrt(2.0 / n_in)).astype(np.float32)
+    b = rng.randn(n_out).astype(np.float32) if bias else None
+    t = lambda a: torch.from_numpy(a).to(cuda)
+    got, flops = cabi.nin_forward(t(x), t(w), t(b) if bias else None)
+    close(got, O.nin_forward(x, w, b))
+    assert flops == 4099.0 * n_in * n_out
+
+
+@pytest.mark.parametrize("mode", [3, 4])
+def test_input_output_layers(cuda, mode):
+    rng = np.random.RandomState(11)
+    c = rng.randint(1, 30, size=(30000, 3))
+    f = rng.randn(30000, 3).astype(np.float32)
+    m = cabi.Metadata()
+    m.input_layer_build(32, torch.from_numpy(c).to(cuda), mode=mode)
+    g = O.Grid(c)
+    vox = m.input_forward(torch.from_numpy(f).to(cuda))
+    close(vox, O.input_forward(f, g, mode), 1e-5)
+    h = rng.randn(g.n, 32).astype(np.float32)
+    pts = m.output_forward(torch.from_numpy(h).to(cuda))
+    assert torch.equal(pts.cpu(), O.output_forward(h, g))
+
+
+def test_linearity_at_full_size(cuda):
+    # size-independent property on the 250k-voxel room: SSC(a*x + y) == a*SSC(x) + SSC(y)
+    c = synth.room(0)
+    m = cabi.Metadata()
+    n = m.input_layer_build(4096, torch.from_numpy(c).to(cuda), mode=4)
+    assert n == c.shape[0]
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn(n, 32, generator=g).to(cuda)
+    y = torch.randn(n, 32, generator=g).to(cuda)
+    w = (torch.randn(27, 32, 32, generator=g) * 0.05).to(cuda)
+    a, _ = m.ssc_forward(4096, 2.5 * x + y, w)
+    b1, _ = m.ssc_forward(4096, x, w)
+    b2, _ = m.ssc_forward(4096, y, w)
+    close(a, (2.5 * b1 + b2).cpu(), 1e-4)
+    # and the centre-only filter is a plain matmul
+    w0 = torch.zeros_like(w)
+    w0[13] = w[13]
+    c0, _ = m.ssc_forward(4096, x, w0)
+    close(c0, (x @ w[13]).cpu(), 1e-4)

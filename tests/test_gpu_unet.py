@@ -1,0 +1,107 @@
+"""The sparseconvnet module graph (reference model.py topology) on the GPU library vs the CPU oracle."""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from insconv import synth
+from oracle.scn_graph import GraphRunner
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def rel_err(got, want):
+    got = got.detach().cpu().float()
+    want = want.detach().cpu().float()
+    assert got.shape == want.shape
+    return float((got - want).abs().max()) / max(float(want.abs().max()), 1e-6)
+
+
+def small_unet(scn, planes, reps=2, residual=True, n_classes=20, full_scale=256):
+    class Net(torch.nn.Module):
+        def __init__(self):
+            torch.nn.Module.__init__(self)
+            self.sparseModel = scn.Sequential().add(
+                scn.InputLayer(3, full_scale, mode=4)).add(
+                scn.SubmanifoldConvolution(3, 3, planes[0], 3, False)).add(
+                scn.UNet(3, reps, planes, residual)).add(
+                scn.BatchNormReLU(planes[0])).add(
+                scn.OutputLayer(3))
+            self.linear = torch.nn.Linear(planes[0], n_classes)
+
+        def forward(self, x, increment=False):
+            return self.linear(self.sparseModel(x, increment))
+    return Net()
+
+
+def randomize_bn(model, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    for m in model.modules():
+        if type(m).__name__.startswith("BatchNorm"):
+            m.running_mean.copy_(torch.randn(m.nPlanes, generator=g) * 0.1)
+            m.running_var.copy_(torch.rand(m.nPlanes, generator=g) + 0.5)
+            m.weight.data.copy_(torch.rand(m.nPlanes, generator=g) + 0.5)
+            m.bias.data.copy_(torch.randn(m.nPlanes, generator=g) * 0.1)
+
+
+def run_oracle(model, inputs, increment=False, runner=None):
+    runner = runner or GraphRunner(model)
+    seq = lambda x, inc: runner._run(model.linear, runner._run(model.sparseModel, x, inc), inc)
+    return seq(inputs, increment), runner
+
+
+@pytest.mark.parametrize("residual", [True, False])
+def test_small_unet_matches_oracle(cuda, residual):
+    import sparseconvnet as scn
+    torch.manual_seed(0)
+    model = small_unet(scn, [16, 32, 48, 64], residual=residual).eval()
+    randomize_bn(model)
+    c = synth.boxes_and_spheres(0)
+    f = synth.rgb(0, c.shape[0])
+    want, _ = run_oracle(model, [torch.from_numpy(c), torch.from_numpy(f)])
+    model = model.to(cuda)
+    got = model([torch.from_numpy(c).to(cuda), torch.from_numpy(f).to(cuda)])
+    assert rel_err(got, want) <= 1e-4
+
+
+def test_small_unet_incremental_matches_oracle(cuda):
+    # reference (non-dilating, insert-only) incremental semantics, layer by layer through the whole graph
+    import sparseconvnet as scn
+    torch.manual_seed(1)
+    model = small_unet(scn, [16, 32, 48], residual=True).eval()
+    randomize_bn(model, 1)
+    c = synth.boxes_and_spheres(1)
+    rng = np.random.RandomState(1)
+    f = synth.rgb(1, c.shape[0])
+    nf = synth.next_frame(c, f, seed=1)
+    want0, runner = run_oracle(model, [torch.from_numpy(c), torch.from_numpy(f)])
+    want1, _ = run_oracle(model, [torch.from_numpy(nf["new_coords"]), torch.from_numpy(nf["new_feats"])], True, runner)
+    model = model.to(cuda)
+    got0 = model([torch.from_numpy(c).to(cuda), torch.from_numpy(f).to(cuda)])
+    got1 = model([torch.from_numpy(nf["new_coords"]).to(cuda), torch.from_numpy(nf["new_feats"]).to(cuda)], True)
+    assert rel_err(got0, want0) <= 1e-4
+    assert got1.shape[0] == nf["new_coords"].shape[0]
+    assert rel_err(got1, want1) <= 1e-4
+
+
+def test_reference_model_py_topology(cuda):
+    # the Naive_UNet of the reference's model.py (m=32, planes 32..224, reps 2, residual), reproduced here
+    # because the reference tree does not travel with the tests
+    import sparseconvnet as scn
+    torch.manual_seed(2)
+    model = small_unet(scn, [32, 64, 96, 128, 160, 192, 224], full_scale=4096).eval()
+    assert sum(1 for m in model.modules() if isinstance(m, scn.SubmanifoldConvolution)) == 53
+    assert sum(1 for m in model.modules() if isinstance(m, scn.BatchNormalization)) == 65
+    assert sum(p.numel() for p in model.parameters()) == 30104372
+    c = synth.room(0, target=60000)
+    f = synth.rgb(0, c.shape[0])
+    want, _ = run_oracle(model, [torch.from_numpy(c), torch.from_numpy(f)])
+    model = model.to(cuda)
+    got = model([torch.from_numpy(c).to(cuda), torch.from_numpy(f).to(cuda)])
+    assert rel_err(got, want) <= 1e-4
+    # CPU coordinates (the reference's calling convention) give the same result
+    got2 = model([torch.from_numpy(c), torch.from_numpy(f).to(cuda), 1])
+    assert torch.equal(got, got2)
