@@ -1,0 +1,382 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse-convolution hot path on B200.
+
+A step is one full frame of the SCN UNet of the reference's model.py (InputLayer mode 4, SSC 3->32,
+UNet planes [32..224] x reps 2 residual, BN+ReLU, OutputLayer, Linear 32->20) over one seeded
+synthetic room of ~250k voxels: voxel hashing, all rulebooks, 53 submanifold convolutions, 6+6 strided
+(de)convolutions, 65 BatchNorm+ReLU, 6 1x1 convolutions.  The metric is BASELINE.json's "active voxels/s
+per SSC layer": the active sites summed over the 53 submanifold-convolution layers of the frame, divided
+by the time of the whole frame (everything else is charged to it).  The incremental frame (5 % of the
+voxels changed, reference semantics) is timed beside it and reported as ms/frame.
+
+  value      inputs resident in HBM when the timed region starts
+  e2e        the same through the public module API with pinned HOST inputs and a host read of the result
+  roofline   the dominant kernel (the gather-GEMM of the level-0 32->32 submanifold convolution), timed
+             with CUDA events on the launching stream inside the timed region
+  cpu_baseline  the CPU restatement of the reference (oracle/) on this box's host cores, rank 0, N=1 only
+
+N > 1 (torchrun, one rank per GPU): every rank runs its own seeded room, no data-path collective; the
+step time is the max over ranks (weak scaling).
+
+`--impl reference` times the CPU restatement of the reference on the same workload instead.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "ins-conv_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+METRIC = "active voxels/s per SSC layer (UNet frame); incremental ms/frame beside it"
+UNIT = "voxel-layers/s"
+PLANES = [32, 64, 96, 128, 160, 192, 224]
+WORKLOAD = "configs[2]: model.py SCN UNet, one synthetic room (~250k voxels, 2 cm, 8x8x3 m), full frame"
+
+
+def build_model(scn, torch):
+    class NaiveUNet(torch.nn.Module):  # same topology as the reference's model.py:9-26
+        def __init__(self):
+            torch.nn.Module.__init__(self)
+            m = PLANES[0]
+            self.sparseModel = scn.Sequential().add(
+                scn.InputLayer(3, 4096, mode=4)).add(
+                scn.SubmanifoldConvolution(3, 3, m, 3, False)).add(
+                scn.UNet(3, 2, PLANES, True)).add(
+                scn.BatchNormReLU(m)).add(
+                scn.OutputLayer(3))
+            self.linear = torch.nn.Linear(m, 20)
+
+        def forward(self, x, increment=False):
+            return self.linear(self.sparseModel(x, increment))
+    torch.manual_seed(0)
+    return NaiveUNet().eval()
+
+
+def make_scene(seed, voxels):
+    import numpy as np
+    from insconv import synth
+    coords = synth.room(seed, target=voxels)
+    feats = synth.rgb(seed, coords.shape[0])
+    new_c, pert = synth.sweep_frame(coords, frame=50, seed=seed)
+    # 5 % of the sites change: new surface voxels plus 1 % perturbed colours
+    want = int(0.05 * coords.shape[0])
+    new_c = new_c[:max(want - pert.shape[0], 1)]
+    rng = np.random.RandomState(seed + 99)
+    inc_coords = np.concatenate([new_c, coords[pert]], 0)
+    inc_feats = np.concatenate([synth.rgb(seed + 1, new_c.shape[0]),
+                                feats[pert] + rng.normal(0, 0.05, (pert.shape[0], 3)).astype(np.float32)], 0)
+    return coords, feats, inc_coords, inc_feats.astype(np.float32)
+
+
+class ClockSampler(object):
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+class SscTimer(object):
+    """CUDA-event pairs around every SubmanifoldConvolution_updateOutput call, on the launching stream."""
+
+    def __init__(self, scn, torch):
+        self.scn, self.torch = scn, torch
+        self.records = []
+        self.enabled = False
+        self.orig = scn.SCN.SubmanifoldConvolution_updateOutput
+
+        def wrapped(size, filt, meta, x, out, w, b, dil):
+            if not self.enabled:
+                return self.orig(size, filt, meta, x, out, w, b, dil)
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            madds = self.orig(size, filt, meta, x, out, w, b, dil)
+            e1.record()
+            self.records.append((x.shape[0], w.shape[1], w.shape[2], madds, e0, e1))
+            return madds
+        scn.SCN.SubmanifoldConvolution_updateOutput = wrapped
+
+    def summary(self, hbm_peak, tensor_peak_tf32):
+        shapes = {}
+        for n, ci, co, madds, e0, e1 in self.records:
+            ms = e0.elapsed_time(e1)
+            s = shapes.setdefault((n, ci, co), {"ms": 0.0, "launches": 0, "pairs": madds / (ci * co)})
+            s["ms"] += ms
+            s["launches"] += 1
+        out = []
+        for (n, ci, co), s in shapes.items():
+            t = s["ms"] / s["launches"] * 1e-3
+            byts = 4.0 * n * ci + 4.0 * n * co + 8.0 * s["pairs"] + 4.0 * 27 * ci * co
+            flops = 2.0 * s["pairs"] * ci * co
+            out.append({"sites": n, "n_in": ci, "n_out": co, "pairs": int(s["pairs"]), "launches": s["launches"],
+                        "us_per_launch": t * 1e6, "total_ms": s["ms"], "GBps": byts / t / 1e9,
+                        "TFLOPs": flops / t / 1e12, "hbm_frac": byts / t / 1e9 / hbm_peak,
+                        "tensor_frac": flops / t / 1e12 / tensor_peak_tf32, "bytes": byts, "flops": flops})
+        out.sort(key=lambda r: -r["total_ms"])
+        return out
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def cpu_reference(voxels, steps, warmup, seed=0):
+    """The CPU restatement of the reference (oracle/) on the host cores: full UNet frame on a room."""
+    import torch
+    torch.set_num_threads(os.cpu_count())
+    import sparseconvnet as scn
+    from oracle.scn_graph import GraphRunner
+    model = build_model(scn, torch)
+    coords, feats, _, _ = make_scene(seed, voxels)
+    x = [torch.from_numpy(coords), torch.from_numpy(feats)]
+    times, layers = [], 0
+    for i in range(warmup + steps):
+        runner = GraphRunner(model)
+        t0 = time.perf_counter()
+        runner._run(model.linear, runner._run(model.sparseModel, x, False), False)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+        layers = voxel_layers_of(runner)
+    t = sum(times) / len(times)
+    return {"value": layers / t, "ms_per_step": t * 1e3, "voxels": int(coords.shape[0]), "voxel_layers": layers,
+            "cores": os.cpu_count()}
+
+
+def voxel_layers_of(runner):
+    total = 0
+    # the oracle runner keeps the input tensor of every SubmanifoldConvolution it evaluated
+    import sparseconvnet as scn
+    for m in runner.root.modules():
+        if isinstance(m, scn.SubmanifoldConvolution) and id(m) in runner.saved:
+            total += int(runner.saved[id(m)].features.shape[0])
+    return total
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--voxels", type=int, default=250000)
+    ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "fp32"), choices=["fp32", "tf32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        sample_voxels = min(args.voxels, 120000)
+        r = cpu_reference(sample_voxels, max(1, min(args.steps, 3)), min(args.warmup, 1))
+        line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": {"workload": WORKLOAD, "voxels": r["voxels"]},
+                "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
+                                 "sample": "one full UNet frame on a %d-voxel room (same generator, thinned), torch CPU "
+                                           "threads = cores" % r["voxels"]},
+                "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return 0
+
+    import numpy as np
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: this library has no CPU fallback"}))
+        return 1
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    import sparseconvnet as scn
+    scn.set_precision(args.precision)
+    model = build_model(scn, torch).to(dev)
+    coords, feats, inc_c, inc_f = make_scene(rank, args.voxels)
+    d_coords, d_feats = torch.from_numpy(coords).to(dev), torch.from_numpy(feats).to(dev)
+    d_inc_c, d_inc_f = torch.from_numpy(inc_c).to(dev), torch.from_numpy(inc_f).to(dev)
+    h_coords, h_feats = torch.from_numpy(coords).pin_memory(), torch.from_numpy(feats).pin_memory()
+    timer = SscTimer(scn, torch)
+    hbm_peak, bf16_peak, peak_kind = load_peaks()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(v):
+        if dist is None:
+            return v
+        t = torch.tensor([float(v)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = scn.SCN.launch_count()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1) / steps), (scn.SCN.launch_count() - l0) // steps
+
+    # ---- value: full frame, inputs resident in HBM ------------------------------------------------
+    out_holder = {}
+
+    def full_frame():
+        out_holder["y"] = model([d_coords, d_feats])
+
+    full_frame()
+    torch.cuda.synchronize()
+    ssc_mods = [m for m in model.modules() if isinstance(m, scn.SubmanifoldConvolution)]
+    voxel_layers = sum(int(m.save_input_feats.shape[0]) for m in ssc_mods)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    timer.enabled = True
+    ms_full, launches = timed(full_frame, args.steps, args.warmup)
+    timer.enabled = False
+    clocks = sampler.stop() if rank == 0 else None
+    # drop the warm-up records: keep the last steps * 53
+    timer.records = timer.records[-args.steps * len(ssc_mods):]
+    total_layers = sum_over_ranks(voxel_layers)
+    value = total_layers / (ms_full * 1e-3)
+
+    # ---- incremental frame (reference semantics) against the saved full frame -----------------------
+    def incre_frame():
+        out_holder["y1"] = model([d_inc_c, d_inc_f], True)
+
+    ms_incre, launches_incre = timed(incre_frame, args.steps, args.warmup)
+
+    # ---- e2e: pinned host inputs, host read of the result -------------------------------------------
+    def e2e_frame():
+        y = model([h_coords, h_feats.to(dev, non_blocking=True)])
+        out_holder["host"] = y.to("cpu")
+
+    ms_e2e, _ = timed(e2e_frame, args.steps, args.warmup)
+    e2e_value = total_layers / (ms_e2e * 1e-3)
+    h2d = coords.nbytes + feats.nbytes
+    d2h = int(out_holder["y"].numel()) * 4
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return 0
+
+    shapes = timer.summary(hbm_peak, bf16_peak / 2.0)
+    top = shapes[0] if shapes else None
+    roofline = None
+    if top:
+        hbm_bound = top["n_in"] <= 64
+        roofline = {"kernel": "gather-GEMM %s, SSC %d->%d on %d sites" % (args.precision, top["n_in"], top["n_out"],
+                                                                           top["sites"]),
+                    "bound": "hbm" if hbm_bound else "tensor",
+                    "achieved": top["GBps"] if hbm_bound else top["TFLOPs"],
+                    "peak": hbm_peak if hbm_bound else bf16_peak / 2.0,
+                    "unit": "GB/s" if hbm_bound else "TFLOP/s",
+                    "frac": top["hbm_frac"] if hbm_bound else top["tensor_frac"],
+                    "peak_kind": peak_kind + (" HBM copy" if hbm_bound else " bf16/2 taken as the tf32 peak"),
+                    "us_per_launch": top["us_per_launch"], "launches": top["launches"],
+                    "algorithmic_bytes": top["bytes"], "algorithmic_flops": top["flops"],
+                    "traffic": None}
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_full, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32" if args.precision == "fp32" else "tf32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "voxels_per_scene": int(coords.shape[0]), "scenes": world,
+                       "voxel_layers_per_scene": voxel_layers, "precision": args.precision,
+                       "l2": "no flush: one frame streams ~1.5 GB of activations and maps, far above the 126 MB L2"},
+            "incremental": {"ms_per_frame": ms_incre, "changed_points": int(inc_c.shape[0]),
+                            "changed_frac": float(inc_c.shape[0]) / coords.shape[0],
+                            "semantics": "reference (insert-only, no dilation)", "launches": int(launches_incre)},
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(h2d),
+                    "d2h_bytes_per_step": int(d2h)},
+            "gpu_launches": int(launches) * args.steps, "clocks": clocks, "roofline": roofline,
+            "ssc_by_shape": [{k: (round(v, 4) if isinstance(v, float) else v) for k, v in s.items()
+                              if k not in ("bytes", "flops")} for s in shapes[:8]]}
+    if world == 1 and not args.no_cpu_baseline:
+        sample = min(args.voxels, 120000)
+        r = cpu_reference(sample, 2, 1)
+        line["cpu_baseline"] = {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
+                                "ms_per_step": r["ms_per_step"],
+                                "sample": "one full UNet frame on a %d-voxel room (same generator, thinned), "
+                                          "torch CPU threads = cores" % r["voxels"]}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

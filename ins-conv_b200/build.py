@@ -69,12 +69,12 @@ def build_lib(force=False, verbose=False, ptxas_info=False):
 
 
 def build_ext(force=False, verbose=False):
-    import torch
-    from torch.utils import cpp_extension as ce
     src = os.path.join(CSRC, "scn_ext.cpp")
     out = ext_path()
     if not (force or _stale(out, [src, os.path.join(INCLUDE, "insconv_b200.h"), LIB])):
         return out
+    import torch
+    from torch.utils import cpp_extension as ce
     inc = ce.include_paths("cuda") if "device_type" in ce.include_paths.__code__.co_varnames else ce.include_paths(True)
     cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", src, "-o", out,
            "-DTORCH_EXTENSION_NAME=SCN", "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI),
