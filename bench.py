@@ -131,19 +131,25 @@ class SscTimer(object):
         self.scn, self.torch = scn, torch
         self.records = []
         self.enabled = False
+        self.pool = []
         self.orig = scn.SCN.SubmanifoldConvolution_updateOutput
 
         def wrapped(size, filt, meta, x, out, w, b, dil):
             if not self.enabled:
                 return self.orig(size, filt, meta, x, out, w, b, dil)
-            e0 = torch.cuda.Event(enable_timing=True)
-            e1 = torch.cuda.Event(enable_timing=True)
+            if len(self.pool) < 2:
+                self.reserve(64)
+            e0, e1 = self.pool.pop(), self.pool.pop()
             e0.record()
             madds = self.orig(size, filt, meta, x, out, w, b, dil)
             e1.record()
             self.records.append((x.shape[0], w.shape[1], w.shape[2], madds, e0, e1))
             return madds
         scn.SCN.SubmanifoldConvolution_updateOutput = wrapped
+
+    def reserve(self, n):
+        """Creates events ahead of the timed region (event creation is the expensive part)."""
+        self.pool.extend(self.torch.cuda.Event(enable_timing=True) for _ in range(n))
 
     def summary(self, hbm_peak, tensor_peak_tf32):
         shapes = {}
@@ -216,8 +222,12 @@ def main():
     ap.add_argument("--voxels", type=int, default=250000)
     ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "fp32"), choices=["fp32", "tf32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--legs", default="full,incre,e2e", help="which timed legs to run (profiling aid)")
+    ap.add_argument("--profile", action="store_true", help="allow fewer than 3 warm-up steps (numbers are not bench values)")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "b200" and not args.profile:
+        args.warmup = max(args.warmup, 3)
+    legs = set(args.legs.split(","))
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -305,6 +315,7 @@ def main():
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    timer.reserve(2 * len(ssc_mods) * (args.steps + args.warmup) + 8)
     timer.enabled = True
     ms_full, launches = timed(full_frame, args.steps, args.warmup)
     timer.enabled = False
@@ -318,14 +329,14 @@ def main():
     def incre_frame():
         out_holder["y1"] = model([d_inc_c, d_inc_f], True)
 
-    ms_incre, launches_incre = timed(incre_frame, args.steps, args.warmup)
+    ms_incre, launches_incre = timed(incre_frame, args.steps, args.warmup) if "incre" in legs else (float("nan"), 0)
 
     # ---- e2e: pinned host inputs, host read of the result -------------------------------------------
     def e2e_frame():
         y = model([h_coords, h_feats.to(dev, non_blocking=True)])
         out_holder["host"] = y.to("cpu")
 
-    ms_e2e, _ = timed(e2e_frame, args.steps, args.warmup)
+    ms_e2e, _ = timed(e2e_frame, args.steps, args.warmup) if "e2e" in legs else (float("nan"), 0)
     e2e_value = total_layers / (ms_e2e * 1e-3)
     h2d = coords.nbytes + feats.nbytes
     d2h = int(out_holder["y"].numel()) * 4

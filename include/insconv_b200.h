@@ -63,6 +63,10 @@ SCN_API const char *scn_last_error(void);
 SCN_API const char *scn_version(void);
 /* Number of kernel launches issued by this library since load (all threads). */
 SCN_API uint64_t scn_launch_count(void);
+/* Synchronises `stream` and reports errors that kernels can only flag asynchronously (a bounded
+ * wait inside a tensor-core kernel that ran out).  No counterpart in the reference, whose kernels
+ * have no such waits. */
+SCN_API int scn_check_errors(void *stream);
 /* 32: width of a rulebook entry.  Replaces n_rulebook_bits (pybind.cpp:304). */
 SCN_API int scn_n_rulebook_bits(void);
 

@@ -58,7 +58,7 @@ def build_lib(force=False, verbose=False, ptxas_info=False):
         s = os.path.join(CSRC, src)
         o = os.path.join(CSRC, src.replace(".cu", ".o"))
         if force or _stale(o, [s] + headers):
-            cmd = [_nvcc()] + NVCC_FLAGS + ["-I" + INCLUDE, "-I" + CSRC, "-c", s, "-o", o]
+            cmd = [_nvcc()] + NVCC_FLAGS + os.environ.get("INSCONV_NVCC_FLAGS", "").split() + ["-I" + INCLUDE, "-I" + CSRC, "-c", s, "-o", o]
             if ptxas_info:
                 cmd += ["-Xptxas", "-v"]
             _run(cmd, verbose or ptxas_info)

@@ -160,6 +160,10 @@ const char *scn_last_error(void) { return t_error.c_str(); }
 const char *scn_version(void) { return "insconv_b200 0.1 (sm_100a)"; }
 uint64_t scn_launch_count(void) { return g_launches.load(); }
 int scn_n_rulebook_bits(void) { return 32; }
+int scn_check_errors(void *stream) {
+  SCN_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  return tc_check_errors((cudaStream_t)stream);
+}
 
 int scn_metadata_create(scn_metadata **out) {
   if (!out) return fail(SCN_E_INVALID, "null output pointer");

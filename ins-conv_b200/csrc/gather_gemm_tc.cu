@@ -1,12 +1,407 @@
-// Tensor-core (tcgen05, kind::tf32) gather-GEMM.  Not built yet: every shape reports "not handled"
-// and the caller runs the fp32 kernel instead.
+// Tensor-core gather-GEMM for sm_100a: tcgen05.mma kind::tf32 with the accumulator in TMEM.
+//
+//     out[o] = init(o) + sum_k in[ map[k][o] ] * W[k]           (same contract as the fp32 kernel)
+//
+// One CTA owns 128 consecutive output rows and all n_out <= 256 output planes; the accumulator tile
+// [128 x n_out] fp32 lives in tensor memory.  The reduction runs over (offset k, 32-plane block kb):
+// for every step the 128 threads stage
+//     A = the 128 gathered input rows x 32 planes (16 KB)  -> K-major, 128-byte swizzle
+//     B = W[k]^T, n_out rows x 32 planes                    -> K-major, 128-byte swizzle
+// with 16-byte cp.async copies (missing neighbours are zero-filled without touching memory), and one
+// thread issues four tcgen05.mma (K = 8 each) on the staged tile.  A ring of stages keeps several steps
+// of copies in flight while the tensor core works; tcgen05.commit signals an mbarrier when the MMAs
+// that read a stage have retired, which is what lets the stage be refilled.  Offsets for which no row
+// of the tile has a neighbour are skipped altogether.  The epilogue reads TMEM with tcgen05.ld (one
+// row per thread), adds the bias or the previous output and writes each output row exactly once.
+//
+// The weights are transposed once per call to [volume][n_out][n_in] by a small kernel, so that both
+// operands are K-major (the layout in which 32-bit operands take the plain 128-byte swizzle).
+//
+// fp32 inputs are consumed as tf32 (the low 13 mantissa bits are ignored), accumulation is fp32.
+// Every wait on an mbarrier is bounded; a wait that runs out sets an error word that the host reads
+// at its next synchronisation, and the kernel still releases its tensor memory before returning.
 #include "internal.h"
 
 namespace scn {
 
-int gather_gemm_tf32(const float *, int64_t, const int32_t *, int, int64_t, const float *, const float *, float *,
-                     int64_t, int64_t, int64_t, int, cudaStream_t, bool *handled) {
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kThreads = 128;
+constexpr int kABytes = kTileM * 128;  // 128 rows x 32 fp32
+constexpr uint32_t kSpinLimit = 1u << 20;
+
+__device__ unsigned int g_tc_error = 0;  // 1: an mbarrier wait ran out
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and records the failure) when the phase never completes.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *failed) {
+  if (*failed) return false;
+  for (uint32_t i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  *failed = 1;
+  atomicOr(&g_tc_error, 1u);
+  return false;
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+// shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100)
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // version
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+// instruction descriptor: D fp32, A/B tf32, both K-major, M = 128, N = n
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (0u << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(kTileM >> 4) << 24);
+}
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct Ctl {                 // control block at the start of dynamic shared memory
+  unsigned long long done[8];  // per stage: MMAs that read the stage have retired
+  unsigned long long acc;      // all MMAs of the tile have retired
+  uint32_t tmem_base;
+  int failed;
+  int nk;                      // offsets with at least one valid row
+  int klist[32];
+};
+
+// STAGES ring slots; copies run AHEAD steps in front of the tensor core, which leaves the MMAs of a
+// step STAGES - AHEAD iterations to retire before their slot is refilled.
+// gridDim.y > 1 splits the reduction steps of a tile over several CTAs (few tiles, long reductions):
+// each CTA then writes its partial tile to `partial` [gridDim.y][tiles * 128][Cout] and a second kernel
+// adds the partials in a fixed order.
+template <int STAGES, int AHEAD>
+__global__ void __launch_bounds__(kThreads)
+k_gather_gemm_tf32(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K,
+                   long long n_out, const float *__restrict__ W, const float *__restrict__ bias,
+                   float *__restrict__ out, long long out_stride, int Cin, int Cout, int accumulate,
+                   uint32_t tmem_cols, float *__restrict__ partial) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // layout: [stages: A (16 KB) + B (Cout*128 B)] [Ctl] [s_map: K*128 ints]
+  const uint32_t stage_bytes = kABytes + (uint32_t)Cout * 128u;
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Ctl *ctl = reinterpret_cast<Ctl *>(smem + (size_t)STAGES * stage_bytes);
+  int *s_map = reinterpret_cast<int *>(ctl + 1);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long long row0 = (long long)blockIdx.x * kTileM;
+  const int KB = Cin >> 5;
+
+  // ---- neighbour rows of the tile, and the list of offsets that have any -------------------------
+  if (tid == 0) {
+    ctl->failed = 0;
+    ctl->nk = 0;
+  }
+  __syncthreads();
+  for (int k = 0; k < K; ++k) {
+    const long long row = row0 + tid;
+    int v = -1;
+    if (row < n_out) v = map ? __ldg(map + (long long)k * n_out + row) : (int)row;
+    s_map[k * kTileM + tid] = v;
+    if (__syncthreads_or(v >= 0)) {
+      if (tid == 0) ctl->klist[ctl->nk++] = k;
+    }
+  }
+  __syncthreads();
+  const int nk = ctl->nk;
+  const int Tall = nk * KB;
+  const int t0 = (int)(((long long)Tall * blockIdx.y) / gridDim.y);
+  const int T = (int)(((long long)Tall * (blockIdx.y + 1)) / gridDim.y) - t0;
+  float *pdst = partial ? partial + ((long long)blockIdx.y * gridDim.x * kTileM + (long long)blockIdx.x * kTileM) * Cout : nullptr;
+  if (T == 0) {  // nothing to reduce here: the tile (or this share of it) contributes zero
+    if (pdst) {
+      for (int i = tid; i < kTileM * Cout; i += kThreads) pdst[i] = 0.f;
+    } else if (!accumulate) {
+      for (long long i = tid; i < (long long)kTileM * Cout; i += kThreads) {
+        const long long row = row0 + i / Cout;
+        const int c = (int)(i % Cout);
+        if (row < n_out) out[row * out_stride + c] = bias ? __ldg(bias + c) : 0.f;
+      }
+    }
+    return;
+  }
+
+  // ---- barriers and tensor memory ----------------------------------------------------------------
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(smem_u32(&ctl->done[s]), 1);
+    mbar_init(smem_u32(&ctl->acc), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&ctl->tmem_base)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = ctl->tmem_base;
+  const uint32_t idesc = instr_desc(Cout);
+  const uint32_t smem_base = smem_u32(smem);
+  volatile int *failed = &ctl->failed;
+
+  // stage the operands of reduction step `it` into ring slot `slot`
+  auto load_step = [&](int it, int slot) {
+    const int k = ctl->klist[(t0 + it) / KB];
+    const int kb = (t0 + it) % KB;
+    const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
+    const uint32_t b_base = a_base + kABytes;
+    const int *mrow = s_map + k * kTileM;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int q = tid + kThreads * i;
+      const int r = q >> 3, c = q & 7;
+      const int src = mrow[r];
+      const float *p = in + (src >= 0 ? (long long)src * in_stride + (kb << 5) + (c << 2) : 0);
+      const uint32_t dst = a_base + (uint32_t)((r >> 3) << 10) + (uint32_t)((r & 7) << 7) + (uint32_t)((c ^ (r & 7)) << 4);
+      cp_async16(dst, p, src >= 0 ? 16u : 0u);
+    }
+    // transposed weights Wt[k][n][Cin]: row n of the tile is 32 consecutive planes of Wt[k][n]
+    const float *wk = W + (long long)k * Cout * Cin + (kb << 5);
+    const int total = Cout << 3;
+    for (int q = tid; q < total; q += kThreads) {
+      const int n = q >> 3, c = q & 7;
+      const uint32_t dst = b_base + (uint32_t)((n >> 3) << 10) + (uint32_t)((n & 7) << 7) + (uint32_t)((c ^ (n & 7)) << 4);
+      cp_async16(dst, wk + (long long)n * Cin + (c << 2), 16u);
+    }
+  };
+
+  // ---- software pipeline --------------------------------------------------------------------------
+  for (int st = 0; st < AHEAD; ++st) {
+    if (st < T) load_step(st, st % STAGES);
+    cp_async_commit();
+  }
+  for (int it = 0; it < T; ++it) {
+    cp_async_wait<AHEAD - 1>();  // this thread's copies of step `it` have landed
+    fence_async_proxy();         // make them visible to the tensor core (async proxy)
+    __syncthreads();
+    const int slot = it % STAGES;
+    if (tid == 0 && !*failed) {
+      tc_fence_after();
+      const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
+      const uint32_t b_base = a_base + kABytes;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint64_t a_desc = smem_desc(a_base + j * 32, 16, 1024);
+        const uint64_t b_desc = smem_desc(b_base + j * 32, 16, 1024);
+        mma_tf32(tmem_d, a_desc, b_desc, idesc, (it > 0 || j > 0) ? 1u : 0u);
+      }
+      mma_commit(smem_u32(&ctl->done[slot]));
+      if (it == T - 1) mma_commit(smem_u32(&ctl->acc));
+    }
+    // refill: step it+AHEAD goes into the slot last read by step it+AHEAD-STAGES
+    const int nxt = it + AHEAD;
+    if (nxt < T) {
+      const int prev = nxt - STAGES;
+      if (prev >= 0) mbar_wait(smem_u32(&ctl->done[prev % STAGES]), (uint32_t)((prev / STAGES) & 1), failed);
+      if (!*failed) load_step(nxt, nxt % STAGES);
+    }
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
+
+  // ---- epilogue: TMEM -> registers -> global ------------------------------------------------------
+  mbar_wait(smem_u32(&ctl->acc), 0, failed);
+  __syncthreads();
+  const bool ok = !*failed;  // block-uniform: tcgen05.ld below is warp-collective
+  tc_fence_after();
+  if (ok) {
+    const long long row = row0 + warp * 32 + lane;
+    for (int c0 = 0; c0 < Cout; c0 += 32) {
+      float v[32];
+      tmem_ld32(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);  // warp-collective: all lanes take part
+      if (pdst) {
+        float *o = pdst + (long long)(warp * 32 + lane) * Cout + c0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else if (row < n_out) {
+        float *o = out + row * out_stride + c0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          float4 r = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          if (accumulate) {
+            const float4 old = *reinterpret_cast<const float4 *>(o + j);
+            r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
+          } else if (bias) {
+            r.x += __ldg(bias + c0 + j); r.y += __ldg(bias + c0 + j + 1);
+            r.z += __ldg(bias + c0 + j + 2); r.w += __ldg(bias + c0 + j + 3);
+          }
+          *reinterpret_cast<float4 *>(o + j) = r;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+  }
+}
+
+// W [vol][Cin][Cout] -> Wt [vol][Cout][Cin]; 32x32 tiles through shared memory
+__global__ void k_transpose_weights(const float *__restrict__ W, float *__restrict__ Wt, int Cin, int Cout) {
+  __shared__ float tile[32][33];
+  const float *w = W + (long long)blockIdx.z * Cin * Cout;
+  float *wt = Wt + (long long)blockIdx.z * Cin * Cout;
+  const int ci0 = blockIdx.y * 32, co0 = blockIdx.x * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) tile[r][threadIdx.x] = w[(long long)(ci0 + r) * Cout + co0 + threadIdx.x];
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) wt[(long long)(co0 + r) * Cin + ci0 + threadIdx.x] = tile[threadIdx.x][r];
+}
+
+// out[r][c] = (accumulate ? out : bias) + sum_z partial[z][r][c], z ascending
+__global__ void k_splitk_reduce(const float *__restrict__ partial, int Z, long long rows_padded, long long n_out, int Cout,
+                                const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
+                                int accumulate) {
+  const int cv = Cout >> 2;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_out * cv) return;
+  const long long r = i / cv;
+  const int c = (int)(i % cv) << 2;
+  float4 acc;
+  float *o = out + r * out_stride + c;
+  if (accumulate) acc = *reinterpret_cast<const float4 *>(o);
+  else if (bias) acc = __ldg(reinterpret_cast<const float4 *>(bias + c));
+  else acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int z = 0; z < Z; ++z) {
+    const float4 p = __ldg(reinterpret_cast<const float4 *>(partial + ((long long)z * rows_padded + r) * Cout + c));
+    acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+  }
+  *reinterpret_cast<float4 *>(o) = acc;
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+// Reads and clears the error word of the tensor-core kernels (synchronises the stream).
+int tc_check_errors(cudaStream_t s) {
+  unsigned int e = 0, zero = 0;
+  SCN_CUDA(cudaMemcpyFromSymbolAsync(&e, g_tc_error, sizeof(e), 0, cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  if (e) {
+    SCN_CUDA(cudaMemcpyToSymbolAsync(g_tc_error, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, s));
+    return fail(SCN_E_CUDA, "a tensor-core kernel gave up waiting on an mbarrier; its output is invalid");
+  }
+  return SCN_OK;
+}
+
+int gather_gemm_tf32(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *W,
+                     const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate,
+                     cudaStream_t s, bool *handled) {
   *handled = false;
+  if (Cin % 32 != 0 || Cout % 32 != 0 || Cout > 256 || K > 27) return SCN_OK;
+  if (in_stride % 4 != 0 || out_stride % 4 != 0 || !aligned16(in) || !aligned16(W) || !aligned16(out)) return SCN_OK;
+  if (bias && !aligned16(bias)) return SCN_OK;
+  const size_t stage_bytes = (size_t)kABytes + (size_t)Cout * 128;
+  const size_t fixed = sizeof(Ctl) + (size_t)K * kTileM * sizeof(int) + 1024;  // + alignment slack
+  // two CTAs per SM when four stages fit in half an SM's shared memory, else as many stages as fit
+  int stages = 4;
+  if (4 * stage_bytes + fixed > 112 * 1024) {
+    stages = (int)((200 * 1024 - fixed) / stage_bytes);
+    if (stages > 6) stages = 6;
+  }
+  if (stages < 3) return SCN_OK;
+  const size_t smem = (size_t)stages * stage_bytes + fixed;
+  uint32_t cols = 32;
+  while (cols < (uint32_t)Cout) cols <<= 1;
+  const long long tiles = (n_out + kTileM - 1) / kTileM;
+  // few tiles and a long reduction: share the steps of a tile among Z CTAs
+  const int steps_max = K * (int)(Cin / 32);
+  int Z = 1;
+  if (tiles < 148) {
+    Z = (int)((2 * 148 + tiles - 1) / tiles);
+    if (Z > steps_max / 2) Z = steps_max / 2;
+    if (Z > 64) Z = 64;
+    if (Z < 1) Z = 1;
+  }
+  float *Wt = nullptr, *partial = nullptr;
+  SCN_TRY(dev_alloc_t(&Wt, (size_t)K * Cin * Cout, s));
+  if (Z > 1) SCN_TRY(dev_alloc_t(&partial, (size_t)Z * tiles * kTileM * Cout, s));
+  k_transpose_weights<<<dim3((unsigned)(Cout / 32), (unsigned)(Cin / 32), (unsigned)K), dim3(32, 8), 0, s>>>(W, Wt, (int)Cin,
+                                                                                                          (int)Cout);
+  SCN_LAUNCHED();
+  const dim3 grid((unsigned)tiles, (unsigned)Z);
+#define SCN_TC_LAUNCH(S, A)                                                                                          \
+  do {                                                                                                               \
+    SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tf32<S, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    k_gather_gemm_tf32<S, A><<<grid, kThreads, smem, s>>>(in, in_stride, map, K, n_out, Wt, bias, out, out_stride,    \
+                                                           (int)Cin, (int)Cout, accumulate, cols, partial);          \
+  } while (0)
+  if (stages >= 6) SCN_TC_LAUNCH(6, 3);
+  else if (stages == 5) SCN_TC_LAUNCH(5, 3);
+  else if (stages == 4) SCN_TC_LAUNCH(4, 2);
+  else SCN_TC_LAUNCH(3, 2);
+#undef SCN_TC_LAUNCH
+  SCN_LAUNCHED();
+  if (Z > 1) {
+    const long long work = n_out * (Cout / 4);
+    k_splitk_reduce<<<(unsigned)((work + 255) / 256), 256, 0, s>>>(partial, Z, tiles * kTileM, n_out, (int)Cout, bias, out,
+                                                                  out_stride, accumulate);
+    SCN_LAUNCHED();
+  }
+  dev_free(partial, s);
+  dev_free(Wt, s);
+  *handled = true;
   return SCN_OK;
 }
 

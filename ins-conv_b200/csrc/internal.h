@@ -116,6 +116,8 @@ int build_incre_up(const Grid &coarse, const int32_t *pe_coarse, const int32_t *
 int gather_gemm(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *W,
                 const float *bias, float *out, int64_t out_stride, int64_t n_in, int64_t n_planes_out,
                 int accumulate, int precision, cudaStream_t s);
+// reads and clears the error word of the tensor-core kernels; synchronises s
+int tc_check_errors(cudaStream_t s);
 int bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,
                const float *mean, const float *var, const float *gamma, const float *beta, float eps,
                float leak, const int32_t *pre_exist, const float *pre_out, const float *pre_in,

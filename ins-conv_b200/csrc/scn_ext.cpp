@@ -364,6 +364,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
   mod.def("set_precision", &set_precision, "arithmetic of the convolution kernels: 'fp32' or 'tf32'");
   mod.def("get_precision", &get_precision);
   mod.def("launch_count", []() { return scn_launch_count(); });
+  mod.def("check_errors", []() { check(scn_check_errors((void *)c10::cuda::getCurrentCUDAStream().stream()), "check_errors"); },
+          "synchronise the current stream and raise if a kernel flagged an asynchronous error");
   for (const char *name :
        {"SubmanifoldConvolution_backward", "Convolution_backward", "Deconvolution_backward",
         "BatchNormalization_backward", "NetworkInNetwork_updateGradInput", "NetworkInNetwork_accGradParameters",

@@ -37,6 +37,7 @@ PROTOTYPES = {
     "scn_version": (C.c_char_p, []),
     "scn_launch_count": (C.c_uint64, []),
     "scn_n_rulebook_bits": (_int, []),
+    "scn_check_errors": (_int, [_p]),
     "scn_metadata_create": (_int, [C.POINTER(_p)]),
     "scn_metadata_destroy": (None, [_p]),
     "scn_metadata_clear": (_int, [_p, _p]),
@@ -302,6 +303,11 @@ def _split(pairs, counts):
         out.append(pairs[o:o + int(c)])
         o += int(c)
     return out
+
+
+def check_errors():
+    """Synchronises the current stream and raises if a kernel flagged an asynchronous error."""
+    call("scn_check_errors", _stream())
 
 
 def bn_forward(x, mean, var, gamma, beta, eps, leak):

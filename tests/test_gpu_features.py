@@ -134,3 +134,44 @@ def test_linearity_at_full_size(cuda):
     w0[13] = w[13]
     c0, _ = m.ssc_forward(4096, x, w0)
     close(c0, (x @ w[13]).cpu(), 1e-4)
+
+
+# ---- tensor-core (tcgen05, tf32) path: 2e-2 relative per layer -------------------------------------
+TF32_TOL = 2e-2
+
+
+@pytest.mark.parametrize("n_in,n_out,bias", [(32, 32, False), (64, 32, True), (32, 64, False), (96, 96, True),
+                                             (224, 224, False), (448, 224, False)])
+def test_ssc_forward_tf32(cuda, n_in, n_out, bias):
+    m, g = _scene(cuda, 0)
+    rng = np.random.RandomState(n_in * 1000 + n_out + 1)
+    x = rng.randn(g.n, n_in).astype(np.float32)
+    w = synth.kaiming_uniform(rng, 27, n_in, n_out)
+    b = rng.randn(n_out).astype(np.float32) if bias else None
+    want = O.conv_forward(x, w, O.ssc_rules(g), g.n, b)
+    got, _ = m.ssc_forward(128, torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda),
+                           torch.from_numpy(b).to(cuda) if bias else None, precision=cabi.PREC_TF32)
+    cabi.check_errors()
+    close(got, want, TF32_TOL)
+    # tf32 keeps 10 mantissa bits: the error should in fact be far below the stated bar
+    err = float((got.cpu() - want).abs().max()) / float(want.abs().max())
+    assert err < 5e-3, err
+
+
+def test_conv_deconv_nin_tf32(cuda):
+    m, g = _scene(cuda, 1)
+    rng = np.random.RandomState(17)
+    coarse, rules = O.conv2_rules(g)
+    x = rng.randn(g.n, 32).astype(np.float32)
+    w = synth.kaiming_uniform(rng, 8, 32, 64)
+    got, _ = m.conv_forward(128, 64, torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda), None, cabi.PREC_TF32)
+    close(got, O.conv_forward(x, w, rules, coarse.n, None), TF32_TOL)
+    wd = synth.kaiming_uniform(rng, 8, 64, 32)
+    y = rng.randn(coarse.n, 64).astype(np.float32)
+    got, _ = m.deconv_forward(64, 128, torch.from_numpy(y).to(cuda), torch.from_numpy(wd).to(cuda), None, cabi.PREC_TF32)
+    close(got, O.conv_forward(y, wd, rules, g.n, None, reverse=True), TF32_TOL)
+    wn = (rng.randn(64, 32) * np.sqrt(2.0 / 64)).astype(np.float32)
+    z = rng.randn(5000, 64).astype(np.float32)
+    got, _ = cabi.nin_forward(torch.from_numpy(z).to(cuda), torch.from_numpy(wn).to(cuda), None, cabi.PREC_TF32)
+    close(got, O.nin_forward(z, wn), TF32_TOL)
+    cabi.check_errors()
