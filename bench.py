@@ -171,6 +171,44 @@ class SscTimer(object):
         return out
 
 
+def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
+    """One submanifold convolution on the room, rulebook cached, through the C ABI: the 'active voxels/s per
+    SSC layer' figure in isolation.  L2 is flushed between launches; each launch is timed with CUDA events."""
+    import torch
+    from insconv import cabi
+    prec = cabi.PREC_TF32 if args.precision == "tf32" else cabi.PREC_FP32
+    coords, _, _, _ = make_scene(0, args.voxels)
+    m = cabi.Metadata()
+    n = m.input_layer_build(4096, torch.from_numpy(coords).to(dev), mode=4)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn(n, args.n_in, generator=g).to(dev)
+    w = (torch.randn(27, args.n_in, args.n_out, generator=g) * (2.0 / (27 * args.n_in)) ** 0.5).to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out, madds = m.ssc_forward(4096, x, w, None, prec)
+    times = []
+    for i in range(args.warmup + args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out, madds = m.ssc_forward(4096, x, w, None, prec)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= args.warmup:
+            times.append(e0.elapsed_time(e1) * 1e-3)
+    cabi.check_errors()
+    t = sum(times) / len(times)
+    pairs = madds / (args.n_in * args.n_out)
+    byts = 4.0 * n * (args.n_in + args.n_out) + 8.0 * pairs + 4.0 * 27 * args.n_in * args.n_out
+    flops = 2.0 * madds
+    hbm_bound = args.n_in <= 64
+    return {"sites": int(n), "n_in": args.n_in, "n_out": args.n_out, "pairs": int(pairs), "us_per_launch": t * 1e6,
+            "voxels_per_s": n / t, "GBps": byts / t / 1e9, "TFLOPs": flops / t / 1e12,
+            "roofline": {"bound": "hbm" if hbm_bound else "tensor", "achieved": byts / t / 1e9 if hbm_bound else flops / t / 1e12,
+                         "peak": hbm_peak if hbm_bound else bf16_peak / 2, "unit": "GB/s" if hbm_bound else "TFLOP/s",
+                         "frac": (byts / t / 1e9 / hbm_peak) if hbm_bound else (flops / t / 1e12 / (bf16_peak / 2)),
+                         "peak_kind": peak_kind, "algorithmic_bytes": byts, "algorithmic_flops": flops}}
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -223,6 +261,9 @@ def main():
     ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "fp32"), choices=["fp32", "tf32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--legs", default="full,incre,e2e", help="which timed legs to run (profiling aid)")
+    ap.add_argument("--layer", action="store_true", help="time one SSC layer alone (rulebook cached) and exit")
+    ap.add_argument("--n-in", type=int, default=32)
+    ap.add_argument("--n-out", type=int, default=32)
     ap.add_argument("--profile", action="store_true", help="allow fewer than 3 warm-up steps (numbers are not bench values)")
     args = ap.parse_args()
     if args.impl == "b200" and not args.profile:
@@ -260,6 +301,10 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+    if args.layer:
+        hbm_peak, bf16_peak, peak_kind = load_peaks()
+        print(json.dumps({"layer": layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind), "precision": args.precision}))
+        return 0
     import sparseconvnet as scn
     scn.set_precision(args.precision)
     model = build_model(scn, torch).to(dev)
@@ -332,9 +377,12 @@ def main():
     ms_incre, launches_incre = timed(incre_frame, args.steps, args.warmup) if "incre" in legs else (float("nan"), 0)
 
     # ---- e2e: pinned host inputs, host read of the result -------------------------------------------
+    h_out = torch.empty(coords.shape[0], 20, dtype=torch.float32).pin_memory()
+
     def e2e_frame():
         y = model([h_coords, h_feats.to(dev, non_blocking=True)])
-        out_holder["host"] = y.to("cpu")
+        h_out.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the host reads the result every step
 
     ms_e2e, _ = timed(e2e_frame, args.steps, args.warmup) if "e2e" in legs else (float("nan"), 0)
     e2e_value = total_layers / (ms_e2e * 1e-3)

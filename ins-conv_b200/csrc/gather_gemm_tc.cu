@@ -21,6 +21,8 @@
 // Every wait on an mbarrier is bounded; a wait that runs out sets an error word that the host reads
 // at its next synchronisation, and the kernel still releases its tensor memory before returning.
 #include "internal.h"
+#include <cuda.h>
+#include <stdlib.h>
 
 namespace scn {
 
@@ -115,12 +117,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-struct Ctl {                 // control block at the start of dynamic shared memory
+struct alignas(16) Ctl {     // control block behind the stages in dynamic shared memory
   unsigned long long done[8];  // per stage: MMAs that read the stage have retired
   unsigned long long acc;      // all MMAs of the tile have retired
   uint32_t tmem_base;
   int failed;
   int nk;                      // offsets with at least one valid row
+  unsigned int kmask;          // bit k: offset k has a valid row
   int klist[32];
 };
 
@@ -146,19 +149,34 @@ k_gather_gemm_tf32(const float *__restrict__ in, long long in_stride, const int3
   const int KB = Cin >> 5;
 
   // ---- neighbour rows of the tile, and the list of offsets that have any -------------------------
+  // thread t owns row t: all K loads are issued back to back (independent), then one block-wide OR
   if (tid == 0) {
     ctl->failed = 0;
-    ctl->nk = 0;
+    ctl->kmask = 0;
   }
   __syncthreads();
-  for (int k = 0; k < K; ++k) {
+  {
     const long long row = row0 + tid;
-    int v = -1;
-    if (row < n_out) v = map ? __ldg(map + (long long)k * n_out + row) : (int)row;
-    s_map[k * kTileM + tid] = v;
-    if (__syncthreads_or(v >= 0)) {
-      if (tid == 0) ctl->klist[ctl->nk++] = k;
+    unsigned int mine = 0;
+#pragma unroll
+    for (int k = 0; k < 27; ++k) {
+      if (k < K) {
+        int v = -1;
+        if (row < n_out) v = map ? __ldg(map + (long long)k * n_out + row) : (int)row;
+        s_map[k * kTileM + tid] = v;
+        mine |= (v >= 0 ? 1u : 0u) << k;
+      }
     }
+    mine = __reduce_or_sync(0xffffffffu, mine);
+    if (lane == 0 && mine) atomicOr(&ctl->kmask, mine);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int n = 0;
+    const unsigned int km = ctl->kmask;
+    for (int k = 0; k < K; ++k)
+      if (km >> k & 1u) ctl->klist[n++] = k;
+    ctl->nk = n;
   }
   __syncthreads();
   const int nk = ctl->nk;
@@ -201,7 +219,9 @@ k_gather_gemm_tf32(const float *__restrict__ in, long long in_stride, const int3
 
   // stage the operands of reduction step `it` into ring slot `slot`
   auto load_step = [&](int it, int slot) {
-    const int k = ctl->klist[(t0 + it) / KB];
+    // tiles start at different offsets so that concurrently running CTAs do not all fetch the same
+    // weight block from the same L2 lines at the same time
+    const int k = ctl->klist[((t0 + it) / KB + (int)(blockIdx.x % 27u)) % nk];
     const int kb = (t0 + it) % KB;
     const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
     const uint32_t b_base = a_base + kABytes;
@@ -297,6 +317,239 @@ k_gather_gemm_tf32(const float *__restrict__ in, long long in_stride, const int3
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// TMA-fed, warp-specialised variant
+// ---------------------------------------------------------------------------------------------
+// Same tile and the same shared-memory layout as above, but the operands are staged by the tensor
+// memory accelerator and the roles are split by warp, so no thread ever waits for a copy it issued:
+//   warp 0  producer: per step one tile::gather4 bulk-tensor copy per lane (4 gathered rows x 128 bytes
+//           each, the hardware applies the 128-byte swizzle and zero-fills rows whose index is -1) plus one
+//           2-D bulk-tensor copy of the weight block; the copies complete on the step's `full` mbarrier
+//   warp 1  consumer: waits `full`, issues the four tcgen05.mma, tcgen05.commit -> the slot's `empty` barrier
+//   all 4   epilogue: TMEM -> registers -> global
+// The producer runs up to STAGES steps ahead of the tensor core.
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap *tm, uint32_t bar, int col, int r0, int r1,
+                                            int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_tile2d(uint32_t dst, const CUtensorMap *tm, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+struct alignas(16) CtlTma {
+  unsigned long long full[8];   // per slot: the step's copies have landed
+  unsigned long long empty[8];  // per slot: the MMAs that read it have retired
+  unsigned long long acc;
+  uint32_t tmem_base;
+  int failed;
+  int nk;
+  unsigned int kmask;
+  int klist[32];
+};
+
+template <int STAGES>
+__global__ void __launch_bounds__(kThreads)
+k_gather_gemm_tf32_tma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const int32_t *__restrict__ map, int K, long long n_out, const float *__restrict__ bias,
+                       float *__restrict__ out, long long out_stride, int Cin, int Cout, int accumulate,
+                       uint32_t tmem_cols, float *__restrict__ partial) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t stage_bytes = kABytes + (uint32_t)Cout * 128u;
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  CtlTma *ctl = reinterpret_cast<CtlTma *>(smem + (size_t)STAGES * stage_bytes);
+  int *s_map = reinterpret_cast<int *>(ctl + 1);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const long long row0 = (long long)blockIdx.x * kTileM;
+  const int KB = Cin >> 5;
+
+  if (tid == 0) {
+    ctl->failed = 0;
+    ctl->kmask = 0;
+  }
+  __syncthreads();
+  {
+    const long long row = row0 + tid;
+    unsigned int mine = 0;
+#pragma unroll
+    for (int k = 0; k < 27; ++k) {
+      if (k < K) {
+        int v = -1;
+        if (row < n_out) v = map ? __ldg(map + (long long)k * n_out + row) : (int)row;
+        s_map[k * kTileM + tid] = v;
+        mine |= (v >= 0 ? 1u : 0u) << k;
+      }
+    }
+    mine = __reduce_or_sync(0xffffffffu, mine);
+    if (lane == 0 && mine) atomicOr(&ctl->kmask, mine);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int n = 0;
+    const unsigned int km = ctl->kmask;
+    for (int k = 0; k < K; ++k)
+      if (km >> k & 1u) ctl->klist[n++] = k;
+    ctl->nk = n;
+  }
+  __syncthreads();
+  const int nk = ctl->nk;
+  const int Tall = nk * KB;
+  const int t0 = (int)(((long long)Tall * blockIdx.y) / gridDim.y);
+  const int T = (int)(((long long)Tall * (blockIdx.y + 1)) / gridDim.y) - t0;
+  float *pdst = partial ? partial + ((long long)blockIdx.y * gridDim.x * kTileM + (long long)blockIdx.x * kTileM) * Cout : nullptr;
+  if (T == 0) {
+    if (pdst) {
+      for (int i = tid; i < kTileM * Cout; i += kThreads) pdst[i] = 0.f;
+    } else if (!accumulate) {
+      for (long long i = tid; i < (long long)kTileM * Cout; i += kThreads) {
+        const long long row = row0 + i / Cout;
+        const int c = (int)(i % Cout);
+        if (row < n_out) out[row * out_stride + c] = bias ? __ldg(bias + c) : 0.f;
+      }
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 1);
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctl->acc), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&ctl->tmem_base)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = ctl->tmem_base;
+  const uint32_t smem_base = smem_u32(smem);
+  volatile int *failed = &ctl->failed;
+
+  if (warp == 0) {
+    // ---- producer ------------------------------------------------------------------------------
+    for (int it = 0; it < T; ++it) {
+      const int slot = it % STAGES, use = it / STAGES;
+      if (use > 0) mbar_wait(smem_u32(&ctl->empty[slot]), (uint32_t)((use - 1) & 1), failed);
+      if (*failed) break;
+      const int k = ctl->klist[((t0 + it) / KB + (int)(blockIdx.x % 27u)) % nk];
+      const int kb = (t0 + it) % KB;
+      const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
+      const uint32_t bar = smem_u32(&ctl->full[slot]);
+      if (lane == 0) mbar_expect_tx(bar, stage_bytes);
+      __syncwarp();
+      const int4 rows = *reinterpret_cast<const int4 *>(s_map + k * kTileM + lane * 4);
+      tma_gather4(a_base + (uint32_t)lane * 512u, &tmA, bar, kb << 5, rows.x, rows.y, rows.z, rows.w);
+      if (lane == 0) tma_tile2d(a_base + kABytes, &tmB, bar, kb << 5, k * Cout);
+    }
+  } else if (warp == 1) {
+    // ---- consumer: one lane drives the tensor core ------------------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(Cout);
+      for (int it = 0; it < T; ++it) {
+        const int slot = it % STAGES;
+        if (!mbar_wait(smem_u32(&ctl->full[slot]), (uint32_t)((it / STAGES) & 1), failed)) break;
+        tc_fence_after();
+        const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
+        const uint32_t b_base = a_base + kABytes;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint64_t a_desc = smem_desc(a_base + j * 32, 16, 1024);
+          const uint64_t b_desc = smem_desc(b_base + j * 32, 16, 1024);
+          mma_tf32(tmem_d, a_desc, b_desc, idesc, (it > 0 || j > 0) ? 1u : 0u);
+        }
+        mma_commit(smem_u32(&ctl->empty[slot]));
+        if (it == T - 1) mma_commit(smem_u32(&ctl->acc));
+      }
+    }
+    __syncwarp();
+  }
+
+  // ---- epilogue -----------------------------------------------------------------------------------
+  mbar_wait(smem_u32(&ctl->acc), 0, failed);
+  __syncthreads();
+  const bool ok = !*failed;
+  tc_fence_after();
+  if (ok) {
+    const long long row = row0 + warp * 32 + lane;
+    for (int c0 = 0; c0 < Cout; c0 += 32) {
+      float v[32];
+      tmem_ld32(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+      if (pdst) {
+        float *o = pdst + (long long)(warp * 32 + lane) * Cout + c0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else if (row < n_out) {
+        float *o = out + row * out_stride + c0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          float4 r = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          if (accumulate) {
+            const float4 old = *reinterpret_cast<const float4 *>(o + j);
+            r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
+          } else if (bias) {
+            r.x += __ldg(bias + c0 + j); r.y += __ldg(bias + c0 + j + 1);
+            r.z += __ldg(bias + c0 + j + 2); r.w += __ldg(bias + c0 + j + 3);
+          }
+          *reinterpret_cast<float4 *>(o + j) = r;
+        }
+      }
+    }
+  } else if (warp == 0 && lane == 0) {
+    // a wait ran out: give copies that may still be in flight a bounded time to land before the CTA
+    // (and its shared memory) goes away
+    for (int s = 0; s < STAGES; ++s)
+      for (uint32_t i = 0; i < (1u << 16); ++i)
+        if (mbar_try_wait(smem_u32(&ctl->full[s]), 0) || mbar_try_wait(smem_u32(&ctl->full[s]), 1)) break;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link-time libcuda dependency)
+static int encode_2d(CUtensorMap *tm, const float *base, uint64_t cols, uint64_t rows, uint64_t row_stride_bytes,
+                     uint32_t box_cols, uint32_t box_rows) {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    SCN_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    if (!p || q != cudaDriverEntryPointSuccess) return fail(SCN_E_CUDA, "cuTensorMapEncodeTiled is not available");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SCN_E_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return SCN_OK;
+}
+
 // W [vol][Cin][Cout] -> Wt [vol][Cout][Cin]; 32x32 tiles through shared memory
 __global__ void k_transpose_weights(const float *__restrict__ W, float *__restrict__ Wt, int Cin, int Cout) {
   __shared__ float tile[32][33];
@@ -345,7 +598,7 @@ int tc_check_errors(cudaStream_t s) {
   return SCN_OK;
 }
 
-int gather_gemm_tf32(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *W,
+int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out, const float *W,
                      const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate,
                      cudaStream_t s, bool *handled) {
   *handled = false;
@@ -381,6 +634,36 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, const int32_t *map, int
                                                                                                           (int)Cout);
   SCN_LAUNCHED();
   const dim3 grid((unsigned)tiles, (unsigned)Z);
+  static const bool use_tma = []() {
+    // INSCONV_TC_COPY=tma selects the kernel whose rows are staged by tile::gather4 bulk-tensor copies.
+    // It is correct but measured slower than the cp.async kernel (gather4 moves four 128-byte rows per
+    // request and the copy engine keeps few such requests in flight), so it is not the default.
+    const char *e = getenv("INSCONV_TC_COPY");
+    return e && e[0] == 't';
+  }();
+  if (use_tma) {
+    CUtensorMap tmA, tmB;
+    SCN_TRY(encode_2d(&tmA, in, (uint64_t)Cin, (uint64_t)in_rows, (uint64_t)in_stride * 4, 32, 1));
+    SCN_TRY(encode_2d(&tmB, Wt, (uint64_t)Cin, (uint64_t)K * Cout, (uint64_t)Cin * 4, 32, (uint32_t)Cout));
+    const size_t fixed_t = sizeof(CtlTma) + (size_t)K * kTileM * sizeof(int) + 1024;
+    int st = 4;
+    if (4 * stage_bytes + fixed_t > 112 * 1024) {
+      st = (int)((200 * 1024 - fixed_t) / stage_bytes);
+      if (st > 6) st = 6;
+    }
+    const size_t smem_t = (size_t)st * stage_bytes + fixed_t;
+#define SCN_TMA_LAUNCH(S)                                                                                           \
+  do {                                                                                                              \
+    SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tf32_tma<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_t)); \
+    k_gather_gemm_tf32_tma<S><<<grid, kThreads, smem_t, s>>>(tmA, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, \
+                                                              (int)Cout, accumulate, cols, partial);                \
+  } while (0)
+    if (st >= 6) SCN_TMA_LAUNCH(6);
+    else if (st == 5) SCN_TMA_LAUNCH(5);
+    else if (st == 4) SCN_TMA_LAUNCH(4);
+    else SCN_TMA_LAUNCH(3);
+#undef SCN_TMA_LAUNCH
+  } else {
 #define SCN_TC_LAUNCH(S, A)                                                                                          \
   do {                                                                                                               \
     SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tf32<S, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
@@ -392,6 +675,7 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, const int32_t *map, int
   else if (stages == 4) SCN_TC_LAUNCH(4, 2);
   else SCN_TC_LAUNCH(3, 2);
 #undef SCN_TC_LAUNCH
+  }
   SCN_LAUNCHED();
   if (Z > 1) {
     const long long work = n_out * (Cout / 4);

@@ -113,7 +113,8 @@ int build_incre_up(const Grid &coarse, const int32_t *pe_coarse, const int32_t *
 
 // ---- feature kernels --------------------------------------------------------
 // out[o] = (accumulate ? out[o] : bias) + sum_k in[map[k*n_out + o]] * W[k]   (map == nullptr: identity, K = 1)
-int gather_gemm(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *W,
+// in has in_rows rows; map entries are -1 or in [0, in_rows).
+int gather_gemm(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out, const float *W,
                 const float *bias, float *out, int64_t out_stride, int64_t n_in, int64_t n_planes_out,
                 int accumulate, int precision, cudaStream_t s);
 // reads and clears the error word of the tensor-core kernels; synchronises s
