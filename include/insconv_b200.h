@@ -177,6 +177,25 @@ SCN_API int scn_nin_forward(const float *in, int64_t in_stride, float *out, int6
                     const float *weight, const float *bias, int64_t n_in, int64_t n_out, int precision,
                     void *stream, double *flops);
 
+/* The same 1x1 convolution as scn_nin_forward with SCN_PREC_TF32, for hosts that must not allocate.
+ * It has no counterpart in the reference.  Some embedders run with a device-memory budget that is
+ * handed out once at start-up (a perception process sharing its GPU with a mapping stack, a service
+ * whose memory belongs to another framework's pool): for them a library call that reaches the device
+ * allocator in steady state can fail late, stall on an implicit synchronisation, or break their
+ * accounting.  This entry point calls no allocator of any kind.  The transposed copy of the weights
+ * that the tensor-core kernel needs lives in a fixed 512 KiB buffer inside the library image (every GPU
+ * that loads the library holds it until the process exits), which sets the limit:
+ *   n_in * n_out <= 131072, n_in and n_out multiples of 32, n_out <= 256;
+ * anything else is refused with SCN_E_CAPACITY or SCN_E_INVALID and a message.  Pointers must be
+ * 16-byte aligned and strides multiples of 4 elements.
+ * The first call on each device looks up the buffer's device address; make that call before starting
+ * a stream capture on that device.  All calls share the one buffer: it is rewritten at the start of
+ * every call (nothing in it has to be cleared), so two calls whose GPU work can overlap -- different
+ * streams, or different threads -- race on it; keep them on one stream or serialise them. */
+SCN_API int scn_nin_forward_noalloc(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
+                                    const float *weight, const float *bias, int64_t n_in, int64_t n_out,
+                                    void *stream);
+
 /* ---------------------------------------------------------------------------
  * Incremental ("Incre_*") path.  `m` holds only the sites touched by the new
  * points of this frame; `pre` is the metadata of the last full frame and the

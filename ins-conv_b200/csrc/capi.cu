@@ -401,6 +401,11 @@ int scn_nin_forward(const float *in, int64_t in_stride, float *out, int64_t out_
                      (cudaStream_t)stream);
 }
 
+int scn_nin_forward_noalloc(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
+                            const float *weight, const float *bias, int64_t n_in, int64_t n_out, void *stream) {
+  return nin_forward_noalloc(in, in_stride, out, out_stride, rows, weight, bias, n_in, n_out, (cudaStream_t)stream);
+}
+
 // ---- incremental path --------------------------------------------------------------------------
 int scn_incre_pre_exist(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const int32_t **map, int64_t *n,
                         void *stream) {

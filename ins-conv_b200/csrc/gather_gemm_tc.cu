@@ -689,4 +689,73 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
   return SCN_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// 1x1 convolution that allocates nothing
+// ---------------------------------------------------------------------------------------------
+// The tensor-core kernels above want the weights transposed, and normally park the transposed copy in
+// memory taken from the device pool for the duration of the call.  This variant parks it in a fixed
+// buffer that is part of the library image instead, so the call never reaches a device allocator.
+// Every GPU that loads the library carries the buffer (512 KiB) until the process exits.
+constexpr size_t kNoAllocMaxWeights = 512 * 256;  // floats: n_in * n_out may not exceed this
+static __device__ __align__(256) float g_noalloc_weights[kNoAllocMaxWeights];
+
+// In host code `g_noalloc_weights` is only a handle for the runtime, not an address a kernel can use:
+// the device address is looked up once per device with cudaGetSymbolAddress and cached here.
+static float *g_noalloc_ptr[64] = {nullptr};
+static int noalloc_scratch(float **p) {
+  int dev = 0;
+  SCN_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(SCN_E_INVALID, "device index out of range");
+  if (!g_noalloc_ptr[dev]) {
+    void *addr = nullptr;
+    SCN_CUDA(cudaGetSymbolAddress(&addr, g_noalloc_weights));
+    g_noalloc_ptr[dev] = static_cast<float *>(addr);
+  }
+  *p = g_noalloc_ptr[dev];
+  return SCN_OK;
+}
+
+int nin_forward_noalloc(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
+                        const float *W, const float *bias, int64_t Cin, int64_t Cout, cudaStream_t s) {
+  if (rows < 0) return fail(SCN_E_INVALID, "negative row count");
+  if (rows == 0) return SCN_OK;
+  if (!in || !out || !W) return fail(SCN_E_INVALID, "null feature or weight pointer");
+  if (Cin <= 0 || Cout <= 0 || Cin % 32 != 0 || Cout % 32 != 0 || Cout > 256)
+    return fail(SCN_E_INVALID, "the no-allocation 1x1 convolution needs n_in and n_out to be multiples of 32 and n_out <= 256");
+  if ((size_t)Cin * (size_t)Cout > kNoAllocMaxWeights)
+    return fail(SCN_E_CAPACITY, "n_in * n_out exceeds the fixed scratch buffer of the no-allocation 1x1 convolution (131072 weights)");
+  if (in_stride % 4 != 0 || out_stride % 4 != 0 || !aligned16(in) || !aligned16(W) || !aligned16(out) ||
+      (bias && !aligned16(bias)))
+    return fail(SCN_E_INVALID, "pointers must be 16-byte aligned and row strides multiples of 4 elements");
+  float *Wt = nullptr;
+  SCN_TRY(noalloc_scratch(&Wt));
+  const size_t stage_bytes = (size_t)kABytes + (size_t)Cout * 128;
+  const size_t fixed = sizeof(Ctl) + (size_t)kTileM * sizeof(int) + 1024;
+  int stages = 4;
+  if (4 * stage_bytes + fixed > 112 * 1024) {
+    stages = (int)((200 * 1024 - fixed) / stage_bytes);
+    if (stages > 6) stages = 6;
+  }
+  const size_t smem = (size_t)stages * stage_bytes + fixed;
+  uint32_t cols = 32;
+  while (cols < (uint32_t)Cout) cols <<= 1;
+  const long long tiles = (rows + kTileM - 1) / kTileM;
+  k_transpose_weights<<<dim3((unsigned)(Cout / 32), (unsigned)(Cin / 32), 1), dim3(32, 8), 0, s>>>(W, Wt, (int)Cin, (int)Cout);
+  SCN_LAUNCHED();
+  const dim3 grid((unsigned)tiles, 1);
+#define SCN_NA_LAUNCH(S, A)                                                                                          \
+  do {                                                                                                               \
+    SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tf32<S, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    k_gather_gemm_tf32<S, A><<<grid, kThreads, smem, s>>>(in, in_stride, nullptr, 1, rows, Wt, bias, out, out_stride, \
+                                                           (int)Cin, (int)Cout, 0, cols, nullptr);                   \
+  } while (0)
+  if (stages >= 6) SCN_NA_LAUNCH(6, 3);
+  else if (stages == 5) SCN_NA_LAUNCH(5, 3);
+  else if (stages == 4) SCN_NA_LAUNCH(4, 2);
+  else SCN_NA_LAUNCH(3, 2);
+#undef SCN_NA_LAUNCH
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
 }  // namespace scn

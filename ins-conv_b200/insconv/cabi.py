@@ -59,6 +59,7 @@ PROTOTYPES = {
     "scn_deconv_forward": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_bn_forward": (_int, [_p, _i64, _p, _i64, _i64, _i64, _p, _p, _p, _p, _dbl, _dbl, _p]),
     "scn_nin_forward": (_int, [_p, _i64, _p, _i64, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
+    "scn_nin_forward_noalloc": (_int, [_p, _i64, _p, _i64, _i64, _p, _p, _i64, _i64, _p]),
     "scn_incre_pre_exist": (_int, [_p, _p, _i64p, C.POINTER(_p), _i64p, _p]),
     "scn_incre_input_layer_forward": (_int, [_p, _p, _p, _p, _p, _i64, _p]),
     "scn_incre_output_layer_forward": (_int, [_p, _p, _p, _p, _p, _i64, _p]),
