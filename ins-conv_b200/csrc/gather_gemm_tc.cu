@@ -21,6 +21,12 @@
 // Every wait on an mbarrier is bounded; a wait that runs out sets an error word that the host reads
 // at its next synchronisation, and the kernel still releases its tensor memory before returning.
 #include "internal.h"
+#ifdef SCN_TC_PROFILE
+#include <stdio.h>
+#define PROF(x) x
+#else
+#define PROF(x)
+#endif
 #include <cuda.h>
 #include <stdlib.h>
 
@@ -62,6 +68,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and records the failure) when the phase never completes.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *failed) {
+  if (mbar_try_wait(bar, parity)) return true;
   if (*failed) return false;
   for (uint32_t i = 0; i < kSpinLimit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
@@ -218,30 +225,37 @@ k_gather_gemm_tf32(const float *__restrict__ in, long long in_stride, const int3
   volatile int *failed = &ctl->failed;
 
   // stage the operands of reduction step `it` into ring slot `slot`
-  auto load_step = [&](int it, int slot) {
-    // tiles start at different offsets so that concurrently running CTAs do not all fetch the same
-    // weight block from the same L2 lines at the same time
-    const int k = ctl->klist[((t0 + it) / KB + (int)(blockIdx.x % 27u)) % nk];
-    const int kb = (t0 + it) % KB;
+  // the step to be staged next: offset index into klist and plane block, advanced without divisions;
+  // tiles start at different offsets so that concurrently running CTAs do not all fetch the same weight
+  // block from the same L2 lines at the same time
+  int ld_ki = (t0 / KB + (int)(blockIdx.x % 27u)) % nk, ld_kb = t0 % KB;
+  const int lc = tid & 7, lr0 = tid >> 3;
+  const uint32_t ldst0 = (uint32_t)((lr0 >> 3) << 10) + (uint32_t)((lr0 & 7) << 7) + (uint32_t)((lc ^ (lr0 & 7)) << 4);
+  const float *in_c = in + (lc << 2);
+  auto load_step = [&](int /*it*/, int slot) {
+    const int k = ctl->klist[ld_ki];
+    const int kb = ld_kb;
+    if (++ld_kb == KB) {
+      ld_kb = 0;
+      if (++ld_ki == nk) ld_ki = 0;
+    }
     const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
     const uint32_t b_base = a_base + kABytes;
-    const int *mrow = s_map + k * kTileM;
+    const int *mr = s_map + k * kTileM + lr0;
+    int src[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int q = tid + kThreads * i;
-      const int r = q >> 3, c = q & 7;
-      const int src = mrow[r];
-      const float *p = in + (src >= 0 ? (long long)src * in_stride + (kb << 5) + (c << 2) : 0);
-      const uint32_t dst = a_base + (uint32_t)((r >> 3) << 10) + (uint32_t)((r & 7) << 7) + (uint32_t)((c ^ (r & 7)) << 4);
-      cp_async16(dst, p, src >= 0 ? 16u : 0u);
+    for (int j = 0; j < 8; ++j) src[j] = mr[16 * j];
+    const float *in_kb = in_c + (kb << 5);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float *p = src[j] >= 0 ? in_kb + (long long)src[j] * in_stride : in;
+      cp_async16(a_base + ldst0 + (uint32_t)(j << 11), p, src[j] >= 0 ? 16u : 0u);
     }
     // transposed weights Wt[k][n][Cin]: row n of the tile is 32 consecutive planes of Wt[k][n]
-    const float *wk = W + (long long)k * Cout * Cin + (kb << 5);
-    const int total = Cout << 3;
-    for (int q = tid; q < total; q += kThreads) {
-      const int n = q >> 3, c = q & 7;
-      const uint32_t dst = b_base + (uint32_t)((n >> 3) << 10) + (uint32_t)((n & 7) << 7) + (uint32_t)((c ^ (n & 7)) << 4);
-      cp_async16(dst, wk + (long long)n * Cin + (c << 2), 16u);
+    const float *wk = W + (long long)k * Cout * Cin + (kb << 5) + (lc << 2);
+    for (int n = lr0; n < Cout; n += 16) {
+      const uint32_t dst = b_base + (uint32_t)((n >> 3) << 10) + (uint32_t)((n & 7) << 7) + (uint32_t)((lc ^ (n & 7)) << 4);
+      cp_async16(dst, wk + (long long)n * Cin, 16u);
     }
   };
 
@@ -524,6 +538,350 @@ k_gather_gemm_tf32_tma(const __grid_constant__ CUtensorMap tmA, const __grid_con
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// persistent, warp-specialised kernel for large grids
+// ---------------------------------------------------------------------------------------------
+// One CTA per SM walks over tiles (tile = blockIdx.x + i * gridDim.x).  Nine warps, three roles:
+//   warps 0-3  epilogue   wait for a finished accumulator, TMEM -> registers -> global, hand the
+//                         accumulator back (two accumulators alternate, so the tensor core starts the
+//                         next tile while this one is written out)
+//   warps 4-7  producers  gather the rows of each reduction step with 16-byte cp.async copies (zero-fill
+//                         for missing neighbours) into a ring of STAGES slots and signal the slot's `full`
+//                         barrier with cp.async.mbarrier.arrive, so nobody waits for a copy it issued:
+//                         the producers run ahead of the tensor core by as many slots as are free, across
+//                         tile boundaries.  One producer thread also fetches the step's weight block with a
+//                         single bulk-tensor copy.  The neighbour rows of the next tile are prefetched into
+//                         registers while the current tile is being issued.
+//   warp 8     tensor core one lane waits `full`, issues the four tcgen05.mma of the step, and lets
+//                         tcgen05.commit release the slot (`empty`) and, at the end of a tile, publish the
+//                         accumulator (`accfull`).
+// Every blocking primitive is a bounded mbarrier wait.  A tile with no neighbour at all still runs one step
+// of zero rows so that all roles see the same sequence of tiles.
+constexpr int kPThreads = 416;  // 4 epilogue warps, 8 producer warps, 1 tensor-core warp
+constexpr int kMaxStages = 8;
+constexpr uint32_t kInfoFirst = 1, kInfoLast = 2, kInfoDone = 4;
+
+struct alignas(16) CtlP {
+  unsigned long long full[kMaxStages];
+  unsigned long long empty[kMaxStages];
+  unsigned long long accfull[2];
+  unsigned long long accempty[2];
+  unsigned long long mapfull[2];
+  uint32_t info[kMaxStages];
+  uint32_t kmask_part[2][8];
+  uint32_t tmem_base;
+  int failed;
+};
+
+__global__ void __launch_bounds__(kPThreads, 1)
+k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, const __grid_constant__ CUtensorMap tmB,
+                           const int32_t *__restrict__ map, int K, long long n_out, const float *__restrict__ bias,
+                           float *__restrict__ out, long long out_stride, int Cin, int Cout, int accumulate,
+                           uint32_t acc_cols, int stages, long long tiles, int Z, float *__restrict__ partial,
+                           int dbg) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t b_bytes = (uint32_t)Cout * 128u;
+  const uint32_t stage_bytes = kABytes + b_bytes;
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  CtlP *ctl = reinterpret_cast<CtlP *>(smem + (size_t)stages * stage_bytes);
+  int *s_map = reinterpret_cast<int *>(ctl + 1);  // [2][K][128]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int KB = Cin >> 5;
+  // work items: (tile, share z of its reduction steps); Z == 1 means whole tiles
+  const long long items = tiles * Z;
+  const long long my_tiles = (items - (long long)blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+  if (tid == 0) {
+    ctl->failed = 0;
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&ctl->full[s]), 9);  // one arrival per producer warp + the weight copy's expect_tx arrival
+      mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&ctl->accfull[b]), 1);
+      mbar_init(smem_u32(&ctl->accempty[b]), 4);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&ctl->mapfull[b]), 8);   // one arrival per producer warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&ctl->tmem_base)),
+                 "r"(acc_cols * 2)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const uint32_t smem_base = smem_u32(smem);
+  volatile int *failed = &ctl->failed;
+
+  if (warp >= 4 && warp < 12) {
+    // =========================== producers ========================================================
+    const int tp = tid - 128, pw = warp - 4;
+    // thread tp and thread tp + 128 share row (tp & 127) of the tile: one takes the even offsets, the other the odd
+    const int prow = tp & 127, par = tp >> 7;
+    int nxt[14];  // neighbour rows of this thread's row in the next tile, offsets par, par + 2, ...
+    auto prefetch_map = [&](long long item) {
+      const long long tile = item / Z;
+      const long long row = tile * kTileM + prow;
+#pragma unroll
+      for (int j = 0; j < 14; ++j) {
+        const int k = 2 * j + par;
+        int v = -1;
+        if (k < K && item < items && row < n_out) v = map ? __ldg(map + (long long)k * n_out + row) : (int)row;
+        nxt[j] = v;
+      }
+    };
+    prefetch_map(blockIdx.x);
+    // ring position, kept without divisions: slot index and how often the ring has wrapped
+    int slot = 0;
+    uint32_t wrapped = 0;  // number of completed passes over the ring
+    constexpr int kLag = 3;  // a step is signalled when three younger steps have been issued (stages >= 4)
+    long long issued = 0;
+    // this thread copies chunk c of rows r0, r0+32, r0+64, r0+96: the swizzle term depends on r0 & 7 only
+    const int c = tp & 7, r0 = tp >> 3;
+    const uint32_t dst0 = (uint32_t)((r0 >> 3) << 10) + (uint32_t)((r0 & 7) << 7) + (uint32_t)((c ^ (r0 & 7)) << 4);
+    const float *in_c = in + (c << 2);
+    PROF(long long t_map = 0; long long t_empty = 0; long long t_issue = 0; long long t_lag = 0; long long t_all0 = clock64();)
+    for (long long i = 0; i < my_tiles && !*failed; ++i) {
+      const long long item = (long long)blockIdx.x + i * gridDim.x;
+      const int buf = (int)(i & 1);
+      int *mrows = s_map + buf * K * kTileM;
+      PROF(long long tm0 = clock64();)
+      // publish this tile's rows, learn which offsets have any
+      unsigned int mine = 0;
+#pragma unroll
+      for (int j = 0; j < 14; ++j) {
+        const int k = 2 * j + par;
+        if (k < K) {
+          mrows[k * kTileM + prow] = nxt[j];
+          mine |= (nxt[j] >= 0 ? 1u : 0u) << k;
+        }
+      }
+      mine = __reduce_or_sync(0xffffffffu, mine);
+      __syncwarp();
+      if (lane == 0) {
+        ctl->kmask_part[buf][pw] = mine;
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->mapfull[buf])) : "memory");
+      }
+      prefetch_map(item + gridDim.x);  // in flight while this tile is issued
+      if (!mbar_wait(smem_u32(&ctl->mapfull[buf]), (uint32_t)((i >> 1) & 1), failed)) break;
+      const uint4 km0 = *reinterpret_cast<const uint4 *>(&ctl->kmask_part[buf][0]);
+      const uint4 km1 = *reinterpret_cast<const uint4 *>(&ctl->kmask_part[buf][4]);
+      const unsigned int kmask = km0.x | km0.y | km0.z | km0.w | km1.x | km1.y | km1.z | km1.w;
+      // this item's share [t0, t1) of the tile's reduction steps; an empty share still runs one step of zero rows
+      const int z = (int)(item % Z);
+      const int nk_all = __popc(kmask);
+      const int Tall = nk_all * KB;
+      const int t0 = (int)(((long long)Tall * z) / Z);
+      const int Tz = (int)(((long long)Tall * (z + 1)) / Z) - t0;
+      const int nk = Tz > 0 ? nk_all : 0;  // 0: stage zero rows only
+      const int T = Tz > 0 ? Tz : 1;
+      unsigned int rest = kmask;
+      int kb = 0;
+      if (Tz > 0) {
+        for (int q = t0 / KB; q > 0; --q) rest &= rest - 1;
+        kb = t0 % KB;
+      }
+      int k = (Tz > 0 && rest) ? __ffs(rest) - 1 : 0;
+      bool stop = false;
+      PROF(t_map += clock64() - tm0;)
+      for (int it = 0; it < T; ++it) {
+        PROF(long long te0 = clock64();)
+        if (wrapped > 0 && !mbar_wait(smem_u32(&ctl->empty[slot]), (wrapped - 1) & 1u, failed)) {
+          stop = true;
+          break;
+        }
+        PROF(long long te1 = clock64(); t_empty += te1 - te0;)
+        const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
+        const uint32_t bar = smem_u32(&ctl->full[slot]);
+        if (!(dbg & 8)) {
+        const int *mr = mrows + k * kTileM + r0;
+        int src[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) src[j] = nk ? mr[32 * j] : -1;
+        const float *in_kb = in_c + (kb << 5);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float *p = src[j] >= 0 ? in_kb + (long long)src[j] * in_stride : in;
+          if (!(dbg & 2)) cp_async16(a_base + dst0 + (uint32_t)(j << 12), p, src[j] >= 0 ? 16u : 0u);
+        }
+        }
+        if (tp == 0) {
+          ctl->info[slot] = (it == 0 ? kInfoFirst : 0u) | (it == T - 1 ? kInfoLast : 0u);
+          if (dbg & 4) {
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+          } else {
+            mbar_expect_tx(bar, b_bytes);
+            tma_tile2d(a_base + kABytes, &tmB, bar, kb << 5, k * Cout);
+          }
+        }
+        PROF(long long tl0 = clock64(); t_issue += tl0 - te1;)
+        // signal the step issued kLag steps ago: its copies (this thread's share) have landed by now
+        cp_async_commit();
+        ++issued;
+        if (issued > kLag) {
+          cp_async_wait<kLag>();
+          fence_async_proxy();
+          __syncwarp();
+          if (lane == 0) {
+            int ls = slot - kLag;
+            if (ls < 0) ls += stages;
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->full[ls])) : "memory");
+          }
+        }
+        PROF(t_lag += clock64() - tl0;)
+        if (++slot == stages) {
+          slot = 0;
+          ++wrapped;
+        }
+        if (++kb == KB) {
+          kb = 0;
+          rest &= rest - 1;
+          k = rest ? __ffs(rest) - 1 : 0;
+        }
+      }
+      if (stop) break;
+    }
+    PROF(if (blockIdx.x == 0 && tp == 0) printf("prod: total %lld map %lld empty-wait %lld issue %lld lag-wait %lld steps %lld tiles %lld\n", clock64() - t_all0, t_map, t_empty, t_issue, t_lag, issued, my_tiles);)
+    // drain: signal the last steps, oldest first
+    cp_async_wait<0>();
+    fence_async_proxy();
+    __syncwarp();
+    if (lane == 0) {
+      const int pending = issued < kLag ? (int)issued : kLag;
+      for (int d = pending; d >= 1; --d) {
+        int ls = slot - d;
+        if (ls < 0) ls += stages;
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->full[ls])) : "memory");
+      }
+    }
+    // sentinel step: tells the tensor-core warp that no more work follows
+    if (!*failed) {
+      bool okw = true;
+      if (wrapped > 0) okw = mbar_wait(smem_u32(&ctl->empty[slot]), (wrapped - 1) & 1u, failed);
+      if (okw) {
+        const uint32_t bar = smem_u32(&ctl->full[slot]);
+        if (tp == 0) {
+          ctl->info[slot] = kInfoDone;
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+        }
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+      }
+    }
+    asm volatile("cp.async.wait_all;\n" ::: "memory");
+  } else if (warp == 12) {
+    // =========================== tensor core ======================================================
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(Cout);
+      long long tile_i = 0;
+      uint32_t tmem_d = tmem_base;
+      int buf = 0, slot = 0;
+      uint32_t phase = 0;
+      bool first_mma = true;
+      PROF(long long t_full = 0; long long t_acc = 0; long long t0 = clock64(); long long nsteps = 0; long long t_info = 0; long long t_mma = 0; long long t_commit = 0;)
+      while (!*failed) {
+        PROF(long long a0 = clock64();)
+        if (!mbar_wait(smem_u32(&ctl->full[slot]), phase, failed)) break;
+        PROF(long long c0 = clock64(); t_full += c0 - a0; ++nsteps;)
+        const uint32_t info = ctl->info[slot];
+        if (info & kInfoDone) break;
+        if (info & kInfoFirst) {
+          buf = (int)(tile_i & 1);
+          tmem_d = tmem_base + (uint32_t)buf * acc_cols;
+          // the epilogue must have drained this accumulator (used by tile tile_i - 2)
+          PROF(long long b0 = clock64();)
+          if (tile_i >= 2 && !mbar_wait(smem_u32(&ctl->accempty[buf]), (uint32_t)(((tile_i >> 1) - 1) & 1), failed)) break;
+          PROF(t_acc += clock64() - b0;)
+          tc_fence_after();  // the epilogue's TMEM reads of this accumulator are ordered before the new MMAs
+          first_mma = true;
+        }
+        const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
+        const uint32_t b_base = a_base + kABytes;
+        PROF(long long c1 = clock64(); t_info += c1 - c0;)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint64_t a_desc = smem_desc(a_base + j * 32, 16, 1024);
+          const uint64_t b_desc = smem_desc(b_base + j * 32, 16, 1024);
+          if (!(dbg & 1)) mma_tf32(tmem_d, a_desc, b_desc, idesc, (first_mma && j == 0) ? 0u : 1u);
+        }
+        first_mma = false;
+        PROF(long long c2 = clock64(); t_mma += c2 - c1;)
+        if (dbg & 16) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->empty[slot])) : "memory");
+        else mma_commit(smem_u32(&ctl->empty[slot]));
+        if (info & kInfoLast) {
+          if (dbg & 16) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->accfull[buf])) : "memory");
+          else
+          mma_commit(smem_u32(&ctl->accfull[buf]));
+          ++tile_i;
+        }
+        if (++slot == stages) {
+          slot = 0;
+          phase ^= 1u;
+        }
+        PROF(t_commit += clock64() - c2;)
+      }
+      PROF(if (blockIdx.x == 0) printf("mma: total %lld full-wait %lld accempty-wait %lld info %lld mma-issue %lld commit %lld steps %lld\n", clock64() - t0, t_full, t_acc, t_info, t_mma, t_commit, nsteps);)
+    }
+    __syncwarp();
+  } else {
+    // =========================== epilogue =========================================================
+    PROF(long long t_wait = 0; long long t_work = 0; long long t0 = clock64();)
+    for (long long i = 0; i < my_tiles; ++i) {
+      const long long item = (long long)blockIdx.x + i * gridDim.x;
+      const long long tile = item / Z;
+      float *pdst = partial ? partial + (((item % Z) * tiles + tile) * kTileM + warp * 32 + lane) * Cout : nullptr;
+      const int buf = (int)(i & 1);
+      PROF(long long w0 = clock64();)
+      if (!mbar_wait(smem_u32(&ctl->accfull[buf]), (uint32_t)((i >> 1) & 1), failed)) break;
+      PROF(long long w1 = clock64(); t_wait += w1 - w0;)
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t)buf * acc_cols + ((uint32_t)(warp * 32) << 16);
+      const long long row = tile * kTileM + warp * 32 + lane;
+      for (int c0 = 0; c0 < Cout; c0 += 32) {
+        float v[32];
+        tmem_ld32(taddr + (uint32_t)c0, v);
+        if (c0 + 32 >= Cout) {  // last read of this accumulator: hand it back before the stores
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->accempty[buf])) : "memory");
+        }
+        if (pdst) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4 *>(pdst + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else if (row < n_out) {
+          float *o = out + row * out_stride + c0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 r = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            if (accumulate) {
+              const float4 old = *reinterpret_cast<const float4 *>(o + j);
+              r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
+            } else if (bias) {
+              r.x += __ldg(bias + c0 + j); r.y += __ldg(bias + c0 + j + 1);
+              r.z += __ldg(bias + c0 + j + 2); r.w += __ldg(bias + c0 + j + 3);
+            }
+            *reinterpret_cast<float4 *>(o + j) = r;
+          }
+        }
+      }
+      PROF(t_work += clock64() - w1;)
+    }
+    PROF(if (blockIdx.x == 0 && tid == 0) printf("epi: total %lld accfull-wait %lld work %lld\n", clock64() - t0, t_wait, t_work);)
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(acc_cols * 2) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -575,9 +933,18 @@ __global__ void k_splitk_reduce(const float *__restrict__ partial, int Z, long l
   if (accumulate) acc = *reinterpret_cast<const float4 *>(o);
   else if (bias) acc = __ldg(reinterpret_cast<const float4 *>(bias + c));
   else acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int z = 0; z < Z; ++z) {
-    const float4 p = __ldg(reinterpret_cast<const float4 *>(partial + ((long long)z * rows_padded + r) * Cout + c));
-    acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+  const float *p0 = partial + r * Cout + c;
+  const long long zstride = rows_padded * Cout;
+  for (int z0 = 0; z0 < Z; z0 += 8) {  // eight independent loads in flight, added in ascending z
+    float4 p[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      p[u] = (z0 + u < Z) ? __ldg(reinterpret_cast<const float4 *>(p0 + (long long)(z0 + u) * zstride))
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      acc.x += p[u].x; acc.y += p[u].y; acc.z += p[u].z; acc.w += p[u].w;
+    }
   }
   *reinterpret_cast<float4 *>(o) = acc;
 }
@@ -618,14 +985,31 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
   uint32_t cols = 32;
   while (cols < (uint32_t)Cout) cols <<= 1;
   const long long tiles = (n_out + kTileM - 1) / kTileM;
-  // few tiles and a long reduction: share the steps of a tile among Z CTAs
+  int sm_count = 148;
+  {
+    int dev = 0;
+    SCN_CUDA(cudaGetDevice(&dev));
+    static int cached[64] = {0};
+    if (dev >= 0 && dev < 64) {
+      if (!cached[dev]) SCN_CUDA(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
+      sm_count = cached[dev];
+    }
+  }
+  // Few tiles and a long reduction: share the steps of a tile among Z work items.  Z minimises the
+  // longest chain of steps any CTA runs (items per CTA x steps per item, plus a fixed cost per item).
   const int steps_max = K * (int)(Cin / 32);
   int Z = 1;
-  if (tiles < 148) {
-    Z = (int)((2 * 148 + tiles - 1) / tiles);
-    if (Z > steps_max / 2) Z = steps_max / 2;
-    if (Z > 64) Z = 64;
-    if (Z < 1) Z = 1;
+  if (tiles < 2 * sm_count && steps_max >= 4) {
+    long long best = -1;
+    const int zmax = steps_max / 2 < 32 ? steps_max / 2 : 32;
+    for (int z = 1; z <= zmax; ++z) {
+      const long long per_cta = (tiles * z + sm_count - 1) / sm_count;
+      const long long cost = per_cta * ((steps_max + z - 1) / z + 3) + (z > 1 ? 2 + z / 4 : 0);
+      if (best < 0 || cost < best) {
+        best = cost;
+        Z = z;
+      }
+    }
   }
   float *Wt = nullptr, *partial = nullptr;
   SCN_TRY(dev_alloc_t(&Wt, (size_t)K * Cin * Cout, s));
@@ -641,7 +1025,24 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
     const char *e = getenv("INSCONV_TC_COPY");
     return e && e[0] == 't';
   }();
-  if (use_tma) {
+  static const bool use_persist = []() {
+    const char *e = getenv("INSCONV_TC_COPY");
+    return !(e && (e[0] == 't' || e[0] == 'c'));  // "tma" / "cpasync" force the per-tile kernels (development aid)
+  }();
+  const size_t fixed_p = sizeof(CtlP) + (size_t)2 * K * kTileM * sizeof(int) + 1024;
+  int st_p = (int)((220 * 1024 - fixed_p) / stage_bytes);
+  if (st_p > kMaxStages) st_p = kMaxStages;
+  if (use_persist && cols * 2 <= 512 && st_p >= 4) {
+    CUtensorMap tmB;
+    SCN_TRY(encode_2d(&tmB, Wt, (uint64_t)Cin, (uint64_t)K * Cout, (uint64_t)Cin * 4, 32, (uint32_t)Cout));
+    const int st = st_p;
+    const size_t smem_p = (size_t)st * stage_bytes + fixed_p;
+    SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tf32_persist, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p));
+    const long long n_items = tiles * Z;
+    k_gather_gemm_tf32_persist<<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads, smem_p, s>>>(
+        in, in_stride, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, (int)Cout, accumulate, cols, st, tiles, Z, partial,
+                                                                            getenv("INSCONV_DBG") ? atoi(getenv("INSCONV_DBG")) : 0);
+  } else if (use_tma) {
     CUtensorMap tmA, tmB;
     SCN_TRY(encode_2d(&tmA, in, (uint64_t)Cin, (uint64_t)in_rows, (uint64_t)in_stride * 4, 32, 1));
     SCN_TRY(encode_2d(&tmB, Wt, (uint64_t)Cin, (uint64_t)K * Cout, (uint64_t)Cin * 4, 32, (uint32_t)Cout));
