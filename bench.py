@@ -12,7 +12,8 @@ voxels changed, reference semantics) is timed beside it and reported as ms/frame
   value      inputs resident in HBM when the timed region starts
   e2e        the same through the public module API with pinned HOST inputs and a host read of the result
   roofline   the dominant kernel (the gather-GEMM of the level-0 32->32 submanifold convolution), timed
-             with CUDA events on the launching stream inside the timed region
+             alone with CUDA events on the launching stream, L2 flushed between launches
+  hash_build the grid build (voxel hash + site ranking + input rules) at 36k, 255k and 4M points
   cpu_baseline  the CPU restatement of the reference (oracle/) on this box's host cores, rank 0, N=1 only
 
 N > 1 (torchrun, one rank per GPU): every rank runs its own seeded room, no data-path collective; the
@@ -124,53 +125,6 @@ class ClockSampler(object):
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-class SscTimer(object):
-    """CUDA-event pairs around every SubmanifoldConvolution_updateOutput call, on the launching stream."""
-
-    def __init__(self, scn, torch):
-        self.scn, self.torch = scn, torch
-        self.records = []
-        self.enabled = False
-        self.pool = []
-        self.orig = scn.SCN.SubmanifoldConvolution_updateOutput
-
-        def wrapped(size, filt, meta, x, out, w, b, dil):
-            if not self.enabled:
-                return self.orig(size, filt, meta, x, out, w, b, dil)
-            if len(self.pool) < 2:
-                self.reserve(64)
-            e0, e1 = self.pool.pop(), self.pool.pop()
-            e0.record()
-            madds = self.orig(size, filt, meta, x, out, w, b, dil)
-            e1.record()
-            self.records.append((x.shape[0], w.shape[1], w.shape[2], madds, e0, e1))
-            return madds
-        scn.SCN.SubmanifoldConvolution_updateOutput = wrapped
-
-    def reserve(self, n):
-        """Creates events ahead of the timed region (event creation is the expensive part)."""
-        self.pool.extend(self.torch.cuda.Event(enable_timing=True) for _ in range(n))
-
-    def summary(self, hbm_peak, tensor_peak_tf32):
-        shapes = {}
-        for n, ci, co, madds, e0, e1 in self.records:
-            ms = e0.elapsed_time(e1)
-            s = shapes.setdefault((n, ci, co), {"ms": 0.0, "launches": 0, "pairs": madds / (ci * co)})
-            s["ms"] += ms
-            s["launches"] += 1
-        out = []
-        for (n, ci, co), s in shapes.items():
-            t = s["ms"] / s["launches"] * 1e-3
-            byts = 4.0 * n * ci + 4.0 * n * co + 8.0 * s["pairs"] + 4.0 * 27 * ci * co
-            flops = 2.0 * s["pairs"] * ci * co
-            out.append({"sites": n, "n_in": ci, "n_out": co, "pairs": int(s["pairs"]), "launches": s["launches"],
-                        "us_per_launch": t * 1e6, "total_ms": s["ms"], "GBps": byts / t / 1e9,
-                        "TFLOPs": flops / t / 1e12, "hbm_frac": byts / t / 1e9 / hbm_peak,
-                        "tensor_frac": flops / t / 1e12 / tensor_peak_tf32, "bytes": byts, "flops": flops})
-        out.sort(key=lambda r: -r["total_ms"])
-        return out
-
-
 def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
     """One submanifold convolution on the room, rulebook cached, through the C ABI: the 'active voxels/s per
     SSC layer' figure in isolation.  L2 is flushed between launches; each launch is timed with CUDA events."""
@@ -207,6 +161,46 @@ def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
                          "peak": hbm_peak if hbm_bound else bf16_peak / 2, "unit": "GB/s" if hbm_bound else "TFLOP/s",
                          "frac": (byts / t / 1e9 / hbm_peak) if hbm_bound else (flops / t / 1e12 / (bf16_peak / 2)),
                          "peak_kind": peak_kind, "algorithmic_bytes": byts, "algorithmic_flops": flops}}
+
+
+def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
+    """Grid build (points -> ranked sites + open-addressing table + input rules) through the C ABI, coordinates
+    resident on the device.  Algorithmic bytes: 32 per point in (int64 x,y,z,batch), 8 per table slot,
+    12 per site (coordinates out), 4 per point (point -> site)."""
+    import torch
+    from insconv import cabi, synth
+    out = []
+    for name in sizes:
+        if name == "c1":
+            c = synth.boxes_and_spheres(0)
+            size = 128
+        elif name == "room":
+            c = synth.room(0)
+            size = 4096
+        else:
+            c = synth.building(0, target=4000000)
+            size = 4096
+        import numpy as np
+        c4 = np.concatenate([c, np.zeros((c.shape[0], 1), np.int64)], 1)
+        d = torch.from_numpy(c4).to(dev)
+        m = cabi.Metadata()
+        ts = []
+        for i in range(warmup + steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            n = m.input_layer_build(size, d, mode=4)
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                ts.append(e0.elapsed_time(e1) * 1e-3)
+        t = sorted(ts)[len(ts) // 2]
+        cap = 16
+        while cap < 2 * n:
+            cap *= 2
+        byts = 32.0 * c4.shape[0] + 8.0 * cap + 12.0 * n + 4.0 * c4.shape[0]
+        out.append({"scene": name, "points": int(c4.shape[0]), "sites": int(n), "us": t * 1e6,
+                    "points_per_s": c4.shape[0] / t, "GBps": byts / t / 1e9})
+    return out
 
 
 def load_peaks():
@@ -258,10 +252,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--voxels", type=int, default=250000)
-    ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "fp32"), choices=["fp32", "tf32"])
+    ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "tf32"), choices=["fp32", "tf32"])
+    ap.add_argument("--quick", action="store_true", help="skip the 4M-point hash build (profiling aid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--legs", default="full,incre,e2e", help="which timed legs to run (profiling aid)")
     ap.add_argument("--layer", action="store_true", help="time one SSC layer alone (rulebook cached) and exit")
+    ap.add_argument("--hash", action="store_true", help="time the grid build alone and exit")
     ap.add_argument("--n-in", type=int, default=32)
     ap.add_argument("--n-out", type=int, default=32)
     ap.add_argument("--profile", action="store_true", help="allow fewer than 3 warm-up steps (numbers are not bench values)")
@@ -301,6 +297,9 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+    if args.hash:
+        print(json.dumps({"hash_build": hash_bench(dev, args.steps, args.warmup, ("c1", "room") if args.quick else ("c1", "room", "building"))}))
+        return 0
     if args.layer:
         hbm_peak, bf16_peak, peak_kind = load_peaks()
         print(json.dumps({"layer": layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind), "precision": args.precision}))
@@ -312,7 +311,6 @@ def main():
     d_coords, d_feats = torch.from_numpy(coords).to(dev), torch.from_numpy(feats).to(dev)
     d_inc_c, d_inc_f = torch.from_numpy(inc_c).to(dev), torch.from_numpy(inc_f).to(dev)
     h_coords, h_feats = torch.from_numpy(coords).pin_memory(), torch.from_numpy(feats).pin_memory()
-    timer = SscTimer(scn, torch)
     hbm_peak, bf16_peak, peak_kind = load_peaks()
 
     def barrier():
@@ -360,13 +358,7 @@ def main():
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    timer.reserve(2 * len(ssc_mods) * (args.steps + args.warmup) + 8)
-    timer.enabled = True
     ms_full, launches = timed(full_frame, args.steps, args.warmup)
-    timer.enabled = False
-    clocks = sampler.stop() if rank == 0 else None
-    # drop the warm-up records: keep the last steps * 53
-    timer.records = timer.records[-args.steps * len(ssc_mods):]
     total_layers = sum_over_ranks(voxel_layers)
     value = total_layers / (ms_full * 1e-3)
 
@@ -385,6 +377,7 @@ def main():
         torch.cuda.current_stream().synchronize()  # the host reads the result every step
 
     ms_e2e, _ = timed(e2e_frame, args.steps, args.warmup) if "e2e" in legs else (float("nan"), 0)
+    clocks = sampler.stop() if rank == 0 else None  # sampled across the three timed legs
     e2e_value = total_layers / (ms_e2e * 1e-3)
     h2d = coords.nbytes + feats.nbytes
     d2h = int(out_holder["y"].numel()) * 4
@@ -394,22 +387,18 @@ def main():
             dist.destroy_process_group()
         return 0
 
-    shapes = timer.summary(hbm_peak, bf16_peak / 2.0)
-    top = shapes[0] if shapes else None
-    roofline = None
-    if top:
-        hbm_bound = top["n_in"] <= 64
-        roofline = {"kernel": "gather-GEMM %s, SSC %d->%d on %d sites" % (args.precision, top["n_in"], top["n_out"],
-                                                                           top["sites"]),
-                    "bound": "hbm" if hbm_bound else "tensor",
-                    "achieved": top["GBps"] if hbm_bound else top["TFLOPs"],
-                    "peak": hbm_peak if hbm_bound else bf16_peak / 2.0,
-                    "unit": "GB/s" if hbm_bound else "TFLOP/s",
-                    "frac": top["hbm_frac"] if hbm_bound else top["tensor_frac"],
-                    "peak_kind": peak_kind + (" HBM copy" if hbm_bound else " bf16/2 taken as the tf32 peak"),
-                    "us_per_launch": top["us_per_launch"], "launches": top["launches"],
-                    "algorithmic_bytes": top["bytes"], "algorithmic_flops": top["flops"],
-                    "traffic": None}
+    # roofline of the dominant kernel: the level-0 submanifold convolution (32 -> 32 planes on every site of the
+    # room), timed alone with CUDA events on its stream, L2 flushed between launches
+    args.n_in, args.n_out = 32, 32
+    lay = layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind)
+    roofline = dict(lay["roofline"])
+    roofline.update({"kernel": "gather-GEMM %s, SSC 32->32 on %d sites (level 0 of the UNet, 9 of the 53 SSC layers)"
+                               % (args.precision, lay["sites"]),
+                     "us_per_launch": lay["us_per_launch"], "voxels_per_s": lay["voxels_per_s"], "traffic": None,
+                     "l2": "flushed between launches (256 MB write)"})
+    hashes = hash_bench(dev, 5, 2, ("c1", "room") if args.quick else ("c1", "room", "building"))
+    for h in hashes:
+        h["hbm_frac"] = h["GBps"] / hbm_peak
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_full, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32" if args.precision == "fp32" else "tf32", "data": "synthetic",
@@ -422,8 +411,7 @@ def main():
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches) * args.steps, "clocks": clocks, "roofline": roofline,
-            "ssc_by_shape": [{k: (round(v, 4) if isinstance(v, float) else v) for k, v in s.items()
-                              if k not in ("bytes", "flops")} for s in shapes[:8]]}
+            "hash_build": hashes}
     if world == 1 and not args.no_cpu_baseline:
         sample = min(args.voxels, 120000)
         r = cpu_reference(sample, 2, 1)

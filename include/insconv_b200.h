@@ -171,6 +171,14 @@ SCN_API int scn_deconv_forward(scn_metadata *m, const int64_t in_size[3], const 
 SCN_API int scn_bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
                    int64_t planes, const float *running_mean, const float *running_var, const float *gamma,
                    const float *beta, double eps, double leakiness, void *stream);
+/* Train-mode forward: batch statistics over the rows (biased variance for the normalisation), running
+ * statistics updated in place as running = momentum*running + (1-momentum)*batch (unbiased variance),
+ * save_mean / save_invstd (may be NULL) receive the batch mean and 1/sqrt(var+eps).  Replaces
+ * BatchNormalization_f_train (CUDA/BatchNormalization.cu:14-72). */
+SCN_API int scn_bn_forward_train(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
+                                 int64_t planes, float *running_mean, float *running_var, float *save_mean,
+                                 float *save_invstd, const float *gamma, const float *beta, double eps,
+                                 double momentum, double leakiness, void *stream);
 /* out = in * weight (+ bias), weight [n_in, n_out].  Replaces cuda_NetworkInNetwork_updateOutput
  * (CUDA/NetworkInNetwork.cpp:9-25). */
 SCN_API int scn_nin_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,

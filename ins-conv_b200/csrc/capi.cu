@@ -391,6 +391,16 @@ int scn_bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_s
   return bn_forward(in, in_stride, out, out_stride, rows, planes, running_mean, running_var, gamma, beta, (float)eps,
                     (float)leakiness, nullptr, nullptr, nullptr, (cudaStream_t)stream);
 }
+int scn_bn_forward_train(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
+                         int64_t planes, float *running_mean, float *running_var, float *save_mean,
+                         float *save_invstd, const float *gamma, const float *beta, double eps, double momentum,
+                         double leakiness, void *stream) {
+  if (rows < 0 || planes < 0) return fail(SCN_E_INVALID, "negative size");
+  if (rows && planes && (!in || !out || !running_mean || !running_var)) return fail(SCN_E_INVALID, "null pointer");
+  if (rows == 1) return fail(SCN_E_INVALID, "batch statistics need at least two rows");
+  return bn_forward_train(in, in_stride, out, out_stride, rows, planes, running_mean, running_var, save_mean,
+                          save_invstd, gamma, beta, (float)eps, (float)momentum, (float)leakiness, (cudaStream_t)stream);
+}
 int scn_nin_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
                     const float *weight, const float *bias, int64_t n_in, int64_t n_out, int precision, void *stream,
                     double *flops) {

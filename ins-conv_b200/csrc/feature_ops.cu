@@ -252,6 +252,84 @@ int bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_strid
   return SCN_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// BatchNorm with batch statistics (train mode forward; CUDA/BatchNormalization.cu:14-72)
+// ---------------------------------------------------------------------------------------------
+// pass 1: per-plane sum and sum of squares.  A block owns a slab of rows; threads (32 planes x 8 rows)
+// accumulate in fp32, the block reduces in shared memory and adds into fp64 totals.
+__global__ void k_bn_stats(const float *__restrict__ in, long long in_stride, long long rows, int C,
+                           long long rows_per_block, double *__restrict__ sums /*[2][C]*/) {
+  __shared__ float s1[8][33], s2[8][33];
+  const long long r0 = (long long)blockIdx.x * rows_per_block;
+  const long long r1 = min(rows, r0 + rows_per_block);
+  for (int c0 = 0; c0 < C; c0 += 32) {
+    const int c = c0 + threadIdx.x;
+    float a = 0.f, b = 0.f;
+    if (c < C)
+      for (long long r = r0 + threadIdx.y; r < r1; r += 8) {
+        const float v = in[r * in_stride + c];
+        a += v;
+        b += v * v;
+      }
+    s1[threadIdx.y][threadIdx.x] = a;
+    s2[threadIdx.y][threadIdx.x] = b;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < C) {
+      double ta = 0, tb = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        ta += s1[j][threadIdx.x];
+        tb += s2[j][threadIdx.x];
+      }
+      atomicAdd(&sums[c], ta);
+      atomicAdd(&sums[C + c], tb);
+    }
+    __syncthreads();
+  }
+}
+// pass 2: mean, biased variance for the normalisation, running statistics (unbiased variance) updated in place
+__global__ void k_bn_finalize(const double *__restrict__ sums, long long rows, int C, float eps, float momentum,
+                              float *save_mean, float *save_invstd, float *running_mean, float *running_var,
+                              float *batch_var) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const double mean = sums[c] / (double)rows;
+  const double ss = sums[C + c] - mean * mean * (double)rows;  // sum of squared deviations
+  if (save_mean) save_mean[c] = (float)mean;
+  running_mean[c] = momentum * running_mean[c] + (1.f - momentum) * (float)mean;
+  running_var[c] = momentum * running_var[c] + (1.f - momentum) * (float)(ss / (double)(rows - 1));
+  const float var_b = (float)(ss / (double)rows);
+  batch_var[c] = var_b;
+  if (save_invstd) save_invstd[c] = 1.0f / sqrtf(var_b + eps);
+  batch_var[C + c] = (float)mean;
+}
+
+int bn_forward_train(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,
+                     float *running_mean, float *running_var, float *save_mean, float *save_invstd, const float *gamma,
+                     const float *beta, float eps, float momentum, float leak, cudaStream_t s) {
+  if (rows == 0 || planes == 0) return SCN_OK;
+  if (planes > 4096) return fail(SCN_E_INVALID, "BatchNorm over more than 4096 planes");
+  double *sums = nullptr;
+  float *stat = nullptr;  // [0..C): batch variance, [C..2C): batch mean
+  SCN_TRY(dev_alloc_t(&sums, (size_t)planes * 2, s));
+  SCN_TRY(dev_alloc_t(&stat, (size_t)planes * 2, s));
+  SCN_CUDA(cudaMemsetAsync(sums, 0, (size_t)planes * 2 * sizeof(double), s));
+  long long blocks = (rows + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  const long long rpb = (rows + blocks - 1) / blocks;
+  k_bn_stats<<<(unsigned)blocks, dim3(32, 8), 0, s>>>(in, in_stride, rows, (int)planes, rpb, sums);
+  SCN_LAUNCHED();
+  k_bn_finalize<<<blocks_for(planes, 128), 128, 0, s>>>(sums, rows, (int)planes, eps, momentum, save_mean, save_invstd,
+                                                        running_mean, running_var, stat);
+  SCN_LAUNCHED();
+  int r = bn_forward(in, in_stride, out, out_stride, rows, planes, stat + planes, stat, gamma, beta, eps, leak, nullptr,
+                     nullptr, nullptr, s);
+  dev_free(sums, s);
+  dev_free(stat, s);
+  return r;
+}
+
 // ---------------------------------------------------------------------------------------------
 // InputLayer / OutputLayer
 // ---------------------------------------------------------------------------------------------

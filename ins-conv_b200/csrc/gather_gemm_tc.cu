@@ -1037,7 +1037,16 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
     SCN_TRY(encode_2d(&tmB, Wt, (uint64_t)Cin, (uint64_t)K * Cout, (uint64_t)Cin * 4, 32, (uint32_t)Cout));
     const int st = st_p;
     const size_t smem_p = (size_t)st * stage_bytes + fixed_p;
-    SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tf32_persist, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p));
+    {
+      // the opt-in shared memory limit is raised once per device, to the most this kernel ever asks for
+      static bool raised[64] = {false};
+      int dev = 0;
+      SCN_CUDA(cudaGetDevice(&dev));
+      if (dev < 0 || dev >= 64 || !raised[dev]) {
+        SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tf32_persist, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        if (dev >= 0 && dev < 64) raised[dev] = true;
+      }
+    }
     const long long n_items = tiles * Z;
     k_gather_gemm_tf32_persist<<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads, smem_p, s>>>(
         in, in_stride, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, (int)Cout, accumulate, cols, st, tiles, Z, partial,

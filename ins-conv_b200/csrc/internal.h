@@ -125,6 +125,9 @@ int bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_strid
                const float *mean, const float *var, const float *gamma, const float *beta, float eps,
                float leak, const int32_t *pre_exist, const float *pre_out, const float *pre_in,
                cudaStream_t s);
+int bn_forward_train(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,
+                     float *running_mean, float *running_var, float *save_mean, float *save_invstd, const float *gamma,
+                     const float *beta, float eps, float momentum, float leak, cudaStream_t s);
 int input_forward(const Grid &g, const float *in, float *out, int64_t planes, int average,
                   const int32_t *pre_exist, const Grid *pre, const float *pre_out, cudaStream_t s);
 int output_forward(const Grid &g, const float *in, float *out, int64_t planes, const int32_t *pre_exist,

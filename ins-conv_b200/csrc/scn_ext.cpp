@@ -37,14 +37,23 @@ struct Size3 {
   int64_t v[3];
   explicit Size3(const at::Tensor &t) {
     TORCH_CHECK(t.numel() == 3, "only dimension 3 is supported; got a size of ", t.numel(), " elements");
-    auto c = t.to(at::kCPU, at::kLong).contiguous();
-    for (int i = 0; i < 3; ++i) v[i] = c.data_ptr<int64_t>()[i];
+    if (t.device().is_cpu() && t.scalar_type() == at::kLong && t.is_contiguous()) {
+      for (int i = 0; i < 3; ++i) v[i] = t.data_ptr<int64_t>()[i];  // the usual case: no temporary tensor
+    } else {
+      auto c = t.to(at::kCPU, at::kLong).contiguous();
+      for (int i = 0; i < 3; ++i) v[i] = c.data_ptr<int64_t>()[i];
+    }
   }
 };
 
 const float *opt_ptr(const at::Tensor &t) { return t.numel() ? t.data_ptr<float>() : nullptr; }
 
 void expect_filter(const at::Tensor &filt, int64_t want, const char *what) {
+  if (filt.device().is_cpu() && filt.scalar_type() == at::kLong && filt.is_contiguous()) {
+    for (int64_t i = 0; i < filt.numel(); ++i)
+      TORCH_CHECK(filt.data_ptr<int64_t>()[i] == want, what, ": only filter size / stride ", want, " is supported");
+    return;
+  }
   auto c = filt.to(at::kCPU, at::kLong);
   for (int64_t i = 0; i < c.numel(); ++i)
     TORCH_CHECK(c.data_ptr<int64_t>()[i] == want, what, ": only filter size / stride ", want, " is supported");
@@ -151,11 +160,20 @@ void BatchNormalization_updateOutput(at::Tensor input_features, at::Tensor outpu
                                      at::Tensor weight, at::Tensor bias, double eps, double momentum, bool train,
                                      double leakiness) {
   need_cuda_f32(input_features, "input_features");
-  TORCH_CHECK(!train, "BatchNormalization: only inference (running statistics) is on the hot path; call model.eval()");
   c10::cuda::CUDAGuard guard(input_features.device());
   auto in = input_features.contiguous();
   output_features.resize_as_(in);
   if (in.numel() == 0) return;
+  if (train) {  // batch statistics, running statistics updated in place (what demo.py exercises on its first frame)
+    saveMean.resize_({in.size(1)});
+    saveInvStd.resize_({in.size(1)});
+    check(scn_bn_forward_train(in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(), in.size(1), in.size(0),
+                               in.size(1), runningMean.data_ptr<float>(), runningVar.data_ptr<float>(),
+                               saveMean.data_ptr<float>(), saveInvStd.data_ptr<float>(), opt_ptr(weight), opt_ptr(bias),
+                               eps, momentum, leakiness, stream_of(in)),
+          "BatchNormalization_updateOutput");
+    return;
+  }
   check(scn_bn_forward(in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(), in.size(1), in.size(0),
                        in.size(1), runningMean.data_ptr<float>(), runningVar.data_ptr<float>(), opt_ptr(weight),
                        opt_ptr(bias), eps, leakiness, stream_of(in)),
@@ -281,7 +299,7 @@ void Incre_BatchNormalization_updateOutput(at::Tensor input_features, at::Tensor
                                            at::Tensor pre_output_feats, at::Tensor pre_input_feats,
                                            at::Tensor spatialSize) {
   need_cuda_f32(input_features, "input_features");
-  TORCH_CHECK(!train, "BatchNormalization: only inference (running statistics) is on the hot path; call model.eval()");
+  (void)train;  // the incremental form always uses the running statistics (CUDA/BatchNormalization.cu:181-195)
   c10::cuda::CUDAGuard guard(input_features.device());
   Size3 s(spatialSize);
   auto in = input_features.contiguous();

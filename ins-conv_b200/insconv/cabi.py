@@ -58,6 +58,7 @@ PROTOTYPES = {
     "scn_conv_forward": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_deconv_forward": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_bn_forward": (_int, [_p, _i64, _p, _i64, _i64, _i64, _p, _p, _p, _p, _dbl, _dbl, _p]),
+    "scn_bn_forward_train": (_int, [_p, _i64, _p, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _dbl, _dbl, _dbl, _p]),
     "scn_nin_forward": (_int, [_p, _i64, _p, _i64, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_nin_forward_noalloc": (_int, [_p, _i64, _p, _i64, _i64, _p, _p, _i64, _i64, _p]),
     "scn_incre_pre_exist": (_int, [_p, _p, _i64p, C.POINTER(_p), _i64p, _p]),
@@ -318,6 +319,18 @@ def bn_forward(x, mean, var, gamma, beta, eps, leak):
     call("scn_bn_forward", ptr(x), x.stride(0) if x.dim() == 2 and x.shape[0] else x.shape[1], ptr(out), x.shape[1],
          x.shape[0], x.shape[1], ptr(mean), ptr(var), ptr(gamma), ptr(beta), float(eps), float(leak), _stream())
     return out
+
+
+def bn_forward_train(x, running_mean, running_var, gamma, beta, eps, momentum, leak):
+    """Returns (out, save_mean, save_invstd); running_mean / running_var are updated in place."""
+    import torch
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    sm = torch.empty(x.shape[1], dtype=torch.float32, device=x.device)
+    si = torch.empty(x.shape[1], dtype=torch.float32, device=x.device)
+    call("scn_bn_forward_train", ptr(x), x.shape[1], ptr(out), x.shape[1], x.shape[0], x.shape[1], ptr(running_mean),
+         ptr(running_var), ptr(sm), ptr(si), ptr(gamma), ptr(beta), float(eps), float(momentum), float(leak), _stream())
+    return out, sm, si
 
 
 def nin_forward(x, weight, bias=None, precision=PREC_FP32):

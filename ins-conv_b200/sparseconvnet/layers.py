@@ -11,7 +11,7 @@ of its reference counterpart:
 `forward(input, increment=False)`: a full frame (increment False) computes on every site and keeps what
 the next incremental frames need (`save_meta`, `save_input_feats`, `save_output`, `save_input`); an
 incremental frame computes residuals on the sites touched by the new points only.  The modules are
-inference only: outputs carry no autograd history.
+inference only: the operators do not record autograd history, whatever the grad mode.
 """
 import torch
 from torch.nn import Module, Parameter
@@ -21,6 +21,12 @@ from . import SCN
 from .metadata import Metadata
 from .tensor import SparseConvNetTensor
 from .utils import toLongTensor, optionalTensor
+
+
+def _keep(module, **state):
+    """Stores per-frame state on a module without torch.nn.Module.__setattr__ (which walks the parameter,
+    buffer and sub-module tables on every assignment and is the slowest thing a layer call would do)."""
+    module.__dict__.update(state)
 
 
 def _count(madds, out):
@@ -47,7 +53,6 @@ class SubmanifoldConvolution(Module):
         if bias:
             self.bias = Parameter(torch.zeros(nOut))
 
-    @torch.no_grad()
     def forward(self, input, increment=False):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, self.nOut, input)
         out = input.features.new_empty(0)
@@ -55,8 +60,7 @@ class SubmanifoldConvolution(Module):
             madds = SCN.SubmanifoldConvolution_updateOutput(
                 input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
                 optionalTensor(self, "bias"), self.dilated_rate)
-            self.save_meta = input.metadata
-            self.save_input_feats = input.features
+            _keep(self, save_meta=input.metadata, save_input_feats=input.features)
         else:
             madds = SCN.Incre_SubmanifoldConvolution_updateOutput(
                 input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
@@ -88,7 +92,6 @@ class _Strided(Module):
 
 
 class Convolution(_Strided):
-    @torch.no_grad()
     def forward(self, input, increment=False):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
         out_size = torch.div(input.spatial_size - self.filter_size, self.filter_stride, rounding_mode="floor") + 1
@@ -109,7 +112,6 @@ class Convolution(_Strided):
 
 
 class Deconvolution(_Strided):
-    @torch.no_grad()
     def forward(self, input, increment=False):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
         out_size = (input.spatial_size - 1) * self.filter_stride + self.filter_size
@@ -118,8 +120,7 @@ class Deconvolution(_Strided):
             madds = SCN.Deconvolution_updateOutput(
                 input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
                 out, self.weight, optionalTensor(self, "bias"))
-            self.save_meta = input.metadata
-            self.save_input_feats = input.features
+            _keep(self, save_meta=input.metadata, save_input_feats=input.features)
         else:
             madds = SCN.Incre_Deconvolution_updateOutput(
                 input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
@@ -148,7 +149,6 @@ class BatchNormalization(Module):
             self.weight = Parameter(torch.ones(nPlanes))
             self.bias = Parameter(torch.zeros(nPlanes))
 
-    @torch.no_grad()
     def forward(self, input, increment=False):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nPlanes, \
             (self.nPlanes, input.features.shape)
@@ -156,11 +156,10 @@ class BatchNormalization(Module):
         scratch = input.features.new_empty(0)
         if not increment:
             SCN.BatchNormalization_updateOutput(
-                input.features, out, scratch, scratch, self.running_mean, self.running_var,
+                input.features, out, scratch, input.features.new_empty(0), self.running_mean, self.running_var,
                 optionalTensor(self, "weight"), optionalTensor(self, "bias"), self.eps, self.momentum, self.training,
                 self.leakiness)
-            self.save_output = input.like(out)
-            self.save_input = input.like(input.features)
+            _keep(self, save_output=input.like(out), save_input=input)
         else:
             SCN.Incre_BatchNormalization_updateOutput(
                 input.features, out, scratch, scratch, self.running_mean, self.running_var,
@@ -197,7 +196,6 @@ class NetworkInNetwork(Module):
         if bias:
             self.bias = Parameter(torch.zeros(nOut))
 
-    @torch.no_grad()
     def forward(self, input, increment=False):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, input.features.shape)
         out = input.features.new_empty(0)
@@ -232,7 +230,6 @@ class InputLayer(Module):
         self.device = device
         return self
 
-    @torch.no_grad()
     def forward(self, input, increment=False):
         assert len(input) >= 2, len(input)
         coords, feats = input[0], input[1]
@@ -245,7 +242,7 @@ class InputLayer(Module):
         if not increment:
             SCN.InputLayer_updateOutput(output.metadata, self.spatial_size, coords, feats, out, batch_size, self.mode)
             output.features = out
-            self.save_output = output
+            _keep(self, save_output=output)
         else:
             SCN.Incre_InputLayer_updateOutput(output.metadata, self.spatial_size, coords, feats, out, batch_size,
                                               self.mode, self.save_output.metadata, self.save_output.features)
@@ -260,13 +257,11 @@ class OutputLayer(Module):
         Module.__init__(self)
         self.dimension = dimension
 
-    @torch.no_grad()
     def forward(self, input, increment=False):
         out = input.features.new_empty(0)
         if not increment:
             SCN.OutputLayer_updateOutput(input.metadata, input.features, out)
-            self.save_input_feats = input.features
-            self.save_meta = input.metadata
+            _keep(self, save_input_feats=input.features, save_meta=input.metadata)
         else:
             SCN.Incre_OutputLayer_updateOutput(input.metadata, input.features, out, self.save_meta,
                                                self.save_input_feats)

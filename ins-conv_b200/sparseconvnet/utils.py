@@ -4,6 +4,9 @@ import torch
 from . import SCN
 
 
+_EMPTY = torch.empty(0)
+
+
 def toLongTensor(dimension, x):
     """int, list/tuple or LongTensor -> CPU LongTensor of `dimension` entries."""
     if isinstance(x, torch.Tensor):
@@ -16,8 +19,8 @@ def toLongTensor(dimension, x):
 
 def optionalTensor(module, name):
     """The named attribute, or an empty tensor ('no bias' convention of the operator interface)."""
-    t = getattr(module, name, None)
-    return t if t is not None else torch.empty(0)
+    t = module._parameters.get(name)  # direct table lookup: a missing attribute on a Module is slow to discover
+    return t if t is not None else _EMPTY
 
 
 def set_precision(p):

@@ -221,6 +221,21 @@ def bn_forward(x, running_mean, running_var, gamma, beta, eps, leakiness):
     return torch.where(o > 0, o, o * leakiness)
 
 
+def bn_forward_train(x, running_mean, running_var, gamma, beta, eps, momentum, leakiness):
+    """BatchNormalization_ForwardPass, train mode (CPU/BatchNormalization.cpp:22-40): batch statistics, running
+    statistics updated as momentum*running + (1-momentum)*batch with the unbiased variance.  Returns
+    (out, new_running_mean, new_running_var)."""
+    x = torch.as_tensor(x, dtype=torch.float32)
+    n = x.shape[0]
+    xd = x.double()
+    mean = xd.mean(0)
+    ss = (xd * xd).sum(0) - mean * mean * n
+    new_rm = momentum * torch.as_tensor(running_mean, dtype=torch.float32) + (1 - momentum) * mean.float()
+    new_rv = momentum * torch.as_tensor(running_var, dtype=torch.float32) + (1 - momentum) * (ss / (n - 1)).float()
+    out = bn_forward(x, mean.float(), (ss / n).float(), gamma, beta, eps, leakiness)
+    return out, new_rm, new_rv
+
+
 def nin_forward(x, weight, bias=None):
     """cpu_NetworkInNetwork_updateOutput (CPU/NetworkInNetwork.cpp:8-23)."""
     x = torch.as_tensor(x, dtype=torch.float32)

@@ -175,3 +175,20 @@ def test_conv_deconv_nin_tf32(cuda):
     got, _ = cabi.nin_forward(torch.from_numpy(z).to(cuda), torch.from_numpy(wn).to(cuda), None, cabi.PREC_TF32)
     close(got, O.nin_forward(z, wn), TF32_TOL)
     cabi.check_errors()
+
+
+def test_bn_train_mode(cuda):
+    rng = np.random.RandomState(21)
+    x = (rng.randn(30011, 32) * 2 + 0.7).astype(np.float32)
+    rm = rng.randn(32).astype(np.float32)
+    rv = rng.uniform(0.5, 2, 32).astype(np.float32)
+    gamma = rng.randn(32).astype(np.float32)
+    beta = rng.randn(32).astype(np.float32)
+    want, want_rm, want_rv = O.bn_forward_train(x, rm, rv, gamma, beta, 1e-4, 0.9, 0.0)
+    t = lambda a: torch.from_numpy(a.copy()).to(cuda)
+    d_rm, d_rv = t(rm), t(rv)
+    got, sm, si = cabi.bn_forward_train(t(x), d_rm, d_rv, t(gamma), t(beta), 1e-4, 0.9, 0.0)
+    close(got, want, 1e-4)
+    close(d_rm, want_rm, 1e-5)
+    close(d_rv, want_rv, 1e-5)
+    close(sm, torch.from_numpy(x).double().mean(0).float(), 1e-5)

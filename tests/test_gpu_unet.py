@@ -105,3 +105,23 @@ def test_reference_model_py_topology(cuda):
     # CPU coordinates (the reference's calling convention) give the same result
     got2 = model([torch.from_numpy(c), torch.from_numpy(f).to(cuda), 1])
     assert torch.equal(got, got2)
+
+
+def test_demo_py_flow_runs_unchanged(cuda):
+    # the calling sequence of the reference's demo.py:14-36: model left in train mode, CUDA LongTensor points,
+    # two-element input lists, one full frame then one incremental frame
+    import sparseconvnet as scn
+    torch.manual_seed(3)
+    model = small_unet(scn, [32, 64, 96, 128, 160, 192, 224], full_scale=4096).cuda()
+    g = torch.Generator().manual_seed(0)
+    points_0 = torch.randint(100, 150, (10000, 3), generator=g).cuda()
+    features_0 = torch.rand(10000, 3, generator=g).cuda()
+    out_0 = model([points_0, features_0], increment=False)
+    points_1 = torch.randint(100, 150, (1000, 3), generator=g).cuda()
+    features_1 = torch.rand(1000, 3, generator=g).cuda()
+    out_1 = model([points_1, features_1], increment=True)
+    assert out_0.shape == (10000, 20) and out_1.shape == (1000, 20)
+    assert bool(torch.isfinite(out_0).all()) and bool(torch.isfinite(out_1).all())
+    # the first frame moved the running statistics (train-mode BatchNorm)
+    bn = [m for m in model.modules() if isinstance(m, scn.BatchNormalization)][0]
+    assert float((bn.running_var - 1).abs().max()) > 0
