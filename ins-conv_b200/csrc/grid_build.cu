@@ -92,22 +92,36 @@ __global__ void k_init_info(BuildInfo *info) {
   }
 }
 
+// Bounding box: warp shuffle, then one shared-memory round per block, then at most eight global
+// atomics per block -- and none when the block cannot widen the box it already sees.
 __device__ __forceinline__ void reduce_box(int x, int y, int z, int b, bool valid, BuildInfo *info) {
+  __shared__ int s_mn[8][4], s_mx[8][4];  // blocks have at most 8 warps
   int mn[4] = {valid ? x : INT_MAX, valid ? y : INT_MAX, valid ? z : INT_MAX, valid ? b : INT_MAX};
   int mx[4] = {valid ? x : INT_MIN, valid ? y : INT_MIN, valid ? z : INT_MIN, valid ? b : INT_MIN};
 #pragma unroll
   for (int d = 0; d < 4; ++d) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      mn[d] = min(mn[d], __shfl_xor_sync(0xffffffffu, mn[d], o));
-      mx[d] = max(mx[d], __shfl_xor_sync(0xffffffffu, mx[d], o));
-    }
+    mn[d] = __reduce_min_sync(0xffffffffu, mn[d]);
+    mx[d] = __reduce_max_sync(0xffffffffu, mx[d]);
   }
-  if ((threadIdx.x & 31) == 0) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (lane == 0) {
 #pragma unroll
     for (int d = 0; d < 4; ++d) {
-      if (mn[d] != INT_MAX) atomicMin(&info->mn[d], mn[d]);
-      if (mx[d] != INT_MIN) atomicMax(&info->mx[d], mx[d]);
+      s_mn[wid][d] = mn[d];
+      s_mx[wid][d] = mx[d];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    const int d = threadIdx.x & 3;
+    const bool is_max = threadIdx.x >= 4;
+    const int nw = (blockDim.x + 31) >> 5;
+    int v = is_max ? INT_MIN : INT_MAX;
+    for (int w = 0; w < nw; ++w) v = is_max ? max(v, s_mx[w][d]) : min(v, s_mn[w][d]);
+    if (is_max) {
+      if (v != INT_MIN && v > *(volatile int *)&info->mx[d]) atomicMax(&info->mx[d], v);
+    } else {
+      if (v != INT_MAX && v < *(volatile int *)&info->mn[d]) atomicMin(&info->mn[d], v);
     }
   }
 }
@@ -142,7 +156,7 @@ __global__ void k_pack_keys_i64(const long long *__restrict__ coords, int ncols,
 
 // int32 SoA coordinates of a finer grid, shifted right (downsampling by 2^shift).
 __global__ void k_pack_keys_soa(const int32_t *__restrict__ c, long long n, int shift,
-                                unsigned long long *__restrict__ keys, BuildInfo *info) {
+                                unsigned long long *__restrict__ keys, BuildInfo *info, int measure_box) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   bool valid = i < n;
   int x = 0, y = 0, z = 0, b = 0;
@@ -153,7 +167,7 @@ __global__ void k_pack_keys_soa(const int32_t *__restrict__ c, long long n, int 
     b = c[3 * n + i];
     keys[i] = pack_key(x, y, z, b);
   }
-  reduce_box(x, y, z, b, valid, info);
+  if (measure_box) reduce_box(x, y, z, b, valid, info);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -316,6 +330,7 @@ struct EmitPairs {
 // ---------------------------------------------------------------------------------------------
 // pass 4: rank -> rows, coordinates, table
 // ---------------------------------------------------------------------------------------------
+template <bool UNIQUE>
 __global__ void k_assign(const unsigned long long *__restrict__ keys, long long n_src, Box bx,
                          const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
                          long long n, int32_t *__restrict__ src_row, int32_t *coords, uint32_t *cnt, Slot *table,
@@ -329,7 +344,8 @@ __global__ void k_assign(const unsigned long long *__restrict__ keys, long long 
   const unsigned long long w = bitmap[p >> 6];
   const uint32_t row = prefix[p >> 6] + (uint32_t)__popcll(w & ((1ull << (p & 63)) - 1ull));
   src_row[i] = (int32_t)row;
-  if (atomicAdd(&cnt[row], 1u) == 0u) {  // first point of the site
+  // UNIQUE: the host saw n == n_src, every point is the only one of its site and no counting is needed
+  if (UNIQUE || atomicAdd(&cnt[row], 1u) == 0u) {  // first point of the site
     coords[row] = x;
     coords[n + row] = y;
     coords[2 * n + row] = z;
@@ -468,7 +484,7 @@ int grid_free(Grid &g, cudaStream_t s) {
 static const unsigned long long kMaxBoxBits = 1ull << 35;
 
 int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift, int64_t n_src,
-               bool want_csr, cudaStream_t s) {
+               bool want_csr, const Box *box_hint, cudaStream_t s) {
   grid_free(g, s);
   g.n_src = n_src;
   if (n_src == 0) return SCN_OK;
@@ -485,18 +501,27 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
     k_pack_keys_i64<<<blocks_for(n_src, T), T, 0, s>>>(reinterpret_cast<const long long *>(coords64), ncols, vec,
                                                       n_src, keys, info_d);
   } else {
-    k_pack_keys_soa<<<blocks_for(n_src, T), T, 0, s>>>(coords_soa, n_src, shift, keys, info_d);
+    k_pack_keys_soa<<<blocks_for(n_src, T), T, 0, s>>>(coords_soa, n_src, shift, keys, info_d, box_hint ? 0 : 1);
   }
   SCN_LAUNCHED();
   BuildInfo info;
-  SCN_CUDA(cudaMemcpyAsync(&info, info_d, sizeof(info), cudaMemcpyDeviceToHost, s));
-  SCN_CUDA(cudaStreamSynchronize(s));
-  if (info.err & 1u) {
-    dev_free(info_d, s);
-    dev_free(keys, s);
-    return fail(SCN_E_RANGE, "coordinate outside [0, 65534] or batch index outside [0, 32766]");
-  }
   Box bx;
+  const bool hinted = box_hint && !coords64;
+  if (hinted) {
+    bx = *box_hint;
+    for (int d = 0; d < 4; ++d) {
+      info.mn[d] = bx.o[d];
+      info.mx[d] = bx.o[d] + (int)bx.e[d] - 1;
+    }
+  } else {
+    SCN_CUDA(cudaMemcpyAsync(&info, info_d, sizeof(info), cudaMemcpyDeviceToHost, s));
+    SCN_CUDA(cudaStreamSynchronize(s));
+    if (info.err & 1u) {
+      dev_free(info_d, s);
+      dev_free(keys, s);
+      return fail(SCN_E_RANGE, "coordinate outside [0, 65534] or batch index outside [0, 32766]");
+    }
+  }
   unsigned long long bits = 1;
   for (int d = 0; d < 4; ++d) {
     bx.o[d] = info.mn[d];
@@ -521,6 +546,7 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
   SCN_CUDA(cudaStreamSynchronize(s));
   const int64_t n = info.n_unique;
   g.n = n;
+  g.box = bx;
   uint64_t cap = 16;
   while (cap < (uint64_t)n * 2) cap <<= 1;
   g.mask = (uint32_t)(cap - 1);
@@ -528,11 +554,16 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
   SCN_TRY(dev_alloc_t(&g.coords, (size_t)n * 4, s));
   SCN_TRY(dev_alloc_t(&g.table, (size_t)cap, s));
   SCN_TRY(dev_alloc_t(&g.src_row, (size_t)n_src, s));
-  SCN_TRY(dev_alloc_t(&cnt, (size_t)n, s));
   SCN_CUDA(cudaMemsetAsync(g.table, 0xFF, (size_t)cap * sizeof(Slot), s));
-  SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n * 4, s));
-  k_assign<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, cnt,
-                                             g.table, g.mask, info_d);
+  if (n == n_src) {
+    k_assign<true><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, nullptr,
+                                                     g.table, g.mask, info_d);
+  } else {
+    SCN_TRY(dev_alloc_t(&cnt, (size_t)n, s));
+    SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n * 4, s));
+    k_assign<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, cnt,
+                                                      g.table, g.mask, info_d);
+  }
   SCN_LAUNCHED();
   g.max_active = 1;
   bool need_info = false;

@@ -69,6 +69,7 @@ struct Box {
 // One scale of a scene.
 struct Grid {
   int64_t n = 0;           // active sites
+  Box box = {{0, 0, 0, 0}, {0, 0, 0, 0}};  // bounding box of the sites (valid when n > 0)
   int32_t *coords = nullptr;  // SoA [4][n]: x, y, z, batch
   Slot *table = nullptr;
   uint32_t mask = 0;       // capacity - 1
@@ -94,8 +95,10 @@ int grid_free(Grid &g, cudaStream_t s);
 // Builds g from source points.  Exactly one of coords64 / coords_soa is given:
 //   coords64  : int64 [n_src, ncols] rows (x,y,z[,b]) on the device
 //   coords_soa: int32 SoA [4][n_src] on the device, shifted right by `shift` bits (downsampling)
+// box_hint (optional): a box known to contain every source point; saves the host round trip that otherwise
+// fetches the measured bounding box.
 int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift,
-               int64_t n_src, bool want_csr, cudaStream_t s);
+               int64_t n_src, bool want_csr, const Box *box_hint, cudaStream_t s);
 int grid_build_ssc(Grid &g, cudaStream_t s);               // fills nbr / nbr_count
 int grid_build_conv(Grid &coarse, const Grid &fine, cudaStream_t s);  // fills child / fine_up
 int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_stride, int32_t *rows,
