@@ -29,6 +29,14 @@ def _keep(module, **state):
     module.__dict__.update(state)
 
 
+def _residual(input, increment):
+    """True when this call is a residual (reference-style incremental) update.  In the exact incremental mode
+    the InputLayer hands down the whole merged scene and every layer runs its full-frame path instead."""
+    if isinstance(input, (list, tuple)):
+        input = input[0]
+    return bool(increment) and not getattr(input, "recompute_all", False)
+
+
 def _count(madds, out):
     sparseconvnet.forward_pass_multiplyAdd_count += madds
     sparseconvnet.forward_pass_hidden_states += out.nelement()
@@ -56,7 +64,7 @@ class SubmanifoldConvolution(Module):
     def forward(self, input, increment=False):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, self.nOut, input)
         out = input.features.new_empty(0)
-        if not increment:
+        if not _residual(input, increment):
             madds = SCN.SubmanifoldConvolution_updateOutput(
                 input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
                 optionalTensor(self, "bias"), self.dilated_rate)
@@ -98,7 +106,7 @@ class Convolution(_Strided):
         assert ((out_size - 1) * self.filter_stride + self.filter_size == input.spatial_size).all(), \
             (input.spatial_size, out_size, self.filter_size, self.filter_stride)
         out = input.features.new_empty(0)
-        op = SCN.Incre_Convolution_updateOutput if increment else SCN.Convolution_updateOutput
+        op = SCN.Incre_Convolution_updateOutput if _residual(input, increment) else SCN.Convolution_updateOutput
         madds = op(input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
                    out, self.weight, optionalTensor(self, "bias"))
         _count(madds, out)
@@ -116,7 +124,7 @@ class Deconvolution(_Strided):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
         out_size = (input.spatial_size - 1) * self.filter_stride + self.filter_size
         out = input.features.new_empty(0)
-        if not increment:
+        if not _residual(input, increment):
             madds = SCN.Deconvolution_updateOutput(
                 input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
                 out, self.weight, optionalTensor(self, "bias"))
@@ -154,7 +162,7 @@ class BatchNormalization(Module):
             (self.nPlanes, input.features.shape)
         out = input.features.new_empty(0)
         scratch = input.features.new_empty(0)
-        if not increment:
+        if not _residual(input, increment):
             SCN.BatchNormalization_updateOutput(
                 input.features, out, scratch, input.features.new_empty(0), self.running_mean, self.running_var,
                 optionalTensor(self, "weight"), optionalTensor(self, "bias"), self.eps, self.momentum, self.training,
@@ -231,6 +239,10 @@ class InputLayer(Module):
         return self
 
     def forward(self, input, increment=False):
+        """increment: False = full frame; True = the reference's residual update (insert-only, the changed set is
+        not dilated, results are approximate by design); "exact" = the frame's points are merged into the scene
+        kept from the last full or exact frame (after any delete_voxels / replace_voxels edits) and the network
+        recomputes the merged scene, so the result equals a full recompute and the kept scene advances."""
         assert len(input) >= 2, len(input)
         coords, feats = input[0], input[1]
         batch_size = int(input[2]) if len(input) > 2 else 0
@@ -239,15 +251,48 @@ class InputLayer(Module):
         feats = feats.float()
         output = SparseConvNetTensor(metadata=Metadata(self.dimension), spatial_size=self.spatial_size)
         out = feats.new_empty(0)
-        if not increment:
+        if increment == "exact":
+            assert self.mode == 4, "the exact incremental mode keeps per-voxel means (InputLayer mode 4)"
+            coords = coords.to(feats.device).long()
+            n_old = self.scene_coords.shape[0]
+            all_coords = torch.cat([self.scene_coords, coords], 0)
+            all_feats = torch.cat([self.scene_feats, feats], 0)
+            SCN.InputLayer_updateOutput(output.metadata, self.spatial_size, all_coords, all_feats, out, batch_size,
+                                        self.mode)
+            output.features = out
+            output.recompute_all = True
+            output.new_points = (n_old, coords.shape[0])
+            _keep(self, save_output=output, scene_coords=all_coords, scene_feats=all_feats)
+        elif not increment:
             SCN.InputLayer_updateOutput(output.metadata, self.spatial_size, coords, feats, out, batch_size, self.mode)
             output.features = out
-            _keep(self, save_output=output)
+            _keep(self, save_output=output, scene_coords=coords.to(feats.device).long(), scene_feats=feats)
         else:
             SCN.Incre_InputLayer_updateOutput(output.metadata, self.spatial_size, coords, feats, out, batch_size,
                                               self.mode, self.save_output.metadata, self.save_output.features)
             output.features = out
         return output
+
+    @staticmethod
+    def _voxel_keys(coords):
+        c = coords.long()
+        k = (c[:, 2] << 42) | (c[:, 1] << 21) | c[:, 0]
+        if c.shape[1] > 3:
+            k = k | (c[:, 3] << 58)
+        return k
+
+    def delete_voxels(self, coords):
+        """Removes every kept point that falls in one of the given voxels (effective at the next exact frame).
+        The reference has no deletion; here a deleted voxel simply is no longer part of the scene."""
+        coords = coords.to(self.scene_coords.device)
+        keep = ~torch.isin(self._voxel_keys(self.scene_coords), self._voxel_keys(coords))
+        _keep(self, scene_coords=self.scene_coords[keep], scene_feats=self.scene_feats[keep])
+
+    def replace_voxels(self, coords, feats):
+        """Replaces the content of the given voxels by one point each carrying `feats` (a re-drawn feature)."""
+        self.delete_voxels(coords)
+        _keep(self, scene_coords=torch.cat([self.scene_coords, coords.to(self.scene_coords.device).long()], 0),
+              scene_feats=torch.cat([self.scene_feats, feats.to(self.scene_feats.device).float()], 0))
 
 
 class OutputLayer(Module):
@@ -259,9 +304,12 @@ class OutputLayer(Module):
 
     def forward(self, input, increment=False):
         out = input.features.new_empty(0)
-        if not increment:
+        if not _residual(input, increment):
             SCN.OutputLayer_updateOutput(input.metadata, input.features, out)
             _keep(self, save_input_feats=input.features, save_meta=input.metadata)
+            if increment and input.new_points is not None:  # exact mode: rows of this frame's own points
+                first, count = input.new_points
+                out = out[first:first + count]
         else:
             SCN.Incre_OutputLayer_updateOutput(input.metadata, input.features, out, self.save_meta,
                                                self.save_input_feats)

@@ -3,10 +3,14 @@
 
 
 class SparseConvNetTensor(object):
-    def __init__(self, features=None, metadata=None, spatial_size=None):
+    def __init__(self, features=None, metadata=None, spatial_size=None, recompute_all=False, new_points=None):
         self.features = features
         self.metadata = metadata
         self.spatial_size = spatial_size
+        # set by InputLayer in the exact incremental mode: the tensor holds the whole merged scene, so the
+        # layers downstream run their full-frame path; new_points = (first, count) of the frame's own points
+        self.recompute_all = recompute_all
+        self.new_points = new_points
 
     def get_spatial_locations(self, spatial_size=None):
         """LongTensor [nActive, 4]: x, y, z, batch index of every active site, in row order."""
@@ -14,7 +18,8 @@ class SparseConvNetTensor(object):
 
     def like(self, features, spatial_size=None):
         """A tensor on the same metadata carrying other features."""
-        return SparseConvNetTensor(features, self.metadata, self.spatial_size if spatial_size is None else spatial_size)
+        return SparseConvNetTensor(features, self.metadata, self.spatial_size if spatial_size is None else spatial_size,
+                                   self.recompute_all, self.new_points)
 
     def detach(self):
         return self.like(self.features.detach())

@@ -125,3 +125,39 @@ def test_demo_py_flow_runs_unchanged(cuda):
     # the first frame moved the running statistics (train-mode BatchNorm)
     bn = [m for m in model.modules() if isinstance(m, scn.BatchNormalization)][0]
     assert float((bn.running_var - 1).abs().max()) > 0
+
+
+@pytest.mark.parametrize("precision,tol", [("fp32", 1e-4), ("tf32", 2e-2)])
+def test_exact_incremental_equals_full_recompute(cuda, precision, tol):
+    # BASELINE config 2 on a small UNet: frame t+1 deletes a 16^3 cube, inserts a sphere and re-draws 1 % of the
+    # features; the exact mode must equal a full recompute of frame t+1, and again after one more insertion
+    import sparseconvnet as scn
+    scn.set_precision(precision)
+    try:
+        torch.manual_seed(4)
+        model = small_unet(scn, [32, 64, 96], residual=True, full_scale=128).eval().to(cuda)
+        randomize_bn(model, 4)
+        c = synth.boxes_and_spheres(3)
+        f = synth.rgb(3, c.shape[0])
+        nf = synth.next_frame(c, f, seed=3)
+        n_red = nf["redraw_old_feats"].shape[0]
+        n_sph = nf["new_coords"].shape[0] - n_red
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+        model([dev(c), dev(f)])
+        il = model.sparseModel[0]
+        il.delete_voxels(dev(c[nf["deleted"]]))
+        il.replace_voxels(dev(nf["new_coords"][n_sph:]), dev(nf["new_feats"][n_sph:]))
+        got = model([dev(nf["new_coords"][:n_sph]), dev(nf["new_feats"][:n_sph])], "exact")
+        assert got.shape == (n_sph, 20)
+        fresh = small_unet(scn, [32, 64, 96], residual=True, full_scale=128).eval().to(cuda)
+        fresh.load_state_dict(model.state_dict())
+        want = fresh([dev(nf["coords"]), dev(nf["feats"])])[-n_sph:]
+        assert rel_err(got, want) <= tol
+        # the kept scene advanced: a further insertion is again exact
+        more = synth.sphere_surface((40, 40, 40), 7)
+        more_f = synth.rgb(9, more.shape[0])
+        got2 = model([dev(more), dev(more_f)], "exact")
+        want2 = fresh([dev(np.concatenate([nf["coords"], more], 0)), dev(np.concatenate([nf["feats"], more_f], 0))])
+        assert rel_err(got2, want2[-more.shape[0]:]) <= tol
+    finally:
+        scn.set_precision("fp32")
