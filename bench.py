@@ -203,6 +203,70 @@ def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
     return out
 
 
+def slab_bench(args, rank, world, local, dist):
+    """configs[4], second part: one 4M-voxel building split into x-slabs (one per GPU) with halo rows exchanged by
+    grouped NCCL send/recv after every submanifold and strided convolution.  Strong scaling: the scene is fixed."""
+    import numpy as np
+    import torch
+    import sparseconvnet as scn
+    from insconv import slab, synth
+    dev = torch.device("cuda", local)
+    scn.set_precision(args.precision)
+    model = build_model(scn, torch).to(dev)
+    coords = synth.building(0, target=args.voxels if args.voxels > 1000000 else 4000000)
+    feats = synth.rgb(0, coords.shape[0])
+    align = 2 ** (len(PLANES) - 1)
+    cuts = slab.cuts_for(coords[:, 0].min(), coords[:, 0].max(), world, align)
+    ext = slab.extended_mask(coords[:, 0], cuts, rank, align)
+    n_own = int(slab.owned_mask(coords[:, 0], cuts, rank).sum())
+    ex = slab.SlabExchange(dist, rank, world, cuts, 4096)
+    if world > 1:
+        slab.install(model, ex, (scn.SubmanifoldConvolution, scn.Convolution))
+    dc, df = torch.from_numpy(coords[ext]).to(dev), torch.from_numpy(feats[ext]).to(dev)
+
+    def frame():
+        return model([dc, df])
+
+    for _ in range(args.warmup):
+        frame()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = scn.SCN.launch_count()
+    e0.record()
+    for _ in range(args.steps):
+        frame()
+    e1.record()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = scn.SCN.launch_count() - l0
+    ssc_mods = [m for m in model.modules() if isinstance(m, scn.SubmanifoldConvolution)]
+    layers_local = sum(int(m.save_input_feats.shape[0]) for m in ssc_mods)
+    if dist is not None:
+        t = torch.tensor([ms, float(layers_local), float(ex.bytes_sent)], device=dev, dtype=torch.float64)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms, layers_all, sent = float(tmax[0]), float(t[1]), float(t[2])
+    else:
+        layers_all, sent = float(layers_local), 0.0
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": coords.shape[0] * 53 / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": args.precision, "data": "synthetic",
+                          "config": {"workload": "configs[4] part 2: one %d-voxel building (5 rooms x 4 floors) in %d x-slabs, "
+                                                 "halo rows exchanged by NCCL after every SSC / strided convolution"
+                                                 % (coords.shape[0], world),
+                                     "cuts": cuts, "ghost_zone_voxels": align,
+                                     "voxel_layers_computed_incl_ghost": layers_all,
+                                     "halo_bytes_sent_per_frame": sent / max(args.steps + args.warmup, 1),
+                                     "exchanges_per_frame": ex.exchanges // max(args.steps + args.warmup, 1)},
+                          "gpu_launches": int(launches)}))
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -258,6 +322,8 @@ def main():
     ap.add_argument("--legs", default="full,incre,e2e", help="which timed legs to run (profiling aid)")
     ap.add_argument("--layer", action="store_true", help="time one SSC layer alone (rulebook cached) and exit")
     ap.add_argument("--hash", action="store_true", help="time the grid build alone and exit")
+    ap.add_argument("--workload", default="room", choices=["room", "building"],
+                    help="room: one scene per GPU (default); building: one 4M-voxel scene split into x-slabs")
     ap.add_argument("--n-in", type=int, default=32)
     ap.add_argument("--n-out", type=int, default=32)
     ap.add_argument("--profile", action="store_true", help="allow fewer than 3 warm-up steps (numbers are not bench values)")
@@ -297,6 +363,11 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "building":
+        slab_bench(args, rank, world, local, dist)
+        if dist is not None:
+            dist.destroy_process_group()
+        return 0
     if args.hash:
         print(json.dumps({"hash_build": hash_bench(dev, args.steps, args.warmup, ("c1", "room") if args.quick else ("c1", "room", "building"))}))
         return 0

@@ -28,6 +28,10 @@ class OMeta(object):
             self.ssc_rules[size] = O.ssc_rules(self.grids[size])
         return self.ssc_rules[size]
 
+    def getSpatialLocations(self, size):
+        """[n,4] (x,y,z,batch) of the sites of a scale, in row order (Metadata::getSpatialLocations)."""
+        return torch.from_numpy(self.grids[tuple(int(v) for v in size)].coords.copy())
+
     def coarse(self, in_size, out_size):
         key = (in_size, out_size)
         if key not in self.conv_rules:
@@ -52,10 +56,12 @@ def _size(t):
 
 
 class GraphRunner(object):
-    def __init__(self, root):
+    def __init__(self, root, post=None):
+        """post(module, output): optional callback run on the output of every SubmanifoldConvolution and
+        Convolution (the multi-GPU slab tests exchange halo rows there)."""
         self.root = root
         self.saved = {}
-        self.times = {}
+        self.post = post
 
     def __call__(self, inputs, increment=False):
         return self._run(self.root, inputs, increment)
@@ -135,13 +141,19 @@ class GraphRunner(object):
                 x.metadata.ssc_rules[key] = O.incre_ssc_rules(g, pg)
             out = O.conv_forward(x.features, w, x.metadata.ssc(x.spatial_size), g.n, b)
             out = O.conv_forward(pre.features, w, x.metadata.ssc_rules[key], g.n, out=out)
-        return OTensor(out, x.metadata, x.spatial_size)
+        res = OTensor(out, x.metadata, x.spatial_size)
+        if self.post:
+            self.post(m, res)
+        return res
 
     def _Convolution(self, m, x, inc):
         out_size = tuple((s - int(f)) // int(st) + 1 for s, f, st in zip(x.spatial_size, m.filter_size, m.filter_stride))
         coarse, rules = x.metadata.coarse(x.spatial_size, out_size)
         out = O.conv_forward(x.features, _p(m, "weight"), rules, coarse.n, _p(m, "bias"))
-        return OTensor(out, x.metadata, out_size)
+        res = OTensor(out, x.metadata, out_size)
+        if self.post:
+            self.post(m, res)
+        return res
 
     def _Deconvolution(self, m, x, inc):
         out_size = tuple((s - 1) * int(st) + int(f) for s, f, st in zip(x.spatial_size, m.filter_size, m.filter_stride))

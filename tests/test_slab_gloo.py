@@ -1,0 +1,91 @@
+"""One scene split into x-slabs over two gloo ranks on CPU: halo rows exchanged after every submanifold and
+strided convolution.  The per-rank compute is the CPU oracle (this is test infrastructure); what is under test
+is the slab logic of insconv.slab -- cuts, ghost zone, row lists, exchange -- which is the code the GPU ranks run."""
+import os
+import socket
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PLANES = [8, 16, 24]
+
+
+def _paths():
+    for p in (ROOT, os.path.join(ROOT, "ins-conv_b200"), os.path.join(ROOT, "tests")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+
+
+def _model():
+    _paths()
+    import sparseconvnet as scn
+    from test_gpu_unet import small_unet, randomize_bn
+    torch.manual_seed(7)
+    model = small_unet(scn, PLANES, residual=True, full_scale=128).eval()
+    randomize_bn(model, 7)
+    return model
+
+
+def _scene():
+    _paths()
+    from insconv import synth
+    c = synth.boxes_and_spheres(5)
+    return c, synth.rgb(5, c.shape[0])
+
+
+def _worker(rank, world, port, out):
+    _paths()
+    from insconv import slab
+    from oracle.scn_graph import GraphRunner
+    dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+    model = _model()
+    c, f = _scene()
+    align = 2 ** (len(PLANES) - 1)
+    cuts = slab.cuts_for(c[:, 0].min(), c[:, 0].max(), world, align)
+    ext = slab.extended_mask(c[:, 0], cuts, rank, align)
+    own = slab.owned_mask(c[ext][:, 0], cuts, rank)
+    ex = slab.SlabExchange(dist, rank, world, cuts, 128)
+    runner = GraphRunner(model, post=lambda m, t: ex(t))
+    y = runner._run(model.linear, runner._run(model.sparseModel, [torch.from_numpy(c[ext]), torch.from_numpy(f[ext])], False), False)
+    out[rank] = (np.nonzero(ext)[0][own], y[torch.from_numpy(own)].numpy(), ex.exchanges, cuts)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_slabs_equal_the_whole_scene():
+    _paths()
+    from oracle.scn_graph import GraphRunner
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_worker, args=(2, port, out), nprocs=2, join=True)
+    model = _model()
+    c, f = _scene()
+    runner = GraphRunner(model)
+    want = runner._run(model.linear, runner._run(model.sparseModel, [torch.from_numpy(c), torch.from_numpy(f)], False), False).numpy()
+    got = np.full_like(want, np.nan)
+    for r in (0, 1):
+        idx, y, n_ex, cuts = out[r]
+        got[idx] = y
+        assert n_ex > 10  # one exchange per submanifold / strided convolution
+    assert not np.isnan(got).any()  # every point is owned by exactly one rank
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= 1e-5 * scale
+
+
+def test_cuts_are_aligned_and_cover():
+    _paths()
+    from insconv import slab
+    for world in (1, 2, 3, 8):
+        cuts = slab.cuts_for(8, 2007, world, 64)
+        assert len(cuts) == world + 1 and cuts[0] <= 8 and cuts[-1] > 2007
+        assert all(c % 64 == 0 for c in cuts) and all(b >= a for a, b in zip(cuts, cuts[1:]))
+    x = np.arange(0, 300)
+    cuts = slab.cuts_for(0, 299, 2, 64)
+    assert (slab.owned_mask(x, cuts, 0) ^ slab.owned_mask(x, cuts, 1)).all()
