@@ -11,6 +11,7 @@
 #include <torch/extension.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
+#include <cuda_runtime.h>
 
 #include <stdexcept>
 #include <string>
@@ -75,6 +76,21 @@ class Metadata3 {
     auto out = at::empty({n, 4}, at::TensorOptions().dtype(at::kLong).device(at::kCPU));
     check(scn_metadata_spatial_locations(h_, s.v, out.data_ptr<int64_t>(), (void *)c10::cuda::getCurrentCUDAStream().stream()),
           "getSpatialLocations");
+    return out;
+  }
+  // int32 CUDA tensor [4, n]: x, y, z, batch of every site in row order, without leaving the device
+  at::Tensor getSpatialLocationsDevice(at::Tensor spatialSize) {
+    Size3 s(spatialSize);
+    const int32_t *coords = nullptr;
+    int64_t n = 0;
+    check(scn_metadata_site_coords(h_, s.v, &coords, &n), "getSpatialLocationsDevice");
+    auto out = at::empty({4, n}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA));
+    if (n) {
+      auto stream = c10::cuda::getCurrentCUDAStream().stream();
+      TORCH_CHECK(cudaMemcpyAsync(out.data_ptr<int>(), coords, (size_t)n * 16, cudaMemcpyDeviceToDevice, stream) ==
+                      cudaSuccess,
+                  "getSpatialLocationsDevice: copy failed");
+    }
     return out;
   }
   int64_t getNActive(at::Tensor spatialSize) {
@@ -364,6 +380,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
       .def(pybind11::init<>())
       .def("clear", &Metadata3::clear)
       .def("getSpatialLocations", &Metadata3::getSpatialLocations)
+      .def("getSpatialLocationsDevice", &Metadata3::getSpatialLocationsDevice)
       .def("getNActive", &Metadata3::getNActive);
   mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput);
   mod.def("Convolution_updateOutput", &Convolution_updateOutput);

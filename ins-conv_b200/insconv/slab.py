@@ -48,22 +48,24 @@ class SlabExchange(object):
 
     def _rows(self, tensor):
         size = int(tensor.spatial_size[0])
-        key = (id(tensor.metadata), size)
-        hit = self.cache.get(key)
-        if hit is not None:
+        hit = self.cache.get(size)
+        if hit is not None and hit["meta"] is tensor.metadata:  # one entry per scale, replaced when the scene changes
             return hit
         shift = int(round(np.log2(self.full_scale / size)))
-        loc = tensor.metadata.getSpatialLocations(tensor.spatial_size)
-        x = torch.as_tensor(loc)[:, 0]
-        lo, hi = self.cuts[self.rank] >> shift, self.cuts[self.rank + 1] >> shift
         dev = tensor.features.device
+        if hasattr(tensor.metadata, "getSpatialLocationsDevice"):  # stays on the GPU
+            x = tensor.metadata.getSpatialLocationsDevice(tensor.spatial_size)[0]
+        else:
+            x = torch.as_tensor(tensor.metadata.getSpatialLocations(tensor.spatial_size))[:, 0]
+        lo, hi = self.cuts[self.rank] >> shift, self.cuts[self.rank + 1] >> shift
         rows = {
+            "meta": tensor.metadata,
             "send_left": torch.nonzero(x == lo).flatten().to(dev),       # my first owned plane
             "recv_left": torch.nonzero(x == lo - 1).flatten().to(dev),   # left neighbour's last plane
             "send_right": torch.nonzero(x == hi - 1).flatten().to(dev),
             "recv_right": torch.nonzero(x == hi).flatten().to(dev),
         }
-        self.cache[key] = rows
+        self.cache[size] = rows
         return rows
 
     def __call__(self, tensor):

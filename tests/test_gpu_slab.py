@@ -43,11 +43,11 @@ def _worker(rank, world, port, out):
     ex = slab.SlabExchange(dist, rank, world, cuts, 128)
     handles = slab.install(model, ex, (scn.SubmanifoldConvolution, scn.Convolution))
     y = model([torch.from_numpy(c[ext]).to(dev), torch.from_numpy(f[ext]).to(dev)])
-    res = {"idx": np.nonzero(ext)[0][own], "y": y[torch.from_numpy(own).to(dev)].cpu().numpy(), "n_ex": ex.exchanges}
+    res = {"idx": np.nonzero(ext)[0][own], "y": y[torch.from_numpy(own).to(dev)].detach().cpu().numpy(), "n_ex": ex.exchanges}
     if rank == 0:
         for h in handles:
             h.remove()
-        res["whole"] = model([torch.from_numpy(c).to(dev), torch.from_numpy(f).to(dev)]).cpu().numpy()
+        res["whole"] = model([torch.from_numpy(c).to(dev), torch.from_numpy(f).to(dev)]).detach().cpu().numpy()
     out[rank] = res
     dist.barrier()
     dist.destroy_process_group()
