@@ -51,6 +51,7 @@ extern "C" {
 /* arithmetic used by the gather-GEMM kernels */
 #define SCN_PREC_FP32 0      /* fp32 FFMA, fp32 accumulate (bit-for-bit deterministic)  */
 #define SCN_PREC_TF32 1      /* tcgen05 kind::tf32 tensor cores, fp32 accumulate in TMEM */
+#define SCN_PREC_TF32_PACKED 2 /* as TF32, and `weight` already is the packed copy made by scn_pack_weights */
 
 /* Largest coordinate and batch index a key can hold. */
 #define SCN_MAX_COORD 65534
@@ -146,6 +147,15 @@ SCN_API int scn_conv_rulebook(scn_metadata *m, const int64_t in_size[3], const i
  * Feature ops.  *flops receives the multiply-add count the reference returns
  * (pairs * n_in * n_out); may be NULL.
  * ------------------------------------------------------------------------- */
+/* The tensor-core kernels read the weights transposed, [volume, n_out, n_in].  Normally every convolution call
+ * makes that copy itself; a caller whose weights do not change between calls can make it once with this
+ * function (packed: device buffer of volume*n_in*n_out floats) and pass it as `weight` with
+ * SCN_PREC_TF32_PACKED.  Only shapes the tensor-core kernels accept can be packed: scn_weights_packable() != 0
+ * (n_in and n_out multiples of 32, n_out <= 256).  No counterpart in the reference. */
+SCN_API int scn_weights_packable(int64_t volume, int64_t n_in, int64_t n_out);
+SCN_API int scn_pack_weights(const float *weight, int64_t volume, int64_t n_in, int64_t n_out, float *packed,
+                             void *stream);
+
 /* Replaces cuda_SubmanifoldConvolution_updateOutput (CUDA/Convolution.cpp:152-218).
  * in [n, n_in], out [n, n_out] over the sites of `size`. */
 SCN_API int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,

@@ -343,6 +343,10 @@ int scn_conv_rulebook(scn_metadata *m, const int64_t in_size[3], const int64_t o
 }
 
 // ---- feature ops -------------------------------------------------------------------------------
+int scn_weights_packable(int64_t volume, int64_t n_in, int64_t n_out) { return tc_packable(volume, n_in, n_out) ? 1 : 0; }
+int scn_pack_weights(const float *weight, int64_t volume, int64_t n_in, int64_t n_out, float *packed, void *stream) {
+  return tc_pack_weights(weight, volume, n_in, n_out, packed, (cudaStream_t)stream);
+}
 int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
                     int64_t out_stride, const float *weight, const float *bias, int64_t n_in, int64_t n_out,
                     int precision, void *stream, double *flops) {

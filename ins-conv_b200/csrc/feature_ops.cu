@@ -140,19 +140,22 @@ k_gather_gemm_f32(const float *__restrict__ in, long long in_stride, const int32
 
 int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out, const float *W,
                      const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate,
-                     cudaStream_t s, bool *handled);
+                     bool packed, cudaStream_t s, bool *handled);
 
 int gather_gemm(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out, const float *W,
                 const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate,
                 int precision, cudaStream_t s) {
   if (n_out == 0) return SCN_OK;
   if (Cin <= 0 || Cout <= 0 || Cin > 65536 || Cout > 65536) return fail(SCN_E_INVALID, "bad plane count");
-  if (precision != SCN_PREC_FP32 && precision != SCN_PREC_TF32) return fail(SCN_E_INVALID, "unknown precision");
-  if (precision == SCN_PREC_TF32) {
+  if (precision != SCN_PREC_FP32 && precision != SCN_PREC_TF32 && precision != SCN_PREC_TF32_PACKED)
+    return fail(SCN_E_INVALID, "unknown precision");
+  if (precision != SCN_PREC_FP32) {
     bool handled = false;
-    SCN_TRY(gather_gemm_tf32(in, in_stride, in_rows, map, K, n_out, W, bias, out, out_stride, Cin, Cout, accumulate, s,
-                             &handled));
+    SCN_TRY(gather_gemm_tf32(in, in_stride, in_rows, map, K, n_out, W, bias, out, out_stride, Cin, Cout, accumulate,
+                             precision == SCN_PREC_TF32_PACKED, s, &handled));
     if (handled) return SCN_OK;
+    if (precision == SCN_PREC_TF32_PACKED)
+      return fail(SCN_E_INVALID, "packed weights given for a shape or alignment the tensor-core kernel does not take");
     // shapes the tensor-core kernel does not tile (n_in not a multiple of 8, ...) use the fp32 kernel,
     // which is at least as accurate.
   }

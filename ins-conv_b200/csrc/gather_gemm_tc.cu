@@ -953,6 +953,18 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 }  // namespace
 
+bool tc_packable(int64_t K, int64_t Cin, int64_t Cout) {
+  return K >= 1 && K <= 27 && Cin > 0 && Cout > 0 && Cin % 32 == 0 && Cout % 32 == 0 && Cout <= 256;
+}
+int tc_pack_weights(const float *W, int64_t K, int64_t Cin, int64_t Cout, float *packed, cudaStream_t s) {
+  if (!tc_packable(K, Cin, Cout)) return fail(SCN_E_INVALID, "shape cannot be packed for the tensor-core kernels");
+  if (!W || !packed) return fail(SCN_E_INVALID, "null pointer");
+  k_transpose_weights<<<dim3((unsigned)(Cout / 32), (unsigned)(Cin / 32), (unsigned)K), dim3(32, 8), 0, s>>>(W, packed, (int)Cin,
+                                                                                                          (int)Cout);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
 // Reads and clears the error word of the tensor-core kernels (synchronises the stream).
 int tc_check_errors(cudaStream_t s) {
   unsigned int e = 0, zero = 0;
@@ -967,7 +979,7 @@ int tc_check_errors(cudaStream_t s) {
 
 int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out, const float *W,
                      const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate,
-                     cudaStream_t s, bool *handled) {
+                     bool packed, cudaStream_t s, bool *handled) {
   *handled = false;
   if (Cin % 32 != 0 || Cout % 32 != 0 || Cout > 256 || K > 27) return SCN_OK;
   if (in_stride % 4 != 0 || out_stride % 4 != 0 || !aligned16(in) || !aligned16(W) || !aligned16(out)) return SCN_OK;
@@ -1011,12 +1023,17 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
       }
     }
   }
-  float *Wt = nullptr, *partial = nullptr;
-  SCN_TRY(dev_alloc_t(&Wt, (size_t)K * Cin * Cout, s));
+  float *Wt = nullptr, *Wt_own = nullptr, *partial = nullptr;
+  if (packed) {
+    Wt = const_cast<float *>(W);  // the caller made the transposed copy once (scn_pack_weights)
+  } else {
+    SCN_TRY(dev_alloc_t(&Wt_own, (size_t)K * Cin * Cout, s));
+    Wt = Wt_own;
+    k_transpose_weights<<<dim3((unsigned)(Cout / 32), (unsigned)(Cin / 32), (unsigned)K), dim3(32, 8), 0, s>>>(
+        W, Wt, (int)Cin, (int)Cout);
+    SCN_LAUNCHED();
+  }
   if (Z > 1) SCN_TRY(dev_alloc_t(&partial, (size_t)Z * tiles * kTileM * Cout, s));
-  k_transpose_weights<<<dim3((unsigned)(Cout / 32), (unsigned)(Cin / 32), (unsigned)K), dim3(32, 8), 0, s>>>(W, Wt, (int)Cin,
-                                                                                                          (int)Cout);
-  SCN_LAUNCHED();
   const dim3 grid((unsigned)tiles, (unsigned)Z);
   static const bool use_tma = []() {
     // INSCONV_TC_COPY=tma selects the kernel whose rows are staged by tile::gather4 bulk-tensor copies.
@@ -1094,7 +1111,7 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
     SCN_LAUNCHED();
   }
   dev_free(partial, s);
-  dev_free(Wt, s);
+  dev_free(Wt_own, s);
   *handled = true;
   return SCN_OK;
 }

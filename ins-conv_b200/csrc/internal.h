@@ -122,6 +122,8 @@ int gather_gemm(const float *in, int64_t in_stride, int64_t in_rows, const int32
                 int accumulate, int precision, cudaStream_t s);
 // reads and clears the error word of the tensor-core kernels; synchronises s
 int tc_check_errors(cudaStream_t s);
+bool tc_packable(int64_t K, int64_t Cin, int64_t Cout);
+int tc_pack_weights(const float *W, int64_t K, int64_t Cin, int64_t Cout, float *packed, cudaStream_t s);
 int nin_forward_noalloc(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
                         const float *W, const float *bias, int64_t Cin, int64_t Cout, cudaStream_t s);
 int bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,

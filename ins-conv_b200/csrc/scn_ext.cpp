@@ -60,6 +60,23 @@ void expect_filter(const at::Tensor &filt, int64_t want, const char *what) {
     TORCH_CHECK(c.data_ptr<int64_t>()[i] == want, what, ": only filter size / stride ", want, " is supported");
 }
 
+// Weights for a convolution call: the caller's packed copy (made once by pack_weights) when the tensor-core
+// path is selected and a matching copy was handed in, else the plain weights.
+struct WeightArg {
+  const float *ptr;
+  int precision;
+  WeightArg(const at::Tensor &w, const at::Tensor &packed) {
+    if (g_precision == SCN_PREC_TF32 && packed.defined() && packed.numel() == w.numel() && packed.numel() > 0 &&
+        packed.is_cuda() && packed.scalar_type() == at::kFloat) {
+      ptr = packed.data_ptr<float>();
+      precision = SCN_PREC_TF32_PACKED;
+    } else {
+      ptr = w.data_ptr<float>();
+      precision = g_precision;
+    }
+  }
+};
+
 class Metadata3 {
  public:
   Metadata3() { check(scn_metadata_create(&h_), "Metadata"); }
@@ -105,7 +122,7 @@ class Metadata3 {
 // ---- full-frame ops ------------------------------------------------------------------------------
 double SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filterSize, Metadata3 &m,
                                            at::Tensor input_features, at::Tensor output_features, at::Tensor weight,
-                                           at::Tensor bias, int dilated_rate) {
+                                           at::Tensor bias, int dilated_rate, at::Tensor packed) {
   need_cuda_f32(input_features, "input_features");
   need_cuda_f32(weight, "weight");
   TORCH_CHECK(dilated_rate == 1, "dilated submanifold convolutions are outside the hot path");
@@ -120,15 +137,16 @@ double SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filt
   TORCH_CHECK(in.size(0) == n && in.size(1) == w.size(1), "input_features must be [nActive, nIn]");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
+  WeightArg wa(w, packed);
   check(scn_ssc_forward(m.h(), s.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(), w.size(2),
-                        w.data_ptr<float>(), opt_ptr(bias), w.size(1), w.size(2), g_precision, stream_of(in), &flops),
+                        wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision, stream_of(in), &flops),
         "SubmanifoldConvolution_updateOutput");
   return flops;
 }
 
 double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
                                 at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
-                                at::Tensor output_features, at::Tensor weight, at::Tensor bias) {
+                                at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed) {
   need_cuda_f32(input_features, "input_features");
   need_cuda_f32(weight, "weight");
   expect_filter(filterSize, 2, "Convolution");
@@ -142,8 +160,9 @@ double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at:
   check(scn_conv_prepare(m.h(), si.v, so.v, stream_of(in), &n), "Convolution_updateOutput");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
+  WeightArg wa(w, packed);
   check(scn_conv_forward(m.h(), si.v, so.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(),
-                         w.size(2), w.data_ptr<float>(), opt_ptr(bias), w.size(1), w.size(2), g_precision,
+                         w.size(2), wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision,
                          stream_of(in), &flops),
         "Convolution_updateOutput");
   return flops;
@@ -151,7 +170,7 @@ double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at:
 
 double Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
                                   at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
-                                  at::Tensor output_features, at::Tensor weight, at::Tensor bias) {
+                                  at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed) {
   need_cuda_f32(input_features, "input_features");
   need_cuda_f32(weight, "weight");
   expect_filter(filterSize, 2, "Deconvolution");
@@ -164,8 +183,9 @@ double Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, a
   TORCH_CHECK(n >= 0, "Deconvolution: Metadata has no grid at the output spatial size");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
+  WeightArg wa(w, packed);
   check(scn_deconv_forward(m.h(), si.v, so.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(),
-                           w.size(2), w.data_ptr<float>(), opt_ptr(bias), w.size(1), w.size(2), g_precision,
+                           w.size(2), wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision,
                            stream_of(in), &flops),
         "Deconvolution_updateOutput");
   return flops;
@@ -197,7 +217,7 @@ void BatchNormalization_updateOutput(at::Tensor input_features, at::Tensor outpu
 }
 
 double NetworkInNetwork_updateOutput(at::Tensor input_features, at::Tensor output_features, at::Tensor weight,
-                                     at::Tensor bias) {
+                                     at::Tensor bias, at::Tensor packed) {
   need_cuda_f32(input_features, "input_features");
   need_cuda_f32(weight, "weight");
   c10::cuda::CUDAGuard guard(input_features.device());
@@ -205,8 +225,9 @@ double NetworkInNetwork_updateOutput(at::Tensor input_features, at::Tensor outpu
   auto w = weight.contiguous();
   output_features.resize_({in.size(0), w.size(1)});
   double flops = 0;
+  WeightArg wa(w, packed);
   check(scn_nin_forward(in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(), w.size(1), in.size(0),
-                        w.data_ptr<float>(), opt_ptr(bias), w.size(0), w.size(1), g_precision, stream_of(in), &flops),
+                        wa.ptr, opt_ptr(bias), w.size(0), w.size(1), wa.precision, stream_of(in), &flops),
         "NetworkInNetwork_updateOutput");
   return flops;
 }
@@ -255,7 +276,7 @@ void OutputLayer_updateOutput(Metadata3 &m, at::Tensor input_features, at::Tenso
 double Incre_SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filterSize, Metadata3 &m,
                                                  at::Tensor input_features, at::Tensor output_features,
                                                  at::Tensor weight, at::Tensor bias, Metadata3 &pre_m,
-                                                 at::Tensor pre_input_feats) {
+                                                 at::Tensor pre_input_feats, at::Tensor packed) {
   need_cuda_f32(input_features, "input_features");
   need_cuda_f32(pre_input_feats, "pre_input_feats");
   expect_filter(filterSize, 3, "SubmanifoldConvolution");
@@ -268,9 +289,10 @@ double Incre_SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tenso
   TORCH_CHECK(n >= 0, "Metadata has no grid at this spatial size");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
+  WeightArg wa(w, packed);
   check(scn_incre_ssc_forward(m.h(), pre_m.h(), s.v, in.data_ptr<float>(), in.size(1),
-                              output_features.data_ptr<float>(), w.size(2), w.data_ptr<float>(), opt_ptr(bias),
-                              pre.data_ptr<float>(), pre.size(1), w.size(1), w.size(2), g_precision, stream_of(in),
+                              output_features.data_ptr<float>(), w.size(2), wa.ptr, opt_ptr(bias),
+                              pre.data_ptr<float>(), pre.size(1), w.size(1), w.size(2), wa.precision, stream_of(in),
                               &flops),
         "Incre_SubmanifoldConvolution_updateOutput");
   return flops;
@@ -278,17 +300,17 @@ double Incre_SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tenso
 
 double Incre_Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
                                       at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
-                                      at::Tensor output_features, at::Tensor weight, at::Tensor bias) {
+                                      at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed) {
   // a 2/2 convolution has no overlap between cells: the residual of the output is the convolution of
   // the residual (reference: CUDA/Convolution.cpp:83-113)
   return Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features, output_features,
-                                  weight, bias);
+                                  weight, bias, packed);
 }
 
 double Incre_Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
                                         at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
                                         at::Tensor output_features, at::Tensor weight, at::Tensor bias,
-                                        Metadata3 &pre_m, at::Tensor pre_input_feats) {
+                                        Metadata3 &pre_m, at::Tensor pre_input_feats, at::Tensor packed) {
   need_cuda_f32(input_features, "input_features");
   need_cuda_f32(pre_input_feats, "pre_input_feats");
   c10::cuda::CUDAGuard guard(input_features.device());
@@ -300,9 +322,10 @@ double Incre_Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputS
   TORCH_CHECK(n >= 0, "Deconvolution: Metadata has no grid at the output spatial size");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
+  WeightArg wa(w, packed);
   check(scn_incre_deconv_forward(m.h(), pre_m.h(), si.v, so.v, in.data_ptr<float>(), in.size(1),
-                                 output_features.data_ptr<float>(), w.size(2), w.data_ptr<float>(), opt_ptr(bias),
-                                 pre.data_ptr<float>(), pre.size(1), w.size(1), w.size(2), g_precision, stream_of(in),
+                                 output_features.data_ptr<float>(), w.size(2), wa.ptr, opt_ptr(bias),
+                                 pre.data_ptr<float>(), pre.size(1), w.size(1), w.size(2), wa.precision, stream_of(in),
                                  &flops),
         "Incre_Deconvolution_updateOutput");
   return flops;
@@ -361,6 +384,19 @@ void Incre_OutputLayer_updateOutput(Metadata3 &m, at::Tensor input_features, at:
         "Incre_OutputLayer_updateOutput");
 }
 
+// Transposed copy of a convolution weight for the tensor-core kernels; an empty tensor when the shape is not
+// one those kernels take.  weight: [volume, nIn, nOut] or [nIn, nOut].
+at::Tensor pack_weights(at::Tensor weight) {
+  need_cuda_f32(weight, "weight");
+  auto w = weight.contiguous();
+  const int64_t vol = w.dim() == 3 ? w.size(0) : 1, n_in = w.size(w.dim() - 2), n_out = w.size(w.dim() - 1);
+  if (!scn_weights_packable(vol, n_in, n_out)) return at::empty({0}, w.options());
+  c10::cuda::CUDAGuard guard(w.device());
+  auto packed = at::empty_like(w);
+  check(scn_pack_weights(w.data_ptr<float>(), vol, n_in, n_out, packed.data_ptr<float>(), stream_of(w)), "pack_weights");
+  return packed;
+}
+
 void set_precision(const std::string &p) {
   if (p == "fp32") g_precision = SCN_PREC_FP32;
   else if (p == "tf32") g_precision = SCN_PREC_TF32;
@@ -382,20 +418,21 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
       .def("getSpatialLocations", &Metadata3::getSpatialLocations)
       .def("getSpatialLocationsDevice", &Metadata3::getSpatialLocationsDevice)
       .def("getNActive", &Metadata3::getNActive);
-  mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput);
-  mod.def("Convolution_updateOutput", &Convolution_updateOutput);
-  mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput);
+  mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("dilated_rate"), pybind11::arg("packed") = at::Tensor());
+  mod.def("Convolution_updateOutput", &Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());
+  mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());
   mod.def("BatchNormalization_updateOutput", &BatchNormalization_updateOutput);
-  mod.def("NetworkInNetwork_updateOutput", &NetworkInNetwork_updateOutput);
+  mod.def("NetworkInNetwork_updateOutput", &NetworkInNetwork_updateOutput, pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());
   mod.def("InputLayer_updateOutput", &InputLayer_updateOutput);
   mod.def("OutputLayer_updateOutput", &OutputLayer_updateOutput);
-  mod.def("Incre_SubmanifoldConvolution_updateOutput", &Incre_SubmanifoldConvolution_updateOutput);
-  mod.def("Incre_Convolution_updateOutput", &Incre_Convolution_updateOutput);
-  mod.def("Incre_Deconvolution_updateOutput", &Incre_Deconvolution_updateOutput);
+  mod.def("Incre_SubmanifoldConvolution_updateOutput", &Incre_SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("pre_metadata"), pybind11::arg("pre_input_feats"), pybind11::arg("packed") = at::Tensor());
+  mod.def("Incre_Convolution_updateOutput", &Incre_Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());
+  mod.def("Incre_Deconvolution_updateOutput", &Incre_Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("pre_metadata"), pybind11::arg("pre_input_feats"), pybind11::arg("packed") = at::Tensor());
   mod.def("Incre_BatchNormalization_updateOutput", &Incre_BatchNormalization_updateOutput);
   mod.def("Incre_InputLayer_updateOutput", &Incre_InputLayer_updateOutput);
   mod.def("Incre_OutputLayer_updateOutput", &Incre_OutputLayer_updateOutput);
   mod.def("n_rulebook_bits", []() { return scn_n_rulebook_bits(); });
+  mod.def("pack_weights", &pack_weights, "transposed weight copy for the tensor-core kernels (empty if not applicable)");
   mod.def("set_precision", &set_precision, "arithmetic of the convolution kernels: 'fp32' or 'tf32'");
   mod.def("get_precision", &get_precision);
   mod.def("launch_count", []() { return scn_launch_count(); });

@@ -17,6 +17,7 @@ HEADER_PATH = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "include", "
 
 PREC_FP32 = 0
 PREC_TF32 = 1
+PREC_TF32_PACKED = 2
 
 
 class ScnError(RuntimeError):
@@ -53,6 +54,8 @@ PROTOTYPES = {
     "scn_input_layer_rules": (_int, [_p, _p, _p, _p]),
     "scn_ssc_rulebook": (_int, [_p, _i64p, _p, _p, _p]),
     "scn_conv_rulebook": (_int, [_p, _i64p, _i64p, _p, _p, _p]),
+    "scn_weights_packable": (_int, [_i64, _i64, _i64]),
+    "scn_pack_weights": (_int, [_p, _i64, _i64, _i64, _p, _p]),
     "scn_ssc_forward": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_conv_prepare": (_int, [_p, _i64p, _i64p, _p, _i64p]),
     "scn_conv_forward": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
@@ -70,7 +73,7 @@ PROTOTYPES = {
     "scn_incre_bn_forward": (_int, [_p, _p, _i64p, _p, _i64, _p, _i64, _i64, _p, _p, _p, _p, _dbl, _dbl, _p, _p, _p]),
 }
 
-_STATUS = {n for n, (r, _) in PROTOTYPES.items() if r is _int and n != "scn_n_rulebook_bits"}
+_STATUS = {n for n, (r, _) in PROTOTYPES.items() if r is _int and n not in ("scn_n_rulebook_bits", "scn_weights_packable")}
 
 
 def declared_symbols():

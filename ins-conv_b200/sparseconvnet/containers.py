@@ -11,10 +11,17 @@ class _Container(torch.nn.Sequential):
         return self
 
 
+def _run(module, input, increment):
+    """module(input, increment) without torch.nn.Module.__call__'s bookkeeping when no hook is installed."""
+    if module._forward_hooks or module._forward_pre_hooks:
+        return module(input, increment)
+    return module.forward(input, increment)
+
+
 class Sequential(_Container):
     def forward(self, input, increment=False):
-        for module in self:
-            input = module(input, increment)
+        for module in self._modules.values():
+            input = _run(module, input, increment)
         return input
 
     def input_spatial_size(self, out_size):
@@ -27,7 +34,7 @@ class ConcatTable(_Container):
     """Feeds the same input to every child and returns the list of results."""
 
     def forward(self, input, increment=False):
-        return [module(input, increment) for module in self]
+        return [_run(module, input, increment) for module in self._modules.values()]
 
     def input_spatial_size(self, out_size):
         return self._modules["0"].input_spatial_size(out_size)

@@ -22,6 +22,8 @@ from .metadata import Metadata
 from .tensor import SparseConvNetTensor
 from .utils import toLongTensor, optionalTensor
 
+_NONE = torch.empty(0)
+
 
 def _keep(module, **state):
     """Stores per-frame state on a module without torch.nn.Module.__setattr__ (which walks the parameter,
@@ -35,6 +37,20 @@ def _residual(input, increment):
     if isinstance(input, (list, tuple)):
         input = input[0]
     return bool(increment) and not getattr(input, "recompute_all", False)
+
+
+def _packed(module):
+    """The tensor-core kernels read weights transposed.  The copy is made once per weight version and kept on the
+    module (keyed on the Parameter object, its version counter and its address), instead of once per call."""
+    if SCN.get_precision() != "tf32":
+        return _NONE
+    w = module.weight
+    c = module.__dict__.get("_pack_cache")
+    if c is not None and c[0] is w and c[1] == w._version and c[2] == w.data_ptr():
+        return c[3]
+    p = SCN.pack_weights(w) if w.is_cuda else _NONE
+    module.__dict__["_pack_cache"] = (w, w._version, w.data_ptr(), p)
+    return p
 
 
 def _count(madds, out):
@@ -67,12 +83,12 @@ class SubmanifoldConvolution(Module):
         if not _residual(input, increment):
             madds = SCN.SubmanifoldConvolution_updateOutput(
                 input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
-                optionalTensor(self, "bias"), self.dilated_rate)
+                optionalTensor(self, "bias"), self.dilated_rate, _packed(self))
             _keep(self, save_meta=input.metadata, save_input_feats=input.features)
         else:
             madds = SCN.Incre_SubmanifoldConvolution_updateOutput(
                 input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
-                optionalTensor(self, "bias"), self.save_meta, self.save_input_feats)
+                optionalTensor(self, "bias"), self.save_meta, self.save_input_feats, _packed(self))
         _count(madds, out)
         return input.like(out)
 
@@ -108,7 +124,7 @@ class Convolution(_Strided):
         out = input.features.new_empty(0)
         op = SCN.Incre_Convolution_updateOutput if _residual(input, increment) else SCN.Convolution_updateOutput
         madds = op(input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                   out, self.weight, optionalTensor(self, "bias"))
+                   out, self.weight, optionalTensor(self, "bias"), _packed(self))
         _count(madds, out)
         return input.like(out, out_size)
 
@@ -127,12 +143,12 @@ class Deconvolution(_Strided):
         if not _residual(input, increment):
             madds = SCN.Deconvolution_updateOutput(
                 input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                out, self.weight, optionalTensor(self, "bias"))
+                out, self.weight, optionalTensor(self, "bias"), _packed(self))
             _keep(self, save_meta=input.metadata, save_input_feats=input.features)
         else:
             madds = SCN.Incre_Deconvolution_updateOutput(
                 input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                out, self.weight, optionalTensor(self, "bias"), self.save_meta, self.save_input_feats)
+                out, self.weight, optionalTensor(self, "bias"), self.save_meta, self.save_input_feats, _packed(self))
         _count(madds, out)
         return input.like(out, out_size)
 
@@ -207,7 +223,8 @@ class NetworkInNetwork(Module):
     def forward(self, input, increment=False):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, input.features.shape)
         out = input.features.new_empty(0)
-        madds = SCN.NetworkInNetwork_updateOutput(input.features, out, self.weight, optionalTensor(self, "bias"))
+        madds = SCN.NetworkInNetwork_updateOutput(input.features, out, self.weight, optionalTensor(self, "bias"),
+                                                  _packed(self))
         _count(madds, out)
         return input.like(out)
 
