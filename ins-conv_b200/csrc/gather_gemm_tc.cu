@@ -2,24 +2,29 @@
 //
 //     out[o] = init(o) + sum_k in[ map[k][o] ] * W[k]           (same contract as the fp32 kernel)
 //
-// One CTA owns 128 consecutive output rows and all n_out <= 256 output planes; the accumulator tile
-// [128 x n_out] fp32 lives in tensor memory.  The reduction runs over (offset k, 32-plane block kb):
-// for every step the 128 threads stage
+// A work item is a tile of 128 consecutive output rows and all n_out <= 256 output planes; its accumulator
+// [128 x n_out] fp32 lives in tensor memory.  The reduction runs over (offset k, 32-plane block kb); every
+// step stages
 //     A = the 128 gathered input rows x 32 planes (16 KB)  -> K-major, 128-byte swizzle
 //     B = W[k]^T, n_out rows x 32 planes                    -> K-major, 128-byte swizzle
-// with 16-byte cp.async copies (missing neighbours are zero-filled without touching memory), and one
-// thread issues four tcgen05.mma (K = 8 each) on the staged tile.  A ring of stages keeps several steps
-// of copies in flight while the tensor core works; tcgen05.commit signals an mbarrier when the MMAs
-// that read a stage have retired, which is what lets the stage be refilled.  Offsets for which no row
-// of the tile has a neighbour are skipped altogether.  The epilogue reads TMEM with tcgen05.ld (one
-// row per thread), adds the bias or the previous output and writes each output row exactly once.
+// and issues four tcgen05.mma (K = 8 each).  Offsets for which no row of the tile has a neighbour are skipped.
+// The weights are used transposed, [volume][n_out][n_in], so that both operands are K-major (the layout in
+// which 32-bit operands take the plain 128-byte swizzle); the copy is made per call, or once by the caller
+// (scn_pack_weights).  fp32 inputs are consumed as tf32 (the low 13 mantissa bits are ignored), accumulation
+// is fp32.
 //
-// The weights are transposed once per call to [volume][n_out][n_in] by a small kernel, so that both
-// operands are K-major (the layout in which 32-bit operands take the plain 128-byte swizzle).
+// Two kernels:
+//   k_gather_gemm_tf32_persist  the production kernel: persistent CTAs, warp-specialised (cp.async producers for
+//                               the gathered rows, one bulk-tensor (TMA) copy per step for the weight block, one
+//                               lane driving the tensor core, epilogue warps), two accumulators, split-K items
+//   k_gather_gemm_tf32          one CTA per tile, all threads copy and one issues the MMAs, a CTA barrier per
+//                               step; kept for the entry point that must not allocate and as a fallback
+// Staging the gathered rows with bulk-tensor copies in tile::gather4 mode (four rows per request) was built
+// and measured too: correct, but 1.3x slower than cp.async on the 250k-voxel layer, because the copy engine keeps
+// few such small requests in flight; it is not part of the code any more.
 //
-// fp32 inputs are consumed as tf32 (the low 13 mantissa bits are ignored), accumulation is fp32.
 // Every wait on an mbarrier is bounded; a wait that runs out sets an error word that the host reads
-// at its next synchronisation, and the kernel still releases its tensor memory before returning.
+// at its next scn_check_errors, and the kernel still releases its tensor memory before returning.
 #include "internal.h"
 #ifdef SCN_TC_PROFILE
 #include <stdio.h>
@@ -332,210 +337,16 @@ k_gather_gemm_tf32(const float *__restrict__ in, long long in_stride, const int3
 }
 
 // ---------------------------------------------------------------------------------------------
-// TMA-fed, warp-specialised variant
+// bulk-tensor (TMA) helpers
 // ---------------------------------------------------------------------------------------------
-// Same tile and the same shared-memory layout as above, but the operands are staged by the tensor
-// memory accelerator and the roles are split by warp, so no thread ever waits for a copy it issued:
-//   warp 0  producer: per step one tile::gather4 bulk-tensor copy per lane (4 gathered rows x 128 bytes
-//           each, the hardware applies the 128-byte swizzle and zero-fills rows whose index is -1) plus one
-//           2-D bulk-tensor copy of the weight block; the copies complete on the step's `full` mbarrier
-//   warp 1  consumer: waits `full`, issues the four tcgen05.mma, tcgen05.commit -> the slot's `empty` barrier
-//   all 4   epilogue: TMEM -> registers -> global
-// The producer runs up to STAGES steps ahead of the tensor core.
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap *tm, uint32_t bar, int col, int r0, int r1,
-                                            int r2, int r3) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
-      : "memory");
 }
 __device__ __forceinline__ void tma_tile2d(uint32_t dst, const CUtensorMap *tm, uint32_t bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
-}
-
-struct alignas(16) CtlTma {
-  unsigned long long full[8];   // per slot: the step's copies have landed
-  unsigned long long empty[8];  // per slot: the MMAs that read it have retired
-  unsigned long long acc;
-  uint32_t tmem_base;
-  int failed;
-  int nk;
-  unsigned int kmask;
-  int klist[32];
-};
-
-template <int STAGES>
-__global__ void __launch_bounds__(kThreads)
-k_gather_gemm_tf32_tma(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                       const int32_t *__restrict__ map, int K, long long n_out, const float *__restrict__ bias,
-                       float *__restrict__ out, long long out_stride, int Cin, int Cout, int accumulate,
-                       uint32_t tmem_cols, float *__restrict__ partial) {
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  const uint32_t stage_bytes = kABytes + (uint32_t)Cout * 128u;
-  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  CtlTma *ctl = reinterpret_cast<CtlTma *>(smem + (size_t)STAGES * stage_bytes);
-  int *s_map = reinterpret_cast<int *>(ctl + 1);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const long long row0 = (long long)blockIdx.x * kTileM;
-  const int KB = Cin >> 5;
-
-  if (tid == 0) {
-    ctl->failed = 0;
-    ctl->kmask = 0;
-  }
-  __syncthreads();
-  {
-    const long long row = row0 + tid;
-    unsigned int mine = 0;
-#pragma unroll
-    for (int k = 0; k < 27; ++k) {
-      if (k < K) {
-        int v = -1;
-        if (row < n_out) v = map ? __ldg(map + (long long)k * n_out + row) : (int)row;
-        s_map[k * kTileM + tid] = v;
-        mine |= (v >= 0 ? 1u : 0u) << k;
-      }
-    }
-    mine = __reduce_or_sync(0xffffffffu, mine);
-    if (lane == 0 && mine) atomicOr(&ctl->kmask, mine);
-  }
-  __syncthreads();
-  if (tid == 0) {
-    int n = 0;
-    const unsigned int km = ctl->kmask;
-    for (int k = 0; k < K; ++k)
-      if (km >> k & 1u) ctl->klist[n++] = k;
-    ctl->nk = n;
-  }
-  __syncthreads();
-  const int nk = ctl->nk;
-  const int Tall = nk * KB;
-  const int t0 = (int)(((long long)Tall * blockIdx.y) / gridDim.y);
-  const int T = (int)(((long long)Tall * (blockIdx.y + 1)) / gridDim.y) - t0;
-  float *pdst = partial ? partial + ((long long)blockIdx.y * gridDim.x * kTileM + (long long)blockIdx.x * kTileM) * Cout : nullptr;
-  if (T == 0) {
-    if (pdst) {
-      for (int i = tid; i < kTileM * Cout; i += kThreads) pdst[i] = 0.f;
-    } else if (!accumulate) {
-      for (long long i = tid; i < (long long)kTileM * Cout; i += kThreads) {
-        const long long row = row0 + i / Cout;
-        const int c = (int)(i % Cout);
-        if (row < n_out) out[row * out_stride + c] = bias ? __ldg(bias + c) : 0.f;
-      }
-    }
-    return;
-  }
-
-  if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&ctl->full[s]), 1);
-      mbar_init(smem_u32(&ctl->empty[s]), 1);
-    }
-    mbar_init(smem_u32(&ctl->acc), 1);
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-  }
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&ctl->tmem_base)),
-                 "r"(tmem_cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_d = ctl->tmem_base;
-  const uint32_t smem_base = smem_u32(smem);
-  volatile int *failed = &ctl->failed;
-
-  if (warp == 0) {
-    // ---- producer ------------------------------------------------------------------------------
-    for (int it = 0; it < T; ++it) {
-      const int slot = it % STAGES, use = it / STAGES;
-      if (use > 0) mbar_wait(smem_u32(&ctl->empty[slot]), (uint32_t)((use - 1) & 1), failed);
-      if (*failed) break;
-      const int k = ctl->klist[((t0 + it) / KB + (int)(blockIdx.x % 27u)) % nk];
-      const int kb = (t0 + it) % KB;
-      const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
-      const uint32_t bar = smem_u32(&ctl->full[slot]);
-      if (lane == 0) mbar_expect_tx(bar, stage_bytes);
-      __syncwarp();
-      const int4 rows = *reinterpret_cast<const int4 *>(s_map + k * kTileM + lane * 4);
-      tma_gather4(a_base + (uint32_t)lane * 512u, &tmA, bar, kb << 5, rows.x, rows.y, rows.z, rows.w);
-      if (lane == 0) tma_tile2d(a_base + kABytes, &tmB, bar, kb << 5, k * Cout);
-    }
-  } else if (warp == 1) {
-    // ---- consumer: one lane drives the tensor core ------------------------------------------------
-    if (lane == 0) {
-      const uint32_t idesc = instr_desc(Cout);
-      for (int it = 0; it < T; ++it) {
-        const int slot = it % STAGES;
-        if (!mbar_wait(smem_u32(&ctl->full[slot]), (uint32_t)((it / STAGES) & 1), failed)) break;
-        tc_fence_after();
-        const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
-        const uint32_t b_base = a_base + kABytes;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint64_t a_desc = smem_desc(a_base + j * 32, 16, 1024);
-          const uint64_t b_desc = smem_desc(b_base + j * 32, 16, 1024);
-          mma_tf32(tmem_d, a_desc, b_desc, idesc, (it > 0 || j > 0) ? 1u : 0u);
-        }
-        mma_commit(smem_u32(&ctl->empty[slot]));
-        if (it == T - 1) mma_commit(smem_u32(&ctl->acc));
-      }
-    }
-    __syncwarp();
-  }
-
-  // ---- epilogue -----------------------------------------------------------------------------------
-  mbar_wait(smem_u32(&ctl->acc), 0, failed);
-  __syncthreads();
-  const bool ok = !*failed;
-  tc_fence_after();
-  if (ok) {
-    const long long row = row0 + warp * 32 + lane;
-    for (int c0 = 0; c0 < Cout; c0 += 32) {
-      float v[32];
-      tmem_ld32(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
-      if (pdst) {
-        float *o = pdst + (long long)(warp * 32 + lane) * Cout + c0;
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-      } else if (row < n_out) {
-        float *o = out + row * out_stride + c0;
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          float4 r = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          if (accumulate) {
-            const float4 old = *reinterpret_cast<const float4 *>(o + j);
-            r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
-          } else if (bias) {
-            r.x += __ldg(bias + c0 + j); r.y += __ldg(bias + c0 + j + 1);
-            r.z += __ldg(bias + c0 + j + 2); r.w += __ldg(bias + c0 + j + 3);
-          }
-          *reinterpret_cast<float4 *>(o + j) = r;
-        }
-      }
-    }
-  } else if (warp == 0 && lane == 0) {
-    // a wait ran out: give copies that may still be in flight a bounded time to land before the CTA
-    // (and its shared memory) goes away
-    for (int s = 0; s < STAGES; ++s)
-      for (uint32_t i = 0; i < (1u << 16); ++i)
-        if (mbar_try_wait(smem_u32(&ctl->full[s]), 0) || mbar_try_wait(smem_u32(&ctl->full[s]), 1)) break;
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_d), "r"(tmem_cols) : "memory");
-  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -577,8 +388,7 @@ __global__ void __launch_bounds__(kPThreads, 1)
 k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, const __grid_constant__ CUtensorMap tmB,
                            const int32_t *__restrict__ map, int K, long long n_out, const float *__restrict__ bias,
                            float *__restrict__ out, long long out_stride, int Cin, int Cout, int accumulate,
-                           uint32_t acc_cols, int stages, long long tiles, int Z, float *__restrict__ partial,
-                           int dbg) {
+                           uint32_t acc_cols, int stages, long long tiles, int Z, float *__restrict__ partial) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t b_bytes = (uint32_t)Cout * 128u;
   const uint32_t stage_bytes = kABytes + b_bytes;
@@ -698,7 +508,6 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
         PROF(long long te1 = clock64(); t_empty += te1 - te0;)
         const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
         const uint32_t bar = smem_u32(&ctl->full[slot]);
-        if (!(dbg & 8)) {
         const int *mr = mrows + k * kTileM + r0;
         int src[4];
 #pragma unroll
@@ -707,17 +516,12 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float *p = src[j] >= 0 ? in_kb + (long long)src[j] * in_stride : in;
-          if (!(dbg & 2)) cp_async16(a_base + dst0 + (uint32_t)(j << 12), p, src[j] >= 0 ? 16u : 0u);
-        }
+          cp_async16(a_base + dst0 + (uint32_t)(j << 12), p, src[j] >= 0 ? 16u : 0u);
         }
         if (tp == 0) {
           ctl->info[slot] = (it == 0 ? kInfoFirst : 0u) | (it == T - 1 ? kInfoLast : 0u);
-          if (dbg & 4) {
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-          } else {
-            mbar_expect_tx(bar, b_bytes);
-            tma_tile2d(a_base + kABytes, &tmB, bar, kb << 5, k * Cout);
-          }
+          mbar_expect_tx(bar, b_bytes);
+          tma_tile2d(a_base + kABytes, &tmB, bar, kb << 5, k * Cout);
         }
         PROF(long long tl0 = clock64(); t_issue += tl0 - te1;)
         // signal the step issued kLag steps ago: its copies (this thread's share) have landed by now
@@ -807,15 +611,12 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
         for (int j = 0; j < 4; ++j) {
           const uint64_t a_desc = smem_desc(a_base + j * 32, 16, 1024);
           const uint64_t b_desc = smem_desc(b_base + j * 32, 16, 1024);
-          if (!(dbg & 1)) mma_tf32(tmem_d, a_desc, b_desc, idesc, (first_mma && j == 0) ? 0u : 1u);
+          mma_tf32(tmem_d, a_desc, b_desc, idesc, (first_mma && j == 0) ? 0u : 1u);
         }
         first_mma = false;
         PROF(long long c2 = clock64(); t_mma += c2 - c1;)
-        if (dbg & 16) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->empty[slot])) : "memory");
-        else mma_commit(smem_u32(&ctl->empty[slot]));
+        mma_commit(smem_u32(&ctl->empty[slot]));
         if (info & kInfoLast) {
-          if (dbg & 16) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->accfull[buf])) : "memory");
-          else
           mma_commit(smem_u32(&ctl->accfull[buf]));
           ++tile_i;
         }
@@ -1035,16 +836,9 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
   }
   if (Z > 1) SCN_TRY(dev_alloc_t(&partial, (size_t)Z * tiles * kTileM * Cout, s));
   const dim3 grid((unsigned)tiles, (unsigned)Z);
-  static const bool use_tma = []() {
-    // INSCONV_TC_COPY=tma selects the kernel whose rows are staged by tile::gather4 bulk-tensor copies.
-    // It is correct but measured slower than the cp.async kernel (gather4 moves four 128-byte rows per
-    // request and the copy engine keeps few such requests in flight), so it is not the default.
-    const char *e = getenv("INSCONV_TC_COPY");
-    return e && e[0] == 't';
-  }();
   static const bool use_persist = []() {
-    const char *e = getenv("INSCONV_TC_COPY");
-    return !(e && (e[0] == 't' || e[0] == 'c'));  // "tma" / "cpasync" force the per-tile kernels (development aid)
+    const char *e = getenv("INSCONV_TC_KERNEL");
+    return !(e && e[0] == 't');  // INSCONV_TC_KERNEL=tile forces the simple per-tile kernel (development aid)
   }();
   const size_t fixed_p = sizeof(CtlP) + (size_t)2 * K * kTileM * sizeof(int) + 1024;
   int st_p = (int)((220 * 1024 - fixed_p) / stage_bytes);
@@ -1066,30 +860,7 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
     }
     const long long n_items = tiles * Z;
     k_gather_gemm_tf32_persist<<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads, smem_p, s>>>(
-        in, in_stride, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, (int)Cout, accumulate, cols, st, tiles, Z, partial,
-                                                                            getenv("INSCONV_DBG") ? atoi(getenv("INSCONV_DBG")) : 0);
-  } else if (use_tma) {
-    CUtensorMap tmA, tmB;
-    SCN_TRY(encode_2d(&tmA, in, (uint64_t)Cin, (uint64_t)in_rows, (uint64_t)in_stride * 4, 32, 1));
-    SCN_TRY(encode_2d(&tmB, Wt, (uint64_t)Cin, (uint64_t)K * Cout, (uint64_t)Cin * 4, 32, (uint32_t)Cout));
-    const size_t fixed_t = sizeof(CtlTma) + (size_t)K * kTileM * sizeof(int) + 1024;
-    int st = 4;
-    if (4 * stage_bytes + fixed_t > 112 * 1024) {
-      st = (int)((200 * 1024 - fixed_t) / stage_bytes);
-      if (st > 6) st = 6;
-    }
-    const size_t smem_t = (size_t)st * stage_bytes + fixed_t;
-#define SCN_TMA_LAUNCH(S)                                                                                           \
-  do {                                                                                                              \
-    SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tf32_tma<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_t)); \
-    k_gather_gemm_tf32_tma<S><<<grid, kThreads, smem_t, s>>>(tmA, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, \
-                                                              (int)Cout, accumulate, cols, partial);                \
-  } while (0)
-    if (st >= 6) SCN_TMA_LAUNCH(6);
-    else if (st == 5) SCN_TMA_LAUNCH(5);
-    else if (st == 4) SCN_TMA_LAUNCH(4);
-    else SCN_TMA_LAUNCH(3);
-#undef SCN_TMA_LAUNCH
+        in, in_stride, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, (int)Cout, accumulate, cols, st, tiles, Z, partial);
   } else {
 #define SCN_TC_LAUNCH(S, A)                                                                                          \
   do {                                                                                                               \
