@@ -529,7 +529,9 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
         ++issued;
         if (issued > kLag) {
           cp_async_wait<kLag>();
+#ifndef SCN_NO_STEP_FENCE
           fence_async_proxy();
+#endif
           __syncwarp();
           if (lane == 0) {
             int ls = slot - kLag;

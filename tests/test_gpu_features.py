@@ -192,3 +192,45 @@ def test_bn_train_mode(cuda):
     close(d_rm, want_rm, 1e-5)
     close(d_rv, want_rv, 1e-5)
     close(sm, torch.from_numpy(x).double().mean(0).float(), 1e-5)
+
+
+@pytest.mark.parametrize("rows", [1, 7, 128, 129, 300])
+def test_tf32_tiny_row_counts(cuda, rows):
+    # one-row and ragged tiles through the persistent tensor-core kernel (1x1 convolution and a tiny grid)
+    rng = np.random.RandomState(rows)
+    x = rng.randn(rows, 64).astype(np.float32)
+    w = (rng.randn(64, 96) * 0.2).astype(np.float32)
+    b = rng.randn(96).astype(np.float32)
+    got, _ = cabi.nin_forward(torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda), torch.from_numpy(b).to(cuda),
+                              cabi.PREC_TF32)
+    cabi.check_errors()
+    close(got, O.nin_forward(x, w, b), TF32_TOL)
+    # a chain of `rows` voxels along x: every site has at most two neighbours
+    c = np.stack([np.arange(rows) + 3, np.full(rows, 5), np.full(rows, 7)], 1)
+    m = cabi.Metadata()
+    m.input_layer_build(4096, torch.from_numpy(c).to(cuda), mode=4)
+    g = O.Grid(c)
+    xs = rng.randn(rows, 32).astype(np.float32)
+    ws = synth.kaiming_uniform(rng, 27, 32, 32)
+    got, _ = m.ssc_forward(4096, torch.from_numpy(xs).to(cuda), torch.from_numpy(ws).to(cuda), None, cabi.PREC_TF32)
+    cabi.check_errors()
+    close(got, O.conv_forward(xs, ws, O.ssc_rules(g), g.n), TF32_TOL)
+
+
+def test_packed_weights_match_unpacked(cuda):
+    import ctypes as C
+    m, g = _scene(cuda, 2)
+    rng = np.random.RandomState(5)
+    x = torch.from_numpy(rng.randn(g.n, 64).astype(np.float32)).to(cuda)
+    w = torch.from_numpy(synth.kaiming_uniform(rng, 27, 64, 32)).to(cuda)
+    assert cabi.lib().scn_weights_packable(27, 64, 32) == 1 and cabi.lib().scn_weights_packable(27, 3, 32) == 0
+    packed = torch.empty_like(w)
+    cabi.call("scn_pack_weights", cabi.ptr(w), 27, 64, 32, cabi.ptr(packed), torch.cuda.current_stream().cuda_stream)
+    assert torch.equal(packed.view(27, 32, 64), w.transpose(1, 2).contiguous())
+    a, _ = m.ssc_forward(128, x, w, None, cabi.PREC_TF32)
+    out = torch.empty_like(a)
+    fl = C.c_double(0)
+    cabi.call("scn_ssc_forward", m.h, cabi.size3(128), cabi.ptr(x), 64, cabi.ptr(out), 32, cabi.ptr(packed), None, 64, 32,
+              cabi.PREC_TF32_PACKED, torch.cuda.current_stream().cuda_stream, C.byref(fl))
+    cabi.check_errors()
+    assert torch.equal(a, out)
