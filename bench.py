@@ -4,7 +4,7 @@
 A step is one full frame of the SCN UNet of the reference's model.py (InputLayer mode 4, SSC 3->32,
 UNet planes [32..224] x reps 2 residual, BN+ReLU, OutputLayer, Linear 32->20) over one seeded
 synthetic room of ~250k voxels: voxel hashing, all rulebooks, 53 submanifold convolutions, 6+6 strided
-(de)convolutions, 65 BatchNorm+ReLU, 6 1x1 convolutions.  The metric is BASELINE.json's "active voxels/s
+(de)convolutions, 65 BatchNorm+ReLU, 6 1x1 convolutions.  The metric is "active voxels/s
 per SSC layer": the active sites summed over the 53 submanifold-convolution layers of the frame, divided
 by the time of the whole frame (everything else is charged to it).  The incremental frame (5 % of the
 voxels changed, reference semantics) is timed beside it and reported as ms/frame.
@@ -472,7 +472,10 @@ def main():
     roofline = dict(lay["roofline"])
     roofline.update({"kernel": "gather-GEMM %s, SSC 32->32 on %d sites (level 0 of the UNet, 9 of the 53 SSC layers)"
                                % (args.precision, lay["sites"]),
-                     "us_per_launch": lay["us_per_launch"], "voxels_per_s": lay["voxels_per_s"], "traffic": None,
+                     "us_per_launch": lay["us_per_launch"], "voxels_per_s": lay["voxels_per_s"],
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
+                     # profiles/gather_gemm_tf32_persist_ssc32_room.md (same kernel, same workload)
+                     "traffic": 66.7e6 if args.precision == "tf32" and args.voxels == 250000 else None,
                      "l2": "flushed between launches (256 MB write)"})
     hashes = hash_bench(dev, 5, 2, ("c1", "room") if args.quick else ("c1", "room", "building"))
     for h in hashes:

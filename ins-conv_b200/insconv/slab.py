@@ -12,8 +12,7 @@ convolution, add, concatenate) and the Deconvolution preserve it.  Deeper ghost 
 feed other ghost rows.
 
 Both sides of a cut hold the same sites on the planes they exchange and number them in the same (key) order,
-so a message is just the feature rows of one plane in row order.  The reference has no multi-GPU path; this
-follows the slab scheme sketched for it in this repository's design notes.
+so a message is just the feature rows of one plane in row order.  The reference has no multi-GPU path.
 """
 import numpy as np
 import torch

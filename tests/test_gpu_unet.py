@@ -129,7 +129,7 @@ def test_demo_py_flow_runs_unchanged(cuda):
 
 @pytest.mark.parametrize("precision,tol", [("fp32", 1e-4), ("tf32", 2e-2)])
 def test_exact_incremental_equals_full_recompute(cuda, precision, tol):
-    # BASELINE config 2 on a small UNet: frame t+1 deletes a 16^3 cube, inserts a sphere and re-draws 1 % of the
+    # benchmark configuration 2 (incremental layer over two frames) on a small UNet: frame t+1 deletes a 16^3 cube, inserts a sphere and re-draws 1 % of the
     # features; the exact mode must equal a full recompute of frame t+1, and again after one more insertion
     import sparseconvnet as scn
     scn.set_precision(precision)
@@ -164,7 +164,7 @@ def test_exact_incremental_equals_full_recompute(cuda, precision, tol):
 
 
 def test_config3_full_room_tf32_vs_fp32_oracle(cuda):
-    # BASELINE config 3 at full size: the model.py UNet on the ~250k-voxel synthetic room, tensor-core (tf32) path
+    # benchmark configuration 3 at full size: the model.py UNet on the ~250k-voxel synthetic room, tensor-core (tf32) path
     # against the fp32 CPU oracle.  53 tf32 layers compound, so the end-to-end bar is looser than the per-layer
     # 2e-2 (which tests/test_gpu_features.py checks layer by layer); fp32 must still meet 1e-4.
     import sparseconvnet as scn
@@ -190,7 +190,7 @@ def test_config3_full_room_tf32_vs_fp32_oracle(cuda):
 
 
 def test_config4_sweep_frames(cuda):
-    # BASELINE config 4 in miniature: a few frames of the camera sweep; every frame both incremental modes run,
+    # benchmark configuration 4 in miniature: a few frames of the camera sweep; every frame both incremental modes run,
     # the exact mode is compared with a full recompute of the merged scene
     import sparseconvnet as scn
     torch.manual_seed(6)
