@@ -319,7 +319,8 @@ def main():
     ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "tf32"), choices=["fp32", "tf32"])
     ap.add_argument("--quick", action="store_true", help="skip the 4M-point hash build (profiling aid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--legs", default="full,incre,e2e", help="which timed legs to run (profiling aid)")
+    ap.add_argument("--legs", default="full,incre,sweep,e2e", help="which timed legs to run (profiling aid)")
+    ap.add_argument("--sweep-frames", type=int, default=100)
     ap.add_argument("--layer", action="store_true", help="time one SSC layer alone (rulebook cached) and exit")
     ap.add_argument("--hash", action="store_true", help="time the grid build alone and exit")
     ap.add_argument("--workload", default="room", choices=["room", "building"],
@@ -446,6 +447,34 @@ def main():
 
     ms_exact, _ = timed(exact_frame, args.steps, args.warmup) if "incre" in legs else (float("nan"), 0)
 
+    # ---- online sequence (configs[3]): seeded camera sweep, one insertion of 2-8 % new surface voxels per frame.
+    # Per-frame latency of the reference-style residual update and of the exact update (kept scene advances).
+    sweep = None
+    if "sweep" in legs and world == 1:
+        from insconv import synth
+        n_frames = args.sweep_frames
+        model([d_coords, d_feats])  # reset the kept scene to the base room
+        lat = {"reference": [], "exact": []}
+        for fr in range(n_frames):
+            nc, _ = synth.sweep_frame(coords, fr, n_frames=n_frames, seed=rank)
+            nfeat = synth.rgb(1000 + fr, nc.shape[0])
+            dn, dfn = torch.from_numpy(nc).to(dev), torch.from_numpy(nfeat).to(dev)
+            for mode, key in ((True, "reference"), ("exact", "exact")):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                y = model([dn, dfn], mode)
+                torch.cuda.synchronize()
+                lat[key].append((time.perf_counter() - t0) * 1e3)
+        pct = lambda v, q: float(sorted(v)[min(len(v) - 1, int(q * len(v)))])
+        sweep = {"frames": n_frames,
+                 "scene_points_at_end": int(model.sparseModel[0].scene_coords.shape[0]),
+                 "reference_ms": {"mean": sum(lat["reference"]) / n_frames, "p50": pct(lat["reference"], 0.5),
+                                  "p99": pct(lat["reference"], 0.99)},
+                 "exact_ms": {"mean": sum(lat["exact"]) / n_frames, "p50": pct(lat["exact"], 0.5),
+                              "p99": pct(lat["exact"], 0.99)},
+                 "timing": "host wall clock around each frame, device synchronised on both sides"}
+        model([d_coords, d_feats])
+
     # ---- e2e: pinned host inputs, host read of the result -------------------------------------------
     h_out = torch.empty(coords.shape[0], 20, dtype=torch.float32).pin_memory()
 
@@ -492,6 +521,7 @@ def main():
             "incremental_exact": {"ms_per_frame": ms_exact,
                                   "semantics": "new points merged into the kept scene, merged scene recomputed: "
                                                "equal to a full recompute, kept scene advances"},
+            "sweep": sweep,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches) * args.steps, "clocks": clocks, "roofline": roofline,
