@@ -810,8 +810,10 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
       sm_count = cached[dev];
     }
   }
-  // Few tiles and a long reduction: share the steps of a tile among Z work items.  Z minimises the
-  // longest chain of steps any CTA runs (items per CTA x steps per item, plus a fixed cost per item).
+  // Few tiles and a long reduction: share the steps of a tile among Z work items.  The longest chain of
+  // steps any CTA runs is (items per CTA) x (steps per item + a fixed cost per item); a step takes about half a
+  // microsecond.  The smallest Z whose chain is short anyway (<= 40 steps, ~20 us) is taken, because every Z > 1
+  // costs a scratch allocation and a reduction launch; otherwise the Z with the shortest chain.
   const int steps_max = K * (int)(Cin / 32);
   int Z = 1;
   if (tiles < 2 * sm_count && steps_max >= 4) {
@@ -824,6 +826,7 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
         best = cost;
         Z = z;
       }
+      if (cost <= 40) break;
     }
   }
   float *Wt = nullptr, *Wt_own = nullptr, *partial = nullptr;
