@@ -50,7 +50,7 @@ extern "C" {
 
 /* arithmetic used by the gather-GEMM kernels */
 #define SCN_PREC_FP32 0      /* fp32 FFMA, fp32 accumulate (bit-for-bit deterministic)  */
-#define SCN_PREC_TF32 1      /* tcgen05 kind::tf32 tensor cores, fp32 accumulate in TMEM */
+#define SCN_PREC_TF32 1      /* tf32 tensor cores (tcgen05 with TMEM accumulators, or warp-level mma.sync for narrow layers), fp32 accumulate */
 #define SCN_PREC_TF32_PACKED 2 /* as TF32, and `weight` already is the packed copy made by scn_pack_weights */
 
 /* Largest coordinate and batch index a key can hold. */
@@ -147,11 +147,14 @@ SCN_API int scn_conv_rulebook(scn_metadata *m, const int64_t in_size[3], const i
  * Feature ops.  *flops receives the multiply-add count the reference returns
  * (pairs * n_in * n_out); may be NULL.
  * ------------------------------------------------------------------------- */
-/* The tensor-core kernels read the weights transposed, [volume, n_out, n_in].  Normally every convolution call
- * makes that copy itself; a caller whose weights do not change between calls can make it once with this
- * function (packed: device buffer of volume*n_in*n_out floats) and pass it as `weight` with
- * SCN_PREC_TF32_PACKED.  Only shapes the tensor-core kernels accept can be packed: scn_weights_packable() != 0
- * (n_in and n_out multiples of 32, n_out <= 256).  No counterpart in the reference. */
+/* The tensor-core kernels read the weights in a layout of their own: transposed, [volume, n_out, n_in], for
+ * the tcgen05 kernel; in mma.sync fragment order, rounded to tf32, for the warp-level kernel that takes the
+ * narrow layers (n_in, n_out in {16, 32, 64}).  Which one applies depends on (volume, n_in, n_out) alone.
+ * Normally every convolution call makes that copy itself; a caller whose weights do not change between calls
+ * can make it once with this function (packed: device buffer of volume*n_in*n_out floats, contents opaque)
+ * and pass it as `weight` with SCN_PREC_TF32_PACKED.  Only shapes these kernels accept can be packed:
+ * scn_weights_packable() != 0 (narrow shapes as above, or n_in and n_out multiples of 32 with n_out <= 256).
+ * No counterpart in the reference. */
 SCN_API int scn_weights_packable(int64_t volume, int64_t n_in, int64_t n_out);
 SCN_API int scn_pack_weights(const float *weight, int64_t volume, int64_t n_in, int64_t n_out, float *packed,
                              void *stream);

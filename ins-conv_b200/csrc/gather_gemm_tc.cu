@@ -757,11 +757,13 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 }  // namespace
 
 bool tc_packable(int64_t K, int64_t Cin, int64_t Cout) {
+  if (warp_mma_shape(K, Cin, Cout)) return true;
   return K >= 1 && K <= 27 && Cin > 0 && Cout > 0 && Cin % 32 == 0 && Cout % 32 == 0 && Cout <= 256;
 }
 int tc_pack_weights(const float *W, int64_t K, int64_t Cin, int64_t Cout, float *packed, cudaStream_t s) {
   if (!tc_packable(K, Cin, Cout)) return fail(SCN_E_INVALID, "shape cannot be packed for the tensor-core kernels");
   if (!W || !packed) return fail(SCN_E_INVALID, "null pointer");
+  if (warp_mma_shape(K, Cin, Cout)) return warp_mma_pack(W, K, Cin, Cout, packed, s);
   k_transpose_weights<<<dim3((unsigned)(Cout / 32), (unsigned)(Cin / 32), (unsigned)K), dim3(32, 8), 0, s>>>(W, packed, (int)Cin,
                                                                                                           (int)Cout);
   SCN_LAUNCHED();

@@ -122,6 +122,13 @@ int gather_gemm(const float *in, int64_t in_stride, int64_t in_rows, const int32
                 int accumulate, int precision, cudaStream_t s);
 // reads and clears the error word of the tensor-core kernels; synchronises s
 int tc_check_errors(cudaStream_t s);
+// narrow layers (n_in, n_out in {16, 32, 64}) run a warp-level mma.sync kernel with its own packed weight layout;
+// which kernel a shape uses, and therefore which layout tc_pack_weights produces, depends on the shape alone
+bool warp_mma_shape(int64_t K, int64_t Cin, int64_t Cout);
+int warp_mma_pack(const float *W, int64_t K, int64_t Cin, int64_t Cout, float *packed, cudaStream_t s);
+int gather_mma_warp(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *W,
+                    const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate, bool packed,
+                    cudaStream_t s, bool *handled);
 bool tc_packable(int64_t K, int64_t Cin, int64_t Cout);
 int tc_pack_weights(const float *W, int64_t K, int64_t Cin, int64_t Cout, float *packed, cudaStream_t s);
 int nin_forward_noalloc(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,

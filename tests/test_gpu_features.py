@@ -136,11 +136,12 @@ def test_linearity_at_full_size(cuda):
     close(c0, (x @ w[13]).cpu(), 1e-4)
 
 
-# ---- tensor-core (tcgen05, tf32) path: 2e-2 relative per layer -------------------------------------
+# ---- tensor-core (tf32) paths, tcgen05 and warp-level: 2e-2 relative per layer -------------------------------------
 TF32_TOL = 2e-2
 
 
-@pytest.mark.parametrize("n_in,n_out,bias", [(32, 32, False), (64, 32, True), (32, 64, False), (96, 96, True),
+@pytest.mark.parametrize("n_in,n_out,bias", [(16, 16, False), (32, 32, False), (64, 32, True), (32, 64, False),
+                                             (64, 64, True), (16, 64, False), (64, 16, True), (96, 96, True),
                                              (224, 224, False), (448, 224, False)])
 def test_ssc_forward_tf32(cuda, n_in, n_out, bias):
     m, g = _scene(cuda, 0)
@@ -205,6 +206,10 @@ def test_tf32_tiny_row_counts(cuda, rows):
                               cabi.PREC_TF32)
     cabi.check_errors()
     close(got, O.nin_forward(x, w, b), TF32_TOL)
+    # the same through the warp-level kernel (narrow layer)
+    got, _ = cabi.nin_forward(torch.from_numpy(x).to(cuda), torch.from_numpy(w[:, :32].copy()).to(cuda),
+                              torch.from_numpy(b[:32].copy()).to(cuda), cabi.PREC_TF32)
+    close(got, O.nin_forward(x, w[:, :32], b[:32]), TF32_TOL)
     # a chain of `rows` voxels along x: every site has at most two neighbours
     c = np.stack([np.arange(rows) + 3, np.full(rows, 5), np.full(rows, 7)], 1)
     m = cabi.Metadata()
@@ -217,20 +222,27 @@ def test_tf32_tiny_row_counts(cuda, rows):
     close(got, O.conv_forward(xs, ws, O.ssc_rules(g), g.n), TF32_TOL)
 
 
-def test_packed_weights_match_unpacked(cuda):
+@pytest.mark.parametrize("n_in,n_out", [(64, 32), (96, 128)])
+def test_packed_weights_match_unpacked(cuda, n_in, n_out):
+    # (64, 32) runs the warp-level kernel, (96, 128) the tcgen05 kernel; each has its own packed layout
     import ctypes as C
     m, g = _scene(cuda, 2)
     rng = np.random.RandomState(5)
-    x = torch.from_numpy(rng.randn(g.n, 64).astype(np.float32)).to(cuda)
-    w = torch.from_numpy(synth.kaiming_uniform(rng, 27, 64, 32)).to(cuda)
-    assert cabi.lib().scn_weights_packable(27, 64, 32) == 1 and cabi.lib().scn_weights_packable(27, 3, 32) == 0
+    x = torch.from_numpy(rng.randn(g.n, n_in).astype(np.float32)).to(cuda)
+    w = torch.from_numpy(synth.kaiming_uniform(rng, 27, n_in, n_out)).to(cuda)
+    assert cabi.lib().scn_weights_packable(27, n_in, n_out) == 1 and cabi.lib().scn_weights_packable(27, 3, 32) == 0
     packed = torch.empty_like(w)
-    cabi.call("scn_pack_weights", cabi.ptr(w), 27, 64, 32, cabi.ptr(packed), torch.cuda.current_stream().cuda_stream)
-    assert torch.equal(packed.view(27, 32, 64), w.transpose(1, 2).contiguous())
+    cabi.call("scn_pack_weights", cabi.ptr(w), 27, n_in, n_out, cabi.ptr(packed), torch.cuda.current_stream().cuda_stream)
+    if n_in > 64:
+        assert torch.equal(packed.view(27, n_out, n_in), w.transpose(1, 2).contiguous())
+    else:  # a permutation of the weights rounded to tf32 (13 low mantissa bits cleared)
+        bits = packed.view(torch.int32)
+        assert int((bits & 0x1FFF).abs().max()) == 0
+        assert torch.allclose(packed.flatten().sort().values, w.flatten().sort().values, rtol=1e-3, atol=0)
     a, _ = m.ssc_forward(128, x, w, None, cabi.PREC_TF32)
     out = torch.empty_like(a)
     fl = C.c_double(0)
-    cabi.call("scn_ssc_forward", m.h, cabi.size3(128), cabi.ptr(x), 64, cabi.ptr(out), 32, cabi.ptr(packed), None, 64, 32,
-              cabi.PREC_TF32_PACKED, torch.cuda.current_stream().cuda_stream, C.byref(fl))
+    cabi.call("scn_ssc_forward", m.h, cabi.size3(128), cabi.ptr(x), n_in, cabi.ptr(out), n_out, cabi.ptr(packed), None, n_in,
+              n_out, cabi.PREC_TF32_PACKED, torch.cuda.current_stream().cuda_stream, C.byref(fl))
     cabi.check_errors()
     assert torch.equal(a, out)
