@@ -1,4 +1,4 @@
-// Warp-level gather-GEMM for narrow layers (n_in, n_out <= 64): rows gathered straight into registers.
+// Warp-level gather-GEMM for narrow layers (n_in, n_out in {16, 32, 64}): rows gathered straight into registers.
 //
 //     out[o] = init(o) + sum_k in[ map[k][o] ] * W[k]           (same contract as the other gather-GEMM kernels)
 //
@@ -7,16 +7,26 @@
 // barriers and descriptor traffic (measured: ~1300 cycles per 128-row step of 4 MMAs).  Here a warp owns 16 or 32
 // consecutive output rows and all output planes, keeps the accumulator in registers and works through the
 // offsets that have at least one neighbour among its rows:
-//   * the rows' map entries [K][rows] are staged once in a warp-private slice of shared memory,
-//   * for an offset, lane (g, t) (g = lane / 4, t = lane % 4) loads 16 bytes of rows g and g + 8 for every
+//   * the rows' map entries [K][rows] are staged once in a warp-private slice of shared memory (all loads of
+//     the slice in flight together),
+//   * for an offset, lane (g, t) (g = lane / 4, t = lane % 4) loads 16 bytes of rows g, g + 8, ... for every
 //     16-plane chunk, straight from global memory through L1 (neighbouring rows of a tile share most of their
-//     neighbours, so L1 catches the reuse); absent neighbours load nothing and contribute zeros,
-//   * the four floats of such a load feed two mma.sync.m16n8k8 (tf32) as the k-slots (t, t + 4): the reduction
-//     index is permuted so that no shuffle or shared-memory transpose is needed; the weights are packed once in
-//     the matching order, [K][n_in / 16][n_out / 8][lane] float4, rounded to tf32, and read through L1,
+//     neighbours, so L1 catches the reuse); absent neighbours read a row of zeros,
+//   * the product is formed transposed, out^T = W^T * in^T, with mma.sync.m16n8k8 (tf32): the gathered rows are
+//     the 8-column operand, whose two registers per lane are (k-slot t, k-slot t + 4) of ONE row.  The reduction
+//     index is permuted so that these are two adjacent floats of a 16-byte load: a load feeds two MMAs with no
+//     shuffle, no shared-memory transpose and no register moves (an MMA operand must sit in consecutive
+//     registers; with the rows as the 16-row operand every MMA needed four moves).  The weights are the 16-row
+//     operand, packed once in fragment order, [K][n_in / 16][n_out / 16][2][lane] float4, rounded to tf32,
 //   * the loads of the next offset are issued before the MMAs of the current one (two register buffers).
-// No barrier, no block-wide synchronisation, no scratch memory; skipping works at 16/32-row granularity instead
-// of 128.  fp32 inputs are consumed as tf32 (low 13 mantissa bits ignored), accumulation is fp32.
+// No barrier inside the reduction, no scratch memory; skipping works at 16/32-row granularity instead of 128.
+// fp32 inputs are consumed as tf32 (low 13 mantissa bits ignored), accumulation is fp32.
+//
+// Two launch forms of the same warp code:
+//   resident   the whole packed weight tensor fits in shared memory (<= 112 KB, e.g. 27 x 32 x 32): one CTA of
+//              16 warps per SM copies it once and its warps walk over the row tiles; weight fragments come from
+//              shared memory, L1 is left to the gathered rows
+//   streaming  larger weight tensors: one tile per warp, weight fragments read through L1
 #include "internal.h"
 #include <stdlib.h>
 
@@ -24,81 +34,91 @@ namespace scn {
 
 namespace {
 
-constexpr int kWarps = 4;  // warps per block; every warp works alone
+constexpr int kWarps = 4;      // streaming form: warps per block; every warp works alone
+constexpr int kResWarps = 16;  // resident form: warps per CTA, one CTA per SM
 constexpr int kMaxK = 27;
+constexpr size_t kResMaxWeightBytes = 112 * 1024;
 
-__device__ __forceinline__ void mma_m16n8k8_tf32(float (&d)[4], float a0, float a1, float a2, float a3, float b0, float b1) {
+__device__ __align__(16) float g_zero_row[64];  // stands in for an absent neighbour (zero-initialised, never written)
+
+// D[16 x 8] += A[16 x 8] * B[8 x 8]; here A holds weights (rows = output planes) and B gathered rows
+// (columns = output rows), so that both register groups of an instruction are what one 16-byte load delivers.
+__device__ __forceinline__ void mma_m16n8k8_tf32(float (&d)[4], const float4 &a, float b0, float b1) {
   asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(__float_as_uint(a0)), "r"(__float_as_uint(a1)), "r"(__float_as_uint(a2)), "r"(__float_as_uint(a3)),
+      : "r"(__float_as_uint(a.x)), "r"(__float_as_uint(a.y)), "r"(__float_as_uint(a.z)), "r"(__float_as_uint(a.w)),
         "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)));
 }
 
-// gathered rows of one offset: [m-tile][row half: g, g + 8][16-plane chunk]
-template <int CIN, int MT> struct Frag {
-  float4 v[MT][2][CIN / 16];
+// gathered rows of one offset: [group of 8 rows][16-plane chunk]; lane (g, t) holds planes 4t..4t+3 of row g
+template <int CIN, int NTR> struct Frag {
+  float4 v[NTR][CIN / 16];
 };
 
-template <int CIN, int MT>
-__device__ __forceinline__ void load_rows(Frag<CIN, MT> &f, const int *mp_k, const float *__restrict__ in, long long in_stride,
-                                          int g, int t) {
+template <int CIN, int NTR>
+__device__ __forceinline__ void load_rows(Frag<CIN, NTR> &f, const int *mp_k, const float *__restrict__ in_t, long long in_stride,
+                                          const float *zero_t, int g) {
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
+  for (int n = 0; n < NTR; ++n) {
+    const int s = mp_k[n * 8 + g];
+    const float4 *p = reinterpret_cast<const float4 *>(s >= 0 ? in_t + (long long)s * in_stride : zero_t);
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int s = mp_k[mt * 16 + g + 8 * h];
-      const float4 *p = reinterpret_cast<const float4 *>(in + (long long)(s >= 0 ? s : 0) * in_stride) + t;
-#pragma unroll
-      for (int c = 0; c < CIN / 16; ++c) f.v[mt][h][c] = s >= 0 ? __ldg(p + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
+    for (int c = 0; c < CIN / 16; ++c) f.v[n][c] = __ldg(p + 4 * c);
+  }
 }
 
-template <int CIN, int COUT, int MT>
-__device__ __forceinline__ void mma_rows(float (&acc)[MT][COUT / 8][4], const Frag<CIN, MT> &f, const float4 *__restrict__ wk) {
-  constexpr int NT = COUT / 8;
+// wk: this lane's float4 of the first weight fragment of offset k; SMEM_B: wk points into shared memory
+template <int CIN, int COUT, int NTR, bool SMEM_B>
+__device__ __forceinline__ void mma_rows(float (&acc)[COUT / 16][NTR][4], const Frag<CIN, NTR> &f, const float4 *__restrict__ wk) {
+  constexpr int MTC = COUT / 16;
 #pragma unroll
   for (int c = 0; c < CIN / 16; ++c)
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const float4 b = __ldg(wk + (c * NT + nt) * 32);
+    for (int m = 0; m < MTC; ++m) {
+      const float4 *w = wk + ((c * MTC + m) * 2) * 32;
+      const float4 a0 = SMEM_B ? w[0] : __ldg(w);
+      const float4 a1 = SMEM_B ? w[32] : __ldg(w + 32);
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        mma_m16n8k8_tf32(acc[mt][nt], f.v[mt][0][c].x, f.v[mt][1][c].x, f.v[mt][0][c].y, f.v[mt][1][c].y, b.x, b.y);
-        mma_m16n8k8_tf32(acc[mt][nt], f.v[mt][0][c].z, f.v[mt][1][c].z, f.v[mt][0][c].w, f.v[mt][1][c].w, b.z, b.w);
+      for (int n = 0; n < NTR; ++n) {
+        mma_m16n8k8_tf32(acc[m][n], a0, f.v[n][c].x, f.v[n][c].y);
+        mma_m16n8k8_tf32(acc[m][n], a1, f.v[n][c].z, f.v[n][c].w);
       }
     }
 }
 
-template <int CIN, int COUT, int MT, int MINB>
-__global__ void __launch_bounds__(kWarps * 32, MINB)
-k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
-                  const float4 *__restrict__ Wp, const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
-                  int accumulate) {
-  constexpr int ROWS = 16 * MT, NT = COUT / 8, C16 = CIN / 16;
-  __shared__ int s_map[kWarps][kMaxK * ROWS];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// One tile of 8 * NTR output rows, done by one warp.  mp: the warp's [K][ROWS] slice of shared memory.
+template <int CIN, int COUT, int NTR, bool SMEM_B>
+__device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *__restrict__ in, long long in_stride,
+                                          const int32_t *__restrict__ map, int K, long long n_out, const float4 *wl,
+                                          const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
+                                          int accumulate, int lane) {
+  constexpr int ROWS = 8 * NTR, MTC = COUT / 16, C16 = CIN / 16;
   const int g = lane >> 2, t = lane & 3;
-  const long long row0 = ((long long)blockIdx.x * kWarps + warp) * ROWS;
-  if (row0 >= n_out) return;  // warps never synchronise with each other
-  int *mp = s_map[warp];
 
-  // stage the map entries of this warp's rows and note which offsets have any
+  // stage the map entries of this tile's rows and note which offsets have any
   unsigned int mask = 0;
   if (map) {
-    constexpr int PER = 32 / ROWS;  // offsets covered by one warp-wide load
+    constexpr int PER = 32 / ROWS;               // offsets covered by one warp-wide load
+    constexpr int NL = (kMaxK + PER - 1) / PER;  // warp-wide loads for the largest K
     const int r = lane % ROWS, ksub = lane / ROWS;
     const bool row_ok = row0 + r < n_out;
-    for (int k0 = 0; k0 < K; k0 += PER) {
-      const int k = k0 + ksub;
-      int v = -1;
-      if (k < K && row_ok) v = __ldg(map + (long long)k * n_out + row0 + r);
-      if (k < K) mp[k * ROWS + r] = v;
-      const unsigned int b = __ballot_sync(0xffffffffu, v >= 0);
+    const int32_t *mrow = map + row0 + r;
+    int vals[NL];
+#pragma unroll
+    for (int j = 0; j < NL; ++j) {  // all loads first, so that they are in flight together
+      const int k = j * PER + ksub;
+      vals[j] = (k < K && row_ok) ? __ldg(mrow + (long long)k * n_out) : -1;
+    }
+#pragma unroll
+    for (int j = 0; j < NL; ++j) {
+      const int k = j * PER + ksub;
+      if (k < K) mp[k * ROWS + r] = vals[j];
+      const unsigned int b = __ballot_sync(0xffffffffu, vals[j] >= 0);
       if (PER == 2) {
-        mask |= ((b & 0xffffu) ? 1u : 0u) << k0;
-        mask |= ((b >> 16) ? 1u : 0u) << (k0 + 1);
+        mask |= ((b & 0xffffu) ? 1u : 0u) << (j * PER);
+        mask |= ((b >> 16) ? 1u : 0u) << (j * PER + 1);
       } else {
-        mask |= (b ? 1u : 0u) << k0;
+        mask |= (b ? 1u : 0u) << j;
       }
     }
   } else {  // identity: row o reads row o
@@ -107,79 +127,120 @@ k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32
   }
   __syncwarp();
 
-  float acc[MT][NT][4];
+  float acc[MTC][NTR][4];
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
+  for (int m = 0; m < MTC; ++m)
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+    for (int n = 0; n < NTR; ++n)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
 
-  const float4 *wl = Wp + lane;
-  constexpr int WK = C16 * NT * 32;  // float4 per offset
+  constexpr int WK = C16 * MTC * 2 * 32;  // float4 per offset
+  const float *in_t = in + 4 * t, *zero_t = g_zero_row + 4 * t;
   if (mask) {
-    Frag<CIN, MT> f0, f1;
+    Frag<CIN, NTR> f0, f1;
     int k0 = __ffs(mask) - 1;
     mask &= mask - 1;
-    load_rows<CIN, MT>(f0, mp + k0 * ROWS, in, in_stride, g, t);
+    load_rows<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, zero_t, g);
     while (true) {
       int k1 = -1;
       if (mask) {
         k1 = __ffs(mask) - 1;
         mask &= mask - 1;
-        load_rows<CIN, MT>(f1, mp + k1 * ROWS, in, in_stride, g, t);
+        load_rows<CIN, NTR>(f1, mp + k1 * ROWS, in_t, in_stride, zero_t, g);
       }
-      mma_rows<CIN, COUT, MT>(acc, f0, wl + (long long)k0 * WK);
+      mma_rows<CIN, COUT, NTR, SMEM_B>(acc, f0, wl + k0 * WK);
       if (k1 < 0) break;
       k0 = -1;
       if (mask) {
         k0 = __ffs(mask) - 1;
         mask &= mask - 1;
-        load_rows<CIN, MT>(f0, mp + k0 * ROWS, in, in_stride, g, t);
+        load_rows<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, zero_t, g);
       }
-      mma_rows<CIN, COUT, MT>(acc, f1, wl + (long long)k1 * WK);
+      mma_rows<CIN, COUT, NTR, SMEM_B>(acc, f1, wl + k1 * WK);
       if (k0 < 0) break;
     }
   }
+  __syncwarp();  // the slice is rewritten by the warp's next tile
 
-  // accumulator fragment: c0,c1 -> row g, planes 8nt + 2t, +1; c2,c3 -> row g + 8
+  // accumulator fragment: c0,c1 -> plane 16m + g, rows 8n + 2t, +1; c2,c3 -> plane 16m + g + 8
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
+  for (int n = 0; n < NTR; ++n)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const long long row = row0 + mt * 16 + g + 8 * h;
+    for (int j = 0; j < 2; ++j) {
+      const long long row = row0 + n * 8 + 2 * t + j;
       if (row < n_out) {
-        float *o = out + row * out_stride + 2 * t;
+        float *o = out + row * out_stride + g;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          float2 v = make_float2(acc[mt][nt][2 * h], acc[mt][nt][2 * h + 1]);
-          if (accumulate) {
-            const float2 old = *reinterpret_cast<const float2 *>(o + 8 * nt);
-            v.x += old.x;
-            v.y += old.y;
-          } else if (bias) {
-            v.x += __ldg(bias + 8 * nt + 2 * t);
-            v.y += __ldg(bias + 8 * nt + 2 * t + 1);
+        for (int m = 0; m < MTC; ++m)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float v = acc[m][n][2 * h + j];
+            const int c = 16 * m + 8 * h;
+            if (accumulate) v += o[c];
+            else if (bias) v += __ldg(bias + c + g);
+            o[c] = v;
           }
-          *reinterpret_cast<float2 *>(o + 8 * nt) = v;
-        }
       }
     }
 }
 
-// W [K][n_in][n_out] -> [K][n_in/16][n_out/8][lane][4], rounded to tf32 (round to nearest, ties away)
+// streaming form: one tile per warp, weights through L1
+template <int CIN, int COUT, int NTR, int MINB>
+__global__ void __launch_bounds__(kWarps * 32, MINB)
+k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
+                  const float4 *__restrict__ Wp, const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
+                  int accumulate) {
+  constexpr int ROWS = 8 * NTR;
+  __shared__ int s_map[kWarps][kMaxK * ROWS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long row0 = ((long long)blockIdx.x * kWarps + warp) * ROWS;
+  if (row0 >= n_out) return;  // warps never synchronise with each other
+  warp_tile<CIN, COUT, NTR, false>(row0, s_map[warp], in, in_stride, map, K, n_out, Wp + lane, bias, out, out_stride,
+                                  accumulate, lane);
+}
+
+// resident form: weights copied to shared memory once per CTA, warps walk over the tiles
+template <int CIN, int COUT, int NTR>
+__global__ void __launch_bounds__(kResWarps * 32, 1)
+k_gather_mma_tf32_res(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
+                      const float4 *__restrict__ Wp, const float *__restrict__ bias, float *__restrict__ out,
+                      long long out_stride, int accumulate, long long tiles) {
+  constexpr int ROWS = 8 * NTR, WK = (CIN / 16) * (COUT / 16) * 2 * 32;
+  extern __shared__ float4 s_res[];  // [K * WK] weight fragments, then [kResWarps][K * ROWS] map entries
+  float4 *sW = s_res;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int *mp = reinterpret_cast<int *>(s_res + (size_t)K * WK) + warp * (K * ROWS);
+  for (int i = threadIdx.x; i < K * WK; i += kResWarps * 32) sW[i] = __ldg(Wp + i);
+  __syncthreads();
+  // consecutive warps take consecutive tiles: a CTA works on 16 * ROWS neighbouring rows at a time
+  for (long long tile = (long long)blockIdx.x * kResWarps + warp; tile < tiles; tile += (long long)gridDim.x * kResWarps) {
+    const long long next = tile + (long long)gridDim.x * kResWarps;
+    if (map && next < tiles && lane < K) {  // pull the next tile's map entries into L2 meanwhile
+      const long long first = (long long)lane * n_out + next * ROWS, last_valid = (long long)K * n_out - 1;
+      const long long last = first + ROWS - 1 < last_valid ? first + ROWS - 1 : last_valid;
+      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(map + first));
+      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(map + last));
+    }
+    warp_tile<CIN, COUT, NTR, true>(tile * ROWS, mp, in, in_stride, map, K, n_out, sW + lane, bias, out, out_stride, accumulate,
+                                   lane);
+  }
+}
+
+// W [K][n_in][n_out] -> [K][n_in/16][n_out/16][2][lane][4], rounded to tf32 (round to nearest, ties away):
+// element e of the float4 of (k, c, m, j, lane = 4g + t) is W[k][16c + 4t + 2j + (e >> 1)][16m + g + 8(e & 1)]
 __global__ void k_pack_weights_mma(const float *__restrict__ W, float *__restrict__ Wp, int Cin, int Cout, long long total) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
-  const int NT = Cout / 8, C16 = Cin / 16;
-  const int j = (int)(i & 3), lane = (int)((i >> 2) & 31);
-  long long rest = i >> 7;
-  const int nt = (int)(rest % NT);
-  rest /= NT;
+  const int MTC = Cout / 16, C16 = Cin / 16;
+  const int e = (int)(i & 3), lane = (int)((i >> 2) & 31), j = (int)((i >> 7) & 1);
+  long long rest = i >> 8;
+  const int m = (int)(rest % MTC);
+  rest /= MTC;
   const int c = (int)(rest % C16);
   const long long k = rest / C16;
   const int g = lane >> 2, t = lane & 3;
-  const int ci = c * 16 + 4 * t + j, co = nt * 8 + g;
+  const int ci = c * 16 + 4 * t + 2 * j + (e >> 1), co = m * 16 + g + 8 * (e & 1);
   const float w = W[(k * Cin + ci) * Cout + co];
   uint32_t u;
   asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(u) : "f"(w));
@@ -188,12 +249,44 @@ __global__ void k_pack_weights_mma(const float *__restrict__ W, float *__restric
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-int max_planes() {
-  static const int v = []() {
-    const char *e = getenv("INSCONV_WARP_MMA_MAX");  // development aid: widest layer the warp-level kernel takes (0: off)
-    return e ? atoi(e) : 64;
-  }();
+int env_int(const char *name, int dflt) {
+  const char *e = getenv(name);
+  return e ? atoi(e) : dflt;
+}
+int max_planes() {  // development aid: widest layer the warp-level kernels take (0: off)
+  static const int v = env_int("INSCONV_WARP_MMA_MAX", 64);
   return v;
+}
+bool allow_resident() {  // development aid: 0 forces the streaming form
+  static const int v = env_int("INSCONV_WARP_MMA_RESIDENT", 1);
+  return v != 0;
+}
+
+template <int CI, int CO, int NTR, int MINB>
+int launch_warp(bool resident, int sm_count, const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out,
+                const float *Wp, const float *bias, float *out, int64_t out_stride, int accumulate, cudaStream_t s) {
+  const long long tiles = (n_out + 8 * NTR - 1) / (8 * NTR);
+  const float4 *W4 = reinterpret_cast<const float4 *>(Wp);
+  if constexpr (CI * CO < 64 * 64) {  // 64 x 64 needs more registers than a 512-thread CTA has
+    if (resident) {
+      const size_t smem = (size_t)K * CI * CO * sizeof(float) + (size_t)kResWarps * K * 8 * NTR * sizeof(int);
+      static bool raised[64] = {false};  // the opt-in shared memory limit is raised once per device and kernel
+      int dev = 0;
+      SCN_CUDA(cudaGetDevice(&dev));
+      if (dev < 0 || dev >= 64 || !raised[dev]) {
+        SCN_CUDA(cudaFuncSetAttribute(k_gather_mma_tf32_res<CI, CO, NTR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      (int)(kResMaxWeightBytes + kResWarps * kMaxK * 32 * sizeof(int))));
+        if (dev >= 0 && dev < 64) raised[dev] = true;
+      }
+      const long long ctas = (tiles + kResWarps - 1) / kResWarps;
+      k_gather_mma_tf32_res<CI, CO, NTR><<<(unsigned)(ctas < sm_count ? ctas : sm_count), kResWarps * 32, smem, s>>>(
+          in, in_stride, map, K, n_out, W4, bias, out, out_stride, accumulate, tiles);
+      return SCN_OK;
+    }
+  }
+  k_gather_mma_tf32<CI, CO, NTR, MINB><<<(unsigned)((tiles + kWarps - 1) / kWarps), kWarps * 32, 0, s>>>(
+      in, in_stride, map, K, n_out, W4, bias, out, out_stride, accumulate);
+  return SCN_OK;
 }
 
 }  // namespace
@@ -226,28 +319,40 @@ int gather_mma_warp(const float *in, int64_t in_stride, const int32_t *map, int 
     SCN_TRY(warp_mma_pack(W, K, Cin, Cout, own, s));
     Wp = own;
   }
-#define SCN_WARP_LAUNCH(CI, CO, MT, MINB)                                                                             \
-  do {                                                                                                                \
-    const long long tiles = (n_out + 16 * MT - 1) / (16 * MT);                                                        \
-    k_gather_mma_tf32<CI, CO, MT, MINB><<<(unsigned)((tiles + kWarps - 1) / kWarps), kWarps * 32, 0, s>>>(            \
-        in, in_stride, map, K, n_out, reinterpret_cast<const float4 *>(Wp), bias, out, out_stride, accumulate);       \
-  } while (0)
+  int sm_count = 148;
+  {
+    int dev = 0;
+    SCN_CUDA(cudaGetDevice(&dev));
+    static int cached[64] = {0};
+    if (dev >= 0 && dev < 64) {
+      if (!cached[dev]) SCN_CUDA(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
+      sm_count = cached[dev];
+    }
+  }
+  const size_t w_bytes = (size_t)K * Cin * Cout * sizeof(float);
+  // resident form only when every SM gets a few tiles per warp: the weight copy has to pay off
+  const bool resident = allow_resident() && w_bytes <= kResMaxWeightBytes && n_out >= (int64_t)sm_count * kResWarps * 32 * 2;
+#define SCN_WARP_LAUNCH(CI, CO, NTR, MINB)                                                                        \
+  rc = launch_warp<CI, CO, NTR, MINB>(resident, sm_count, in, in_stride, map, K, n_out, Wp, bias, out, out_stride, \
+                                     accumulate, s)
+  int rc = SCN_OK;
   const int key = (int)Cin * 100 + (int)Cout;
   switch (key) {
-    case 1616: SCN_WARP_LAUNCH(16, 16, 2, 4); break;
-    case 1632: SCN_WARP_LAUNCH(16, 32, 2, 4); break;
-    case 1664: SCN_WARP_LAUNCH(16, 64, 1, 4); break;
-    case 3216: SCN_WARP_LAUNCH(32, 16, 2, 4); break;
-    case 3232: SCN_WARP_LAUNCH(32, 32, 2, 4); break;
-    case 3264: SCN_WARP_LAUNCH(32, 64, 1, 4); break;
-    case 6416: SCN_WARP_LAUNCH(64, 16, 1, 4); break;
-    case 6432: SCN_WARP_LAUNCH(64, 32, 1, 4); break;
-    case 6464: SCN_WARP_LAUNCH(64, 64, 1, 3); break;
+    case 1616: SCN_WARP_LAUNCH(16, 16, 4, 4); break;
+    case 1632: SCN_WARP_LAUNCH(16, 32, 4, 4); break;
+    case 1664: SCN_WARP_LAUNCH(16, 64, 2, 4); break;
+    case 3216: SCN_WARP_LAUNCH(32, 16, 4, 4); break;
+    case 3232: SCN_WARP_LAUNCH(32, 32, 4, 4); break;
+    case 3264: SCN_WARP_LAUNCH(32, 64, 2, 4); break;
+    case 6416: SCN_WARP_LAUNCH(64, 16, 2, 4); break;
+    case 6432: SCN_WARP_LAUNCH(64, 32, 2, 4); break;
+    case 6464: SCN_WARP_LAUNCH(64, 64, 2, 3); break;
     default: dev_free(own, s); return SCN_OK;
   }
 #undef SCN_WARP_LAUNCH
-  SCN_LAUNCHED();
   dev_free(own, s);
+  if (rc != SCN_OK) return rc;
+  SCN_LAUNCHED();
   *handled = true;
   return SCN_OK;
 }
