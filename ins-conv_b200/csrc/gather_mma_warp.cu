@@ -21,12 +21,8 @@
 //   * the loads of the next offset are issued before the MMAs of the current one (two register buffers).
 // No barrier inside the reduction, no scratch memory; skipping works at 16/32-row granularity instead of 128.
 // fp32 inputs are consumed as tf32 (low 13 mantissa bits ignored), accumulation is fp32.
-//
-// Two launch forms of the same warp code:
-//   resident   the whole packed weight tensor fits in shared memory (<= 112 KB, e.g. 27 x 32 x 32): one CTA of
-//              16 warps per SM copies it once and its warps walk over the row tiles; weight fragments come from
-//              shared memory, L1 is left to the gathered rows
-//   streaming  larger weight tensors: one tile per warp, weight fragments read through L1
+// One tile per warp; the weight fragments are read through L1 (a variant that kept them in shared memory, one
+// persistent CTA per SM, measured the same: both go through the same L1 data pipe, which is the busiest unit).
 #include "internal.h"
 #include <stdlib.h>
 
@@ -34,10 +30,8 @@ namespace scn {
 
 namespace {
 
-constexpr int kWarps = 4;      // streaming form: warps per block; every warp works alone
-constexpr int kResWarps = 16;  // resident form: warps per CTA, one CTA per SM
+constexpr int kWarps = 4;  // warps per block; every warp works alone
 constexpr int kMaxK = 27;
-constexpr size_t kResMaxWeightBytes = 112 * 1024;
 
 __device__ __align__(16) float g_zero_row[64];  // stands in for an absent neighbour (zero-initialised, never written)
 
@@ -67,27 +61,32 @@ __device__ __forceinline__ void load_rows(Frag<CIN, NTR> &f, const int *mp_k, co
   }
 }
 
-// wk: this lane's float4 of the first weight fragment of offset k; SMEM_B: wk points into shared memory
-template <int CIN, int COUT, int NTR, bool SMEM_B>
+// wk: this lane's float4 of the first weight fragment of offset k
+template <int CIN, int COUT, int NTR>
 __device__ __forceinline__ void mma_rows(float (&acc)[COUT / 16][NTR][4], const Frag<CIN, NTR> &f, const float4 *__restrict__ wk) {
   constexpr int MTC = COUT / 16;
 #pragma unroll
-  for (int c = 0; c < CIN / 16; ++c)
+  for (int c = 0; c < CIN / 16; ++c) {
+    float4 a[MTC][2];
 #pragma unroll
     for (int m = 0; m < MTC; ++m) {
-      const float4 *w = wk + ((c * MTC + m) * 2) * 32;
-      const float4 a0 = SMEM_B ? w[0] : __ldg(w);
-      const float4 a1 = SMEM_B ? w[32] : __ldg(w + 32);
-#pragma unroll
-      for (int n = 0; n < NTR; ++n) {
-        mma_m16n8k8_tf32(acc[m][n], a0, f.v[n][c].x, f.v[n][c].y);
-        mma_m16n8k8_tf32(acc[m][n], a1, f.v[n][c].z, f.v[n][c].w);
-      }
+      a[m][0] = __ldg(wk + ((c * MTC + m) * 2) * 32);
+      a[m][1] = __ldg(wk + ((c * MTC + m) * 2 + 1) * 32);
     }
+    // consecutive MMAs go to different accumulators: the same one comes up again MTC * NTR instructions later
+#pragma unroll
+    for (int m = 0; m < MTC; ++m)
+#pragma unroll
+      for (int n = 0; n < NTR; ++n) mma_m16n8k8_tf32(acc[m][n], a[m][0], f.v[n][c].x, f.v[n][c].y);
+#pragma unroll
+    for (int m = 0; m < MTC; ++m)
+#pragma unroll
+      for (int n = 0; n < NTR; ++n) mma_m16n8k8_tf32(acc[m][n], a[m][1], f.v[n][c].z, f.v[n][c].w);
+  }
 }
 
 // One tile of 8 * NTR output rows, done by one warp.  mp: the warp's [K][ROWS] slice of shared memory.
-template <int CIN, int COUT, int NTR, bool SMEM_B>
+template <int CIN, int COUT, int NTR>
 __device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *__restrict__ in, long long in_stride,
                                           const int32_t *__restrict__ map, int K, long long n_out, const float4 *wl,
                                           const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
@@ -149,7 +148,7 @@ __device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *
         mask &= mask - 1;
         load_rows<CIN, NTR>(f1, mp + k1 * ROWS, in_t, in_stride, zero_t, g);
       }
-      mma_rows<CIN, COUT, NTR, SMEM_B>(acc, f0, wl + k0 * WK);
+      mma_rows<CIN, COUT, NTR>(acc, f0, wl + k0 * WK);
       if (k1 < 0) break;
       k0 = -1;
       if (mask) {
@@ -157,11 +156,10 @@ __device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *
         mask &= mask - 1;
         load_rows<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, zero_t, g);
       }
-      mma_rows<CIN, COUT, NTR, SMEM_B>(acc, f1, wl + k1 * WK);
+      mma_rows<CIN, COUT, NTR>(acc, f1, wl + k1 * WK);
       if (k0 < 0) break;
     }
   }
-  __syncwarp();  // the slice is rewritten by the warp's next tile
 
   // accumulator fragment: c0,c1 -> plane 16m + g, rows 8n + 2t, +1; c2,c3 -> plane 16m + g + 8
 #pragma unroll
@@ -185,7 +183,6 @@ __device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *
     }
 }
 
-// streaming form: one tile per warp, weights through L1
 template <int CIN, int COUT, int NTR, int MINB>
 __global__ void __launch_bounds__(kWarps * 32, MINB)
 k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
@@ -196,35 +193,8 @@ k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long row0 = ((long long)blockIdx.x * kWarps + warp) * ROWS;
   if (row0 >= n_out) return;  // warps never synchronise with each other
-  warp_tile<CIN, COUT, NTR, false>(row0, s_map[warp], in, in_stride, map, K, n_out, Wp + lane, bias, out, out_stride,
+  warp_tile<CIN, COUT, NTR>(row0, s_map[warp], in, in_stride, map, K, n_out, Wp + lane, bias, out, out_stride,
                                   accumulate, lane);
-}
-
-// resident form: weights copied to shared memory once per CTA, warps walk over the tiles
-template <int CIN, int COUT, int NTR>
-__global__ void __launch_bounds__(kResWarps * 32, 1)
-k_gather_mma_tf32_res(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
-                      const float4 *__restrict__ Wp, const float *__restrict__ bias, float *__restrict__ out,
-                      long long out_stride, int accumulate, long long tiles) {
-  constexpr int ROWS = 8 * NTR, WK = (CIN / 16) * (COUT / 16) * 2 * 32;
-  extern __shared__ float4 s_res[];  // [K * WK] weight fragments, then [kResWarps][K * ROWS] map entries
-  float4 *sW = s_res;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int *mp = reinterpret_cast<int *>(s_res + (size_t)K * WK) + warp * (K * ROWS);
-  for (int i = threadIdx.x; i < K * WK; i += kResWarps * 32) sW[i] = __ldg(Wp + i);
-  __syncthreads();
-  // consecutive warps take consecutive tiles: a CTA works on 16 * ROWS neighbouring rows at a time
-  for (long long tile = (long long)blockIdx.x * kResWarps + warp; tile < tiles; tile += (long long)gridDim.x * kResWarps) {
-    const long long next = tile + (long long)gridDim.x * kResWarps;
-    if (map && next < tiles && lane < K) {  // pull the next tile's map entries into L2 meanwhile
-      const long long first = (long long)lane * n_out + next * ROWS, last_valid = (long long)K * n_out - 1;
-      const long long last = first + ROWS - 1 < last_valid ? first + ROWS - 1 : last_valid;
-      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(map + first));
-      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(map + last));
-    }
-    warp_tile<CIN, COUT, NTR, true>(tile * ROWS, mp, in, in_stride, map, K, n_out, sW + lane, bias, out, out_stride, accumulate,
-                                   lane);
-  }
 }
 
 // W [K][n_in][n_out] -> [K][n_in/16][n_out/16][2][lane][4], rounded to tf32 (round to nearest, ties away):
@@ -257,36 +227,12 @@ int max_planes() {  // development aid: widest layer the warp-level kernels take
   static const int v = env_int("INSCONV_WARP_MMA_MAX", 64);
   return v;
 }
-bool allow_resident() {  // development aid: 0 forces the streaming form
-  static const int v = env_int("INSCONV_WARP_MMA_RESIDENT", 1);
-  return v != 0;
-}
-
 template <int CI, int CO, int NTR, int MINB>
-int launch_warp(bool resident, int sm_count, const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out,
-                const float *Wp, const float *bias, float *out, int64_t out_stride, int accumulate, cudaStream_t s) {
+void launch_warp(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *Wp,
+                 const float *bias, float *out, int64_t out_stride, int accumulate, cudaStream_t s) {
   const long long tiles = (n_out + 8 * NTR - 1) / (8 * NTR);
-  const float4 *W4 = reinterpret_cast<const float4 *>(Wp);
-  if constexpr (CI * CO < 64 * 64) {  // 64 x 64 needs more registers than a 512-thread CTA has
-    if (resident) {
-      const size_t smem = (size_t)K * CI * CO * sizeof(float) + (size_t)kResWarps * K * 8 * NTR * sizeof(int);
-      static bool raised[64] = {false};  // the opt-in shared memory limit is raised once per device and kernel
-      int dev = 0;
-      SCN_CUDA(cudaGetDevice(&dev));
-      if (dev < 0 || dev >= 64 || !raised[dev]) {
-        SCN_CUDA(cudaFuncSetAttribute(k_gather_mma_tf32_res<CI, CO, NTR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      (int)(kResMaxWeightBytes + kResWarps * kMaxK * 32 * sizeof(int))));
-        if (dev >= 0 && dev < 64) raised[dev] = true;
-      }
-      const long long ctas = (tiles + kResWarps - 1) / kResWarps;
-      k_gather_mma_tf32_res<CI, CO, NTR><<<(unsigned)(ctas < sm_count ? ctas : sm_count), kResWarps * 32, smem, s>>>(
-          in, in_stride, map, K, n_out, W4, bias, out, out_stride, accumulate, tiles);
-      return SCN_OK;
-    }
-  }
   k_gather_mma_tf32<CI, CO, NTR, MINB><<<(unsigned)((tiles + kWarps - 1) / kWarps), kWarps * 32, 0, s>>>(
-      in, in_stride, map, K, n_out, W4, bias, out, out_stride, accumulate);
-  return SCN_OK;
+      in, in_stride, map, K, n_out, reinterpret_cast<const float4 *>(Wp), bias, out, out_stride, accumulate);
 }
 
 }  // namespace
@@ -319,23 +265,8 @@ int gather_mma_warp(const float *in, int64_t in_stride, const int32_t *map, int 
     SCN_TRY(warp_mma_pack(W, K, Cin, Cout, own, s));
     Wp = own;
   }
-  int sm_count = 148;
-  {
-    int dev = 0;
-    SCN_CUDA(cudaGetDevice(&dev));
-    static int cached[64] = {0};
-    if (dev >= 0 && dev < 64) {
-      if (!cached[dev]) SCN_CUDA(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
-      sm_count = cached[dev];
-    }
-  }
-  const size_t w_bytes = (size_t)K * Cin * Cout * sizeof(float);
-  // resident form only when every SM gets a few tiles per warp: the weight copy has to pay off
-  const bool resident = allow_resident() && w_bytes <= kResMaxWeightBytes && n_out >= (int64_t)sm_count * kResWarps * 32 * 2;
-#define SCN_WARP_LAUNCH(CI, CO, NTR, MINB)                                                                        \
-  rc = launch_warp<CI, CO, NTR, MINB>(resident, sm_count, in, in_stride, map, K, n_out, Wp, bias, out, out_stride, \
-                                     accumulate, s)
-  int rc = SCN_OK;
+#define SCN_WARP_LAUNCH(CI, CO, NTR, MINB) \
+  launch_warp<CI, CO, NTR, MINB>(in, in_stride, map, K, n_out, Wp, bias, out, out_stride, accumulate, s)
   const int key = (int)Cin * 100 + (int)Cout;
   switch (key) {
     case 1616: SCN_WARP_LAUNCH(16, 16, 4, 4); break;
@@ -351,7 +282,6 @@ int gather_mma_warp(const float *in, int64_t in_stride, const int32_t *map, int 
   }
 #undef SCN_WARP_LAUNCH
   dev_free(own, s);
-  if (rc != SCN_OK) return rc;
   SCN_LAUNCHED();
   *handled = true;
   return SCN_OK;
