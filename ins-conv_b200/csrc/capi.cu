@@ -116,16 +116,7 @@ static int need_coarse(scn_metadata *m, const int64_t *in_size, const int64_t *o
   *coarse = m->find(out_size);
   if (!*coarse) {
     std::unique_ptr<Grid> g(new Grid());
-    // the coarse box is the fine box halved: no need to measure it
-    Box hint;
-    for (int d = 0; d < 3; ++d) {
-      const int lo = (*fine)->box.o[d] >> 1, hi = ((*fine)->box.o[d] + (int)(*fine)->box.e[d] - 1) >> 1;
-      hint.o[d] = lo;
-      hint.e[d] = (unsigned)(hi - lo + 1);
-    }
-    hint.o[3] = (*fine)->box.o[3];
-    hint.e[3] = (*fine)->box.e[3];
-    SCN_TRY(grid_build(*g, nullptr, 0, (*fine)->coords, 1, (*fine)->n, false, (*fine)->n ? &hint : nullptr, s));
+    SCN_TRY(grid_build_coarse(*g, **fine, ssc_expected(), s));
     *coarse = g.get();
     m->grids[to_size(out_size)] = std::move(g);
   }
@@ -250,7 +241,7 @@ int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t 
     SCN_CUDA(cudaMemcpyAsync(staged, coords, (size_t)n_in * ncols * 8, cudaMemcpyHostToDevice, s));
     dev_coords = staged;
   }
-  int r = grid_build(*g, dev_coords, ncols, nullptr, 0, n_in, true, nullptr, s);
+  int r = grid_build(*g, dev_coords, ncols, nullptr, 0, n_in, true, nullptr, ssc_expected(), s);
   dev_free(staged, s);
   if (r != SCN_OK) {
     grid_free(*g, s);

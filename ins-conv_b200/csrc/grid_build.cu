@@ -88,7 +88,7 @@ __global__ void k_init_info(BuildInfo *info) {
     info->err = 0;
     info->n_unique = 0;
     info->max_active = 0;
-    info->pad = 0;
+    info->mask = 0;
   }
 }
 
@@ -334,9 +334,13 @@ template <bool UNIQUE>
 __global__ void k_assign(const unsigned long long *__restrict__ keys, long long n_src, Box bx,
                          const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
                          long long n, int32_t *__restrict__ src_row, int32_t *coords, uint32_t *cnt, Slot *table,
-                         uint32_t mask, BuildInfo *info) {
+                         uint32_t mask, BuildInfo *info, int dyn) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_src) return;
+  if (dyn) {  // site count and capacity were decided on the device (k_plan_table)
+    n = info->n_unique;
+    mask = info->mask;
+  }
   const unsigned long long key = keys[i];
   int x, y, z, b;
   unpack_key(key, x, y, z, b);
@@ -351,6 +355,15 @@ __global__ void k_assign(const unsigned long long *__restrict__ keys, long long 
     coords[2 * n + row] = z;
     coords[3 * n + row] = b;
     if (!table_insert(table, mask, key, (int)row)) atomicOr(&info->err, 2u);
+  }
+}
+
+// table capacity for the counted sites: the smallest power of two >= 2n, at least 16 (same rule as the host path)
+__global__ void k_plan_table(BuildInfo *info) {
+  if (threadIdx.x == 0) {
+    unsigned long long cap = 16;
+    while (cap < 2ull * info->n_unique) cap <<= 1;
+    info->mask = (unsigned int)(cap - 1);
   }
 }
 
@@ -403,7 +416,11 @@ __global__ void k_query(const int32_t *__restrict__ c, long long stride, long lo
 // looked up (incremental rulebook against the saved grid), the others get -1.
 __global__ void k_ssc_nbr(const int32_t *__restrict__ c, long long n, const Slot *__restrict__ table, uint32_t mask,
                           const int32_t *__restrict__ absent, int self_ok, int32_t *__restrict__ nbr,
-                          unsigned long long *counts) {
+                          unsigned long long *counts, const BuildInfo *dyn) {
+  if (dyn) {  // launched with a grid sized for an upper bound of n
+    n = dyn->n_unique;
+    mask = dyn->mask;
+  }
   const int k = blockIdx.y;
   const int dx = k / 9 - 1, dy = (k / 3) % 3 - 1, dz = k % 3 - 1;
   long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -423,7 +440,8 @@ __global__ void k_ssc_nbr(const int32_t *__restrict__ c, long long n, const Slot
 
 // 2x2x2 / stride 2: offset of a fine site inside its coarse cell k = (x&1)*4 + (y&1)*2 + (z&1)
 __global__ void k_conv_maps(const int32_t *__restrict__ fc, long long nf, const int32_t *__restrict__ parent,
-                            long long nc, int32_t *child, int32_t *up, unsigned long long *counts) {
+                            long long nc, int32_t *child, int32_t *up, unsigned long long *counts, const BuildInfo *dyn) {
+  if (dyn) nc = dyn->n_unique;
   long long f = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   __shared__ unsigned int hist[8];
   if (threadIdx.x < 8) hist[threadIdx.x] = 0;
@@ -483,8 +501,11 @@ int grid_free(Grid &g, cudaStream_t s) {
 // Bitmaps above this many bits (4 GiB of words plus 2 GiB of prefixes) are refused.
 static const unsigned long long kMaxBoxBits = 1ull << 35;
 
+static std::atomic<bool> g_ssc_seen{false};
+bool ssc_expected() { return g_ssc_seen.load(std::memory_order_relaxed); }
+
 int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift, int64_t n_src,
-               bool want_csr, const Box *box_hint, cudaStream_t s) {
+               bool want_csr, const Box *box_hint, bool with_ssc, cudaStream_t s) {
   grid_free(g, s);
   g.n_src = n_src;
   if (n_src == 0) return SCN_OK;
@@ -557,12 +578,12 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
   SCN_CUDA(cudaMemsetAsync(g.table, 0xFF, (size_t)cap * sizeof(Slot), s));
   if (n == n_src) {
     k_assign<true><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, nullptr,
-                                                     g.table, g.mask, info_d);
+                                                     g.table, g.mask, info_d, 0);
   } else {
     SCN_TRY(dev_alloc_t(&cnt, (size_t)n, s));
     SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n * 4, s));
     k_assign<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, cnt,
-                                                      g.table, g.mask, info_d);
+                                                      g.table, g.mask, info_d, 0);
   }
   SCN_LAUNCHED();
   g.max_active = 1;
@@ -583,15 +604,118 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
       need_info = true;
     }
   }
+  // the neighbour map rides along when asked for: its counts come back with the error word
+  unsigned long long *nbr_counts_d = nullptr, nbr_counts[27];
+  if (with_ssc && n > 0) {
+    SCN_TRY(dev_alloc_t(&nbr_counts_d, 27, s));
+    SCN_CUDA(cudaMemsetAsync(nbr_counts_d, 0, 27 * 8, s));
+    SCN_TRY(dev_alloc_t(&g.nbr, (size_t)n * 27, s));
+    k_ssc_nbr<<<dim3(blocks_for(n, 256), 27), 256, 0, s>>>(g.coords, n, g.table, g.mask, nullptr, 1, g.nbr, nbr_counts_d, nullptr);
+    SCN_LAUNCHED();
+    SCN_CUDA(cudaMemcpyAsync(nbr_counts, nbr_counts_d, sizeof(nbr_counts), cudaMemcpyDeviceToHost, s));
+  }
   // the error word (table overflow) always comes back; max_active with it when duplicates exist
   SCN_CUDA(cudaMemcpyAsync(&info, info_d, sizeof(info), cudaMemcpyDeviceToHost, s));
   SCN_CUDA(cudaStreamSynchronize(s));
   if (need_info) g.max_active = (int32_t)info.max_active;
+  if (nbr_counts_d) {
+    g.nbr_total = 0;
+    for (int k = 0; k < 27; ++k) {
+      g.nbr_count[k] = (int64_t)nbr_counts[k];
+      g.nbr_total += g.nbr_count[k];
+    }
+    dev_free(nbr_counts_d, s);
+  }
   dev_free(cnt, s);
   dev_free(prefix, s);
   dev_free(bitmap, s);
   dev_free(keys, s);
   dev_free(info_d, s);
+  if (info.err & 2u) return fail(SCN_E_CAPACITY, "hash table overflow");
+  return SCN_OK;
+}
+
+int grid_build_coarse(Grid &g, const Grid &fine, bool with_ssc, cudaStream_t s) {
+  grid_free(g, s);
+  const int64_t n_src = fine.n;
+  g.n_src = n_src;
+  if (n_src == 0) return SCN_OK;
+  const int T = 256;
+  // the coarse box is the fine box halved: nothing to measure
+  Box bx;
+  unsigned long long bits = 1;
+  for (int d = 0; d < 4; ++d) {
+    const int sh = d < 3 ? 1 : 0;
+    const int lo = fine.box.o[d] >> sh, hi = (fine.box.o[d] + (int)fine.box.e[d] - 1) >> sh;
+    bx.o[d] = lo;
+    bx.e[d] = (unsigned)(hi - lo + 1);
+    bits *= bx.e[d];
+  }
+  if (bits > kMaxBoxBits) return fail(SCN_E_CAPACITY, "scene bounding box larger than 2^35 cells");
+  const long long nwords = (long long)((bits + 63) >> 6);
+  uint64_t cap_bound = 16;  // n_coarse <= n_fine bounds every buffer
+  while (cap_bound < (uint64_t)n_src * 2) cap_bound <<= 1;
+  BuildInfo *info_d = nullptr;
+  unsigned long long *keys = nullptr, *bitmap = nullptr, *counts_d = nullptr;
+  uint32_t *prefix = nullptr, *cnt = nullptr;
+  SCN_TRY(dev_alloc_t(&info_d, 1, s));
+  SCN_TRY(dev_alloc_t(&keys, (size_t)n_src, s));
+  SCN_TRY(dev_alloc_t(&bitmap, (size_t)nwords, s));
+  SCN_TRY(dev_alloc_t(&prefix, (size_t)nwords, s));
+  SCN_TRY(dev_alloc_t(&cnt, (size_t)n_src, s));
+  SCN_TRY(dev_alloc_t(&counts_d, 8 + 27, s));
+  SCN_TRY(dev_alloc_t(&g.coords, (size_t)n_src * 4, s));
+  SCN_TRY(dev_alloc_t(&g.table, (size_t)cap_bound, s));
+  SCN_TRY(dev_alloc_t(&g.src_row, (size_t)n_src, s));
+  SCN_TRY(dev_alloc_t(&g.child, (size_t)n_src * 8, s));
+  SCN_TRY(dev_alloc_t(&g.fine_up, (size_t)n_src * 8, s));
+  k_init_info<<<1, 32, 0, s>>>(info_d);
+  SCN_LAUNCHED();
+  k_pack_keys_soa<<<blocks_for(n_src, T), T, 0, s>>>(fine.coords, n_src, 1, keys, info_d, 0);
+  SCN_LAUNCHED();
+  SCN_CUDA(cudaMemsetAsync(bitmap, 0, (size_t)nwords * 8, s));
+  k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap);
+  SCN_LAUNCHED();
+  SCN_TRY(scan_emit(PopcWords{bitmap}, StorePrefix{prefix}, nwords, &info_d->n_unique, s));
+  k_plan_table<<<1, 32, 0, s>>>(info_d);
+  SCN_LAUNCHED();
+  SCN_CUDA(cudaMemsetAsync(g.table, 0xFF, (size_t)cap_bound * sizeof(Slot), s));
+  SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n_src * 4, s));
+  SCN_CUDA(cudaMemsetAsync(counts_d, 0, (8 + 27) * 8, s));
+  k_assign<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, 0, g.src_row, g.coords, cnt, g.table, 0,
+                                                    info_d, 1);
+  SCN_LAUNCHED();
+  SCN_CUDA(cudaMemsetAsync(g.child, 0xFF, (size_t)n_src * 8 * 4, s));
+  k_conv_maps<<<blocks_for(n_src, 256), 256, 0, s>>>(fine.coords, n_src, g.src_row, 0, g.child, g.fine_up, counts_d, info_d);
+  SCN_LAUNCHED();
+  if (with_ssc) {
+    SCN_TRY(dev_alloc_t(&g.nbr, (size_t)n_src * 27, s));
+    k_ssc_nbr<<<dim3(blocks_for(n_src, 256), 27), 256, 0, s>>>(g.coords, 0, g.table, 0, nullptr, 1, g.nbr, counts_d + 8, info_d);
+    SCN_LAUNCHED();
+  }
+  BuildInfo info;
+  unsigned long long h[8 + 27];
+  SCN_CUDA(cudaMemcpyAsync(&info, info_d, sizeof(info), cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaMemcpyAsync(h, counts_d, sizeof(h), cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  dev_free(counts_d, s);
+  dev_free(cnt, s);
+  dev_free(prefix, s);
+  dev_free(bitmap, s);
+  dev_free(keys, s);
+  dev_free(info_d, s);
+  g.n = info.n_unique;
+  g.box = bx;
+  g.mask = info.mask;
+  g.max_active = 1;
+  for (int k = 0; k < 8; ++k) g.child_count[k] = (int64_t)h[k];
+  if (with_ssc) {
+    g.nbr_total = 0;
+    for (int k = 0; k < 27; ++k) {
+      g.nbr_count[k] = (int64_t)h[8 + k];
+      g.nbr_total += g.nbr_count[k];
+    }
+  }
   if (info.err & 2u) return fail(SCN_E_CAPACITY, "hash table overflow");
   return SCN_OK;
 }
@@ -614,7 +738,7 @@ static int nbr_common(const Grid &g, const Grid &lookup, const int32_t *absent, 
   SCN_TRY(dev_alloc_t(&counts_d, 27, s));
   SCN_CUDA(cudaMemsetAsync(counts_d, 0, 27 * 8, s));
   dim3 grid(blocks_for(g.n, 256), 27);
-  k_ssc_nbr<<<grid, 256, 0, s>>>(g.coords, g.n, lookup.table, lookup.mask, absent, self_ok, nbr, counts_d);
+  k_ssc_nbr<<<grid, 256, 0, s>>>(g.coords, g.n, lookup.table, lookup.mask, absent, self_ok, nbr, counts_d, nullptr);
   SCN_LAUNCHED();
   unsigned long long h[27];
   SCN_CUDA(cudaMemcpyAsync(h, counts_d, sizeof(h), cudaMemcpyDeviceToHost, s));
@@ -625,6 +749,7 @@ static int nbr_common(const Grid &g, const Grid &lookup, const int32_t *absent, 
 }
 
 int grid_build_ssc(Grid &g, cudaStream_t s) {
+  g_ssc_seen.store(true, std::memory_order_relaxed);
   if (g.nbr || g.n == 0) return SCN_OK;
   SCN_TRY(dev_alloc_t(&g.nbr, (size_t)g.n * 27, s));
   SCN_TRY(nbr_common(g, g, nullptr, 1, g.nbr, g.nbr_count, s));
@@ -653,7 +778,7 @@ int grid_build_conv(Grid &coarse, const Grid &fine, cudaStream_t s) {
   SCN_TRY(dev_alloc_t(&coarse.fine_up, (size_t)fine.n * 8, s));
   SCN_CUDA(cudaMemsetAsync(coarse.child, 0xFF, (size_t)coarse.n * 8 * 4, s));
   k_conv_maps<<<blocks_for(fine.n, 256), 256, 0, s>>>(fine.coords, fine.n, coarse.src_row, coarse.n, coarse.child,
-                                                     coarse.fine_up, counts_d);
+                                                     coarse.fine_up, counts_d, nullptr);
   SCN_LAUNCHED();
   unsigned long long h[8];
   SCN_CUDA(cudaMemcpyAsync(h, counts_d, sizeof(h), cudaMemcpyDeviceToHost, s));

@@ -57,7 +57,7 @@ struct BuildInfo {
   unsigned int err;         // bit0: coordinate out of key range, bit1: table overflow
   unsigned int n_unique;    // sites found
   unsigned int max_active;  // most source points in one site
-  unsigned int pad;
+  unsigned int mask;        // table capacity - 1, when the capacity is chosen on the device (coarse builds)
 };
 
 // Bounding box in key order used to rank keys: pos = ((b*ez + z)*ey + y)*ex + x (box-relative).
@@ -97,8 +97,16 @@ int grid_free(Grid &g, cudaStream_t s);
 //   coords_soa: int32 SoA [4][n_src] on the device, shifted right by `shift` bits (downsampling)
 // box_hint (optional): a box known to contain every source point; saves the host round trip that otherwise
 // fetches the measured bounding box.
+// with_ssc: also fill the 3x3x3 neighbour map before the build's last host round trip (saves the one
+// grid_build_ssc would make).
 int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift,
-               int64_t n_src, bool want_csr, const Box *box_hint, cudaStream_t s);
+               int64_t n_src, bool want_csr, const Box *box_hint, bool with_ssc, cudaStream_t s);
+// The next coarser scale of `fine` (sites at coordinates >> 1) with its size-2/stride-2 maps and, on request,
+// its neighbour map, in one pass with a single host round trip at the end: site count and table capacity stay
+// on the device while the kernels run, buffers are sized by the bound n_coarse <= n_fine.
+int grid_build_coarse(Grid &coarse, const Grid &fine, bool with_ssc, cudaStream_t s);
+// true once a neighbour map has been asked for in this process: later grids build theirs right away
+bool ssc_expected();
 int grid_build_ssc(Grid &g, cudaStream_t s);               // fills nbr / nbr_count
 int grid_build_conv(Grid &coarse, const Grid &fine, cudaStream_t s);  // fills child / fine_up
 int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_stride, int32_t *rows,
