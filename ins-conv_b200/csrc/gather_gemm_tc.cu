@@ -33,6 +33,7 @@
 #define PROF(x)
 #endif
 #include <cuda.h>
+#include <stddef.h>
 #include <stdlib.h>
 
 namespace scn {
@@ -350,26 +351,31 @@ __device__ __forceinline__ void tma_tile2d(uint32_t dst, const CUtensorMap *tm, 
 }
 
 // ---------------------------------------------------------------------------------------------
-// persistent, warp-specialised kernel for large grids
+// persistent, warp-specialised kernel
 // ---------------------------------------------------------------------------------------------
-// One CTA per SM walks over tiles (tile = blockIdx.x + i * gridDim.x).  Nine warps, three roles:
-//   warps 0-3  epilogue   wait for a finished accumulator, TMEM -> registers -> global, hand the
-//                         accumulator back (two accumulators alternate, so the tensor core starts the
-//                         next tile while this one is written out)
-//   warps 4-7  producers  gather the rows of each reduction step with 16-byte cp.async copies (zero-fill
-//                         for missing neighbours) into a ring of STAGES slots and signal the slot's `full`
-//                         barrier with cp.async.mbarrier.arrive, so nobody waits for a copy it issued:
-//                         the producers run ahead of the tensor core by as many slots as are free, across
-//                         tile boundaries.  One producer thread also fetches the step's weight block with a
-//                         single bulk-tensor copy.  The neighbour rows of the next tile are prefetched into
-//                         registers while the current tile is being issued.
-//   warp 8     tensor core one lane waits `full`, issues the four tcgen05.mma of the step, and lets
-//                         tcgen05.commit release the slot (`empty`) and, at the end of a tile, publish the
-//                         accumulator (`accfull`).
+// One CTA per SM walks over work items (item = blockIdx.x + i * gridDim.x).  Thirteen warps, three roles:
+//   warps 0-3   epilogue   wait for a finished accumulator, TMEM -> registers -> global, hand the
+//                          accumulator back (two accumulators alternate, so the tensor core starts the
+//                          next tile while this one is written out)
+//   warps 4-11  producers  every reduction step (offset k, 32-plane block kb) belongs to ONE producer warp
+//                          (the one that owns the step's ring slot): the warp waits for the slot, copies all 128
+//                          gathered rows with 16-byte cp.async (zero-fill for missing neighbours; 32 copies per
+//                          lane, all in flight together), has one lane fetch the step's weight block with a
+//                          single bulk-tensor copy, waits for its own copies, makes them visible to the tensor
+//                          core's proxy and arrives on the slot's `full` barrier.  As many steps as there are
+//                          slots (up to eight) are therefore in flight and the fixed cost of a step (barrier waits, fences, arrivals) is
+//                          paid by one warp instead of all eight.  The producers together stage each tile's map
+//                          entries in shared memory one tile ahead (three buffers) and agree on the offsets
+//                          that have any neighbour; all of them walk the same list of steps.
+//   warp 12     tensor core one lane waits `full`, issues the four tcgen05.mma of the step (descriptors are
+//                          advanced by adding to their low words) and lets tcgen05.commit release the slot
+//                          (`empty`) and, at the end of a tile, publish the accumulator (`accfull`).
 // Every blocking primitive is a bounded mbarrier wait.  A tile with no neighbour at all still runs one step
 // of zero rows so that all roles see the same sequence of tiles.
 constexpr int kPThreads = 416;  // 4 epilogue warps, 8 producer warps, 1 tensor-core warp
+constexpr int kProdWarps = 8;
 constexpr int kMaxStages = 8;
+constexpr int kMapBufs = 3;
 constexpr uint32_t kInfoFirst = 1, kInfoLast = 2, kInfoDone = 4;
 
 struct alignas(16) CtlP {
@@ -377,12 +383,27 @@ struct alignas(16) CtlP {
   unsigned long long empty[kMaxStages];
   unsigned long long accfull[2];
   unsigned long long accempty[2];
-  unsigned long long mapfull[2];
+  unsigned long long mapfull[kMapBufs];
+  unsigned long long pad_;  // keeps kmask_part on a 16-byte boundary (it is read as two uint4)
   uint32_t info[kMaxStages];
-  uint32_t kmask_part[2][8];
+  uint32_t kmask_part[kMapBufs][kProdWarps];
   uint32_t tmem_base;
   int failed;
 };
+static_assert(offsetof(CtlP, kmask_part) % 16 == 0, "kmask_part is read with 16-byte loads");
+
+// tcgen05.mma with the descriptors given as (low word, shared high word)
+__device__ __forceinline__ void mma_tf32_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %4, p;\n\t}\n" ::"r"(tmem_d),
+      "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 __global__ void __launch_bounds__(kPThreads, 1)
 k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, const __grid_constant__ CUtensorMap tmB,
@@ -394,7 +415,7 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
   const uint32_t stage_bytes = kABytes + b_bytes;
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   CtlP *ctl = reinterpret_cast<CtlP *>(smem + (size_t)stages * stage_bytes);
-  int *s_map = reinterpret_cast<int *>(ctl + 1);  // [2][K][128]
+  int *s_map = reinterpret_cast<int *>(ctl + 1);  // [kMapBufs][K][128]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int KB = Cin >> 5;
   // work items: (tile, share z of its reduction steps); Z == 1 means whole tiles
@@ -404,14 +425,14 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
   if (tid == 0) {
     ctl->failed = 0;
     for (int s = 0; s < stages; ++s) {
-      mbar_init(smem_u32(&ctl->full[s]), 9);  // one arrival per producer warp + the weight copy's expect_tx arrival
+      mbar_init(smem_u32(&ctl->full[s]), 2);  // the owning warp's arrival + the weight copy's expect_tx arrival
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl->accfull[b]), 1);
       mbar_init(smem_u32(&ctl->accempty[b]), 4);  // one arrival per epilogue warp
-      mbar_init(smem_u32(&ctl->mapfull[b]), 8);   // one arrival per producer warp
     }
+    for (int b = 0; b < kMapBufs; ++b) mbar_init(smem_u32(&ctl->mapfull[b]), kProdWarps);  // one arrival per producer warp
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
@@ -428,13 +449,13 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
   const uint32_t smem_base = smem_u32(smem);
   volatile int *failed = &ctl->failed;
 
-  if (warp >= 4 && warp < 12) {
+  if (warp >= 4 && warp < 4 + kProdWarps) {
     // =========================== producers ========================================================
     const int tp = tid - 128, pw = warp - 4;
-    // thread tp and thread tp + 128 share row (tp & 127) of the tile: one takes the even offsets, the other the odd
+    // map staging: thread tp and thread tp + 128 share row (tp & 127) of a tile: one takes the even offsets, the other the odd
     const int prow = tp & 127, par = tp >> 7;
-    int nxt[14];  // neighbour rows of this thread's row in the next tile, offsets par, par + 2, ...
-    auto prefetch_map = [&](long long item) {
+    int nxt[14];  // map entries of this thread's row, offsets par, par + 2, ..., of the tile after the current one
+    auto load_map = [&](long long item) {
       const long long tile = item / Z;
       const long long row = tile * kTileM + prow;
 #pragma unroll
@@ -445,23 +466,8 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
         nxt[j] = v;
       }
     };
-    prefetch_map(blockIdx.x);
-    // ring position, kept without divisions: slot index and how often the ring has wrapped
-    int slot = 0;
-    uint32_t wrapped = 0;  // number of completed passes over the ring
-    constexpr int kLag = 3;  // a step is signalled when three younger steps have been issued (stages >= 4)
-    long long issued = 0;
-    // this thread copies chunk c of rows r0, r0+32, r0+64, r0+96: the swizzle term depends on r0 & 7 only
-    const int c = tp & 7, r0 = tp >> 3;
-    const uint32_t dst0 = (uint32_t)((r0 >> 3) << 10) + (uint32_t)((r0 & 7) << 7) + (uint32_t)((c ^ (r0 & 7)) << 4);
-    const float *in_c = in + (c << 2);
-    PROF(long long t_map = 0; long long t_empty = 0; long long t_issue = 0; long long t_lag = 0; long long t_all0 = clock64();)
-    for (long long i = 0; i < my_tiles && !*failed; ++i) {
-      const long long item = (long long)blockIdx.x + i * gridDim.x;
-      const int buf = (int)(i & 1);
+    auto publish_map = [&](int buf) {  // registers -> shared memory; which offsets have any row
       int *mrows = s_map + buf * K * kTileM;
-      PROF(long long tm0 = clock64();)
-      // publish this tile's rows, learn which offsets have any
       unsigned int mine = 0;
 #pragma unroll
       for (int j = 0; j < 14; ++j) {
@@ -477,11 +483,41 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
         ctl->kmask_part[buf][pw] = mine;
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->mapfull[buf])) : "memory");
       }
-      prefetch_map(item + gridDim.x);  // in flight while this tile is issued
-      if (!mbar_wait(smem_u32(&ctl->mapfull[buf]), (uint32_t)((i >> 1) & 1), failed)) break;
-      const uint4 km0 = *reinterpret_cast<const uint4 *>(&ctl->kmask_part[buf][0]);
-      const uint4 km1 = *reinterpret_cast<const uint4 *>(&ctl->kmask_part[buf][4]);
+    };
+    load_map(blockIdx.x);
+    publish_map(0);
+    load_map((long long)blockIdx.x + gridDim.x);
+    // ring position of the step being enumerated, kept without divisions
+    int slot = 0;
+    uint32_t wrapped = 0;  // completed passes over the ring
+    // A ring slot belongs to one producer warp (slot s to warp s): the warp then waits for consecutive phases of
+    // the slot's `empty` barrier, which a parity wait can tell apart; with fewer slots than producer warps the
+    // surplus warps only help staging the maps.
+    // copies of a step: lane covers 16-byte chunk c of rows q + 4j, j = 0..31; the swizzle term depends on row & 7
+    const int c = lane & 7, q = lane >> 3;
+    const uint32_t dst_even = (uint32_t)(q << 7) + (uint32_t)((c ^ q) << 4);
+    const uint32_t dst_odd = (uint32_t)((q + 4) << 7) + (uint32_t)((c ^ (q + 4)) << 4);
+    const float *in_c = in + (c << 2);
+    PROF(long long t_map = 0; long long t_empty = 0; long long t_issue = 0; long long t_land = 0; long long t_all0 = clock64(); long long own = 0;)
+    int mbuf = 0;
+    uint32_t mphase = 0;
+    for (long long i = 0; i < my_tiles && !*failed; ++i) {
+      const long long item = (long long)blockIdx.x + i * gridDim.x;
+      PROF(long long tm0 = clock64();)
+      // This tile's map entries were published while the previous tile ran, so the wait is normally free.  Once it
+      // has passed, every producer warp is done with the tile before the previous one, whose buffer (the third)
+      // takes the next tile's entries; the loads for the tile after that start right away.
+      if (!mbar_wait(smem_u32(&ctl->mapfull[mbuf]), mphase, failed)) break;
+      publish_map(mbuf + 1 == kMapBufs ? 0 : mbuf + 1);
+      load_map(item + 2ll * gridDim.x);
+      const int *mrows = s_map + mbuf * K * kTileM;
+      const uint4 km0 = *reinterpret_cast<const uint4 *>(&ctl->kmask_part[mbuf][0]);
+      const uint4 km1 = *reinterpret_cast<const uint4 *>(&ctl->kmask_part[mbuf][4]);
       const unsigned int kmask = km0.x | km0.y | km0.z | km0.w | km1.x | km1.y | km1.z | km1.w;
+      if (++mbuf == kMapBufs) {
+        mbuf = 0;
+        mphase ^= 1u;
+      }
       // this item's share [t0, t1) of the tile's reduction steps; an empty share still runs one step of zero rows
       const int z = (int)(item % Z);
       const int nk_all = __popc(kmask);
@@ -493,53 +529,49 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
       unsigned int rest = kmask;
       int kb = 0;
       if (Tz > 0) {
-        for (int q = t0 / KB; q > 0; --q) rest &= rest - 1;
+        for (int r = t0 / KB; r > 0; --r) rest &= rest - 1;
         kb = t0 % KB;
       }
       int k = (Tz > 0 && rest) ? __ffs(rest) - 1 : 0;
       bool stop = false;
       PROF(t_map += clock64() - tm0;)
       for (int it = 0; it < T; ++it) {
-        PROF(long long te0 = clock64();)
-        if (wrapped > 0 && !mbar_wait(smem_u32(&ctl->empty[slot]), (wrapped - 1) & 1u, failed)) {
-          stop = true;
-          break;
-        }
-        PROF(long long te1 = clock64(); t_empty += te1 - te0;)
-        const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
-        const uint32_t bar = smem_u32(&ctl->full[slot]);
-        const int *mr = mrows + k * kTileM + r0;
-        int src[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) src[j] = nk ? mr[32 * j] : -1;
-        const float *in_kb = in_c + (kb << 5);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float *p = src[j] >= 0 ? in_kb + (long long)src[j] * in_stride : in;
-          cp_async16(a_base + dst0 + (uint32_t)(j << 12), p, src[j] >= 0 ? 16u : 0u);
-        }
-        if (tp == 0) {
-          ctl->info[slot] = (it == 0 ? kInfoFirst : 0u) | (it == T - 1 ? kInfoLast : 0u);
-          mbar_expect_tx(bar, b_bytes);
-          tma_tile2d(a_base + kABytes, &tmB, bar, kb << 5, k * Cout);
-        }
-        PROF(long long tl0 = clock64(); t_issue += tl0 - te1;)
-        // signal the step issued kLag steps ago: its copies (this thread's share) have landed by now
-        cp_async_commit();
-        ++issued;
-        if (issued > kLag) {
-          cp_async_wait<kLag>();
-#ifndef SCN_NO_STEP_FENCE
-          fence_async_proxy();
-#endif
-          __syncwarp();
-          if (lane == 0) {
-            int ls = slot - kLag;
-            if (ls < 0) ls += stages;
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->full[ls])) : "memory");
+        if (slot == pw) {
+          PROF(long long te0 = clock64(); ++own;)
+          if (wrapped > 0 && !mbar_wait(smem_u32(&ctl->empty[slot]), (wrapped - 1) & 1u, failed)) {
+            stop = true;
+            break;
           }
+          PROF(long long te1 = clock64(); t_empty += te1 - te0;)
+          const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
+          const uint32_t bar = smem_u32(&ctl->full[slot]);
+          if (lane == 0) {
+            ctl->info[slot] = (it == 0 ? kInfoFirst : 0u) | (it == T - 1 ? kInfoLast : 0u);
+            mbar_expect_tx(bar, b_bytes);
+            tma_tile2d(a_base + kABytes, &tmB, bar, kb << 5, k * Cout);
+          }
+          const int *mr = mrows + k * kTileM + q;
+          const float *in_kb = in_c + (kb << 5);
+#pragma unroll
+          for (int j0 = 0; j0 < 32; j0 += 8) {
+            int src[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) src[j] = nk ? mr[4 * (j0 + j)] : -1;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float *p = src[j] >= 0 ? in_kb + (long long)src[j] * in_stride : in;
+              const uint32_t dst = a_base + (uint32_t)(((j0 + j) >> 1) << 10) + (((j0 + j) & 1) ? dst_odd : dst_even);
+              cp_async16(dst, p, src[j] >= 0 ? 16u : 0u);
+            }
+          }
+          cp_async_commit();
+          PROF(long long tl0 = clock64(); t_issue += tl0 - te1;)
+          cp_async_wait<0>();
+          fence_async_proxy();
+          __syncwarp();
+          if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+          PROF(t_land += clock64() - tl0;)
         }
-        PROF(t_lag += clock64() - tl0;)
         if (++slot == stages) {
           slot = 0;
           ++wrapped;
@@ -552,47 +584,37 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
       }
       if (stop) break;
     }
-    PROF(if (blockIdx.x == 0 && tp == 0) printf("prod: total %lld map %lld empty-wait %lld issue %lld lag-wait %lld steps %lld tiles %lld\n", clock64() - t_all0, t_map, t_empty, t_issue, t_lag, issued, my_tiles);)
-    // drain: signal the last steps, oldest first
-    cp_async_wait<0>();
-    fence_async_proxy();
-    __syncwarp();
-    if (lane == 0) {
-      const int pending = issued < kLag ? (int)issued : kLag;
-      for (int d = pending; d >= 1; --d) {
-        int ls = slot - d;
-        if (ls < 0) ls += stages;
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->full[ls])) : "memory");
-      }
-    }
+    PROF(if (blockIdx.x == 0 && lane == 0) printf("prod %d: total %lld map %lld empty-wait %lld issue %lld landing %lld own steps %lld tiles %lld\n", pw, clock64() - t_all0, t_map, t_empty, t_issue, t_land, own, my_tiles);)
     // sentinel step: tells the tensor-core warp that no more work follows
-    if (!*failed) {
+    if (slot == pw && !*failed) {
       bool okw = true;
       if (wrapped > 0) okw = mbar_wait(smem_u32(&ctl->empty[slot]), (wrapped - 1) & 1u, failed);
-      if (okw) {
+      if (okw && lane == 0) {
         const uint32_t bar = smem_u32(&ctl->full[slot]);
-        if (tp == 0) {
-          ctl->info[slot] = kInfoDone;
-          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-        }
-        __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+        ctl->info[slot] = kInfoDone;
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
       }
     }
-    asm volatile("cp.async.wait_all;\n" ::: "memory");
-  } else if (warp == 12) {
+    __syncwarp();
+  } else if (warp == 4 + kProdWarps) {
     // =========================== tensor core ======================================================
     if (lane == 0) {
       const uint32_t idesc = instr_desc(Cout);
+      // descriptor words: low = start address / 16 | leading offset 16 B; high = stride offset 1024 B, version, 128-byte swizzle
+      const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t a_lo0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);
+      const uint32_t stage16 = stage_bytes >> 4, b_off16 = kABytes >> 4;
+      const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
       long long tile_i = 0;
       uint32_t tmem_d = tmem_base;
       int buf = 0, slot = 0;
-      uint32_t phase = 0;
-      bool first_mma = true;
-      PROF(long long t_full = 0; long long t_acc = 0; long long t0 = clock64(); long long nsteps = 0; long long t_info = 0; long long t_mma = 0; long long t_commit = 0;)
+      uint32_t phase = 0, a_lo = a_lo0;
+      uint32_t acc_flag = 0;
+      PROF(long long t_full = 0; long long t_acc = 0; long long t0 = clock64(); long long nsteps = 0; long long t_mma = 0;)
       while (!*failed) {
         PROF(long long a0 = clock64();)
-        if (!mbar_wait(smem_u32(&ctl->full[slot]), phase, failed)) break;
+        if (!mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) break;
         PROF(long long c0 = clock64(); t_full += c0 - a0; ++nsteps;)
         const uint32_t info = ctl->info[slot];
         if (info & kInfoDone) break;
@@ -604,31 +626,29 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
           if (tile_i >= 2 && !mbar_wait(smem_u32(&ctl->accempty[buf]), (uint32_t)(((tile_i >> 1) - 1) & 1), failed)) break;
           PROF(t_acc += clock64() - b0;)
           tc_fence_after();  // the epilogue's TMEM reads of this accumulator are ordered before the new MMAs
-          first_mma = true;
+          acc_flag = 0;
         }
-        const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
-        const uint32_t b_base = a_base + kABytes;
-        PROF(long long c1 = clock64(); t_info += c1 - c0;)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint64_t a_desc = smem_desc(a_base + j * 32, 16, 1024);
-          const uint64_t b_desc = smem_desc(b_base + j * 32, 16, 1024);
-          mma_tf32(tmem_d, a_desc, b_desc, idesc, (first_mma && j == 0) ? 0u : 1u);
-        }
-        first_mma = false;
-        PROF(long long c2 = clock64(); t_mma += c2 - c1;)
-        mma_commit(smem_u32(&ctl->empty[slot]));
+        PROF(long long c1 = clock64();)
+        const uint32_t b_lo = a_lo + b_off16;
+        mma_tf32_lohi(tmem_d, a_lo, b_lo, desc_hi, idesc, acc_flag);
+        mma_tf32_lohi(tmem_d, a_lo + 2, b_lo + 2, desc_hi, idesc, 1u);
+        mma_tf32_lohi(tmem_d, a_lo + 4, b_lo + 4, desc_hi, idesc, 1u);
+        mma_tf32_lohi(tmem_d, a_lo + 6, b_lo + 6, desc_hi, idesc, 1u);
+        acc_flag = 1u;
+        mma_commit(empty0 + 8u * (uint32_t)slot);
         if (info & kInfoLast) {
           mma_commit(smem_u32(&ctl->accfull[buf]));
           ++tile_i;
         }
+        a_lo += stage16;
         if (++slot == stages) {
           slot = 0;
           phase ^= 1u;
+          a_lo = a_lo0;
         }
-        PROF(t_commit += clock64() - c2;)
+        PROF(t_mma += clock64() - c1;)
       }
-      PROF(if (blockIdx.x == 0) printf("mma: total %lld full-wait %lld accempty-wait %lld info %lld mma-issue %lld commit %lld steps %lld\n", clock64() - t0, t_full, t_acc, t_info, t_mma, t_commit, nsteps);)
+      PROF(if (blockIdx.x == 0) printf("mma: total %lld full-wait %lld accempty-wait %lld issue+commit %lld steps %lld\n", clock64() - t0, t_full, t_acc, t_mma, nsteps);)
     }
     __syncwarp();
   } else {
@@ -847,7 +867,7 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
     const char *e = getenv("INSCONV_TC_KERNEL");
     return !(e && e[0] == 't');  // INSCONV_TC_KERNEL=tile forces the simple per-tile kernel (development aid)
   }();
-  const size_t fixed_p = sizeof(CtlP) + (size_t)2 * K * kTileM * sizeof(int) + 1024;
+  const size_t fixed_p = sizeof(CtlP) + (size_t)kMapBufs * K * kTileM * sizeof(int) + 1024;
   int st_p = (int)((220 * 1024 - fixed_p) / stage_bytes);
   if (st_p > kMaxStages) st_p = kMaxStages;
   if (use_persist && cols * 2 <= 512 && st_p >= 4) {
