@@ -152,7 +152,7 @@ int gather_gemm(const float *in, int64_t in_stride, int64_t in_rows, const int32
   if (precision != SCN_PREC_FP32) {
     bool handled = false;
     const bool packed = precision == SCN_PREC_TF32_PACKED;
-    if (warp_mma_shape(K, Cin, Cout)) {
+    if (warp_mma_shape(K, Cin, Cout) || (Cin <= 4 && !packed)) {
       SCN_TRY(gather_mma_warp(in, in_stride, map, K, n_out, W, bias, out, out_stride, Cin, Cout, accumulate, packed, s, &handled));
       if (handled) return SCN_OK;
       if (packed) return fail(SCN_E_INVALID, "packed weights given with an alignment the warp-level kernel does not take");

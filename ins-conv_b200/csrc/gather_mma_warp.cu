@@ -85,16 +85,11 @@ __device__ __forceinline__ void mma_rows(float (&acc)[COUT / 16][NTR][4], const 
   }
 }
 
-// One tile of 8 * NTR output rows, done by one warp.  mp: the warp's [K][ROWS] slice of shared memory.
-template <int CIN, int COUT, int NTR>
-__device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *__restrict__ in, long long in_stride,
-                                          const int32_t *__restrict__ map, int K, long long n_out, const float4 *wl,
-                                          const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
-                                          int accumulate, int lane) {
-  constexpr int ROWS = 8 * NTR, MTC = COUT / 16, C16 = CIN / 16;
-  const int g = lane >> 2, t = lane & 3;
-
-  // stage the map entries of this tile's rows and note which offsets have any
+// Stages the map entries [K][ROWS] of a tile's rows in the warp's slice of shared memory (all loads in flight
+// together) and returns the set of offsets that have any entry.  map == nullptr: identity, K = 1.
+template <int ROWS>
+__device__ __forceinline__ unsigned int stage_map(long long row0, int *mp, const int32_t *__restrict__ map, int K, long long n_out,
+                                                  int lane) {
   unsigned int mask = 0;
   if (map) {
     constexpr int PER = 32 / ROWS;               // offsets covered by one warp-wide load
@@ -104,7 +99,7 @@ __device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *
     const int32_t *mrow = map + row0 + r;
     int vals[NL];
 #pragma unroll
-    for (int j = 0; j < NL; ++j) {  // all loads first, so that they are in flight together
+    for (int j = 0; j < NL; ++j) {
       const int k = j * PER + ksub;
       vals[j] = (k < K && row_ok) ? __ldg(mrow + (long long)k * n_out) : -1;
     }
@@ -120,11 +115,49 @@ __device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *
         mask |= (b ? 1u : 0u) << j;
       }
     }
-  } else {  // identity: row o reads row o
+  } else {
     if (lane < ROWS) mp[lane] = row0 + lane < n_out ? (int)(row0 + lane) : -1;
     mask = 1u;
   }
   __syncwarp();
+  return mask;
+}
+
+// accumulator fragment: c0,c1 -> plane 16m + g, rows 8n + 2t, +1; c2,c3 -> plane 16m + g + 8
+template <int COUT, int NTR>
+__device__ __forceinline__ void store_acc(const float (&acc)[COUT / 16][NTR][4], long long row0, long long n_out,
+                                          const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
+                                          int accumulate, int g, int t) {
+#pragma unroll
+  for (int n = 0; n < NTR; ++n)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const long long row = row0 + n * 8 + 2 * t + j;
+      if (row < n_out) {
+        float *o = out + row * out_stride + g;
+#pragma unroll
+        for (int m = 0; m < COUT / 16; ++m)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float v = acc[m][n][2 * h + j];
+            const int c = 16 * m + 8 * h;
+            if (accumulate) v += o[c];
+            else if (bias) v += __ldg(bias + c + g);
+            o[c] = v;
+          }
+      }
+    }
+}
+
+// One tile of 8 * NTR output rows, done by one warp.  mp: the warp's [K][ROWS] slice of shared memory.
+template <int CIN, int COUT, int NTR>
+__device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *__restrict__ in, long long in_stride,
+                                          const int32_t *__restrict__ map, int K, long long n_out, const float4 *wl,
+                                          const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
+                                          int accumulate, int lane) {
+  constexpr int ROWS = 8 * NTR, MTC = COUT / 16, C16 = CIN / 16;
+  const int g = lane >> 2, t = lane & 3;
+  unsigned int mask = stage_map<ROWS>(row0, mp, map, K, n_out, lane);
 
   float acc[MTC][NTR][4];
 #pragma unroll
@@ -160,27 +193,7 @@ __device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *
       if (k0 < 0) break;
     }
   }
-
-  // accumulator fragment: c0,c1 -> plane 16m + g, rows 8n + 2t, +1; c2,c3 -> plane 16m + g + 8
-#pragma unroll
-  for (int n = 0; n < NTR; ++n)
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const long long row = row0 + n * 8 + 2 * t + j;
-      if (row < n_out) {
-        float *o = out + row * out_stride + g;
-#pragma unroll
-        for (int m = 0; m < MTC; ++m)
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            float v = acc[m][n][2 * h + j];
-            const int c = 16 * m + 8 * h;
-            if (accumulate) v += o[c];
-            else if (bias) v += __ldg(bias + c + g);
-            o[c] = v;
-          }
-      }
-    }
+  store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, accumulate, g, t);
 }
 
 template <int CIN, int COUT, int NTR, int MINB>
@@ -195,6 +208,55 @@ k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32
   if (row0 >= n_out) return;  // warps never synchronise with each other
   warp_tile<CIN, COUT, NTR>(row0, s_map[warp], in, in_stride, map, K, n_out, Wp + lane, bias, out, out_stride,
                                   accumulate, lane);
+}
+
+// Layers with 1 to 4 input planes (the first layer of a network: colours, a constant one): the planes of a
+// row fill k-slots 0..3 of one MMA, the other slots are zero, so an offset costs n_out / 16 MMAs per 8 rows and
+// a 4-byte load per row.  The weights are read as they are (no packing), the hardware ignores their low
+// mantissa bits.
+template <int COUT, int NTR>
+__global__ void __launch_bounds__(kWarps * 32)
+k_gather_mma_tf32_small(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
+                        const float *__restrict__ W, const float *__restrict__ bias, float *__restrict__ out,
+                        long long out_stride, int Cin, int accumulate) {
+  constexpr int ROWS = 8 * NTR, MTC = COUT / 16;
+  __shared__ int s_map[kWarps][kMaxK * ROWS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const long long row0 = ((long long)blockIdx.x * kWarps + warp) * ROWS;
+  if (row0 >= n_out) return;
+  int *mp = s_map[warp];
+  unsigned int mask = stage_map<ROWS>(row0, mp, map, K, n_out, lane);
+  float acc[MTC][NTR][4];
+#pragma unroll
+  for (int m = 0; m < MTC; ++m)
+#pragma unroll
+    for (int n = 0; n < NTR; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
+  const bool plane_ok = t < Cin;
+  while (mask) {
+    const int k = __ffs(mask) - 1;
+    mask &= mask - 1;
+    float b[NTR];
+#pragma unroll
+    for (int n = 0; n < NTR; ++n) {
+      const int s = mp[k * ROWS + n * 8 + g];
+      b[n] = (s >= 0 && plane_ok) ? __ldg(in + (long long)s * in_stride + t) : 0.f;
+    }
+    const float *wk = W + ((long long)k * Cin + t) * COUT + g;
+#pragma unroll
+    for (int m = 0; m < MTC; ++m) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);  // (plane t -> 16m + g, plane t -> 16m + g + 8, slots t + 4: unused)
+      if (plane_ok) {
+        a.x = __ldg(wk + 16 * m);
+        a.y = __ldg(wk + 16 * m + 8);
+      }
+#pragma unroll
+      for (int n = 0; n < NTR; ++n) mma_m16n8k8_tf32(acc[m][n], a, b[n], 0.f);
+    }
+  }
+  store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, accumulate, g, t);
 }
 
 // W [K][n_in][n_out] -> [K][n_in/16][n_out/16][2][lane][4], rounded to tf32 (round to nearest, ties away):
@@ -255,8 +317,24 @@ int gather_mma_warp(const float *in, int64_t in_stride, const int32_t *map, int 
                     const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate, bool packed,
                     cudaStream_t s, bool *handled) {
   *handled = false;
-  if (!warp_mma_shape(K, Cin, Cout)) return SCN_OK;
   if (!map && K != 1) return SCN_OK;
+  if (!packed && Cin >= 1 && Cin <= 4 && K <= kMaxK && max_planes() > 0 && (Cout == 16 || Cout == 32 || Cout == 64)) {
+    const long long tiles = (n_out + 31) / 32;
+    const unsigned blocks = (unsigned)((tiles + kWarps - 1) / kWarps);
+    if (Cout == 16)
+      k_gather_mma_tf32_small<16, 4><<<blocks, kWarps * 32, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
+                                                                   (int)Cin, accumulate);
+    else if (Cout == 32)
+      k_gather_mma_tf32_small<32, 4><<<blocks, kWarps * 32, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
+                                                                   (int)Cin, accumulate);
+    else
+      k_gather_mma_tf32_small<64, 4><<<blocks, kWarps * 32, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
+                                                                   (int)Cin, accumulate);
+    SCN_LAUNCHED();
+    *handled = true;
+    return SCN_OK;
+  }
+  if (!warp_mma_shape(K, Cin, Cout)) return SCN_OK;
   if (in_stride % 4 != 0 || out_stride % 2 != 0 || !aligned16(in) || !aligned16(W) || !aligned16(out)) return SCN_OK;
   float *own = nullptr;
   const float *Wp = W;

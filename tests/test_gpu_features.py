@@ -140,7 +140,7 @@ def test_linearity_at_full_size(cuda):
 TF32_TOL = 2e-2
 
 
-@pytest.mark.parametrize("n_in,n_out,bias", [(16, 16, False), (32, 32, False), (64, 32, True), (32, 64, False),
+@pytest.mark.parametrize("n_in,n_out,bias", [(3, 32, True), (1, 16, False), (4, 64, False), (16, 16, False), (32, 32, False), (64, 32, True), (32, 64, False),
                                              (64, 64, True), (16, 64, False), (64, 16, True), (96, 96, True),
                                              (224, 224, False), (448, 224, False)])
 def test_ssc_forward_tf32(cuda, n_in, n_out, bias):
