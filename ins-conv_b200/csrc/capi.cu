@@ -106,6 +106,11 @@ static int need_grid(scn_metadata *m, const int64_t *size, Grid **g) {
   return SCN_OK;
 }
 
+// How many stride-2 levels below the input scale networks of this process have asked for so far.  Once known,
+// the input layer builds that many coarse grids right away, while nothing else is queued on the stream: a build
+// ends with a host round trip, which in the middle of a network drains the queue of feature kernels first.
+static std::atomic<int> g_pyramid_levels{0};
+
 // coarse grid of in_size -> out_size (filter 2, stride 2), built on first use
 static int need_coarse(scn_metadata *m, const int64_t *in_size, const int64_t *out_size, Grid **fine, Grid **coarse,
                        cudaStream_t s) {
@@ -117,6 +122,12 @@ static int need_coarse(scn_metadata *m, const int64_t *in_size, const int64_t *o
   if (!*coarse) {
     std::unique_ptr<Grid> g(new Grid());
     SCN_TRY(grid_build_coarse(*g, **fine, ssc_expected(), s));
+    if (m->has_input && out_size[0] > 0) {  // remember how deep below the input scale this is
+      int level = 0;
+      for (int64_t sz = m->input_size[0]; sz > out_size[0] && sz % 2 == 0; sz /= 2) ++level;
+      int seen = g_pyramid_levels.load(std::memory_order_relaxed);
+      while (level > seen && !g_pyramid_levels.compare_exchange_weak(seen, level, std::memory_order_relaxed)) {}
+    }
     *coarse = g.get();
     m->grids[to_size(out_size)] = std::move(g);
   }
@@ -253,6 +264,16 @@ int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t 
   m->has_input = true;
   m->mode = mode;
   m->batch_size = batch_size;
+  // the coarse scales earlier networks went down to, now rather than in the middle of the network
+  Size3 cur = m->input_size;
+  for (int level = 0; level < g_pyramid_levels.load(std::memory_order_relaxed); ++level) {
+    if (cur[0] % 2 || cur[1] % 2 || cur[2] % 2 || cur[0] < 2 || cur[1] < 2 || cur[2] < 2) break;
+    const Size3 next{{cur[0] / 2, cur[1] / 2, cur[2] / 2}};
+    Grid *fine = nullptr, *coarse = nullptr;
+    SCN_TRY(need_coarse(m, cur.data(), next.data(), &fine, &coarse, s));
+    if (coarse->n == 0) break;
+    cur = next;
+  }
   return SCN_OK;
 }
 
