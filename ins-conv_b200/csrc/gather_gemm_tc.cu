@@ -110,6 +110,15 @@ __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t a_desc, uint6
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
@@ -367,16 +376,17 @@ __device__ __forceinline__ void tma_tile2d(uint32_t dst, const CUtensorMap *tm, 
 //                          paid by one warp instead of all eight.  The producers together stage each tile's map
 //                          entries in shared memory one tile ahead (three buffers) and agree on the offsets
 //                          that have any neighbour; all of them walk the same list of steps.
-//   warp 12     tensor core one lane waits `full`, issues the four tcgen05.mma of the step (descriptors are
-//                          advanced by adding to their low words) and lets tcgen05.commit release the slot
-//                          (`empty`) and, at the end of a tile, publish the accumulator (`accfull`).
+//   warp 12     tensor core waits `full`; one elected lane issues the four tcgen05.mma of the step (descriptors
+//                          are advanced by adding to their low words) and lets tcgen05.commit release the slot
+//                          (`empty`) and, at the end of a tile, publish the accumulator (`accfull`).  The whole
+//                          warp runs the loop so that the ring position stays a warp-uniform value.
 // Every blocking primitive is a bounded mbarrier wait.  A tile with no neighbour at all still runs one step
 // of zero rows so that all roles see the same sequence of tiles.
 constexpr int kPThreads = 416;  // 4 epilogue warps, 8 producer warps, 1 tensor-core warp
 constexpr int kProdWarps = 8;
 constexpr int kMaxStages = 8;
 constexpr int kMapBufs = 3;
-constexpr uint32_t kInfoFirst = 1, kInfoLast = 2, kInfoDone = 4;
+constexpr uint32_t kInfoDone = 1;  // info word of a step: (steps of the item << 8) on an item's first step, or this flag
 
 struct alignas(16) CtlP {
   unsigned long long full[kMaxStages];
@@ -546,7 +556,7 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
           const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
           const uint32_t bar = smem_u32(&ctl->full[slot]);
           if (lane == 0) {
-            ctl->info[slot] = (it == 0 ? kInfoFirst : 0u) | (it == T - 1 ? kInfoLast : 0u);
+            if (it == 0) ctl->info[slot] = (uint32_t)T << 8;  // the item's step count rides on its first step
             mbar_expect_tx(bar, b_bytes);
             tma_tile2d(a_base + kABytes, &tmB, bar, kb << 5, k * Cout);
           }
@@ -599,46 +609,51 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
     __syncwarp();
   } else if (warp == 4 + kProdWarps) {
     // =========================== tensor core ======================================================
-    if (lane == 0) {
-      const uint32_t idesc = instr_desc(Cout);
-      // descriptor words: low = start address / 16 | leading offset 16 B; high = stride offset 1024 B, version, 128-byte swizzle
-      const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-      const uint32_t a_lo0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);
-      const uint32_t stage16 = stage_bytes >> 4, b_off16 = kABytes >> 4;
-      const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
-      long long tile_i = 0;
-      uint32_t tmem_d = tmem_base;
-      int buf = 0, slot = 0;
-      uint32_t phase = 0, a_lo = a_lo0;
-      uint32_t acc_flag = 0;
-      PROF(long long t_full = 0; long long t_acc = 0; long long t0 = clock64(); long long nsteps = 0; long long t_mma = 0;)
-      while (!*failed) {
-        PROF(long long a0 = clock64();)
-        if (!mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) break;
-        PROF(long long c0 = clock64(); t_full += c0 - a0; ++nsteps;)
-        const uint32_t info = ctl->info[slot];
-        if (info & kInfoDone) break;
-        if (info & kInfoFirst) {
-          buf = (int)(tile_i & 1);
-          tmem_d = tmem_base + (uint32_t)buf * acc_cols;
-          // the epilogue must have drained this accumulator (used by tile tile_i - 2)
-          PROF(long long b0 = clock64();)
-          if (tile_i >= 2 && !mbar_wait(smem_u32(&ctl->accempty[buf]), (uint32_t)(((tile_i >> 1) - 1) & 1), failed)) break;
-          PROF(t_acc += clock64() - b0;)
-          tc_fence_after();  // the epilogue's TMEM reads of this accumulator are ordered before the new MMAs
-          acc_flag = 0;
+    // The whole warp runs the loop, so that ring position and descriptors are warp-uniform values; one elected
+    // lane issues.  The first step of an item carries the item's step count, the steps after it are counted.
+    const uint32_t idesc = instr_desc(Cout);
+    // descriptor words: low = start address / 16 | leading offset 16 B; high = stride offset 1024 B, version, 128-byte swizzle
+    const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    const uint32_t a_lo0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);
+    const uint32_t stage16 = stage_bytes >> 4, b_off16 = kABytes >> 4;
+    const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
+    long long tile_i = 0;
+    int slot = 0;
+    uint32_t phase = 0, a_lo = a_lo0;
+    PROF(long long t_full = 0; long long t_acc = 0; long long t0 = clock64(); long long nsteps = 0; long long t_mma = 0;)
+    bool alive = true;
+    while (alive) {
+      PROF(long long a0 = clock64();)
+      if (!mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) break;
+      PROF(t_full += clock64() - a0;)
+      const uint32_t info = __shfl_sync(0xffffffffu, ctl->info[slot], 0);
+      if (info & kInfoDone) break;
+      const int T = (int)(info >> 8);
+      const int buf = (int)(tile_i & 1);
+      const uint32_t tmem_d = tmem_base + (uint32_t)buf * acc_cols;
+      // the epilogue must have drained this accumulator (used by tile tile_i - 2)
+      PROF(long long b0 = clock64();)
+      if (tile_i >= 2 && !mbar_wait(smem_u32(&ctl->accempty[buf]), (uint32_t)(((tile_i >> 1) - 1) & 1), failed)) break;
+      PROF(t_acc += clock64() - b0;)
+      tc_fence_after();  // the epilogue's TMEM reads of this accumulator are ordered before the new MMAs
+      for (int t = 0; t < T; ++t) {
+        if (t > 0) {
+          PROF(long long a1 = clock64();)
+          if (!mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) {
+            alive = false;
+            break;
+          }
+          PROF(t_full += clock64() - a1;)
         }
-        PROF(long long c1 = clock64();)
-        const uint32_t b_lo = a_lo + b_off16;
-        mma_tf32_lohi(tmem_d, a_lo, b_lo, desc_hi, idesc, acc_flag);
-        mma_tf32_lohi(tmem_d, a_lo + 2, b_lo + 2, desc_hi, idesc, 1u);
-        mma_tf32_lohi(tmem_d, a_lo + 4, b_lo + 4, desc_hi, idesc, 1u);
-        mma_tf32_lohi(tmem_d, a_lo + 6, b_lo + 6, desc_hi, idesc, 1u);
-        acc_flag = 1u;
-        mma_commit(empty0 + 8u * (uint32_t)slot);
-        if (info & kInfoLast) {
-          mma_commit(smem_u32(&ctl->accfull[buf]));
-          ++tile_i;
+        PROF(long long c1 = clock64(); ++nsteps;)
+        if (elect_one()) {
+          const uint32_t b_lo = a_lo + b_off16;
+          mma_tf32_lohi(tmem_d, a_lo, b_lo, desc_hi, idesc, t > 0 ? 1u : 0u);
+          mma_tf32_lohi(tmem_d, a_lo + 2, b_lo + 2, desc_hi, idesc, 1u);
+          mma_tf32_lohi(tmem_d, a_lo + 4, b_lo + 4, desc_hi, idesc, 1u);
+          mma_tf32_lohi(tmem_d, a_lo + 6, b_lo + 6, desc_hi, idesc, 1u);
+          mma_commit(empty0 + 8u * (uint32_t)slot);
+          if (t == T - 1) mma_commit(smem_u32(&ctl->accfull[buf]));
         }
         a_lo += stage16;
         if (++slot == stages) {
@@ -648,8 +663,9 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
         }
         PROF(t_mma += clock64() - c1;)
       }
-      PROF(if (blockIdx.x == 0) printf("mma: total %lld full-wait %lld accempty-wait %lld issue+commit %lld steps %lld\n", clock64() - t0, t_full, t_acc, t_mma, nsteps);)
+      ++tile_i;
     }
+    PROF(if (blockIdx.x == 0 && lane == 0) printf("mma: total %lld full-wait %lld accempty-wait %lld issue+commit %lld steps %lld\n", clock64() - t0, t_full, t_acc, t_mma, nsteps);)
     __syncwarp();
   } else {
     // =========================== epilogue =========================================================
