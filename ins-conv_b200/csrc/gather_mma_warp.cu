@@ -11,7 +11,7 @@
 //     the slice in flight together),
 //   * for an offset, lane (g, t) (g = lane / 4, t = lane % 4) loads 16 bytes of rows g, g + 8, ... for every
 //     16-plane chunk, straight from global memory through L1 (neighbouring rows of a tile share most of their
-//     neighbours, so L1 catches the reuse); absent neighbours read a row of zeros,
+//     neighbours, so L1 catches the reuse); absent neighbours load nothing and contribute zeros,
 //   * the product is formed transposed, out^T = W^T * in^T, with mma.sync.m16n8k8 (tf32): the gathered rows are
 //     the 8-column operand, whose two registers per lane are (k-slot t, k-slot t + 4) of ONE row.  The reduction
 //     index is permuted so that these are two adjacent floats of a 16-byte load: a load feeds two MMAs with no
@@ -33,8 +33,6 @@ namespace {
 constexpr int kWarps = 4;  // warps per block; every warp works alone
 constexpr int kMaxK = 27;
 
-__device__ __align__(16) float g_zero_row[64];  // stands in for an absent neighbour (zero-initialised, never written)
-
 // D[16 x 8] += A[16 x 8] * B[8 x 8]; here A holds weights (rows = output planes) and B gathered rows
 // (columns = output rows), so that both register groups of an instruction are what one 16-byte load delivers.
 __device__ __forceinline__ void mma_m16n8k8_tf32(float (&d)[4], const float4 &a, float b0, float b1) {
@@ -51,13 +49,16 @@ template <int CIN, int NTR> struct Frag {
 
 template <int CIN, int NTR>
 __device__ __forceinline__ void load_rows(Frag<CIN, NTR> &f, const int *mp_k, const float *__restrict__ in_t, long long in_stride,
-                                          const float *zero_t, int g) {
+                                          int g) {
 #pragma unroll
   for (int n = 0; n < NTR; ++n) {
     const int s = mp_k[n * 8 + g];
-    const float4 *p = reinterpret_cast<const float4 *>(s >= 0 ? in_t + (long long)s * in_stride : zero_t);
+    const float4 *p = reinterpret_cast<const float4 *>(in_t + (long long)s * in_stride);
 #pragma unroll
-    for (int c = 0; c < CIN / 16; ++c) f.v[n][c] = __ldg(p + 4 * c);
+    for (int c = 0; c < CIN / 16; ++c) {
+      f.v[n][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (s >= 0) f.v[n][c] = __ldg(p + 4 * c);  // an absent neighbour costs no load
+    }
   }
 }
 
@@ -85,39 +86,50 @@ __device__ __forceinline__ void mma_rows(float (&acc)[COUT / 16][NTR][4], const 
   }
 }
 
-// Stages the map entries [K][ROWS] of a tile's rows in the warp's slice of shared memory (all loads in flight
-// together) and returns the set of offsets that have any entry.  map == nullptr: identity, K = 1.
+// Map entries [K][ROWS] of a tile's rows: loaded into registers with all loads in flight together, then published
+// in the warp's slice of shared memory together with the set of offsets that have any entry.
+// map == nullptr: identity, K = 1.
+template <int ROWS> struct MapRegs {
+  static constexpr int PER = 32 / ROWS;               // offsets covered by one warp-wide load
+  static constexpr int NL = (kMaxK + PER - 1) / PER;  // warp-wide loads for the largest K
+  int v[NL];
+};
+
 template <int ROWS>
-__device__ __forceinline__ unsigned int stage_map(long long row0, int *mp, const int32_t *__restrict__ map, int K, long long n_out,
-                                                  int lane) {
-  unsigned int mask = 0;
+__device__ __forceinline__ void load_map(MapRegs<ROWS> &m, long long row0, const int32_t *__restrict__ map, int K, long long n_out,
+                                         int lane) {
+  constexpr int PER = MapRegs<ROWS>::PER, NL = MapRegs<ROWS>::NL;
+  const int r = lane % ROWS, ksub = lane / ROWS;
+  const bool row_ok = row0 + r < n_out;
   if (map) {
-    constexpr int PER = 32 / ROWS;               // offsets covered by one warp-wide load
-    constexpr int NL = (kMaxK + PER - 1) / PER;  // warp-wide loads for the largest K
-    const int r = lane % ROWS, ksub = lane / ROWS;
-    const bool row_ok = row0 + r < n_out;
     const int32_t *mrow = map + row0 + r;
-    int vals[NL];
 #pragma unroll
     for (int j = 0; j < NL; ++j) {
       const int k = j * PER + ksub;
-      vals[j] = (k < K && row_ok) ? __ldg(mrow + (long long)k * n_out) : -1;
-    }
-#pragma unroll
-    for (int j = 0; j < NL; ++j) {
-      const int k = j * PER + ksub;
-      if (k < K) mp[k * ROWS + r] = vals[j];
-      const unsigned int b = __ballot_sync(0xffffffffu, vals[j] >= 0);
-      if (PER == 2) {
-        mask |= ((b & 0xffffu) ? 1u : 0u) << (j * PER);
-        mask |= ((b >> 16) ? 1u : 0u) << (j * PER + 1);
-      } else {
-        mask |= (b ? 1u : 0u) << j;
-      }
+      m.v[j] = (k < K && row_ok) ? __ldg(mrow + (long long)k * n_out) : -1;
     }
   } else {
-    if (lane < ROWS) mp[lane] = row0 + lane < n_out ? (int)(row0 + lane) : -1;
-    mask = 1u;
+#pragma unroll
+    for (int j = 0; j < NL; ++j) m.v[j] = (j == 0 && ksub == 0 && row_ok) ? (int)(row0 + r) : -1;
+  }
+}
+
+template <int ROWS>
+__device__ __forceinline__ unsigned int publish_map(const MapRegs<ROWS> &m, int *mp, int K, int lane) {
+  constexpr int PER = MapRegs<ROWS>::PER, NL = MapRegs<ROWS>::NL;
+  const int r = lane % ROWS, ksub = lane / ROWS;
+  unsigned int mask = 0;
+#pragma unroll
+  for (int j = 0; j < NL; ++j) {
+    const int k = j * PER + ksub;
+    if (k < K) mp[k * ROWS + r] = m.v[j];
+    const unsigned int b = __ballot_sync(0xffffffffu, m.v[j] >= 0);
+    if (PER == 2) {
+      mask |= ((b & 0xffffu) ? 1u : 0u) << (j * PER);
+      mask |= ((b >> 16) ? 1u : 0u) << (j * PER + 1);
+    } else {
+      mask |= (b ? 1u : 0u) << j;
+    }
   }
   __syncwarp();
   return mask;
@@ -149,15 +161,15 @@ __device__ __forceinline__ void store_acc(const float (&acc)[COUT / 16][NTR][4],
     }
 }
 
-// One tile of 8 * NTR output rows, done by one warp.  mp: the warp's [K][ROWS] slice of shared memory.
+// One tile of 8 * NTR output rows, done by one warp.  mp: the warp's [K][ROWS] slice of shared memory, holding the
+// tile's map entries; mask: the offsets that have any.
 template <int CIN, int COUT, int NTR>
-__device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *__restrict__ in, long long in_stride,
-                                          const int32_t *__restrict__ map, int K, long long n_out, const float4 *wl,
+__device__ __forceinline__ void warp_tile(long long row0, const int *mp, unsigned int mask, const float *__restrict__ in,
+                                          long long in_stride, long long n_out, const float4 *wl,
                                           const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
                                           int accumulate, int lane) {
   constexpr int ROWS = 8 * NTR, MTC = COUT / 16, C16 = CIN / 16;
   const int g = lane >> 2, t = lane & 3;
-  unsigned int mask = stage_map<ROWS>(row0, mp, map, K, n_out, lane);
 
   float acc[MTC][NTR][4];
 #pragma unroll
@@ -168,18 +180,18 @@ __device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *
       for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
 
   constexpr int WK = C16 * MTC * 2 * 32;  // float4 per offset
-  const float *in_t = in + 4 * t, *zero_t = g_zero_row + 4 * t;
+  const float *in_t = in + 4 * t;
   if (mask) {
     Frag<CIN, NTR> f0, f1;
     int k0 = __ffs(mask) - 1;
     mask &= mask - 1;
-    load_rows<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, zero_t, g);
+    load_rows<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
     while (true) {
       int k1 = -1;
       if (mask) {
         k1 = __ffs(mask) - 1;
         mask &= mask - 1;
-        load_rows<CIN, NTR>(f1, mp + k1 * ROWS, in_t, in_stride, zero_t, g);
+        load_rows<CIN, NTR>(f1, mp + k1 * ROWS, in_t, in_stride, g);
       }
       mma_rows<CIN, COUT, NTR>(acc, f0, wl + k0 * WK);
       if (k1 < 0) break;
@@ -187,7 +199,7 @@ __device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *
       if (mask) {
         k0 = __ffs(mask) - 1;
         mask &= mask - 1;
-        load_rows<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, zero_t, g);
+        load_rows<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
       }
       mma_rows<CIN, COUT, NTR>(acc, f1, wl + k1 * WK);
       if (k0 < 0) break;
@@ -196,6 +208,9 @@ __device__ __forceinline__ void warp_tile(long long row0, int *mp, const float *
   store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, accumulate, g, t);
 }
 
+// One tile per warp.  (A persistent form, warps walking over tiles and fetching the next tile's map entries
+// while working on the current one, measured 10-15 % slower: the hardware's block scheduler balances the uneven
+// tiles better than a fixed stride does.)
 template <int CIN, int COUT, int NTR, int MINB>
 __global__ void __launch_bounds__(kWarps * 32, MINB)
 k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
@@ -206,8 +221,11 @@ k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long row0 = ((long long)blockIdx.x * kWarps + warp) * ROWS;
   if (row0 >= n_out) return;  // warps never synchronise with each other
-  warp_tile<CIN, COUT, NTR>(row0, s_map[warp], in, in_stride, map, K, n_out, Wp + lane, bias, out, out_stride,
-                                  accumulate, lane);
+  int *mp = s_map[warp];
+  MapRegs<ROWS> regs;
+  load_map<ROWS>(regs, row0, map, K, n_out, lane);
+  const unsigned int mask = publish_map<ROWS>(regs, mp, K, lane);
+  warp_tile<CIN, COUT, NTR>(row0, mp, mask, in, in_stride, n_out, Wp + lane, bias, out, out_stride, accumulate, lane);
 }
 
 // Layers with 1 to 4 input planes (the first layer of a network: colours, a constant one): the planes of a
@@ -226,7 +244,9 @@ k_gather_mma_tf32_small(const float *__restrict__ in, long long in_stride, const
   const long long row0 = ((long long)blockIdx.x * kWarps + warp) * ROWS;
   if (row0 >= n_out) return;
   int *mp = s_map[warp];
-  unsigned int mask = stage_map<ROWS>(row0, mp, map, K, n_out, lane);
+  MapRegs<ROWS> regs;
+  load_map<ROWS>(regs, row0, map, K, n_out, lane);
+  unsigned int mask = publish_map<ROWS>(regs, mp, K, lane);
   float acc[MTC][NTR][4];
 #pragma unroll
   for (int m = 0; m < MTC; ++m)
