@@ -164,6 +164,13 @@ SCN_API int scn_pack_weights(const float *weight, int64_t volume, int64_t n_in, 
 SCN_API int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
                     int64_t out_stride, const float *weight, const float *bias, int64_t n_in, int64_t n_out,
                     int precision, void *stream, double *flops);
+/* out = addend + submanifold convolution(in), no bias: the residual sum of a ResNet block formed in the
+ * convolution's epilogue instead of by a separate pass over both tensors.  addend [n, n_out] rows with stride
+ * addend_stride; it may be `out` itself.  No counterpart in the reference, which adds with AddTable
+ * (sparseconvnet/tables.py) after the convolution. */
+SCN_API int scn_ssc_forward_add(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
+                        int64_t out_stride, const float *weight, const float *addend, int64_t addend_stride,
+                        int64_t n_in, int64_t n_out, int precision, void *stream, double *flops);
 /* Makes sure the coarse grid and rulebook for in_size -> out_size exist and returns the coarse site
  * count (callers size the output with it).  Part of Metadata::getRuleBook (Metadata/Metadata.cpp:669-697). */
 SCN_API int scn_conv_prepare(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], void *stream,

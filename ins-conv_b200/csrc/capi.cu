@@ -369,7 +369,23 @@ int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int
   SCN_TRY(check_feat(in, out, weight, n_in, n_out));
   cudaStream_t s = (cudaStream_t)stream;
   SCN_TRY(grid_build_ssc(*g, s));
-  SCN_TRY(gather_gemm(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, 0, precision, s));
+  SCN_TRY(gather_gemm(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0, precision, s));
+  if (flops) *flops = (double)g->nbr_total * (double)n_in * (double)n_out;
+  return SCN_OK;
+}
+int scn_ssc_forward_add(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
+                        int64_t out_stride, const float *weight, const float *addend, int64_t addend_stride, int64_t n_in,
+                        int64_t n_out, int precision, void *stream, double *flops) {
+  Grid *g;
+  SCN_TRY(need_grid(m, size, &g));
+  if (flops) *flops = 0;
+  if (g->n == 0) return SCN_OK;
+  SCN_TRY(check_feat(in, out, weight, n_in, n_out));
+  if (!addend) return fail(SCN_E_INVALID, "null addend");
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(grid_build_ssc(*g, s));
+  SCN_TRY(gather_gemm(in, in_stride, g->n, g->nbr, 27, g->n, weight, nullptr, out, out_stride, n_in, n_out, addend,
+                      addend_stride, precision, s));
   if (flops) *flops = (double)g->nbr_total * (double)n_in * (double)n_out;
   return SCN_OK;
 }
@@ -389,7 +405,7 @@ int scn_conv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t ou
   if (flops) *flops = 0;
   if (coarse->n == 0) return SCN_OK;
   SCN_TRY(check_feat(in, out, weight, n_in, n_out));
-  SCN_TRY(gather_gemm(in, in_stride, fine->n, coarse->child, 8, coarse->n, weight, bias, out, out_stride, n_in, n_out, 0,
+  SCN_TRY(gather_gemm(in, in_stride, fine->n, coarse->child, 8, coarse->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
                       precision, s));
   if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
   return SCN_OK;
@@ -403,7 +419,7 @@ int scn_deconv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t 
   if (flops) *flops = 0;
   if (fine->n == 0) return SCN_OK;
   SCN_TRY(check_feat(in, out, weight, n_in, n_out));
-  SCN_TRY(gather_gemm(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, 0,
+  SCN_TRY(gather_gemm(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
                       precision, s));
   if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
   return SCN_OK;
@@ -432,7 +448,7 @@ int scn_nin_forward(const float *in, int64_t in_stride, float *out, int64_t out_
   if (flops) *flops = (double)rows * (double)n_in * (double)n_out;
   if (rows == 0) return SCN_OK;
   SCN_TRY(check_feat(in, out, weight, n_in, n_out));
-  return gather_gemm(in, in_stride, rows, nullptr, 1, rows, weight, bias, out, out_stride, n_in, n_out, 0, precision,
+  return gather_gemm(in, in_stride, rows, nullptr, 1, rows, weight, bias, out, out_stride, n_in, n_out, nullptr, 0, precision,
                      (cudaStream_t)stream);
 }
 
@@ -497,9 +513,9 @@ int scn_incre_ssc_forward(scn_metadata *m, scn_metadata *pre, const int64_t size
   if (!pre_in) return fail(SCN_E_INVALID, "null saved features");
   SCN_TRY(grid_build_ssc(*g, s));
   SCN_TRY(need_nbr2(g, pg, im, s));
-  SCN_TRY(gather_gemm(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, 0, precision, s));
+  SCN_TRY(gather_gemm(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0, precision, s));
   if (im->nbr2_total)
-    SCN_TRY(gather_gemm(pre_in, pre_in_stride, pg->n, im->nbr2, 27, g->n, weight, nullptr, out, out_stride, n_in, n_out, 1,
+    SCN_TRY(gather_gemm(pre_in, pre_in_stride, pg->n, im->nbr2, 27, g->n, weight, nullptr, out, out_stride, n_in, n_out, out, out_stride,
                         precision, s));
   if (flops) *flops = (double)(g->nbr_total + im->nbr2_total) * (double)n_in * (double)n_out;
   return SCN_OK;
@@ -535,9 +551,9 @@ int scn_incre_deconv_forward(scn_metadata *m, scn_metadata *pre, const int64_t i
     SCN_TRY(dev_alloc_t(&im_c->up2, (size_t)fine->n * 8, s));
     SCN_TRY(build_incre_up(*coarse, im_c->pre_exist, im_f->pre_exist, im_c->up2, s));
   }
-  SCN_TRY(gather_gemm(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, 0,
+  SCN_TRY(gather_gemm(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
                       precision, s));
-  SCN_TRY(gather_gemm(pre_in, pre_in_stride, pg1->n, im_c->up2, 8, fine->n, weight, nullptr, out, out_stride, n_in, n_out, 1,
+  SCN_TRY(gather_gemm(pre_in, pre_in_stride, pg1->n, im_c->up2, 8, fine->n, weight, nullptr, out, out_stride, n_in, n_out, out, out_stride,
                       precision, s));
   if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
   return SCN_OK;

@@ -31,7 +31,7 @@ template <int TM, int TN, int RM, int RN>
 __global__ void __launch_bounds__((TM / RM) * (TN / RN))
 k_gather_gemm_f32(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K,
                   long long n_out, const float *__restrict__ W, const float *__restrict__ bias,
-                  float *__restrict__ out, long long out_stride, int Cin, int Cout, int accumulate, int vecA,
+                  float *out, long long out_stride, int Cin, int Cout, const float *init, long long init_stride, int vecA,
                   int vecB) {
   constexpr int NT = (TM / RM) * (TN / RN);
   constexpr int CG = TN / RN;  // threads along the output channels
@@ -131,7 +131,7 @@ k_gather_gemm_f32(const float *__restrict__ in, long long in_stride, const int32
       if (co >= Cout) continue;
       float v = acc[i][j];
       float *o = out + row * out_stride + co;
-      if (accumulate) v += *o;
+      if (init) v += init[row * init_stride + co];
       else if (bias) v += __ldg(bias + co);
       *o = v;
     }
@@ -139,12 +139,12 @@ k_gather_gemm_f32(const float *__restrict__ in, long long in_stride, const int32
 }
 
 int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out, const float *W,
-                     const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate,
-                     bool packed, cudaStream_t s, bool *handled);
+                     const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
+                     int64_t init_stride, bool packed, cudaStream_t s, bool *handled);
 
 int gather_gemm(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out, const float *W,
-                const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate,
-                int precision, cudaStream_t s) {
+                const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
+                int64_t init_stride, int precision, cudaStream_t s) {
   if (n_out == 0) return SCN_OK;
   if (Cin <= 0 || Cout <= 0 || Cin > 65536 || Cout > 65536) return fail(SCN_E_INVALID, "bad plane count");
   if (precision != SCN_PREC_FP32 && precision != SCN_PREC_TF32 && precision != SCN_PREC_TF32_PACKED)
@@ -153,11 +153,12 @@ int gather_gemm(const float *in, int64_t in_stride, int64_t in_rows, const int32
     bool handled = false;
     const bool packed = precision == SCN_PREC_TF32_PACKED;
     if (warp_mma_shape(K, Cin, Cout) || (Cin <= 4 && !packed)) {
-      SCN_TRY(gather_mma_warp(in, in_stride, map, K, n_out, W, bias, out, out_stride, Cin, Cout, accumulate, packed, s, &handled));
+      SCN_TRY(gather_mma_warp(in, in_stride, map, K, n_out, W, bias, out, out_stride, Cin, Cout, init, init_stride, packed, s,
+                              &handled));
       if (handled) return SCN_OK;
       if (packed) return fail(SCN_E_INVALID, "packed weights given with an alignment the warp-level kernel does not take");
     }
-    SCN_TRY(gather_gemm_tf32(in, in_stride, in_rows, map, K, n_out, W, bias, out, out_stride, Cin, Cout, accumulate,
+    SCN_TRY(gather_gemm_tf32(in, in_stride, in_rows, map, K, n_out, W, bias, out, out_stride, Cin, Cout, init, init_stride,
                              packed, s, &handled));
     if (handled) return SCN_OK;
     if (precision == SCN_PREC_TF32_PACKED)
@@ -170,15 +171,15 @@ int gather_gemm(const float *in, int64_t in_stride, int64_t in_rows, const int32
   if (Cout <= 16) {
     dim3 grid(blocks_for(n_out, 128), 1);
     k_gather_gemm_f32<128, 16, 4, 4><<<grid, 128, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
-                                                        (int)Cin, (int)Cout, accumulate, vecA, vecB);
+                                                        (int)Cin, (int)Cout, init, init_stride, vecA, vecB);
   } else if (Cout <= 32) {
     dim3 grid(blocks_for(n_out, 64), 1);
     k_gather_gemm_f32<64, 32, 4, 4><<<grid, 128, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
-                                                       (int)Cin, (int)Cout, accumulate, vecA, vecB);
+                                                       (int)Cin, (int)Cout, init, init_stride, vecA, vecB);
   } else {
     dim3 grid(blocks_for(n_out, 64), blocks_for(Cout, 64));
     k_gather_gemm_f32<64, 64, 8, 4><<<grid, 128, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
-                                                       (int)Cin, (int)Cout, accumulate, vecA, vecB);
+                                                       (int)Cin, (int)Cout, init, init_stride, vecA, vecB);
   }
   SCN_LAUNCHED();
   return SCN_OK;

@@ -158,7 +158,7 @@ template <int STAGES, int AHEAD>
 __global__ void __launch_bounds__(kThreads)
 k_gather_gemm_tf32(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K,
                    long long n_out, const float *__restrict__ W, const float *__restrict__ bias,
-                   float *__restrict__ out, long long out_stride, int Cin, int Cout, int accumulate,
+                   float *out, long long out_stride, int Cin, int Cout, const float *init, long long init_stride,
                    uint32_t tmem_cols, float *__restrict__ partial) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // layout: [stages: A (16 KB) + B (Cout*128 B)] [Ctl] [s_map: K*128 ints]
@@ -209,11 +209,11 @@ k_gather_gemm_tf32(const float *__restrict__ in, long long in_stride, const int3
   if (T == 0) {  // nothing to reduce here: the tile (or this share of it) contributes zero
     if (pdst) {
       for (int i = tid; i < kTileM * Cout; i += kThreads) pdst[i] = 0.f;
-    } else if (!accumulate) {
+    } else if (init != out) {
       for (long long i = tid; i < (long long)kTileM * Cout; i += kThreads) {
         const long long row = row0 + i / Cout;
         const int c = (int)(i % Cout);
-        if (row < n_out) out[row * out_stride + c] = bias ? __ldg(bias + c) : 0.f;
+        if (row < n_out) out[row * out_stride + c] = init ? init[row * init_stride + c] : (bias ? __ldg(bias + c) : 0.f);
       }
     }
     return;
@@ -327,8 +327,8 @@ k_gather_gemm_tf32(const float *__restrict__ in, long long in_stride, const int3
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
           float4 r = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          if (accumulate) {
-            const float4 old = *reinterpret_cast<const float4 *>(o + j);
+          if (init) {
+            const float4 old = *reinterpret_cast<const float4 *>(init + row * init_stride + c0 + j);
             r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
           } else if (bias) {
             r.x += __ldg(bias + c0 + j); r.y += __ldg(bias + c0 + j + 1);
@@ -418,7 +418,7 @@ __device__ __forceinline__ void mma_tf32_lohi(uint32_t tmem_d, uint32_t a_lo, ui
 __global__ void __launch_bounds__(kPThreads, 1)
 k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, const __grid_constant__ CUtensorMap tmB,
                            const int32_t *__restrict__ map, int K, long long n_out, const float *__restrict__ bias,
-                           float *__restrict__ out, long long out_stride, int Cin, int Cout, int accumulate,
+                           float *out, long long out_stride, int Cin, int Cout, const float *init, long long init_stride,
                            uint32_t acc_cols, int stages, long long tiles, int Z, float *__restrict__ partial) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t b_bytes = (uint32_t)Cout * 128u;
@@ -699,8 +699,8 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             float4 r = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            if (accumulate) {
-              const float4 old = *reinterpret_cast<const float4 *>(o + j);
+            if (init) {
+              const float4 old = *reinterpret_cast<const float4 *>(init + row * init_stride + c0 + j);
               r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
             } else if (bias) {
               r.x += __ldg(bias + c0 + j); r.y += __ldg(bias + c0 + j + 1);
@@ -758,10 +758,10 @@ __global__ void k_transpose_weights(const float *__restrict__ W, float *__restri
   for (int r = threadIdx.y; r < 32; r += blockDim.y) wt[(long long)(co0 + r) * Cin + ci0 + threadIdx.x] = tile[threadIdx.x][r];
 }
 
-// out[r][c] = (accumulate ? out : bias) + sum_z partial[z][r][c], z ascending
+// out[r][c] = (init ? init : bias) + sum_z partial[z][r][c], z ascending
 __global__ void k_splitk_reduce(const float *__restrict__ partial, int Z, long long rows_padded, long long n_out, int Cout,
-                                const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
-                                int accumulate) {
+                                const float *__restrict__ bias, float *out, long long out_stride, const float *init,
+                                long long init_stride) {
   const int cv = Cout >> 2;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_out * cv) return;
@@ -769,7 +769,7 @@ __global__ void k_splitk_reduce(const float *__restrict__ partial, int Z, long l
   const int c = (int)(i % cv) << 2;
   float4 acc;
   float *o = out + r * out_stride + c;
-  if (accumulate) acc = *reinterpret_cast<const float4 *>(o);
+  if (init) acc = *reinterpret_cast<const float4 *>(init + r * init_stride + c);
   else if (bias) acc = __ldg(reinterpret_cast<const float4 *>(bias + c));
   else acc = make_float4(0.f, 0.f, 0.f, 0.f);
   const float *p0 = partial + r * Cout + c;
@@ -819,12 +819,13 @@ int tc_check_errors(cudaStream_t s) {
 }
 
 int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out, const float *W,
-                     const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate,
-                     bool packed, cudaStream_t s, bool *handled) {
+                     const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
+                     int64_t init_stride, bool packed, cudaStream_t s, bool *handled) {
   *handled = false;
   if (Cin % 32 != 0 || Cout % 32 != 0 || Cout > 256 || K > 27) return SCN_OK;
   if (in_stride % 4 != 0 || out_stride % 4 != 0 || !aligned16(in) || !aligned16(W) || !aligned16(out)) return SCN_OK;
   if (bias && !aligned16(bias)) return SCN_OK;
+  if (init && (!aligned16(init) || init_stride % 4 != 0)) return SCN_OK;
   const size_t stage_bytes = (size_t)kABytes + (size_t)Cout * 128;
   const size_t fixed = sizeof(Ctl) + (size_t)K * kTileM * sizeof(int) + 1024;  // + alignment slack
   // two CTAs per SM when four stages fit in half an SM's shared memory, else as many stages as fit
@@ -903,13 +904,14 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
     }
     const long long n_items = tiles * Z;
     k_gather_gemm_tf32_persist<<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads, smem_p, s>>>(
-        in, in_stride, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, (int)Cout, accumulate, cols, st, tiles, Z, partial);
+        in, in_stride, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, (int)Cout, init, init_stride, cols, st, tiles, Z,
+        partial);
   } else {
 #define SCN_TC_LAUNCH(S, A)                                                                                          \
   do {                                                                                                               \
     SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tf32<S, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
     k_gather_gemm_tf32<S, A><<<grid, kThreads, smem, s>>>(in, in_stride, map, K, n_out, Wt, bias, out, out_stride,    \
-                                                           (int)Cin, (int)Cout, accumulate, cols, partial);          \
+                                                           (int)Cin, (int)Cout, init, init_stride, cols, partial); \
   } while (0)
   if (stages >= 6) SCN_TC_LAUNCH(6, 3);
   else if (stages == 5) SCN_TC_LAUNCH(5, 3);
@@ -921,7 +923,7 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
   if (Z > 1) {
     const long long work = n_out * (Cout / 4);
     k_splitk_reduce<<<(unsigned)((work + 255) / 256), 256, 0, s>>>(partial, Z, tiles * kTileM, n_out, (int)Cout, bias, out,
-                                                                  out_stride, accumulate);
+                                                                  out_stride, init, init_stride);
     SCN_LAUNCHED();
   }
   dev_free(partial, s);
@@ -988,7 +990,7 @@ int nin_forward_noalloc(const float *in, int64_t in_stride, float *out, int64_t 
   do {                                                                                                               \
     SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tf32<S, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
     k_gather_gemm_tf32<S, A><<<grid, kThreads, smem, s>>>(in, in_stride, nullptr, 1, rows, Wt, bias, out, out_stride, \
-                                                           (int)Cin, (int)Cout, 0, cols, nullptr);                   \
+                                                           (int)Cin, (int)Cout, nullptr, 0, cols, nullptr);          \
   } while (0)
   if (stages >= 6) SCN_NA_LAUNCH(6, 3);
   else if (stages == 5) SCN_NA_LAUNCH(5, 3);

@@ -138,8 +138,8 @@ __device__ __forceinline__ unsigned int publish_map(const MapRegs<ROWS> &m, int 
 // accumulator fragment: c0,c1 -> plane 16m + g, rows 8n + 2t, +1; c2,c3 -> plane 16m + g + 8
 template <int COUT, int NTR>
 __device__ __forceinline__ void store_acc(const float (&acc)[COUT / 16][NTR][4], long long row0, long long n_out,
-                                          const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
-                                          int accumulate, int g, int t) {
+                                          const float *__restrict__ bias, float *out, long long out_stride,
+                                          const float *init, long long init_stride, int g, int t) {
 #pragma unroll
   for (int n = 0; n < NTR; ++n)
 #pragma unroll
@@ -147,13 +147,14 @@ __device__ __forceinline__ void store_acc(const float (&acc)[COUT / 16][NTR][4],
       const long long row = row0 + n * 8 + 2 * t + j;
       if (row < n_out) {
         float *o = out + row * out_stride + g;
+        const float *ini = init ? init + row * init_stride + g : nullptr;
 #pragma unroll
         for (int m = 0; m < COUT / 16; ++m)
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             float v = acc[m][n][2 * h + j];
             const int c = 16 * m + 8 * h;
-            if (accumulate) v += o[c];
+            if (ini) v += ini[c];
             else if (bias) v += __ldg(bias + c + g);
             o[c] = v;
           }
@@ -166,8 +167,8 @@ __device__ __forceinline__ void store_acc(const float (&acc)[COUT / 16][NTR][4],
 template <int CIN, int COUT, int NTR>
 __device__ __forceinline__ void warp_tile(long long row0, const int *mp, unsigned int mask, const float *__restrict__ in,
                                           long long in_stride, long long n_out, const float4 *wl,
-                                          const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
-                                          int accumulate, int lane) {
+                                          const float *__restrict__ bias, float *out, long long out_stride,
+                                          const float *init, long long init_stride, int lane) {
   constexpr int ROWS = 8 * NTR, MTC = COUT / 16, C16 = CIN / 16;
   const int g = lane >> 2, t = lane & 3;
 
@@ -205,7 +206,7 @@ __device__ __forceinline__ void warp_tile(long long row0, const int *mp, unsigne
       if (k0 < 0) break;
     }
   }
-  store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, accumulate, g, t);
+  store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, init, init_stride, g, t);
 }
 
 // One tile per warp.  (A persistent form, warps walking over tiles and fetching the next tile's map entries
@@ -214,8 +215,8 @@ __device__ __forceinline__ void warp_tile(long long row0, const int *mp, unsigne
 template <int CIN, int COUT, int NTR, int MINB>
 __global__ void __launch_bounds__(kWarps * 32, MINB)
 k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
-                  const float4 *__restrict__ Wp, const float *__restrict__ bias, float *__restrict__ out, long long out_stride,
-                  int accumulate) {
+                  const float4 *__restrict__ Wp, const float *__restrict__ bias, float *out, long long out_stride,
+                  const float *init, long long init_stride) {
   constexpr int ROWS = 8 * NTR;
   __shared__ int s_map[kWarps][kMaxK * ROWS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -225,7 +226,7 @@ k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32
   MapRegs<ROWS> regs;
   load_map<ROWS>(regs, row0, map, K, n_out, lane);
   const unsigned int mask = publish_map<ROWS>(regs, mp, K, lane);
-  warp_tile<CIN, COUT, NTR>(row0, mp, mask, in, in_stride, n_out, Wp + lane, bias, out, out_stride, accumulate, lane);
+  warp_tile<CIN, COUT, NTR>(row0, mp, mask, in, in_stride, n_out, Wp + lane, bias, out, out_stride, init, init_stride, lane);
 }
 
 // Layers with 1 to 4 input planes (the first layer of a network: colours, a constant one): the planes of a
@@ -235,8 +236,8 @@ k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32
 template <int COUT, int NTR>
 __global__ void __launch_bounds__(kWarps * 32)
 k_gather_mma_tf32_small(const float *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
-                        const float *__restrict__ W, const float *__restrict__ bias, float *__restrict__ out,
-                        long long out_stride, int Cin, int accumulate) {
+                        const float *__restrict__ W, const float *__restrict__ bias, float *out, long long out_stride,
+                        int Cin, const float *init, long long init_stride) {
   constexpr int ROWS = 8 * NTR, MTC = COUT / 16;
   __shared__ int s_map[kWarps][kMaxK * ROWS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -276,7 +277,7 @@ k_gather_mma_tf32_small(const float *__restrict__ in, long long in_stride, const
       for (int n = 0; n < NTR; ++n) mma_m16n8k8_tf32(acc[m][n], a, b[n], 0.f);
     }
   }
-  store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, accumulate, g, t);
+  store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, init, init_stride, g, t);
 }
 
 // W [K][n_in][n_out] -> [K][n_in/16][n_out/16][2][lane][4], rounded to tf32 (round to nearest, ties away):
@@ -311,10 +312,10 @@ int max_planes() {  // development aid: widest layer the warp-level kernels take
 }
 template <int CI, int CO, int NTR, int MINB>
 void launch_warp(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *Wp,
-                 const float *bias, float *out, int64_t out_stride, int accumulate, cudaStream_t s) {
+                 const float *bias, float *out, int64_t out_stride, const float *init, int64_t init_stride, cudaStream_t s) {
   const long long tiles = (n_out + 8 * NTR - 1) / (8 * NTR);
   k_gather_mma_tf32<CI, CO, NTR, MINB><<<(unsigned)((tiles + kWarps - 1) / kWarps), kWarps * 32, 0, s>>>(
-      in, in_stride, map, K, n_out, reinterpret_cast<const float4 *>(Wp), bias, out, out_stride, accumulate);
+      in, in_stride, map, K, n_out, reinterpret_cast<const float4 *>(Wp), bias, out, out_stride, init, init_stride);
 }
 
 }  // namespace
@@ -334,8 +335,8 @@ int warp_mma_pack(const float *W, int64_t K, int64_t Cin, int64_t Cout, float *p
 }
 
 int gather_mma_warp(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *W,
-                    const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate, bool packed,
-                    cudaStream_t s, bool *handled) {
+                    const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
+                    int64_t init_stride, bool packed, cudaStream_t s, bool *handled) {
   *handled = false;
   if (!map && K != 1) return SCN_OK;
   if (!packed && Cin >= 1 && Cin <= 4 && K <= kMaxK && max_planes() > 0 && (Cout == 16 || Cout == 32 || Cout == 64)) {
@@ -343,13 +344,13 @@ int gather_mma_warp(const float *in, int64_t in_stride, const int32_t *map, int 
     const unsigned blocks = (unsigned)((tiles + kWarps - 1) / kWarps);
     if (Cout == 16)
       k_gather_mma_tf32_small<16, 4><<<blocks, kWarps * 32, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
-                                                                   (int)Cin, accumulate);
+                                                                   (int)Cin, init, init_stride);
     else if (Cout == 32)
       k_gather_mma_tf32_small<32, 4><<<blocks, kWarps * 32, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
-                                                                   (int)Cin, accumulate);
+                                                                   (int)Cin, init, init_stride);
     else
       k_gather_mma_tf32_small<64, 4><<<blocks, kWarps * 32, 0, s>>>(in, in_stride, map, K, n_out, W, bias, out, out_stride,
-                                                                   (int)Cin, accumulate);
+                                                                   (int)Cin, init, init_stride);
     SCN_LAUNCHED();
     *handled = true;
     return SCN_OK;
@@ -364,7 +365,7 @@ int gather_mma_warp(const float *in, int64_t in_stride, const int32_t *map, int 
     Wp = own;
   }
 #define SCN_WARP_LAUNCH(CI, CO, NTR, MINB) \
-  launch_warp<CI, CO, NTR, MINB>(in, in_stride, map, K, n_out, Wp, bias, out, out_stride, accumulate, s)
+  launch_warp<CI, CO, NTR, MINB>(in, in_stride, map, K, n_out, Wp, bias, out, out_stride, init, init_stride, s)
   const int key = (int)Cin * 100 + (int)Cout;
   switch (key) {
     case 1616: SCN_WARP_LAUNCH(16, 16, 4, 4); break;

@@ -123,11 +123,12 @@ int build_incre_up(const Grid &coarse, const int32_t *pe_coarse, const int32_t *
                    cudaStream_t s);
 
 // ---- feature kernels --------------------------------------------------------
-// out[o] = (accumulate ? out[o] : bias) + sum_k in[map[k*n_out + o]] * W[k]   (map == nullptr: identity, K = 1)
+// out[o] = (init ? init[o] : bias) + sum_k in[map[k*n_out + o]] * W[k]   (map == nullptr: identity, K = 1)
+// init: rows [n_out, n_planes_out] with stride init_stride, or nullptr; it may be `out` itself (accumulate in place).
 // in has in_rows rows; map entries are -1 or in [0, in_rows).
 int gather_gemm(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out, const float *W,
                 const float *bias, float *out, int64_t out_stride, int64_t n_in, int64_t n_planes_out,
-                int accumulate, int precision, cudaStream_t s);
+                const float *init, int64_t init_stride, int precision, cudaStream_t s);
 // reads and clears the error word of the tensor-core kernels; synchronises s
 int tc_check_errors(cudaStream_t s);
 // narrow layers (n_in, n_out in {16, 32, 64}) run a warp-level mma.sync kernel with its own packed weight layout;
@@ -135,7 +136,8 @@ int tc_check_errors(cudaStream_t s);
 bool warp_mma_shape(int64_t K, int64_t Cin, int64_t Cout);
 int warp_mma_pack(const float *W, int64_t K, int64_t Cin, int64_t Cout, float *packed, cudaStream_t s);
 int gather_mma_warp(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *W,
-                    const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, int accumulate, bool packed,
+                    const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
+                    int64_t init_stride, bool packed,
                     cudaStream_t s, bool *handled);
 bool tc_packable(int64_t K, int64_t Cin, int64_t Cout);
 int tc_pack_weights(const float *W, int64_t K, int64_t Cin, int64_t Cout, float *packed, cudaStream_t s);

@@ -122,7 +122,7 @@ class Metadata3 {
 // ---- full-frame ops ------------------------------------------------------------------------------
 double SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filterSize, Metadata3 &m,
                                            at::Tensor input_features, at::Tensor output_features, at::Tensor weight,
-                                           at::Tensor bias, int dilated_rate, at::Tensor packed) {
+                                           at::Tensor bias, int dilated_rate, at::Tensor packed, at::Tensor addend) {
   need_cuda_f32(input_features, "input_features");
   need_cuda_f32(weight, "weight");
   TORCH_CHECK(dilated_rate == 1, "dilated submanifold convolutions are outside the hot path");
@@ -138,6 +138,17 @@ double SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filt
   output_features.resize_({n, w.size(2)});
   double flops = 0;
   WeightArg wa(w, packed);
+  if (addend.defined() && addend.numel() > 0) {  // out = addend + convolution: the residual sum formed in the epilogue
+    need_cuda_f32(addend, "addend");
+    TORCH_CHECK(!bias.defined() || bias.numel() == 0, "the fused residual sum takes no bias");
+    TORCH_CHECK(addend.dim() == 2 && addend.size(0) == n && addend.size(1) == w.size(2) && addend.stride(1) == 1,
+                "addend must be [nActive, nOut] with unit plane stride");
+    check(scn_ssc_forward_add(m.h(), s.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(), w.size(2),
+                              wa.ptr, addend.data_ptr<float>(), addend.stride(0), w.size(1), w.size(2), wa.precision,
+                              stream_of(in), &flops),
+          "SubmanifoldConvolution_updateOutput");
+    return flops;
+  }
   check(scn_ssc_forward(m.h(), s.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(), w.size(2),
                         wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision, stream_of(in), &flops),
         "SubmanifoldConvolution_updateOutput");
@@ -418,7 +429,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
       .def("getSpatialLocations", &Metadata3::getSpatialLocations)
       .def("getSpatialLocationsDevice", &Metadata3::getSpatialLocationsDevice)
       .def("getNActive", &Metadata3::getNActive);
-  mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("dilated_rate"), pybind11::arg("packed") = at::Tensor());
+  mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("dilated_rate"), pybind11::arg("packed") = at::Tensor(), pybind11::arg("addend") = at::Tensor());
   mod.def("Convolution_updateOutput", &Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());
   mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());
   mod.def("BatchNormalization_updateOutput", &BatchNormalization_updateOutput);

@@ -57,6 +57,7 @@ PROTOTYPES = {
     "scn_weights_packable": (_int, [_i64, _i64, _i64]),
     "scn_pack_weights": (_int, [_p, _i64, _i64, _i64, _p, _p]),
     "scn_ssc_forward": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
+    "scn_ssc_forward_add": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_conv_prepare": (_int, [_p, _i64p, _i64p, _p, _i64p]),
     "scn_conv_forward": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_deconv_forward": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
@@ -267,6 +268,16 @@ class Metadata(object):
         fl = _dbl(0)
         call("scn_ssc_forward", self.h, size3(size), ptr(x), x.stride(0), ptr(out), n_out, ptr(weight), ptr(bias),
              weight.shape[1], n_out, precision, _stream(), C.byref(fl))
+        return out, fl.value
+
+    def ssc_forward_add(self, size, x, weight, addend, precision=PREC_FP32):
+        import torch
+        x = x.contiguous()
+        n_out = weight.shape[2]
+        out = torch.empty(x.shape[0], n_out, dtype=torch.float32, device=x.device)
+        fl = _dbl(0)
+        call("scn_ssc_forward_add", self.h, size3(size), ptr(x), x.stride(0), ptr(out), n_out, ptr(weight), ptr(addend),
+             addend.stride(0), weight.shape[1], n_out, precision, _stream(), C.byref(fl))
         return out, fl.value
 
     def conv_forward(self, in_size, out_size, x, weight, bias=None, precision=PREC_FP32):

@@ -159,6 +159,24 @@ def test_ssc_forward_tf32(cuda, n_in, n_out, bias):
     assert err < 5e-3, err
 
 
+@pytest.mark.parametrize("n_in,n_out,prec", [(32, 32, "fp32"), (32, 32, "tf32"), (64, 32, "tf32"), (96, 96, "tf32"),
+                                             (224, 224, "tf32"), (3, 32, "tf32")])
+def test_ssc_forward_add(cuda, n_in, n_out, prec):
+    # out = addend + convolution, formed in the epilogue (direct, split-K reduction and warp-level kernels)
+    m, g = _scene(cuda, 3)
+    rng = np.random.RandomState(n_in + n_out)
+    x = torch.from_numpy(rng.randn(g.n, n_in).astype(np.float32)).to(cuda)
+    w = torch.from_numpy(synth.kaiming_uniform(rng, 27, n_in, n_out)).to(cuda)
+    base = torch.from_numpy(rng.randn(g.n, n_out + 4).astype(np.float32)).to(cuda)[:, :n_out]  # strided rows
+    p = cabi.PREC_TF32 if prec == "tf32" else cabi.PREC_FP32
+    plain, fl0 = m.ssc_forward(128, x, w, None, p)
+    got, fl1 = m.ssc_forward_add(128, x, w, base, p)
+    cabi.check_errors()
+    assert fl0 == fl1
+    want = plain + base
+    assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
+
+
 def test_conv_deconv_nin_tf32(cuda):
     m, g = _scene(cuda, 1)
     rng = np.random.RandomState(17)
