@@ -11,8 +11,10 @@ voxels changed, reference semantics) is timed beside it and reported as ms/frame
 
   value      inputs resident in HBM when the timed region starts
   e2e        the same through the public module API with pinned HOST inputs and a host read of the result
-  roofline   the dominant kernel (the gather-GEMM of the level-0 32->32 submanifold convolution), timed
-             alone with CUDA events on the launching stream, L2 flushed between launches
+  roofline   the dominant kernel (the gather-GEMM of the level-0 32->32 submanifold convolution: the warp-level
+             tf32 kernel), timed alone with CUDA events on the launching stream, L2 flushed between launches
+  tcgen05    the same measurement for the tcgen05 kernel on a wide layer (128->128 on the room's sites),
+             reported against the tensor roofline
   hash_build the grid build (voxel hash + site ranking + input rules) at 36k, 255k and 4M points
   cpu_baseline  the CPU restatement of the reference (oracle/) on this box's host cores, rank 0, N=1 only
 
@@ -89,9 +91,13 @@ class ClockSampler(object):
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            # the tool's start-up (driver library initialisation, first query) must be over before anything is timed
+            t0 = time.time()
+            while not self.lines and time.time() - t0 < 5.0:
+                time.sleep(0.05)
         except Exception:
             self.proc = None
 
@@ -184,22 +190,31 @@ def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
         c4 = np.concatenate([c, np.zeros((c.shape[0], 1), np.int64)], 1)
         d = torch.from_numpy(c4).to(dev)
         m = cabi.Metadata()
-        ts = []
-        for i in range(warmup + steps):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            n = m.input_layer_build(size, d, mode=4)
-            e1.record()
-            torch.cuda.synchronize()
-            if i >= warmup:
-                ts.append(e0.elapsed_time(e1) * 1e-3)
-        t = sorted(ts)[len(ts) // 2]
+
+        def median_build():
+            ts = []
+            for i in range(warmup + steps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                n = m.input_layer_build(size, d, mode=4)
+                e1.record()
+                torch.cuda.synchronize()
+                if i >= warmup:
+                    ts.append(e0.elapsed_time(e1) * 1e-3)
+            return sorted(ts)[len(ts) // 2], n
+
+        cabi.call("scn_set_build_ahead", 0, 0)  # the hash build alone: input scale, no neighbour map
+        t, n = median_build()
+        cabi.call("scn_set_build_ahead", 1, 6)  # what a UNet frame pays: 7 scales with their rulebook maps
+        t_all, _ = median_build()
+        cabi.call("scn_set_build_ahead", -1, -1)
         cap = 16
         while cap < 2 * n:
             cap *= 2
         byts = 32.0 * c4.shape[0] + 8.0 * cap + 12.0 * n + 4.0 * c4.shape[0]
         out.append({"scene": name, "points": int(c4.shape[0]), "sites": int(n), "us": t * 1e6,
-                    "points_per_s": c4.shape[0] / t, "GBps": byts / t / 1e9})
+                    "points_per_s": c4.shape[0] / t, "GBps": byts / t / 1e9,
+                    "us_with_6_coarse_scales_and_all_maps": t_all * 1e6})
     return out
 
 
@@ -312,7 +327,7 @@ def voxel_layers_of(runner):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--voxels", type=int, default=250000)
@@ -499,13 +514,25 @@ def main():
     args.n_in, args.n_out = 32, 32
     lay = layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind)
     roofline = dict(lay["roofline"])
-    roofline.update({"kernel": "gather-GEMM %s, SSC 32->32 on %d sites (level 0 of the UNet, 9 of the 53 SSC layers)"
-                               % (args.precision, lay["sites"]),
+    roofline.update({"kernel": "gather-GEMM %s (%s), SSC 32->32 on %d sites (level 0 of the UNet: 9 of the 53 SSC "
+                               "layers, 78 %% of the frame's voxel-layers)"
+                               % (args.precision, "warp-level mma.sync kernel" if args.precision == "tf32" else "FFMA kernel",
+                                  lay["sites"]),
                      "us_per_launch": lay["us_per_launch"], "voxels_per_s": lay["voxels_per_s"],
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
-                     # profiles/gather_gemm_tf32_persist_ssc32_room.md (same kernel, same workload)
-                     "traffic": 66.7e6 if args.precision == "tf32" and args.voxels == 250000 else None,
+                     # profiles/gather_mma_tf32_warp_ssc32_room.md (same kernel, same workload)
+                     "traffic": 67.5e6 if args.precision == "tf32" and args.voxels == 250000 else None,
                      "l2": "flushed between launches (256 MB write)"})
+    tcgen05 = None
+    if args.precision == "tf32":  # the tcgen05 kernel on a wide layer, against the tensor roofline
+        args.n_in, args.n_out = 128, 128
+        wide = layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind)
+        tcgen05 = dict(wide["roofline"])
+        tcgen05.update({"kernel": "gather-GEMM tf32 (tcgen05 persistent kernel), SSC 128->128 on %d sites" % wide["sites"],
+                        "us_per_launch": wide["us_per_launch"],
+                        "peak_note": "tf32 peak taken as half the measured dense bf16 peak",
+                        # from profiles/gather_gemm_tf32_persist_ssc128_room.md
+                        "traffic": 248.4e6 if args.voxels == 250000 else None})
     hashes = hash_bench(dev, 5, 2, ("c1", "room") if args.quick else ("c1", "room", "building"))
     for h in hashes:
         h["hbm_frac"] = h["GBps"] / hbm_peak
@@ -524,7 +551,7 @@ def main():
             "sweep": sweep,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h)},
-            "gpu_launches": int(launches) * args.steps, "clocks": clocks, "roofline": roofline,
+            "gpu_launches": int(launches) * args.steps, "clocks": clocks, "roofline": roofline, "tcgen05": tcgen05,
             "hash_build": hashes}
     if world == 1 and not args.no_cpu_baseline:
         sample = min(args.voxels, 120000)

@@ -101,6 +101,14 @@ SCN_API int scn_metadata_query(scn_metadata *m, const int64_t size[3], const int
 /* ---------------------------------------------------------------------------
  * InputLayer / OutputLayer.
  * ------------------------------------------------------------------------- */
+/* What scn_input_layer_build builds beyond the input scale.  By default the library learns from use: once a
+ * network of this process has asked for a 3x3x3 neighbour map, later grids get theirs inside the build (its counts
+ * ride on the build's last host round trip), and once networks have gone down L stride-2 scales, the input layer
+ * builds those L coarse scales right away, before feature kernels are queued behind which a round trip would have
+ * to wait.  neighbour_maps: 1 always, 0 never (built on first use), -1 learn.  coarse_levels: 0..16, or -1 learn.
+ * Results never depend on these settings, only when the work is done.  No counterpart in the reference. */
+SCN_API int scn_set_build_ahead(int neighbour_maps, int coarse_levels);
+
 /* Builds the finest grid from input points.  Replaces Metadata::inputLayer ->
  * inputLayerRulesSimple (Metadata/Metadata.cpp:442-463, Metadata/IOLayersRules.h:135-203)
  * and HashInputPointClouds / InsertAndCompactPointCloud (CUDA/CUDPPWrapper.hpp:668-796).

@@ -110,6 +110,16 @@ static int need_grid(scn_metadata *m, const int64_t *size, Grid **g) {
 // the input layer builds that many coarse grids right away, while nothing else is queued on the stream: a build
 // ends with a host round trip, which in the middle of a network drains the queue of feature kernels first.
 static std::atomic<int> g_pyramid_levels{0};
+// scn_set_build_ahead overrides what was learned (-1: use what was learned)
+static std::atomic<int> g_force_ssc{-1}, g_force_levels{-1};
+static bool want_ssc() {
+  const int f = g_force_ssc.load(std::memory_order_relaxed);
+  return f >= 0 ? f != 0 : ssc_expected();
+}
+static int want_levels() {
+  const int f = g_force_levels.load(std::memory_order_relaxed);
+  return f >= 0 ? f : g_pyramid_levels.load(std::memory_order_relaxed);
+}
 
 // coarse grid of in_size -> out_size (filter 2, stride 2), built on first use
 static int need_coarse(scn_metadata *m, const int64_t *in_size, const int64_t *out_size, Grid **fine, Grid **coarse,
@@ -121,7 +131,7 @@ static int need_coarse(scn_metadata *m, const int64_t *in_size, const int64_t *o
   *coarse = m->find(out_size);
   if (!*coarse) {
     std::unique_ptr<Grid> g(new Grid());
-    SCN_TRY(grid_build_coarse(*g, **fine, ssc_expected(), s));
+    SCN_TRY(grid_build_coarse(*g, **fine, want_ssc(), s));
     if (m->has_input && out_size[0] > 0) {  // remember how deep below the input scale this is
       int level = 0;
       for (int64_t sz = m->input_size[0]; sz > out_size[0] && sz % 2 == 0; sz /= 2) ++level;
@@ -235,6 +245,14 @@ int scn_metadata_query(scn_metadata *m, const int64_t size[3], const int32_t *co
 }
 
 // ---- input / output layer ----------------------------------------------------------------------
+int scn_set_build_ahead(int neighbour_maps, int coarse_levels) {
+  if (neighbour_maps < -1 || neighbour_maps > 1 || coarse_levels < -1 || coarse_levels > 16)
+    return fail(SCN_E_INVALID, "build-ahead settings out of range");
+  g_force_ssc.store(neighbour_maps, std::memory_order_relaxed);
+  g_force_levels.store(coarse_levels, std::memory_order_relaxed);
+  return SCN_OK;
+}
+
 int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t *coords, int coords_on_host,
                           int64_t n_in, int ncols, int64_t batch_size, int mode, void *stream, int64_t *n_active) {
   if (!m || !size) return fail(SCN_E_INVALID, "null metadata or size");
@@ -252,7 +270,7 @@ int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t 
     SCN_CUDA(cudaMemcpyAsync(staged, coords, (size_t)n_in * ncols * 8, cudaMemcpyHostToDevice, s));
     dev_coords = staged;
   }
-  int r = grid_build(*g, dev_coords, ncols, nullptr, 0, n_in, true, nullptr, ssc_expected(), s);
+  int r = grid_build(*g, dev_coords, ncols, nullptr, 0, n_in, true, nullptr, want_ssc(), s);
   dev_free(staged, s);
   if (r != SCN_OK) {
     grid_free(*g, s);
@@ -266,7 +284,7 @@ int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t 
   m->batch_size = batch_size;
   // the coarse scales earlier networks went down to, now rather than in the middle of the network
   Size3 cur = m->input_size;
-  for (int level = 0; level < g_pyramid_levels.load(std::memory_order_relaxed); ++level) {
+  for (int level = 0, levels = want_levels(); level < levels; ++level) {
     if (cur[0] % 2 || cur[1] % 2 || cur[2] % 2 || cur[0] < 2 || cur[1] < 2 || cur[2] < 2) break;
     const Size3 next{{cur[0] / 2, cur[1] / 2, cur[2] / 2}};
     Grid *fine = nullptr, *coarse = nullptr;

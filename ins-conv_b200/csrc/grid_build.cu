@@ -501,6 +501,33 @@ int grid_free(Grid &g, cudaStream_t s) {
 // Bitmaps above this many bits (4 GiB of words plus 2 GiB of prefixes) are refused.
 static const unsigned long long kMaxBoxBits = 1ull << 35;
 
+// The few words a build reads back land in pinned host memory: a copy into pageable memory goes through a driver
+// staging buffer and costs several microseconds more per round trip.  One 2 KB block per host thread; when it
+// cannot be had the reads go to the caller's stack as before.
+static unsigned char *pinned_scratch() {
+  thread_local unsigned char *p = nullptr;
+  thread_local bool tried = false;
+  if (!tried) {
+    tried = true;
+    void *q = nullptr;
+    if (cudaHostAlloc(&q, 2048, cudaHostAllocDefault) == cudaSuccess) p = static_cast<unsigned char *>(q);
+    else (void)cudaGetLastError();
+  }
+  return p;
+}
+// reads `bytes` from the device into dst through the pinned block (at `slot`, 512-byte slots) and waits for the stream
+static int read_back(void *dst, const void *src, size_t bytes, int slot, cudaStream_t s, bool sync) {
+  unsigned char *pin = pinned_scratch();
+  void *land = (pin && bytes <= 512) ? pin + 512 * slot : dst;
+  SCN_CUDA(cudaMemcpyAsync(land, src, bytes, cudaMemcpyDeviceToHost, s));
+  if (sync) SCN_CUDA(cudaStreamSynchronize(s));
+  return SCN_OK;
+}
+static void take(void *dst, size_t bytes, int slot) {  // after the synchronisation that followed read_back(..., false)
+  unsigned char *pin = pinned_scratch();
+  if (pin && bytes <= 512) memcpy(dst, pin + 512 * slot, bytes);
+}
+
 static std::atomic<bool> g_ssc_seen{false};
 bool ssc_expected() { return g_ssc_seen.load(std::memory_order_relaxed); }
 
@@ -535,8 +562,8 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
       info.mx[d] = bx.o[d] + (int)bx.e[d] - 1;
     }
   } else {
-    SCN_CUDA(cudaMemcpyAsync(&info, info_d, sizeof(info), cudaMemcpyDeviceToHost, s));
-    SCN_CUDA(cudaStreamSynchronize(s));
+    SCN_TRY(read_back(&info, info_d, sizeof(info), 0, s, true));
+    take(&info, sizeof(info), 0);
     if (info.err & 1u) {
       dev_free(info_d, s);
       dev_free(keys, s);
@@ -563,8 +590,8 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
   k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap);
   SCN_LAUNCHED();
   SCN_TRY(scan_emit(PopcWords{bitmap}, StorePrefix{prefix}, nwords, &info_d->n_unique, s));
-  SCN_CUDA(cudaMemcpyAsync(&info.n_unique, &info_d->n_unique, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
-  SCN_CUDA(cudaStreamSynchronize(s));
+  SCN_TRY(read_back(&info.n_unique, &info_d->n_unique, sizeof(uint32_t), 0, s, true));
+  take(&info.n_unique, sizeof(uint32_t), 0);
   const int64_t n = info.n_unique;
   g.n = n;
   g.box = bx;
@@ -612,11 +639,12 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
     SCN_TRY(dev_alloc_t(&g.nbr, (size_t)n * 27, s));
     k_ssc_nbr<<<dim3(blocks_for(n, 256), 27), 256, 0, s>>>(g.coords, n, g.table, g.mask, nullptr, 1, g.nbr, nbr_counts_d, nullptr);
     SCN_LAUNCHED();
-    SCN_CUDA(cudaMemcpyAsync(nbr_counts, nbr_counts_d, sizeof(nbr_counts), cudaMemcpyDeviceToHost, s));
+    SCN_TRY(read_back(nbr_counts, nbr_counts_d, sizeof(nbr_counts), 1, s, false));
   }
   // the error word (table overflow) always comes back; max_active with it when duplicates exist
-  SCN_CUDA(cudaMemcpyAsync(&info, info_d, sizeof(info), cudaMemcpyDeviceToHost, s));
-  SCN_CUDA(cudaStreamSynchronize(s));
+  SCN_TRY(read_back(&info, info_d, sizeof(info), 0, s, true));
+  take(&info, sizeof(info), 0);
+  if (nbr_counts_d) take(nbr_counts, sizeof(nbr_counts), 1);
   if (need_info) g.max_active = (int32_t)info.max_active;
   if (nbr_counts_d) {
     g.nbr_total = 0;
@@ -695,9 +723,10 @@ int grid_build_coarse(Grid &g, const Grid &fine, bool with_ssc, cudaStream_t s) 
   }
   BuildInfo info;
   unsigned long long h[8 + 27];
-  SCN_CUDA(cudaMemcpyAsync(&info, info_d, sizeof(info), cudaMemcpyDeviceToHost, s));
-  SCN_CUDA(cudaMemcpyAsync(h, counts_d, sizeof(h), cudaMemcpyDeviceToHost, s));
-  SCN_CUDA(cudaStreamSynchronize(s));
+  SCN_TRY(read_back(h, counts_d, sizeof(h), 1, s, false));
+  SCN_TRY(read_back(&info, info_d, sizeof(info), 0, s, true));
+  take(&info, sizeof(info), 0);
+  take(h, sizeof(h), 1);
   dev_free(counts_d, s);
   dev_free(cnt, s);
   dev_free(prefix, s);

@@ -57,6 +57,7 @@ PROTOTYPES = {
     "scn_weights_packable": (_int, [_i64, _i64, _i64]),
     "scn_pack_weights": (_int, [_p, _i64, _i64, _i64, _p, _p]),
     "scn_ssc_forward": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
+    "scn_set_build_ahead": (_int, [_int, _int]),
     "scn_ssc_forward_add": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_conv_prepare": (_int, [_p, _i64p, _i64p, _p, _i64p]),
     "scn_conv_forward": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),

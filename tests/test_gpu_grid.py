@@ -142,3 +142,34 @@ def test_query(cuda):
     soa = torch.from_numpy(np.ascontiguousarray(q4.T.astype(np.int32))).to(cuda)
     rows = m.query(128, soa).cpu().numpy()
     np.testing.assert_array_equal(rows, g.lookup(q4))
+
+
+def test_build_ahead_changes_when_not_what(cuda):
+    # scn_set_build_ahead: coarse scales and neighbour maps built inside the input layer's call, or on first use;
+    # grids, hash tables and rulebooks are the same either way
+    c = synth.boxes_and_spheres(4)
+    d = torch.from_numpy(c).to(cuda)
+    results = []
+    try:
+        for ssc, levels in ((0, 0), (1, 3)):
+            cabi.call("scn_set_build_ahead", ssc, levels)
+            m = cabi.Metadata()
+            n = m.input_layer_build(128, d, mode=4)
+            assert (m.n_active(64) >= 0) == (levels >= 1)
+            assert (m.n_active(16) >= 0) == (levels >= 3) and m.n_active(8) < 0
+            rb = [m.ssc_rulebook(128), m.conv_rulebook(128, 64), m.ssc_rulebook(64), m.conv_rulebook(64, 32),
+                  m.conv_rulebook(32, 16)]
+            locs = [m.spatial_locations(s) for s in (128, 64, 32, 16)]
+            results.append((n, rb, locs))
+        with pytest.raises(cabi.ScnError):
+            cabi.call("scn_set_build_ahead", 2, 0)
+    finally:
+        cabi.call("scn_set_build_ahead", -1, -1)
+    (n0, rb0, l0), (n1, rb1, l1) = results
+    assert n0 == n1
+    for a, b in zip(l0, l1):
+        assert np.array_equal(a, b)
+    for a, b in zip(rb0, rb1):
+        assert len(a) == len(b)
+        for x, y in zip(a, b):
+            assert np.array_equal(x, y)
