@@ -24,6 +24,7 @@ step time is the max over ranks (weak scaling).
 `--impl reference` times the CPU restatement of the reference on the same workload instead.
 """
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -205,6 +206,21 @@ def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
 
         cabi.call("scn_set_build_ahead", 0, 0)  # the hash build alone: input scale, no neighbour map
         t, n = median_build()
+        # the 3x3x3 rulebook (27 table lookups per site) of that grid, built on first request
+        counts = np.zeros(27, dtype=np.int64)
+        rts = []
+        for i in range(warmup + steps):
+            m.input_layer_build(size, d, mode=4)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            cabi.call("scn_ssc_rulebook", m.h, cabi.size3(size), counts.ctypes.data, None,
+                      torch.cuda.current_stream().cuda_stream)
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                rts.append(e0.elapsed_time(e1) * 1e-3)
+        t_rules, pairs = sorted(rts)[len(rts) // 2], int(counts.sum())
         cabi.call("scn_set_build_ahead", 1, 6)  # what a UNet frame pays: 7 scales with their rulebook maps
         t_all, _ = median_build()
         cabi.call("scn_set_build_ahead", -1, -1)
@@ -214,7 +230,10 @@ def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
         byts = 32.0 * c4.shape[0] + 8.0 * cap + 12.0 * n + 4.0 * c4.shape[0]
         out.append({"scene": name, "points": int(c4.shape[0]), "sites": int(n), "us": t * 1e6,
                     "points_per_s": c4.shape[0] / t, "GBps": byts / t / 1e9,
-                    "us_with_6_coarse_scales_and_all_maps": t_all * 1e6})
+                    "us_with_6_coarse_scales_and_all_maps": t_all * 1e6,
+                    # algorithmic bytes of the rulebook build: coordinates in, table read once, pairs out
+                    "ssc_rulebook": {"pairs": pairs, "us": t_rules * 1e6,
+                                     "GBps": (12.0 * n + 8.0 * cap + 8.0 * pairs) / t_rules / 1e9}})
     return out
 
 
@@ -455,6 +474,23 @@ def main():
 
     ms_incre, launches_incre = timed(incre_frame, args.steps, args.warmup) if "incre" in legs else (float("nan"), 0)
 
+    def sites_per_level(c):
+        from insconv import cabi
+        m = cabi.Metadata()
+        counts = [int(m.input_layer_build(4096, c, mode=4))]
+        size = 4096
+        for _ in range(len(PLANES) - 1):
+            n_out = ctypes.c_int64(0)
+            cabi.call("scn_conv_prepare", m.h, cabi.size3(size), cabi.size3(size // 2), torch.cuda.current_stream().cuda_stream,
+                      ctypes.byref(n_out))
+            counts.append(int(n_out.value))
+            size //= 2
+        return counts
+
+    # fraction of the sites of each scale that the incremental frame computes on
+    lv_full, lv_inc = sites_per_level(d_coords), sites_per_level(d_inc_c)
+    recomputed = [round(a / max(b, 1), 4) for a, b in zip(lv_inc, lv_full)]
+
     # ---- exact incremental frame: the new points are merged into the kept scene and the merged scene is
     # recomputed (equals a full recompute; the kept scene advances each frame)
     def exact_frame():
@@ -544,7 +580,8 @@ def main():
                        "l2": "no flush: one frame streams ~1.5 GB of activations and maps, far above the 126 MB L2"},
             "incremental": {"ms_per_frame": ms_incre, "changed_points": int(inc_c.shape[0]),
                             "changed_frac": float(inc_c.shape[0]) / coords.shape[0],
-                            "semantics": "reference (insert-only, no dilation)", "launches": int(launches_incre)},
+                            "semantics": "reference (insert-only, no dilation)", "launches": int(launches_incre),
+                            "sites_per_level": lv_inc, "fraction_of_full_frame_sites_per_level": recomputed},
             "incremental_exact": {"ms_per_frame": ms_exact,
                                   "semantics": "new points merged into the kept scene, merged scene recomputed: "
                                                "equal to a full recompute, kept scene advances"},
