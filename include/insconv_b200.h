@@ -52,6 +52,9 @@ extern "C" {
 #define SCN_PREC_FP32 0      /* fp32 FFMA, fp32 accumulate (bit-for-bit deterministic)  */
 #define SCN_PREC_TF32 1      /* tf32 tensor cores (tcgen05 with TMEM accumulators, or warp-level mma.sync for narrow layers), fp32 accumulate */
 #define SCN_PREC_TF32_PACKED 2 /* as TF32, and `weight` already is the packed copy made by scn_pack_weights */
+#define SCN_PREC_F16 3       /* scn_ssc/conv/deconv_forward only: `in` points to fp16 rows [n, n_in] (in_stride in fp16
+                                elements; written by scn_bn_forward_f16) and `weight` to the fp16 copy made by
+                                scn_pack_weights_f16; fp16 x fp16 products, fp32 accumulation, fp32 `out` */
 
 /* Largest coordinate and batch index a key can hold. */
 #define SCN_MAX_COORD 65534
@@ -166,6 +169,19 @@ SCN_API int scn_conv_rulebook(scn_metadata *m, const int64_t in_size[3], const i
 SCN_API int scn_weights_packable(int64_t volume, int64_t n_in, int64_t n_out);
 SCN_API int scn_pack_weights(const float *weight, int64_t volume, int64_t n_in, int64_t n_out, float *packed,
                              void *stream);
+
+/* fp16 activations between a BatchNorm and the convolution that follows it (no counterpart in the reference, whose
+ * features are fp32 throughout).  In the narrow layers the convolution is bound by the bytes it gathers, and
+ * BatchNorm+ReLU output is well inside fp16's range; fp16 keeps 11 significant bits, one more than the tf32 the
+ * other tensor-core kernels read.  scn_bn_forward_f16 writes the normalised rows as fp16 (out: [rows, planes] fp16,
+ * out_stride in fp16 elements, planes and out_stride multiples of 8); scn_ssc/conv/deconv_forward with SCN_PREC_F16
+ * read them.  Shapes: scn_weights_packable_f16() != 0 (n_in and n_out 32 or 64); packed: volume*n_in*n_out fp16. */
+SCN_API int scn_weights_packable_f16(int64_t volume, int64_t n_in, int64_t n_out);
+SCN_API int scn_pack_weights_f16(const float *weight, int64_t volume, int64_t n_in, int64_t n_out, void *packed,
+                                 void *stream);
+SCN_API int scn_bn_forward_f16(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows,
+                               int64_t planes, const float *running_mean, const float *running_var, const float *gamma,
+                               const float *beta, double eps, double leakiness, void *stream);
 
 /* Replaces cuda_SubmanifoldConvolution_updateOutput (CUDA/Convolution.cpp:152-218).
  * in [n, n_in], out [n, n_out] over the sites of `size`. */

@@ -171,6 +171,17 @@ static int check_feat(const void *in, const void *out, const void *w, int64_t n_
   return SCN_OK;
 }
 
+// One convolution through the gather-GEMM; SCN_PREC_F16: `in` holds fp16 rows and `weight` fp16 fragments
+static int run_conv(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out,
+                    const float *weight, const float *bias, float *out, int64_t out_stride, int64_t n_in, int64_t n_planes_out,
+                    const float *init, int64_t init_stride, int precision, cudaStream_t s) {
+  if (precision == SCN_PREC_F16)
+    return gather_mma_warp_f16(in, in_stride, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
+                               init_stride, s);
+  return gather_gemm(in, in_stride, in_rows, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
+                     init_stride, precision, s);
+}
+
 }  // namespace scn
 
 using namespace scn;
@@ -377,6 +388,12 @@ int scn_weights_packable(int64_t volume, int64_t n_in, int64_t n_out) { return t
 int scn_pack_weights(const float *weight, int64_t volume, int64_t n_in, int64_t n_out, float *packed, void *stream) {
   return tc_pack_weights(weight, volume, n_in, n_out, packed, (cudaStream_t)stream);
 }
+int scn_weights_packable_f16(int64_t volume, int64_t n_in, int64_t n_out) {
+  return warp_mma_f16_shape(volume, n_in, n_out) ? 1 : 0;
+}
+int scn_pack_weights_f16(const float *weight, int64_t volume, int64_t n_in, int64_t n_out, void *packed, void *stream) {
+  return warp_mma_pack_f16(weight, volume, n_in, n_out, packed, (cudaStream_t)stream);
+}
 int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
                     int64_t out_stride, const float *weight, const float *bias, int64_t n_in, int64_t n_out,
                     int precision, void *stream, double *flops) {
@@ -387,7 +404,7 @@ int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int
   SCN_TRY(check_feat(in, out, weight, n_in, n_out));
   cudaStream_t s = (cudaStream_t)stream;
   SCN_TRY(grid_build_ssc(*g, s));
-  SCN_TRY(gather_gemm(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0, precision, s));
+  SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0, precision, s));
   if (flops) *flops = (double)g->nbr_total * (double)n_in * (double)n_out;
   return SCN_OK;
 }
@@ -402,8 +419,8 @@ int scn_ssc_forward_add(scn_metadata *m, const int64_t size[3], const float *in,
   if (!addend) return fail(SCN_E_INVALID, "null addend");
   cudaStream_t s = (cudaStream_t)stream;
   SCN_TRY(grid_build_ssc(*g, s));
-  SCN_TRY(gather_gemm(in, in_stride, g->n, g->nbr, 27, g->n, weight, nullptr, out, out_stride, n_in, n_out, addend,
-                      addend_stride, precision, s));
+  SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, nullptr, out, out_stride, n_in, n_out, addend,
+                   addend_stride, precision, s));
   if (flops) *flops = (double)g->nbr_total * (double)n_in * (double)n_out;
   return SCN_OK;
 }
@@ -423,8 +440,8 @@ int scn_conv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t ou
   if (flops) *flops = 0;
   if (coarse->n == 0) return SCN_OK;
   SCN_TRY(check_feat(in, out, weight, n_in, n_out));
-  SCN_TRY(gather_gemm(in, in_stride, fine->n, coarse->child, 8, coarse->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
-                      precision, s));
+  SCN_TRY(run_conv(in, in_stride, fine->n, coarse->child, 8, coarse->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
+                   precision, s));
   if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
   return SCN_OK;
 }
@@ -437,10 +454,18 @@ int scn_deconv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t 
   if (flops) *flops = 0;
   if (fine->n == 0) return SCN_OK;
   SCN_TRY(check_feat(in, out, weight, n_in, n_out));
-  SCN_TRY(gather_gemm(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
-                      precision, s));
+  SCN_TRY(run_conv(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
+                   precision, s));
   if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
   return SCN_OK;
+}
+int scn_bn_forward_f16(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows, int64_t planes,
+                       const float *running_mean, const float *running_var, const float *gamma, const float *beta,
+                       double eps, double leakiness, void *stream) {
+  if (rows < 0 || planes < 0) return fail(SCN_E_INVALID, "negative size");
+  if (rows && planes && (!in || !out || !running_mean || !running_var)) return fail(SCN_E_INVALID, "null pointer");
+  return bn_forward_f16out(in, in_stride, out, out_stride, rows, planes, running_mean, running_var, gamma, beta, (float)eps,
+                           (float)leakiness, (cudaStream_t)stream);
 }
 int scn_bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,
                    const float *running_mean, const float *running_var, const float *gamma, const float *beta,

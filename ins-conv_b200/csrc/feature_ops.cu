@@ -16,6 +16,7 @@
 //   Input / Output layer    CUDA/IOLayers.cu:18-62, incremental :82-142
 //   NetworkInNetwork        CUDA/NetworkInNetwork.cpp:9-25
 #include "internal.h"
+#include <cuda_fp16.h>
 
 namespace scn {
 
@@ -239,6 +240,55 @@ __global__ void k_bn(const float *__restrict__ in, long long in_stride, float *_
       out[row * out_stride + c] = y;
     }
   }
+}
+
+// The same BatchNorm + leaky ReLU with the result rounded to fp16: the 16-bit rows are what the fp16 gather-GEMM
+// of the following convolution reads (half the bytes per gathered row).  Eight planes per thread.
+__global__ void k_bn_f16out(const float *__restrict__ in, long long in_stride, __half *__restrict__ out, long long out_stride,
+                            long long rows, int C, const float *__restrict__ mean, const float *__restrict__ var,
+                            const float *__restrict__ gamma, const float *__restrict__ beta, float eps, float leak) {
+  extern __shared__ float sm[];  // scale[C], shift[C]
+  float *sw = sm, *sb = sm + C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    const float w = (1.0f / sqrtf(var[c] + eps)) * (gamma ? gamma[c] : 1.f);
+    sw[c] = w;
+    sb[c] = (beta ? beta[c] : 0.f) - mean[c] * w;
+  }
+  __syncthreads();
+  const int cv = C / 8;
+  const long long total = rows * cv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / cv;
+    const int c = (int)(i % cv) * 8;
+    const float4 x0 = *reinterpret_cast<const float4 *>(in + row * in_stride + c);
+    const float4 x1 = *reinterpret_cast<const float4 *>(in + row * in_stride + c + 4);
+    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    __align__(16) __half2 y[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = leaky(sw[c + 2 * j] * xs[2 * j] + sb[c + 2 * j], leak);
+      const float b = leaky(sw[c + 2 * j + 1] * xs[2 * j + 1] + sb[c + 2 * j + 1], leak);
+      y[j] = __floats2half2_rn(a, b);
+    }
+    *reinterpret_cast<uint4 *>(out + row * out_stride + c) = *reinterpret_cast<const uint4 *>(y);
+  }
+}
+
+int bn_forward_f16out(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows, int64_t planes,
+                      const float *mean, const float *var, const float *gamma, const float *beta, float eps, float leak,
+                      cudaStream_t s) {
+  if (rows == 0 || planes == 0) return SCN_OK;
+  if (planes > 4096) return fail(SCN_E_INVALID, "BatchNorm over more than 4096 planes");
+  if (planes % 8 != 0 || in_stride % 4 != 0 || out_stride % 8 != 0 || !aligned16(in) || !aligned16(out))
+    return fail(SCN_E_INVALID, "fp16 BatchNorm output needs planes and the output stride to be multiples of 8 and 16-byte aligned rows");
+  const long long work = rows * (planes / 8);
+  unsigned blocks = blocks_for(work, 256);
+  if (blocks > 148u * 16u) blocks = 148u * 16u;
+  k_bn_f16out<<<blocks, 256, (size_t)planes * 2 * sizeof(float), s>>>(in, in_stride, static_cast<__half *>(out), out_stride, rows,
+                                                                      (int)planes, mean, var, gamma, beta, eps, leak);
+  SCN_LAUNCHED();
+  return SCN_OK;
 }
 
 int bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,

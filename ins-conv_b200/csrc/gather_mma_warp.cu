@@ -24,6 +24,7 @@
 // One tile per warp; the weight fragments are read through L1 (a variant that kept them in shared memory, one
 // persistent CTA per SM, measured the same: both go through the same L1 data pipe, which is the busiest unit).
 #include "internal.h"
+#include <cuda_fp16.h>
 #include <stdlib.h>
 
 namespace scn {
@@ -229,6 +230,130 @@ k_gather_mma_tf32(const float *__restrict__ in, long long in_stride, const int32
   warp_tile<CIN, COUT, NTR>(row0, mp, mask, in, in_stride, n_out, Wp + lane, bias, out, out_stride, init, init_stride, lane);
 }
 
+// ---------------------------------------------------------------------------------------------
+// fp16 form: the gathered rows are fp16 (written by the BatchNorm in front of the convolution), the weights are
+// packed as fp16 fragments, mma.sync.m16n8k16, fp32 accumulation.  Same structure as above with half of
+// everything per unit: a 32-plane row is 64 bytes = ONE 16-byte load per lane of the quad, which feeds two K = 16
+// MMAs; lane (g, t) holds planes 8t..8t+7 of row g, the k-slots (2t, 2t+1) and (2t+8, 2t+9) of the two MMAs are
+// planes 8t+4j+{0,1} and 8t+4j+{2,3} (j = 0, 1).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_m16n8k16_f16(float (&d)[4], const uint4 &a, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+}
+
+template <int CIN, int NTR> struct FragH {
+  uint4 v[NTR][CIN / 32];
+};
+
+template <int CIN, int NTR>
+__device__ __forceinline__ void load_rows_h(FragH<CIN, NTR> &f, const int *mp_k, const __half *__restrict__ in_t, long long in_stride,
+                                            int g) {
+#pragma unroll
+  for (int n = 0; n < NTR; ++n) {
+    const int s = mp_k[n * 8 + g];
+    const uint4 *p = reinterpret_cast<const uint4 *>(in_t + (long long)s * in_stride);
+#pragma unroll
+    for (int c = 0; c < CIN / 32; ++c) {
+      f.v[n][c] = make_uint4(0u, 0u, 0u, 0u);
+      if (s >= 0) f.v[n][c] = __ldg(p + 4 * c);
+    }
+  }
+}
+
+template <int CIN, int COUT, int NTR>
+__device__ __forceinline__ void mma_rows_h(float (&acc)[COUT / 16][NTR][4], const FragH<CIN, NTR> &f, const uint4 *__restrict__ wk) {
+  constexpr int MTC = COUT / 16;
+#pragma unroll
+  for (int c = 0; c < CIN / 32; ++c) {
+    uint4 a[MTC][2];
+#pragma unroll
+    for (int m = 0; m < MTC; ++m) {
+      a[m][0] = __ldg(wk + ((c * MTC + m) * 2) * 32);
+      a[m][1] = __ldg(wk + ((c * MTC + m) * 2 + 1) * 32);
+    }
+#pragma unroll
+    for (int m = 0; m < MTC; ++m)
+#pragma unroll
+      for (int n = 0; n < NTR; ++n) mma_m16n8k16_f16(acc[m][n], a[m][0], f.v[n][c].x, f.v[n][c].y);
+#pragma unroll
+    for (int m = 0; m < MTC; ++m)
+#pragma unroll
+      for (int n = 0; n < NTR; ++n) mma_m16n8k16_f16(acc[m][n], a[m][1], f.v[n][c].z, f.v[n][c].w);
+  }
+}
+
+template <int CIN, int COUT, int NTR, int MINB>
+__global__ void __launch_bounds__(kWarps * 32, MINB)
+k_gather_mma_f16(const __half *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
+                 const uint4 *__restrict__ Wp, const float *__restrict__ bias, float *out, long long out_stride,
+                 const float *init, long long init_stride) {
+  constexpr int ROWS = 8 * NTR, MTC = COUT / 16;
+  __shared__ int s_map[kWarps][kMaxK * ROWS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const long long row0 = ((long long)blockIdx.x * kWarps + warp) * ROWS;
+  if (row0 >= n_out) return;
+  int *mp = s_map[warp];
+  MapRegs<ROWS> regs;
+  load_map<ROWS>(regs, row0, map, K, n_out, lane);
+  unsigned int mask = publish_map<ROWS>(regs, mp, K, lane);
+  float acc[MTC][NTR][4];
+#pragma unroll
+  for (int m = 0; m < MTC; ++m)
+#pragma unroll
+    for (int n = 0; n < NTR; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
+  constexpr int WK = (CIN / 32) * MTC * 2 * 32;  // uint4 per offset
+  const __half *in_t = in + 8 * t;
+  const uint4 *wl = Wp + lane;
+  if (mask) {
+    FragH<CIN, NTR> f0, f1;
+    int k0 = __ffs(mask) - 1;
+    mask &= mask - 1;
+    load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
+    while (true) {
+      int k1 = -1;
+      if (mask) {
+        k1 = __ffs(mask) - 1;
+        mask &= mask - 1;
+        load_rows_h<CIN, NTR>(f1, mp + k1 * ROWS, in_t, in_stride, g);
+      }
+      mma_rows_h<CIN, COUT, NTR>(acc, f0, wl + k0 * WK);
+      if (k1 < 0) break;
+      k0 = -1;
+      if (mask) {
+        k0 = __ffs(mask) - 1;
+        mask &= mask - 1;
+        load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
+      }
+      mma_rows_h<CIN, COUT, NTR>(acc, f1, wl + k1 * WK);
+      if (k0 < 0) break;
+    }
+  }
+  store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, init, init_stride, g, t);
+}
+
+// W [K][n_in][n_out] fp32 -> fp16 fragments [K][n_in/32][n_out/16][2][lane][8]: half e of (k, c, m, j, lane = 4g + t)
+// is W[k][32c + 8t + 4j + 2(e >> 2) + (e & 1)][16m + g + 8((e >> 1) & 1)]
+__global__ void k_pack_weights_f16(const float *__restrict__ W, __half *__restrict__ Wp, int Cin, int Cout, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int MTC = Cout / 16, C32 = Cin / 32;
+  const int e = (int)(i & 7), lane = (int)((i >> 3) & 31), j = (int)((i >> 8) & 1);
+  long long rest = i >> 9;
+  const int m = (int)(rest % MTC);
+  rest /= MTC;
+  const int c = (int)(rest % C32);
+  const long long k = rest / C32;
+  const int g = lane >> 2, t = lane & 3;
+  const int r = e >> 1, h = e & 1;  // register a0..a3 of the fragment, half inside it
+  const int ci = 32 * c + 8 * t + 4 * j + 2 * (r >> 1) + h, co = 16 * m + g + 8 * (r & 1);
+  Wp[i] = __float2half_rn(W[(k * Cin + ci) * Cout + co]);
+}
+
 // Layers with 1 to 4 input planes (the first layer of a network: colours, a constant one): the planes of a
 // row fill k-slots 0..3 of one MMA, the other slots are zero, so an offset costs n_out / 16 MMAs per 8 rows and
 // a 4-byte load per row.  The weights are read as they are (no packing), the hardware ignores their low
@@ -383,6 +508,44 @@ int gather_mma_warp(const float *in, int64_t in_stride, const int32_t *map, int 
   dev_free(own, s);
   SCN_LAUNCHED();
   *handled = true;
+  return SCN_OK;
+}
+
+static bool f16_shape(int64_t K, int64_t Cin, int64_t Cout) {
+  return K >= 1 && K <= kMaxK && (Cin == 32 || Cin == 64) && (Cout == 32 || Cout == 64);
+}
+bool warp_mma_f16_shape(int64_t K, int64_t Cin, int64_t Cout) { return f16_shape(K, Cin, Cout); }
+
+int warp_mma_pack_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s) {
+  if (!f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "shape cannot be packed for the fp16 kernel (planes 32 or 64)");
+  if (!W || !packed) return fail(SCN_E_INVALID, "null pointer");
+  const long long total = K * Cin * Cout;
+  k_pack_weights_f16<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(W, static_cast<__half *>(packed), (int)Cin, (int)Cout, total);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+int gather_mma_warp_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
+                        const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
+                        int64_t init_stride, cudaStream_t s) {
+  if (!f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "the fp16 gather-GEMM takes 32 or 64 planes on either side");
+  if (!map && K != 1) return fail(SCN_E_INVALID, "no map given for a filter volume above 1");
+  if (in_stride % 8 != 0 || !aligned16(in) || !aligned16(Wp))
+    return fail(SCN_E_INVALID, "fp16 rows must be 16-byte aligned with a stride that is a multiple of 8 elements");
+  const __half *inh = static_cast<const __half *>(in);
+  const uint4 *W4 = static_cast<const uint4 *>(Wp);
+#define SCN_F16_LAUNCH(CI, CO, NTR, MINB)                                                                         \
+  do {                                                                                                            \
+    const long long tiles = (n_out + 8 * NTR - 1) / (8 * NTR);                                                    \
+    k_gather_mma_f16<CI, CO, NTR, MINB><<<(unsigned)((tiles + kWarps - 1) / kWarps), kWarps * 32, 0, s>>>(        \
+        inh, in_stride, map, K, n_out, W4, bias, out, out_stride, init, init_stride);                             \
+  } while (0)
+  if (Cin == 32 && Cout == 32) SCN_F16_LAUNCH(32, 32, 4, 5);
+  else if (Cin == 32 && Cout == 64) SCN_F16_LAUNCH(32, 64, 4, 4);
+  else if (Cin == 64 && Cout == 32) SCN_F16_LAUNCH(64, 32, 4, 4);
+  else SCN_F16_LAUNCH(64, 64, 2, 4);
+#undef SCN_F16_LAUNCH
+  SCN_LAUNCHED();
   return SCN_OK;
 }
 

@@ -147,6 +147,17 @@ int bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_strid
                const float *mean, const float *var, const float *gamma, const float *beta, float eps,
                float leak, const int32_t *pre_exist, const float *pre_out, const float *pre_in,
                cudaStream_t s);
+// BatchNorm + leaky ReLU (running statistics) with the result stored as fp16 rows (out: __half [rows, planes],
+// out_stride in fp16 elements)
+int bn_forward_f16out(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows, int64_t planes,
+                      const float *mean, const float *var, const float *gamma, const float *beta, float eps, float leak,
+                      cudaStream_t s);
+// fp16 form of the warp-level gather-GEMM: in = __half rows, weights packed by warp_mma_pack_f16 (fp16 fragments)
+bool warp_mma_f16_shape(int64_t K, int64_t Cin, int64_t Cout);
+int warp_mma_pack_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
+int gather_mma_warp_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
+                        const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
+                        int64_t init_stride, cudaStream_t s);
 int bn_forward_train(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,
                      float *running_mean, float *running_var, float *save_mean, float *save_invstd, const float *gamma,
                      const float *beta, float eps, float momentum, float leak, cudaStream_t s);

@@ -18,6 +18,7 @@ HEADER_PATH = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "include", "
 PREC_FP32 = 0
 PREC_TF32 = 1
 PREC_TF32_PACKED = 2
+PREC_F16 = 3
 
 
 class ScnError(RuntimeError):
@@ -58,6 +59,9 @@ PROTOTYPES = {
     "scn_pack_weights": (_int, [_p, _i64, _i64, _i64, _p, _p]),
     "scn_ssc_forward": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_set_build_ahead": (_int, [_int, _int]),
+    "scn_weights_packable_f16": (_int, [_i64, _i64, _i64]),
+    "scn_pack_weights_f16": (_int, [_p, _i64, _i64, _i64, _p, _p]),
+    "scn_bn_forward_f16": (_int, [_p, _i64, _p, _i64, _i64, _i64, _p, _p, _p, _p, _dbl, _dbl, _p]),
     "scn_ssc_forward_add": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_conv_prepare": (_int, [_p, _i64p, _i64p, _p, _i64p]),
     "scn_conv_forward": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),

@@ -177,6 +177,68 @@ def test_ssc_forward_add(cuda, n_in, n_out, prec):
     assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
 
 
+@pytest.mark.parametrize("n_in,n_out", [(32, 32), (32, 64), (64, 32), (64, 64)])
+def test_f16_activations_bn_then_convolutions(cuda, n_in, n_out):
+    # BatchNorm+ReLU writing fp16 rows, then SSC / stride-2 convolution / deconvolution reading them (warp-level fp16
+    # kernel), against the oracle's fp32 result of the same two layers
+    import ctypes as C
+    m, g = _scene(cuda, 1)
+    rng = np.random.RandomState(n_in * 7 + n_out)
+    stream = torch.cuda.current_stream().cuda_stream
+    t = lambda a: torch.from_numpy(a).to(cuda)
+
+    def bn_f16(x, planes):
+        mean, var = rng.randn(planes).astype(np.float32), rng.uniform(0.5, 2, planes).astype(np.float32)
+        gamma, beta = rng.randn(planes).astype(np.float32), rng.randn(planes).astype(np.float32)
+        want = torch.as_tensor(O.bn_forward(x, mean, var, gamma, beta, 1e-4, 0.0)).numpy()
+        xd, dm, dv, dg, db = t(x), t(mean), t(var), t(gamma), t(beta)  # kept alive until the kernel has run
+        out = torch.empty(x.shape[0], planes, dtype=torch.float16, device=cuda)
+        cabi.call("scn_bn_forward_f16", cabi.ptr(xd), planes, cabi.ptr(out), planes, x.shape[0], planes, cabi.ptr(dm),
+                  cabi.ptr(dv), cabi.ptr(dg), cabi.ptr(db), 1e-4, 0.0, stream)
+        torch.cuda.synchronize()
+        assert float(np.abs(out.float().cpu().numpy() - want).max()) <= 1e-3 * float(np.abs(want).max())
+        return out, want
+
+    def packed(w):
+        p = torch.empty(w.size, dtype=torch.float16, device=cuda)
+        dw = t(w)
+        cabi.call("scn_pack_weights_f16", cabi.ptr(dw), w.shape[0], w.shape[1], w.shape[2], cabi.ptr(p), stream)
+        torch.cuda.synchronize()
+        return p
+
+    assert cabi.lib().scn_weights_packable_f16(27, n_in, n_out) == 1 and cabi.lib().scn_weights_packable_f16(27, 96, 96) == 0
+    fl = C.c_double(0)
+    # submanifold convolution
+    h, ref = bn_f16(rng.randn(g.n, n_in).astype(np.float32), n_in)
+    w = synth.kaiming_uniform(rng, 27, n_in, n_out)
+    out = torch.empty(g.n, n_out, dtype=torch.float32, device=cuda)
+    pw = packed(w)
+    cabi.call("scn_ssc_forward", m.h, cabi.size3(128), cabi.ptr(h), n_in, cabi.ptr(out), n_out, cabi.ptr(pw), None, n_in,
+              n_out, cabi.PREC_F16, stream, C.byref(fl))
+    torch.cuda.synchronize()
+    want = torch.as_tensor(O.conv_forward(ref, w, O.ssc_rules(g), g.n, None))
+    close(out, want, TF32_TOL)
+    assert float((out.cpu() - want).abs().max()) / float(want.abs().max()) < 3e-3
+    # stride-2 convolution and deconvolution
+    coarse, rules = O.conv2_rules(g)
+    w8 = synth.kaiming_uniform(rng, 8, n_in, n_out)
+    pw8 = packed(w8)
+    n_cc = C.c_int64(0)
+    cabi.call("scn_conv_prepare", m.h, cabi.size3(128), cabi.size3(64), stream, C.byref(n_cc))
+    n_c = int(n_cc.value)
+    assert n_c == coarse.n
+    out = torch.empty(n_c, n_out, dtype=torch.float32, device=cuda)
+    cabi.call("scn_conv_forward", m.h, cabi.size3(128), cabi.size3(64), cabi.ptr(h), n_in, cabi.ptr(out), n_out,
+              cabi.ptr(pw8), None, n_in, n_out, cabi.PREC_F16, stream, C.byref(fl))
+    close(out, O.conv_forward(ref, w8, rules, coarse.n, None), TF32_TOL)
+    hc, refc = bn_f16(rng.randn(coarse.n, n_in).astype(np.float32), n_in)
+    out = torch.empty(g.n, n_out, dtype=torch.float32, device=cuda)
+    cabi.call("scn_deconv_forward", m.h, cabi.size3(64), cabi.size3(128), cabi.ptr(hc), n_in, cabi.ptr(out), n_out,
+              cabi.ptr(pw8), None, n_in, n_out, cabi.PREC_F16, stream, C.byref(fl))
+    close(out, O.conv_forward(refc, w8, rules, g.n, None, reverse=True), TF32_TOL)
+    cabi.check_errors()
+
+
 def test_conv_deconv_nin_tf32(cuda):
     m, g = _scene(cuda, 1)
     rng = np.random.RandomState(17)
