@@ -137,7 +137,8 @@ def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
     SSC layer' figure in isolation.  L2 is flushed between launches; each launch is timed with CUDA events."""
     import torch
     from insconv import cabi
-    prec = cabi.PREC_TF32 if args.precision == "tf32" else cabi.PREC_FP32
+    half = args.precision == "fp16" and args.n_in in (32, 64) and args.n_out in (32, 64)
+    prec = cabi.PREC_FP32 if args.precision == "fp32" else cabi.PREC_TF32
     coords, _, _, _ = make_scene(0, args.voxels)
     m = cabi.Metadata()
     n = m.input_layer_build(4096, torch.from_numpy(coords).to(dev), mode=4)
@@ -145,13 +146,29 @@ def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
     x = torch.randn(n, args.n_in, generator=g).to(dev)
     w = (torch.randn(27, args.n_in, args.n_out, generator=g) * (2.0 / (27 * args.n_in)) ** 0.5).to(dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    out, madds = m.ssc_forward(4096, x, w, None, prec)
+    if half:  # fp16 rows (as a BatchNorm in front of the layer writes them) and the fp16 weight pack
+        import ctypes
+        x = x.half()
+        wp = torch.empty(w.numel(), dtype=torch.float16, device=dev)
+        stream = torch.cuda.current_stream().cuda_stream
+        cabi.call("scn_pack_weights_f16", cabi.ptr(w), 27, args.n_in, args.n_out, cabi.ptr(wp), stream)
+        out = torch.empty(n, args.n_out, dtype=torch.float32, device=dev)
+        fl = ctypes.c_double(0)
+
+        def run():
+            cabi.call("scn_ssc_forward", m.h, cabi.size3(4096), cabi.ptr(x), args.n_in, cabi.ptr(out), args.n_out, cabi.ptr(wp),
+                      None, args.n_in, args.n_out, cabi.PREC_F16, stream, ctypes.byref(fl))
+            return out, fl.value
+    else:
+        def run():
+            return m.ssc_forward(4096, x, w, None, prec)
+    out, madds = run()
     times = []
     for i in range(args.warmup + args.steps):
         flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        out, madds = m.ssc_forward(4096, x, w, None, prec)
+        out, madds = run()
         e1.record()
         torch.cuda.synchronize()
         if i >= args.warmup:
@@ -159,7 +176,8 @@ def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
     cabi.check_errors()
     t = sum(times) / len(times)
     pairs = madds / (args.n_in * args.n_out)
-    byts = 4.0 * n * (args.n_in + args.n_out) + 8.0 * pairs + 4.0 * 27 * args.n_in * args.n_out
+    s_in = 2.0 if half else 4.0  # bytes per input feature and per weight
+    byts = s_in * n * args.n_in + 4.0 * n * args.n_out + 8.0 * pairs + s_in * 27 * args.n_in * args.n_out
     flops = 2.0 * madds
     hbm_bound = args.n_in <= 64
     return {"sites": int(n), "n_in": args.n_in, "n_out": args.n_out, "pairs": int(pairs), "us_per_launch": t * 1e6,
@@ -350,7 +368,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--voxels", type=int, default=250000)
-    ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "tf32"), choices=["fp32", "tf32"])
+    ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "tf32"), choices=["fp32", "tf32", "fp16"])
     ap.add_argument("--quick", action="store_true", help="skip the 4M-point hash build (profiling aid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--legs", default="full,incre,sweep,e2e", help="which timed legs to run (profiling aid)")
@@ -552,7 +570,7 @@ def main():
     roofline = dict(lay["roofline"])
     roofline.update({"kernel": "gather-GEMM %s (%s), SSC 32->32 on %d sites (level 0 of the UNet: 9 of the 53 SSC "
                                "layers, 78 %% of the frame's voxel-layers)"
-                               % (args.precision, "warp-level mma.sync kernel" if args.precision == "tf32" else "FFMA kernel",
+                               % (args.precision, "FFMA kernel" if args.precision == "fp32" else "warp-level mma.sync kernel",
                                   lay["sites"]),
                      "us_per_launch": lay["us_per_launch"], "voxels_per_s": lay["voxels_per_s"],
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
@@ -560,7 +578,7 @@ def main():
                      "traffic": 67.5e6 if args.precision == "tf32" and args.voxels == 250000 else None,
                      "l2": "flushed between launches (256 MB write)"})
     tcgen05 = None
-    if args.precision == "tf32":  # the tcgen05 kernel on a wide layer, against the tensor roofline
+    if args.precision != "fp32":  # the tcgen05 kernel on a wide layer, against the tensor roofline
         args.n_in, args.n_out = 128, 128
         wide = layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind)
         tcgen05 = dict(wide["roofline"])
@@ -574,7 +592,7 @@ def main():
         h["hbm_frac"] = h["GBps"] / hbm_peak
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_full, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32" if args.precision == "fp32" else "tf32", "data": "synthetic",
+            "vs_baseline": None, "dtype": {"fp32": "f32", "tf32": "tf32", "fp16": "f16 rows into the 32/64-plane layers, tf32 elsewhere"}[args.precision], "data": "synthetic",
             "config": {"workload": WORKLOAD, "voxels_per_scene": int(coords.shape[0]), "scenes": world,
                        "voxel_layers_per_scene": voxel_layers, "precision": args.precision,
                        "l2": "no flush: one frame streams ~1.5 GB of activations and maps, far above the 126 MB L2"},

@@ -34,6 +34,21 @@ void need_cuda_f32(const at::Tensor &t, const char *name) {
   TORCH_CHECK(t.scalar_type() == at::kFloat, name, " must be float32");
 }
 
+// Feature rows handed to a convolution: fp32, or fp16 as written by a BatchNorm in front of it ('fp16' precision).
+// With fp16 rows the caller must hand in the matching fp16 weight pack (pack_weights_f16).
+struct FeatArg {
+  at::Tensor t;
+  const float *ptr;
+  bool half;
+  FeatArg(const at::Tensor &x, const char *name) {
+    TORCH_CHECK(x.is_cuda(), name, " must be a CUDA tensor (this build has no CPU path)");
+    half = x.scalar_type() == at::kHalf;
+    TORCH_CHECK(half || x.scalar_type() == at::kFloat, name, " must be float32 (or float16 rows from a BatchNorm)");
+    t = x.contiguous();
+    ptr = half ? reinterpret_cast<const float *>(t.data_ptr<at::Half>()) : t.data_ptr<float>();
+  }
+};
+
 struct Size3 {
   int64_t v[3];
   explicit Size3(const at::Tensor &t) {
@@ -65,7 +80,14 @@ void expect_filter(const at::Tensor &filt, int64_t want, const char *what) {
 struct WeightArg {
   const float *ptr;
   int precision;
-  WeightArg(const at::Tensor &w, const at::Tensor &packed) {
+  WeightArg(const at::Tensor &w, const at::Tensor &packed, bool half_rows = false) {
+    if (half_rows) {
+      TORCH_CHECK(packed.defined() && packed.is_cuda() && packed.scalar_type() == at::kHalf && packed.numel() == w.numel(),
+                  "float16 feature rows need the float16 weight pack of this layer (pack_weights_f16)");
+      ptr = reinterpret_cast<const float *>(packed.data_ptr<at::Half>());
+      precision = SCN_PREC_F16;
+      return;
+    }
     if (g_precision == SCN_PREC_TF32 && packed.defined() && packed.numel() == w.numel() && packed.numel() > 0 &&
         packed.is_cuda() && packed.scalar_type() == at::kFloat) {
       ptr = packed.data_ptr<float>();
@@ -123,33 +145,33 @@ class Metadata3 {
 double SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filterSize, Metadata3 &m,
                                            at::Tensor input_features, at::Tensor output_features, at::Tensor weight,
                                            at::Tensor bias, int dilated_rate, at::Tensor packed, at::Tensor addend) {
-  need_cuda_f32(input_features, "input_features");
+  FeatArg fa(input_features, "input_features");
   need_cuda_f32(weight, "weight");
   TORCH_CHECK(dilated_rate == 1, "dilated submanifold convolutions are outside the hot path");
   TORCH_CHECK(weight.dim() == 3 && weight.size(0) == 27, "weight must be [27, nIn, nOut]");
   expect_filter(filterSize, 3, "SubmanifoldConvolution");
   c10::cuda::CUDAGuard guard(input_features.device());
   Size3 s(inputSize);
-  auto in = input_features.contiguous();
+  const at::Tensor &in = fa.t;
   auto w = weight.contiguous();
   const int64_t n = scn_metadata_n_active(m.h(), s.v);
   TORCH_CHECK(n >= 0, "Metadata has no grid at this spatial size");
   TORCH_CHECK(in.size(0) == n && in.size(1) == w.size(1), "input_features must be [nActive, nIn]");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
-  WeightArg wa(w, packed);
+  WeightArg wa(w, packed, fa.half);
   if (addend.defined() && addend.numel() > 0) {  // out = addend + convolution: the residual sum formed in the epilogue
     need_cuda_f32(addend, "addend");
     TORCH_CHECK(!bias.defined() || bias.numel() == 0, "the fused residual sum takes no bias");
     TORCH_CHECK(addend.dim() == 2 && addend.size(0) == n && addend.size(1) == w.size(2) && addend.stride(1) == 1,
                 "addend must be [nActive, nOut] with unit plane stride");
-    check(scn_ssc_forward_add(m.h(), s.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(), w.size(2),
+    check(scn_ssc_forward_add(m.h(), s.v, fa.ptr, in.size(1), output_features.data_ptr<float>(), w.size(2),
                               wa.ptr, addend.data_ptr<float>(), addend.stride(0), w.size(1), w.size(2), wa.precision,
                               stream_of(in), &flops),
           "SubmanifoldConvolution_updateOutput");
     return flops;
   }
-  check(scn_ssc_forward(m.h(), s.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(), w.size(2),
+  check(scn_ssc_forward(m.h(), s.v, fa.ptr, in.size(1), output_features.data_ptr<float>(), w.size(2),
                         wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision, stream_of(in), &flops),
         "SubmanifoldConvolution_updateOutput");
   return flops;
@@ -158,21 +180,21 @@ double SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filt
 double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
                                 at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
                                 at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed) {
-  need_cuda_f32(input_features, "input_features");
+  FeatArg fa(input_features, "input_features");
   need_cuda_f32(weight, "weight");
   expect_filter(filterSize, 2, "Convolution");
   expect_filter(filterStride, 2, "Convolution");
   TORCH_CHECK(weight.dim() == 3 && weight.size(0) == 8, "weight must be [8, nIn, nOut]");
   c10::cuda::CUDAGuard guard(input_features.device());
   Size3 si(inputSize), so(outputSize);
-  auto in = input_features.contiguous();
+  const at::Tensor &in = fa.t;
   auto w = weight.contiguous();
   int64_t n = 0;
   check(scn_conv_prepare(m.h(), si.v, so.v, stream_of(in), &n), "Convolution_updateOutput");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
-  WeightArg wa(w, packed);
-  check(scn_conv_forward(m.h(), si.v, so.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(),
+  WeightArg wa(w, packed, fa.half);
+  check(scn_conv_forward(m.h(), si.v, so.v, fa.ptr, in.size(1), output_features.data_ptr<float>(),
                          w.size(2), wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision,
                          stream_of(in), &flops),
         "Convolution_updateOutput");
@@ -182,20 +204,20 @@ double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at:
 double Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
                                   at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
                                   at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed) {
-  need_cuda_f32(input_features, "input_features");
+  FeatArg fa(input_features, "input_features");
   need_cuda_f32(weight, "weight");
   expect_filter(filterSize, 2, "Deconvolution");
   expect_filter(filterStride, 2, "Deconvolution");
   c10::cuda::CUDAGuard guard(input_features.device());
   Size3 si(inputSize), so(outputSize);
-  auto in = input_features.contiguous();
+  const at::Tensor &in = fa.t;
   auto w = weight.contiguous();
   const int64_t n = scn_metadata_n_active(m.h(), so.v);
   TORCH_CHECK(n >= 0, "Deconvolution: Metadata has no grid at the output spatial size");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
-  WeightArg wa(w, packed);
-  check(scn_deconv_forward(m.h(), si.v, so.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<float>(),
+  WeightArg wa(w, packed, fa.half);
+  check(scn_deconv_forward(m.h(), si.v, so.v, fa.ptr, in.size(1), output_features.data_ptr<float>(),
                            w.size(2), wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision,
                            stream_of(in), &flops),
         "Deconvolution_updateOutput");
@@ -209,6 +231,16 @@ void BatchNormalization_updateOutput(at::Tensor input_features, at::Tensor outpu
   need_cuda_f32(input_features, "input_features");
   c10::cuda::CUDAGuard guard(input_features.device());
   auto in = input_features.contiguous();
+  if (output_features.scalar_type() == at::kHalf) {  // fp16 rows for the convolution that follows ('fp16' precision)
+    TORCH_CHECK(!train, "float16 BatchNorm output is for inference with running statistics");
+    output_features.resize_(in.sizes());
+    if (in.numel() == 0) return;
+    check(scn_bn_forward_f16(in.data_ptr<float>(), in.size(1), output_features.data_ptr<at::Half>(), in.size(1), in.size(0),
+                             in.size(1), runningMean.data_ptr<float>(), runningVar.data_ptr<float>(), opt_ptr(weight),
+                             opt_ptr(bias), eps, leakiness, stream_of(in)),
+          "BatchNormalization_updateOutput");
+    return;
+  }
   output_features.resize_as_(in);
   if (in.numel() == 0) return;
   if (train) {  // batch statistics, running statistics updated in place (what demo.py exercises on its first frame)
@@ -408,12 +440,29 @@ at::Tensor pack_weights(at::Tensor weight) {
   return packed;
 }
 
+// fp16 fragments for the convolutions that read fp16 rows (empty when the shape has no fp16 kernel)
+at::Tensor pack_weights_f16(at::Tensor weight) {
+  need_cuda_f32(weight, "weight");
+  auto w = weight.contiguous();
+  const int64_t vol = w.dim() == 3 ? w.size(0) : 1, n_in = w.size(w.dim() - 2), n_out = w.size(w.dim() - 1);
+  if (!scn_weights_packable_f16(vol, n_in, n_out)) return at::empty({0}, w.options().dtype(at::kHalf));
+  c10::cuda::CUDAGuard guard(w.device());
+  auto packed = at::empty(w.sizes(), w.options().dtype(at::kHalf));
+  check(scn_pack_weights_f16(w.data_ptr<float>(), vol, n_in, n_out, packed.data_ptr<at::Half>(), stream_of(w)),
+        "pack_weights_f16");
+  return packed;
+}
+
+// 'fp16' = tf32 kernels, plus fp16 rows between a BatchNorm and a narrow convolution behind it (the Python
+// containers arrange that); the extension itself treats it as tf32.
+bool g_half_rows = false;
 void set_precision(const std::string &p) {
   if (p == "fp32") g_precision = SCN_PREC_FP32;
-  else if (p == "tf32") g_precision = SCN_PREC_TF32;
-  else throw std::runtime_error("precision must be 'fp32' or 'tf32'");
+  else if (p == "tf32" || p == "fp16") g_precision = SCN_PREC_TF32;
+  else throw std::runtime_error("precision must be 'fp32', 'tf32' or 'fp16'");
+  g_half_rows = p == "fp16";
 }
-std::string get_precision() { return g_precision == SCN_PREC_TF32 ? "tf32" : "fp32"; }
+std::string get_precision() { return g_precision == SCN_PREC_TF32 ? (g_half_rows ? "fp16" : "tf32") : "fp32"; }
 
 void no_backward(pybind11::args, pybind11::kwargs) {
   throw std::runtime_error("this build of sparseconvnet.SCN is inference only: backward passes are not part of the hot path");
@@ -444,7 +493,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
   mod.def("Incre_OutputLayer_updateOutput", &Incre_OutputLayer_updateOutput);
   mod.def("n_rulebook_bits", []() { return scn_n_rulebook_bits(); });
   mod.def("pack_weights", &pack_weights, "transposed weight copy for the tensor-core kernels (empty if not applicable)");
-  mod.def("set_precision", &set_precision, "arithmetic of the convolution kernels: 'fp32' or 'tf32'");
+  mod.def("pack_weights_f16", &pack_weights_f16, "fp16 weight fragments for convolutions that read fp16 rows (empty if not applicable)");
+  mod.def("set_precision", &set_precision, "arithmetic of the convolution kernels: 'fp32', 'tf32' or 'fp16'");
   mod.def("get_precision", &get_precision);
   mod.def("launch_count", []() { return scn_launch_count(); });
   mod.def("check_errors", []() { check(scn_check_errors((void *)c10::cuda::getCurrentCUDAStream().stream()), "check_errors"); },

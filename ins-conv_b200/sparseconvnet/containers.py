@@ -20,8 +20,20 @@ def _run(module, input, increment):
 
 class Sequential(_Container):
     def forward(self, input, increment=False):
-        for module in self._modules.values():
-            input = _run(module, input, increment)
+        from . import SCN
+        if SCN.get_precision() != "fp16":
+            for module in self._modules.values():
+                input = _run(module, input, increment)
+            return input
+        # 'fp16' precision: a BatchNorm directly in front of a narrow convolution writes fp16 rows for it
+        from .layers import BatchNormalization, takes_half_rows
+        mods = list(self._modules.values())
+        for i, module in enumerate(mods):
+            if isinstance(module, BatchNormalization) and i + 1 < len(mods) and takes_half_rows(mods[i + 1]) and \
+                    not (module._forward_hooks or module._forward_pre_hooks or mods[i + 1]._forward_pre_hooks):
+                input = module.forward(input, increment, half_rows=True)
+            else:
+                input = _run(module, input, increment)
         return input
 
     def input_spatial_size(self, out_size):

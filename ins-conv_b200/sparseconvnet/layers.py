@@ -42,7 +42,7 @@ def _residual(input, increment):
 def _packed(module):
     """The tensor-core kernels read weights transposed.  The copy is made once per weight version and kept on the
     module (keyed on the Parameter object, its version counter and its address), instead of once per call."""
-    if SCN.get_precision() != "tf32":
+    if SCN.get_precision() == "fp32":
         return _NONE
     w = module.weight
     c = module.__dict__.get("_pack_cache")
@@ -51,6 +51,31 @@ def _packed(module):
     p = SCN.pack_weights(w) if w.is_cuda else _NONE
     module.__dict__["_pack_cache"] = (w, w._version, w.data_ptr(), p)
     return p
+
+
+def _packed_for(module, features):
+    """The weight pack that goes with these feature rows: fp16 fragments for fp16 rows (written by a BatchNorm in
+    'fp16' precision), else the tf32 pack."""
+    if features.dtype != torch.float16:
+        return _packed(module)
+    w = module.weight
+    c = module.__dict__.get("_pack_cache_h")
+    if c is not None and c[0] is w and c[1] == w._version and c[2] == w.data_ptr():
+        return c[3]
+    p = SCN.pack_weights_f16(w)
+    module.__dict__["_pack_cache_h"] = (w, w._version, w.data_ptr(), p)
+    return p
+
+
+def takes_half_rows(module):
+    """True for a convolution module whose shape has an fp16 gather-GEMM kernel (planes 32 or 64 on both sides)."""
+    return isinstance(module, (SubmanifoldConvolution, Convolution, Deconvolution)) and \
+        module.nIn in (32, 64) and module.nOut in (32, 64) and not hasattr(module, "bias")
+
+
+def _f32(t):
+    """Saved fp16 rows as fp32, for the residual operators (they read fp32)."""
+    return t.float() if t.dtype == torch.float16 else t
 
 
 def _count(madds, out):
@@ -83,16 +108,17 @@ class SubmanifoldConvolution(Module):
         separate, fully coalesced addition (the epilogue reads the addend in 32-byte pieces), so the containers do
         not; the argument stays for callers that want the sum without a temporary."""
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, self.nOut, input)
-        out = input.features.new_empty(0)
+        out = input.features.new_empty(0, dtype=torch.float32)
         if not _residual(input, increment):
             madds = SCN.SubmanifoldConvolution_updateOutput(
                 input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
-                optionalTensor(self, "bias"), self.dilated_rate, _packed(self), _NONE if addend is None else addend)
+                optionalTensor(self, "bias"), self.dilated_rate, _packed_for(self, input.features),
+                _NONE if addend is None else addend)
             _keep(self, save_meta=input.metadata, save_input_feats=input.features)
         else:
             madds = SCN.Incre_SubmanifoldConvolution_updateOutput(
                 input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
-                optionalTensor(self, "bias"), self.save_meta, self.save_input_feats, _packed(self))
+                optionalTensor(self, "bias"), self.save_meta, _f32(self.save_input_feats), _packed(self))
         _count(madds, out)
         return input.like(out)
 
@@ -125,10 +151,10 @@ class Convolution(_Strided):
         out_size = torch.div(input.spatial_size - self.filter_size, self.filter_stride, rounding_mode="floor") + 1
         assert ((out_size - 1) * self.filter_stride + self.filter_size == input.spatial_size).all(), \
             (input.spatial_size, out_size, self.filter_size, self.filter_stride)
-        out = input.features.new_empty(0)
+        out = input.features.new_empty(0, dtype=torch.float32)
         op = SCN.Incre_Convolution_updateOutput if _residual(input, increment) else SCN.Convolution_updateOutput
         madds = op(input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                   out, self.weight, optionalTensor(self, "bias"), _packed(self))
+                   out, self.weight, optionalTensor(self, "bias"), _packed_for(self, input.features))
         _count(madds, out)
         return input.like(out, out_size)
 
@@ -143,16 +169,17 @@ class Deconvolution(_Strided):
     def forward(self, input, increment=False):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
         out_size = (input.spatial_size - 1) * self.filter_stride + self.filter_size
-        out = input.features.new_empty(0)
+        out = input.features.new_empty(0, dtype=torch.float32)
         if not _residual(input, increment):
             madds = SCN.Deconvolution_updateOutput(
                 input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                out, self.weight, optionalTensor(self, "bias"), _packed(self))
+                out, self.weight, optionalTensor(self, "bias"), _packed_for(self, input.features))
             _keep(self, save_meta=input.metadata, save_input_feats=input.features)
         else:
             madds = SCN.Incre_Deconvolution_updateOutput(
                 input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                out, self.weight, optionalTensor(self, "bias"), self.save_meta, self.save_input_feats, _packed(self))
+                out, self.weight, optionalTensor(self, "bias"), self.save_meta, _f32(self.save_input_feats),
+                _packed(self))
         _count(madds, out)
         return input.like(out, out_size)
 
@@ -177,10 +204,13 @@ class BatchNormalization(Module):
             self.weight = Parameter(torch.ones(nPlanes))
             self.bias = Parameter(torch.zeros(nPlanes))
 
-    def forward(self, input, increment=False):
+    def forward(self, input, increment=False, half_rows=False):
+        """half_rows ('fp16' precision, full frames, running statistics): the result is written as fp16 rows; a
+        Sequential asks for it when the next module is a convolution that reads fp16 rows."""
         assert input.features.nelement() == 0 or input.features.size(1) == self.nPlanes, \
             (self.nPlanes, input.features.shape)
-        out = input.features.new_empty(0)
+        half_rows = half_rows and not self.training and not _residual(input, increment) and self.nPlanes % 8 == 0
+        out = input.features.new_empty(0, dtype=torch.float16 if half_rows else torch.float32)
         scratch = input.features.new_empty(0)
         if not _residual(input, increment):
             SCN.BatchNormalization_updateOutput(
@@ -192,7 +222,7 @@ class BatchNormalization(Module):
             SCN.Incre_BatchNormalization_updateOutput(
                 input.features, out, scratch, scratch, self.running_mean, self.running_var,
                 optionalTensor(self, "weight"), optionalTensor(self, "bias"), self.eps, self.momentum, self.training,
-                self.leakiness, input.metadata, self.save_output.metadata, self.save_output.features,
+                self.leakiness, input.metadata, self.save_output.metadata, _f32(self.save_output.features),
                 self.save_input.features, input.spatial_size)
         return input.like(out)
 

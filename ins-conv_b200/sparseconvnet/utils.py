@@ -24,7 +24,9 @@ def optionalTensor(module, name):
 
 
 def set_precision(p):
-    """'fp32' (default, bit-for-bit deterministic FFMA) or 'tf32' (tcgen05 tensor cores)."""
+    """'fp32' (default, bit-for-bit deterministic FFMA), 'tf32' (tensor cores reading the fp32 features as tf32), or
+    'fp16' (as tf32, and a BatchNorm directly in front of a convolution with 32 or 64 planes on both sides hands it
+    fp16 rows: half the bytes to gather, 11 significant bits instead of tf32's 10)."""
     SCN.set_precision(p)
 
 

@@ -127,7 +127,7 @@ def test_demo_py_flow_runs_unchanged(cuda):
     assert float((bn.running_var - 1).abs().max()) > 0
 
 
-@pytest.mark.parametrize("precision,tol", [("fp32", 1e-4), ("tf32", 2e-2)])
+@pytest.mark.parametrize("precision,tol", [("fp32", 1e-4), ("tf32", 2e-2), ("fp16", 2e-2)])
 def test_exact_incremental_equals_full_recompute(cuda, precision, tol):
     # benchmark configuration 2 (incremental layer over two frames) on a small UNet: frame t+1 deletes a 16^3 cube, inserts a sphere and re-draws 1 % of the
     # features; the exact mode must equal a full recompute of frame t+1, and again after one more insertion
@@ -178,15 +178,29 @@ def test_config3_full_room_tf32_vs_fp32_oracle(cuda):
     x = [torch.from_numpy(c).to(cuda), torch.from_numpy(f).to(cuda)]
     got32 = model(x)
     assert rel_err(got32, want) <= 1e-4
-    scn.set_precision("tf32")
+    for precision in ("tf32", "fp16"):
+        scn.set_precision(precision)
+        try:
+            got = model(x)
+            scn.SCN.check_errors()
+        finally:
+            scn.set_precision("fp32")
+        assert rel_err(got, want) <= 5e-2, precision
+        # relative L2 error over the whole output is far smaller than the max-norm bar
+        assert float((got.cpu() - want).norm() / want.norm()) <= 1e-2, precision
+    # 'fp16': the BatchNorms in front of the 32- and 64-plane convolutions handed over fp16 rows
+    halves = [m for m in model.modules() if isinstance(m, scn.BatchNormalization)
+              and getattr(m, "save_output", None) is not None and m.save_output.features.dtype == torch.float16]
+    assert len(halves) >= 10
+    # a reference-style incremental frame after an fp16 full frame still works (saved fp16 rows are widened)
+    scn.set_precision("fp16")
     try:
-        got = model(x)
+        model(x)
+        inc = model([x[0][:500] + torch.tensor([1, 0, 0], device=cuda), x[1][:500]], True)
         scn.SCN.check_errors()
+        assert inc.shape[0] == 500 and bool(torch.isfinite(inc).all())
     finally:
         scn.set_precision("fp32")
-    assert rel_err(got, want) <= 5e-2
-    # relative L2 error over the whole output is far smaller than the max-norm bar
-    assert float((got.cpu() - want).norm() / want.norm()) <= 1e-2
 
 
 def test_config4_sweep_frames(cuda):
