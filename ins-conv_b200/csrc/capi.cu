@@ -293,15 +293,25 @@ int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t 
   m->has_input = true;
   m->mode = mode;
   m->batch_size = batch_size;
-  // the coarse scales earlier networks went down to, now rather than in the middle of the network
+  // the coarse scales earlier networks went down to, now rather than in the middle of the network, chained on the
+  // device with one host round trip for all of them
+  std::vector<Size3> sizes;
   Size3 cur = m->input_size;
   for (int level = 0, levels = want_levels(); level < levels; ++level) {
     if (cur[0] % 2 || cur[1] % 2 || cur[2] % 2 || cur[0] < 2 || cur[1] < 2 || cur[2] < 2) break;
-    const Size3 next{{cur[0] / 2, cur[1] / 2, cur[2] / 2}};
-    Grid *fine = nullptr, *coarse = nullptr;
-    SCN_TRY(need_coarse(m, cur.data(), next.data(), &fine, &coarse, s));
-    if (coarse->n == 0) break;
-    cur = next;
+    cur = Size3{{cur[0] / 2, cur[1] / 2, cur[2] / 2}};
+    sizes.push_back(cur);
+  }
+  if (!sizes.empty()) {
+    std::vector<std::unique_ptr<Grid>> owned;
+    std::vector<Grid *> ptrs;
+    for (size_t i = 0; i < sizes.size(); ++i) {
+      owned.emplace_back(new Grid());
+      ptrs.push_back(owned.back().get());
+    }
+    Grid *fine0 = m->find(m->input_size.data());
+    SCN_TRY(grid_build_coarse_chain(ptrs.data(), (int)ptrs.size(), *fine0, want_ssc(), s));
+    for (size_t i = 0; i < sizes.size(); ++i) m->grids[sizes[i]] = std::move(owned[i]);
   }
   return SCN_OK;
 }

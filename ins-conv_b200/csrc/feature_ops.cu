@@ -267,8 +267,9 @@ __global__ void k_bn_f16out(const float *__restrict__ in, long long in_stride, _
     __align__(16) __half2 y[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float a = leaky(sw[c + 2 * j] * xs[2 * j] + sb[c + 2 * j], leak);
-      const float b = leaky(sw[c + 2 * j + 1] * xs[2 * j + 1] + sb[c + 2 * j + 1], leak);
+      // values beyond fp16's range saturate at +-65504 instead of becoming infinities
+      const float a = fminf(fmaxf(leaky(sw[c + 2 * j] * xs[2 * j] + sb[c + 2 * j], leak), -65504.f), 65504.f);
+      const float b = fminf(fmaxf(leaky(sw[c + 2 * j + 1] * xs[2 * j + 1] + sb[c + 2 * j + 1], leak), -65504.f), 65504.f);
       y[j] = __floats2half2_rn(a, b);
     }
     *reinterpret_cast<uint4 *>(out + row * out_stride + c) = *reinterpret_cast<const uint4 *>(y);

@@ -4,7 +4,7 @@
 //
 // With 32 or 64 planes a reduction step carries too little arithmetic to pay for staging 128-row operand tiles
 // in shared memory and driving them through tcgen05 from a single thread: that pipeline spends its time on
-// barriers and descriptor traffic (measured: ~1300 cycles per 128-row step of 4 MMAs).  Here a warp owns 16 or 32
+// barriers, copies and issue overhead (measured: 850-1300 cycles per 128-row step of 4 MMAs).  Here a warp owns 16 or 32
 // consecutive output rows and all output planes, keeps the accumulator in registers and works through the
 // offsets that have at least one neighbour among its rows:
 //   * the rows' map entries [K][rows] are staged once in a warp-private slice of shared memory (all loads of

@@ -155,8 +155,11 @@ __global__ void k_pack_keys_i64(const long long *__restrict__ coords, int ncols,
 }
 
 // int32 SoA coordinates of a finer grid, shifted right (downsampling by 2^shift).
+// src (optional): the build record of the grid c belongs to, when its site count is not known on the host yet
 __global__ void k_pack_keys_soa(const int32_t *__restrict__ c, long long n, int shift,
-                                unsigned long long *__restrict__ keys, BuildInfo *info, int measure_box) {
+                                unsigned long long *__restrict__ keys, BuildInfo *info, int measure_box,
+                                const BuildInfo *src) {
+  if (src) n = src->n_unique;
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   bool valid = i < n;
   int x = 0, y = 0, z = 0, b = 0;
@@ -174,7 +177,8 @@ __global__ void k_pack_keys_soa(const int32_t *__restrict__ c, long long n, int 
 // pass 2: occupancy bitmap in key order
 // ---------------------------------------------------------------------------------------------
 __global__ void k_mark(const unsigned long long *__restrict__ keys, long long n, Box bx,
-                       unsigned long long *bitmap) {
+                       unsigned long long *bitmap, const BuildInfo *src) {
+  if (src) n = src->n_unique;
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   int x, y, z, b;
@@ -334,7 +338,8 @@ template <bool UNIQUE>
 __global__ void k_assign(const unsigned long long *__restrict__ keys, long long n_src, Box bx,
                          const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
                          long long n, int32_t *__restrict__ src_row, int32_t *coords, uint32_t *cnt, Slot *table,
-                         uint32_t mask, BuildInfo *info, int dyn) {
+                         uint32_t mask, BuildInfo *info, int dyn, const BuildInfo *src) {
+  if (src) n_src = src->n_unique;
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_src) return;
   if (dyn) {  // site count and capacity were decided on the device (k_plan_table)
@@ -440,8 +445,10 @@ __global__ void k_ssc_nbr(const int32_t *__restrict__ c, long long n, const Slot
 
 // 2x2x2 / stride 2: offset of a fine site inside its coarse cell k = (x&1)*4 + (y&1)*2 + (z&1)
 __global__ void k_conv_maps(const int32_t *__restrict__ fc, long long nf, const int32_t *__restrict__ parent,
-                            long long nc, int32_t *child, int32_t *up, unsigned long long *counts, const BuildInfo *dyn) {
+                            long long nc, int32_t *child, int32_t *up, unsigned long long *counts, const BuildInfo *dyn,
+                            const BuildInfo *src) {
   if (dyn) nc = dyn->n_unique;
+  if (src) nf = src->n_unique;
   long long f = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   __shared__ unsigned int hist[8];
   if (threadIdx.x < 8) hist[threadIdx.x] = 0;
@@ -502,15 +509,16 @@ int grid_free(Grid &g, cudaStream_t s) {
 static const unsigned long long kMaxBoxBits = 1ull << 35;
 
 // The few words a build reads back land in pinned host memory: a copy into pageable memory goes through a driver
-// staging buffer and costs several microseconds more per round trip.  One 2 KB block per host thread; when it
+// staging buffer and costs several microseconds more per round trip.  One 8 KB block per host thread; when it
 // cannot be had the reads go to the caller's stack as before.
+constexpr size_t kPinnedBytes = 8192;
 static unsigned char *pinned_scratch() {
   thread_local unsigned char *p = nullptr;
   thread_local bool tried = false;
   if (!tried) {
     tried = true;
     void *q = nullptr;
-    if (cudaHostAlloc(&q, 2048, cudaHostAllocDefault) == cudaSuccess) p = static_cast<unsigned char *>(q);
+    if (cudaHostAlloc(&q, kPinnedBytes, cudaHostAllocDefault) == cudaSuccess) p = static_cast<unsigned char *>(q);
     else (void)cudaGetLastError();
   }
   return p;
@@ -549,7 +557,7 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
     k_pack_keys_i64<<<blocks_for(n_src, T), T, 0, s>>>(reinterpret_cast<const long long *>(coords64), ncols, vec,
                                                       n_src, keys, info_d);
   } else {
-    k_pack_keys_soa<<<blocks_for(n_src, T), T, 0, s>>>(coords_soa, n_src, shift, keys, info_d, box_hint ? 0 : 1);
+    k_pack_keys_soa<<<blocks_for(n_src, T), T, 0, s>>>(coords_soa, n_src, shift, keys, info_d, box_hint ? 0 : 1, nullptr);
   }
   SCN_LAUNCHED();
   BuildInfo info;
@@ -587,7 +595,7 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
   SCN_TRY(dev_alloc_t(&bitmap, (size_t)nwords, s));
   SCN_TRY(dev_alloc_t(&prefix, (size_t)nwords, s));
   SCN_CUDA(cudaMemsetAsync(bitmap, 0, (size_t)nwords * 8, s));
-  k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap);
+  k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, nullptr);
   SCN_LAUNCHED();
   SCN_TRY(scan_emit(PopcWords{bitmap}, StorePrefix{prefix}, nwords, &info_d->n_unique, s));
   SCN_TRY(read_back(&info.n_unique, &info_d->n_unique, sizeof(uint32_t), 0, s, true));
@@ -605,12 +613,12 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
   SCN_CUDA(cudaMemsetAsync(g.table, 0xFF, (size_t)cap * sizeof(Slot), s));
   if (n == n_src) {
     k_assign<true><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, nullptr,
-                                                     g.table, g.mask, info_d, 0);
+                                                     g.table, g.mask, info_d, 0, nullptr);
   } else {
     SCN_TRY(dev_alloc_t(&cnt, (size_t)n, s));
     SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n * 4, s));
     k_assign<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, cnt,
-                                                      g.table, g.mask, info_d, 0);
+                                                      g.table, g.mask, info_d, 0, nullptr);
   }
   SCN_LAUNCHED();
   g.max_active = 1;
@@ -663,90 +671,137 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
   return SCN_OK;
 }
 
-int grid_build_coarse(Grid &g, const Grid &fine, bool with_ssc, cudaStream_t s) {
-  grid_free(g, s);
-  const int64_t n_src = fine.n;
-  g.n_src = n_src;
-  if (n_src == 0) return SCN_OK;
-  const int T = 256;
-  // the coarse box is the fine box halved: nothing to measure
-  Box bx;
-  unsigned long long bits = 1;
-  for (int d = 0; d < 4; ++d) {
-    const int sh = d < 3 ? 1 : 0;
-    const int lo = fine.box.o[d] >> sh, hi = (fine.box.o[d] + (int)fine.box.e[d] - 1) >> sh;
-    bx.o[d] = lo;
-    bx.e[d] = (unsigned)(hi - lo + 1);
-    bits *= bx.e[d];
-  }
-  if (bits > kMaxBoxBits) return fail(SCN_E_CAPACITY, "scene bounding box larger than 2^35 cells");
-  const long long nwords = (long long)((bits + 63) >> 6);
-  uint64_t cap_bound = 16;  // n_coarse <= n_fine bounds every buffer
-  while (cap_bound < (uint64_t)n_src * 2) cap_bound <<= 1;
-  BuildInfo *info_d = nullptr;
-  unsigned long long *keys = nullptr, *bitmap = nullptr, *counts_d = nullptr;
-  uint32_t *prefix = nullptr, *cnt = nullptr;
-  SCN_TRY(dev_alloc_t(&info_d, 1, s));
-  SCN_TRY(dev_alloc_t(&keys, (size_t)n_src, s));
-  SCN_TRY(dev_alloc_t(&bitmap, (size_t)nwords, s));
-  SCN_TRY(dev_alloc_t(&prefix, (size_t)nwords, s));
-  SCN_TRY(dev_alloc_t(&cnt, (size_t)n_src, s));
-  SCN_TRY(dev_alloc_t(&counts_d, 8 + 27, s));
-  SCN_TRY(dev_alloc_t(&g.coords, (size_t)n_src * 4, s));
-  SCN_TRY(dev_alloc_t(&g.table, (size_t)cap_bound, s));
-  SCN_TRY(dev_alloc_t(&g.src_row, (size_t)n_src, s));
-  SCN_TRY(dev_alloc_t(&g.child, (size_t)n_src * 8, s));
-  SCN_TRY(dev_alloc_t(&g.fine_up, (size_t)n_src * 8, s));
-  k_init_info<<<1, 32, 0, s>>>(info_d);
-  SCN_LAUNCHED();
-  k_pack_keys_soa<<<blocks_for(n_src, T), T, 0, s>>>(fine.coords, n_src, 1, keys, info_d, 0);
-  SCN_LAUNCHED();
-  SCN_CUDA(cudaMemsetAsync(bitmap, 0, (size_t)nwords * 8, s));
-  k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap);
-  SCN_LAUNCHED();
-  SCN_TRY(scan_emit(PopcWords{bitmap}, StorePrefix{prefix}, nwords, &info_d->n_unique, s));
-  k_plan_table<<<1, 32, 0, s>>>(info_d);
-  SCN_LAUNCHED();
-  SCN_CUDA(cudaMemsetAsync(g.table, 0xFF, (size_t)cap_bound * sizeof(Slot), s));
-  SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n_src * 4, s));
-  SCN_CUDA(cudaMemsetAsync(counts_d, 0, (8 + 27) * 8, s));
-  k_assign<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, 0, g.src_row, g.coords, cnt, g.table, 0,
-                                                    info_d, 1);
-  SCN_LAUNCHED();
-  SCN_CUDA(cudaMemsetAsync(g.child, 0xFF, (size_t)n_src * 8 * 4, s));
-  k_conv_maps<<<blocks_for(n_src, 256), 256, 0, s>>>(fine.coords, n_src, g.src_row, 0, g.child, g.fine_up, counts_d, info_d);
-  SCN_LAUNCHED();
-  if (with_ssc) {
-    SCN_TRY(dev_alloc_t(&g.nbr, (size_t)n_src * 27, s));
-    k_ssc_nbr<<<dim3(blocks_for(n_src, 256), 27), 256, 0, s>>>(g.coords, 0, g.table, 0, nullptr, 1, g.nbr, counts_d + 8, info_d);
-    SCN_LAUNCHED();
-  }
+// What one level of a chained coarse build leaves on the device for the host to read at the end.
+struct LevelRecord {
   BuildInfo info;
-  unsigned long long h[8 + 27];
-  SCN_TRY(read_back(h, counts_d, sizeof(h), 1, s, false));
-  SCN_TRY(read_back(&info, info_d, sizeof(info), 0, s, true));
-  take(&info, sizeof(info), 0);
-  take(h, sizeof(h), 1);
-  dev_free(counts_d, s);
-  dev_free(cnt, s);
-  dev_free(prefix, s);
-  dev_free(bitmap, s);
-  dev_free(keys, s);
-  dev_free(info_d, s);
-  g.n = info.n_unique;
-  g.box = bx;
-  g.mask = info.mask;
-  g.max_active = 1;
-  for (int k = 0; k < 8; ++k) g.child_count[k] = (int64_t)h[k];
-  if (with_ssc) {
-    g.nbr_total = 0;
-    for (int k = 0; k < 27; ++k) {
-      g.nbr_count[k] = (int64_t)h[8 + k];
-      g.nbr_total += g.nbr_count[k];
-    }
+  unsigned long long counts[8 + 27];  // stride-2 offsets, then the 27 neighbour offsets
+};
+
+int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, bool with_ssc, cudaStream_t s) {
+  for (int l = 0; l < count; ++l) grid_free(*levels[l], s);
+  if (count <= 0) return SCN_OK;
+  if (fine0.n == 0) {
+    for (int l = 0; l < count; ++l) levels[l]->n_src = 0;
+    return SCN_OK;
   }
-  if (info.err & 2u) return fail(SCN_E_CAPACITY, "hash table overflow");
-  return SCN_OK;
+  const int T = 256;
+  LevelRecord *rec_d = nullptr;
+  SCN_TRY(dev_alloc_t(&rec_d, (size_t)count, s));
+  SCN_CUDA(cudaMemsetAsync(rec_d, 0, (size_t)count * sizeof(LevelRecord), s));
+  std::vector<void *> temps;
+  auto temp = [&](size_t bytes, void **p) {
+    SCN_TRY(dev_alloc(p, bytes, s));
+    temps.push_back(*p);
+    return (int)SCN_OK;
+  };
+  Box box = fine0.box;
+  int64_t bound = fine0.n;  // upper bound of the site count of the source level (exact for the first level)
+  const int32_t *src_coords = fine0.coords;
+  std::vector<Box> boxes((size_t)count);
+  int rc = SCN_OK;
+  for (int l = 0; l < count && rc == SCN_OK; ++l) {
+    Grid &g = *levels[l];
+    const BuildInfo *src = l == 0 ? nullptr : &rec_d[l - 1].info;  // level 0 knows its source count on the host
+    BuildInfo *info_d = &rec_d[l].info;
+    unsigned long long *counts_d = rec_d[l].counts;
+    // the coarse box is the fine box halved: nothing to measure
+    Box bx;
+    unsigned long long bits = 1;
+    for (int d = 0; d < 4; ++d) {
+      const int sh = d < 3 ? 1 : 0;
+      const int lo = box.o[d] >> sh, hi = (box.o[d] + (int)box.e[d] - 1) >> sh;
+      bx.o[d] = lo;
+      bx.e[d] = (unsigned)(hi - lo + 1);
+      bits *= bx.e[d];
+    }
+    if (bits > kMaxBoxBits) {
+      rc = fail(SCN_E_CAPACITY, "scene bounding box larger than 2^35 cells");
+      break;
+    }
+    boxes[(size_t)l] = bx;
+    const long long nwords = (long long)((bits + 63) >> 6);
+    const int64_t n_src = bound;                                         // rows the source level may have
+    const int64_t n_max = (int64_t)bits < bound ? (int64_t)bits : bound;  // rows this level may have
+    uint64_t cap_bound = 16;
+    while (cap_bound < (uint64_t)n_max * 2) cap_bound <<= 1;
+    unsigned long long *keys = nullptr, *bitmap = nullptr;
+    uint32_t *prefix = nullptr, *cnt = nullptr;
+    if ((rc = temp((size_t)n_src * 8, (void **)&keys)) != SCN_OK) break;
+    if ((rc = temp((size_t)nwords * 8, (void **)&bitmap)) != SCN_OK) break;
+    if ((rc = temp((size_t)nwords * 4, (void **)&prefix)) != SCN_OK) break;
+    if ((rc = temp((size_t)n_max * 4, (void **)&cnt)) != SCN_OK) break;
+    if ((rc = dev_alloc_t(&g.coords, (size_t)n_max * 4, s)) != SCN_OK) break;
+    if ((rc = dev_alloc_t(&g.table, (size_t)cap_bound, s)) != SCN_OK) break;
+    if ((rc = dev_alloc_t(&g.src_row, (size_t)n_src, s)) != SCN_OK) break;
+    if ((rc = dev_alloc_t(&g.child, (size_t)n_max * 8, s)) != SCN_OK) break;
+    if ((rc = dev_alloc_t(&g.fine_up, (size_t)n_src * 8, s)) != SCN_OK) break;
+    k_init_info<<<1, 32, 0, s>>>(info_d);
+    k_pack_keys_soa<<<blocks_for(n_src, T), T, 0, s>>>(src_coords, n_src, 1, keys, info_d, 0, src);
+    SCN_CUDA(cudaMemsetAsync(bitmap, 0, (size_t)nwords * 8, s));
+    k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, src);
+    if ((rc = scan_emit(PopcWords{bitmap}, StorePrefix{prefix}, nwords, &info_d->n_unique, s)) != SCN_OK) break;
+    k_plan_table<<<1, 32, 0, s>>>(info_d);
+    SCN_CUDA(cudaMemsetAsync(g.table, 0xFF, (size_t)cap_bound * sizeof(Slot), s));
+    SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n_max * 4, s));
+    k_assign<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, 0, g.src_row, g.coords, cnt, g.table, 0,
+                                                      info_d, 1, src);
+    SCN_CUDA(cudaMemsetAsync(g.child, 0xFF, (size_t)n_max * 8 * 4, s));
+    k_conv_maps<<<blocks_for(n_src, 256), 256, 0, s>>>(src_coords, n_src, g.src_row, 0, g.child, g.fine_up, counts_d, info_d, src);
+    if (with_ssc) {
+      if ((rc = dev_alloc_t(&g.nbr, (size_t)n_max * 27, s)) != SCN_OK) break;
+      k_ssc_nbr<<<dim3(blocks_for(n_max, 256), 27), 256, 0, s>>>(g.coords, 0, g.table, 0, nullptr, 1, g.nbr, counts_d + 8, info_d);
+    }
+    for (int i = 0; i < 6 + (with_ssc ? 1 : 0); ++i) g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (cudaGetLastError() != cudaSuccess) {
+      rc = fail(SCN_E_CUDA, "a kernel of the coarse grid build could not be launched");
+      break;
+    }
+    box = bx;
+    bound = n_max;
+    src_coords = g.coords;
+  }
+  // one host round trip for all levels
+  std::vector<LevelRecord> rec((size_t)count);
+  if (rc == SCN_OK) {
+    unsigned char *pin = pinned_scratch();
+    const size_t bytes = (size_t)count * sizeof(LevelRecord);
+    void *land = (pin && bytes <= kPinnedBytes) ? (void *)pin : (void *)rec.data();
+    if (cudaMemcpyAsync(land, rec_d, bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess)
+      rc = fail(SCN_E_CUDA, std::string("coarse grid build: ") + cudaGetErrorString(cudaGetLastError()));
+    else if (land != rec.data()) memcpy(rec.data(), land, bytes);
+  }
+  for (void *p : temps) dev_free(p, s);
+  dev_free(rec_d, s);
+  if (rc != SCN_OK) {
+    for (int l = 0; l < count; ++l) grid_free(*levels[l], s);
+    return rc;
+  }
+  int64_t n_prev = fine0.n;
+  for (int l = 0; l < count; ++l) {
+    Grid &g = *levels[l];
+    const LevelRecord &r = rec[(size_t)l];
+    g.n_src = n_prev;
+    g.n = r.info.n_unique;
+    g.box = boxes[(size_t)l];
+    g.mask = r.info.mask;
+    g.max_active = 1;
+    for (int k = 0; k < 8; ++k) g.child_count[k] = (int64_t)r.counts[k];
+    if (with_ssc) {
+      g.nbr_total = 0;
+      for (int k = 0; k < 27; ++k) {
+        g.nbr_count[k] = (int64_t)r.counts[8 + k];
+        g.nbr_total += g.nbr_count[k];
+      }
+    }
+    if (r.info.err & 2u) rc = fail(SCN_E_CAPACITY, "hash table overflow");
+    n_prev = g.n;
+  }
+  return rc;
+}
+
+int grid_build_coarse(Grid &g, const Grid &fine, bool with_ssc, cudaStream_t s) {
+  Grid *one = &g;
+  return grid_build_coarse_chain(&one, 1, fine, with_ssc, s);
 }
 
 int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_stride, int32_t *rows,
@@ -807,7 +862,7 @@ int grid_build_conv(Grid &coarse, const Grid &fine, cudaStream_t s) {
   SCN_TRY(dev_alloc_t(&coarse.fine_up, (size_t)fine.n * 8, s));
   SCN_CUDA(cudaMemsetAsync(coarse.child, 0xFF, (size_t)coarse.n * 8 * 4, s));
   k_conv_maps<<<blocks_for(fine.n, 256), 256, 0, s>>>(fine.coords, fine.n, coarse.src_row, coarse.n, coarse.child,
-                                                     coarse.fine_up, counts_d, nullptr);
+                                                     coarse.fine_up, counts_d, nullptr, nullptr);
   SCN_LAUNCHED();
   unsigned long long h[8];
   SCN_CUDA(cudaMemcpyAsync(h, counts_d, sizeof(h), cudaMemcpyDeviceToHost, s));
