@@ -137,7 +137,7 @@ def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
     SSC layer' figure in isolation.  L2 is flushed between launches; each launch is timed with CUDA events."""
     import torch
     from insconv import cabi
-    half = args.precision == "fp16" and args.n_in in (32, 64) and args.n_out in (32, 64)
+    half = args.precision == "fp16" and cabi.lib().scn_weights_packable_f16(27, args.n_in, args.n_out) == 1
     prec = cabi.PREC_FP32 if args.precision == "fp32" else cabi.PREC_TF32
     coords, _, _, _ = make_scene(0, args.voxels)
     m = cabi.Metadata()
@@ -149,7 +149,7 @@ def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
     if half:  # fp16 rows (as a BatchNorm in front of the layer writes them) and the fp16 weight pack
         import ctypes
         x = x.half()
-        wp = torch.empty(w.numel(), dtype=torch.float16, device=dev)
+        wp = torch.empty(cabi.lib().scn_packed_size_f16(27, args.n_in, args.n_out), dtype=torch.float16, device=dev)
         stream = torch.cuda.current_stream().cuda_stream
         cabi.call("scn_pack_weights_f16", cabi.ptr(w), 27, args.n_in, args.n_out, cabi.ptr(wp), stream)
         out = torch.empty(n, args.n_out, dtype=torch.float32, device=dev)

@@ -175,7 +175,11 @@ SCN_API int scn_pack_weights(const float *weight, int64_t volume, int64_t n_in, 
  * BatchNorm+ReLU output is well inside fp16's range; fp16 keeps 11 significant bits, one more than the tf32 the
  * other tensor-core kernels read.  scn_bn_forward_f16 writes the normalised rows as fp16 (out: [rows, planes] fp16,
  * out_stride in fp16 elements, planes and out_stride multiples of 8); scn_ssc/conv/deconv_forward with SCN_PREC_F16
- * read them.  Shapes: scn_weights_packable_f16() != 0 (n_in and n_out 32 or 64); packed: volume*n_in*n_out fp16. */
+ * read them.  Shapes: scn_weights_packable_f16() != 0 (n_in and n_out multiples of 32, n_out <= 224: planes 32 or
+ * 64 on both sides run the warp-level kernel, the rest the tcgen05 kernel with kind::f16 and 64 planes per
+ * reduction step); packed: scn_packed_size_f16() fp16 elements (n_in is padded to a multiple of 64 for the
+ * tcgen05 layout), contents opaque. */
+SCN_API int64_t scn_packed_size_f16(int64_t volume, int64_t n_in, int64_t n_out);
 SCN_API int scn_weights_packable_f16(int64_t volume, int64_t n_in, int64_t n_out);
 SCN_API int scn_pack_weights_f16(const float *weight, int64_t volume, int64_t n_in, int64_t n_out, void *packed,
                                  void *stream);

@@ -175,9 +175,13 @@ static int check_feat(const void *in, const void *out, const void *w, int64_t n_
 static int run_conv(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out,
                     const float *weight, const float *bias, float *out, int64_t out_stride, int64_t n_in, int64_t n_planes_out,
                     const float *init, int64_t init_stride, int precision, cudaStream_t s) {
-  if (precision == SCN_PREC_F16)
-    return gather_mma_warp_f16(in, in_stride, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
-                               init_stride, s);
+  if (precision == SCN_PREC_F16) {  // narrow layers: warp-level kernel; wide layers: tcgen05 kernel
+    if (warp_mma_f16_shape(K, n_in, n_planes_out))
+      return gather_mma_warp_f16(in, in_stride, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
+                                 init_stride, s);
+    return gather_gemm_tc_f16(in, in_stride, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
+                              init_stride, s);
+  }
   return gather_gemm(in, in_stride, in_rows, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
                      init_stride, precision, s);
 }
@@ -398,11 +402,18 @@ int scn_weights_packable(int64_t volume, int64_t n_in, int64_t n_out) { return t
 int scn_pack_weights(const float *weight, int64_t volume, int64_t n_in, int64_t n_out, float *packed, void *stream) {
   return tc_pack_weights(weight, volume, n_in, n_out, packed, (cudaStream_t)stream);
 }
+int64_t scn_packed_size_f16(int64_t volume, int64_t n_in, int64_t n_out) {
+  if (warp_mma_f16_shape(volume, n_in, n_out)) return volume * n_in * n_out;
+  if (tc_f16_shape(volume, n_in, n_out)) return tc_f16_packed_size(volume, n_in, n_out);
+  return 0;
+}
 int scn_weights_packable_f16(int64_t volume, int64_t n_in, int64_t n_out) {
-  return warp_mma_f16_shape(volume, n_in, n_out) ? 1 : 0;
+  return scn_packed_size_f16(volume, n_in, n_out) > 0 ? 1 : 0;
 }
 int scn_pack_weights_f16(const float *weight, int64_t volume, int64_t n_in, int64_t n_out, void *packed, void *stream) {
-  return warp_mma_pack_f16(weight, volume, n_in, n_out, packed, (cudaStream_t)stream);
+  if (warp_mma_f16_shape(volume, n_in, n_out))
+    return warp_mma_pack_f16(weight, volume, n_in, n_out, packed, (cudaStream_t)stream);
+  return tc_pack_weights_f16(weight, volume, n_in, n_out, packed, (cudaStream_t)stream);
 }
 int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
                     int64_t out_stride, const float *weight, const float *bias, int64_t n_in, int64_t n_out,

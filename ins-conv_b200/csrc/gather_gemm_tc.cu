@@ -14,7 +14,7 @@
 // is fp32.
 //
 // Two kernels:
-//   k_gather_gemm_tf32_persist  the production kernel: persistent CTAs, warp-specialised (cp.async producers for
+//   k_gather_gemm_tc_persist    the production kernel: persistent CTAs, warp-specialised (cp.async producers for
 //                               the gathered rows, one bulk-tensor (TMA) copy per step for the weight block, one
 //                               lane driving the tensor core, epilogue warps), two accumulators, split-K items
 //   k_gather_gemm_tf32          one CTA per tile, all threads copy and one issues the MMAs, a CTA barrier per
@@ -33,6 +33,7 @@
 #define PROF(x)
 #endif
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <stddef.h>
 #include <stdlib.h>
 
@@ -99,6 +100,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 // instruction descriptor: D fp32, A/B tf32, both K-major, M = 128, N = n
 __host__ __device__ constexpr uint32_t instr_desc(int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (0u << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(kTileM >> 4) << 24);
+}
+// the same for fp16 operands (kind::f16): A and B format fields 0 (F16)
+__host__ __device__ constexpr uint32_t instr_desc_f16(int n) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | ((uint32_t)(n >> 3) << 17) |
          ((uint32_t)(kTileM >> 4) << 24);
 }
 __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -403,20 +409,34 @@ struct alignas(16) CtlP {
 static_assert(offsetof(CtlP, kmask_part) % 16 == 0, "kmask_part is read with 16-byte loads");
 
 // tcgen05.mma with the descriptors given as (low word, shared high word)
-__device__ __forceinline__ void mma_tf32_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
-                                              uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-      "mov.b64 da, {%1, %3};\n\t"
-      "mov.b64 db, {%2, %3};\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %4, p;\n\t}\n" ::"r"(tmem_d),
-      "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
-      : "memory");
+template <bool HALF>
+__device__ __forceinline__ void mma_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                         uint32_t accumulate) {
+  if (HALF)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}\n" ::"r"(tmem_d),
+        "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %4, p;\n\t}\n" ::"r"(tmem_d),
+        "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 
+// HALF: the feature rows are fp16 (in_stride in fp16 elements) and so are the weights; a reduction step then covers
+// 64 planes (a 128-byte operand row holds 64 fp16) with four K = 16 MMAs, planes beyond n_in are zero-filled.
+template <bool HALF>
 __global__ void __launch_bounds__(kPThreads, 1)
-k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, const __grid_constant__ CUtensorMap tmB,
+k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, const __grid_constant__ CUtensorMap tmB,
                            const int32_t *__restrict__ map, int K, long long n_out, const float *__restrict__ bias,
                            float *out, long long out_stride, int Cin, int Cout, const float *init, long long init_stride,
                            uint32_t acc_cols, int stages, long long tiles, int Z, float *__restrict__ partial) {
@@ -427,7 +447,11 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
   CtlP *ctl = reinterpret_cast<CtlP *>(smem + (size_t)stages * stage_bytes);
   int *s_map = reinterpret_cast<int *>(ctl + 1);  // [kMapBufs][K][128]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int KB = Cin >> 5;
+  constexpr int kStepPlanes = HALF ? 64 : 32;  // planes per reduction step (128 bytes of a row)
+  constexpr int kChunkPlanes = HALF ? 8 : 4;   // planes per 16-byte copy
+  constexpr int kElem = HALF ? 2 : 4;
+  const int KB = (Cin + kStepPlanes - 1) / kStepPlanes;
+  const unsigned char *in = static_cast<const unsigned char *>(in_v);
   // work items: (tile, share z of its reduction steps); Z == 1 means whole tiles
   const long long items = tiles * Z;
   const long long my_tiles = (items - (long long)blockIdx.x + gridDim.x - 1) / gridDim.x;
@@ -507,7 +531,7 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
     const int c = lane & 7, q = lane >> 3;
     const uint32_t dst_even = (uint32_t)(q << 7) + (uint32_t)((c ^ q) << 4);
     const uint32_t dst_odd = (uint32_t)((q + 4) << 7) + (uint32_t)((c ^ (q + 4)) << 4);
-    const float *in_c = in + (c << 2);
+    const unsigned char *in_c = in + (size_t)c * 16;  // this lane's 16-byte chunk of a row block
     PROF(long long t_map = 0; long long t_empty = 0; long long t_issue = 0; long long t_land = 0; long long t_all0 = clock64(); long long own = 0;)
     int mbuf = 0;
     uint32_t mphase = 0;
@@ -558,18 +582,20 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
           if (lane == 0) {
             if (it == 0) ctl->info[slot] = (uint32_t)T << 8;  // the item's step count rides on its first step
             mbar_expect_tx(bar, b_bytes);
-            tma_tile2d(a_base + kABytes, &tmB, bar, kb << 5, k * Cout);
+            tma_tile2d(a_base + kABytes, &tmB, bar, kb * kStepPlanes, k * Cout);
           }
           const int *mr = mrows + k * kTileM + q;
-          const float *in_kb = in_c + (kb << 5);
+          const unsigned char *in_kb = in_c + (size_t)kb * 128;
+          // fp16 rows: the last block of a row may be half empty (n_in = 96, 160, 224): those chunks are zero-filled
+          const bool chunk_ok = !HALF || kb * kStepPlanes + c * kChunkPlanes < Cin;
 #pragma unroll
           for (int j0 = 0; j0 < 32; j0 += 8) {
             int src[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) src[j] = nk ? mr[4 * (j0 + j)] : -1;
+            for (int j = 0; j < 8; ++j) src[j] = (nk && chunk_ok) ? mr[4 * (j0 + j)] : -1;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float *p = src[j] >= 0 ? in_kb + (long long)src[j] * in_stride : in;
+              const unsigned char *p = src[j] >= 0 ? in_kb + (long long)src[j] * in_stride * kElem : in;
               const uint32_t dst = a_base + (uint32_t)(((j0 + j) >> 1) << 10) + (((j0 + j) & 1) ? dst_odd : dst_even);
               cp_async16(dst, p, src[j] >= 0 ? 16u : 0u);
             }
@@ -611,7 +637,7 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
     // =========================== tensor core ======================================================
     // The whole warp runs the loop, so that ring position and descriptors are warp-uniform values; one elected
     // lane issues.  The first step of an item carries the item's step count, the steps after it are counted.
-    const uint32_t idesc = instr_desc(Cout);
+    const uint32_t idesc = HALF ? instr_desc_f16(Cout) : instr_desc(Cout);
     // descriptor words: low = start address / 16 | leading offset 16 B; high = stride offset 1024 B, version, 128-byte swizzle
     const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
     const uint32_t a_lo0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);
@@ -648,10 +674,10 @@ k_gather_gemm_tf32_persist(const float *__restrict__ in, long long in_stride, co
         PROF(long long c1 = clock64(); ++nsteps;)
         if (elect_one()) {
           const uint32_t b_lo = a_lo + b_off16;
-          mma_tf32_lohi(tmem_d, a_lo, b_lo, desc_hi, idesc, t > 0 ? 1u : 0u);
-          mma_tf32_lohi(tmem_d, a_lo + 2, b_lo + 2, desc_hi, idesc, 1u);
-          mma_tf32_lohi(tmem_d, a_lo + 4, b_lo + 4, desc_hi, idesc, 1u);
-          mma_tf32_lohi(tmem_d, a_lo + 6, b_lo + 6, desc_hi, idesc, 1u);
+          mma_lohi<HALF>(tmem_d, a_lo, b_lo, desc_hi, idesc, t > 0 ? 1u : 0u);
+          mma_lohi<HALF>(tmem_d, a_lo + 2, b_lo + 2, desc_hi, idesc, 1u);
+          mma_lohi<HALF>(tmem_d, a_lo + 4, b_lo + 4, desc_hi, idesc, 1u);
+          mma_lohi<HALF>(tmem_d, a_lo + 6, b_lo + 6, desc_hi, idesc, 1u);
           mma_commit(empty0 + 8u * (uint32_t)slot);
           if (t == T - 1) mma_commit(smem_u32(&ctl->accfull[buf]));
         }
@@ -726,7 +752,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link-time libcuda dependency)
-static int encode_2d(CUtensorMap *tm, const float *base, uint64_t cols, uint64_t rows, uint64_t row_stride_bytes,
+static int encode_2d(CUtensorMap *tm, const void *base, bool half, uint64_t cols, uint64_t rows, uint64_t row_stride_bytes,
                      uint32_t box_cols, uint32_t box_rows) {
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
@@ -740,7 +766,8 @@ static int encode_2d(CUtensorMap *tm, const float *base, uint64_t cols, uint64_t
   const cuuint64_t strides[1] = {row_stride_bytes};
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims, strides, box, estr,
+  CUresult r = fn(tm, half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims,
+                  strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(SCN_E_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
@@ -889,7 +916,7 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
   if (st_p > kMaxStages) st_p = kMaxStages;
   if (use_persist && cols * 2 <= 512 && st_p >= 4) {
     CUtensorMap tmB;
-    SCN_TRY(encode_2d(&tmB, Wt, (uint64_t)Cin, (uint64_t)K * Cout, (uint64_t)Cin * 4, 32, (uint32_t)Cout));
+    SCN_TRY(encode_2d(&tmB, Wt, false, (uint64_t)Cin, (uint64_t)K * Cout, (uint64_t)Cin * 4, 32, (uint32_t)Cout));
     const int st = st_p;
     const size_t smem_p = (size_t)st * stage_bytes + fixed_p;
     {
@@ -898,12 +925,13 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
       int dev = 0;
       SCN_CUDA(cudaGetDevice(&dev));
       if (dev < 0 || dev >= 64 || !raised[dev]) {
-        SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tf32_persist, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tc_persist<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tc_persist<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
         if (dev >= 0 && dev < 64) raised[dev] = true;
       }
     }
     const long long n_items = tiles * Z;
-    k_gather_gemm_tf32_persist<<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads, smem_p, s>>>(
+    k_gather_gemm_tc_persist<false><<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads, smem_p, s>>>(
         in, in_stride, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, (int)Cout, init, init_stride, cols, st, tiles, Z,
         partial);
   } else {
@@ -929,6 +957,117 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
   dev_free(partial, s);
   dev_free(Wt_own, s);
   *handled = true;
+  return SCN_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// fp16 rows through the persistent tcgen05 kernel (wide layers of the 'fp16' precision)
+// ---------------------------------------------------------------------------------------------
+namespace {
+inline int64_t padded_planes(int64_t Cin) { return (Cin + 63) / 64 * 64; }
+inline int persist_stages(int64_t K, int64_t Cout) {
+  const size_t stage_bytes = (size_t)kABytes + (size_t)Cout * 128;
+  const size_t fixed_p = sizeof(CtlP) + (size_t)kMapBufs * K * kTileM * sizeof(int) + 1024;
+  const int st = (int)((220 * 1024 - fixed_p) / stage_bytes);
+  return st > kMaxStages ? kMaxStages : st;
+}
+
+// W [vol][n_in][n_out] fp32 -> [vol][n_out][n_in padded to a multiple of 64] fp16, zero in the padding
+__global__ void k_pack_weights_tc_f16(const float *__restrict__ W, __half *__restrict__ Wp, int Cin, int Cout, int Cin_pad,
+                                      long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int ci = (int)(i % Cin_pad);
+  const long long rest = i / Cin_pad;
+  const int co = (int)(rest % Cout);
+  const long long k = rest / Cout;
+  Wp[i] = __float2half_rn(ci < Cin ? W[(k * Cin + ci) * Cout + co] : 0.f);
+}
+}  // namespace
+
+bool tc_f16_shape(int64_t K, int64_t Cin, int64_t Cout) {
+  return K >= 1 && K <= 27 && Cin >= 32 && Cin % 32 == 0 && Cout >= 32 && Cout % 32 == 0 && Cout <= 256 &&
+         persist_stages(K, Cout) >= 4;
+}
+int64_t tc_f16_packed_size(int64_t K, int64_t Cin, int64_t Cout) { return K * Cout * padded_planes(Cin); }
+
+int tc_pack_weights_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s) {
+  if (!tc_f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "shape cannot be packed for the fp16 tcgen05 kernel");
+  if (!W || !packed) return fail(SCN_E_INVALID, "null pointer");
+  const long long total = tc_f16_packed_size(K, Cin, Cout);
+  k_pack_weights_tc_f16<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(W, static_cast<__half *>(packed), (int)Cin, (int)Cout,
+                                                                       (int)padded_planes(Cin), total);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
+                       const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
+                       int64_t init_stride, cudaStream_t s) {
+  if (!tc_f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "the fp16 tcgen05 gather-GEMM takes planes that are multiples of 32, n_out <= 224");
+  if (!map && K != 1) return fail(SCN_E_INVALID, "no map given for a filter volume above 1");
+  if (in_stride % 8 != 0 || out_stride % 4 != 0 || !aligned16(in) || !aligned16(Wp) || !aligned16(out) ||
+      (bias && !aligned16(bias)) || (init && (!aligned16(init) || init_stride % 4 != 0)))
+    return fail(SCN_E_INVALID, "rows must be 16-byte aligned (fp16 stride a multiple of 8, fp32 strides multiples of 4)");
+  const size_t stage_bytes = (size_t)kABytes + (size_t)Cout * 128;
+  const size_t fixed_p = sizeof(CtlP) + (size_t)kMapBufs * K * kTileM * sizeof(int) + 1024;
+  const int st = persist_stages(K, Cout);
+  uint32_t cols = 32;
+  while (cols < (uint32_t)Cout) cols <<= 1;
+  const long long tiles = (n_out + kTileM - 1) / kTileM;
+  int sm_count = 148;
+  {
+    int dev = 0;
+    SCN_CUDA(cudaGetDevice(&dev));
+    static int cached[64] = {0};
+    static bool raised[64] = {false};
+    if (dev >= 0 && dev < 64) {
+      if (!cached[dev]) SCN_CUDA(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
+      sm_count = cached[dev];
+    }
+    if (dev < 0 || dev >= 64 || !raised[dev]) {
+      SCN_CUDA(cudaFuncSetAttribute(k_gather_gemm_tc_persist<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+      if (dev >= 0 && dev < 64) raised[dev] = true;
+    }
+  }
+  // split-K choice as for tf32, with 64 planes per step
+  const int64_t Cin_pad = padded_planes(Cin);
+  const int steps_max = K * (int)(Cin_pad / 64);
+  int Z = 1;
+  if (tiles < 2 * sm_count && steps_max >= 4) {
+    long long best = -1;
+    const int zmax = steps_max / 2 < 32 ? steps_max / 2 : 32;
+    for (int z = 1; z <= zmax; ++z) {
+      const long long per_cta = (tiles * z + sm_count - 1) / sm_count;
+      const long long cost = per_cta * ((steps_max + z - 1) / z + 3) + (z > 1 ? 2 + z / 4 : 0);
+      if (best < 0 || cost < best) {
+        best = cost;
+        Z = z;
+      }
+      if (cost <= 40) break;
+    }
+  }
+  float *partial = nullptr;
+  if (Z > 1) SCN_TRY(dev_alloc_t(&partial, (size_t)Z * tiles * kTileM * Cout, s));
+  CUtensorMap tmB;
+  int rc = encode_2d(&tmB, Wp, true, (uint64_t)Cin_pad, (uint64_t)K * Cout, (uint64_t)Cin_pad * 2, 64, (uint32_t)Cout);
+  if (rc != SCN_OK) {
+    dev_free(partial, s);
+    return rc;
+  }
+  const long long n_items = tiles * Z;
+  k_gather_gemm_tc_persist<true><<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads,
+                                   (size_t)st * stage_bytes + fixed_p, s>>>(in, in_stride, tmB, map, K, n_out, bias, out, out_stride,
+                                                                            (int)Cin, (int)Cout, init, init_stride, cols, st,
+                                                                            tiles, Z, partial);
+  SCN_LAUNCHED();
+  if (Z > 1) {
+    const long long work = n_out * (Cout / 4);
+    k_splitk_reduce<<<(unsigned)((work + 255) / 256), 256, 0, s>>>(partial, Z, tiles * kTileM, n_out, (int)Cout, bias, out,
+                                                                  out_stride, init, init_stride);
+    SCN_LAUNCHED();
+  }
+  dev_free(partial, s);
   return SCN_OK;
 }
 

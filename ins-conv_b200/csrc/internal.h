@@ -157,6 +157,13 @@ int bn_forward_f16out(const float *in, int64_t in_stride, void *out, int64_t out
                       cudaStream_t s);
 // fp16 form of the warp-level gather-GEMM: in = __half rows, weights packed by warp_mma_pack_f16 (fp16 fragments)
 bool warp_mma_f16_shape(int64_t K, int64_t Cin, int64_t Cout);
+// fp16 rows through the persistent tcgen05 kernel: planes multiples of 32, weights [vol][n_out][n_in padded to 64] fp16
+bool tc_f16_shape(int64_t K, int64_t Cin, int64_t Cout);
+int64_t tc_f16_packed_size(int64_t K, int64_t Cin, int64_t Cout);
+int tc_pack_weights_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
+int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
+                       const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
+                       int64_t init_stride, cudaStream_t s);
 int warp_mma_pack_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
 int gather_mma_warp_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,

@@ -82,7 +82,9 @@ struct WeightArg {
   int precision;
   WeightArg(const at::Tensor &w, const at::Tensor &packed, bool half_rows = false) {
     if (half_rows) {
-      TORCH_CHECK(packed.defined() && packed.is_cuda() && packed.scalar_type() == at::kHalf && packed.numel() == w.numel(),
+      const int64_t vol = w.dim() == 3 ? w.size(0) : 1;
+      TORCH_CHECK(packed.defined() && packed.is_cuda() && packed.scalar_type() == at::kHalf && packed.numel() > 0 &&
+                      packed.numel() == scn_packed_size_f16(vol, w.size(w.dim() - 2), w.size(w.dim() - 1)),
                   "float16 feature rows need the float16 weight pack of this layer (pack_weights_f16)");
       ptr = reinterpret_cast<const float *>(packed.data_ptr<at::Half>());
       precision = SCN_PREC_F16;
@@ -445,9 +447,10 @@ at::Tensor pack_weights_f16(at::Tensor weight) {
   need_cuda_f32(weight, "weight");
   auto w = weight.contiguous();
   const int64_t vol = w.dim() == 3 ? w.size(0) : 1, n_in = w.size(w.dim() - 2), n_out = w.size(w.dim() - 1);
-  if (!scn_weights_packable_f16(vol, n_in, n_out)) return at::empty({0}, w.options().dtype(at::kHalf));
+  const int64_t size = scn_packed_size_f16(vol, n_in, n_out);
+  if (size <= 0) return at::empty({0}, w.options().dtype(at::kHalf));
   c10::cuda::CUDAGuard guard(w.device());
-  auto packed = at::empty(w.sizes(), w.options().dtype(at::kHalf));
+  auto packed = at::empty({size}, w.options().dtype(at::kHalf));
   check(scn_pack_weights_f16(w.data_ptr<float>(), vol, n_in, n_out, packed.data_ptr<at::Half>(), stream_of(w)),
         "pack_weights_f16");
   return packed;

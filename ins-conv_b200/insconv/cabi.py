@@ -59,6 +59,7 @@ PROTOTYPES = {
     "scn_pack_weights": (_int, [_p, _i64, _i64, _i64, _p, _p]),
     "scn_ssc_forward": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_set_build_ahead": (_int, [_int, _int]),
+    "scn_packed_size_f16": (_i64, [_i64, _i64, _i64]),
     "scn_weights_packable_f16": (_int, [_i64, _i64, _i64]),
     "scn_pack_weights_f16": (_int, [_p, _i64, _i64, _i64, _p, _p]),
     "scn_bn_forward_f16": (_int, [_p, _i64, _p, _i64, _i64, _i64, _p, _p, _p, _p, _dbl, _dbl, _p]),

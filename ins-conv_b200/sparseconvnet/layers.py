@@ -68,9 +68,11 @@ def _packed_for(module, features):
 
 
 def takes_half_rows(module):
-    """True for a convolution module whose shape has an fp16 gather-GEMM kernel (planes 32 or 64 on both sides)."""
+    """True for a convolution module whose shape has an fp16 gather-GEMM kernel (planes multiples of 32, at most
+    224 out: warp-level kernel for 32/64 planes, tcgen05 kernel above)."""
     return isinstance(module, (SubmanifoldConvolution, Convolution, Deconvolution)) and \
-        module.nIn in (32, 64) and module.nOut in (32, 64) and not hasattr(module, "bias")
+        module.nIn % 32 == 0 and module.nOut % 32 == 0 and 32 <= module.nOut <= 224 and module.nIn >= 32 and \
+        not hasattr(module, "bias")
 
 
 def _f32(t):

@@ -177,10 +177,12 @@ def test_ssc_forward_add(cuda, n_in, n_out, prec):
     assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max())
 
 
-@pytest.mark.parametrize("n_in,n_out", [(32, 32), (32, 64), (64, 32), (64, 64)])
+@pytest.mark.parametrize("n_in,n_out", [(32, 32), (32, 64), (64, 32), (64, 64), (96, 96), (64, 96), (160, 128), (96, 32),
+                                        (224, 224)])
 def test_f16_activations_bn_then_convolutions(cuda, n_in, n_out):
     # BatchNorm+ReLU writing fp16 rows, then SSC / stride-2 convolution / deconvolution reading them (warp-level fp16
-    # kernel), against the oracle's fp32 result of the same two layers
+    # kernel for 32/64 planes, tcgen05 kind::f16 kernel above, with n_in padded to a multiple of 64), against the
+    # oracle's fp32 result of the same two layers
     import ctypes as C
     m, g = _scene(cuda, 1)
     rng = np.random.RandomState(n_in * 7 + n_out)
@@ -200,13 +202,16 @@ def test_f16_activations_bn_then_convolutions(cuda, n_in, n_out):
         return out, want
 
     def packed(w):
-        p = torch.empty(w.size, dtype=torch.float16, device=cuda)
+        size = cabi.lib().scn_packed_size_f16(w.shape[0], w.shape[1], w.shape[2])
+        assert size >= w.size
+        p = torch.empty(size, dtype=torch.float16, device=cuda)
         dw = t(w)
         cabi.call("scn_pack_weights_f16", cabi.ptr(dw), w.shape[0], w.shape[1], w.shape[2], cabi.ptr(p), stream)
         torch.cuda.synchronize()
         return p
 
-    assert cabi.lib().scn_weights_packable_f16(27, n_in, n_out) == 1 and cabi.lib().scn_weights_packable_f16(27, 96, 96) == 0
+    assert cabi.lib().scn_weights_packable_f16(27, n_in, n_out) == 1 and cabi.lib().scn_weights_packable_f16(27, 48, 96) == 0
+    assert cabi.lib().scn_weights_packable_f16(27, 256, 256) == 0
     fl = C.c_double(0)
     # submanifold convolution
     h, ref = bn_f16(rng.randn(g.n, n_in).astype(np.float32), n_in)
