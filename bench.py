@@ -180,11 +180,12 @@ def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
     byts = s_in * n * args.n_in + 4.0 * n * args.n_out + 8.0 * pairs + s_in * 27 * args.n_in * args.n_out
     flops = 2.0 * madds
     hbm_bound = args.n_in <= 64
+    tensor_peak = bf16_peak if half else bf16_peak / 2  # 16-bit operands: the measured dense bf16 peak; tf32: half of it
     return {"sites": int(n), "n_in": args.n_in, "n_out": args.n_out, "pairs": int(pairs), "us_per_launch": t * 1e6,
             "voxels_per_s": n / t, "GBps": byts / t / 1e9, "TFLOPs": flops / t / 1e12,
             "roofline": {"bound": "hbm" if hbm_bound else "tensor", "achieved": byts / t / 1e9 if hbm_bound else flops / t / 1e12,
-                         "peak": hbm_peak if hbm_bound else bf16_peak / 2, "unit": "GB/s" if hbm_bound else "TFLOP/s",
-                         "frac": (byts / t / 1e9 / hbm_peak) if hbm_bound else (flops / t / 1e12 / (bf16_peak / 2)),
+                         "peak": hbm_peak if hbm_bound else tensor_peak, "unit": "GB/s" if hbm_bound else "TFLOP/s",
+                         "frac": (byts / t / 1e9 / hbm_peak) if hbm_bound else (flops / t / 1e12 / tensor_peak),
                          "peak_kind": peak_kind, "algorithmic_bytes": byts, "algorithmic_flops": flops}}
 
 
@@ -368,7 +369,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--voxels", type=int, default=250000)
-    ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "tf32"), choices=["fp32", "tf32", "fp16"])
+    ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "fp16"), choices=["fp32", "tf32", "fp16"])
     ap.add_argument("--quick", action="store_true", help="skip the 4M-point hash build (profiling aid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--legs", default="full,incre,sweep,e2e", help="which timed legs to run (profiling aid)")
@@ -582,19 +583,25 @@ def main():
         args.n_in, args.n_out = 128, 128
         wide = layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind)
         tcgen05 = dict(wide["roofline"])
-        tcgen05.update({"kernel": "gather-GEMM tf32 (tcgen05 persistent kernel), SSC 128->128 on %d sites" % wide["sites"],
+        tcgen05.update({"kernel": "gather-GEMM %s (tcgen05 persistent kernel), SSC 128->128 on %d sites"
+                                  % ("fp16 rows, kind::f16" if args.precision == "fp16" else "tf32", wide["sites"]),
                         "us_per_launch": wide["us_per_launch"],
-                        "peak_note": "tf32 peak taken as half the measured dense bf16 peak",
-                        # from profiles/gather_gemm_tf32_persist_ssc128_room.md
-                        "traffic": 248.4e6 if args.voxels == 250000 else None})
+                        "peak_note": "fp16: the measured dense bf16 peak; tf32: half of it (tf32 is not in MEASURED_PEAKS.json)",
+                        # from profiles/gather_gemm_tf32_persist_ssc128_room.md (tf32 capture)
+                        "traffic": 248.4e6 if args.voxels == 250000 and args.precision == "tf32" else None})
     hashes = hash_bench(dev, 5, 2, ("c1", "room") if args.quick else ("c1", "room", "building"))
     for h in hashes:
         h["hbm_frac"] = h["GBps"] / hbm_peak
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_full, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": {"fp32": "f32", "tf32": "tf32", "fp16": "f16 rows into the 32/64-plane layers, tf32 elsewhere"}[args.precision], "data": "synthetic",
+            "vs_baseline": None, "dtype": {"fp32": "f32", "tf32": "tf32", "fp16": "f16"}[args.precision], "data": "synthetic",
             "config": {"workload": WORKLOAD, "voxels_per_scene": int(coords.shape[0]), "scenes": world,
                        "voxel_layers_per_scene": voxel_layers, "precision": args.precision,
+                       "precision_note": {"fp32": "fp32 FFMA throughout",
+                                          "tf32": "fp32 tensors, tensor cores read them as tf32, fp32 accumulation",
+                                          "fp16": "BatchNorm hands fp16 rows to the convolution behind it (fp16 x fp16 products, "
+                                                  "fp32 accumulation and fp32 outputs); layers without a BatchNorm in front (first "
+                                                  "layer, 1x1 shortcuts) read fp32 as tf32"}[args.precision],
                        "l2": "no flush: one frame streams ~1.5 GB of activations and maps, far above the 126 MB L2"},
             "incremental": {"ms_per_frame": ms_incre, "changed_points": int(inc_c.shape[0]),
                             "changed_frac": float(inc_c.shape[0]) / coords.shape[0],

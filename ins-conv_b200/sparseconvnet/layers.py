@@ -75,9 +75,16 @@ def takes_half_rows(module):
         not hasattr(module, "bias")
 
 
-def _f32(t):
-    """Saved fp16 rows as fp32, for the residual operators (they read fp32)."""
-    return t.float() if t.dtype == torch.float16 else t
+def _f32(module, t):
+    """Saved fp16 rows as fp32, for the residual operators (they read fp32).  Widened once per saved tensor."""
+    if t.dtype != torch.float16:
+        return t
+    c = module.__dict__.get("_f32_cache")
+    if c is not None and c[0] is t:
+        return c[1]
+    wide = t.float()
+    module.__dict__["_f32_cache"] = (t, wide)
+    return wide
 
 
 def _count(madds, out):
@@ -120,7 +127,7 @@ class SubmanifoldConvolution(Module):
         else:
             madds = SCN.Incre_SubmanifoldConvolution_updateOutput(
                 input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
-                optionalTensor(self, "bias"), self.save_meta, _f32(self.save_input_feats), _packed(self))
+                optionalTensor(self, "bias"), self.save_meta, _f32(self, self.save_input_feats), _packed(self))
         _count(madds, out)
         return input.like(out)
 
@@ -180,7 +187,7 @@ class Deconvolution(_Strided):
         else:
             madds = SCN.Incre_Deconvolution_updateOutput(
                 input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                out, self.weight, optionalTensor(self, "bias"), self.save_meta, _f32(self.save_input_feats),
+                out, self.weight, optionalTensor(self, "bias"), self.save_meta, _f32(self, self.save_input_feats),
                 _packed(self))
         _count(madds, out)
         return input.like(out, out_size)
@@ -224,7 +231,7 @@ class BatchNormalization(Module):
             SCN.Incre_BatchNormalization_updateOutput(
                 input.features, out, scratch, scratch, self.running_mean, self.running_var,
                 optionalTensor(self, "weight"), optionalTensor(self, "bias"), self.eps, self.momentum, self.training,
-                self.leakiness, input.metadata, self.save_output.metadata, _f32(self.save_output.features),
+                self.leakiness, input.metadata, self.save_output.metadata, _f32(self, self.save_output.features),
                 self.save_input.features, input.spatial_size)
         return input.like(out)
 
