@@ -518,30 +518,48 @@ def main():
     ms_exact, _ = timed(exact_frame, args.steps, args.warmup) if "incre" in legs else (float("nan"), 0)
 
     # ---- online sequence (configs[3]): seeded camera sweep, one insertion of 2-8 % new surface voxels per frame.
-    # Per-frame latency of the reference-style residual update and of the exact update (kept scene advances).
+    # Pass 1, reference semantics: every frame is a residual update against the last full frame; every 10th frame the
+    # accumulated scene is recomputed in full (which renews the saved state).  Pass 2, exact mode: every frame merges
+    # its points into the kept scene and recomputes it (the kept scene advances by itself).
     sweep = None
     if "sweep" in legs and world == 1:
         from insconv import synth
+        import numpy as np
         n_frames = args.sweep_frames
-        model([d_coords, d_feats])  # reset the kept scene to the base room
-        lat = {"reference": [], "exact": []}
+        frames = []
         for fr in range(n_frames):
             nc, _ = synth.sweep_frame(coords, fr, n_frames=n_frames, seed=rank)
-            nfeat = synth.rgb(1000 + fr, nc.shape[0])
-            dn, dfn = torch.from_numpy(nc).to(dev), torch.from_numpy(nfeat).to(dev)
-            for mode, key in ((True, "reference"), ("exact", "exact")):
-                torch.cuda.synchronize()
-                t0 = time.perf_counter()
-                y = model([dn, dfn], mode)
-                torch.cuda.synchronize()
-                lat[key].append((time.perf_counter() - t0) * 1e3)
+            frames.append((torch.from_numpy(nc).to(dev), torch.from_numpy(synth.rgb(1000 + fr, nc.shape[0])).to(dev)))
+
+        def clocked(fn):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            fn()
+            torch.cuda.synchronize()
+            return (time.perf_counter() - t0) * 1e3
+
+        lat = {"reference": [], "full": [], "exact": []}
+        model([d_coords, d_feats])  # the last full frame: the base room
+        acc_c, acc_f = [d_coords], [d_feats]
+        for fr, (dn, dfn) in enumerate(frames):
+            lat["reference"].append(clocked(lambda: model([dn, dfn], True)))
+            acc_c.append(dn)
+            acc_f.append(dfn)
+            if fr % 10 == 9:
+                all_c, all_f = torch.cat(acc_c), torch.cat(acc_f)
+                lat["full"].append(clocked(lambda: model([all_c, all_f])))
+        scene_points_reference = int(sum(c.shape[0] for c in acc_c))
+        model([d_coords, d_feats])  # reset the kept scene to the base room
+        for dn, dfn in frames:
+            lat["exact"].append(clocked(lambda: model([dn, dfn], "exact")))
         pct = lambda v, q: float(sorted(v)[min(len(v) - 1, int(q * len(v)))])
+        stats = lambda v: {"mean": sum(v) / len(v), "p50": pct(v, 0.5), "p99": pct(v, 0.99)}
         sweep = {"frames": n_frames,
                  "scene_points_at_end": int(model.sparseModel[0].scene_coords.shape[0]),
-                 "reference_ms": {"mean": sum(lat["reference"]) / n_frames, "p50": pct(lat["reference"], 0.5),
-                                  "p99": pct(lat["reference"], 0.99)},
-                 "exact_ms": {"mean": sum(lat["exact"]) / n_frames, "p50": pct(lat["exact"], 0.5),
-                              "p99": pct(lat["exact"], 0.99)},
+                 "reference_ms": stats(lat["reference"]),
+                 "full_recompute_every_10th_frame_ms": stats(lat["full"]),
+                 "exact_ms": stats(lat["exact"]),
+                 "points_fed_in_reference_pass": scene_points_reference,
                  "timing": "host wall clock around each frame, device synchronised on both sides"}
         model([d_coords, d_feats])
 
@@ -574,9 +592,10 @@ def main():
                                % (args.precision, "FFMA kernel" if args.precision == "fp32" else "warp-level mma.sync kernel",
                                   lay["sites"]),
                      "us_per_launch": lay["us_per_launch"], "voxels_per_s": lay["voxels_per_s"],
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
-                     # profiles/gather_mma_tf32_warp_ssc32_room.md (same kernel, same workload)
-                     "traffic": 67.5e6 if args.precision == "tf32" and args.voxels == 250000 else None,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised in
+                     # profiles/gather_mma_f16_warp_ssc32_room.md and profiles/gather_mma_tf32_warp_ssc32_room.md
+                     # (same kernel, same workload)
+                     "traffic": {"fp16": 46.8e6, "tf32": 67.5e6}.get(args.precision) if args.voxels == 250000 else None,
                      "l2": "flushed between launches (256 MB write)"})
     tcgen05 = None
     if args.precision != "fp32":  # the tcgen05 kernel on a wide layer, against the tensor roofline
@@ -587,8 +606,8 @@ def main():
                                   % ("fp16 rows, kind::f16" if args.precision == "fp16" else "tf32", wide["sites"]),
                         "us_per_launch": wide["us_per_launch"],
                         "peak_note": "fp16: the measured dense bf16 peak; tf32: half of it (tf32 is not in MEASURED_PEAKS.json)",
-                        # from profiles/gather_gemm_tf32_persist_ssc128_room.md (tf32 capture)
-                        "traffic": 248.4e6 if args.voxels == 250000 and args.precision == "tf32" else None})
+                        # from profiles/gather_gemm_tc_persist_f16_ssc128_room.md / gather_gemm_tf32_persist_ssc128_room.md
+                        "traffic": {"fp16": 170.8e6, "tf32": 248.4e6}.get(args.precision) if args.voxels == 250000 else None})
     hashes = hash_bench(dev, 5, 2, ("c1", "room") if args.quick else ("c1", "room", "building"))
     for h in hashes:
         h["hbm_frac"] = h["GBps"] / hbm_peak
