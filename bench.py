@@ -309,7 +309,8 @@ def slab_bench(args, rank, world, local, dist):
     if rank == 0:
         print(json.dumps({"metric": METRIC, "value": coords.shape[0] * 53 / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
                           "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-                          "scaling": "strong", "vs_baseline": None, "dtype": args.precision, "data": "synthetic",
+                          "scaling": "strong", "vs_baseline": None,
+                          "dtype": {"fp32": "f32", "tf32": "tf32", "fp16": "f16"}[args.precision], "data": "synthetic",
                           "config": {"workload": "configs[4] part 2: one %d-voxel building (5 rooms x 4 floors) in %d x-slabs, "
                                                  "halo rows exchanged by NCCL after every SSC / strided convolution"
                                                  % (coords.shape[0], world),

@@ -13,6 +13,8 @@ the next incremental frames need (`save_meta`, `save_input_feats`, `save_output`
 incremental frame computes residuals on the sites touched by the new points only.  The modules are
 inference only: the operators do not record autograd history, whatever the grad mode.
 """
+import weakref
+
 import torch
 from torch.nn import Module, Parameter
 
@@ -75,15 +77,20 @@ def takes_half_rows(module):
         not hasattr(module, "bias")
 
 
+_wide_rows = {}  # id(fp16 tensor) -> (weak reference to it, its fp32 copy)
+
+
 def _f32(module, t):
-    """Saved fp16 rows as fp32, for the residual operators (they read fp32).  Widened once per saved tensor."""
+    """Saved fp16 rows as fp32, for the residual operators (they read fp32).  Widened once per saved tensor: a
+    BatchNorm's saved output and the saved input of the convolution behind it are the same tensor."""
     if t.dtype != torch.float16:
         return t
-    c = module.__dict__.get("_f32_cache")
-    if c is not None and c[0] is t:
-        return c[1]
+    hit = _wide_rows.get(id(t))
+    if hit is not None and hit[0]() is t:
+        return hit[1]
+    key = id(t)
     wide = t.float()
-    module.__dict__["_f32_cache"] = (t, wide)
+    _wide_rows[key] = (weakref.ref(t, lambda _, key=key: _wide_rows.pop(key, None)), wide)
     return wide
 
 
