@@ -774,6 +774,66 @@ static int encode_2d(CUtensorMap *tm, const void *base, bool half, uint64_t cols
   return SCN_OK;
 }
 
+// The persistent kernel's launches sit in the host-bound part of a frame (deep levels: kernels of 10-20 us), so the
+// host side of a launch is kept short: tensor maps are encoded once per (weights, shape) and kept, and the split-K
+// scratch is one grow-only block per host thread that consecutive launches on the same stream reuse (stream order
+// makes that safe); a launch on another stream falls back to the stream-ordered pool.
+struct TensorMapKey {
+  const void *base;
+  uint64_t cols, rows;
+  uint32_t box_cols, box_rows;
+  bool half;
+  bool operator==(const TensorMapKey &o) const {
+    return base == o.base && cols == o.cols && rows == o.rows && box_cols == o.box_cols && box_rows == o.box_rows && half == o.half;
+  }
+};
+static int cached_tensor_map(CUtensorMap *tm, const void *base, bool half, uint64_t cols, uint64_t rows, uint32_t box_cols,
+                             uint32_t box_rows) {
+  constexpr int kSlots = 256;  // direct-mapped on the weight address; a network has tens of weight tensors
+  thread_local TensorMapKey keys[kSlots] = {};
+  thread_local CUtensorMap maps[kSlots];
+  const TensorMapKey k{base, cols, rows, box_cols, box_rows, half};
+  const size_t slot = (reinterpret_cast<uintptr_t>(base) >> 8) % kSlots;
+  if (keys[slot].base && keys[slot] == k) {
+    *tm = maps[slot];
+    return SCN_OK;
+  }
+  SCN_TRY(encode_2d(tm, base, half, cols, rows, cols * (half ? 2 : 4), box_cols, box_rows));
+  keys[slot] = k;
+  maps[slot] = *tm;
+  return SCN_OK;
+}
+
+struct SplitKScratch {
+  float *p = nullptr;
+  size_t floats = 0;
+  cudaStream_t stream = nullptr;
+  int device = -1;
+};
+// returns scratch for `floats` floats; *pooled tells the caller to hand it back with dev_free
+static int splitk_scratch(float **out, size_t floats, cudaStream_t s, bool *pooled) {
+  thread_local SplitKScratch sc;
+  int dev = 0;
+  SCN_CUDA(cudaGetDevice(&dev));
+  *pooled = false;
+  if (sc.p && (sc.stream != s || sc.device != dev)) {  // another stream or device: leave the cached block alone
+    *pooled = true;
+    return dev_alloc_t(out, floats, s);
+  }
+  if (sc.floats < floats) {
+    if (sc.p) dev_free(sc.p, s);
+    sc.p = nullptr;
+    sc.floats = 0;
+    const size_t want = floats + floats / 2;
+    SCN_TRY(dev_alloc_t(&sc.p, want, s));
+    sc.floats = want;
+    sc.stream = s;
+    sc.device = dev;
+  }
+  *out = sc.p;
+  return SCN_OK;
+}
+
 // W [vol][Cin][Cout] -> Wt [vol][Cout][Cin]; 32x32 tiles through shared memory
 __global__ void k_transpose_weights(const float *__restrict__ W, float *__restrict__ Wt, int Cin, int Cout) {
   __shared__ float tile[32][33];
@@ -905,7 +965,8 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
         W, Wt, (int)Cin, (int)Cout);
     SCN_LAUNCHED();
   }
-  if (Z > 1) SCN_TRY(dev_alloc_t(&partial, (size_t)Z * tiles * kTileM * Cout, s));
+  bool partial_pooled = false;
+  if (Z > 1) SCN_TRY(splitk_scratch(&partial, (size_t)Z * tiles * kTileM * Cout, s, &partial_pooled));
   const dim3 grid((unsigned)tiles, (unsigned)Z);
   static const bool use_persist = []() {
     const char *e = getenv("INSCONV_TC_KERNEL");
@@ -916,7 +977,8 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
   if (st_p > kMaxStages) st_p = kMaxStages;
   if (use_persist && cols * 2 <= 512 && st_p >= 4) {
     CUtensorMap tmB;
-    SCN_TRY(encode_2d(&tmB, Wt, false, (uint64_t)Cin, (uint64_t)K * Cout, (uint64_t)Cin * 4, 32, (uint32_t)Cout));
+    if (packed) SCN_TRY(cached_tensor_map(&tmB, Wt, false, (uint64_t)Cin, (uint64_t)K * Cout, 32, (uint32_t)Cout));
+    else SCN_TRY(encode_2d(&tmB, Wt, false, (uint64_t)Cin, (uint64_t)K * Cout, (uint64_t)Cin * 4, 32, (uint32_t)Cout));
     const int st = st_p;
     const size_t smem_p = (size_t)st * stage_bytes + fixed_p;
     {
@@ -954,7 +1016,7 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
                                                                   out_stride, init, init_stride);
     SCN_LAUNCHED();
   }
-  dev_free(partial, s);
+  if (partial_pooled) dev_free(partial, s);
   dev_free(Wt_own, s);
   *handled = true;
   return SCN_OK;
@@ -1048,11 +1110,12 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
     }
   }
   float *partial = nullptr;
-  if (Z > 1) SCN_TRY(dev_alloc_t(&partial, (size_t)Z * tiles * kTileM * Cout, s));
+  bool partial_pooled = false;
+  if (Z > 1) SCN_TRY(splitk_scratch(&partial, (size_t)Z * tiles * kTileM * Cout, s, &partial_pooled));
   CUtensorMap tmB;
-  int rc = encode_2d(&tmB, Wp, true, (uint64_t)Cin_pad, (uint64_t)K * Cout, (uint64_t)Cin_pad * 2, 64, (uint32_t)Cout);
+  int rc = cached_tensor_map(&tmB, Wp, true, (uint64_t)Cin_pad, (uint64_t)K * Cout, 64, (uint32_t)Cout);
   if (rc != SCN_OK) {
-    dev_free(partial, s);
+    if (partial_pooled) dev_free(partial, s);
     return rc;
   }
   const long long n_items = tiles * Z;
@@ -1067,7 +1130,7 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
                                                                   out_stride, init, init_stride);
     SCN_LAUNCHED();
   }
-  dev_free(partial, s);
+  if (partial_pooled) dev_free(partial, s);
   return SCN_OK;
 }
 
