@@ -2,12 +2,14 @@
 (reference: sparseconvnet/sequential.py:9-25, tables.py:13-55, identity.py:10-15)."""
 import torch
 
+from . import SCN
 from .tensor import SparseConvNetTensor
 
 
 class _Container(torch.nn.Sequential):
     def add(self, module):
         self._modules[str(len(self._modules))] = module
+        self.__dict__.pop("_half_plan", None)
         return self
 
 
@@ -20,18 +22,24 @@ def _run(module, input, increment):
 
 class Sequential(_Container):
     def forward(self, input, increment=False):
-        from . import SCN
         if SCN.get_precision() != "fp16":
             for module in self._modules.values():
                 input = _run(module, input, increment)
             return input
-        # 'fp16' precision: a BatchNorm directly in front of a narrow convolution writes fp16 rows for it
-        from .layers import BatchNormalization, takes_half_rows
-        mods = list(self._modules.values())
-        for i, module in enumerate(mods):
-            if isinstance(module, BatchNormalization) and i + 1 < len(mods) and takes_half_rows(mods[i + 1]) and \
-                    not (module._forward_hooks or module._forward_pre_hooks or mods[i + 1]._forward_pre_hooks):
-                input = module.forward(input, increment, half_rows=True)
+        # 'fp16' precision: a BatchNorm directly in front of a convolution with an fp16 kernel writes fp16 rows for it.
+        # Which modules those are depends on the module list alone and is worked out once.
+        plan = self.__dict__.get("_half_plan")
+        if plan is None or plan[0] != len(self._modules):
+            from .layers import BatchNormalization, takes_half_rows
+            mods = list(self._modules.values())
+            plan = (len(mods), [isinstance(m, BatchNormalization) and i + 1 < len(mods) and takes_half_rows(mods[i + 1])
+                                for i, m in enumerate(mods)], mods)
+            self.__dict__["_half_plan"] = plan
+        mods = plan[2]
+        for i, half in enumerate(plan[1]):
+            module = mods[i]
+            if half and not (module._forward_hooks or module._forward_pre_hooks or mods[i + 1]._forward_pre_hooks):
+                input = module.forward(input, increment, True)
             else:
                 input = _run(module, input, increment)
         return input
