@@ -443,6 +443,48 @@ __global__ void k_ssc_nbr(const int32_t *__restrict__ c, long long n, const Slot
   if (threadIdx.x == 0 && cnt) atomicAdd(&counts[k], (unsigned long long)cnt);
 }
 
+// The same map for a grid looked up in itself, from the ranking structure instead of the hash table.
+// blockIdx.y = line (dy, dz); a thread handles site o and the three offsets dx = -1, 0, +1 of that line: the cells
+// (x-1, x, x+1) of a line are adjacent bits of the bitmap (x runs fastest in key order), so one word read (two when
+// the three bits straddle a word) and one prefix read answer three queries, and neighbouring sites read
+// neighbouring words.
+__global__ void k_ssc_nbr_rank(const int32_t *__restrict__ c, long long n, Box bx,
+                               const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
+                               int32_t *__restrict__ nbr, unsigned long long *counts, const BuildInfo *dyn) {
+  if (dyn) n = dyn->n_unique;
+  const int line = blockIdx.y, dy = line / 3 - 1, dz = line % 3 - 1;
+  const long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  int r[3] = {-1, -1, -1};
+  if (o < n) {
+    const int x = c[o], y = c[n + o] + dy, z = c[2 * n + o] + dz, b = c[3 * n + o];
+    const unsigned uy = (unsigned)(y - bx.o[1]), uz = (unsigned)(z - bx.o[2]);
+    if (uy < bx.e[1] && uz < bx.e[2]) {
+      const unsigned long long p0 = box_pos(bx, x, y, z, b);  // cell of dx = 0; x itself is inside the box
+      if (line == 4) {
+        r[1] = (int)o;  // the site itself
+      } else {
+        const unsigned long long w = __ldg(bitmap + (p0 >> 6));
+        if ((w >> (p0 & 63)) & 1ull) r[1] = (int)(__ldg(prefix + (p0 >> 6)) + (uint32_t)__popcll(w & ((1ull << (p0 & 63)) - 1ull)));
+      }
+      if (x > bx.o[0]) {
+        const unsigned long long p = p0 - 1, w = __ldg(bitmap + (p >> 6));
+        if ((w >> (p & 63)) & 1ull) r[0] = (int)(__ldg(prefix + (p >> 6)) + (uint32_t)__popcll(w & ((1ull << (p & 63)) - 1ull)));
+      }
+      if ((unsigned)(x - bx.o[0]) + 1u < bx.e[0]) {
+        const unsigned long long p = p0 + 1, w = __ldg(bitmap + (p >> 6));
+        if ((w >> (p & 63)) & 1ull) r[2] = (int)(__ldg(prefix + (p >> 6)) + (uint32_t)__popcll(w & ((1ull << (p & 63)) - 1ull)));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 3; ++j) nbr[(long long)(j * 9 + line) * n + o] = r[j];
+  }
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const int cnt = __syncthreads_count(r[j] >= 0);
+    if (threadIdx.x == 0 && cnt) atomicAdd(&counts[j * 9 + line], (unsigned long long)cnt);
+  }
+}
+
 // 2x2x2 / stride 2: offset of a fine site inside its coarse cell k = (x&1)*4 + (y&1)*2 + (z&1)
 __global__ void k_conv_maps(const int32_t *__restrict__ fc, long long nf, const int32_t *__restrict__ parent,
                             long long nc, int32_t *child, int32_t *up, unsigned long long *counts, const BuildInfo *dyn,
@@ -499,6 +541,8 @@ int grid_free(Grid &g, cudaStream_t s) {
   dev_free(g.csr_off, s);
   dev_free(g.csr_item, s);
   dev_free(g.nbr, s);
+  dev_free(g.bitmap, s);
+  dev_free(g.prefix, s);
   dev_free(g.child, s);
   dev_free(g.fine_up, s);
   g = Grid();
@@ -590,10 +634,10 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
     }
   }
   const long long nwords = (long long)((bits + 63) >> 6);
-  unsigned long long *bitmap = nullptr;
-  uint32_t *prefix = nullptr;
-  SCN_TRY(dev_alloc_t(&bitmap, (size_t)nwords, s));
-  SCN_TRY(dev_alloc_t(&prefix, (size_t)nwords, s));
+  SCN_TRY(dev_alloc_t(&g.bitmap, (size_t)nwords, s));
+  SCN_TRY(dev_alloc_t(&g.prefix, (size_t)nwords, s));
+  unsigned long long *bitmap = g.bitmap;  // kept with the grid: the neighbour map is built from them
+  uint32_t *prefix = g.prefix;
   SCN_CUDA(cudaMemsetAsync(bitmap, 0, (size_t)nwords * 8, s));
   k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, nullptr);
   SCN_LAUNCHED();
@@ -645,7 +689,7 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
     SCN_TRY(dev_alloc_t(&nbr_counts_d, 27, s));
     SCN_CUDA(cudaMemsetAsync(nbr_counts_d, 0, 27 * 8, s));
     SCN_TRY(dev_alloc_t(&g.nbr, (size_t)n * 27, s));
-    k_ssc_nbr<<<dim3(blocks_for(n, 256), 27), 256, 0, s>>>(g.coords, n, g.table, g.mask, nullptr, 1, g.nbr, nbr_counts_d, nullptr);
+    k_ssc_nbr_rank<<<dim3(blocks_for(n, 256), 9), 256, 0, s>>>(g.coords, n, bx, g.bitmap, g.prefix, g.nbr, nbr_counts_d, nullptr);
     SCN_LAUNCHED();
     SCN_TRY(read_back(nbr_counts, nbr_counts_d, sizeof(nbr_counts), 1, s, false));
   }
@@ -663,8 +707,6 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
     dev_free(nbr_counts_d, s);
   }
   dev_free(cnt, s);
-  dev_free(prefix, s);
-  dev_free(bitmap, s);
   dev_free(keys, s);
   dev_free(info_d, s);
   if (info.err & 2u) return fail(SCN_E_CAPACITY, "hash table overflow");
@@ -727,8 +769,10 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
     unsigned long long *keys = nullptr, *bitmap = nullptr;
     uint32_t *prefix = nullptr, *cnt = nullptr;
     if ((rc = temp((size_t)n_src * 8, (void **)&keys)) != SCN_OK) break;
-    if ((rc = temp((size_t)nwords * 8, (void **)&bitmap)) != SCN_OK) break;
-    if ((rc = temp((size_t)nwords * 4, (void **)&prefix)) != SCN_OK) break;
+    if ((rc = dev_alloc_t(&g.bitmap, (size_t)nwords, s)) != SCN_OK) break;  // kept with the grid
+    if ((rc = dev_alloc_t(&g.prefix, (size_t)nwords, s)) != SCN_OK) break;
+    bitmap = g.bitmap;
+    prefix = g.prefix;
     if ((rc = temp((size_t)n_max * 4, (void **)&cnt)) != SCN_OK) break;
     if ((rc = dev_alloc_t(&g.coords, (size_t)n_max * 4, s)) != SCN_OK) break;
     if ((rc = dev_alloc_t(&g.table, (size_t)cap_bound, s)) != SCN_OK) break;
@@ -749,7 +793,7 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
     k_conv_maps<<<blocks_for(n_src, 256), 256, 0, s>>>(src_coords, n_src, g.src_row, 0, g.child, g.fine_up, counts_d, info_d, src);
     if (with_ssc) {
       if ((rc = dev_alloc_t(&g.nbr, (size_t)n_max * 27, s)) != SCN_OK) break;
-      k_ssc_nbr<<<dim3(blocks_for(n_max, 256), 27), 256, 0, s>>>(g.coords, 0, g.table, 0, nullptr, 1, g.nbr, counts_d + 8, info_d);
+      k_ssc_nbr_rank<<<dim3(blocks_for(n_max, 256), 9), 256, 0, s>>>(g.coords, 0, bx, g.bitmap, g.prefix, g.nbr, counts_d + 8, info_d);
     }
     for (int i = 0; i < 6 + (with_ssc ? 1 : 0); ++i) g_launches.fetch_add(1, std::memory_order_relaxed);
     if (cudaGetLastError() != cudaSuccess) {
@@ -836,7 +880,19 @@ int grid_build_ssc(Grid &g, cudaStream_t s) {
   g_ssc_seen.store(true, std::memory_order_relaxed);
   if (g.nbr || g.n == 0) return SCN_OK;
   SCN_TRY(dev_alloc_t(&g.nbr, (size_t)g.n * 27, s));
-  SCN_TRY(nbr_common(g, g, nullptr, 1, g.nbr, g.nbr_count, s));
+  if (g.bitmap && g.prefix) {
+    unsigned long long *counts_d = nullptr, h[27];
+    SCN_TRY(dev_alloc_t(&counts_d, 27, s));
+    SCN_CUDA(cudaMemsetAsync(counts_d, 0, 27 * 8, s));
+    k_ssc_nbr_rank<<<dim3(blocks_for(g.n, 256), 9), 256, 0, s>>>(g.coords, g.n, g.box, g.bitmap, g.prefix, g.nbr, counts_d, nullptr);
+    SCN_LAUNCHED();
+    SCN_TRY(read_back(h, counts_d, sizeof(h), 1, s, true));
+    take(h, sizeof(h), 1);
+    dev_free(counts_d, s);
+    for (int k = 0; k < 27; ++k) g.nbr_count[k] = (int64_t)h[k];
+  } else {
+    SCN_TRY(nbr_common(g, g, nullptr, 1, g.nbr, g.nbr_count, s));
+  }
   g.nbr_total = 0;
   for (int k = 0; k < 27; ++k) g.nbr_total += g.nbr_count[k];
   return SCN_OK;

@@ -80,6 +80,11 @@ struct Grid {
   int32_t *csr_off = nullptr;   // [n+1]  (nullptr when every site has exactly one source: off[i] = i)
   int32_t *csr_item = nullptr;  // [n_src] sources of each site, ascending
   int32_t max_active = 0;
+  // occupancy bitmap of the box in key order and the exclusive prefix sums of its word popcounts: the ranking
+  // structure of the build, kept because "row of the site at (x,y,z)" = prefix[word] + popcount(bits below) answers
+  // the neighbour queries of the 3x3x3 map with coherent reads instead of hash probes
+  unsigned long long *bitmap = nullptr;
+  uint32_t *prefix = nullptr;
   // submanifold 3x3x3 neighbour map: nbr[k*n + o] = input row of offset k for output o, or -1
   int32_t *nbr = nullptr;
   int64_t nbr_count[27] = {0};
