@@ -159,7 +159,7 @@ static int need_incre(scn_metadata *m, scn_metadata *pre, const int64_t *size, G
     x = IncreMaps();
     x.pre = pre;
     SCN_TRY(dev_alloc_t(&x.pre_exist, (size_t)(*g)->n, s));
-    SCN_TRY(grid_query(**pg, (*g)->coords, (*g)->n, (*g)->n, x.pre_exist, s));
+    SCN_TRY(grid_query(**pg, (*g)->coords, (*g)->n, (*g)->n, x.pre_exist, true, s));
   }
   *im = &x;
   return SCN_OK;
@@ -256,7 +256,7 @@ int scn_metadata_query(scn_metadata *m, const int64_t size[3], const int32_t *co
   Grid *g;
   SCN_TRY(need_grid(m, size, &g));
   if (n < 0 || (n && (!coords_soa || !rows))) return fail(SCN_E_INVALID, "bad query arguments");
-  return grid_query(*g, coords_soa, n, n, rows, (cudaStream_t)stream);
+  return grid_query(*g, coords_soa, n, n, rows, false, (cudaStream_t)stream);  // the hash table's query path
 }
 
 // ---- input / output layer ----------------------------------------------------------------------

@@ -443,36 +443,41 @@ __global__ void k_ssc_nbr(const int32_t *__restrict__ c, long long n, const Slot
   if (threadIdx.x == 0 && cnt) atomicAdd(&counts[k], (unsigned long long)cnt);
 }
 
-// The same map for a grid looked up in itself, from the ranking structure instead of the hash table.
-// blockIdx.y = line (dy, dz); a thread handles site o and the three offsets dx = -1, 0, +1 of that line: the cells
-// (x-1, x, x+1) of a line are adjacent bits of the bitmap (x runs fastest in key order), so one word read (two when
-// the three bits straddle a word) and one prefix read answer three queries, and neighbouring sites read
-// neighbouring words.
+// The same map from the ranking structure of the looked-up grid (its box, bitmap and prefix sums) instead of its
+// hash table.  blockIdx.y = line (dy, dz); a thread handles site o and the three offsets dx = -1, 0, +1 of that
+// line: the cells (x-1, x, x+1) of a line are adjacent bits of the bitmap (x runs fastest in key order), so one
+// word read (two when the three bits straddle a word) and one prefix read answer three queries, and neighbouring
+// sites read neighbouring words.  self_ok: the grid is looked up in itself and the centre is the site's own row.
+__device__ __forceinline__ int rank_lookup(const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
+                                           unsigned long long p) {
+  const unsigned long long w = __ldg(bitmap + (p >> 6));
+  if (!((w >> (p & 63)) & 1ull)) return -1;
+  return (int)(__ldg(prefix + (p >> 6)) + (uint32_t)__popcll(w & ((1ull << (p & 63)) - 1ull)));
+}
+
 __global__ void k_ssc_nbr_rank(const int32_t *__restrict__ c, long long n, Box bx,
                                const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
-                               int32_t *__restrict__ nbr, unsigned long long *counts, const BuildInfo *dyn) {
+                               const int32_t *__restrict__ absent, int self_ok, int32_t *__restrict__ nbr,
+                               unsigned long long *counts, const BuildInfo *dyn) {
   if (dyn) n = dyn->n_unique;
   const int line = blockIdx.y, dy = line / 3 - 1, dz = line % 3 - 1;
   const long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   int r[3] = {-1, -1, -1};
   if (o < n) {
-    const int x = c[o], y = c[n + o] + dy, z = c[2 * n + o] + dz, b = c[3 * n + o];
-    const unsigned uy = (unsigned)(y - bx.o[1]), uz = (unsigned)(z - bx.o[2]);
-    if (uy < bx.e[1] && uz < bx.e[2]) {
-      const unsigned long long p0 = box_pos(bx, x, y, z, b);  // cell of dx = 0; x itself is inside the box
-      if (line == 4) {
-        r[1] = (int)o;  // the site itself
-      } else {
-        const unsigned long long w = __ldg(bitmap + (p0 >> 6));
-        if ((w >> (p0 & 63)) & 1ull) r[1] = (int)(__ldg(prefix + (p0 >> 6)) + (uint32_t)__popcll(w & ((1ull << (p0 & 63)) - 1ull)));
-      }
-      if (x > bx.o[0]) {
-        const unsigned long long p = p0 - 1, w = __ldg(bitmap + (p >> 6));
-        if ((w >> (p & 63)) & 1ull) r[0] = (int)(__ldg(prefix + (p >> 6)) + (uint32_t)__popcll(w & ((1ull << (p & 63)) - 1ull)));
-      }
-      if ((unsigned)(x - bx.o[0]) + 1u < bx.e[0]) {
-        const unsigned long long p = p0 + 1, w = __ldg(bitmap + (p >> 6));
-        if ((w >> (p & 63)) & 1ull) r[2] = (int)(__ldg(prefix + (p >> 6)) + (uint32_t)__popcll(w & ((1ull << (p & 63)) - 1ull)));
+    if (absent == nullptr || absent[o] < 0) {
+      const int x = c[o], y = c[n + o] + dy, z = c[2 * n + o] + dz, b = c[3 * n + o];
+      const unsigned uy = (unsigned)(y - bx.o[1]), uz = (unsigned)(z - bx.o[2]), ub = (unsigned)(b - bx.o[3]);
+      if (uy < bx.e[1] && uz < bx.e[2] && ub < bx.e[3]) {
+        const long long ux = (long long)x - bx.o[0];  // may lie outside the box of another grid
+        const unsigned long long row_base =
+            (((unsigned long long)ub * bx.e[2] + uz) * bx.e[1] + uy) * bx.e[0];  // cell (box x origin, y, z, b)
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+          const long long cx = ux + j - 1;
+          if (cx < 0 || cx >= (long long)bx.e[0]) continue;
+          if (j == 1 && line == 4 && self_ok) r[1] = (int)o;
+          else r[j] = rank_lookup(bitmap, prefix, row_base + (unsigned long long)cx);
+        }
       }
     }
 #pragma unroll
@@ -483,6 +488,20 @@ __global__ void k_ssc_nbr_rank(const int32_t *__restrict__ c, long long n, Box b
     const int cnt = __syncthreads_count(r[j] >= 0);
     if (threadIdx.x == 0 && cnt) atomicAdd(&counts[j * 9 + line], (unsigned long long)cnt);
   }
+}
+
+// sites of another grid (SoA coordinates, stride `stride`) -> row in this grid or -1, from the ranking structure
+__global__ void k_query_rank(const int32_t *__restrict__ c, long long stride, long long n, Box bx,
+                             const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
+                             int32_t *__restrict__ rows) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const unsigned ux = (unsigned)(c[i] - bx.o[0]), uy = (unsigned)(c[stride + i] - bx.o[1]),
+                 uz = (unsigned)(c[2 * stride + i] - bx.o[2]), ub = (unsigned)(c[3 * stride + i] - bx.o[3]);
+  int r = -1;
+  if (ux < bx.e[0] && uy < bx.e[1] && uz < bx.e[2] && ub < bx.e[3])
+    r = rank_lookup(bitmap, prefix, (((unsigned long long)ub * bx.e[2] + uz) * bx.e[1] + uy) * bx.e[0] + ux);
+  rows[i] = r;
 }
 
 // 2x2x2 / stride 2: offset of a fine site inside its coarse cell k = (x&1)*4 + (y&1)*2 + (z&1)
@@ -689,7 +708,7 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
     SCN_TRY(dev_alloc_t(&nbr_counts_d, 27, s));
     SCN_CUDA(cudaMemsetAsync(nbr_counts_d, 0, 27 * 8, s));
     SCN_TRY(dev_alloc_t(&g.nbr, (size_t)n * 27, s));
-    k_ssc_nbr_rank<<<dim3(blocks_for(n, 256), 9), 256, 0, s>>>(g.coords, n, bx, g.bitmap, g.prefix, g.nbr, nbr_counts_d, nullptr);
+    k_ssc_nbr_rank<<<dim3(blocks_for(n, 256), 9), 256, 0, s>>>(g.coords, n, bx, g.bitmap, g.prefix, nullptr, 1, g.nbr, nbr_counts_d, nullptr);
     SCN_LAUNCHED();
     SCN_TRY(read_back(nbr_counts, nbr_counts_d, sizeof(nbr_counts), 1, s, false));
   }
@@ -793,7 +812,7 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
     k_conv_maps<<<blocks_for(n_src, 256), 256, 0, s>>>(src_coords, n_src, g.src_row, 0, g.child, g.fine_up, counts_d, info_d, src);
     if (with_ssc) {
       if ((rc = dev_alloc_t(&g.nbr, (size_t)n_max * 27, s)) != SCN_OK) break;
-      k_ssc_nbr_rank<<<dim3(blocks_for(n_max, 256), 9), 256, 0, s>>>(g.coords, 0, bx, g.bitmap, g.prefix, g.nbr, counts_d + 8, info_d);
+      k_ssc_nbr_rank<<<dim3(blocks_for(n_max, 256), 9), 256, 0, s>>>(g.coords, 0, bx, g.bitmap, g.prefix, nullptr, 1, g.nbr, counts_d + 8, info_d);
     }
     for (int i = 0; i < 6 + (with_ssc ? 1 : 0); ++i) g_launches.fetch_add(1, std::memory_order_relaxed);
     if (cudaGetLastError() != cudaSuccess) {
@@ -848,14 +867,17 @@ int grid_build_coarse(Grid &g, const Grid &fine, bool with_ssc, cudaStream_t s) 
   return grid_build_coarse_chain(&one, 1, fine, with_ssc, s);
 }
 
-int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_stride, int32_t *rows,
+int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_stride, int32_t *rows, bool by_rank,
                cudaStream_t s) {
   if (n == 0) return SCN_OK;
   if (g.n == 0) {
     SCN_CUDA(cudaMemsetAsync(rows, 0xFF, (size_t)n * 4, s));
     return SCN_OK;
   }
-  k_query<<<blocks_for(n, 256), 256, 0, s>>>(coords_soa, soa_stride, n, g.table, g.mask, rows);
+  if (by_rank && g.bitmap && g.prefix)
+    k_query_rank<<<blocks_for(n, 256), 256, 0, s>>>(coords_soa, soa_stride, n, g.box, g.bitmap, g.prefix, rows);
+  else
+    k_query<<<blocks_for(n, 256), 256, 0, s>>>(coords_soa, soa_stride, n, g.table, g.mask, rows);
   SCN_LAUNCHED();
   return SCN_OK;
 }
@@ -865,8 +887,13 @@ static int nbr_common(const Grid &g, const Grid &lookup, const int32_t *absent, 
   unsigned long long *counts_d = nullptr;
   SCN_TRY(dev_alloc_t(&counts_d, 27, s));
   SCN_CUDA(cudaMemsetAsync(counts_d, 0, 27 * 8, s));
-  dim3 grid(blocks_for(g.n, 256), 27);
-  k_ssc_nbr<<<grid, 256, 0, s>>>(g.coords, g.n, lookup.table, lookup.mask, absent, self_ok, nbr, counts_d, nullptr);
+  if (lookup.bitmap && lookup.prefix) {
+    k_ssc_nbr_rank<<<dim3(blocks_for(g.n, 256), 9), 256, 0, s>>>(g.coords, g.n, lookup.box, lookup.bitmap, lookup.prefix, absent,
+                                                                self_ok, nbr, counts_d, nullptr);
+  } else {
+    dim3 grid(blocks_for(g.n, 256), 27);
+    k_ssc_nbr<<<grid, 256, 0, s>>>(g.coords, g.n, lookup.table, lookup.mask, absent, self_ok, nbr, counts_d, nullptr);
+  }
   SCN_LAUNCHED();
   unsigned long long h[27];
   SCN_CUDA(cudaMemcpyAsync(h, counts_d, sizeof(h), cudaMemcpyDeviceToHost, s));
@@ -884,7 +911,7 @@ int grid_build_ssc(Grid &g, cudaStream_t s) {
     unsigned long long *counts_d = nullptr, h[27];
     SCN_TRY(dev_alloc_t(&counts_d, 27, s));
     SCN_CUDA(cudaMemsetAsync(counts_d, 0, 27 * 8, s));
-    k_ssc_nbr_rank<<<dim3(blocks_for(g.n, 256), 9), 256, 0, s>>>(g.coords, g.n, g.box, g.bitmap, g.prefix, g.nbr, counts_d, nullptr);
+    k_ssc_nbr_rank<<<dim3(blocks_for(g.n, 256), 9), 256, 0, s>>>(g.coords, g.n, g.box, g.bitmap, g.prefix, nullptr, 1, g.nbr, counts_d, nullptr);
     SCN_LAUNCHED();
     SCN_TRY(read_back(h, counts_d, sizeof(h), 1, s, true));
     take(h, sizeof(h), 1);

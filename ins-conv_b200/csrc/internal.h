@@ -117,7 +117,8 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
 bool ssc_expected();
 int grid_build_ssc(Grid &g, cudaStream_t s);               // fills nbr / nbr_count
 int grid_build_conv(Grid &coarse, const Grid &fine, cudaStream_t s);  // fills child / fine_up
-int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_stride, int32_t *rows,
+// by_rank: answer from the grid's ranking structure (bitmap + prefix sums) instead of probing its hash table
+int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_stride, int32_t *rows, bool by_rank,
                cudaStream_t s);
 // ordered compaction of a [K][n] map (entries >= 0) into `expected_pairs` pairs, k-major and ascending
 // in the column inside each k.  swap = 0: pair (value, column); swap = 1: pair (column, value).
