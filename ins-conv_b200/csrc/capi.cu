@@ -540,6 +540,28 @@ int scn_incre_input_layer_forward(scn_metadata *m, scn_metadata *pre, const floa
   cudaStream_t s = (cudaStream_t)stream;
   SCN_TRY(need_incre(m, pre, m->input_size.data(), &g, &pg, &im, s));
   if (g->n && (!in || !out || !pre_out)) return fail(SCN_E_INVALID, "null features");
+  // The incremental neighbour maps of every scale both frames have, now and with one host round trip, instead of
+  // one round trip per scale in the middle of the network (once a network has used neighbour maps at all).
+  if (want_ssc()) {
+    std::vector<IncreNbrJob> jobs;
+    std::vector<IncreMaps *> ims;
+    for (auto &kv : m->grids) {
+      Grid *gl = kv.second.get(), *pl = pre->find(kv.first.data());
+      if (!pl || gl->n == 0) continue;
+      Grid *g2, *p2;
+      IncreMaps *im2;
+      SCN_TRY(need_incre(m, pre, kv.first.data(), &g2, &p2, &im2, s));
+      if (im2->nbr2) continue;
+      SCN_TRY(dev_alloc_t(&im2->nbr2, (size_t)gl->n * 27, s));
+      jobs.push_back(IncreNbrJob{gl, pl, im2->pre_exist, im2->nbr2, im2->nbr2_count});
+      ims.push_back(im2);
+    }
+    SCN_TRY(build_incre_nbr_batch(jobs.data(), (int)jobs.size(), s));
+    for (IncreMaps *x : ims) {
+      x->nbr2_total = 0;
+      for (int k = 0; k < 27; ++k) x->nbr2_total += x->nbr2_count[k];
+    }
+  }
   return input_forward(*g, in, out, planes, m->mode == 4, im->pre_exist, pg, pre_out, s);
 }
 int scn_incre_output_layer_forward(scn_metadata *m, scn_metadata *pre, const float *in, float *out,

@@ -882,11 +882,9 @@ int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_
   return SCN_OK;
 }
 
-static int nbr_common(const Grid &g, const Grid &lookup, const int32_t *absent, int self_ok, int32_t *nbr,
-                      int64_t *counts_host, cudaStream_t s) {
-  unsigned long long *counts_d = nullptr;
-  SCN_TRY(dev_alloc_t(&counts_d, 27, s));
-  SCN_CUDA(cudaMemsetAsync(counts_d, 0, 27 * 8, s));
+// launches the neighbour-map kernel of g looked up in `lookup`; counts_d: 27 zeroed device counters
+static int nbr_launch(const Grid &g, const Grid &lookup, const int32_t *absent, int self_ok, int32_t *nbr,
+                      unsigned long long *counts_d, cudaStream_t s) {
   if (lookup.bitmap && lookup.prefix) {
     k_ssc_nbr_rank<<<dim3(blocks_for(g.n, 256), 9), 256, 0, s>>>(g.coords, g.n, lookup.box, lookup.bitmap, lookup.prefix, absent,
                                                                 self_ok, nbr, counts_d, nullptr);
@@ -895,11 +893,42 @@ static int nbr_common(const Grid &g, const Grid &lookup, const int32_t *absent, 
     k_ssc_nbr<<<grid, 256, 0, s>>>(g.coords, g.n, lookup.table, lookup.mask, absent, self_ok, nbr, counts_d, nullptr);
   }
   SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+static int nbr_common(const Grid &g, const Grid &lookup, const int32_t *absent, int self_ok, int32_t *nbr,
+                      int64_t *counts_host, cudaStream_t s) {
+  unsigned long long *counts_d = nullptr;
+  SCN_TRY(dev_alloc_t(&counts_d, 27, s));
+  SCN_CUDA(cudaMemsetAsync(counts_d, 0, 27 * 8, s));
+  SCN_TRY(nbr_launch(g, lookup, absent, self_ok, nbr, counts_d, s));
   unsigned long long h[27];
-  SCN_CUDA(cudaMemcpyAsync(h, counts_d, sizeof(h), cudaMemcpyDeviceToHost, s));
-  SCN_CUDA(cudaStreamSynchronize(s));
+  SCN_TRY(read_back(h, counts_d, sizeof(h), 1, s, true));
+  take(h, sizeof(h), 1);
   dev_free(counts_d, s);
   for (int k = 0; k < 27; ++k) counts_host[k] = (int64_t)h[k];
+  return SCN_OK;
+}
+
+// The incremental neighbour maps of several scales with one host round trip: jobs[i] = (grid, saved grid, pre_exist,
+// nbr2 out, counts out [27]).
+int build_incre_nbr_batch(const IncreNbrJob *jobs, int count, cudaStream_t s) {
+  if (count <= 0) return SCN_OK;
+  unsigned long long *counts_d = nullptr;
+  SCN_TRY(dev_alloc_t(&counts_d, (size_t)count * 27, s));
+  SCN_CUDA(cudaMemsetAsync(counts_d, 0, (size_t)count * 27 * 8, s));
+  for (int i = 0; i < count; ++i) {
+    const IncreNbrJob &j = jobs[i];
+    if (j.g->n == 0) continue;
+    if (j.pre->n == 0) SCN_CUDA(cudaMemsetAsync(j.nbr2, 0xFF, (size_t)j.g->n * 27 * 4, s));
+    else SCN_TRY(nbr_launch(*j.g, *j.pre, j.pre_exist, 0, j.nbr2, counts_d + 27 * i, s));
+  }
+  std::vector<unsigned long long> h((size_t)count * 27);
+  SCN_CUDA(cudaMemcpyAsync(h.data(), counts_d, h.size() * 8, cudaMemcpyDeviceToHost, s));
+  SCN_CUDA(cudaStreamSynchronize(s));
+  dev_free(counts_d, s);
+  for (int i = 0; i < count; ++i)
+    for (int k = 0; k < 27; ++k) jobs[i].counts_host[k] = (int64_t)h[(size_t)i * 27 + k];
   return SCN_OK;
 }
 

@@ -128,6 +128,13 @@ int grid_locations(const Grid &g, int64_t *out_host, cudaStream_t s);
 // incremental helpers
 int build_incre_nbr(const Grid &g, const Grid &pre, const int32_t *pre_exist, int32_t *nbr2,
                     int64_t *counts_host, cudaStream_t s);
+struct IncreNbrJob {
+  const Grid *g, *pre;
+  const int32_t *pre_exist;
+  int32_t *nbr2;
+  int64_t *counts_host;  // [27]
+};
+int build_incre_nbr_batch(const IncreNbrJob *jobs, int count, cudaStream_t s);
 int build_incre_up(const Grid &coarse, const int32_t *pe_coarse, const int32_t *pe_fine, int32_t *up2,
                    cudaStream_t s);
 
