@@ -1051,15 +1051,20 @@ bool tc_f16_shape(int64_t K, int64_t Cin, int64_t Cout) {
   return K >= 1 && K <= 27 && Cin >= 32 && Cin % 32 == 0 && Cout >= 32 && Cout % 32 == 0 && Cout <= 256 &&
          persist_stages(K, Cout) >= 4;
 }
-int64_t tc_f16_packed_size(int64_t K, int64_t Cin, int64_t Cout) { return K * Cout * padded_planes(Cin); }
+// the pack of a wide layer: the tcgen05 layout, followed (where the slab kernel covers the shape) by the warp-fragment
+// layout that kernel reads on small grids
+int64_t tc_f16_packed_size(int64_t K, int64_t Cin, int64_t Cout) {
+  return K * Cout * padded_planes(Cin) + (warp_slab_f16_shape(K, Cin, Cout) ? K * Cin * Cout : 0);
+}
 
 int tc_pack_weights_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s) {
   if (!tc_f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "shape cannot be packed for the fp16 tcgen05 kernel");
   if (!W || !packed) return fail(SCN_E_INVALID, "null pointer");
-  const long long total = tc_f16_packed_size(K, Cin, Cout);
+  const long long total = K * Cout * padded_planes(Cin);
   k_pack_weights_tc_f16<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(W, static_cast<__half *>(packed), (int)Cin, (int)Cout,
                                                                        (int)padded_planes(Cin), total);
   SCN_LAUNCHED();
+  if (warp_slab_f16_shape(K, Cin, Cout)) SCN_TRY(warp_mma_pack_f16_any(W, K, Cin, Cout, static_cast<__half *>(packed) + total, s));
   return SCN_OK;
 }
 
@@ -1068,6 +1073,16 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
                        int64_t init_stride, cudaStream_t s) {
   if (!tc_f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "the fp16 tcgen05 gather-GEMM takes planes that are multiples of 32, n_out <= 224");
   if (!map && K != 1) return fail(SCN_E_INVALID, "no map given for a filter volume above 1");
+  {
+    // small grids: too few 128-row tiles for the persistent kernel to fill the GPU without splitting reductions
+    static const long long slab_rows = []() {
+      const char *e = getenv("INSCONV_SLAB_MAX_ROWS");  // development aid
+      return e ? atoll(e) : 4096ll;
+    }();
+    if (n_out <= slab_rows && warp_slab_f16_shape(K, Cin, Cout))
+      return gather_mma_slab_f16(in, in_stride, map, K, n_out, static_cast<const __half *>(Wp) + K * Cout * padded_planes(Cin), bias,
+                                 out, out_stride, Cin, Cout, init, init_stride, s);
+  }
   if (in_stride % 8 != 0 || out_stride % 4 != 0 || !aligned16(in) || !aligned16(Wp) || !aligned16(out) ||
       (bias && !aligned16(bias)) || (init && (!aligned16(init) || init_stride % 4 != 0)))
     return fail(SCN_E_INVALID, "rows must be 16-byte aligned (fp16 stride a multiple of 8, fp32 strides multiples of 4)");

@@ -336,6 +336,86 @@ k_gather_mma_f16(const __half *__restrict__ in, long long in_stride, const int32
   store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, init, init_stride, g, t);
 }
 
+// Wide layers on small grids (the deep levels of a UNet: a few hundred to a few thousand rows, 96-224 planes).  There
+// the tcgen05 kernel has too few 128-row tiles to fill the GPU, shares a tile's reduction among work items and needs a
+// second launch to add the partial tiles; this form gives a warp 16 rows and a slab of 32 output planes
+// (blockIdx.y) and lets it run the whole reduction, so the layer is one launch of rows/16 x n_out/32 independent warps.
+template <int C32, int NTR>
+__device__ __forceinline__ void mma_rows_slab(float (&acc)[2][NTR][4], const FragH<C32 * 32, NTR> &f, const uint4 *__restrict__ wk,
+                                              int mtc_total) {
+#pragma unroll
+  for (int c = 0; c < C32; ++c) {
+    uint4 a[2][2];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      a[m][0] = __ldg(wk + ((c * mtc_total + m) * 2) * 32);
+      a[m][1] = __ldg(wk + ((c * mtc_total + m) * 2 + 1) * 32);
+    }
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+      for (int n = 0; n < NTR; ++n) mma_m16n8k16_f16(acc[m][n], a[m][0], f.v[n][c].x, f.v[n][c].y);
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+      for (int n = 0; n < NTR; ++n) mma_m16n8k16_f16(acc[m][n], a[m][1], f.v[n][c].z, f.v[n][c].w);
+  }
+}
+
+template <int C32, int NTR>
+__global__ void __launch_bounds__(kWarps * 32, 3)
+k_gather_mma_f16_slab(const __half *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
+                      const uint4 *__restrict__ Wp, int Cout, const float *__restrict__ bias, float *out, long long out_stride,
+                      const float *init, long long init_stride) {
+  constexpr int ROWS = 8 * NTR, CIN = C32 * 32;
+  __shared__ int s_map[kWarps][kMaxK * ROWS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const long long row0 = ((long long)blockIdx.x * kWarps + warp) * ROWS;
+  if (row0 >= n_out) return;
+  const int slab = blockIdx.y, mtc_total = Cout >> 4;
+  int *mp = s_map[warp];
+  MapRegs<ROWS> regs;
+  load_map<ROWS>(regs, row0, map, K, n_out, lane);
+  unsigned int mask = publish_map<ROWS>(regs, mp, K, lane);
+  float acc[2][NTR][4];
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int n = 0; n < NTR; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
+  const int WK = C32 * mtc_total * 2 * 32;  // uint4 per offset
+  const __half *in_t = in + 8 * t;
+  const uint4 *wl = Wp + lane + (2 * slab) * 2 * 32;  // this slab's two 16-plane tiles inside a 32-plane block's fragments
+  if (mask) {
+    FragH<CIN, NTR> f0, f1;
+    int k0 = __ffs(mask) - 1;
+    mask &= mask - 1;
+    load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
+    while (true) {
+      int k1 = -1;
+      if (mask) {
+        k1 = __ffs(mask) - 1;
+        mask &= mask - 1;
+        load_rows_h<CIN, NTR>(f1, mp + k1 * ROWS, in_t, in_stride, g);
+      }
+      mma_rows_slab<C32, NTR>(acc, f0, wl + (long long)k0 * WK, mtc_total);
+      if (k1 < 0) break;
+      k0 = -1;
+      if (mask) {
+        k0 = __ffs(mask) - 1;
+        mask &= mask - 1;
+        load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
+      }
+      mma_rows_slab<C32, NTR>(acc, f1, wl + (long long)k1 * WK, mtc_total);
+      if (k0 < 0) break;
+    }
+  }
+  store_acc<32, NTR>(acc, row0, n_out, bias ? bias + 32 * slab : nullptr, out + 32 * slab, out_stride,
+                     init ? init + 32 * slab : nullptr, init_stride, g, t);
+}
+
 // W [K][n_in][n_out] fp32 -> fp16 fragments [K][n_in/32][n_out/16][2][lane][8]: half e of (k, c, m, j, lane = 4g + t)
 // is W[k][32c + 8t + 4j + 2(e >> 2) + (e & 1)][16m + g + 8((e >> 1) & 1)]
 __global__ void k_pack_weights_f16(const float *__restrict__ W, __half *__restrict__ Wp, int Cin, int Cout, long long total) {
@@ -521,6 +601,43 @@ int warp_mma_pack_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void
   if (!W || !packed) return fail(SCN_E_INVALID, "null pointer");
   const long long total = K * Cin * Cout;
   k_pack_weights_f16<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(W, static_cast<__half *>(packed), (int)Cin, (int)Cout, total);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+// warp-fragment pack for any n_in multiple of 32 and n_out multiple of 32 (the slab kernel's weights)
+int warp_mma_pack_f16_any(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s) {
+  const long long total = K * Cin * Cout;
+  k_pack_weights_f16<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(W, static_cast<__half *>(packed), (int)Cin, (int)Cout, total);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+bool warp_slab_f16_shape(int64_t K, int64_t Cin, int64_t Cout) {
+  return K >= 1 && K <= kMaxK && Cin % 32 == 0 && Cin >= 96 && Cin <= 224 && Cout % 32 == 0 && Cout >= 32 && Cout <= 256;
+}
+
+int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
+                        const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
+                        int64_t init_stride, cudaStream_t s) {
+  if (!warp_slab_f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "shape not covered by the slab kernel");
+  if (in_stride % 8 != 0 || !aligned16(in) || !aligned16(Wp))
+    return fail(SCN_E_INVALID, "fp16 rows must be 16-byte aligned with a stride that is a multiple of 8 elements");
+  const __half *inh = static_cast<const __half *>(in);
+  const uint4 *W4 = static_cast<const uint4 *>(Wp);
+  const long long tiles = (n_out + 15) / 16;
+  const dim3 grid((unsigned)((tiles + kWarps - 1) / kWarps), (unsigned)(Cout / 32));
+#define SCN_SLAB_LAUNCH(C32)                                                                                          \
+  k_gather_mma_f16_slab<C32, 2><<<grid, kWarps * 32, 0, s>>>(inh, in_stride, map, K, n_out, W4, (int)Cout, bias, out, \
+                                                             out_stride, init, init_stride)
+  switch ((int)(Cin / 32)) {
+    case 3: SCN_SLAB_LAUNCH(3); break;
+    case 4: SCN_SLAB_LAUNCH(4); break;
+    case 5: SCN_SLAB_LAUNCH(5); break;
+    case 6: SCN_SLAB_LAUNCH(6); break;
+    default: SCN_SLAB_LAUNCH(7); break;
+  }
+#undef SCN_SLAB_LAUNCH
   SCN_LAUNCHED();
   return SCN_OK;
 }

@@ -244,6 +244,36 @@ def test_f16_activations_bn_then_convolutions(cuda, n_in, n_out):
     cabi.check_errors()
 
 
+@pytest.mark.parametrize("n_in,n_out", [(96, 96), (128, 160), (160, 128), (224, 224), (192, 32)])
+def test_f16_wide_layers_on_small_grids(cuda, n_in, n_out):
+    # a few thousand rows and many planes (the deep levels of a UNet): the slab kernel, 16 rows x 32 output planes per
+    # warp, instead of the tcgen05 kernel with split reductions
+    import ctypes as C
+    c = np.concatenate([synth.sphere_surface((30, 30, 30), 11), synth.sphere_surface((60, 50, 40), 8)], 0)
+    m = cabi.Metadata()
+    n = m.input_layer_build(128, torch.from_numpy(c).to(cuda), mode=4)
+    g = O.Grid(c)
+    assert n == g.n and n < 4096
+    rng = np.random.RandomState(n_in + 3 * n_out)
+    stream = torch.cuda.current_stream().cuda_stream
+    x = np.maximum(rng.randn(g.n, n_in), 0).astype(np.float32)  # like a BatchNorm+ReLU output
+    h = torch.from_numpy(x).to(cuda).half()
+    ref = h.float().cpu().numpy()
+    w = synth.kaiming_uniform(rng, 27, n_in, n_out)
+    dw = torch.from_numpy(w).to(cuda)
+    pw = torch.empty(cabi.lib().scn_packed_size_f16(27, n_in, n_out), dtype=torch.float16, device=cuda)
+    cabi.call("scn_pack_weights_f16", cabi.ptr(dw), 27, n_in, n_out, cabi.ptr(pw), stream)
+    out = torch.empty(g.n, n_out, dtype=torch.float32, device=cuda)
+    fl = C.c_double(0)
+    cabi.call("scn_ssc_forward", m.h, cabi.size3(128), cabi.ptr(h), n_in, cabi.ptr(out), n_out, cabi.ptr(pw), None, n_in, n_out,
+              cabi.PREC_F16, stream, C.byref(fl))
+    torch.cuda.synchronize()
+    cabi.check_errors()
+    want = torch.as_tensor(O.conv_forward(ref, w, O.ssc_rules(g), g.n, None))
+    close(out, want, TF32_TOL)
+    assert float((out.cpu() - want).abs().max()) / float(want.abs().max()) < 3e-3
+
+
 def test_conv_deconv_nin_tf32(cuda):
     m, g = _scene(cuda, 1)
     rng = np.random.RandomState(17)
