@@ -2,8 +2,8 @@
 (reference: sparseconvnet/sequential.py:9-25, tables.py:13-55, identity.py:10-15)."""
 import torch
 
-from . import SCN
 from .tensor import SparseConvNetTensor
+from .utils import _precision
 
 
 class _Container(torch.nn.Sequential):
@@ -22,7 +22,7 @@ def _run(module, input, increment):
 
 class Sequential(_Container):
     def forward(self, input, increment=False):
-        if SCN.get_precision() != "fp16":
+        if _precision[0] != "fp16":
             for module in self._modules.values():
                 input = _run(module, input, increment)
             return input

@@ -22,7 +22,7 @@ import sparseconvnet
 from . import SCN
 from .metadata import Metadata
 from .tensor import SparseConvNetTensor
-from .utils import toLongTensor, optionalTensor
+from .utils import toLongTensor, optionalTensor, _precision
 
 _NONE = torch.empty(0)
 
@@ -44,9 +44,9 @@ def _residual(input, increment):
 def _packed(module):
     """The tensor-core kernels read weights transposed.  The copy is made once per weight version and kept on the
     module (keyed on the Parameter object, its version counter and its address), instead of once per call."""
-    if SCN.get_precision() == "fp32":
+    if _precision[0] == "fp32":
         return _NONE
-    w = module.weight
+    w = module._parameters["weight"]
     c = module.__dict__.get("_pack_cache")
     if c is not None and c[0] is w and c[1] == w._version and c[2] == w.data_ptr():
         return c[3]
@@ -60,7 +60,7 @@ def _packed_for(module, features):
     'fp16' precision), else the tf32 pack."""
     if features.dtype != torch.float16:
         return _packed(module)
-    w = module.weight
+    w = module._parameters["weight"]
     c = module.__dict__.get("_pack_cache_h")
     if c is not None and c[0] is w and c[1] == w._version and c[2] == w.data_ptr():
         return c[3]
@@ -127,13 +127,13 @@ class SubmanifoldConvolution(Module):
         out = input.features.new_empty(0, dtype=torch.float32)
         if not _residual(input, increment):
             madds = SCN.SubmanifoldConvolution_updateOutput(
-                input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
+                input.spatial_size, self.filter_size, input.metadata, input.features, out, self._parameters["weight"],
                 optionalTensor(self, "bias"), self.dilated_rate, _packed_for(self, input.features),
                 _NONE if addend is None else addend)
             _keep(self, save_meta=input.metadata, save_input_feats=input.features)
         else:
             madds = SCN.Incre_SubmanifoldConvolution_updateOutput(
-                input.spatial_size, self.filter_size, input.metadata, input.features, out, self.weight,
+                input.spatial_size, self.filter_size, input.metadata, input.features, out, self._parameters["weight"],
                 optionalTensor(self, "bias"), self.save_meta, _f32(self, self.save_input_feats), _packed(self))
         _count(madds, out)
         return input.like(out)
@@ -170,7 +170,7 @@ class Convolution(_Strided):
         out = input.features.new_empty(0, dtype=torch.float32)
         op = SCN.Incre_Convolution_updateOutput if _residual(input, increment) else SCN.Convolution_updateOutput
         madds = op(input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                   out, self.weight, optionalTensor(self, "bias"), _packed_for(self, input.features))
+                   out, self._parameters["weight"], optionalTensor(self, "bias"), _packed_for(self, input.features))
         _count(madds, out)
         return input.like(out, out_size)
 
@@ -189,13 +189,13 @@ class Deconvolution(_Strided):
         if not _residual(input, increment):
             madds = SCN.Deconvolution_updateOutput(
                 input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                out, self.weight, optionalTensor(self, "bias"), _packed_for(self, input.features))
+                out, self._parameters["weight"], optionalTensor(self, "bias"), _packed_for(self, input.features))
             _keep(self, save_meta=input.metadata, save_input_feats=input.features)
         else:
             madds = SCN.Incre_Deconvolution_updateOutput(
                 input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                out, self.weight, optionalTensor(self, "bias"), self.save_meta, _f32(self, self.save_input_feats),
-                _packed(self))
+                out, self._parameters["weight"], optionalTensor(self, "bias"), self.save_meta,
+                _f32(self, self.save_input_feats), _packed(self))
         _count(madds, out)
         return input.like(out, out_size)
 
@@ -225,18 +225,22 @@ class BatchNormalization(Module):
         Sequential asks for it when the next module is a convolution that reads fp16 rows."""
         assert input.features.nelement() == 0 or input.features.size(1) == self.nPlanes, \
             (self.nPlanes, input.features.shape)
-        half_rows = half_rows and not self.training and not _residual(input, increment) and self.nPlanes % 8 == 0
-        out = input.features.new_empty(0, dtype=torch.float16 if half_rows else torch.float32)
-        scratch = input.features.new_empty(0)
-        if not _residual(input, increment):
+        residual = _residual(input, increment)
+        half_rows = half_rows and not self.training and not residual and self.nPlanes % 8 == 0
+        feats = input.features
+        out = feats.new_empty(0, dtype=torch.float16 if half_rows else torch.float32)
+        mean, var = self._buffers["running_mean"], self._buffers["running_var"]
+        if not residual:
+            # the batch-statistics outputs are only written in training mode
+            scratch = feats.new_empty(0) if self.training else _NONE
             SCN.BatchNormalization_updateOutput(
-                input.features, out, scratch, input.features.new_empty(0), self.running_mean, self.running_var,
+                feats, out, scratch, feats.new_empty(0) if self.training else _NONE, mean, var,
                 optionalTensor(self, "weight"), optionalTensor(self, "bias"), self.eps, self.momentum, self.training,
                 self.leakiness)
             _keep(self, save_output=input.like(out), save_input=input)
         else:
             SCN.Incre_BatchNormalization_updateOutput(
-                input.features, out, scratch, scratch, self.running_mean, self.running_var,
+                feats, out, _NONE, _NONE, mean, var,
                 optionalTensor(self, "weight"), optionalTensor(self, "bias"), self.eps, self.momentum, self.training,
                 self.leakiness, input.metadata, self.save_output.metadata, _f32(self, self.save_output.features),
                 self.save_input.features, input.spatial_size)

@@ -28,7 +28,12 @@ def set_precision(p):
     'fp16' (as tf32, and a BatchNorm directly in front of a convolution with 32 or 64 planes on both sides hands it
     fp16 rows: half the bytes to gather, 11 significant bits instead of tf32's 10)."""
     SCN.set_precision(p)
+    _precision[0] = SCN.get_precision()
 
 
 def get_precision():
     return SCN.get_precision()
+
+
+# what set_precision() last selected: the modules read this mirror on every call instead of asking the extension
+_precision = [SCN.get_precision()]
