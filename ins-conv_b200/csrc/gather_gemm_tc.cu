@@ -1074,12 +1074,14 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
   if (!tc_f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "the fp16 tcgen05 gather-GEMM takes planes that are multiples of 32, n_out <= 224");
   if (!map && K != 1) return fail(SCN_E_INVALID, "no map given for a filter volume above 1");
   {
-    // small grids: too few 128-row tiles for the persistent kernel to fill the GPU without splitting reductions
+    // small grids: too few 128-row tiles for the persistent kernel to fill the GPU without splitting reductions.
+    // Below ~500 rows the slab kernel in turn has too few warps (rows/16 x n_out/32) and its serial reduction per
+    // warp is longer than the split reduction plus its second launch (measured on 60- and 230-row levels).
     static const long long slab_rows = []() {
       const char *e = getenv("INSCONV_SLAB_MAX_ROWS");  // development aid
       return e ? atoll(e) : 4096ll;
     }();
-    if (n_out <= slab_rows && warp_slab_f16_shape(K, Cin, Cout))
+    if (n_out >= 512 && n_out <= slab_rows && warp_slab_f16_shape(K, Cin, Cout))
       return gather_mma_slab_f16(in, in_stride, map, K, n_out, static_cast<const __half *>(Wp) + K * Cout * padded_planes(Cin), bias,
                                  out, out_stride, Cin, Cout, init, init_stride, s);
   }
