@@ -1076,10 +1076,11 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
   {
     // small grids: too few 128-row tiles for the persistent kernel to fill the GPU without splitting reductions.
     // Below ~500 rows the slab kernel in turn has too few warps (rows/16 x n_out/32) and its serial reduction per
-    // warp is longer than the split reduction plus its second launch (measured on 60- and 230-row levels).
+    // warp is longer than the split reduction plus its second launch (measured on 60- and 230-row levels).  Measured
+    // with 96 planes: 4.4k rows 17.8 us against 25.6 us, 16k rows 32.0 against 32.4 (and one launch instead of two).
     static const long long slab_rows = []() {
       const char *e = getenv("INSCONV_SLAB_MAX_ROWS");  // development aid
-      return e ? atoll(e) : 4096ll;
+      return e ? atoll(e) : 16384ll;
     }();
     if (n_out >= 512 && n_out <= slab_rows && warp_slab_f16_shape(K, Cin, Cout))
       return gather_mma_slab_f16(in, in_stride, map, K, n_out, static_cast<const __half *>(Wp) + K * Cout * padded_planes(Cin), bias,
