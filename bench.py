@@ -80,6 +80,9 @@ def make_scene(seed, voxels):
 
 
 class ClockSampler(object):
+    """SM clock and throttle reasons of one GPU, sampled while the timed legs run.  In-process NVML queries from a
+    thread (a few tens of microseconds each, every 100 ms); `nvidia-smi -lms` as a subprocess is the fallback.  (The
+    subprocess form perturbs what it watches: one of its queries landing in a 35 ms timed region doubled the region.)"""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
@@ -88,8 +91,33 @@ class ClockSampler(object):
         self.index = index
         self.proc = None
         self.lines = []
+        self.nvml = None
+        self.samples = []  # (sm_mhz, max_mhz, reasons bitmask)
+        self.running = False
+        self.mode = os.environ.get("INSCONV_CLOCK_SAMPLER", "nvml")  # nvml | smi | off (development aid)
 
     def start(self):
+        if self.mode == "off":
+            return
+        if self.mode == "nvml":
+            try:
+                import pynvml
+                pynvml.nvmlInit()
+                visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+                phys = self.index
+                if visible:
+                    ids = [v.strip() for v in visible.split(",") if v.strip()]
+                    if self.index < len(ids) and ids[self.index].isdigit():
+                        phys = int(ids[self.index])
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+                self.nvml = pynvml
+                self._sample_nvml()  # the first query initialises the library's state for the device
+                self.running = True
+                self.thread = threading.Thread(target=self._loop_nvml, daemon=True)
+                self.thread.start()
+                return
+            except Exception:
+                self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
                                           "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
@@ -102,13 +130,41 @@ class ClockSampler(object):
         except Exception:
             self.proc = None
 
+    def _sample_nvml(self):
+        n = self.nvml
+        sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+        mx = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
+        reasons = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+        self.samples.append((float(sm), float(mx), int(reasons)))
+
+    def _loop_nvml(self):
+        while self.running:
+            try:
+                self._sample_nvml()
+            except Exception:
+                pass
+            time.sleep(0.1)
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self.running = False
+            self.thread.join(timeout=2)
+            n = self.nvml
+            names = {"hw_slowdown": n.nvmlClocksThrottleReasonHwSlowdown,
+                     "hw_thermal_slowdown": n.nvmlClocksThrottleReasonHwThermalSlowdown,
+                     "sw_thermal_slowdown": n.nvmlClocksThrottleReasonSwThermalSlowdown,
+                     "sw_power_cap": n.nvmlClocksThrottleReasonSwPowerCap}
+            reasons = sorted(k for k, bit in names.items() if any(s[2] & bit for s in self.samples))
+            sm = [s[0] for s in self.samples]
+            mx = [s[1] for s in self.samples]
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                    "samples": len(sm), "reasons": reasons, "source": "nvml"}
         if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock sampler available"]}
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -129,7 +185,7 @@ class ClockSampler(object):
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
 def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
