@@ -246,9 +246,10 @@ def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
 
 
 def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
-    """Grid build (points -> ranked sites + open-addressing table + input rules) through the C ABI, coordinates
-    resident on the device.  Algorithmic bytes: 32 per point in (int64 x,y,z,batch), 8 per table slot,
-    12 per site (coordinates out), 4 per point (point -> site)."""
+    """Grid build (points -> ranked sites + input rules) through the C ABI, coordinates resident on the device.
+    Algorithmic bytes: 32 per point in (int64 x,y,z,batch), 12 per site (coordinates out), 4 per point (point ->
+    site); with the open-addressing table (filled on the first coordinate query, timed as build + one query of one
+    coordinate) 8 per table slot more."""
     import torch
     from insconv import cabi, synth
     out = []
@@ -267,12 +268,16 @@ def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
         d = torch.from_numpy(c4).to(dev)
         m = cabi.Metadata()
 
-        def median_build():
+        probe = torch.zeros(4, 1, dtype=torch.int32, device=dev)
+
+        def median_build(with_table=False):
             ts = []
             for i in range(warmup + steps):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
                 n = m.input_layer_build(size, d, mode=4)
+                if with_table:
+                    m.query(size, probe)
                 e1.record()
                 torch.cuda.synchronize()
                 if i >= warmup:
@@ -281,7 +286,8 @@ def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
 
         cabi.call("scn_set_build_ahead", 0, 0)  # the hash build alone: input scale, no neighbour map
         t, n = median_build()
-        # the 3x3x3 rulebook (27 table lookups per site) of that grid, built on first request
+        t_table, _ = median_build(True)
+        # the 3x3x3 rulebook (27 lookups per site in the ranking structure) of that grid, built on first request
         counts = np.zeros(27, dtype=np.int64)
         rts = []
         for i in range(warmup + steps):
@@ -302,13 +308,15 @@ def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
         cap = 16
         while cap < 2 * n:
             cap *= 2
-        byts = 32.0 * c4.shape[0] + 8.0 * cap + 12.0 * n + 4.0 * c4.shape[0]
+        byts = 32.0 * c4.shape[0] + 12.0 * n + 4.0 * c4.shape[0]
         out.append({"scene": name, "points": int(c4.shape[0]), "sites": int(n), "us": t * 1e6,
                     "points_per_s": c4.shape[0] / t, "GBps": byts / t / 1e9,
+                    "with_open_addressing_table": {"us": t_table * 1e6, "GBps": (byts + 8.0 * cap) / t_table / 1e9},
                     "us_with_6_coarse_scales_and_all_maps": t_all * 1e6,
-                    # algorithmic bytes of the rulebook build: coordinates in, table read once, pairs out
+                    # algorithmic bytes of the rulebook build: coordinates in, occupied bitmap words and their
+                    # prefixes read once (12 bytes per site at most), pairs out
                     "ssc_rulebook": {"pairs": pairs, "us": t_rules * 1e6,
-                                     "GBps": (12.0 * n + 8.0 * cap + 8.0 * pairs) / t_rules / 1e9}})
+                                     "GBps": (12.0 * n + 12.0 * n + 8.0 * pairs) / t_rules / 1e9}})
     return out
 
 

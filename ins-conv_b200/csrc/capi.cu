@@ -238,6 +238,7 @@ int scn_metadata_hash_dump(scn_metadata *m, const int64_t size[3], uint64_t *key
                            int64_t *capacity, void *stream) {
   Grid *g;
   SCN_TRY(need_grid(m, size, &g));
+  SCN_TRY(grid_ensure_table(*g, (cudaStream_t)stream));
   const int64_t cap = g->table ? (int64_t)g->mask + 1 : 0;
   if (capacity) *capacity = cap;
   if (!keys_host || !rows_host || cap == 0) return SCN_OK;

@@ -5,11 +5,13 @@
 //   1. pack      coordinates -> 64-bit keys, bounding box of the scene          (reads coords once)
 //   2. mark      one bit per occupied cell in a bitmap laid out in key order    (atomicOr, L2 resident)
 //   3. rank      exclusive prefix sum of the bitmap word popcounts
-//   4. assign    row = prefix[word] + popcount(bits below): the rank of the key among the unique
-//                keys, which is the reference's site numbering; the first point to reach a site
-//                writes its coordinates and inserts key -> row into the open-addressing table.
-// The table (linear probing, 16-byte slots, load factor <= 0.5) is what every later lookup uses:
-// neighbour queries of the 3x3x3 rulebook, pre-exist maps and incremental rulebooks.
+//   4. assign    row of a source = prefix[word] + popcount(bits below): the rank of its key among the unique
+//                keys, which is the reference's site numbering; every source writes its site's coordinates
+//                (sources of one site write the same values, so no arbitration is needed).
+// Bitmap and prefixes stay with the grid and answer every later lookup (neighbour queries of the 3x3x3
+// rulebook, pre-exist maps, incremental rulebooks) with one or two coherent reads.  The open-addressing table
+// key -> row (linear probing, 16-byte slots, load factor <= 0.5) serves the public coordinate query and is
+// filled from the site coordinates the first time it is asked for.
 //
 // Reference behaviour restated here (paths relative to sparseconvnet/SCN/):
 //   key order / site numbering   CUDA/CUDPPWrapper.cu:72-119, extra/cudpp/src/cudpp_hash/hash_multivalue.cpp:45-110
@@ -88,7 +90,7 @@ __global__ void k_init_info(BuildInfo *info) {
     info->err = 0;
     info->n_unique = 0;
     info->max_active = 0;
-    info->mask = 0;
+    info->reserved = 0;
   }
 }
 
@@ -188,6 +190,20 @@ __global__ void k_mark(const unsigned long long *__restrict__ keys, long long n,
   unsigned long long *w = bitmap + (p >> 6);
   // most cells hold one point, but duplicates and neighbours share words: skip the atomic when the
   // bit is already visible.
+  if ((*(volatile unsigned long long *)w & bit) == 0) atomicOr(w, bit);
+}
+
+// The same from the SoA coordinates of the next finer grid, shifted right: a coarse level's box is the fine box
+// halved, so no key array and no box measurement are needed.  src (optional): the build record of the grid c
+// belongs to, when its site count is not known on the host yet.
+__global__ void k_mark_soa(const int32_t *__restrict__ c, long long n, int shift, Box bx, unsigned long long *bitmap,
+                           const BuildInfo *src) {
+  if (src) n = src->n_unique;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  unsigned long long p = box_pos(bx, c[i] >> shift, c[n + i] >> shift, c[2 * n + i] >> shift, c[3 * n + i]);
+  unsigned long long bit = 1ull << (p & 63);
+  unsigned long long *w = bitmap + (p >> 6);
   if ((*(volatile unsigned long long *)w & bit) == 0) atomicOr(w, bit);
 }
 
@@ -332,44 +348,33 @@ struct EmitPairs {
 };
 
 // ---------------------------------------------------------------------------------------------
-// pass 4: rank -> rows, coordinates, table
+// pass 4: source -> row
 // ---------------------------------------------------------------------------------------------
 template <bool UNIQUE>
-__global__ void k_assign(const unsigned long long *__restrict__ keys, long long n_src, Box bx,
-                         const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
-                         long long n, int32_t *__restrict__ src_row, int32_t *coords, uint32_t *cnt, Slot *table,
-                         uint32_t mask, BuildInfo *info, int dyn, const BuildInfo *src) {
-  if (src) n_src = src->n_unique;
+__global__ void k_rank_rows(const unsigned long long *__restrict__ keys, long long n_src, Box bx,
+                            const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
+                            long long n, int32_t *__restrict__ src_row, int32_t *coords, uint32_t *cnt) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_src) return;
-  if (dyn) {  // site count and capacity were decided on the device (k_plan_table)
-    n = info->n_unique;
-    mask = info->mask;
-  }
-  const unsigned long long key = keys[i];
   int x, y, z, b;
-  unpack_key(key, x, y, z, b);
+  unpack_key(keys[i], x, y, z, b);
   const unsigned long long p = box_pos(bx, x, y, z, b);
-  const unsigned long long w = bitmap[p >> 6];
-  const uint32_t row = prefix[p >> 6] + (uint32_t)__popcll(w & ((1ull << (p & 63)) - 1ull));
+  const unsigned long long w = __ldg(bitmap + (p >> 6));
+  const uint32_t row = __ldg(prefix + (p >> 6)) + (uint32_t)__popcll(w & ((1ull << (p & 63)) - 1ull));
   src_row[i] = (int32_t)row;
+  coords[row] = x;  // points of one site write the same four values
+  coords[n + row] = y;
+  coords[2 * n + row] = z;
+  coords[3 * n + row] = b;
   // UNIQUE: the host saw n == n_src, every point is the only one of its site and no counting is needed
-  if (UNIQUE || atomicAdd(&cnt[row], 1u) == 0u) {  // first point of the site
-    coords[row] = x;
-    coords[n + row] = y;
-    coords[2 * n + row] = z;
-    coords[3 * n + row] = b;
-    if (!table_insert(table, mask, key, (int)row)) atomicOr(&info->err, 2u);
-  }
+  if (!UNIQUE) atomicAdd(&cnt[row], 1u);
 }
 
-// table capacity for the counted sites: the smallest power of two >= 2n, at least 16 (same rule as the host path)
-__global__ void k_plan_table(BuildInfo *info) {
-  if (threadIdx.x == 0) {
-    unsigned long long cap = 16;
-    while (cap < 2ull * info->n_unique) cap <<= 1;
-    info->mask = (unsigned int)(cap - 1);
-  }
+// key -> row of every site into the (empty) open-addressing table; with capacity >= 2n an insert always finds a slot
+__global__ void k_table_fill(const int32_t *__restrict__ c, long long n, Slot *table, uint32_t mask) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  (void)table_insert(table, mask, pack_key(c[i], c[n + i], c[2 * n + i], c[3 * n + i]), (int)i);
 }
 
 // sources of each site (CSR), ascending source index inside a site
@@ -422,10 +427,7 @@ __global__ void k_query(const int32_t *__restrict__ c, long long stride, long lo
 __global__ void k_ssc_nbr(const int32_t *__restrict__ c, long long n, const Slot *__restrict__ table, uint32_t mask,
                           const int32_t *__restrict__ absent, int self_ok, int32_t *__restrict__ nbr,
                           unsigned long long *counts, const BuildInfo *dyn) {
-  if (dyn) {  // launched with a grid sized for an upper bound of n
-    n = dyn->n_unique;
-    mask = dyn->mask;
-  }
+  if (dyn) n = dyn->n_unique;  // launched with a grid sized for an upper bound of n
   const int k = blockIdx.y;
   const int dx = k / 9 - 1, dy = (k / 3) % 3 - 1, dz = k % 3 - 1;
   long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -504,10 +506,14 @@ __global__ void k_query_rank(const int32_t *__restrict__ c, long long stride, lo
   rows[i] = r;
 }
 
-// 2x2x2 / stride 2: offset of a fine site inside its coarse cell k = (x&1)*4 + (y&1)*2 + (z&1)
+// 2x2x2 / stride 2: offset of a fine site inside its coarse cell k = (x&1)*4 + (y&1)*2 + (z&1).  The coarse row of
+// a fine site is read from `parent`, or -- when parent is null -- ranked here in the coarse grid's bitmap and
+// written to parent_out together with the coarse site's coordinates (the coarse build then needs no pass of its
+// own for either).
 __global__ void k_conv_maps(const int32_t *__restrict__ fc, long long nf, const int32_t *__restrict__ parent,
                             long long nc, int32_t *child, int32_t *up, unsigned long long *counts, const BuildInfo *dyn,
-                            const BuildInfo *src) {
+                            const BuildInfo *src, Box bx, const unsigned long long *__restrict__ bitmap,
+                            const uint32_t *__restrict__ prefix, int32_t *__restrict__ parent_out, int32_t *coarse_coords) {
   if (dyn) nc = dyn->n_unique;
   if (src) nf = src->n_unique;
   long long f = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -515,8 +521,20 @@ __global__ void k_conv_maps(const int32_t *__restrict__ fc, long long nf, const 
   if (threadIdx.x < 8) hist[threadIdx.x] = 0;
   __syncthreads();
   if (f < nf) {
-    int k = ((fc[f] & 1) << 2) | ((fc[nf + f] & 1) << 1) | (fc[2 * nf + f] & 1);
-    int p = parent[f];
+    const int x = fc[f], y = fc[nf + f], z = fc[2 * nf + f];
+    int k = ((x & 1) << 2) | ((y & 1) << 1) | (z & 1);
+    int p;
+    if (parent) {
+      p = parent[f];
+    } else {
+      const int b = fc[3 * nf + f];
+      p = rank_lookup(bitmap, prefix, box_pos(bx, x >> 1, y >> 1, z >> 1, b));
+      parent_out[f] = p;
+      coarse_coords[p] = x >> 1;  // the (up to eight) fine sites of a coarse site write the same four values
+      coarse_coords[nc + p] = y >> 1;
+      coarse_coords[2 * nc + p] = z >> 1;
+      coarse_coords[3 * nc + p] = b;
+    }
     child[(long long)k * nc + p] = (int32_t)f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) up[(long long)j * nf + f] = (j == k) ? p : -1;
@@ -655,7 +673,7 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
   const long long nwords = (long long)((bits + 63) >> 6);
   SCN_TRY(dev_alloc_t(&g.bitmap, (size_t)nwords, s));
   SCN_TRY(dev_alloc_t(&g.prefix, (size_t)nwords, s));
-  unsigned long long *bitmap = g.bitmap;  // kept with the grid: the neighbour map is built from them
+  unsigned long long *bitmap = g.bitmap;  // kept with the grid: every later lookup is answered from them
   uint32_t *prefix = g.prefix;
   SCN_CUDA(cudaMemsetAsync(bitmap, 0, (size_t)nwords * 8, s));
   k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, nullptr);
@@ -666,22 +684,15 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
   const int64_t n = info.n_unique;
   g.n = n;
   g.box = bx;
-  uint64_t cap = 16;
-  while (cap < (uint64_t)n * 2) cap <<= 1;
-  g.mask = (uint32_t)(cap - 1);
   uint32_t *cnt = nullptr;
   SCN_TRY(dev_alloc_t(&g.coords, (size_t)n * 4, s));
-  SCN_TRY(dev_alloc_t(&g.table, (size_t)cap, s));
   SCN_TRY(dev_alloc_t(&g.src_row, (size_t)n_src, s));
-  SCN_CUDA(cudaMemsetAsync(g.table, 0xFF, (size_t)cap * sizeof(Slot), s));
   if (n == n_src) {
-    k_assign<true><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, nullptr,
-                                                     g.table, g.mask, info_d, 0, nullptr);
+    k_rank_rows<true><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, nullptr);
   } else {
     SCN_TRY(dev_alloc_t(&cnt, (size_t)n, s));
     SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n * 4, s));
-    k_assign<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, cnt,
-                                                      g.table, g.mask, info_d, 0, nullptr);
+    k_rank_rows<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, cnt);
   }
   SCN_LAUNCHED();
   g.max_active = 1;
@@ -712,9 +723,12 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
     SCN_LAUNCHED();
     SCN_TRY(read_back(nbr_counts, nbr_counts_d, sizeof(nbr_counts), 1, s, false));
   }
-  // the error word (table overflow) always comes back; max_active with it when duplicates exist
-  SCN_TRY(read_back(&info, info_d, sizeof(info), 0, s, true));
-  take(&info, sizeof(info), 0);
+  // max_active comes back when duplicates exist, the neighbour counts when that map was built; a build of unique
+  // points without the map ends here with nothing to wait for
+  if (need_info || nbr_counts_d) {
+    SCN_TRY(read_back(&info, info_d, sizeof(info), 0, s, true));
+    take(&info, sizeof(info), 0);
+  }
   if (nbr_counts_d) take(nbr_counts, sizeof(nbr_counts), 1);
   if (need_info) g.max_active = (int32_t)info.max_active;
   if (nbr_counts_d) {
@@ -728,7 +742,6 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
   dev_free(cnt, s);
   dev_free(keys, s);
   dev_free(info_d, s);
-  if (info.err & 2u) return fail(SCN_E_CAPACITY, "hash table overflow");
   return SCN_OK;
 }
 
@@ -749,12 +762,6 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
   LevelRecord *rec_d = nullptr;
   SCN_TRY(dev_alloc_t(&rec_d, (size_t)count, s));
   SCN_CUDA(cudaMemsetAsync(rec_d, 0, (size_t)count * sizeof(LevelRecord), s));
-  std::vector<void *> temps;
-  auto temp = [&](size_t bytes, void **p) {
-    SCN_TRY(dev_alloc(p, bytes, s));
-    temps.push_back(*p);
-    return (int)SCN_OK;
-  };
   Box box = fine0.box;
   int64_t bound = fine0.n;  // upper bound of the site count of the source level (exact for the first level)
   const int32_t *src_coords = fine0.coords;
@@ -783,38 +790,24 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
     const long long nwords = (long long)((bits + 63) >> 6);
     const int64_t n_src = bound;                                         // rows the source level may have
     const int64_t n_max = (int64_t)bits < bound ? (int64_t)bits : bound;  // rows this level may have
-    uint64_t cap_bound = 16;
-    while (cap_bound < (uint64_t)n_max * 2) cap_bound <<= 1;
-    unsigned long long *keys = nullptr, *bitmap = nullptr;
-    uint32_t *prefix = nullptr, *cnt = nullptr;
-    if ((rc = temp((size_t)n_src * 8, (void **)&keys)) != SCN_OK) break;
     if ((rc = dev_alloc_t(&g.bitmap, (size_t)nwords, s)) != SCN_OK) break;  // kept with the grid
     if ((rc = dev_alloc_t(&g.prefix, (size_t)nwords, s)) != SCN_OK) break;
-    bitmap = g.bitmap;
-    prefix = g.prefix;
-    if ((rc = temp((size_t)n_max * 4, (void **)&cnt)) != SCN_OK) break;
     if ((rc = dev_alloc_t(&g.coords, (size_t)n_max * 4, s)) != SCN_OK) break;
-    if ((rc = dev_alloc_t(&g.table, (size_t)cap_bound, s)) != SCN_OK) break;
     if ((rc = dev_alloc_t(&g.src_row, (size_t)n_src, s)) != SCN_OK) break;
     if ((rc = dev_alloc_t(&g.child, (size_t)n_max * 8, s)) != SCN_OK) break;
     if ((rc = dev_alloc_t(&g.fine_up, (size_t)n_src * 8, s)) != SCN_OK) break;
-    k_init_info<<<1, 32, 0, s>>>(info_d);
-    k_pack_keys_soa<<<blocks_for(n_src, T), T, 0, s>>>(src_coords, n_src, 1, keys, info_d, 0, src);
-    SCN_CUDA(cudaMemsetAsync(bitmap, 0, (size_t)nwords * 8, s));
-    k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, src);
-    if ((rc = scan_emit(PopcWords{bitmap}, StorePrefix{prefix}, nwords, &info_d->n_unique, s)) != SCN_OK) break;
-    k_plan_table<<<1, 32, 0, s>>>(info_d);
-    SCN_CUDA(cudaMemsetAsync(g.table, 0xFF, (size_t)cap_bound * sizeof(Slot), s));
-    SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n_max * 4, s));
-    k_assign<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, 0, g.src_row, g.coords, cnt, g.table, 0,
-                                                      info_d, 1, src);
+    // the record was zeroed with the others: no error, and the scan leaves the site count in it
+    SCN_CUDA(cudaMemsetAsync(g.bitmap, 0, (size_t)nwords * 8, s));
+    k_mark_soa<<<blocks_for(n_src, T), T, 0, s>>>(src_coords, n_src, 1, bx, g.bitmap, src);
+    if ((rc = scan_emit(PopcWords{g.bitmap}, StorePrefix{g.prefix}, nwords, &info_d->n_unique, s)) != SCN_OK) break;
     SCN_CUDA(cudaMemsetAsync(g.child, 0xFF, (size_t)n_max * 8 * 4, s));
-    k_conv_maps<<<blocks_for(n_src, 256), 256, 0, s>>>(src_coords, n_src, g.src_row, 0, g.child, g.fine_up, counts_d, info_d, src);
+    k_conv_maps<<<blocks_for(n_src, 256), 256, 0, s>>>(src_coords, n_src, nullptr, 0, g.child, g.fine_up, counts_d, info_d, src,
+                                                       bx, g.bitmap, g.prefix, g.src_row, g.coords);
     if (with_ssc) {
       if ((rc = dev_alloc_t(&g.nbr, (size_t)n_max * 27, s)) != SCN_OK) break;
       k_ssc_nbr_rank<<<dim3(blocks_for(n_max, 256), 9), 256, 0, s>>>(g.coords, 0, bx, g.bitmap, g.prefix, nullptr, 1, g.nbr, counts_d + 8, info_d);
     }
-    for (int i = 0; i < 6 + (with_ssc ? 1 : 0); ++i) g_launches.fetch_add(1, std::memory_order_relaxed);
+    for (int i = 0; i < 2 + (with_ssc ? 1 : 0); ++i) g_launches.fetch_add(1, std::memory_order_relaxed);  // the scan counts its own
     if (cudaGetLastError() != cudaSuccess) {
       rc = fail(SCN_E_CUDA, "a kernel of the coarse grid build could not be launched");
       break;
@@ -833,7 +826,6 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
       rc = fail(SCN_E_CUDA, std::string("coarse grid build: ") + cudaGetErrorString(cudaGetLastError()));
     else if (land != rec.data()) memcpy(rec.data(), land, bytes);
   }
-  for (void *p : temps) dev_free(p, s);
   dev_free(rec_d, s);
   if (rc != SCN_OK) {
     for (int l = 0; l < count; ++l) grid_free(*levels[l], s);
@@ -846,7 +838,6 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
     g.n_src = n_prev;
     g.n = r.info.n_unique;
     g.box = boxes[(size_t)l];
-    g.mask = r.info.mask;
     g.max_active = 1;
     for (int k = 0; k < 8; ++k) g.child_count[k] = (int64_t)r.counts[k];
     if (with_ssc) {
@@ -856,7 +847,6 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
         g.nbr_total += g.nbr_count[k];
       }
     }
-    if (r.info.err & 2u) rc = fail(SCN_E_CAPACITY, "hash table overflow");
     n_prev = g.n;
   }
   return rc;
@@ -867,6 +857,20 @@ int grid_build_coarse(Grid &g, const Grid &fine, bool with_ssc, cudaStream_t s) 
   return grid_build_coarse_chain(&one, 1, fine, with_ssc, s);
 }
 
+int grid_ensure_table(const Grid &g, cudaStream_t s) {
+  if (g.table || g.n == 0) return SCN_OK;
+  uint64_t cap = 16;
+  while (cap < (uint64_t)g.n * 2) cap <<= 1;
+  Slot *t = nullptr;
+  SCN_TRY(dev_alloc_t(&t, (size_t)cap, s));
+  SCN_CUDA(cudaMemsetAsync(t, 0xFF, (size_t)cap * sizeof(Slot), s));
+  k_table_fill<<<blocks_for(g.n, 256), 256, 0, s>>>(g.coords, g.n, t, (uint32_t)(cap - 1));
+  SCN_LAUNCHED();
+  g.table = t;
+  g.mask = (uint32_t)(cap - 1);
+  return SCN_OK;
+}
+
 int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_stride, int32_t *rows, bool by_rank,
                cudaStream_t s) {
   if (n == 0) return SCN_OK;
@@ -874,10 +878,12 @@ int grid_query(const Grid &g, const int32_t *coords_soa, int64_t n, int64_t soa_
     SCN_CUDA(cudaMemsetAsync(rows, 0xFF, (size_t)n * 4, s));
     return SCN_OK;
   }
-  if (by_rank && g.bitmap && g.prefix)
+  if (by_rank && g.bitmap && g.prefix) {
     k_query_rank<<<blocks_for(n, 256), 256, 0, s>>>(coords_soa, soa_stride, n, g.box, g.bitmap, g.prefix, rows);
-  else
+  } else {
+    SCN_TRY(grid_ensure_table(g, s));
     k_query<<<blocks_for(n, 256), 256, 0, s>>>(coords_soa, soa_stride, n, g.table, g.mask, rows);
+  }
   SCN_LAUNCHED();
   return SCN_OK;
 }
@@ -889,6 +895,7 @@ static int nbr_launch(const Grid &g, const Grid &lookup, const int32_t *absent, 
     k_ssc_nbr_rank<<<dim3(blocks_for(g.n, 256), 9), 256, 0, s>>>(g.coords, g.n, lookup.box, lookup.bitmap, lookup.prefix, absent,
                                                                 self_ok, nbr, counts_d, nullptr);
   } else {
+    SCN_TRY(grid_ensure_table(lookup, s));
     dim3 grid(blocks_for(g.n, 256), 27);
     k_ssc_nbr<<<grid, 256, 0, s>>>(g.coords, g.n, lookup.table, lookup.mask, absent, self_ok, nbr, counts_d, nullptr);
   }
@@ -974,7 +981,8 @@ int grid_build_conv(Grid &coarse, const Grid &fine, cudaStream_t s) {
   SCN_TRY(dev_alloc_t(&coarse.fine_up, (size_t)fine.n * 8, s));
   SCN_CUDA(cudaMemsetAsync(coarse.child, 0xFF, (size_t)coarse.n * 8 * 4, s));
   k_conv_maps<<<blocks_for(fine.n, 256), 256, 0, s>>>(fine.coords, fine.n, coarse.src_row, coarse.n, coarse.child,
-                                                     coarse.fine_up, counts_d, nullptr, nullptr);
+                                                     coarse.fine_up, counts_d, nullptr, nullptr, coarse.box, nullptr, nullptr,
+                                                     nullptr, nullptr);
   SCN_LAUNCHED();
   unsigned long long h[8];
   SCN_CUDA(cudaMemcpyAsync(h, counts_d, sizeof(h), cudaMemcpyDeviceToHost, s));

@@ -54,10 +54,10 @@ static const unsigned long long kEmptyKey = ~0ull;
 struct BuildInfo {
   int mn[4];  // bounding box minimum  x,y,z,batch
   int mx[4];  // bounding box maximum
-  unsigned int err;         // bit0: coordinate out of key range, bit1: table overflow
+  unsigned int err;         // bit0: coordinate out of key range
   unsigned int n_unique;    // sites found
   unsigned int max_active;  // most source points in one site
-  unsigned int mask;        // table capacity - 1, when the capacity is chosen on the device (coarse builds)
+  unsigned int reserved;
 };
 
 // Bounding box in key order used to rank keys: pos = ((b*ez + z)*ey + y)*ex + x (box-relative).
@@ -71,8 +71,10 @@ struct Grid {
   int64_t n = 0;           // active sites
   Box box = {{0, 0, 0, 0}, {0, 0, 0, 0}};  // bounding box of the sites (valid when n > 0)
   int32_t *coords = nullptr;  // SoA [4][n]: x, y, z, batch
-  Slot *table = nullptr;
-  uint32_t mask = 0;       // capacity - 1
+  // open-addressing table key -> row: a second index beside the ranking structure below, filled on first use
+  // (grid_ensure_table) because only the public coordinate query and the table dump read it
+  mutable Slot *table = nullptr;
+  mutable uint32_t mask = 0;  // capacity - 1
   // relation to the source rows this grid was built from (input points, or the sites of the
   // next finer scale):
   int64_t n_src = 0;
@@ -96,6 +98,9 @@ struct Grid {
 };
 
 int grid_free(Grid &g, cudaStream_t s);
+// Fills g.table from the site coordinates when it does not exist yet (capacity: the smallest power of two >= 2n, at
+// least 16; linear probing cannot fail at that load).  No host round trip.
+int grid_ensure_table(const Grid &g, cudaStream_t s);
 
 // Builds g from source points.  Exactly one of coords64 / coords_soa is given:
 //   coords64  : int64 [n_src, ncols] rows (x,y,z[,b]) on the device
@@ -107,7 +112,7 @@ int grid_free(Grid &g, cudaStream_t s);
 int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift,
                int64_t n_src, bool want_csr, const Box *box_hint, bool with_ssc, cudaStream_t s);
 // The next coarser scale of `fine` (sites at coordinates >> 1) with its size-2/stride-2 maps and, on request,
-// its neighbour map, in one pass with a single host round trip at the end: site count and table capacity stay
+// its neighbour map, in one pass with a single host round trip at the end: the site count stays
 // on the device while the kernels run, buffers are sized by the bound n_coarse <= n_fine.
 int grid_build_coarse(Grid &coarse, const Grid &fine, bool with_ssc, cudaStream_t s);
 // `count` successive coarser scales of fine0 (levels[0] from fine0, levels[1] from levels[0], ...) chained on the

@@ -82,6 +82,25 @@ def test_duplicates_and_batches(cuda):
         _check_rules(m.conv_rulebook(64, 32), crules)
 
 
+@pytest.mark.parametrize("extent", [(1, 1, 7), (1, 3, 2), (2, 5, 3), (3, 1, 11), (5, 7, 2), (63, 2, 2), (65, 3, 1)])
+def test_narrow_boxes(cuda, extent):
+    # bounding boxes whose lines (and planes) are shorter than a 64-cell bitmap word: one word of the ranking
+    # structure then covers several lines, planes and batch entries
+    rng = np.random.RandomState(sum(extent))
+    e = np.array(extent)
+    c = rng.randint(0, 1 << 30, size=(400, 3)) % e + np.array([5, 9, 2])
+    b = np.sort(rng.randint(0, 4, size=(400, 1)), 0)
+    cb = np.concatenate([c, b], 1)
+    m, n = _build(cb, 128, cuda)
+    g = O.Grid(cb)
+    _check_grid(m, n, g, 128)
+    _check_rules(m.ssc_rulebook(128), O.ssc_rules(g))
+    coarse, crules = O.conv2_rules(g)
+    _check_rules(m.conv_rulebook(128, 64), crules)
+    np.testing.assert_array_equal(m.spatial_locations(64), coarse.coords)
+    _check_rules(m.ssc_rulebook(64), O.ssc_rules(coarse))
+
+
 def test_permutation_invariance(cuda):
     c = synth.boxes_and_spheres(2)
     m1, _ = _build(c, 128, cuda)
