@@ -92,6 +92,9 @@ SCN_API int scn_metadata_spatial_locations(scn_metadata *m, const int64_t size[3
 SCN_API int scn_metadata_site_coords(scn_metadata *m, const int64_t size[3], const int32_t **coords, int64_t *n);
 /* Copies the scale's open-addressing table to HOST arrays of `capacity` entries
  * (capacity from a first call with keys == NULL).  Empty slots have key ~0.
+ * The table is a second index beside the build's ranking structure (which serves the
+ * rulebook builds): it is filled from the site coordinates by the first call of this
+ * function or of scn_metadata_query on the scale, on `stream`, without a host round trip.
  * Key layout: batch<<48 | z<<32 | y<<16 | x.  This is the observable content of the
  * reference's Multival_Point_Hashtable (CUDA/CUDPPWrapper.hpp:736-1010): key -> row. */
 SCN_API int scn_metadata_hash_dump(scn_metadata *m, const int64_t size[3], uint64_t *keys_host, int32_t *rows_host,
