@@ -93,6 +93,7 @@ class ClockSampler(object):
         self.lines = []
         self.nvml = None
         self.samples = []  # (sm_mhz, max_mhz, reasons bitmask)
+        self.query_ms = []  # host time of each sample taken by the thread
         self.running = False
         self.mode = os.environ.get("INSCONV_CLOCK_SAMPLER", "nvml")  # nvml | smi | off (development aid)
 
@@ -115,6 +116,11 @@ class ClockSampler(object):
                 self.running = True
                 self.thread = threading.Thread(target=self._loop_nvml, daemon=True)
                 self.thread.start()
+                # the sampling thread's own first queries (per-thread library state) must be over before anything
+                # is timed: a slow first query holds a driver lock that kernel launches wait for
+                t0 = time.time()
+                while len(self.samples) < 3 and time.time() - t0 < 2.0:
+                    time.sleep(0.02)
                 return
             except Exception:
                 self.nvml = None
@@ -137,10 +143,15 @@ class ClockSampler(object):
         reasons = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
         self.samples.append((float(sm), float(mx), int(reasons)))
 
+    def _timed_sample(self):
+        t0 = time.perf_counter()
+        self._sample_nvml()
+        self.query_ms.append((time.perf_counter() - t0) * 1e3)
+
     def _loop_nvml(self):
         while self.running:
             try:
-                self._sample_nvml()
+                self._timed_sample()
             except Exception:
                 pass
             time.sleep(0.1)
@@ -162,7 +173,8 @@ class ClockSampler(object):
             sm = [s[0] for s in self.samples]
             mx = [s[1] for s in self.samples]
             return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                    "samples": len(sm), "reasons": reasons, "source": "nvml"}
+                    "samples": len(sm), "reasons": reasons, "source": "nvml",
+                    "slowest_query_ms": round(max(self.query_ms), 3) if self.query_ms else None}
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock sampler available"]}
         self.proc.terminate()
@@ -430,8 +442,8 @@ def voxel_layers_of(runner):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--voxels", type=int, default=250000)
     ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "fp16"), choices=["fp32", "tf32", "fp16"])
@@ -528,12 +540,19 @@ def main():
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         l0 = scn.SCN.launch_count()
+        stamps = [time.perf_counter()]
         e0.record()
         for _ in range(steps):
             fn()
+            stamps.append(time.perf_counter())  # host side only: when each step's launches had been queued
         e1.record()
         barrier()
+        host_ms = [(b - a) * 1e3 for a, b in zip(stamps, stamps[1:])]
+        step_host_ms.append({"median": round(statistics.median(host_ms), 3), "max": round(max(host_ms), 3),
+                             "max_at_step": host_ms.index(max(host_ms))})
         return max_over_ranks(e0.elapsed_time(e1) / steps), (scn.SCN.launch_count() - l0) // steps
+
+    step_host_ms = []  # one entry per timed leg, in the order full, incremental, exact, e2e
 
     # ---- value: full frame, inputs resident in HBM ------------------------------------------------
     out_holder = {}
@@ -697,7 +716,10 @@ def main():
             "sweep": sweep,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h)},
-            "gpu_launches": int(launches) * args.steps, "clocks": clocks, "roofline": roofline, "tcgen05": tcgen05,
+            "gpu_launches": int(launches) * args.steps,
+            # host time between the ends of consecutive steps of each timed leg (full, incremental, exact, e2e as
+            # run): a single step far above the median is a stall of the host or the driver, not of the kernels
+            "step_host_ms": step_host_ms, "clocks": clocks, "roofline": roofline, "tcgen05": tcgen05,
             "hash_build": hashes}
     if world == 1 and not args.no_cpu_baseline:
         sample = min(args.voxels, 120000)

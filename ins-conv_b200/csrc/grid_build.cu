@@ -289,10 +289,42 @@ __global__ void k_scan_emit(F f, G g, long long n, const uint32_t *__restrict__ 
   }
 }
 
+// The whole scan in one block, for inputs of a few chunks (the bitmaps of the coarse scales): one launch instead of
+// three.  Launched with kScanThreads threads.
+template <class F, class G>
+__global__ void k_scan_one_block(F f, G g, long long n, uint32_t *total_out) {
+  uint32_t carry = 0;
+  for (long long chunk = 0; chunk < n; chunk += kScanChunk) {
+    const long long base = chunk + (long long)threadIdx.x * kScanItems;
+    uint32_t v[kScanItems];
+    uint32_t sum = 0;
+#pragma unroll
+    for (int j = 0; j < kScanItems; ++j) {
+      v[j] = (base + j < n) ? f(base + j) : 0;
+      sum += v[j];
+    }
+    uint32_t total;
+    uint32_t ex = block_exclusive_scan(sum, &total) + carry;
+#pragma unroll
+    for (int j = 0; j < kScanItems; ++j) {
+      if (base + j < n) g(base + j, ex, v[j]);
+      ex += v[j];
+    }
+    carry += total;
+  }
+  if (threadIdx.x == 0 && total_out) *total_out = carry;
+}
+constexpr long long kScanOneBlockMax = 4 * kScanChunk;  // 8192 items: four rounds of one block
+
 template <class F, class G>
 static int scan_emit(F f, G g, long long n, uint32_t *total_dev, cudaStream_t s) {
   if (n <= 0) {
     if (total_dev) SCN_CUDA(cudaMemsetAsync(total_dev, 0, sizeof(uint32_t), s));
+    return SCN_OK;
+  }
+  if (n <= kScanOneBlockMax) {
+    k_scan_one_block<<<1, kScanThreads, 0, s>>>(f, g, n, total_dev);
+    SCN_LAUNCHED();
     return SCN_OK;
   }
   long long nb = (n + kScanChunk - 1) / kScanChunk;
@@ -572,16 +604,21 @@ __global__ void k_locations(const int32_t *__restrict__ c, long long n, long lon
 static inline unsigned blocks_for(long long n, int t) { return (unsigned)((n + t - 1) / t); }
 
 int grid_free(Grid &g, cudaStream_t s) {
-  dev_free(g.coords, s);
-  dev_free(g.table, s);
-  dev_free(g.src_row, s);
-  dev_free(g.csr_off, s);
-  dev_free(g.csr_item, s);
-  dev_free(g.nbr, s);
-  dev_free(g.bitmap, s);
-  dev_free(g.prefix, s);
-  dev_free(g.child, s);
-  dev_free(g.fine_up, s);
+  auto release = [&](const void *p) {  // members carved out of the arena go with it
+    const unsigned char *q = static_cast<const unsigned char *>(p);
+    if (q && !(g.arena && q >= g.arena && q < g.arena + g.arena_bytes)) dev_free(const_cast<void *>(p), s);
+  };
+  release(g.coords);
+  release(g.table);
+  release(g.src_row);
+  release(g.csr_off);
+  release(g.csr_item);
+  release(g.nbr);
+  release(g.bitmap);
+  release(g.prefix);
+  release(g.child);
+  release(g.fine_up);
+  dev_free(g.arena, s);
   g = Grid();
   return SCN_OK;
 }
@@ -790,12 +827,28 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
     const long long nwords = (long long)((bits + 63) >> 6);
     const int64_t n_src = bound;                                         // rows the source level may have
     const int64_t n_max = (int64_t)bits < bound ? (int64_t)bits : bound;  // rows this level may have
-    if ((rc = dev_alloc_t(&g.bitmap, (size_t)nwords, s)) != SCN_OK) break;  // kept with the grid
-    if ((rc = dev_alloc_t(&g.prefix, (size_t)nwords, s)) != SCN_OK) break;
-    if ((rc = dev_alloc_t(&g.coords, (size_t)n_max * 4, s)) != SCN_OK) break;
-    if ((rc = dev_alloc_t(&g.src_row, (size_t)n_src, s)) != SCN_OK) break;
-    if ((rc = dev_alloc_t(&g.child, (size_t)n_max * 8, s)) != SCN_OK) break;
-    if ((rc = dev_alloc_t(&g.fine_up, (size_t)n_src * 8, s)) != SCN_OK) break;
+    // every buffer of the level in one allocation (one pool call instead of seven, and one release per frame)
+    size_t off = 0;
+    auto carve = [&off](size_t bytes) {
+      const size_t at = off;
+      off += (bytes + 255) & ~(size_t)255;
+      return at;
+    };
+    const size_t o_bitmap = carve((size_t)nwords * 8), o_prefix = carve((size_t)nwords * 4);
+    const size_t o_coords = carve((size_t)n_max * 16), o_src_row = carve((size_t)n_src * 4);
+    const size_t o_child = carve((size_t)n_max * 32), o_up = carve((size_t)n_src * 32);
+    const size_t o_nbr = with_ssc ? carve((size_t)n_max * 108) : 0;
+    void *arena = nullptr;
+    if ((rc = dev_alloc(&arena, off, s)) != SCN_OK) break;
+    g.arena = static_cast<unsigned char *>(arena);
+    g.arena_bytes = off;
+    g.bitmap = reinterpret_cast<unsigned long long *>(g.arena + o_bitmap);  // kept with the grid
+    g.prefix = reinterpret_cast<uint32_t *>(g.arena + o_prefix);
+    g.coords = reinterpret_cast<int32_t *>(g.arena + o_coords);
+    g.src_row = reinterpret_cast<int32_t *>(g.arena + o_src_row);
+    g.child = reinterpret_cast<int32_t *>(g.arena + o_child);
+    g.fine_up = reinterpret_cast<int32_t *>(g.arena + o_up);
+    if (with_ssc) g.nbr = reinterpret_cast<int32_t *>(g.arena + o_nbr);
     // the record was zeroed with the others: no error, and the scan leaves the site count in it
     SCN_CUDA(cudaMemsetAsync(g.bitmap, 0, (size_t)nwords * 8, s));
     k_mark_soa<<<blocks_for(n_src, T), T, 0, s>>>(src_coords, n_src, 1, bx, g.bitmap, src);
@@ -804,7 +857,6 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
     k_conv_maps<<<blocks_for(n_src, 256), 256, 0, s>>>(src_coords, n_src, nullptr, 0, g.child, g.fine_up, counts_d, info_d, src,
                                                        bx, g.bitmap, g.prefix, g.src_row, g.coords);
     if (with_ssc) {
-      if ((rc = dev_alloc_t(&g.nbr, (size_t)n_max * 27, s)) != SCN_OK) break;
       k_ssc_nbr_rank<<<dim3(blocks_for(n_max, 256), 9), 256, 0, s>>>(g.coords, 0, bx, g.bitmap, g.prefix, nullptr, 1, g.nbr, counts_d + 8, info_d);
     }
     for (int i = 0; i < 2 + (with_ssc ? 1 : 0); ++i) g_launches.fetch_add(1, std::memory_order_relaxed);  // the scan counts its own

@@ -95,6 +95,10 @@ struct Grid {
   int32_t *child = nullptr;      // [8][n]: fine row of offset k, or -1
   int32_t *fine_up = nullptr;    // [8][n_src]: up[k*n_src+f] = coarse row if offset(f)==k else -1
   int64_t child_count[8] = {0};
+  // one allocation that holds several of the arrays above (coarse scales are built with all their buffers sized
+  // up front): grid_free releases it once and skips the pointers that lie inside
+  unsigned char *arena = nullptr;
+  size_t arena_bytes = 0;
 };
 
 int grid_free(Grid &g, cudaStream_t s);
