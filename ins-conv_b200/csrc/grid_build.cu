@@ -385,7 +385,8 @@ struct EmitPairs {
 template <bool UNIQUE>
 __global__ void k_rank_rows(const unsigned long long *__restrict__ keys, long long n_src, Box bx,
                             const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
-                            long long n, int32_t *__restrict__ src_row, int32_t *coords, uint32_t *cnt) {
+                            long long n, int32_t *__restrict__ src_row, int32_t *coords, uint32_t *cnt,
+                            int32_t *__restrict__ csr_item) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_src) return;
   int x, y, z, b;
@@ -398,8 +399,10 @@ __global__ void k_rank_rows(const unsigned long long *__restrict__ keys, long lo
   coords[n + row] = y;
   coords[2 * n + row] = z;
   coords[3 * n + row] = b;
-  // UNIQUE: the host saw n == n_src, every point is the only one of its site and no counting is needed
+  // UNIQUE: the host saw n == n_src, every point is the only one of its site: no counting is needed and the
+  // site's source list (when asked for) is this point
   if (!UNIQUE) atomicAdd(&cnt[row], 1u);
+  else if (csr_item) csr_item[row] = (int32_t)i;
 }
 
 // key -> row of every site into the (empty) open-addressing table; with capacity >= 2n an insert always finds a slot
@@ -410,10 +413,6 @@ __global__ void k_table_fill(const int32_t *__restrict__ c, long long n, Slot *t
 }
 
 // sources of each site (CSR), ascending source index inside a site
-__global__ void k_csr_identity(const int32_t *__restrict__ src_row, long long n_src, int32_t *item) {
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n_src) item[src_row[i]] = (int32_t)i;
-}
 __global__ void k_csr_fill(const int32_t *__restrict__ src_row, long long n_src, const int32_t *__restrict__ off,
                            uint32_t *cursor, int32_t *item) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -724,22 +723,21 @@ int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coord
   uint32_t *cnt = nullptr;
   SCN_TRY(dev_alloc_t(&g.coords, (size_t)n * 4, s));
   SCN_TRY(dev_alloc_t(&g.src_row, (size_t)n_src, s));
+  if (want_csr) SCN_TRY(dev_alloc_t(&g.csr_item, (size_t)n_src, s));
   if (n == n_src) {
-    k_rank_rows<true><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, nullptr);
+    k_rank_rows<true><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, nullptr,
+                                                        g.csr_item);
   } else {
     SCN_TRY(dev_alloc_t(&cnt, (size_t)n, s));
     SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n * 4, s));
-    k_rank_rows<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, cnt);
+    k_rank_rows<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, cnt,
+                                                         nullptr);
   }
   SCN_LAUNCHED();
   g.max_active = 1;
   bool need_info = false;
   if (want_csr) {
-    SCN_TRY(dev_alloc_t(&g.csr_item, (size_t)n_src, s));
-    if (n == n_src) {
-      k_csr_identity<<<blocks_for(n_src, T), T, 0, s>>>(g.src_row, n_src, g.csr_item);
-      SCN_LAUNCHED();
-    } else {
+    if (n != n_src) {
       SCN_TRY(dev_alloc_t(&g.csr_off, (size_t)n + 1, s));
       SCN_TRY(scan_emit(U32Values{cnt}, StoreOffsets{g.csr_off, (long long)n}, n, nullptr, s));
       SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n * 4, s));
