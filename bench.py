@@ -527,6 +527,14 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def per_rank(ms):
+        if dist is None:
+            return [round(ms, 4)]
+        t = torch.zeros(world, device=dev, dtype=torch.float64)
+        t[rank] = ms
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return [round(float(v), 4) for v in t.tolist()]
+
     def sum_over_ranks(v):
         if dist is None:
             return v
@@ -550,8 +558,11 @@ def main():
         host_ms = [(b - a) * 1e3 for a, b in zip(stamps, stamps[1:])]
         step_host_ms.append({"median": round(statistics.median(host_ms), 3), "max": round(max(host_ms), 3),
                              "max_at_step": host_ms.index(max(host_ms))})
-        return max_over_ranks(e0.elapsed_time(e1) / steps), (scn.SCN.launch_count() - l0) // steps
+        mine = e0.elapsed_time(e1) / steps
+        ms_by_rank.append(per_rank(mine))
+        return max_over_ranks(mine), (scn.SCN.launch_count() - l0) // steps
 
+    ms_by_rank = []  # per timed leg: every rank's own ms per step (the reported figure is the maximum)
     step_host_ms = []  # one entry per timed leg, in the order full, incremental, exact, e2e
 
     # ---- value: full frame, inputs resident in HBM ------------------------------------------------
@@ -719,7 +730,7 @@ def main():
             "gpu_launches": int(launches) * args.steps,
             # host time between the ends of consecutive steps of each timed leg (full, incremental, exact, e2e as
             # run): a single step far above the median is a stall of the host or the driver, not of the kernels
-            "step_host_ms": step_host_ms, "clocks": clocks, "roofline": roofline, "tcgen05": tcgen05,
+            "step_host_ms": step_host_ms, "ms_per_step_by_rank": ms_by_rank, "clocks": clocks, "roofline": roofline, "tcgen05": tcgen05,
             "hash_build": hashes}
     if world == 1 and not args.no_cpu_baseline:
         sample = min(args.voxels, 120000)
