@@ -573,6 +573,14 @@ def main():
 
     full_frame()
     torch.cuda.synchronize()
+    # Python's cyclic collector: a frame creates ~1000 container objects, so a full (oldest-generation) collection
+    # comes round every ~100 frames and then walks every object torch and numpy have created since import, 30-80 ms
+    # with the interpreter lock held.  Freezing what exists now keeps those walks short, as a long-running service
+    # would do after start-up (INSCONV_GC_FREEZE=0 leaves the collector alone).
+    if os.environ.get("INSCONV_GC_FREEZE", "1") != "0":
+        import gc
+        gc.collect()
+        gc.freeze()
     ssc_mods = [m for m in model.modules() if isinstance(m, scn.SubmanifoldConvolution)]
     voxel_layers = sum(int(m.save_input_feats.shape[0]) for m in ssc_mods)
     sampler = ClockSampler(local)
