@@ -41,6 +41,7 @@ for p in (ROOT, os.path.join(ROOT, "ins-conv_b200")):
 METRIC = "active voxels/s per SSC layer (UNet frame); incremental ms/frame beside it"
 UNIT = "voxel-layers/s"
 PLANES = [32, 64, 96, 128, 160, 192, 224]
+L2_NOTE = "no flush: one frame streams ~1.5 GB of activations and maps, far above the 126 MB L2"
 WORKLOAD = "configs[2]: model.py SCN UNet, one synthetic room (~250k voxels, 2 cm, 8x8x3 m), full frame"
 
 
@@ -87,7 +88,7 @@ class ClockSampler(object):
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
+    def __init__(self, index, mode="nvml"):
         self.index = index
         self.proc = None
         self.lines = []
@@ -95,7 +96,7 @@ class ClockSampler(object):
         self.samples = []  # (sm_mhz, max_mhz, reasons bitmask)
         self.query_ms = []  # host time of each sample taken by the thread
         self.running = False
-        self.mode = os.environ.get("INSCONV_CLOCK_SAMPLER", "nvml")  # nvml | smi | off (development aid)
+        self.mode = mode  # nvml | smi | off
 
     def start(self):
         if self.mode == "off":
@@ -257,6 +258,76 @@ def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
                          "peak_kind": peak_kind, "algorithmic_bytes": byts, "algorithmic_flops": flops}}
 
 
+def configs01_bench(dev, steps, warmup):
+    """BASELINE configs[0] and configs[1] as single-layer figures through the C ABI: one SubmanifoldConvolution 16->16,
+    fp32, no bias, on the seeded boxes-and-spheres scene (seed 3: 50,208 voxels in 128^3), rulebook cached; then the same
+    layer over frame t+1's changed sites (insert + re-draw) as the incremental operator, beside the full recompute of
+    frame t+1.  L2 flushed between launches, CUDA events on the launching stream."""
+    import numpy as np
+    import torch
+    from insconv import cabi, synth
+    coords = synth.boxes_and_spheres(3)
+    rng = np.random.RandomState(3)
+    feats = rng.randn(coords.shape[0], 16).astype(np.float32)
+    w = torch.from_numpy(synth.kaiming_uniform(rng, 27, 16, 16)).to(dev)
+    nf = synth.next_frame(coords, feats, 3)
+    t = lambda a: torch.from_numpy(a).to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed_us(fn):
+        ts = []
+        for i in range(warmup + steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                ts.append(e0.elapsed_time(e1) * 1e3)
+        return sum(ts) / len(ts)
+
+    m0 = cabi.Metadata()
+    n0 = m0.input_layer_build(128, t(coords), mode=4)
+    v0 = m0.input_forward(t(feats))
+    out = {}
+    for name, prec in (("fp32", cabi.PREC_FP32), ("tf32", cabi.PREC_TF32)):
+        _, madds = m0.ssc_forward(128, v0, w, None, prec)
+        us = timed_us(lambda: m0.ssc_forward(128, v0, w, None, prec))
+        pairs = madds / 256.0
+        byts = 4.0 * n0 * 16 * 2 + 8.0 * pairs + 4.0 * 27 * 256
+        out["configs0_" + name] = {"sites": int(n0), "pairs": int(pairs), "us_per_launch": us, "voxels_per_s": n0 / (us * 1e-6),
+                                   "GBps_algorithmic": byts / (us * 1e-6) / 1e9}
+    m1, mf = cabi.Metadata(), cabi.Metadata()
+    n1 = m1.input_layer_build(128, t(nf["new_coords"]), mode=4)
+    nfull = mf.input_layer_build(128, t(nf["coords"]), mode=4)
+    res = m1.incre_input_forward(m0, t(nf["new_feats"]), v0)
+    vf = mf.input_forward(t(nf["feats"]))
+    m1.incre_ssc_forward(m0, 128, res, w, v0)
+    mf.ssc_forward(128, vf, w)
+    us_inc = timed_us(lambda: m1.incre_ssc_forward(m0, 128, res, w, v0))
+    us_full = timed_us(lambda: mf.ssc_forward(128, vf, w))
+    out["configs1_fp32"] = {"changed_sites": int(n1), "changed_frac": n1 / float(n0), "incremental_us": us_inc,
+                            "full_recompute_us": us_full, "sites_next_frame": int(nfull),
+                            "semantics": "reference (insert + re-draw, residual on the changed sites)"}
+    return out
+
+
+def dram_traffic(kernel, workload, precision):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch from the ncu capture recorded in
+    profiles/dram_traffic.txt (columns: kernel workload precision bytes commit source), or None when no capture of that
+    kernel and workload is on record."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.txt")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        for ln in f:
+            f_ = ln.split()
+            if len(f_) >= 4 and not ln.startswith("#") and f_[0] == kernel and f_[1] == workload and f_[2] == precision:
+                return {"bytes": float(f_[3]), "commit": f_[4] if len(f_) > 4 else None, "source": f_[5] if len(f_) > 5 else None}
+    return None
+
+
 def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
     """Grid build (points -> ranked sites + input rules) through the C ABI, coordinates resident on the device.
     Algorithmic bytes: 32 per point in (int64 x,y,z,batch), 12 per site (coordinates out), 4 per point (point ->
@@ -407,12 +478,14 @@ def load_peaks():
 
 
 def cpu_reference(voxels, steps, warmup, seed=0):
-    """The CPU restatement of the reference (oracle/) on the host cores: full UNet frame on a room."""
+    """The CPU restatement of the reference (oracle/) on the host cores: full UNet frame on a room.  The module tree
+    comes from the oracle's own topology builder, so this leg never loads the CUDA library."""
     import torch
     torch.set_num_threads(os.cpu_count())
-    import sparseconvnet as scn
+    from oracle import scn_topology
     from oracle.scn_graph import GraphRunner
-    model = build_model(scn, torch)
+    torch.manual_seed(0)
+    model = scn_topology.Naive_UNet().eval()
     coords, feats, _, _ = make_scene(seed, voxels)
     x = [torch.from_numpy(coords), torch.from_numpy(feats)]
     times, layers = [], 0
@@ -432,9 +505,8 @@ def cpu_reference(voxels, steps, warmup, seed=0):
 def voxel_layers_of(runner):
     total = 0
     # the oracle runner keeps the input tensor of every SubmanifoldConvolution it evaluated
-    import sparseconvnet as scn
     for m in runner.root.modules():
-        if isinstance(m, scn.SubmanifoldConvolution) and id(m) in runner.saved:
+        if type(m).__name__ == "SubmanifoldConvolution" and id(m) in runner.saved:
             total += int(runner.saved[id(m)].features.shape[0])
     return total
 
@@ -446,10 +518,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--voxels", type=int, default=250000)
-    ap.add_argument("--precision", default=os.environ.get("INSCONV_PRECISION", "fp16"), choices=["fp32", "tf32", "fp16"])
+    ap.add_argument("--precision", default="fp16", choices=["fp32", "tf32", "fp16"])
     ap.add_argument("--quick", action="store_true", help="skip the 4M-point hash build (profiling aid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--legs", default="full,incre,sweep,e2e", help="which timed legs to run (profiling aid)")
+    ap.add_argument("--legs", default="full,incre,sweep,e2e,precisions,configs01", help="which timed legs to run (profiling aid)")
     ap.add_argument("--sweep-frames", type=int, default=100)
     ap.add_argument("--layer", action="store_true", help="time one SSC layer alone (rulebook cached) and exit")
     ap.add_argument("--hash", action="store_true", help="time the grid build alone and exit")
@@ -458,6 +530,12 @@ def main():
     ap.add_argument("--n-in", type=int, default=32)
     ap.add_argument("--n-out", type=int, default=32)
     ap.add_argument("--profile", action="store_true", help="allow fewer than 3 warm-up steps (numbers are not bench values)")
+    ap.add_argument("--clock-sampler", default="nvml", choices=["nvml", "smi", "off"],
+                    help="how SM clocks and throttle reasons are sampled during the timed legs: in-process NVML queries "
+                         "(default), an nvidia-smi subprocess, or not at all")
+    ap.add_argument("--no-gc-freeze", action="store_true",
+                    help="leave Python's cyclic collector alone (by default the objects that exist after the first frame are "
+                         "frozen out of it, as a long-running service does after start-up)")
     args = ap.parse_args()
     if args.impl == "b200" and not args.profile:
         args.warmup = max(args.warmup, 3)
@@ -469,14 +547,16 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
-        sample_voxels = min(args.voxels, 120000)
-        r = cpu_reference(sample_voxels, max(1, min(args.steps, 3)), min(args.warmup, 1))
+        # the same room as the GPU arm, exactly K timed steps after W warm-up steps (a frame is about 1.5 s on 16 cores)
+        r = cpu_reference(args.voxels, max(1, args.steps), max(0, args.warmup))
         line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": args.gpus,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
+                "steps": max(1, args.steps), "warmup": max(0, args.warmup), "ms_per_step": r["ms_per_step"],
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic", "config": {"workload": WORKLOAD, "voxels": r["voxels"]},
+                "data": "synthetic", "config": {"workload": WORKLOAD, "voxels_per_scene": r["voxels"], "scenes": 1,
+                                                "voxel_layers_per_scene": r["voxel_layers"], "l2": L2_NOTE},
+                "precision": {"name": "fp32", "note": "torch CPU fp32 (index_select -> mm -> index_add_ per offset)"},
                 "cpu_baseline": {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
-                                 "sample": "one full UNet frame on a %d-voxel room (same generator, thinned), torch CPU "
+                                 "sample": "every step is one full UNet frame on the %d-voxel room of the GPU arm, torch CPU "
                                            "threads = cores" % r["voxels"]},
                 "e2e": {"value": r["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
@@ -593,14 +673,14 @@ def main():
     # Python's cyclic collector: a frame creates ~1000 container objects, so a full (oldest-generation) collection
     # comes round every ~100 frames and then walks every object torch and numpy have created since import, 30-80 ms
     # with the interpreter lock held.  Freezing what exists now keeps those walks short, as a long-running service
-    # would do after start-up (INSCONV_GC_FREEZE=0 leaves the collector alone).
-    if os.environ.get("INSCONV_GC_FREEZE", "1") != "0":
+    # would do after start-up (--no-gc-freeze leaves the collector alone).
+    if not args.no_gc_freeze:
         import gc
         gc.collect()
         gc.freeze()
     ssc_mods = [m for m in model.modules() if isinstance(m, scn.SubmanifoldConvolution)]
     voxel_layers = sum(int(m.save_input_feats.shape[0]) for m in ssc_mods)
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(local, args.clock_sampler)
     if rank == 0:
         sampler.start()
     ms_full, launches = timed(full_frame, args.steps, args.warmup)
@@ -693,7 +773,18 @@ def main():
         torch.cuda.current_stream().synchronize()  # the host reads the result every step
 
     ms_e2e, _ = timed(e2e_frame, args.steps, args.warmup) if "e2e" in legs else (float("nan"), 0)
-    clocks = sampler.stop() if rank == 0 else None  # sampled across the three timed legs
+    # the same full frame in the other precisions (fewer steps: these are reported beside the headline, not as it)
+    other = {}
+    if "precisions" in legs:
+        for prec in ("fp16", "tf32", "fp32"):
+            if prec == args.precision:
+                continue
+            scn.set_precision(prec)
+            ms_p, launches_p = timed(full_frame, min(args.steps, 20), 3)
+            other[prec] = {"ms_per_step": ms_p, "value": total_layers / (ms_p * 1e-3), "launches": int(launches_p)}
+        scn.set_precision(args.precision)
+        full_frame()
+    clocks = sampler.stop() if rank == 0 else None  # sampled across the timed legs
     e2e_value = total_layers / (ms_e2e * 1e-3)
     h2d = coords.nbytes + feats.nbytes
     d2h = int(out_holder["y"].numel()) * 4
@@ -713,11 +804,11 @@ def main():
                                % (args.precision, "FFMA kernel" if args.precision == "fp32" else "warp-level mma.sync kernel",
                                   lay["sites"]),
                      "us_per_launch": lay["us_per_launch"], "voxels_per_s": lay["voxels_per_s"],
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised in
-                     # profiles/gather_mma_f16_warp_ssc32_room.md and profiles/gather_mma_tf32_warp_ssc32_room.md
-                     # (same kernel, same workload)
-                     "traffic": {"fp16": 46.8e6, "tf32": 67.5e6}.get(args.precision) if args.voxels == 250000 else None,
+                     "traffic": None,
                      "l2": "flushed between launches (256 MB write)"})
+    tr = dram_traffic("gather_mma_warp", "ssc32_room_%d" % args.voxels, args.precision)
+    if tr:
+        roofline.update({"traffic": tr["bytes"], "traffic_from": tr})
     tcgen05 = None
     if args.precision != "fp32":  # the tcgen05 kernel on a wide layer, against the tensor roofline
         args.n_in, args.n_out = 128, 128
@@ -727,8 +818,10 @@ def main():
                                   % ("fp16 rows, kind::f16" if args.precision == "fp16" else "tf32", wide["sites"]),
                         "us_per_launch": wide["us_per_launch"],
                         "peak_note": "fp16: the measured dense bf16 peak; tf32: half of it (tf32 is not in MEASURED_PEAKS.json)",
-                        # from profiles/gather_gemm_tc_persist_f16_ssc128_room.md / gather_gemm_tf32_persist_ssc128_room.md
-                        "traffic": {"fp16": 170.8e6, "tf32": 248.4e6}.get(args.precision) if args.voxels == 250000 else None})
+                        "traffic": None})
+        tr = dram_traffic("gather_gemm_tc_persist", "ssc128_room_%d" % args.voxels, args.precision)
+        if tr:
+            tcgen05.update({"traffic": tr["bytes"], "traffic_from": tr})
     hashes = hash_bench(dev, 5, 2, ("c1", "room") if args.quick else ("c1", "room", "building"))
     for h in hashes:
         h["hbm_frac"] = h["GBps"] / hbm_peak
@@ -736,13 +829,13 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_full, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": {"fp32": "f32", "tf32": "tf32", "fp16": "f16"}[args.precision], "data": "synthetic",
             "config": {"workload": WORKLOAD, "voxels_per_scene": int(coords.shape[0]), "scenes": world,
-                       "voxel_layers_per_scene": voxel_layers, "precision": args.precision,
-                       "precision_note": {"fp32": "fp32 FFMA throughout",
-                                          "tf32": "fp32 tensors, tensor cores read them as tf32, fp32 accumulation",
-                                          "fp16": "BatchNorm hands fp16 rows to the convolution behind it (fp16 x fp16 products, "
-                                                  "fp32 accumulation and fp32 outputs); layers without a BatchNorm in front (first "
-                                                  "layer, 1x1 shortcuts) read fp32 as tf32"}[args.precision],
-                       "l2": "no flush: one frame streams ~1.5 GB of activations and maps, far above the 126 MB L2"},
+                       "voxel_layers_per_scene": voxel_layers, "l2": L2_NOTE},
+            "precision": {"name": args.precision,
+                          "note": {"fp32": "fp32 FFMA throughout",
+                                   "tf32": "fp32 tensors, tensor cores read them as tf32, fp32 accumulation",
+                                   "fp16": "BatchNorm hands fp16 rows to the convolution behind it (fp16 x fp16 products, "
+                                           "fp32 accumulation and fp32 outputs); layers without a BatchNorm in front (first "
+                                           "layer, 1x1 shortcuts) read fp32 as tf32"}[args.precision]},
             "incremental": {"ms_per_frame": ms_incre, "changed_points": int(inc_c.shape[0]),
                             "changed_frac": float(inc_c.shape[0]) / coords.shape[0],
                             "semantics": "reference (insert-only, no dilation)", "launches": int(launches_incre),
@@ -760,13 +853,15 @@ def main():
             "timing": {"regions_per_leg": REGIONS, "steps_per_region": args.steps, "reported": "median region",
                        "ms_per_step_of_each_region": region_ms, "legs": "full, incremental, exact, e2e as run"},
             "clocks": clocks, "roofline": roofline, "tcgen05": tcgen05,
-            "hash_build": hashes}
+            "hash_build": hashes,
+            # the same frame in the other precisions, value and ms per step (median of 3 regions of min(K, 20) steps)
+            "other_precisions": other,
+            "single_layer": configs01_bench(dev, 20, 3) if "configs01" in legs else None}
     if world == 1 and not args.no_cpu_baseline:
-        sample = min(args.voxels, 120000)
-        r = cpu_reference(sample, 2, 1)
+        r = cpu_reference(args.voxels, 3, 1)
         line["cpu_baseline"] = {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",
                                 "ms_per_step": r["ms_per_step"],
-                                "sample": "one full UNet frame on a %d-voxel room (same generator, thinned), "
+                                "sample": "3 full UNet frames (after 1 warm-up frame) on the same %d-voxel room, "
                                           "torch CPU threads = cores" % r["voxels"]}
     print(json.dumps(line))
     if dist is not None:

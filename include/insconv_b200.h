@@ -107,13 +107,20 @@ SCN_API int scn_metadata_query(scn_metadata *m, const int64_t size[3], const int
 /* ---------------------------------------------------------------------------
  * InputLayer / OutputLayer.
  * ------------------------------------------------------------------------- */
-/* What scn_input_layer_build builds beyond the input scale.  By default the library learns from use: once a
- * network of this process has asked for a 3x3x3 neighbour map, later grids get theirs inside the build (its counts
- * ride on the build's last host round trip), and once networks have gone down L stride-2 scales, the input layer
- * builds those L coarse scales right away, before feature kernels are queued behind which a round trip would have
- * to wait.  neighbour_maps: 1 always, 0 never (built on first use), -1 learn.  coarse_levels: 0..16, or -1 learn.
- * Results never depend on these settings, only when the work is done.  No counterpart in the reference. */
+/* What scn_input_layer_build builds beyond the input scale.  A grid build ends with a host round trip (sizes must reach
+ * the host); in the middle of a network that round trip first drains the queue of feature kernels.  A caller that knows
+ * what its network will ask for has it built by the input layer, while the stream is still empty: the 3x3x3 neighbour
+ * maps (their counts ride on the build's last round trip) and `coarse_levels` stride-2 scales, chained on the device
+ * with one round trip for all of them.  neighbour_maps: 1 build them, 0 leave them to first use; coarse_levels: 0..16.
+ * -1 in either place: no setting (the per-object setting falls back to the process default, the process default to
+ * "nothing ahead").  scn_set_build_ahead sets the process default; scn_metadata_set_build_ahead sets it for the next
+ * scn_input_layer_build on one metadata object; scn_metadata_build_used reports what the operators that ran on a
+ * metadata object went on to ask for (neighbour maps yes/no, deepest stride-2 level), which is what a network should
+ * pass for its next frame -- the Python InputLayer does exactly that, per network.  Results never depend on these
+ * settings, only when the work is done.  No counterpart in the reference. */
 SCN_API int scn_set_build_ahead(int neighbour_maps, int coarse_levels);
+SCN_API int scn_metadata_set_build_ahead(scn_metadata *m, int neighbour_maps, int coarse_levels);
+SCN_API int scn_metadata_build_used(scn_metadata *m, int *neighbour_maps, int *coarse_levels);
 
 /* Builds the finest grid from input points.  Replaces Metadata::inputLayer ->
  * inputLayerRulesSimple (Metadata/Metadata.cpp:442-463, Metadata/IOLayersRules.h:135-203)
@@ -134,6 +141,9 @@ SCN_API int scn_input_layer_forward(scn_metadata *m, const float *in, float *out
 SCN_API int scn_output_layer_forward(scn_metadata *m, const float *in, float *out, int64_t planes, void *stream);
 /* Number of input points of the last scn_input_layer_build (rules[0][2], IOLayersRules.h:11-16). */
 SCN_API int64_t scn_input_layer_n_points(scn_metadata *m);
+/* Number of sites of the input scale (rules[0][3]; Metadata::inputNActive, Metadata/Metadata.h:278), -1 without an
+ * input layer. */
+SCN_API int64_t scn_metadata_input_n_active(scn_metadata *m);
 /* The InputLayer rulebook in the reference's padded layout (CUDA/IOLayers.cu:7-12):
  * header HOST int32[4] = {mode, maxActive, nIn, nOut}; rows HOST int32 [nOut, 1+maxActive]
  * = {count, point indices ascending..., zero padding}.  Call with rows == NULL to get the header. */

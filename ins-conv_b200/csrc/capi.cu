@@ -74,6 +74,11 @@ struct scn_metadata {
   int mode = 0;
   int64_t batch_size = 0;
   cudaStream_t last_stream = nullptr;
+  // what the next scn_input_layer_build on this object builds beyond the input scale (-1: the process default), and
+  // what the network that ran on it went on to ask for (the caller's record for its next frame)
+  int ahead_ssc = -1, ahead_levels = -1;
+  bool used_ssc = false;
+  int used_levels = 0;
 
   scn::Grid *find(const int64_t *size) {
     auto it = grids.find(scn::to_size(size));
@@ -89,6 +94,8 @@ struct scn_metadata {
     }
     incre.clear();
     has_input = false;
+    used_ssc = false;
+    used_levels = 0;
   }
 };
 
@@ -106,19 +113,24 @@ static int need_grid(scn_metadata *m, const int64_t *size, Grid **g) {
   return SCN_OK;
 }
 
-// How many stride-2 levels below the input scale networks of this process have asked for so far.  Once known,
-// the input layer builds that many coarse grids right away, while nothing else is queued on the stream: a build
-// ends with a host round trip, which in the middle of a network drains the queue of feature kernels first.
-static std::atomic<int> g_pyramid_levels{0};
-// scn_set_build_ahead overrides what was learned (-1: use what was learned)
+// What an input-layer build does beyond the input scale: the metadata's own setting (scn_metadata_set_build_ahead),
+// else the process default (scn_set_build_ahead), else nothing.  A build ends with a host round trip, which in the
+// middle of a network drains the queue of feature kernels first: a caller that knows what its network will ask for
+// (the Python InputLayer reads it off the previous frame's metadata) has it built while the stream is still empty.
 static std::atomic<int> g_force_ssc{-1}, g_force_levels{-1};
-static bool want_ssc() {
+static bool want_ssc(const scn_metadata *m) {
+  if (m->ahead_ssc >= 0) return m->ahead_ssc != 0;
   const int f = g_force_ssc.load(std::memory_order_relaxed);
-  return f >= 0 ? f != 0 : ssc_expected();
+  return f > 0;
 }
-static int want_levels() {
+static int want_levels(const scn_metadata *m) {
+  if (m->ahead_levels >= 0) return m->ahead_levels;
   const int f = g_force_levels.load(std::memory_order_relaxed);
-  return f >= 0 ? f : g_pyramid_levels.load(std::memory_order_relaxed);
+  return f > 0 ? f : 0;
+}
+static int ensure_ssc(scn_metadata *m, Grid &g, cudaStream_t s) {
+  m->used_ssc = true;
+  return grid_build_ssc(g, s);
 }
 
 // coarse grid of in_size -> out_size (filter 2, stride 2), built on first use
@@ -131,15 +143,14 @@ static int need_coarse(scn_metadata *m, const int64_t *in_size, const int64_t *o
   *coarse = m->find(out_size);
   if (!*coarse) {
     std::unique_ptr<Grid> g(new Grid());
-    SCN_TRY(grid_build_coarse(*g, **fine, want_ssc(), s));
-    if (m->has_input && out_size[0] > 0) {  // remember how deep below the input scale this is
-      int level = 0;
-      for (int64_t sz = m->input_size[0]; sz > out_size[0] && sz % 2 == 0; sz /= 2) ++level;
-      int seen = g_pyramid_levels.load(std::memory_order_relaxed);
-      while (level > seen && !g_pyramid_levels.compare_exchange_weak(seen, level, std::memory_order_relaxed)) {}
-    }
+    SCN_TRY(grid_build_coarse(*g, **fine, want_ssc(m), s));
     *coarse = g.get();
     m->grids[to_size(out_size)] = std::move(g);
+  }
+  if (m->has_input && out_size[0] > 0) {  // how deep below the input scale the network has gone
+    int level = 0;
+    for (int64_t sz = m->input_size[0]; sz > out_size[0] && sz % 2 == 0; sz /= 2) ++level;
+    if (level > m->used_levels) m->used_levels = level;
   }
   if ((*coarse)->n_src != (*fine)->n) return fail(SCN_E_STATE, "coarse grid was not built from this fine grid");
   SCN_TRY(grid_build_conv(**coarse, **fine, s));
@@ -269,6 +280,21 @@ int scn_set_build_ahead(int neighbour_maps, int coarse_levels) {
   return SCN_OK;
 }
 
+int scn_metadata_set_build_ahead(scn_metadata *m, int neighbour_maps, int coarse_levels) {
+  if (!m) return fail(SCN_E_INVALID, "null metadata");
+  if (neighbour_maps < -1 || neighbour_maps > 1 || coarse_levels < -1 || coarse_levels > 16)
+    return fail(SCN_E_INVALID, "build-ahead settings out of range");
+  m->ahead_ssc = neighbour_maps;
+  m->ahead_levels = coarse_levels;
+  return SCN_OK;
+}
+int scn_metadata_build_used(scn_metadata *m, int *neighbour_maps, int *coarse_levels) {
+  if (!m) return fail(SCN_E_INVALID, "null metadata");
+  if (neighbour_maps) *neighbour_maps = m->used_ssc ? 1 : 0;
+  if (coarse_levels) *coarse_levels = m->used_levels;
+  return SCN_OK;
+}
+
 int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t *coords, int coords_on_host,
                           int64_t n_in, int ncols, int64_t batch_size, int mode, void *stream, int64_t *n_active) {
   if (!m || !size) return fail(SCN_E_INVALID, "null metadata or size");
@@ -286,7 +312,7 @@ int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t 
     SCN_CUDA(cudaMemcpyAsync(staged, coords, (size_t)n_in * ncols * 8, cudaMemcpyHostToDevice, s));
     dev_coords = staged;
   }
-  int r = grid_build(*g, dev_coords, ncols, nullptr, 0, n_in, true, nullptr, want_ssc(), s);
+  int r = grid_build(*g, dev_coords, ncols, nullptr, 0, n_in, true, nullptr, want_ssc(m), s);
   dev_free(staged, s);
   if (r != SCN_OK) {
     grid_free(*g, s);
@@ -302,7 +328,7 @@ int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t 
   // device with one host round trip for all of them
   std::vector<Size3> sizes;
   Size3 cur = m->input_size;
-  for (int level = 0, levels = want_levels(); level < levels; ++level) {
+  for (int level = 0, levels = want_levels(m); level < levels; ++level) {
     if (cur[0] % 2 || cur[1] % 2 || cur[2] % 2 || cur[0] < 2 || cur[1] < 2 || cur[2] < 2) break;
     cur = Size3{{cur[0] / 2, cur[1] / 2, cur[2] / 2}};
     sizes.push_back(cur);
@@ -315,7 +341,7 @@ int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t 
       ptrs.push_back(owned.back().get());
     }
     Grid *fine0 = m->find(m->input_size.data());
-    SCN_TRY(grid_build_coarse_chain(ptrs.data(), (int)ptrs.size(), *fine0, want_ssc(), s));
+    SCN_TRY(grid_build_coarse_chain(ptrs.data(), (int)ptrs.size(), *fine0, want_ssc(m), s));
     for (size_t i = 0; i < sizes.size(); ++i) m->grids[sizes[i]] = std::move(owned[i]);
   }
   return SCN_OK;
@@ -343,6 +369,11 @@ int64_t scn_input_layer_n_points(scn_metadata *m) {
   Grid *g;
   if (input_grid(m, &g) != SCN_OK) return -1;
   return g->n_src;
+}
+int64_t scn_metadata_input_n_active(scn_metadata *m) {
+  Grid *g;
+  if (input_grid(m, &g) != SCN_OK) return -1;
+  return g->n;
 }
 int scn_input_layer_rules(scn_metadata *m, int32_t header_host[4], int32_t *rows_host, void *stream) {
   Grid *g;
@@ -380,7 +411,7 @@ int scn_ssc_rulebook(scn_metadata *m, const int64_t size[3], int64_t counts_host
   Grid *g;
   SCN_TRY(need_grid(m, size, &g));
   cudaStream_t s = (cudaStream_t)stream;
-  SCN_TRY(grid_build_ssc(*g, s));
+  SCN_TRY(ensure_ssc(m, *g, s));
   if (counts_host)
     for (int k = 0; k < 27; ++k) counts_host[k] = g->nbr_count[k];
   if (pairs_host) SCN_TRY(map_to_pairs(g->nbr, 27, g->n, 0, g->nbr_total, pairs_host, s));
@@ -425,7 +456,7 @@ int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int
   if (g->n == 0) return SCN_OK;
   SCN_TRY(check_feat(in, out, weight, n_in, n_out));
   cudaStream_t s = (cudaStream_t)stream;
-  SCN_TRY(grid_build_ssc(*g, s));
+  SCN_TRY(ensure_ssc(m, *g, s));
   SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0, precision, s));
   if (flops) *flops = (double)g->nbr_total * (double)n_in * (double)n_out;
   return SCN_OK;
@@ -440,7 +471,7 @@ int scn_ssc_forward_add(scn_metadata *m, const int64_t size[3], const float *in,
   SCN_TRY(check_feat(in, out, weight, n_in, n_out));
   if (!addend) return fail(SCN_E_INVALID, "null addend");
   cudaStream_t s = (cudaStream_t)stream;
-  SCN_TRY(grid_build_ssc(*g, s));
+  SCN_TRY(ensure_ssc(m, *g, s));
   SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, nullptr, out, out_stride, n_in, n_out, addend,
                    addend_stride, precision, s));
   if (flops) *flops = (double)g->nbr_total * (double)n_in * (double)n_out;
@@ -543,7 +574,7 @@ int scn_incre_input_layer_forward(scn_metadata *m, scn_metadata *pre, const floa
   if (g->n && (!in || !out || !pre_out)) return fail(SCN_E_INVALID, "null features");
   // The incremental neighbour maps of every scale both frames have, now and with one host round trip, instead of
   // one round trip per scale in the middle of the network (once a network has used neighbour maps at all).
-  if (want_ssc()) {
+  if (want_ssc(m)) {
     std::vector<IncreNbrJob> jobs;
     std::vector<IncreMaps *> ims;
     for (auto &kv : m->grids) {
@@ -598,7 +629,7 @@ int scn_incre_ssc_forward(scn_metadata *m, scn_metadata *pre, const int64_t size
   if (g->n == 0) return SCN_OK;
   SCN_TRY(check_feat(in, out, weight, n_in, n_out));
   if (!pre_in) return fail(SCN_E_INVALID, "null saved features");
-  SCN_TRY(grid_build_ssc(*g, s));
+  SCN_TRY(ensure_ssc(m, *g, s));
   SCN_TRY(need_nbr2(g, pg, im, s));
   SCN_TRY(gather_gemm(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0, precision, s));
   if (im->nbr2_total)

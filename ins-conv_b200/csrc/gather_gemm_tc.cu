@@ -26,12 +26,6 @@
 // Every wait on an mbarrier is bounded; a wait that runs out sets an error word that the host reads
 // at its next scn_check_errors, and the kernel still releases its tensor memory before returning.
 #include "internal.h"
-#ifdef SCN_TC_PROFILE
-#include <stdio.h>
-#define PROF(x) x
-#else
-#define PROF(x)
-#endif
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <stddef.h>
@@ -532,12 +526,10 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
     const uint32_t dst_even = (uint32_t)(q << 7) + (uint32_t)((c ^ q) << 4);
     const uint32_t dst_odd = (uint32_t)((q + 4) << 7) + (uint32_t)((c ^ (q + 4)) << 4);
     const unsigned char *in_c = in + (size_t)c * 16;  // this lane's 16-byte chunk of a row block
-    PROF(long long t_map = 0; long long t_empty = 0; long long t_issue = 0; long long t_land = 0; long long t_all0 = clock64(); long long own = 0;)
     int mbuf = 0;
     uint32_t mphase = 0;
     for (long long i = 0; i < my_tiles && !*failed; ++i) {
       const long long item = (long long)blockIdx.x + i * gridDim.x;
-      PROF(long long tm0 = clock64();)
       // This tile's map entries were published while the previous tile ran, so the wait is normally free.  Once it
       // has passed, every producer warp is done with the tile before the previous one, whose buffer (the third)
       // takes the next tile's entries; the loads for the tile after that start right away.
@@ -568,15 +560,12 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
       }
       int k = (Tz > 0 && rest) ? __ffs(rest) - 1 : 0;
       bool stop = false;
-      PROF(t_map += clock64() - tm0;)
       for (int it = 0; it < T; ++it) {
         if (slot == pw) {
-          PROF(long long te0 = clock64(); ++own;)
           if (wrapped > 0 && !mbar_wait(smem_u32(&ctl->empty[slot]), (wrapped - 1) & 1u, failed)) {
             stop = true;
             break;
           }
-          PROF(long long te1 = clock64(); t_empty += te1 - te0;)
           const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
           const uint32_t bar = smem_u32(&ctl->full[slot]);
           if (lane == 0) {
@@ -601,12 +590,10 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
             }
           }
           cp_async_commit();
-          PROF(long long tl0 = clock64(); t_issue += tl0 - te1;)
           cp_async_wait<0>();
           fence_async_proxy();
           __syncwarp();
           if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-          PROF(t_land += clock64() - tl0;)
         }
         if (++slot == stages) {
           slot = 0;
@@ -620,7 +607,6 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
       }
       if (stop) break;
     }
-    PROF(if (blockIdx.x == 0 && lane == 0) printf("prod %d: total %lld map %lld empty-wait %lld issue %lld landing %lld own steps %lld tiles %lld\n", pw, clock64() - t_all0, t_map, t_empty, t_issue, t_land, own, my_tiles);)
     // sentinel step: tells the tensor-core warp that no more work follows
     if (slot == pw && !*failed) {
       bool okw = true;
@@ -646,32 +632,24 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
     long long tile_i = 0;
     int slot = 0;
     uint32_t phase = 0, a_lo = a_lo0;
-    PROF(long long t_full = 0; long long t_acc = 0; long long t0 = clock64(); long long nsteps = 0; long long t_mma = 0;)
     bool alive = true;
     while (alive) {
-      PROF(long long a0 = clock64();)
       if (!mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) break;
-      PROF(t_full += clock64() - a0;)
       const uint32_t info = __shfl_sync(0xffffffffu, ctl->info[slot], 0);
       if (info & kInfoDone) break;
       const int T = (int)(info >> 8);
       const int buf = (int)(tile_i & 1);
       const uint32_t tmem_d = tmem_base + (uint32_t)buf * acc_cols;
       // the epilogue must have drained this accumulator (used by tile tile_i - 2)
-      PROF(long long b0 = clock64();)
       if (tile_i >= 2 && !mbar_wait(smem_u32(&ctl->accempty[buf]), (uint32_t)(((tile_i >> 1) - 1) & 1), failed)) break;
-      PROF(t_acc += clock64() - b0;)
       tc_fence_after();  // the epilogue's TMEM reads of this accumulator are ordered before the new MMAs
       for (int t = 0; t < T; ++t) {
         if (t > 0) {
-          PROF(long long a1 = clock64();)
           if (!mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) {
             alive = false;
             break;
           }
-          PROF(t_full += clock64() - a1;)
         }
-        PROF(long long c1 = clock64(); ++nsteps;)
         if (elect_one()) {
           const uint32_t b_lo = a_lo + b_off16;
           mma_lohi<HALF>(tmem_d, a_lo, b_lo, desc_hi, idesc, t > 0 ? 1u : 0u);
@@ -687,23 +665,18 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
           phase ^= 1u;
           a_lo = a_lo0;
         }
-        PROF(t_mma += clock64() - c1;)
       }
       ++tile_i;
     }
-    PROF(if (blockIdx.x == 0 && lane == 0) printf("mma: total %lld full-wait %lld accempty-wait %lld issue+commit %lld steps %lld\n", clock64() - t0, t_full, t_acc, t_mma, nsteps);)
     __syncwarp();
   } else {
     // =========================== epilogue =========================================================
-    PROF(long long t_wait = 0; long long t_work = 0; long long t0 = clock64();)
     for (long long i = 0; i < my_tiles; ++i) {
       const long long item = (long long)blockIdx.x + i * gridDim.x;
       const long long tile = item / Z;
       float *pdst = partial ? partial + (((item % Z) * tiles + tile) * kTileM + warp * 32 + lane) * Cout : nullptr;
       const int buf = (int)(i & 1);
-      PROF(long long w0 = clock64();)
       if (!mbar_wait(smem_u32(&ctl->accfull[buf]), (uint32_t)((i >> 1) & 1), failed)) break;
-      PROF(long long w1 = clock64(); t_wait += w1 - w0;)
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t)buf * acc_cols + ((uint32_t)(warp * 32) << 16);
       const long long row = tile * kTileM + warp * 32 + lane;
@@ -736,9 +709,7 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
           }
         }
       }
-      PROF(t_work += clock64() - w1;)
     }
-    PROF(if (blockIdx.x == 0 && tid == 0) printf("epi: total %lld accfull-wait %lld work %lld\n", clock64() - t0, t_wait, t_work);)
   }
   tc_fence_before();
   __syncthreads();
@@ -968,14 +939,10 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
   bool partial_pooled = false;
   if (Z > 1) SCN_TRY(splitk_scratch(&partial, (size_t)Z * tiles * kTileM * Cout, s, &partial_pooled));
   const dim3 grid((unsigned)tiles, (unsigned)Z);
-  static const bool use_persist = []() {
-    const char *e = getenv("INSCONV_TC_KERNEL");
-    return !(e && e[0] == 't');  // INSCONV_TC_KERNEL=tile forces the simple per-tile kernel (development aid)
-  }();
   const size_t fixed_p = sizeof(CtlP) + (size_t)kMapBufs * K * kTileM * sizeof(int) + 1024;
   int st_p = (int)((220 * 1024 - fixed_p) / stage_bytes);
   if (st_p > kMaxStages) st_p = kMaxStages;
-  if (use_persist && cols * 2 <= 512 && st_p >= 4) {
+  if (cols * 2 <= 512 && st_p >= 4) {
     CUtensorMap tmB;
     if (packed) SCN_TRY(cached_tensor_map(&tmB, Wt, false, (uint64_t)Cin, (uint64_t)K * Cout, 32, (uint32_t)Cout));
     else SCN_TRY(encode_2d(&tmB, Wt, false, (uint64_t)Cin, (uint64_t)K * Cout, (uint64_t)Cin * 4, 32, (uint32_t)Cout));
@@ -1078,10 +1045,7 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
     // Below ~500 rows the slab kernel in turn has too few warps (rows/16 x n_out/32) and its serial reduction per
     // warp is longer than the split reduction plus its second launch (measured on 60- and 230-row levels).  Measured
     // with 96 planes: 4.4k rows 17.8 us against 25.6 us, 16k rows 32.0 against 32.4 (and one launch instead of two).
-    static const long long slab_rows = []() {
-      const char *e = getenv("INSCONV_SLAB_MAX_ROWS");  // development aid
-      return e ? atoll(e) : 16384ll;
-    }();
+    const long long slab_rows = 16384;
     if (n_out >= 512 && n_out <= slab_rows && warp_slab_f16_shape(K, Cin, Cout))
       return gather_mma_slab_f16(in, in_stride, map, K, n_out, static_cast<const __half *>(Wp) + K * Cout * padded_planes(Cin), bias,
                                  out, out_stride, Cin, Cout, init, init_stride, s);

@@ -507,14 +507,7 @@ __global__ void k_pack_weights_mma(const float *__restrict__ W, float *__restric
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-int env_int(const char *name, int dflt) {
-  const char *e = getenv(name);
-  return e ? atoi(e) : dflt;
-}
-int max_planes() {  // development aid: widest layer the warp-level kernels take (0: off)
-  static const int v = env_int("INSCONV_WARP_MMA_MAX", 64);
-  return v;
-}
+constexpr int max_planes() { return 64; }  // widest layer the warp-level kernels take
 template <int CI, int CO, int NTR, int MINB>
 void launch_warp(const float *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const float *Wp,
                  const float *bias, float *out, int64_t out_stride, const float *init, int64_t init_stride, cudaStream_t s) {

@@ -653,9 +653,6 @@ static void take(void *dst, size_t bytes, int slot) {  // after the synchronisat
   if (pin && bytes <= 512) memcpy(dst, pin + 512 * slot, bytes);
 }
 
-static std::atomic<bool> g_ssc_seen{false};
-bool ssc_expected() { return g_ssc_seen.load(std::memory_order_relaxed); }
-
 int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift, int64_t n_src,
                bool want_csr, const Box *box_hint, bool with_ssc, cudaStream_t s) {
   grid_free(g, s);
@@ -990,7 +987,6 @@ int build_incre_nbr_batch(const IncreNbrJob *jobs, int count, cudaStream_t s) {
 }
 
 int grid_build_ssc(Grid &g, cudaStream_t s) {
-  g_ssc_seen.store(true, std::memory_order_relaxed);
   if (g.nbr || g.n == 0) return SCN_OK;
   SCN_TRY(dev_alloc_t(&g.nbr, (size_t)g.n * 27, s));
   if (g.bitmap && g.prefix) {

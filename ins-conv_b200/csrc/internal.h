@@ -122,8 +122,6 @@ int grid_build_coarse(Grid &coarse, const Grid &fine, bool with_ssc, cudaStream_
 // `count` successive coarser scales of fine0 (levels[0] from fine0, levels[1] from levels[0], ...) chained on the
 // device, one host round trip for all of them; buffers are sized by the bound n_level <= min(n_fine0, cells of the box)
 int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, bool with_ssc, cudaStream_t s);
-// true once a neighbour map has been asked for in this process: later grids build theirs right away
-bool ssc_expected();
 int grid_build_ssc(Grid &g, cudaStream_t s);               // fills nbr / nbr_count
 int grid_build_conv(Grid &coarse, const Grid &fine, cudaStream_t s);  // fills child / fine_up
 // by_rank: answer from the grid's ranking structure (bitmap + prefix sums) instead of probing its hash table

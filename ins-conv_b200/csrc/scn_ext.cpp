@@ -34,6 +34,21 @@ void need_cuda_f32(const at::Tensor &t, const char *name) {
   TORCH_CHECK(t.scalar_type() == at::kFloat, name, " must be float32");
 }
 
+// A tensor that may be empty ("no bias"): when it has elements they must be CUDA float32 and `count` long, so that a
+// module left on the CPU or built for other planes raises here instead of handing a bad pointer to a kernel.
+void need_opt_cuda_f32(const at::Tensor &t, int64_t count, const char *name) {
+  if (!t.defined() || t.numel() == 0) return;
+  need_cuda_f32(t, name);
+  TORCH_CHECK(t.numel() == count && t.is_contiguous(), name, " must hold ", count, " contiguous values; got ", t.numel());
+}
+
+// Feature rows must live on the sites the operator indexes them by: [rows of that grid, planes the weights take].
+void need_rows(const at::Tensor &t, int64_t rows, int64_t planes, const char *name) {
+  TORCH_CHECK(rows >= 0, name, ": Metadata has no grid at the spatial size these features are said to live on");
+  TORCH_CHECK(t.dim() == 2 && t.size(0) == rows && t.size(1) == planes, name, " must be [", rows, ", ", planes, "]; got [",
+              t.dim() == 2 ? t.size(0) : -1, ", ", t.dim() == 2 ? t.size(1) : -1, "]");
+}
+
 // Feature rows handed to a convolution: fp32, or fp16 as written by a BatchNorm in front of it ('fp16' precision).
 // With fp16 rows the caller must hand in the matching fp16 weight pack (pack_weights_f16).
 struct FeatArg {
@@ -138,6 +153,15 @@ class Metadata3 {
     Size3 s(spatialSize);
     return scn_metadata_n_active(h_, s.v);
   }
+  // what the next InputLayer build on this object builds beyond the input scale / what the network then asked for
+  void setBuildAhead(int neighbour_maps, int coarse_levels) {
+    check(scn_metadata_set_build_ahead(h_, neighbour_maps, coarse_levels), "Metadata.setBuildAhead");
+  }
+  std::pair<int, int> buildUsed() {
+    int nm = 0, levels = 0;
+    check(scn_metadata_build_used(h_, &nm, &levels), "Metadata.buildUsed");
+    return {nm, levels};
+  }
 
  private:
   scn_metadata *h_ = nullptr;
@@ -158,7 +182,8 @@ double SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filt
   auto w = weight.contiguous();
   const int64_t n = scn_metadata_n_active(m.h(), s.v);
   TORCH_CHECK(n >= 0, "Metadata has no grid at this spatial size");
-  TORCH_CHECK(in.size(0) == n && in.size(1) == w.size(1), "input_features must be [nActive, nIn]");
+  need_rows(in, n, w.size(1), "input_features");
+  need_opt_cuda_f32(bias, w.size(2), "bias");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
   WeightArg wa(w, packed, fa.half);
@@ -191,6 +216,8 @@ double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at:
   Size3 si(inputSize), so(outputSize);
   const at::Tensor &in = fa.t;
   auto w = weight.contiguous();
+  need_rows(in, scn_metadata_n_active(m.h(), si.v), w.size(1), "input_features");
+  need_opt_cuda_f32(bias, w.size(2), "bias");
   int64_t n = 0;
   check(scn_conv_prepare(m.h(), si.v, so.v, stream_of(in), &n), "Convolution_updateOutput");
   output_features.resize_({n, w.size(2)});
@@ -216,6 +243,9 @@ double Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, a
   auto w = weight.contiguous();
   const int64_t n = scn_metadata_n_active(m.h(), so.v);
   TORCH_CHECK(n >= 0, "Deconvolution: Metadata has no grid at the output spatial size");
+  TORCH_CHECK(weight.dim() == 3 && weight.size(0) == 8, "weight must be [8, nIn, nOut]");
+  need_rows(in, scn_metadata_n_active(m.h(), si.v), w.size(1), "input_features");
+  need_opt_cuda_f32(bias, w.size(2), "bias");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
   WeightArg wa(w, packed, fa.half);
@@ -231,6 +261,13 @@ void BatchNormalization_updateOutput(at::Tensor input_features, at::Tensor outpu
                                      at::Tensor weight, at::Tensor bias, double eps, double momentum, bool train,
                                      double leakiness) {
   need_cuda_f32(input_features, "input_features");
+  TORCH_CHECK(input_features.dim() == 2, "input_features must be [rows, planes]");
+  need_cuda_f32(runningMean, "runningMean");
+  need_cuda_f32(runningVar, "runningVar");
+  need_opt_cuda_f32(runningMean, input_features.size(1), "runningMean");
+  need_opt_cuda_f32(runningVar, input_features.size(1), "runningVar");
+  need_opt_cuda_f32(weight, input_features.size(1), "weight");
+  need_opt_cuda_f32(bias, input_features.size(1), "bias");
   c10::cuda::CUDAGuard guard(input_features.device());
   auto in = input_features.contiguous();
   if (output_features.scalar_type() == at::kHalf) {  // fp16 rows for the convolution that follows ('fp16' precision)
@@ -268,6 +305,9 @@ double NetworkInNetwork_updateOutput(at::Tensor input_features, at::Tensor outpu
   c10::cuda::CUDAGuard guard(input_features.device());
   auto in = input_features.contiguous();
   auto w = weight.contiguous();
+  TORCH_CHECK(w.dim() == 2, "weight must be [nIn, nOut]");
+  need_rows(in, in.dim() == 2 ? in.size(0) : -1, w.size(0), "input_features");
+  need_opt_cuda_f32(bias, w.size(1), "bias");
   output_features.resize_({in.size(0), w.size(1)});
   double flops = 0;
   WeightArg wa(w, packed);
@@ -311,6 +351,8 @@ void OutputLayer_updateOutput(Metadata3 &m, at::Tensor input_features, at::Tenso
   auto in = input_features.contiguous();
   const int64_t n = scn_input_layer_n_points(m.h());
   TORCH_CHECK(n >= 0, "OutputLayer: Metadata has no input layer");
+  TORCH_CHECK(in.dim() == 2 && in.size(0) == scn_metadata_input_n_active(m.h()),
+              "input_features must have one row per site of the input scale");
   output_features.resize_({n, in.size(1)});
   check(scn_output_layer_forward(m.h(), in.data_ptr<float>(), output_features.data_ptr<float>(), in.size(1),
                                  stream_of(in)),
@@ -332,6 +374,11 @@ double Incre_SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tenso
   auto w = weight.contiguous();
   const int64_t n = scn_metadata_n_active(m.h(), s.v);
   TORCH_CHECK(n >= 0, "Metadata has no grid at this spatial size");
+  need_cuda_f32(weight, "weight");
+  TORCH_CHECK(w.dim() == 3 && w.size(0) == 27, "weight must be [27, nIn, nOut]");
+  need_rows(in, n, w.size(1), "input_features");
+  need_rows(pre, scn_metadata_n_active(pre_m.h(), s.v), w.size(1), "pre_input_feats");
+  need_opt_cuda_f32(bias, w.size(2), "bias");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
   WeightArg wa(w, packed);
@@ -365,6 +412,11 @@ double Incre_Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputS
   auto w = weight.contiguous();
   const int64_t n = scn_metadata_n_active(m.h(), so.v);
   TORCH_CHECK(n >= 0, "Deconvolution: Metadata has no grid at the output spatial size");
+  need_cuda_f32(weight, "weight");
+  TORCH_CHECK(w.dim() == 3 && w.size(0) == 8, "weight must be [8, nIn, nOut]");
+  need_rows(in, scn_metadata_n_active(m.h(), si.v), w.size(1), "input_features");
+  need_rows(pre, scn_metadata_n_active(pre_m.h(), si.v), w.size(1), "pre_input_feats");
+  need_opt_cuda_f32(bias, w.size(2), "bias");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
   WeightArg wa(w, packed);
@@ -389,6 +441,18 @@ void Incre_BatchNormalization_updateOutput(at::Tensor input_features, at::Tensor
   auto in = input_features.contiguous();
   auto po = pre_output_feats.contiguous();
   auto pi = pre_input_feats.contiguous();
+  need_cuda_f32(po, "pre_output_feats");
+  need_cuda_f32(pi, "pre_input_feats");
+  TORCH_CHECK(in.dim() == 2, "input_features must be [rows, planes]");
+  need_rows(in, scn_metadata_n_active(m.h(), s.v), in.size(1), "input_features");
+  need_rows(po, scn_metadata_n_active(pre_m.h(), s.v), in.size(1), "pre_output_feats");
+  need_rows(pi, scn_metadata_n_active(pre_m.h(), s.v), in.size(1), "pre_input_feats");
+  need_cuda_f32(runningMean, "runningMean");
+  need_cuda_f32(runningVar, "runningVar");
+  need_opt_cuda_f32(runningMean, in.size(1), "runningMean");
+  need_opt_cuda_f32(runningVar, in.size(1), "runningVar");
+  need_opt_cuda_f32(weight, in.size(1), "weight");
+  need_opt_cuda_f32(bias, in.size(1), "bias");
   output_features.resize_as_(in);
   if (in.numel() == 0) return;
   check(scn_incre_bn_forward(m.h(), pre_m.h(), s.v, in.data_ptr<float>(), in.size(1),
@@ -408,6 +472,7 @@ void Incre_InputLayer_updateOutput(Metadata3 &m, at::Tensor spatialSize, at::Ten
   auto po = pre_output_feats.contiguous();
   build_input(m, spatialSize, input_coords, in, batchSize, mode);
   Size3 s(spatialSize);
+  need_rows(po, scn_metadata_n_active(pre_m.h(), s.v), in.size(1), "pre_output_feats");
   output_features.resize_({scn_metadata_n_active(m.h(), s.v), in.size(1)});
   check(scn_incre_input_layer_forward(m.h(), pre_m.h(), in.data_ptr<float>(), output_features.data_ptr<float>(),
                                       po.data_ptr<float>(), in.size(1), stream_of(in)),
@@ -423,6 +488,9 @@ void Incre_OutputLayer_updateOutput(Metadata3 &m, at::Tensor input_features, at:
   auto pi = pre_input_feats.contiguous();
   const int64_t n = scn_input_layer_n_points(m.h());
   TORCH_CHECK(n >= 0, "OutputLayer: Metadata has no input layer");
+  TORCH_CHECK(in.dim() == 2 && in.size(0) == scn_metadata_input_n_active(m.h()),
+              "input_features must have one row per site of the input scale");
+  need_rows(pi, scn_metadata_input_n_active(pre_m.h()), in.size(1), "pre_input_feats");
   output_features.resize_({n, in.size(1)});
   check(scn_incre_output_layer_forward(m.h(), pre_m.h(), in.data_ptr<float>(), output_features.data_ptr<float>(),
                                        pi.data_ptr<float>(), in.size(1), stream_of(in)),
@@ -480,7 +548,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
       .def("clear", &Metadata3::clear)
       .def("getSpatialLocations", &Metadata3::getSpatialLocations)
       .def("getSpatialLocationsDevice", &Metadata3::getSpatialLocationsDevice)
-      .def("getNActive", &Metadata3::getNActive);
+      .def("getNActive", &Metadata3::getNActive)
+      .def("setBuildAhead", &Metadata3::setBuildAhead)
+      .def("buildUsed", &Metadata3::buildUsed);
   mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("dilated_rate"), pybind11::arg("packed") = at::Tensor(), pybind11::arg("addend") = at::Tensor());
   mod.def("Convolution_updateOutput", &Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());
   mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());

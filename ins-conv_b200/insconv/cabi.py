@@ -52,6 +52,7 @@ PROTOTYPES = {
     "scn_input_layer_forward": (_int, [_p, _p, _p, _i64, _p]),
     "scn_output_layer_forward": (_int, [_p, _p, _p, _i64, _p]),
     "scn_input_layer_n_points": (_i64, [_p]),
+    "scn_metadata_input_n_active": (_i64, [_p]),
     "scn_input_layer_rules": (_int, [_p, _p, _p, _p]),
     "scn_ssc_rulebook": (_int, [_p, _i64p, _p, _p, _p]),
     "scn_conv_rulebook": (_int, [_p, _i64p, _i64p, _p, _p, _p]),
@@ -59,6 +60,8 @@ PROTOTYPES = {
     "scn_pack_weights": (_int, [_p, _i64, _i64, _i64, _p, _p]),
     "scn_ssc_forward": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_set_build_ahead": (_int, [_int, _int]),
+    "scn_metadata_set_build_ahead": (_int, [_p, _int, _int]),
+    "scn_metadata_build_used": (_int, [_p, C.POINTER(_int), C.POINTER(_int)]),
     "scn_packed_size_f16": (_i64, [_i64, _i64, _i64]),
     "scn_weights_packable_f16": (_int, [_i64, _i64, _i64]),
     "scn_pack_weights_f16": (_int, [_p, _i64, _i64, _i64, _p, _p]),
@@ -310,11 +313,65 @@ class Metadata(object):
              ptr(weight), ptr(bias), weight.shape[1], n_out, precision, _stream(), C.byref(fl))
         return out, fl.value
 
+    # -- incremental ("Incre_*") ops: self holds the frame's changed sites, `pre` the last full frame -------------
+    def incre_input_forward(self, pre, feats, pre_out):
+        import torch
+        feats = feats.contiguous()
+        out = torch.empty(self.n_active_input(), feats.shape[1], dtype=torch.float32, device=feats.device)
+        call("scn_incre_input_layer_forward", self.h, pre.h, ptr(feats), ptr(out), ptr(pre_out.contiguous()), feats.shape[1],
+             _stream())
+        return out
+
+    def incre_output_forward(self, pre, feats, pre_in):
+        import torch
+        feats = feats.contiguous()
+        out = torch.empty(self.n_points(), feats.shape[1], dtype=torch.float32, device=feats.device)
+        call("scn_incre_output_layer_forward", self.h, pre.h, ptr(feats), ptr(out), ptr(pre_in.contiguous()), feats.shape[1],
+             _stream())
+        return out
+
+    def incre_ssc_forward(self, pre, size, x, weight, pre_in, bias=None, precision=PREC_FP32):
+        import torch
+        x, weight, pre_in = x.contiguous(), weight.contiguous(), pre_in.contiguous()
+        n_out = weight.shape[2]
+        out = torch.empty(x.shape[0], n_out, dtype=torch.float32, device=x.device)
+        fl = _dbl(0)
+        call("scn_incre_ssc_forward", self.h, pre.h, size3(size), ptr(x), x.shape[1], ptr(out), n_out, ptr(weight), ptr(bias),
+             ptr(pre_in), pre_in.shape[1], weight.shape[1], n_out, precision, _stream(), C.byref(fl))
+        return out, fl.value
+
+    def incre_deconv_forward(self, pre, in_size, out_size, x, weight, pre_in, bias=None, precision=PREC_FP32):
+        import torch
+        x, weight, pre_in = x.contiguous(), weight.contiguous(), pre_in.contiguous()
+        n_out = weight.shape[2]
+        out = torch.empty(self.n_active(out_size), n_out, dtype=torch.float32, device=x.device)
+        fl = _dbl(0)
+        call("scn_incre_deconv_forward", self.h, pre.h, size3(in_size), size3(out_size), ptr(x), x.shape[1], ptr(out), n_out,
+             ptr(weight), ptr(bias), ptr(pre_in), pre_in.shape[1], weight.shape[1], n_out, precision, _stream(), C.byref(fl))
+        return out, fl.value
+
+    def incre_bn_forward(self, pre, size, x, mean, var, gamma, beta, eps, leak, pre_out, pre_in):
+        import torch
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        call("scn_incre_bn_forward", self.h, pre.h, size3(size), ptr(x), x.shape[1], ptr(out), x.shape[1], x.shape[1], ptr(mean),
+             ptr(var), ptr(gamma), ptr(beta), float(eps), float(leak), ptr(pre_out.contiguous()), ptr(pre_in.contiguous()),
+             _stream())
+        return out
+
+
+_cudart = None
+
 
 def _memcpy_d2d(dst, src, nbytes):
-    import torch
-    rt = torch.cuda.cudart()
-    r = rt.cudaMemcpy(dst, src, nbytes, 3)  # cudaMemcpyDeviceToDevice
+    """cudaMemcpy(device -> device) through the CUDA runtime torch has already loaded."""
+    global _cudart
+    import torch  # noqa: F401
+    if _cudart is None:
+        _cudart = C.CDLL("libcudart.so.12")
+        _cudart.cudaMemcpy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+        _cudart.cudaMemcpy.restype = C.c_int
+    r = _cudart.cudaMemcpy(dst, src, nbytes, 3)  # cudaMemcpyDeviceToDevice
     if int(r) != 0:
         raise ScnError(-2, "cudaMemcpy failed: %s" % r)
 

@@ -321,6 +321,18 @@ class InputLayer(Module):
             feats = feats.to(self.device if self.device else "cuda")
         feats = feats.float()
         output = SparseConvNetTensor(metadata=Metadata(self.dimension), spatial_size=self.spatial_size)
+        # What this network asked of its previous frame's metadata beyond the input scale (neighbour maps, stride-2
+        # levels) is built by this frame's input layer right away, before feature kernels are queued (a grid build
+        # ends with a host round trip).  Kept per InputLayer, i.e. per network.
+        last = self.__dict__.get("_last_meta")
+        if last is not None:
+            used = last.buildUsed()
+            ahead = self.__dict__.get("_ahead", (0, 0))
+            _keep(self, _ahead=(max(ahead[0], used[0]), max(ahead[1], used[1])))
+        ahead = self.__dict__.get("_ahead")
+        if ahead is not None:
+            output.metadata.setBuildAhead(*ahead)
+        _keep(self, _last_meta=output.metadata)
         out = feats.new_empty(0)
         if increment == "exact":
             assert self.mode == 4, "the exact incremental mode keeps per-voxel means (InputLayer mode 4)"
@@ -346,10 +358,13 @@ class InputLayer(Module):
 
     @staticmethod
     def _voxel_keys(coords):
+        """The library's own key: batch << 48 | z << 32 | y << 16 | x (coordinates up to 65534, batch up to 32766)."""
         c = coords.long()
-        k = (c[:, 2] << 42) | (c[:, 1] << 21) | c[:, 0]
+        assert c.numel() == 0 or (int(c.min()) >= 0 and int(c[:, :3].max()) <= 65534), "coordinate outside the key range"
+        k = (c[:, 2] << 32) | (c[:, 1] << 16) | c[:, 0]
         if c.shape[1] > 3:
-            k = k | (c[:, 3] << 58)
+            assert int(c[:, 3].max()) <= 32766, "batch index outside the key range"
+            k = k | (c[:, 3] << 48)
         return k
 
     def delete_voxels(self, coords):

@@ -1,6 +1,6 @@
 """Feature kernels through the C ABI vs the CPU oracle.
 
-Tolerances (stated by the north star of this build): fp32 outputs within 1e-4 relative; the metric used
+Tolerances: fp32 outputs within 1e-4 relative, the parity bar for fp32; the metric used
 is max|a-b| / max(|b|_max, 1e-6) per tensor plus an element-wise allclose with rtol = atol = 1e-4.
 """
 import numpy as np
