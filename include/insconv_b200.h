@@ -121,6 +121,14 @@ SCN_API int scn_metadata_query(scn_metadata *m, const int64_t size[3], const int
 SCN_API int scn_set_build_ahead(int neighbour_maps, int coarse_levels);
 SCN_API int scn_metadata_set_build_ahead(scn_metadata *m, int neighbour_maps, int coarse_levels);
 SCN_API int scn_metadata_build_used(scn_metadata *m, int *neighbour_maps, int *coarse_levels);
+/* Hands the experience of the previous frame's metadata object to a new one: what its network asked for becomes the new
+ * object's build-ahead setting, and the bounding box its input layer measured (with a margin) becomes the box the next
+ * input-layer build lays its ranking bitmap out for -- keys, box and occupancy bits then come out of ONE pass over the
+ * coordinates and the build has a single host round trip, at its end.  A frame that does not fit the inherited box is
+ * built again with the box that pass measured; results never depend on what was inherited.  A metadata object that is
+ * built on repeatedly inherits from itself.  No counterpart in the reference (which creates a fresh Metadata per frame,
+ * sparseconvnet/ioLayers.py:54-57, and measures nothing ahead). */
+SCN_API int scn_metadata_inherit(scn_metadata *m, const scn_metadata *previous);
 
 /* Builds the finest grid from input points.  Replaces Metadata::inputLayer ->
  * inputLayerRulesSimple (Metadata/Metadata.cpp:442-463, Metadata/IOLayersRules.h:135-203)
@@ -212,6 +220,40 @@ SCN_API int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float 
 SCN_API int scn_ssc_forward_add(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
                         int64_t out_stride, const float *weight, const float *addend, int64_t addend_stride,
                         int64_t n_in, int64_t n_out, int precision, void *stream, double *flops);
+/* What a convolution's epilogue does with a finished output row besides (or instead of) storing it.  No counterpart in
+ * the reference, whose network runs AddTable (sparseconvnet/tables.py) and BatchNormalization
+ * (CUDA/BatchNormalization.cu:78-107) as passes of their own over the whole tensor.
+ *   addend      rows [n, n_out] (stride addend_stride) added to the result: the residual sum of a ResNet block.  With an
+ *               addend no bias is applied.  It may be `out` itself.
+ *   bn_scale, bn_shift, bn_leakiness, bn_out, bn_out_stride
+ *               second output: leaky(v * bn_scale[c] + bn_shift[c]) of the finished value v (addend included) as fp16
+ *               rows -- the BatchNorm + ReLU that follows in the network (scale = gamma / sqrt(var + eps), shift = beta -
+ *               mean * scale), ready for the next convolution to gather.  Saturates at +-65504 like scn_bn_forward_f16.
+ *               Available where the convolution itself reads fp16 rows (SCN_PREC_F16); bn_out 16-byte aligned,
+ *               bn_out_stride a multiple of 8.
+ *   skip_raw    1: the fp32 result is not stored (`out` may be NULL); only meaningful with bn_out. */
+typedef struct scn_epilogue {
+  const float *addend;
+  int64_t addend_stride;
+  const float *bn_scale;
+  const float *bn_shift;
+  double bn_leakiness;
+  void *bn_out;
+  int64_t bn_out_stride;
+  int skip_raw;
+} scn_epilogue;
+/* scn_ssc_forward / scn_conv_forward / scn_deconv_forward with an epilogue (epi == NULL: exactly those). */
+SCN_API int scn_ssc_forward_ex(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
+                               int64_t out_stride, const float *weight, const float *bias, int64_t n_in, int64_t n_out,
+                               int precision, const scn_epilogue *epi, void *stream, double *flops);
+SCN_API int scn_conv_forward_ex(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
+                                int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
+                                int64_t n_in, int64_t n_out, int precision, const scn_epilogue *epi, void *stream,
+                                double *flops);
+SCN_API int scn_deconv_forward_ex(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
+                                  int64_t in_stride, float *out, int64_t out_stride, const float *weight,
+                                  const float *bias, int64_t n_in, int64_t n_out, int precision, const scn_epilogue *epi,
+                                  void *stream, double *flops);
 /* Makes sure the coarse grid and rulebook for in_size -> out_size exist and returns the coarse site
  * count (callers size the output with it).  Part of Metadata::getRuleBook (Metadata/Metadata.cpp:669-697). */
 SCN_API int scn_conv_prepare(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], void *stream,

@@ -79,6 +79,10 @@ struct scn_metadata {
   int ahead_ssc = -1, ahead_levels = -1;
   bool used_ssc = false;
   int used_levels = 0;
+  // the box the next input-layer build lays its ranking bitmap out for without measuring first (the last build's
+  // bounding box with a margin), and the point count it was measured on; both survive clear()
+  scn::Box hint_box = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+  int64_t hint_points = 0;
 
   scn::Grid *find(const int64_t *size) {
     auto it = grids.find(scn::to_size(size));
@@ -176,6 +180,35 @@ static int need_incre(scn_metadata *m, scn_metadata *pre, const int64_t *size, G
   return SCN_OK;
 }
 
+// the C ABI's epilogue description -> the kernels' (init rows, second output); checks what can be checked here
+static int take_epilogue(const scn_epilogue *epi, const float *bias, int64_t n_out, const float **init, int64_t *init_stride,
+                         const float **bias_out, EpiBn *e, bool *has) {
+  *init = nullptr;
+  *init_stride = 0;
+  *bias_out = bias;
+  *has = false;
+  if (!epi) return SCN_OK;
+  if (epi->addend) {
+    *init = epi->addend;
+    *init_stride = epi->addend_stride;
+    *bias_out = nullptr;
+  }
+  if (epi->bn_out) {
+    if (!epi->bn_scale || !epi->bn_shift) return fail(SCN_E_INVALID, "fused BatchNorm output without scale / shift");
+    if (epi->bn_out_stride < n_out) return fail(SCN_E_INVALID, "fused BatchNorm output stride smaller than the plane count");
+    e->scale = epi->bn_scale;
+    e->shift = epi->bn_shift;
+    e->leak = (float)epi->bn_leakiness;
+    e->dst = epi->bn_out;
+    e->stride = epi->bn_out_stride;
+    e->skip_raw = epi->skip_raw ? 1 : 0;
+    *has = true;
+  } else if (epi->skip_raw) {
+    return fail(SCN_E_INVALID, "skip_raw without a fused BatchNorm output leaves nothing to compute");
+  }
+  return SCN_OK;
+}
+
 static int check_feat(const void *in, const void *out, const void *w, int64_t n_in, int64_t n_out) {
   if (!in || !out || !w) return fail(SCN_E_INVALID, "null feature or weight pointer");
   if (n_in <= 0 || n_out <= 0) return fail(SCN_E_INVALID, "plane counts must be positive");
@@ -185,14 +218,15 @@ static int check_feat(const void *in, const void *out, const void *w, int64_t n_
 // One convolution through the gather-GEMM; SCN_PREC_F16: `in` holds fp16 rows and `weight` fp16 fragments
 static int run_conv(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out,
                     const float *weight, const float *bias, float *out, int64_t out_stride, int64_t n_in, int64_t n_planes_out,
-                    const float *init, int64_t init_stride, int precision, cudaStream_t s) {
+                    const float *init, int64_t init_stride, int precision, cudaStream_t s, const EpiBn *epi = nullptr) {
   if (precision == SCN_PREC_F16) {  // narrow layers: warp-level kernel; wide layers: tcgen05 kernel
     if (warp_mma_f16_shape(K, n_in, n_planes_out))
       return gather_mma_warp_f16(in, in_stride, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
-                                 init_stride, s);
+                                 init_stride, s, epi);
     return gather_gemm_tc_f16(in, in_stride, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
-                              init_stride, s);
+                              init_stride, s, epi);
   }
+  if (epi && epi->dst) return fail(SCN_E_UNSUPPORTED, "a fused BatchNorm output needs a convolution that reads fp16 rows (SCN_PREC_F16)");
   return gather_gemm(in, in_stride, in_rows, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
                      init_stride, precision, s);
 }
@@ -288,6 +322,14 @@ int scn_metadata_set_build_ahead(scn_metadata *m, int neighbour_maps, int coarse
   m->ahead_levels = coarse_levels;
   return SCN_OK;
 }
+int scn_metadata_inherit(scn_metadata *m, const scn_metadata *previous) {
+  if (!m || !previous) return fail(SCN_E_INVALID, "null metadata");
+  m->ahead_ssc = (previous->used_ssc || previous->ahead_ssc > 0) ? 1 : previous->ahead_ssc;
+  m->ahead_levels = previous->used_levels > previous->ahead_levels ? previous->used_levels : previous->ahead_levels;
+  m->hint_box = previous->hint_box;
+  m->hint_points = previous->hint_points;
+  return SCN_OK;
+}
 int scn_metadata_build_used(scn_metadata *m, int *neighbour_maps, int *coarse_levels) {
   if (!m) return fail(SCN_E_INVALID, "null metadata");
   if (neighbour_maps) *neighbour_maps = m->used_ssc ? 1 : 0;
@@ -312,13 +354,20 @@ int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t 
     SCN_CUDA(cudaMemcpyAsync(staged, coords, (size_t)n_in * ncols * 8, cudaMemcpyHostToDevice, s));
     dev_coords = staged;
   }
-  int r = grid_build(*g, dev_coords, ncols, nullptr, 0, n_in, true, nullptr, want_ssc(m), s);
+  // the last build's box serves when this frame is of a similar size (a much smaller or larger point set is
+  // another kind of frame -- the changed sites of an incremental update, say -- and would only miss it)
+  const bool use_hint = m->hint_points > 0 && n_in * 2 >= m->hint_points && n_in <= m->hint_points * 2;
+  int r = grid_build(*g, dev_coords, ncols, nullptr, 0, n_in, true, use_hint ? &m->hint_box : nullptr, want_ssc(m), s);
   dev_free(staged, s);
   if (r != SCN_OK) {
     grid_free(*g, s);
     return r;
   }
   if (n_active) *n_active = g->n;
+  if (g->n > 0) {
+    m->hint_box = box_with_margin(g->tight, 16);
+    m->hint_points = n_in;
+  }
   m->grids[to_size(size)] = std::move(g);
   m->input_size = to_size(size);
   m->has_input = true;
@@ -340,8 +389,16 @@ int scn_input_layer_build(scn_metadata *m, const int64_t size[3], const int64_t 
       owned.emplace_back(new Grid());
       ptrs.push_back(owned.back().get());
     }
-    Grid *fine0 = m->find(m->input_size.data());
-    SCN_TRY(grid_build_coarse_chain(ptrs.data(), (int)ptrs.size(), *fine0, want_ssc(m), s));
+    const Grid *src = m->find(m->input_size.data());
+    size_t first = 0;
+    // scales too spread out for a ranking bitmap (or built from one that has none) one at a time, the rest chained
+    while (first < sizes.size() && (!src->bitmap || !coarse_box_fits_bitmap(src->box, nullptr))) {
+      SCN_TRY(grid_build_coarse(*ptrs[first], *src, want_ssc(m), s));
+      src = ptrs[first];
+      ++first;
+    }
+    if (first < sizes.size())
+      SCN_TRY(grid_build_coarse_chain(ptrs.data() + first, (int)(ptrs.size() - first), *src, want_ssc(m), s));
     for (size_t i = 0; i < sizes.size(); ++i) m->grids[sizes[i]] = std::move(owned[i]);
   }
   return SCN_OK;
@@ -387,6 +444,7 @@ int scn_input_layer_rules(scn_metadata *m, int32_t header_host[4], int32_t *rows
     header_host[3] = (int32_t)g->n;
   }
   if (!rows_host || g->n == 0) return SCN_OK;
+  SCN_TRY(grid_ensure_source_lists(*g, s));
   std::vector<int32_t> off((size_t)g->n + 1), item((size_t)g->n_src);
   if (g->csr_off) {
     SCN_CUDA(cudaMemcpyAsync(off.data(), g->csr_off, off.size() * 4, cudaMemcpyDeviceToHost, s));
@@ -447,35 +505,40 @@ int scn_pack_weights_f16(const float *weight, int64_t volume, int64_t n_in, int6
     return warp_mma_pack_f16(weight, volume, n_in, n_out, packed, (cudaStream_t)stream);
   return tc_pack_weights_f16(weight, volume, n_in, n_out, packed, (cudaStream_t)stream);
 }
-int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
-                    int64_t out_stride, const float *weight, const float *bias, int64_t n_in, int64_t n_out,
-                    int precision, void *stream, double *flops) {
+int scn_ssc_forward_ex(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
+                       int64_t out_stride, const float *weight, const float *bias, int64_t n_in, int64_t n_out, int precision,
+                       const scn_epilogue *epi, void *stream, double *flops) {
   Grid *g;
   SCN_TRY(need_grid(m, size, &g));
   if (flops) *flops = 0;
   if (g->n == 0) return SCN_OK;
-  SCN_TRY(check_feat(in, out, weight, n_in, n_out));
+  const float *init, *b;
+  int64_t init_stride;
+  EpiBn e;
+  bool fused;
+  SCN_TRY(take_epilogue(epi, bias, n_out, &init, &init_stride, &b, &e, &fused));
+  SCN_TRY(check_feat(in, (fused && e.skip_raw) ? (const void *)weight : (const void *)out, weight, n_in, n_out));
   cudaStream_t s = (cudaStream_t)stream;
   SCN_TRY(ensure_ssc(m, *g, s));
-  SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0, precision, s));
+  SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, b, out, out_stride, n_in, n_out, init, init_stride, precision, s,
+                   fused ? &e : nullptr));
   if (flops) *flops = (double)g->nbr_total * (double)n_in * (double)n_out;
   return SCN_OK;
+}
+int scn_ssc_forward(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
+                    int64_t out_stride, const float *weight, const float *bias, int64_t n_in, int64_t n_out,
+                    int precision, void *stream, double *flops) {
+  return scn_ssc_forward_ex(m, size, in, in_stride, out, out_stride, weight, bias, n_in, n_out, precision, nullptr, stream, flops);
 }
 int scn_ssc_forward_add(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
                         int64_t out_stride, const float *weight, const float *addend, int64_t addend_stride, int64_t n_in,
                         int64_t n_out, int precision, void *stream, double *flops) {
-  Grid *g;
-  SCN_TRY(need_grid(m, size, &g));
-  if (flops) *flops = 0;
-  if (g->n == 0) return SCN_OK;
-  SCN_TRY(check_feat(in, out, weight, n_in, n_out));
   if (!addend) return fail(SCN_E_INVALID, "null addend");
-  cudaStream_t s = (cudaStream_t)stream;
-  SCN_TRY(ensure_ssc(m, *g, s));
-  SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, nullptr, out, out_stride, n_in, n_out, addend,
-                   addend_stride, precision, s));
-  if (flops) *flops = (double)g->nbr_total * (double)n_in * (double)n_out;
-  return SCN_OK;
+  scn_epilogue epi;
+  memset(&epi, 0, sizeof epi);
+  epi.addend = addend;
+  epi.addend_stride = addend_stride;
+  return scn_ssc_forward_ex(m, size, in, in_stride, out, out_stride, weight, nullptr, n_in, n_out, precision, &epi, stream, flops);
 }
 int scn_conv_prepare(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], void *stream,
                      int64_t *n_active_out) {
@@ -484,33 +547,55 @@ int scn_conv_prepare(scn_metadata *m, const int64_t in_size[3], const int64_t ou
   if (n_active_out) *n_active_out = coarse->n;
   return SCN_OK;
 }
-int scn_conv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
-                     int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
-                     int64_t n_in, int64_t n_out, int precision, void *stream, double *flops) {
+int scn_conv_forward_ex(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
+                        int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias, int64_t n_in,
+                        int64_t n_out, int precision, const scn_epilogue *epi, void *stream, double *flops) {
   Grid *fine, *coarse;
   cudaStream_t s = (cudaStream_t)stream;
   SCN_TRY(need_coarse(m, in_size, out_size, &fine, &coarse, s));
   if (flops) *flops = 0;
   if (coarse->n == 0) return SCN_OK;
-  SCN_TRY(check_feat(in, out, weight, n_in, n_out));
-  SCN_TRY(run_conv(in, in_stride, fine->n, coarse->child, 8, coarse->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
-                   precision, s));
+  const float *init, *b;
+  int64_t init_stride;
+  EpiBn e;
+  bool fused;
+  SCN_TRY(take_epilogue(epi, bias, n_out, &init, &init_stride, &b, &e, &fused));
+  SCN_TRY(check_feat(in, (fused && e.skip_raw) ? (const void *)weight : (const void *)out, weight, n_in, n_out));
+  SCN_TRY(run_conv(in, in_stride, fine->n, coarse->child, 8, coarse->n, weight, b, out, out_stride, n_in, n_out, init, init_stride,
+                   precision, s, fused ? &e : nullptr));
+  if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
+  return SCN_OK;
+}
+int scn_conv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
+                     int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
+                     int64_t n_in, int64_t n_out, int precision, void *stream, double *flops) {
+  return scn_conv_forward_ex(m, in_size, out_size, in, in_stride, out, out_stride, weight, bias, n_in, n_out, precision, nullptr,
+                             stream, flops);
+}
+int scn_deconv_forward_ex(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
+                          int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
+                          int64_t n_in, int64_t n_out, int precision, const scn_epilogue *epi, void *stream, double *flops) {
+  Grid *fine, *coarse;
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(need_coarse(m, out_size, in_size, &fine, &coarse, s));
+  if (flops) *flops = 0;
+  if (fine->n == 0) return SCN_OK;
+  const float *init, *b;
+  int64_t init_stride;
+  EpiBn e;
+  bool fused;
+  SCN_TRY(take_epilogue(epi, bias, n_out, &init, &init_stride, &b, &e, &fused));
+  SCN_TRY(check_feat(in, (fused && e.skip_raw) ? (const void *)weight : (const void *)out, weight, n_in, n_out));
+  SCN_TRY(run_conv(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, b, out, out_stride, n_in, n_out, init, init_stride,
+                   precision, s, fused ? &e : nullptr));
   if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
   return SCN_OK;
 }
 int scn_deconv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
                        int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
                        int64_t n_in, int64_t n_out, int precision, void *stream, double *flops) {
-  Grid *fine, *coarse;
-  cudaStream_t s = (cudaStream_t)stream;
-  SCN_TRY(need_coarse(m, out_size, in_size, &fine, &coarse, s));
-  if (flops) *flops = 0;
-  if (fine->n == 0) return SCN_OK;
-  SCN_TRY(check_feat(in, out, weight, n_in, n_out));
-  SCN_TRY(run_conv(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
-                   precision, s));
-  if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
-  return SCN_OK;
+  return scn_deconv_forward_ex(m, in_size, out_size, in, in_stride, out, out_stride, weight, bias, n_in, n_out, precision, nullptr,
+                               stream, flops);
 }
 int scn_bn_forward_f16(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows, int64_t planes,
                        const float *running_mean, const float *running_var, const float *gamma, const float *beta,

@@ -418,6 +418,28 @@ __global__ void k_input_fwd(const float *__restrict__ in, float *__restrict__ ou
   out[i] = acc;
 }
 
+// Grids whose sites have exactly one source each (the usual case: deduplicated voxels): one thread per (source, plane)
+// writes the site's row; nothing is summed, so the order of the sources does not matter and no source list is needed.
+__global__ void k_input_fwd_unique(const float *__restrict__ in, float *__restrict__ out, long long n_src, int planes,
+                                   const int32_t *__restrict__ src_row, int average, const int32_t *__restrict__ pre_exist,
+                                   const int32_t *__restrict__ pre_off, const float *__restrict__ pre_out) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_src * planes) return;
+  const long long p = i / planes;
+  const int c = (int)(i % planes);
+  const int r = src_row[p];
+  int pe = -1, pre_cnt = 0;
+  if (pre_exist) {
+    pe = pre_exist[r];
+    if (pe >= 0) pre_cnt = pre_off ? pre_off[pe + 1] - pre_off[pe] : 1;
+  }
+  const float mult = average ? 1.0f / (float)(1 + pre_cnt) : 1.0f;
+  float acc = 0.f;
+  acc += mult * in[i];
+  if (pe >= 0) acc = acc + pre_out[(long long)pe * planes + c] * ((float)pre_cnt * mult - 1.0f);
+  out[(long long)r * planes + c] = acc;
+}
+
 __global__ void k_output_fwd(const float *__restrict__ in, float *__restrict__ out, long long n_pts, int planes,
                              const int32_t *__restrict__ src_row, const int32_t *__restrict__ pre_exist,
                              const float *__restrict__ pre_in) {
@@ -437,6 +459,13 @@ __global__ void k_output_fwd(const float *__restrict__ in, float *__restrict__ o
 int input_forward(const Grid &g, const float *in, float *out, int64_t planes, int average, const int32_t *pre_exist,
                   const Grid *pre, const float *pre_out, cudaStream_t s) {
   if (g.n == 0 || planes == 0) return SCN_OK;
+  if (!g.csr_off && g.n == g.n_src) {  // one source per site
+    if (!g.src_row) return fail(SCN_E_STATE, "grid has no input rules");
+    k_input_fwd_unique<<<blocks_for(g.n_src * planes, 256), 256, 0, s>>>(in, out, g.n_src, (int)planes, g.src_row, average, pre_exist,
+                                                                       pre ? pre->csr_off : nullptr, pre_out);
+    SCN_LAUNCHED();
+    return SCN_OK;
+  }
   if (!g.csr_item) return fail(SCN_E_STATE, "grid has no input rules");
   k_input_fwd<<<blocks_for(g.n * planes, 256), 256, 0, s>>>(in, out, g.n, (int)planes, g.csr_off, g.csr_item, average,
                                                           pre_exist, pre ? pre->csr_off : nullptr, pre_out);

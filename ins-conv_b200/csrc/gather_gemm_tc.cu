@@ -433,7 +433,7 @@ __global__ void __launch_bounds__(kPThreads, 1)
 k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, const __grid_constant__ CUtensorMap tmB,
                            const int32_t *__restrict__ map, int K, long long n_out, const float *__restrict__ bias,
                            float *out, long long out_stride, int Cin, int Cout, const float *init, long long init_stride,
-                           uint32_t acc_cols, int stages, long long tiles, int Z, float *__restrict__ partial) {
+                           uint32_t acc_cols, int stages, long long tiles, int Z, float *__restrict__ partial, const EpiBn epi) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t b_bytes = (uint32_t)Cout * 128u;
   const uint32_t stage_bytes = kABytes + b_bytes;
@@ -705,7 +705,22 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
               r.x += __ldg(bias + c0 + j); r.y += __ldg(bias + c0 + j + 1);
               r.z += __ldg(bias + c0 + j + 2); r.w += __ldg(bias + c0 + j + 3);
             }
-            *reinterpret_cast<float4 *>(o + j) = r;
+            if (!epi.skip_raw) *reinterpret_cast<float4 *>(o + j) = r;
+            v[j] = r.x; v[j + 1] = r.y; v[j + 2] = r.z; v[j + 3] = r.w;
+          }
+          if (epi.dst) {  // the BatchNorm + ReLU behind this convolution, as fp16 rows for the next one
+            __half *hd = static_cast<__half *>(epi.dst) + row * epi.stride + c0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              __align__(16) __half h8[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                float y = fmaf(v[j + u], __ldg(epi.scale + c0 + j + u), __ldg(epi.shift + c0 + j + u));
+                y = y > 0.f ? y : y * epi.leak;
+                h8[u] = __float2half_rn(fminf(fmaxf(y, -65504.f), 65504.f));
+              }
+              *reinterpret_cast<uint4 *>(hd + j) = *reinterpret_cast<const uint4 *>(h8);
+            }
           }
         }
       }
@@ -819,7 +834,7 @@ __global__ void k_transpose_weights(const float *__restrict__ W, float *__restri
 // out[r][c] = (init ? init : bias) + sum_z partial[z][r][c], z ascending
 __global__ void k_splitk_reduce(const float *__restrict__ partial, int Z, long long rows_padded, long long n_out, int Cout,
                                 const float *__restrict__ bias, float *out, long long out_stride, const float *init,
-                                long long init_stride) {
+                                long long init_stride, const EpiBn epi) {
   const int cv = Cout >> 2;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_out * cv) return;
@@ -843,7 +858,18 @@ __global__ void k_splitk_reduce(const float *__restrict__ partial, int Z, long l
       acc.x += p[u].x; acc.y += p[u].y; acc.z += p[u].z; acc.w += p[u].w;
     }
   }
-  *reinterpret_cast<float4 *>(o) = acc;
+  if (!epi.skip_raw) *reinterpret_cast<float4 *>(o) = acc;
+  if (epi.dst) {
+    const float4 sc = __ldg(reinterpret_cast<const float4 *>(epi.scale + c)), sh = __ldg(reinterpret_cast<const float4 *>(epi.shift + c));
+    float y[4] = {fmaf(acc.x, sc.x, sh.x), fmaf(acc.y, sc.y, sh.y), fmaf(acc.z, sc.z, sh.z), fmaf(acc.w, sc.w, sh.w)};
+    __align__(8) __half h4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float t = y[u] > 0.f ? y[u] : y[u] * epi.leak;
+      h4[u] = __float2half_rn(fminf(fmaxf(t, -65504.f), 65504.f));
+    }
+    *reinterpret_cast<uint2 *>(static_cast<__half *>(epi.dst) + r * epi.stride + c) = *reinterpret_cast<const uint2 *>(h4);
+  }
 }
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -962,7 +988,7 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
     const long long n_items = tiles * Z;
     k_gather_gemm_tc_persist<false><<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads, smem_p, s>>>(
         in, in_stride, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, (int)Cout, init, init_stride, cols, st, tiles, Z,
-        partial);
+        partial, EpiBn());
   } else {
 #define SCN_TC_LAUNCH(S, A)                                                                                          \
   do {                                                                                                               \
@@ -980,7 +1006,7 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
   if (Z > 1) {
     const long long work = n_out * (Cout / 4);
     k_splitk_reduce<<<(unsigned)((work + 255) / 256), 256, 0, s>>>(partial, Z, tiles * kTileM, n_out, (int)Cout, bias, out,
-                                                                  out_stride, init, init_stride);
+                                                                  out_stride, init, init_stride, EpiBn());
     SCN_LAUNCHED();
   }
   if (partial_pooled) dev_free(partial, s);
@@ -1037,7 +1063,10 @@ int tc_pack_weights_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, vo
 
 int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                        const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                       int64_t init_stride, cudaStream_t s) {
+                       int64_t init_stride, cudaStream_t s, const EpiBn *epi) {
+  const EpiBn e = epi ? *epi : EpiBn();
+  if (e.dst && (e.stride % 8 != 0 || !aligned16(e.dst) || !aligned16(e.scale) || !aligned16(e.shift)))
+    return fail(SCN_E_INVALID, "the fp16 rows of a fused BatchNorm must be 16-byte aligned with a stride that is a multiple of 8");
   if (!tc_f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "the fp16 tcgen05 gather-GEMM takes planes that are multiples of 32, n_out <= 224");
   if (!map && K != 1) return fail(SCN_E_INVALID, "no map given for a filter volume above 1");
   {
@@ -1048,7 +1077,7 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
     const long long slab_rows = 16384;
     if (n_out >= 512 && n_out <= slab_rows && warp_slab_f16_shape(K, Cin, Cout))
       return gather_mma_slab_f16(in, in_stride, map, K, n_out, static_cast<const __half *>(Wp) + K * Cout * padded_planes(Cin), bias,
-                                 out, out_stride, Cin, Cout, init, init_stride, s);
+                                 out, out_stride, Cin, Cout, init, init_stride, s, epi);
   }
   if (in_stride % 8 != 0 || out_stride % 4 != 0 || !aligned16(in) || !aligned16(Wp) || !aligned16(out) ||
       (bias && !aligned16(bias)) || (init && (!aligned16(init) || init_stride % 4 != 0)))
@@ -1104,12 +1133,12 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
   k_gather_gemm_tc_persist<true><<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads,
                                    (size_t)st * stage_bytes + fixed_p, s>>>(in, in_stride, tmB, map, K, n_out, bias, out, out_stride,
                                                                             (int)Cin, (int)Cout, init, init_stride, cols, st,
-                                                                            tiles, Z, partial);
+                                                                            tiles, Z, partial, Z > 1 ? EpiBn() : e);
   SCN_LAUNCHED();
   if (Z > 1) {
     const long long work = n_out * (Cout / 4);
     k_splitk_reduce<<<(unsigned)((work + 255) / 256), 256, 0, s>>>(partial, Z, tiles * kTileM, n_out, (int)Cout, bias, out,
-                                                                  out_stride, init, init_stride);
+                                                                  out_stride, init, init_stride, e);
     SCN_LAUNCHED();
   }
   if (partial_pooled) dev_free(partial, s);

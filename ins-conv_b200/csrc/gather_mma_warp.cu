@@ -137,10 +137,23 @@ __device__ __forceinline__ unsigned int publish_map(const MapRegs<ROWS> &m, int 
 }
 
 // accumulator fragment: c0,c1 -> plane 16m + g, rows 8n + 2t, +1; c2,c3 -> plane 16m + g + 8
+// e (optional second output): leaky(v * scale + shift) of the finished value as fp16; plane0 = first plane of this
+// call's slab inside the full row (scale, shift and the fp16 rows are indexed by full-row planes).
 template <int COUT, int NTR>
 __device__ __forceinline__ void store_acc(const float (&acc)[COUT / 16][NTR][4], long long row0, long long n_out,
                                           const float *__restrict__ bias, float *out, long long out_stride,
-                                          const float *init, long long init_stride, int g, int t) {
+                                          const float *init, long long init_stride, int g, int t, const EpiBn &e = EpiBn(),
+                                          int plane0 = 0) {
+  float sc[COUT / 16][2], sh[COUT / 16][2];
+  if (e.dst) {
+#pragma unroll
+    for (int m = 0; m < COUT / 16; ++m)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        sc[m][h] = __ldg(e.scale + plane0 + 16 * m + 8 * h + g);
+        sh[m][h] = __ldg(e.shift + plane0 + 16 * m + 8 * h + g);
+      }
+  }
 #pragma unroll
   for (int n = 0; n < NTR; ++n)
 #pragma unroll
@@ -149,6 +162,7 @@ __device__ __forceinline__ void store_acc(const float (&acc)[COUT / 16][NTR][4],
       if (row < n_out) {
         float *o = out + row * out_stride + g;
         const float *ini = init ? init + row * init_stride + g : nullptr;
+        __half *hd = e.dst ? static_cast<__half *>(e.dst) + row * e.stride + plane0 + g : nullptr;
 #pragma unroll
         for (int m = 0; m < COUT / 16; ++m)
 #pragma unroll
@@ -157,7 +171,12 @@ __device__ __forceinline__ void store_acc(const float (&acc)[COUT / 16][NTR][4],
             const int c = 16 * m + 8 * h;
             if (ini) v += ini[c];
             else if (bias) v += __ldg(bias + c + g);
-            o[c] = v;
+            if (!e.skip_raw) o[c] = v;
+            if (hd) {
+              float y = fmaf(v, sc[m][h], sh[m][h]);
+              y = y > 0.f ? y : y * e.leak;
+              hd[c] = __float2half_rn(fminf(fmaxf(y, -65504.f), 65504.f));
+            }
           }
       }
     }
@@ -288,7 +307,7 @@ template <int CIN, int COUT, int NTR, int MINB>
 __global__ void __launch_bounds__(kWarps * 32, MINB)
 k_gather_mma_f16(const __half *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
                  const uint4 *__restrict__ Wp, const float *__restrict__ bias, float *out, long long out_stride,
-                 const float *init, long long init_stride) {
+                 const float *init, long long init_stride, const EpiBn epi) {
   constexpr int ROWS = 8 * NTR, MTC = COUT / 16;
   __shared__ int s_map[kWarps][kMaxK * ROWS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -333,7 +352,7 @@ k_gather_mma_f16(const __half *__restrict__ in, long long in_stride, const int32
       if (k0 < 0) break;
     }
   }
-  store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, init, init_stride, g, t);
+  store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, init, init_stride, g, t, epi);
 }
 
 // Wide layers on small grids (the deep levels of a UNet: a few hundred to a few thousand rows, 96-224 planes).  There
@@ -366,7 +385,7 @@ template <int C32, int NTR>
 __global__ void __launch_bounds__(kWarps * 32, 3)
 k_gather_mma_f16_slab(const __half *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
                       const uint4 *__restrict__ Wp, int Cout, const float *__restrict__ bias, float *out, long long out_stride,
-                      const float *init, long long init_stride) {
+                      const float *init, long long init_stride, const EpiBn epi) {
   constexpr int ROWS = 8 * NTR, CIN = C32 * 32;
   __shared__ int s_map[kWarps][kMaxK * ROWS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -413,7 +432,7 @@ k_gather_mma_f16_slab(const __half *__restrict__ in, long long in_stride, const 
     }
   }
   store_acc<32, NTR>(acc, row0, n_out, bias ? bias + 32 * slab : nullptr, out + 32 * slab, out_stride,
-                     init ? init + 32 * slab : nullptr, init_stride, g, t);
+                     init ? init + 32 * slab : nullptr, init_stride, g, t, epi, 32 * slab);
 }
 
 // W [K][n_in][n_out] fp32 -> fp16 fragments [K][n_in/32][n_out/16][2][lane][8]: half e of (k, c, m, j, lane = 4g + t)
@@ -612,7 +631,8 @@ bool warp_slab_f16_shape(int64_t K, int64_t Cin, int64_t Cout) {
 
 int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                        int64_t init_stride, cudaStream_t s) {
+                        int64_t init_stride, cudaStream_t s, const EpiBn *epi) {
+  const EpiBn e = epi ? *epi : EpiBn();
   if (!warp_slab_f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "shape not covered by the slab kernel");
   if (in_stride % 8 != 0 || !aligned16(in) || !aligned16(Wp))
     return fail(SCN_E_INVALID, "fp16 rows must be 16-byte aligned with a stride that is a multiple of 8 elements");
@@ -622,7 +642,7 @@ int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, i
   const dim3 grid((unsigned)((tiles + kWarps - 1) / kWarps), (unsigned)(Cout / 32));
 #define SCN_SLAB_LAUNCH(C32)                                                                                          \
   k_gather_mma_f16_slab<C32, 2><<<grid, kWarps * 32, 0, s>>>(inh, in_stride, map, K, n_out, W4, (int)Cout, bias, out, \
-                                                             out_stride, init, init_stride)
+                                                             out_stride, init, init_stride, e)
   switch ((int)(Cin / 32)) {
     case 3: SCN_SLAB_LAUNCH(3); break;
     case 4: SCN_SLAB_LAUNCH(4); break;
@@ -637,7 +657,8 @@ int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, i
 
 int gather_mma_warp_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                        int64_t init_stride, cudaStream_t s) {
+                        int64_t init_stride, cudaStream_t s, const EpiBn *epi) {
+  const EpiBn e = epi ? *epi : EpiBn();
   if (!f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "the fp16 gather-GEMM takes 32 or 64 planes on either side");
   if (!map && K != 1) return fail(SCN_E_INVALID, "no map given for a filter volume above 1");
   if (in_stride % 8 != 0 || !aligned16(in) || !aligned16(Wp))
@@ -648,7 +669,7 @@ int gather_mma_warp_f16(const void *in, int64_t in_stride, const int32_t *map, i
   do {                                                                                                            \
     const long long tiles = (n_out + 8 * NTR - 1) / (8 * NTR);                                                    \
     k_gather_mma_f16<CI, CO, NTR, MINB><<<(unsigned)((tiles + kWarps - 1) / kWarps), kWarps * 32, 0, s>>>(        \
-        inh, in_stride, map, K, n_out, W4, bias, out, out_stride, init, init_stride);                             \
+        inh, in_stride, map, K, n_out, W4, bias, out, out_stride, init, init_stride, e);                          \
   } while (0)
   if (Cin == 32 && Cout == 32) SCN_F16_LAUNCH(32, 32, 4, 5);
   else if (Cin == 32 && Cout == 64) SCN_F16_LAUNCH(32, 64, 4, 4);

@@ -51,31 +51,76 @@ __device__ __forceinline__ bool coord_ok(long long x, long long y, long long z, 
   return x >= 0 && y >= 0 && z >= 0 && b >= 0 && x <= SCN_MAX_COORD && y <= SCN_MAX_COORD &&
          z <= SCN_MAX_COORD && b <= SCN_MAX_BATCH;
 }
-__device__ __forceinline__ int table_find(const Slot *__restrict__ t, uint32_t mask, unsigned long long key) {
-  uint32_t h = hash_key(key) & mask;
-  for (uint32_t probe = 0; probe <= mask; ++probe) {  // bounded: at most one sweep of the table
-    const ulonglong2 s = __ldg(reinterpret_cast<const ulonglong2 *>(t + h));
-    if (s.x == key) return (int)(uint32_t)(s.y & 0xFFFFFFFFull);
-    if (s.x == kEmptyKey) return -1;
-    h = (h + 1) & mask;
+// Open-addressing table, linear probing, probed by TEAMS of four lanes: the four lanes read four consecutive 16-byte
+// slots -- one aligned 64-byte line -- per step and vote, so a probe sequence costs one memory round trip per four
+// slots instead of one per slot, and every load of a warp is a whole line.  The window that holds the key's home slot
+// is aligned down to a multiple of four; slots in front of the home slot are not on the key's probe path and are
+// ignored in that first window.  All four lanes of a team call with the same key.  Capacity is a power of two >= 16.
+constexpr int kTeam = 4;
+
+__device__ __forceinline__ int table_find_team(const Slot *__restrict__ t, uint32_t mask, unsigned long long key,
+                                               unsigned team_mask, int lane) {
+  const uint32_t h = hash_key(key) & mask;
+  uint32_t base = h & ~(uint32_t)(kTeam - 1);
+  const uint32_t windows = (mask + 1) / kTeam;
+  const int j = lane & (kTeam - 1);
+  for (uint32_t w = 0; w <= windows; ++w) {  // bounded: at most one sweep of the table
+    const uint32_t idx = base + (uint32_t)j;
+    const ulonglong2 s = __ldg(reinterpret_cast<const ulonglong2 *>(t + idx));
+    const bool on_path = w > 0 || idx >= h;
+    const unsigned hit = __ballot_sync(team_mask, on_path && s.x == key);
+    if (hit) return __shfl_sync(team_mask, (int)(uint32_t)(s.y & 0xFFFFFFFFull), __ffs(hit) - 1);
+    if (__ballot_sync(team_mask, on_path && s.x == kEmptyKey)) return -1;
+    base = (base + kTeam) & mask;
   }
   return -1;
 }
-__device__ __forceinline__ bool table_insert(Slot *t, uint32_t mask, unsigned long long key, int row) {
-  uint32_t h = hash_key(key) & mask;
-  for (uint32_t probe = 0; probe <= mask; ++probe) {
-    unsigned long long old = atomicCAS(&t[h].key, kEmptyKey, key);
-    if (old == kEmptyKey || old == key) {
-      t[h].row = row;
-      return true;
+
+__device__ __forceinline__ bool table_insert_team(Slot *t, uint32_t mask, unsigned long long key, int row, unsigned team_mask,
+                                                  int lane) {
+  const uint32_t h = hash_key(key) & mask;
+  uint32_t base = h & ~(uint32_t)(kTeam - 1);
+  const uint32_t windows = (mask + 1) / kTeam;
+  const int j = lane & (kTeam - 1);
+  for (uint32_t w = 0; w <= windows; ++w) {
+    const uint32_t idx = base + (uint32_t)j;
+    const bool on_path = w > 0 || idx >= h;
+    for (int attempt = 0; attempt <= kTeam; ++attempt) {  // a lost race fills a slot of this window: look again
+      const unsigned long long k = *reinterpret_cast<volatile unsigned long long *>(&t[idx].key);
+      if (__ballot_sync(team_mask, on_path && k == key)) return true;
+      const unsigned empty = __ballot_sync(team_mask, on_path && k == kEmptyKey);
+      if (!empty) break;
+      bool won = false;
+      if (lane == __ffs(empty) - 1) {  // the first empty slot on the path
+        const unsigned long long old = atomicCAS(&t[idx].key, kEmptyKey, key);
+        won = old == kEmptyKey || old == key;
+        if (won) t[idx].row = row;
+      }
+      if (__ballot_sync(team_mask, won)) return true;
     }
-    h = (h + 1) & mask;
+    base = (base + kTeam) & mask;
   }
   return false;
 }
 __device__ __forceinline__ unsigned long long box_pos(const Box &bx, int x, int y, int z, int b) {
   return (((unsigned long long)(unsigned)(b - bx.o[3]) * bx.e[2] + (unsigned)(z - bx.o[2])) * bx.e[1] +
           (unsigned)(y - bx.o[1])) * bx.e[0] + (unsigned)(x - bx.o[0]);
+}
+
+// Sets bit p of the bitmap for every lane with active set.  Lanes of a warp that hit the same 64-bit word (points of
+// a scan arrive surface by surface, so most neighbours in the input are neighbours in space) combine their bits and one
+// of them issues the atomic; a word that already shows all of them is left alone.  Every lane of the warp must call.
+__device__ __forceinline__ void mark_bits_warp(unsigned long long *bitmap, unsigned long long p, bool active) {
+  const int lane = threadIdx.x & 31;
+  const unsigned long long word = active ? (p >> 6) : (~0ull - (unsigned long long)lane);  // idle lanes match nobody
+  const unsigned peers = __match_any_sync(0xffffffffu, word);
+  const unsigned long long mine = active ? (1ull << (p & 63)) : 0ull;
+  unsigned long long all = 0;
+  for (unsigned m = peers; m; m &= m - 1) all |= __shfl_sync(peers, mine, __ffs(m) - 1);
+  if (active && lane == __ffs(peers) - 1) {
+    unsigned long long *w = bitmap + (p >> 6);
+    if ((*(volatile unsigned long long *)w & all) != all) atomicOr(w, all);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -156,6 +201,46 @@ __global__ void k_pack_keys_i64(const long long *__restrict__ coords, int ncols,
   reduce_box((int)x, (int)y, (int)z, (int)b, valid, info);
 }
 
+
+// int64 AoS rows -> keys, bounding box AND the occupancy bits in one pass over the coordinates, for a build that
+// already knows a box (from the previous build of a similar scene) that should hold every point.  A point outside
+// that box sets bit 1 of info->err and marks nothing: the host then repeats the build with the measured box.
+__global__ void k_pack_mark_i64(const long long *__restrict__ coords, int ncols, int vec, long long n, Box bx,
+                                unsigned long long *__restrict__ keys, unsigned long long *bitmap, BuildInfo *info) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  bool valid = i < n, inside = false;
+  unsigned long long p = 0;
+  long long x = 0, y = 0, z = 0, b = 0;
+  if (valid) {
+    if (vec) {
+      const longlong2 *q = reinterpret_cast<const longlong2 *>(coords + 4 * i);
+      longlong2 a = __ldg(q), c = __ldg(q + 1);
+      x = a.x; y = a.y; z = c.x; b = c.y;
+    } else {
+      const long long *q = coords + (long long)ncols * i;
+      x = q[0]; y = q[1]; z = q[2];
+      b = ncols > 3 ? q[3] : 0;
+    }
+    if (!coord_ok(x, y, z, b)) {
+      atomicOr(&info->err, 1u);
+      valid = false;
+      keys[i] = kEmptyKey;
+    } else {
+      keys[i] = pack_key((int)x, (int)y, (int)z, (int)b);
+      const unsigned ux = (unsigned)((int)x - bx.o[0]), uy = (unsigned)((int)y - bx.o[1]), uz = (unsigned)((int)z - bx.o[2]),
+                     ub = (unsigned)((int)b - bx.o[3]);
+      if (ux < bx.e[0] && uy < bx.e[1] && uz < bx.e[2] && ub < bx.e[3]) {
+        p = (((unsigned long long)ub * bx.e[2] + uz) * bx.e[1] + uy) * bx.e[0] + ux;
+        inside = true;
+      } else {
+        atomicOr(&info->err, 2u);
+      }
+    }
+  }
+  mark_bits_warp(bitmap, p, inside);
+  reduce_box((int)x, (int)y, (int)z, (int)b, valid, info);
+}
+
 // int32 SoA coordinates of a finer grid, shifted right (downsampling by 2^shift).
 // src (optional): the build record of the grid c belongs to, when its site count is not known on the host yet
 __global__ void k_pack_keys_soa(const int32_t *__restrict__ c, long long n, int shift,
@@ -181,16 +266,14 @@ __global__ void k_pack_keys_soa(const int32_t *__restrict__ c, long long n, int 
 __global__ void k_mark(const unsigned long long *__restrict__ keys, long long n, Box bx,
                        unsigned long long *bitmap, const BuildInfo *src) {
   if (src) n = src->n_unique;
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  int x, y, z, b;
-  unpack_key(keys[i], x, y, z, b);
-  unsigned long long p = box_pos(bx, x, y, z, b);
-  unsigned long long bit = 1ull << (p & 63);
-  unsigned long long *w = bitmap + (p >> 6);
-  // most cells hold one point, but duplicates and neighbours share words: skip the atomic when the
-  // bit is already visible.
-  if ((*(volatile unsigned long long *)w & bit) == 0) atomicOr(w, bit);
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // blocks are multiples of 32 threads
+  unsigned long long p = 0;
+  if (i < n) {
+    int x, y, z, b;
+    unpack_key(keys[i], x, y, z, b);
+    p = box_pos(bx, x, y, z, b);
+  }
+  mark_bits_warp(bitmap, p, i < n);
 }
 
 // The same from the SoA coordinates of the next finer grid, shifted right: a coarse level's box is the fine box
@@ -200,11 +283,9 @@ __global__ void k_mark_soa(const int32_t *__restrict__ c, long long n, int shift
                            const BuildInfo *src) {
   if (src) n = src->n_unique;
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  unsigned long long p = box_pos(bx, c[i] >> shift, c[n + i] >> shift, c[2 * n + i] >> shift, c[3 * n + i]);
-  unsigned long long bit = 1ull << (p & 63);
-  unsigned long long *w = bitmap + (p >> 6);
-  if ((*(volatile unsigned long long *)w & bit) == 0) atomicOr(w, bit);
+  unsigned long long p = 0;
+  if (i < n) p = box_pos(bx, c[i] >> shift, c[n + i] >> shift, c[2 * n + i] >> shift, c[3 * n + i]);
+  mark_bits_warp(bitmap, p, i < n);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -382,34 +463,158 @@ struct EmitPairs {
 // ---------------------------------------------------------------------------------------------
 // pass 4: source -> row
 // ---------------------------------------------------------------------------------------------
-template <bool UNIQUE>
-__global__ void k_rank_rows(const unsigned long long *__restrict__ keys, long long n_src, Box bx,
-                            const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
-                            long long n, int32_t *__restrict__ src_row, int32_t *coords, uint32_t *cnt,
-                            int32_t *__restrict__ csr_item) {
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+// Second sweep of the popcount scan fused with the decoding of the site coordinates: a thread that knows the exclusive
+// prefix of its words also knows the rows of their set bits, and the position of a bit in the key-ordered bitmap IS the
+// site's coordinate.  Site coordinates are therefore written from here, in row order (consecutive threads write
+// consecutive rows), instead of by four scattered 4-byte writes per source point.
+// block_sums: the per-block popcount totals of the first sweep (offsets_given = 0: every block adds up the totals in
+// front of it -- a few thousand values out of L2) or their exclusive prefix sums made by k_scan_top (offsets_given = 1,
+// for very large bitmaps; the site count is then already in info->n_unique).  coords: SoA [4][n] with n the site count.
+__global__ void k_rank_emit(const unsigned long long *__restrict__ bitmap, long long nwords,
+                            const uint32_t *__restrict__ block_sums, long long nb, int offsets_given, Box bx,
+                            uint32_t *__restrict__ prefix, int32_t *__restrict__ coords, BuildInfo *info) {
+  __shared__ uint32_t s_red[2][kScanThreads / 32];
+  __shared__ uint32_t s_before, s_total;
+  if (offsets_given) {
+    if (threadIdx.x == 0) {
+      s_before = block_sums[blockIdx.x];
+      s_total = info->n_unique;
+    }
+  } else {
+    uint32_t before = 0, total = 0;
+    for (long long i = threadIdx.x; i < nb; i += blockDim.x) {
+      const uint32_t v = block_sums[i];
+      total += v;
+      if (i < (long long)blockIdx.x) before += v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      before += __shfl_xor_sync(0xffffffffu, before, o);
+      total += __shfl_xor_sync(0xffffffffu, total, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+      s_red[0][threadIdx.x >> 5] = before;
+      s_red[1][threadIdx.x >> 5] = total;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      uint32_t b = 0, t = 0;
+      for (int w = 0; w < kScanThreads / 32; ++w) {
+        b += s_red[0][w];
+        t += s_red[1][w];
+      }
+      s_before = b;
+      s_total = t;
+      if (blockIdx.x == 0) info->n_unique = t;
+    }
+  }
+  __syncthreads();
+  const long long n = s_total;
+  const long long base = (long long)blockIdx.x * kScanChunk + (long long)threadIdx.x * kScanItems;
+  // the block's words and their block-relative prefixes, staged for the decode below
+  __shared__ uint32_t s_pref[kScanChunk + 1];
+  __shared__ unsigned long long s_bits[kScanChunk];
+  unsigned long long w[kScanItems];
+  uint32_t sum = 0;
+#pragma unroll
+  for (int j = 0; j < kScanItems; ++j) {
+    w[j] = (base + j < nwords) ? bitmap[base + j] : 0ull;
+    sum += (uint32_t)__popcll(w[j]);
+  }
+  uint32_t total;
+  uint32_t ex = block_exclusive_scan(sum, &total);
+#pragma unroll
+  for (int j = 0; j < kScanItems; ++j) {
+    s_pref[threadIdx.x * kScanItems + j] = ex;
+    s_bits[threadIdx.x * kScanItems + j] = w[j];
+    if (base + j < nwords) prefix[base + j] = ex + s_before;
+    ex += (uint32_t)__popcll(w[j]);
+  }
+  if (threadIdx.x == 0) s_pref[kScanChunk] = total;
+  __syncthreads();
+  // decode: thread t takes the block's sites t, t + 256, ... -- however unevenly the bits are spread over the words,
+  // every thread does the same amount of work and consecutive threads write consecutive rows.  A site's word is found
+  // by bisection over the staged prefixes, its bit with the find-n-th-set instruction; the bit's position in the
+  // key-ordered bitmap (below 2^32 by the limit on the box) is its coordinate.
+  const uint32_t first_pos = (uint32_t)((unsigned long long)blockIdx.x * kScanChunk * 64ull);
+  for (uint32_t sidx = threadIdx.x; sidx < total; sidx += kScanThreads) {
+    int lo = 0, hi = kScanChunk;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (s_pref[mid] <= sidx) lo = mid;
+      else hi = mid;
+    }
+    const uint32_t k = sidx - s_pref[lo];
+    const unsigned long long bits = s_bits[lo];
+    const uint32_t lo32 = (uint32_t)bits, hi32 = (uint32_t)(bits >> 32);
+    const uint32_t c = (uint32_t)__popc(lo32);
+    const uint32_t bit = k < c ? __fns(lo32, 0, (int)k + 1) : 32u + __fns(hi32, 0, (int)(k - c) + 1);
+    uint32_t pos = first_pos + (uint32_t)lo * 64u + bit;
+    const uint32_t cx = pos % bx.e[0];
+    pos /= bx.e[0];
+    const uint32_t cy = pos % bx.e[1];
+    pos /= bx.e[1];
+    const uint32_t cz = pos % bx.e[2];
+    const uint32_t cb = pos / bx.e[2];
+    const long long row = (long long)s_before + sidx;
+    coords[row] = (int)cx + bx.o[0];
+    coords[n + row] = (int)cy + bx.o[1];
+    coords[2 * n + row] = (int)cz + bx.o[2];
+    coords[3 * n + row] = (int)cb + bx.o[3];
+  }
+}
+
+// source -> row from the finished ranking structure (keys made by the pack kernels; ~0 marks a rejected point)
+__global__ void k_rank_src(const unsigned long long *__restrict__ keys, long long n_src, Box bx,
+                           const unsigned long long *__restrict__ bitmap, const uint32_t *__restrict__ prefix,
+                           int32_t *__restrict__ src_row) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_src) return;
-  int x, y, z, b;
-  unpack_key(keys[i], x, y, z, b);
-  const unsigned long long p = box_pos(bx, x, y, z, b);
-  const unsigned long long w = __ldg(bitmap + (p >> 6));
-  const uint32_t row = __ldg(prefix + (p >> 6)) + (uint32_t)__popcll(w & ((1ull << (p & 63)) - 1ull));
-  src_row[i] = (int32_t)row;
-  coords[row] = x;  // points of one site write the same four values
-  coords[n + row] = y;
-  coords[2 * n + row] = z;
-  coords[3 * n + row] = b;
-  // UNIQUE: the host saw n == n_src, every point is the only one of its site: no counting is needed and the
-  // site's source list (when asked for) is this point
-  if (!UNIQUE) atomicAdd(&cnt[row], 1u);
-  else if (csr_item) csr_item[row] = (int32_t)i;
+  const unsigned long long key = keys[i];
+  int row = -1;
+  if (key != kEmptyKey) {
+    int x, y, z, b;
+    unpack_key(key, x, y, z, b);
+    // a point outside the box the bitmap was laid out for (a hinted build that has to be repeated) has no row
+    const unsigned ux = (unsigned)(x - bx.o[0]), uy = (unsigned)(y - bx.o[1]), uz = (unsigned)(z - bx.o[2]), ub = (unsigned)(b - bx.o[3]);
+    if (ux < bx.e[0] && uy < bx.e[1] && uz < bx.e[2] && ub < bx.e[3]) {
+      const unsigned long long p = (((unsigned long long)ub * bx.e[2] + uz) * bx.e[1] + uy) * bx.e[0] + ux;
+      const unsigned long long w = __ldg(bitmap + (p >> 6));
+      row = (int)(__ldg(prefix + (p >> 6)) + (uint32_t)__popcll(w & ((1ull << (p & 63)) - 1ull)));
+    }
+  }
+  src_row[i] = row;
+}
+
+// per-site source counts (only built when some site has more than one source)
+__global__ void k_count_rows(const int32_t *__restrict__ src_row, long long n_src, uint32_t *cnt) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_src) return;
+  const int r = src_row[i];
+  if (r >= 0) atomicAdd(&cnt[r], 1u);
+}
+
+// inverse of a one-to-one source -> row map: item[row] = source (the source list of a grid without duplicates)
+__global__ void k_invert_rows(const int32_t *__restrict__ src_row, long long n_src, int32_t *__restrict__ item) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_src) return;
+  const int r = src_row[i];
+  if (r >= 0) item[r] = (int32_t)i;
 }
 
 // key -> row of every site into the (empty) open-addressing table; with capacity >= 2n an insert always finds a slot
 __global__ void k_table_fill(const int32_t *__restrict__ c, long long n, Slot *table, uint32_t mask) {
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  (void)table_insert(table, mask, pack_key(c[i], c[n + i], c[2 * n + i], c[3 * n + i]), (int)i);
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // blocks are multiples of 32 threads
+  const int lane = threadIdx.x & 31, first = lane & ~(kTeam - 1);
+  const unsigned team_mask = ((1u << kTeam) - 1u) << first;
+  const bool valid = i < n;
+  const unsigned long long key = valid ? pack_key(c[i], c[n + i], c[2 * n + i], c[3 * n + i]) : 0ull;
+#pragma unroll
+  for (int r = 0; r < kTeam; ++r) {  // the team inserts its four sites one after the other
+    const unsigned long long k = __shfl_sync(team_mask, key, first + r);
+    const int v = __shfl_sync(team_mask, (int)valid, first + r);
+    if (v) (void)table_insert_team(table, mask, k, (int)(i - (lane - first) + r), team_mask, lane);
+  }
 }
 
 // sources of each site (CSR), ascending source index inside a site
@@ -446,10 +651,25 @@ __global__ void k_csr_sort(const int32_t *__restrict__ off, long long n, int32_t
 // ---------------------------------------------------------------------------------------------
 __global__ void k_query(const int32_t *__restrict__ c, long long stride, long long n, const Slot *__restrict__ table,
                         uint32_t mask, int32_t *__restrict__ rows) {
-  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
-  int x = c[i], y = c[stride + i], z = c[2 * stride + i], b = c[3 * stride + i];
-  rows[i] = coord_ok(x, y, z, b) ? table_find(table, mask, pack_key(x, y, z, b)) : -1;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31, first = lane & ~(kTeam - 1);
+  const unsigned team_mask = ((1u << kTeam) - 1u) << first;
+  bool valid = i < n;
+  unsigned long long key = 0;
+  if (valid) {
+    const int x = c[i], y = c[stride + i], z = c[2 * stride + i], b = c[3 * stride + i];
+    valid = coord_ok(x, y, z, b);
+    key = pack_key(x, y, z, b);
+  }
+  int mine = -1;
+#pragma unroll
+  for (int r = 0; r < kTeam; ++r) {
+    const unsigned long long k = __shfl_sync(team_mask, key, first + r);
+    const int v = __shfl_sync(team_mask, (int)valid, first + r);
+    const int found = v ? table_find_team(table, mask, k, team_mask, lane) : -1;
+    if (lane == first + r) mine = found;
+  }
+  if (i < n) rows[i] = mine;
 }
 
 // 3x3x3 neighbour map.  blockIdx.y = offset k = (dx+1)*9 + (dy+1)*3 + (dz+1); the input site of
@@ -461,18 +681,30 @@ __global__ void k_ssc_nbr(const int32_t *__restrict__ c, long long n, const Slot
   if (dyn) n = dyn->n_unique;  // launched with a grid sized for an upper bound of n
   const int k = blockIdx.y;
   const int dx = k / 9 - 1, dy = (k / 3) % 3 - 1, dz = k % 3 - 1;
-  long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31, first = lane & ~(kTeam - 1);
+  const unsigned team_mask = ((1u << kTeam) - 1u) << first;
   int r = -1;
+  bool probe = false;
+  unsigned long long key = 0;
   if (o < n && (absent == nullptr || absent[o] < 0)) {
     if (k == 13 && self_ok) {
       r = (int)o;
     } else {
-      int x = c[o] + dx, y = c[n + o] + dy, z = c[2 * n + o] + dz, b = c[3 * n + o];
-      if (coord_ok(x, y, z, b)) r = table_find(table, mask, pack_key(x, y, z, b));
+      const int x = c[o] + dx, y = c[n + o] + dy, z = c[2 * n + o] + dz, b = c[3 * n + o];
+      probe = coord_ok(x, y, z, b);
+      key = pack_key(x, y, z, b);
     }
   }
+#pragma unroll
+  for (int q = 0; q < kTeam; ++q) {  // the team answers its four queries one after the other
+    const unsigned long long kq = __shfl_sync(team_mask, key, first + q);
+    const int v = __shfl_sync(team_mask, (int)probe, first + q);
+    const int found = v ? table_find_team(table, mask, kq, team_mask, lane) : -1;
+    if (v && lane == first + q) r = found;
+  }
   if (o < n) nbr[(long long)k * n + o] = r;
-  int cnt = __syncthreads_count(r >= 0);
+  const int cnt = __syncthreads_count(r >= 0);
   if (threadIdx.x == 0 && cnt) atomicAdd(&counts[k], (unsigned long long)cnt);
 }
 
@@ -622,8 +854,10 @@ int grid_free(Grid &g, cudaStream_t s) {
   return SCN_OK;
 }
 
-// Bitmaps above this many bits (4 GiB of words plus 2 GiB of prefixes) are refused.
-static const unsigned long long kMaxBoxBits = 1ull << 35;
+// A ranking bitmap is laid out for at most this many cells (512 MiB of words plus 256 MiB of prefixes).  Scenes whose
+// bounding box is larger -- two clusters at opposite corners of a 4096^3 volume, say -- are ranked by sorting their keys
+// and answer lookups through the open-addressing table; nothing limits their extent but the key range.
+const unsigned long long kMaxDenseBits = 1ull << 32;
 
 // The few words a build reads back land in pinned host memory: a copy into pageable memory goes through a driver
 // staging buffer and costs several microseconds more per round trip.  One 8 KB block per host thread; when it
@@ -653,128 +887,416 @@ static void take(void *dst, size_t bytes, int slot) {  // after the synchronisat
   if (pin && bytes <= 512) memcpy(dst, pin + 512 * slot, bytes);
 }
 
-int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift, int64_t n_src,
-               bool want_csr, const Box *box_hint, bool with_ssc, cudaStream_t s) {
-  grid_free(g, s);
+
+// Releases a stream-ordered temporary when it goes out of scope, on every path out of a build.
+struct Tmp {
+  void *p = nullptr;
+  cudaStream_t s;
+  explicit Tmp(cudaStream_t s_) : s(s_) {}
+  ~Tmp() { dev_free(p, s); }
+  Tmp(const Tmp &) = delete;
+  Tmp &operator=(const Tmp &) = delete;
+  template <typename T> int alloc(T **out, size_t count) {
+    dev_free(p, s);
+    int r = dev_alloc(&p, count * sizeof(T), s);
+    *out = static_cast<T *>(p);
+    return r;
+  }
+};
+
+Box box_with_margin(const Box &tight, int margin) {
+  Box b = tight;
+  for (int d = 0; d < 3; ++d) {
+    int lo = tight.o[d] - margin, hi = tight.o[d] + (int)tight.e[d] - 1 + margin;
+    if (lo < 0) lo = 0;
+    if (hi > SCN_MAX_COORD) hi = SCN_MAX_COORD;
+    b.o[d] = lo;
+    b.e[d] = (unsigned)(hi - lo + 1);
+  }
+  return b;
+}
+
+static unsigned long long box_cells(const Box &b, bool *fits) {
+  unsigned long long bits = 1;
+  *fits = true;
+  for (int d = 0; d < 4; ++d) {
+    bits *= b.e[d];
+    if (bits > kMaxDenseBits) {
+      *fits = false;
+      return bits;
+    }
+  }
+  return bits;
+}
+
+// ---------------------------------------------------------------------------------------------
+// LSD radix sort of (key, source index) pairs, 4 bits per pass, stable: the ranking of scenes too spread out
+// for a bitmap.  A block sorts nothing itself: it counts its digits, the counts of all blocks are scanned
+// digit-major, and every item is written straight to its final place of the pass (position of its digit's bucket
+// for this block + number of equal digits in front of it inside the block, counted in thread order, then item order,
+// which is the input order -- hence stable).
+// ---------------------------------------------------------------------------------------------
+constexpr int kSortThreads = 256;
+constexpr int kSortItems = 8;
+constexpr int kSortChunk = kSortThreads * kSortItems;
+
+__global__ void k_sort_hist(const unsigned long long *__restrict__ keys, long long n, int shift, uint32_t *__restrict__ hist,
+                            long long nb) {
+  __shared__ uint32_t h[16];
+  if (threadIdx.x < 16) h[threadIdx.x] = 0;
+  __syncthreads();
+  const long long base = (long long)blockIdx.x * kSortChunk + (long long)threadIdx.x * kSortItems;
+#pragma unroll
+  for (int j = 0; j < kSortItems; ++j)
+    if (base + j < n) atomicAdd(&h[(unsigned)(keys[base + j] >> shift) & 15u], 1u);
+  __syncthreads();
+  if (threadIdx.x < 16) hist[(long long)threadIdx.x * nb + blockIdx.x] = h[threadIdx.x];
+}
+
+__global__ void k_sort_scatter(const unsigned long long *__restrict__ keys, const int32_t *__restrict__ idx, long long n, int shift,
+                               const uint32_t *__restrict__ offs, long long nb, unsigned long long *__restrict__ keys_out,
+                               int32_t *__restrict__ idx_out) {
+  __shared__ unsigned short cnt[16][kSortThreads];
+  __shared__ uint32_t dig_base[16];
+  const int t = threadIdx.x;
+#pragma unroll
+  for (int d = 0; d < 16; ++d) cnt[d][t] = 0;
+  const long long base = (long long)blockIdx.x * kSortChunk + (long long)t * kSortItems;
+  unsigned long long k[kSortItems];
+  unsigned short r[kSortItems];
+#pragma unroll
+  for (int j = 0; j < kSortItems; ++j) {
+    k[j] = 0;
+    r[j] = 0;
+    if (base + j < n) {
+      k[j] = keys[base + j];
+      r[j] = cnt[(unsigned)(k[j] >> shift) & 15u][t]++;  // own column: no other thread touches it
+    }
+  }
+  __syncthreads();
+  // exclusive scan of every digit's row across the threads: warp w takes digits 2w and 2w+1, a lane 8 entries
+  const int warp = t >> 5, lane = t & 31;
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int d = 2 * warp + q;
+    uint32_t v[8], sum = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      v[e] = cnt[d][lane * 8 + e];
+      sum += v[e];
+    }
+    uint32_t incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    uint32_t ex = incl - sum;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      cnt[d][lane * 8 + e] = (unsigned short)ex;
+      ex += v[e];
+    }
+  }
+  if (t < 16) dig_base[t] = offs[(long long)t * nb + blockIdx.x];
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kSortItems; ++j) {
+    if (base + j < n) {
+      const unsigned d = (unsigned)(k[j] >> shift) & 15u;
+      const uint32_t pos = dig_base[d] + cnt[d][t] + r[j];
+      keys_out[pos] = k[j];
+      idx_out[pos] = idx ? idx[base + j] : (int32_t)(base + j);
+    }
+  }
+}
+
+// Sorts n (key, index) pairs by key; `vary` has a bit set wherever keys may differ (passes over digits that are the
+// same in every key are skipped).  On return *keys_sorted / *idx_sorted point into the buffers a/b.
+static int radix_sort_pairs(const unsigned long long *keys, long long n, unsigned long long vary, unsigned long long *ka,
+                            unsigned long long *kb, int32_t *ia, int32_t *ib, const unsigned long long **keys_sorted,
+                            const int32_t **idx_sorted, cudaStream_t s) {
+  const long long nb = (n + kSortChunk - 1) / kSortChunk;
+  Tmp t_hist(s), t_offs(s);
+  uint32_t *hist = nullptr, *offs = nullptr;
+  SCN_TRY(t_hist.alloc(&hist, (size_t)nb * 16));
+  SCN_TRY(t_offs.alloc(&offs, (size_t)nb * 16));
+  const unsigned long long *src_k = keys;
+  const int32_t *src_i = nullptr;
+  unsigned long long *dst_k = ka;
+  int32_t *dst_i = ia;
+  bool any = false;
+  for (int shift = 0; shift < 64; shift += 4) {
+    if (((vary >> shift) & 15ull) == 0 && !(shift == 60 && !any)) continue;  // at least one pass: the output buffers must be filled
+    k_sort_hist<<<(unsigned)nb, kSortThreads, 0, s>>>(src_k, n, shift, hist, nb);
+    SCN_LAUNCHED();
+    SCN_TRY(scan_emit(U32Values{hist}, StorePrefix{offs}, nb * 16, nullptr, s));
+    k_sort_scatter<<<(unsigned)nb, kSortThreads, 0, s>>>(src_k, src_i, n, shift, offs, nb, dst_k, dst_i);
+    SCN_LAUNCHED();
+    any = true;
+    src_k = dst_k;
+    src_i = dst_i;
+    dst_k = (dst_k == ka) ? kb : ka;
+    dst_i = (dst_i == ia) ? ib : ia;
+  }
+  *keys_sorted = src_k;
+  *idx_sorted = src_i;
+  return SCN_OK;
+}
+
+struct RunStarts {
+  const unsigned long long *k;
+  __device__ uint32_t operator()(long long i) const { return (i == 0 || k[i] != k[i - 1]) ? 1u : 0u; }
+};
+// row of every sorted element: the number of run starts up to and including it, minus one
+struct StoreRunRow {
+  int32_t *row;
+  __device__ void operator()(long long i, uint32_t ex, uint32_t v) const { row[i] = (int32_t)(ex + v) - 1; }
+};
+__global__ void k_sorted_emit(const unsigned long long *__restrict__ keys, const int32_t *__restrict__ idx,
+                              const int32_t *__restrict__ row_of, long long n_src, long long n, int32_t *__restrict__ src_row,
+                              int32_t *__restrict__ coords, int32_t *__restrict__ csr_off, int32_t *__restrict__ csr_item) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_src) return;
+  const int r = row_of[i];
+  const int src = idx[i];
+  src_row[src] = r;
+  if (csr_item) csr_item[i] = src;  // sources of a site in ascending index: the sort is stable
+  if (i == 0 || keys[i] != keys[i - 1]) {
+    int x, y, z, b;
+    unpack_key(keys[i], x, y, z, b);
+    coords[r] = x;
+    coords[n + r] = y;
+    coords[2 * n + r] = z;
+    coords[3 * n + r] = b;
+    if (csr_off) csr_off[r] = (int32_t)i;
+  }
+  if (i == n_src - 1 && csr_off) csr_off[n] = (int32_t)n_src;
+}
+__global__ void k_max_run(const int32_t *__restrict__ off, long long n, BuildInfo *info) {
+  const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  unsigned int c = r < n ? (unsigned)(off[r + 1] - off[r]) : 0u;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) c = max(c, __shfl_xor_sync(0xffffffffu, c, o));
+  if ((threadIdx.x & 31) == 0 && c) atomicMax(&info->max_active, c);
+}
+
+// Ranking by sorting: site row = rank of the key among the distinct keys, sources of a site in ascending index.
+// Leaves the grid without a bitmap; lookups go through its open-addressing table.
+static int grid_build_sorted(Grid &g, const unsigned long long *keys, const BuildInfo &measured, BuildInfo *info_d,
+                             int64_t n_src, bool want_csr, cudaStream_t s) {
+  unsigned long long vary = 0;
+  const int field_shift[4] = {0, 16, 32, 48};
+  for (int d = 0; d < 4; ++d) {
+    unsigned diff = (unsigned)measured.mn[d] ^ (unsigned)measured.mx[d];
+    unsigned long long m = 0;
+    while (diff) {
+      m = (m << 1) | 1ull;
+      diff >>= 1;
+    }
+    vary |= m << field_shift[d];
+  }
+  Tmp t_ka(s), t_kb(s), t_ia(s), t_ib(s), t_row(s);
+  unsigned long long *ka, *kb;
+  int32_t *ia, *ib, *row_of;
+  SCN_TRY(t_ka.alloc(&ka, (size_t)n_src));
+  SCN_TRY(t_kb.alloc(&kb, (size_t)n_src));
+  SCN_TRY(t_ia.alloc(&ia, (size_t)n_src));
+  SCN_TRY(t_ib.alloc(&ib, (size_t)n_src));
+  SCN_TRY(t_row.alloc(&row_of, (size_t)n_src));
+  const unsigned long long *ks = nullptr;
+  const int32_t *is = nullptr;
+  SCN_TRY(radix_sort_pairs(keys, n_src, vary, ka, kb, ia, ib, &ks, &is, s));
+  SCN_TRY(scan_emit(RunStarts{ks}, StoreRunRow{row_of}, n_src, &info_d->n_unique, s));
+  uint32_t n_u = 0;
+  SCN_TRY(read_back(&n_u, &info_d->n_unique, sizeof(uint32_t), 0, s, true));
+  take(&n_u, sizeof(uint32_t), 0);
+  const int64_t n = n_u;
+  g.n = n;
+  SCN_TRY(dev_alloc_t(&g.coords, (size_t)n * 4, s));
+  SCN_TRY(dev_alloc_t(&g.src_row, (size_t)n_src, s));
+  const bool dup = n != n_src;
+  if (want_csr) {
+    SCN_TRY(dev_alloc_t(&g.csr_item, (size_t)n_src, s));
+    if (dup) SCN_TRY(dev_alloc_t(&g.csr_off, (size_t)n + 1, s));
+  }
+  k_sorted_emit<<<blocks_for(n_src, 256), 256, 0, s>>>(ks, is, row_of, n_src, n, g.src_row, g.coords, g.csr_off, g.csr_item);
+  SCN_LAUNCHED();
+  g.max_active = 1;
+  if (want_csr && dup) {
+    k_max_run<<<blocks_for(n, 256), 256, 0, s>>>(g.csr_off, n, info_d);
+    SCN_LAUNCHED();
+    BuildInfo info;
+    SCN_TRY(read_back(&info, info_d, sizeof(info), 0, s, true));
+    take(&info, sizeof(info), 0);
+    g.max_active = (int32_t)info.max_active;
+  }
+  return SCN_OK;
+}
+
+// the source lists of a grid whose sites have several sources: counts, offsets, items in ascending source index
+static int build_source_lists(Grid &g, BuildInfo *info_d, cudaStream_t s) {
+  const int T = 256;
+  Tmp t_cnt(s);
+  uint32_t *cnt = nullptr;
+  SCN_TRY(t_cnt.alloc(&cnt, (size_t)g.n));
+  SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)g.n * 4, s));
+  k_count_rows<<<blocks_for(g.n_src, T), T, 0, s>>>(g.src_row, g.n_src, cnt);
+  SCN_LAUNCHED();
+  SCN_TRY(dev_alloc_t(&g.csr_off, (size_t)g.n + 1, s));
+  SCN_TRY(dev_alloc_t(&g.csr_item, (size_t)g.n_src, s));
+  SCN_TRY(scan_emit(U32Values{cnt}, StoreOffsets{g.csr_off, (long long)g.n}, g.n, nullptr, s));
+  SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)g.n * 4, s));
+  k_csr_fill<<<blocks_for(g.n_src, T), T, 0, s>>>(g.src_row, g.n_src, g.csr_off, cnt, g.csr_item);
+  SCN_LAUNCHED();
+  k_csr_sort<<<blocks_for(g.n, T), T, 0, s>>>(g.csr_off, g.n, g.csr_item, info_d);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
+int grid_ensure_source_lists(const Grid &g, cudaStream_t s) {
+  if (g.csr_item || g.n == 0) return SCN_OK;
+  int32_t *item = nullptr;
+  SCN_TRY(dev_alloc_t(&item, (size_t)g.n_src, s));
+  k_invert_rows<<<blocks_for(g.n_src, 256), 256, 0, s>>>(g.src_row, g.n_src, item);
+  SCN_LAUNCHED();
+  g.csr_item = item;
+  return SCN_OK;
+}
+
+static int grid_build_impl(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift, int64_t n_src,
+                           bool want_csr, const Box *box_hint, bool with_ssc, cudaStream_t s) {
   g.n_src = n_src;
   if (n_src == 0) return SCN_OK;
   if (n_src > 0x7FFFFFF0ll) return fail(SCN_E_CAPACITY, "more than 2^31 source rows");
   const int T = 256;
+  Tmp t_info(s), t_keys(s), t_sums(s), t_nbr_counts(s);
   BuildInfo *info_d = nullptr;
   unsigned long long *keys = nullptr;
-  SCN_TRY(dev_alloc_t(&info_d, 1, s));
-  SCN_TRY(dev_alloc_t(&keys, (size_t)n_src, s));
+  SCN_TRY(t_info.alloc(&info_d, 1));
+  SCN_TRY(t_keys.alloc(&keys, (size_t)n_src));
   k_init_info<<<1, 32, 0, s>>>(info_d);
-  SCN_LAUNCHED();
-  if (coords64) {
-    int vec = (ncols == 4 && (reinterpret_cast<uintptr_t>(coords64) & 15) == 0) ? 1 : 0;
-    k_pack_keys_i64<<<blocks_for(n_src, T), T, 0, s>>>(reinterpret_cast<const long long *>(coords64), ncols, vec,
-                                                      n_src, keys, info_d);
-  } else {
-    k_pack_keys_soa<<<blocks_for(n_src, T), T, 0, s>>>(coords_soa, n_src, shift, keys, info_d, box_hint ? 0 : 1, nullptr);
-  }
   SCN_LAUNCHED();
   BuildInfo info;
   Box bx;
-  const bool hinted = box_hint && !coords64;
+  bool fits = false;
+  unsigned long long bits = 0;
+  // With a box that should hold the scene (the previous build's, widened), keys, bounding box and occupancy bits come
+  // out of one pass over the coordinates and the build has a single host round trip, at its end.
+  const bool hinted = box_hint != nullptr && coords64 != nullptr && (bits = box_cells(*box_hint, &fits), fits);
   if (hinted) {
     bx = *box_hint;
-    for (int d = 0; d < 4; ++d) {
-      info.mn[d] = bx.o[d];
-      info.mx[d] = bx.o[d] + (int)bx.e[d] - 1;
-    }
   } else {
+    if (coords64) {
+      const int vec = (ncols == 4 && (reinterpret_cast<uintptr_t>(coords64) & 15) == 0) ? 1 : 0;
+      k_pack_keys_i64<<<blocks_for(n_src, T), T, 0, s>>>(reinterpret_cast<const long long *>(coords64), ncols, vec, n_src, keys, info_d);
+    } else {
+      k_pack_keys_soa<<<blocks_for(n_src, T), T, 0, s>>>(coords_soa, n_src, shift, keys, info_d, 1, nullptr);
+    }
+    SCN_LAUNCHED();
     SCN_TRY(read_back(&info, info_d, sizeof(info), 0, s, true));
     take(&info, sizeof(info), 0);
-    if (info.err & 1u) {
-      dev_free(info_d, s);
-      dev_free(keys, s);
-      return fail(SCN_E_RANGE, "coordinate outside [0, 65534] or batch index outside [0, 32766]");
+    if (info.err & 1u) return fail(SCN_E_RANGE, "coordinate outside [0, 65534] or batch index outside [0, 32766]");
+    for (int d = 0; d < 4; ++d) {
+      bx.o[d] = info.mn[d];
+      bx.e[d] = (unsigned)(info.mx[d] - info.mn[d] + 1);
     }
-  }
-  unsigned long long bits = 1;
-  for (int d = 0; d < 4; ++d) {
-    bx.o[d] = info.mn[d];
-    bx.e[d] = (unsigned)(info.mx[d] - info.mn[d] + 1);
-    bits *= bx.e[d];
-    if (bits > kMaxBoxBits) {
-      dev_free(info_d, s);
-      dev_free(keys, s);
-      return fail(SCN_E_CAPACITY, "scene bounding box larger than 2^35 cells");
+    g.tight = bx;
+    bits = box_cells(bx, &fits);
+    if (!fits) {  // too spread out for a bitmap: rank by sorting
+      g.box = bx;
+      return grid_build_sorted(g, keys, info, info_d, n_src, want_csr, s);
     }
   }
   const long long nwords = (long long)((bits + 63) >> 6);
   SCN_TRY(dev_alloc_t(&g.bitmap, (size_t)nwords, s));
   SCN_TRY(dev_alloc_t(&g.prefix, (size_t)nwords, s));
-  unsigned long long *bitmap = g.bitmap;  // kept with the grid: every later lookup is answered from them
-  uint32_t *prefix = g.prefix;
-  SCN_CUDA(cudaMemsetAsync(bitmap, 0, (size_t)nwords * 8, s));
-  k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, nullptr);
-  SCN_LAUNCHED();
-  SCN_TRY(scan_emit(PopcWords{bitmap}, StorePrefix{prefix}, nwords, &info_d->n_unique, s));
-  SCN_TRY(read_back(&info.n_unique, &info_d->n_unique, sizeof(uint32_t), 0, s, true));
-  take(&info.n_unique, sizeof(uint32_t), 0);
-  const int64_t n = info.n_unique;
-  g.n = n;
-  g.box = bx;
-  uint32_t *cnt = nullptr;
-  SCN_TRY(dev_alloc_t(&g.coords, (size_t)n * 4, s));
-  SCN_TRY(dev_alloc_t(&g.src_row, (size_t)n_src, s));
-  if (want_csr) SCN_TRY(dev_alloc_t(&g.csr_item, (size_t)n_src, s));
-  if (n == n_src) {
-    k_rank_rows<true><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, nullptr,
-                                                        g.csr_item);
+  SCN_CUDA(cudaMemsetAsync(g.bitmap, 0, (size_t)nwords * 8, s));
+  if (hinted) {
+    const int vec = (ncols == 4 && (reinterpret_cast<uintptr_t>(coords64) & 15) == 0) ? 1 : 0;
+    k_pack_mark_i64<<<blocks_for(n_src, T), T, 0, s>>>(reinterpret_cast<const long long *>(coords64), ncols, vec, n_src, bx, keys,
+                                                      g.bitmap, info_d);
   } else {
-    SCN_TRY(dev_alloc_t(&cnt, (size_t)n, s));
-    SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n * 4, s));
-    k_rank_rows<false><<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, bitmap, prefix, n, g.src_row, g.coords, cnt,
-                                                         nullptr);
+    k_mark<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, g.bitmap, nullptr);
   }
   SCN_LAUNCHED();
-  g.max_active = 1;
-  bool need_info = false;
-  if (want_csr) {
-    if (n != n_src) {
-      SCN_TRY(dev_alloc_t(&g.csr_off, (size_t)n + 1, s));
-      SCN_TRY(scan_emit(U32Values{cnt}, StoreOffsets{g.csr_off, (long long)n}, n, nullptr, s));
-      SCN_CUDA(cudaMemsetAsync(cnt, 0, (size_t)n * 4, s));
-      k_csr_fill<<<blocks_for(n_src, T), T, 0, s>>>(g.src_row, n_src, g.csr_off, cnt, g.csr_item);
-      SCN_LAUNCHED();
-      k_csr_sort<<<blocks_for(n, T), T, 0, s>>>(g.csr_off, n, g.csr_item, info_d);
-      SCN_LAUNCHED();
-      need_info = true;
-    }
+  // popcount scan; its second sweep also writes the site coordinates.  The site count stays on the device until the
+  // end: buffers are sized by the bound n <= n_src.
+  const long long nb = (nwords + kScanChunk - 1) / kScanChunk;
+  uint32_t *sums = nullptr;
+  SCN_TRY(t_sums.alloc(&sums, (size_t)nb));
+  SCN_TRY(dev_alloc_t(&g.coords, (size_t)n_src * 4, s));
+  SCN_TRY(dev_alloc_t(&g.src_row, (size_t)n_src, s));
+  k_scan_sums<<<(unsigned)nb, kScanThreads, 0, s>>>(PopcWords{g.bitmap}, nwords, sums);
+  SCN_LAUNCHED();
+  const int offsets_given = nb > 8192 ? 1 : 0;
+  if (offsets_given) {
+    k_scan_top<<<1, kScanThreads, 0, s>>>(sums, nb, &info_d->n_unique);
+    SCN_LAUNCHED();
   }
-  // the neighbour map rides along when asked for: its counts come back with the error word
+  k_rank_emit<<<(unsigned)nb, kScanThreads, 0, s>>>(g.bitmap, nwords, sums, nb, offsets_given, bx, g.prefix, g.coords, info_d);
+  SCN_LAUNCHED();
+  k_rank_src<<<blocks_for(n_src, T), T, 0, s>>>(keys, n_src, bx, g.bitmap, g.prefix, g.src_row);
+  SCN_LAUNCHED();
+  // the neighbour map rides along when asked for: its counts come back with the build record
   unsigned long long *nbr_counts_d = nullptr, nbr_counts[27];
-  if (with_ssc && n > 0) {
-    SCN_TRY(dev_alloc_t(&nbr_counts_d, 27, s));
+  if (with_ssc) {
+    SCN_TRY(t_nbr_counts.alloc(&nbr_counts_d, 27));
     SCN_CUDA(cudaMemsetAsync(nbr_counts_d, 0, 27 * 8, s));
-    SCN_TRY(dev_alloc_t(&g.nbr, (size_t)n * 27, s));
-    k_ssc_nbr_rank<<<dim3(blocks_for(n, 256), 9), 256, 0, s>>>(g.coords, n, bx, g.bitmap, g.prefix, nullptr, 1, g.nbr, nbr_counts_d, nullptr);
+    SCN_TRY(dev_alloc_t(&g.nbr, (size_t)n_src * 27, s));
+    k_ssc_nbr_rank<<<dim3(blocks_for(n_src, 256), 9), 256, 0, s>>>(g.coords, 0, bx, g.bitmap, g.prefix, nullptr, 1, g.nbr, nbr_counts_d,
+                                                                  info_d);
     SCN_LAUNCHED();
     SCN_TRY(read_back(nbr_counts, nbr_counts_d, sizeof(nbr_counts), 1, s, false));
   }
-  // max_active comes back when duplicates exist, the neighbour counts when that map was built; a build of unique
-  // points without the map ends here with nothing to wait for
-  if (need_info || nbr_counts_d) {
-    SCN_TRY(read_back(&info, info_d, sizeof(info), 0, s, true));
-    take(&info, sizeof(info), 0);
+  SCN_TRY(read_back(&info, info_d, sizeof(info), 0, s, true));  // the one round trip of a hinted build
+  take(&info, sizeof(info), 0);
+  if (info.err & 1u) return fail(SCN_E_RANGE, "coordinate outside [0, 65534] or batch index outside [0, 32766]");
+  if (hinted) {
+    Box tight;
+    for (int d = 0; d < 4; ++d) {
+      tight.o[d] = info.mn[d];
+      tight.e[d] = (unsigned)(info.mx[d] - info.mn[d] + 1);
+    }
+    g.tight = tight;
+    if (info.err & 2u) return SCN_E_STATE + 100;  // a point outside the hinted box: the caller repeats with the measured one
   }
-  if (nbr_counts_d) take(nbr_counts, sizeof(nbr_counts), 1);
-  if (need_info) g.max_active = (int32_t)info.max_active;
-  if (nbr_counts_d) {
+  if (with_ssc) take(nbr_counts, sizeof(nbr_counts), 1);
+  g.n = info.n_unique;
+  g.box = bx;
+  g.max_active = 1;
+  if (with_ssc) {
     g.nbr_total = 0;
     for (int k = 0; k < 27; ++k) {
       g.nbr_count[k] = (int64_t)nbr_counts[k];
       g.nbr_total += g.nbr_count[k];
     }
-    dev_free(nbr_counts_d, s);
   }
-  dev_free(cnt, s);
-  dev_free(keys, s);
-  dev_free(info_d, s);
+  if (want_csr && g.n != n_src) {  // some site has several sources: their lists, and the longest one
+    SCN_TRY(build_source_lists(g, info_d, s));
+    SCN_TRY(read_back(&info, info_d, sizeof(info), 0, s, true));
+    take(&info, sizeof(info), 0);
+    g.max_active = (int32_t)info.max_active;
+  }
   return SCN_OK;
+}
+
+int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift, int64_t n_src,
+               bool want_csr, const Box *box_hint, bool with_ssc, cudaStream_t s) {
+  grid_free(g, s);
+  int r = grid_build_impl(g, coords64, ncols, coords_soa, shift, n_src, want_csr, box_hint, with_ssc, s);
+  if (r == SCN_E_STATE + 100) {  // the hinted box did not hold the scene; the pass measured the box that does
+    const Box measured = g.tight;
+    grid_free(g, s);
+    r = grid_build_impl(g, coords64, ncols, coords_soa, shift, n_src, want_csr, &measured, with_ssc, s);
+    if (r == SCN_E_STATE + 100) r = fail(SCN_E_STATE, "grid build: the measured bounding box does not hold the scene");
+  }
+  if (r != SCN_OK) {  // never leave a half-built grid behind
+    const int64_t n_src_keep = 0;
+    grid_free(g, s);
+    g.n_src = n_src_keep;
+  }
+  return r;
 }
 
 // What one level of a chained coarse build leaves on the device for the host to read at the end.
@@ -814,8 +1336,8 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
       bx.e[d] = (unsigned)(hi - lo + 1);
       bits *= bx.e[d];
     }
-    if (bits > kMaxBoxBits) {
-      rc = fail(SCN_E_CAPACITY, "scene bounding box larger than 2^35 cells");
+    if (bits > kMaxDenseBits) {
+      rc = fail(SCN_E_CAPACITY, "coarse scale: bounding box too large for a ranking bitmap");
       break;
     }
     boxes[(size_t)l] = bx;
@@ -899,7 +1421,29 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
   return rc;
 }
 
+bool coarse_box_fits_bitmap(const Box &fine_box, Box *coarse_box) {
+  Box bx;
+  for (int d = 0; d < 4; ++d) {
+    const int sh = d < 3 ? 1 : 0;
+    const int lo = fine_box.o[d] >> sh, hi = (fine_box.o[d] + (int)fine_box.e[d] - 1) >> sh;
+    bx.o[d] = lo;
+    bx.e[d] = (unsigned)(hi - lo + 1);
+  }
+  if (coarse_box) *coarse_box = bx;
+  bool fits;
+  (void)box_cells(bx, &fits);
+  return fits;
+}
+
 int grid_build_coarse(Grid &g, const Grid &fine, bool with_ssc, cudaStream_t s) {
+  if (!fine.bitmap || !coarse_box_fits_bitmap(fine.box, nullptr)) {
+    // a scene too spread out for a bitmap at this scale: rank the halved coordinates by sorting, then the stride-2
+    // maps from the source rows; the neighbour map (when asked for) through the table
+    SCN_TRY(grid_build(g, nullptr, 0, fine.coords, 1, fine.n, false, nullptr, false, s));
+    SCN_TRY(grid_build_conv(g, fine, s));
+    if (with_ssc) SCN_TRY(grid_build_ssc(g, s));
+    return SCN_OK;
+  }
   Grid *one = &g;
   return grid_build_coarse_chain(&one, 1, fine, with_ssc, s);
 }

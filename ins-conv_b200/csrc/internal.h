@@ -54,7 +54,7 @@ static const unsigned long long kEmptyKey = ~0ull;
 struct BuildInfo {
   int mn[4];  // bounding box minimum  x,y,z,batch
   int mx[4];  // bounding box maximum
-  unsigned int err;         // bit0: coordinate out of key range
+  unsigned int err;         // bit0: coordinate out of key range; bit1: a point outside the box the bitmap was laid out for
   unsigned int n_unique;    // sites found
   unsigned int max_active;  // most source points in one site
   unsigned int reserved;
@@ -69,7 +69,8 @@ struct Box {
 // One scale of a scene.
 struct Grid {
   int64_t n = 0;           // active sites
-  Box box = {{0, 0, 0, 0}, {0, 0, 0, 0}};  // bounding box of the sites (valid when n > 0)
+  Box box = {{0, 0, 0, 0}, {0, 0, 0, 0}};  // the box the ranking structure is laid out for: contains every site (valid when n > 0)
+  Box tight = {{0, 0, 0, 0}, {0, 0, 0, 0}};  // measured bounding box of the source points (input scale only)
   int32_t *coords = nullptr;  // SoA [4][n]: x, y, z, batch
   // open-addressing table key -> row: a second index beside the ranking structure below, filled on first use
   // (grid_ensure_table) because only the public coordinate query and the table dump read it
@@ -80,7 +81,8 @@ struct Grid {
   int64_t n_src = 0;
   int32_t *src_row = nullptr;   // [n_src] source -> site row
   int32_t *csr_off = nullptr;   // [n+1]  (nullptr when every site has exactly one source: off[i] = i)
-  int32_t *csr_item = nullptr;  // [n_src] sources of each site, ascending
+  mutable int32_t *csr_item = nullptr;  // [n_src] sources of each site, ascending; when every site has one source it is
+                                        // only made on request (grid_ensure_source_lists): row -> its source
   int32_t max_active = 0;
   // occupancy bitmap of the box in key order and the exclusive prefix sums of its word popcounts: the ranking
   // structure of the build, kept because "row of the site at (x,y,z)" = prefix[word] + popcount(bits below) answers
@@ -105,6 +107,9 @@ int grid_free(Grid &g, cudaStream_t s);
 // Fills g.table from the site coordinates when it does not exist yet (capacity: the smallest power of two >= 2n, at
 // least 16; linear probing cannot fail at that load).  No host round trip.
 int grid_ensure_table(const Grid &g, cudaStream_t s);
+int grid_ensure_source_lists(const Grid &g, cudaStream_t s);
+// true when the next coarser scale of `fine_box` (every axis halved) is small enough for a ranking bitmap
+bool coarse_box_fits_bitmap(const Box &fine_box, Box *coarse_box);
 
 // Builds g from source points.  Exactly one of coords64 / coords_soa is given:
 //   coords64  : int64 [n_src, ncols] rows (x,y,z[,b]) on the device
@@ -115,6 +120,12 @@ int grid_ensure_table(const Grid &g, cudaStream_t s);
 // grid_build_ssc would make).
 int grid_build(Grid &g, const int64_t *coords64, int ncols, const int32_t *coords_soa, int shift,
                int64_t n_src, bool want_csr, const Box *box_hint, bool with_ssc, cudaStream_t s);
+// a box that holds `tight` with a margin on the three spatial axes (clipped to the key range): what the next build of
+// a similar scene is laid out for, so that it needs no round trip to measure its own
+Box box_with_margin(const Box &tight, int margin);
+// largest number of cells a ranking bitmap is laid out for; scenes whose bounding box is larger are ranked by sorting
+// their keys and looked up through the open-addressing table
+extern const unsigned long long kMaxDenseBits;
 // The next coarser scale of `fine` (sites at coordinates >> 1) with its size-2/stride-2 maps and, on request,
 // its neighbour map, in one pass with a single host round trip at the end: the site count stays
 // on the device while the kernels run, buffers are sized by the bound n_coarse <= n_fine.
@@ -146,6 +157,18 @@ int build_incre_up(const Grid &coarse, const int32_t *pe_coarse, const int32_t *
                    cudaStream_t s);
 
 // ---- feature kernels --------------------------------------------------------
+// Optional second output of a gather-GEMM, formed in its epilogue from the finished row (after the init/bias term):
+// leaky(v * scale[c] + shift[c]) as fp16 rows -- the BatchNorm + ReLU that follows the convolution in the network,
+// handed to the next convolution without a pass of its own.  skip_raw: the fp32 result itself is not written.
+struct EpiBn {
+  const float *scale = nullptr;  // [n_planes_out]  gamma / sqrt(var + eps)
+  const float *shift = nullptr;  // [n_planes_out]  beta - mean * scale
+  float leak = 0.f;
+  void *dst = nullptr;           // __half rows [n_out, stride]
+  long long stride = 0;
+  int skip_raw = 0;
+};
+
 // out[o] = (init ? init[o] : bias) + sum_k in[map[k*n_out + o]] * W[k]   (map == nullptr: identity, K = 1)
 // init: rows [n_out, n_planes_out] with stride init_stride, or nullptr; it may be `out` itself (accumulate in place).
 // in has in_rows rows; map entries are -1 or in [0, in_rows).
@@ -183,17 +206,17 @@ int64_t tc_f16_packed_size(int64_t K, int64_t Cin, int64_t Cout);
 int tc_pack_weights_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
 int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                        const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                       int64_t init_stride, cudaStream_t s);
+                       int64_t init_stride, cudaStream_t s, const EpiBn *epi = nullptr);
 int warp_mma_pack_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
 // wide layers on small grids: 16 rows x 32 output planes per warp, whole reduction in one launch
 bool warp_slab_f16_shape(int64_t K, int64_t Cin, int64_t Cout);
 int warp_mma_pack_f16_any(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
 int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                        int64_t init_stride, cudaStream_t s);
+                        int64_t init_stride, cudaStream_t s, const EpiBn *epi = nullptr);
 int gather_mma_warp_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                        int64_t init_stride, cudaStream_t s);
+                        int64_t init_stride, cudaStream_t s, const EpiBn *epi = nullptr);
 int bn_forward_train(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,
                      float *running_mean, float *running_var, float *save_mean, float *save_invstd, const float *gamma,
                      const float *beta, float eps, float momentum, float leak, cudaStream_t s);

@@ -116,6 +116,44 @@ struct WeightArg {
   }
 };
 
+// The epilogue a convolution call may carry: addend (residual sum) and / or the BatchNorm + ReLU that follows the
+// convolution in the network, written as fp16 rows into bn_out (resized here).  All tensors optional.
+struct EpiArg {
+  scn_epilogue e;
+  bool any = false;
+  EpiArg(const at::Tensor &addend, const at::Tensor &bn_scale, const at::Tensor &bn_shift, double bn_leak, at::Tensor &bn_out,
+         bool skip_raw, int64_t rows, int64_t planes, const at::Tensor &bias) {
+    memset(&e, 0, sizeof e);
+    if (addend.defined() && addend.numel() > 0) {
+      need_cuda_f32(addend, "addend");
+      TORCH_CHECK(!bias.defined() || bias.numel() == 0, "the fused residual sum takes no bias");
+      TORCH_CHECK(addend.dim() == 2 && addend.size(0) == rows && addend.size(1) == planes && addend.stride(1) == 1,
+                  "addend must be [nActive, nOut] with unit plane stride");
+      e.addend = addend.data_ptr<float>();
+      e.addend_stride = addend.stride(0);
+      any = true;
+    }
+    if (bn_scale.defined() && bn_scale.numel() > 0) {
+      need_opt_cuda_f32(bn_scale, planes, "bn_scale");
+      need_opt_cuda_f32(bn_shift, planes, "bn_shift");
+      TORCH_CHECK(bn_shift.defined() && bn_shift.numel() == planes, "bn_shift must match bn_scale");
+      TORCH_CHECK(bn_out.defined() && bn_out.scalar_type() == at::kHalf && bn_out.is_cuda(),
+                  "bn_out must be a CUDA float16 tensor (it is resized here)");
+      bn_out.resize_({rows, planes});
+      e.bn_scale = bn_scale.data_ptr<float>();
+      e.bn_shift = bn_shift.data_ptr<float>();
+      e.bn_leakiness = bn_leak;
+      e.bn_out = bn_out.data_ptr<at::Half>();
+      e.bn_out_stride = planes;
+      e.skip_raw = skip_raw ? 1 : 0;
+      any = true;
+    } else {
+      TORCH_CHECK(!skip_raw, "skip_raw needs a fused BatchNorm output");
+    }
+  }
+  const scn_epilogue *get() const { return any ? &e : nullptr; }
+};
+
 class Metadata3 {
  public:
   Metadata3() { check(scn_metadata_create(&h_), "Metadata"); }
@@ -157,6 +195,7 @@ class Metadata3 {
   void setBuildAhead(int neighbour_maps, int coarse_levels) {
     check(scn_metadata_set_build_ahead(h_, neighbour_maps, coarse_levels), "Metadata.setBuildAhead");
   }
+  void inherit(Metadata3 &previous) { check(scn_metadata_inherit(h_, previous.h()), "Metadata.inherit"); }
   std::pair<int, int> buildUsed() {
     int nm = 0, levels = 0;
     check(scn_metadata_build_used(h_, &nm, &levels), "Metadata.buildUsed");
@@ -170,7 +209,9 @@ class Metadata3 {
 // ---- full-frame ops ------------------------------------------------------------------------------
 double SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filterSize, Metadata3 &m,
                                            at::Tensor input_features, at::Tensor output_features, at::Tensor weight,
-                                           at::Tensor bias, int dilated_rate, at::Tensor packed, at::Tensor addend) {
+                                           at::Tensor bias, int dilated_rate, at::Tensor packed, at::Tensor addend,
+                                           at::Tensor bn_scale, at::Tensor bn_shift, double bn_leak, at::Tensor bn_out,
+                                           bool skip_raw) {
   FeatArg fa(input_features, "input_features");
   need_cuda_f32(weight, "weight");
   TORCH_CHECK(dilated_rate == 1, "dilated submanifold convolutions are outside the hot path");
@@ -184,29 +225,20 @@ double SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filt
   TORCH_CHECK(n >= 0, "Metadata has no grid at this spatial size");
   need_rows(in, n, w.size(1), "input_features");
   need_opt_cuda_f32(bias, w.size(2), "bias");
-  output_features.resize_({n, w.size(2)});
+  EpiArg epi(addend, bn_scale, bn_shift, bn_leak, bn_out, skip_raw, n, w.size(2), bias);
+  if (!skip_raw) output_features.resize_({n, w.size(2)});
   double flops = 0;
   WeightArg wa(w, packed, fa.half);
-  if (addend.defined() && addend.numel() > 0) {  // out = addend + convolution: the residual sum formed in the epilogue
-    need_cuda_f32(addend, "addend");
-    TORCH_CHECK(!bias.defined() || bias.numel() == 0, "the fused residual sum takes no bias");
-    TORCH_CHECK(addend.dim() == 2 && addend.size(0) == n && addend.size(1) == w.size(2) && addend.stride(1) == 1,
-                "addend must be [nActive, nOut] with unit plane stride");
-    check(scn_ssc_forward_add(m.h(), s.v, fa.ptr, in.size(1), output_features.data_ptr<float>(), w.size(2),
-                              wa.ptr, addend.data_ptr<float>(), addend.stride(0), w.size(1), w.size(2), wa.precision,
-                              stream_of(in), &flops),
-          "SubmanifoldConvolution_updateOutput");
-    return flops;
-  }
-  check(scn_ssc_forward(m.h(), s.v, fa.ptr, in.size(1), output_features.data_ptr<float>(), w.size(2),
-                        wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision, stream_of(in), &flops),
+  check(scn_ssc_forward_ex(m.h(), s.v, fa.ptr, in.size(1), skip_raw ? nullptr : output_features.data_ptr<float>(), w.size(2),
+                           wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision, epi.get(), stream_of(in), &flops),
         "SubmanifoldConvolution_updateOutput");
   return flops;
 }
 
 double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
                                 at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
-                                at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed) {
+                                at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed,
+                                at::Tensor bn_scale, at::Tensor bn_shift, double bn_leak, at::Tensor bn_out, bool skip_raw) {
   FeatArg fa(input_features, "input_features");
   need_cuda_f32(weight, "weight");
   expect_filter(filterSize, 2, "Convolution");
@@ -220,12 +252,13 @@ double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at:
   need_opt_cuda_f32(bias, w.size(2), "bias");
   int64_t n = 0;
   check(scn_conv_prepare(m.h(), si.v, so.v, stream_of(in), &n), "Convolution_updateOutput");
-  output_features.resize_({n, w.size(2)});
+  EpiArg epi(at::Tensor(), bn_scale, bn_shift, bn_leak, bn_out, skip_raw, n, w.size(2), bias);
+  if (!skip_raw) output_features.resize_({n, w.size(2)});
   double flops = 0;
   WeightArg wa(w, packed, fa.half);
-  check(scn_conv_forward(m.h(), si.v, so.v, fa.ptr, in.size(1), output_features.data_ptr<float>(),
-                         w.size(2), wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision,
-                         stream_of(in), &flops),
+  check(scn_conv_forward_ex(m.h(), si.v, so.v, fa.ptr, in.size(1), skip_raw ? nullptr : output_features.data_ptr<float>(),
+                            w.size(2), wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision, epi.get(),
+                            stream_of(in), &flops),
         "Convolution_updateOutput");
   return flops;
 }
@@ -395,8 +428,9 @@ double Incre_Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSiz
                                       at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed) {
   // a 2/2 convolution has no overlap between cells: the residual of the output is the convolution of
   // the residual (reference: CUDA/Convolution.cpp:83-113)
+  at::Tensor none;
   return Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features, output_features,
-                                  weight, bias, packed);
+                                  weight, bias, packed, none, none, 0.0, none, false);
 }
 
 double Incre_Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
@@ -543,6 +577,9 @@ void no_backward(pybind11::args, pybind11::kwargs) {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
   mod.doc() = "B200 sparse-convolution operators behind the sparseconvnet.SCN interface (dimension 3)";
+  // default of every optional tensor argument: an empty tensor (the interface's "no bias" convention), so that calls
+  // with the reference's own argument lists work as they are
+  const at::Tensor none = at::empty({0});
   pybind11::class_<Metadata3>(mod, "Metadata_3")
       .def(pybind11::init<>())
       .def("clear", &Metadata3::clear)
@@ -550,17 +587,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
       .def("getSpatialLocationsDevice", &Metadata3::getSpatialLocationsDevice)
       .def("getNActive", &Metadata3::getNActive)
       .def("setBuildAhead", &Metadata3::setBuildAhead)
-      .def("buildUsed", &Metadata3::buildUsed);
-  mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("dilated_rate"), pybind11::arg("packed") = at::Tensor(), pybind11::arg("addend") = at::Tensor());
-  mod.def("Convolution_updateOutput", &Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());
-  mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());
+      .def("buildUsed", &Metadata3::buildUsed)
+      .def("inherit", &Metadata3::inherit);
+  mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("dilated_rate"), pybind11::arg("packed") = none, pybind11::arg("addend") = none, pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("skip_raw") = false);
+  mod.def("Convolution_updateOutput", &Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none, pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("skip_raw") = false);
+  mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);
   mod.def("BatchNormalization_updateOutput", &BatchNormalization_updateOutput);
-  mod.def("NetworkInNetwork_updateOutput", &NetworkInNetwork_updateOutput, pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());
+  mod.def("NetworkInNetwork_updateOutput", &NetworkInNetwork_updateOutput, pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);
   mod.def("InputLayer_updateOutput", &InputLayer_updateOutput);
   mod.def("OutputLayer_updateOutput", &OutputLayer_updateOutput);
-  mod.def("Incre_SubmanifoldConvolution_updateOutput", &Incre_SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("pre_metadata"), pybind11::arg("pre_input_feats"), pybind11::arg("packed") = at::Tensor());
-  mod.def("Incre_Convolution_updateOutput", &Incre_Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = at::Tensor());
-  mod.def("Incre_Deconvolution_updateOutput", &Incre_Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("pre_metadata"), pybind11::arg("pre_input_feats"), pybind11::arg("packed") = at::Tensor());
+  mod.def("Incre_SubmanifoldConvolution_updateOutput", &Incre_SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("pre_metadata"), pybind11::arg("pre_input_feats"), pybind11::arg("packed") = none);
+  mod.def("Incre_Convolution_updateOutput", &Incre_Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);
+  mod.def("Incre_Deconvolution_updateOutput", &Incre_Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("pre_metadata"), pybind11::arg("pre_input_feats"), pybind11::arg("packed") = none);
   mod.def("Incre_BatchNormalization_updateOutput", &Incre_BatchNormalization_updateOutput);
   mod.def("Incre_InputLayer_updateOutput", &Incre_InputLayer_updateOutput);
   mod.def("Incre_OutputLayer_updateOutput", &Incre_OutputLayer_updateOutput);

@@ -62,6 +62,7 @@ PROTOTYPES = {
     "scn_set_build_ahead": (_int, [_int, _int]),
     "scn_metadata_set_build_ahead": (_int, [_p, _int, _int]),
     "scn_metadata_build_used": (_int, [_p, C.POINTER(_int), C.POINTER(_int)]),
+    "scn_metadata_inherit": (_int, [_p, _p]),
     "scn_packed_size_f16": (_i64, [_i64, _i64, _i64]),
     "scn_weights_packable_f16": (_int, [_i64, _i64, _i64]),
     "scn_pack_weights_f16": (_int, [_p, _i64, _i64, _i64, _p, _p]),
@@ -82,6 +83,22 @@ PROTOTYPES = {
     "scn_incre_deconv_forward": (_int, [_p, _p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _p, _i64, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_incre_bn_forward": (_int, [_p, _p, _i64p, _p, _i64, _p, _i64, _i64, _p, _p, _p, _p, _dbl, _dbl, _p, _p, _p]),
 }
+
+
+
+class Epilogue(C.Structure):
+    """scn_epilogue of include/insconv_b200.h."""
+    _fields_ = [("addend", _p), ("addend_stride", _i64), ("bn_scale", _p), ("bn_shift", _p), ("bn_leakiness", _dbl),
+                ("bn_out", _p), ("bn_out_stride", _i64), ("skip_raw", _int)]
+
+
+PROTOTYPES.update({
+    "scn_ssc_forward_ex": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, C.POINTER(Epilogue), _p, C.POINTER(_dbl)]),
+    "scn_conv_forward_ex": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, C.POINTER(Epilogue), _p,
+                                   C.POINTER(_dbl)]),
+    "scn_deconv_forward_ex": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, C.POINTER(Epilogue), _p,
+                                     C.POINTER(_dbl)]),
+})
 
 _STATUS = {n for n, (r, _) in PROTOTYPES.items() if r is _int and n not in ("scn_n_rulebook_bits", "scn_weights_packable")}
 

@@ -18,3 +18,19 @@ from .layers import (SubmanifoldConvolution, ValidConvolution, Convolution, Deco
                      InputLayer, OutputLayer)
 from .nets import UNet  # noqa: E402
 from .utils import toLongTensor, optionalTensor, set_precision, get_precision  # noqa: E402
+
+
+def set_epilogue_fusion(on):
+    """In 'fp16' precision a full frame folds BatchNorm + ReLU and the sums of residual blocks into the epilogue of
+    the convolution in front of them (default on).  Results are the same to rounding; off runs every module as a
+    kernel of its own."""
+    from . import containers
+    containers.fuse_epilogues[0] = bool(on)
+
+
+def set_incremental_state(on):
+    """Full frames keep the state that reference-style incremental frames (increment=True) read later (default on).
+    Off is for pure full-frame inference: a convolution whose output only feeds a BatchNorm fused into its epilogue then
+    stores the normalised fp16 rows alone; an incremental frame after such a full frame raises."""
+    from . import containers
+    containers.keep_state[0] = bool(on)

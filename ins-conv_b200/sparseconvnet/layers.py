@@ -77,6 +77,44 @@ def takes_half_rows(module):
         not hasattr(module, "bias")
 
 
+def bn_affine(bn):
+    """(scale, shift) with which an inference BatchNorm is y = x * scale + shift: scale = gamma / sqrt(var + eps),
+    shift = beta - mean * scale.  Made once per version of the module's parameters and statistics."""
+    w, b = bn._parameters.get("weight"), bn._parameters.get("bias")
+    m, v = bn._buffers["running_mean"], bn._buffers["running_var"]
+    key = (m._version, v._version, m.data_ptr(), v.data_ptr(), None if w is None else (w._version, w.data_ptr()),
+           None if b is None else (b._version, b.data_ptr()))
+    c = bn.__dict__.get("_affine_cache")
+    if c is not None and c[0] == key:
+        return c[1], c[2]
+    with torch.no_grad():
+        scale = torch.rsqrt(v + bn.eps)
+        if w is not None:
+            scale = scale * w
+        shift = -m * scale
+        if b is not None:
+            shift = shift + b
+    bn.__dict__["_affine_cache"] = (key, scale.contiguous(), shift.contiguous())
+    return bn.__dict__["_affine_cache"][1:]
+
+
+def _fused_bn_args(module, fuse_bn, features):
+    """Arguments for a convolution whose epilogue also applies `fuse_bn` (the BatchNorm + ReLU behind it) and writes
+    the result as fp16 rows: possible when the convolution itself reads fp16 rows (its kernels carry that epilogue)."""
+    if fuse_bn is None or features.dtype != torch.float16 or not takes_half_rows(module):
+        return None
+    scale, shift = bn_affine(fuse_bn)
+    return scale, shift, float(fuse_bn.leakiness), features.new_empty(0, dtype=torch.float16)
+
+
+def _finish_fused(conv_out, fuse_bn, bn_rows):
+    """What BatchNormalization.forward would have done: the tensor it returns and the state it keeps."""
+    normed = conv_out.like(bn_rows)
+    _keep(fuse_bn, save_output=normed, save_input=conv_out)
+    conv_out.bn_ready = (fuse_bn, normed)
+    return conv_out
+
+
 _wide_rows = {}  # id(fp16 tensor) -> (weak reference to it, its fp32 copy)
 
 
@@ -118,23 +156,27 @@ class SubmanifoldConvolution(Module):
         if bias:
             self.bias = Parameter(torch.zeros(nOut))
 
-    def forward(self, input, increment=False, addend=None):
-        """addend (full frames only, no bias): features [nActive, nOut] added to the result in the kernel's epilogue.
-        A Sequential that used it for ConcatTable(shortcut, branch) + AddTable measured 1 % slower per frame than the
-        separate, fully coalesced addition (the epilogue reads the addend in 32-byte pieces), so the containers do
-        not; the argument stays for callers that want the sum without a temporary."""
+    def forward(self, input, increment=False, addend=None, fuse_bn=None, raw_needed=True):
+        """Full frames only: addend (no bias) = features [nActive, nOut] added to the result in the kernel's epilogue
+        (the residual sum of a ResNet block); fuse_bn = the BatchNormalization module that consumes this output: when
+        this convolution reads fp16 rows, its epilogue also writes fuse_bn's result as fp16 rows (picked up by that
+        module without a kernel of its own); raw_needed = False: nothing else reads the fp32 result, it is not stored."""
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, self.nOut, input)
         out = input.features.new_empty(0, dtype=torch.float32)
         if not _residual(input, increment):
+            fused = _fused_bn_args(self, fuse_bn, input.features)
+            skip_raw = fused is not None and not raw_needed
             madds = SCN.SubmanifoldConvolution_updateOutput(
                 input.spatial_size, self.filter_size, input.metadata, input.features, out, self._parameters["weight"],
                 optionalTensor(self, "bias"), self.dilated_rate, _packed_for(self, input.features),
-                _NONE if addend is None else addend)
+                _NONE if addend is None else addend, *(fused if fused else (_NONE, _NONE, 0.0, _NONE)), skip_raw)
             _keep(self, save_meta=input.metadata, save_input_feats=input.features)
-        else:
-            madds = SCN.Incre_SubmanifoldConvolution_updateOutput(
-                input.spatial_size, self.filter_size, input.metadata, input.features, out, self._parameters["weight"],
-                optionalTensor(self, "bias"), self.save_meta, _f32(self, self.save_input_feats), _packed(self))
+            _count(madds, out)
+            res = input.like(out)
+            return _finish_fused(res, fuse_bn, fused[3]) if fused else res
+        madds = SCN.Incre_SubmanifoldConvolution_updateOutput(
+            input.spatial_size, self.filter_size, input.metadata, input.features, out, self._parameters["weight"],
+            optionalTensor(self, "bias"), self.save_meta, _f32(self, self.save_input_feats), _packed(self))
         _count(madds, out)
         return input.like(out)
 
@@ -162,17 +204,22 @@ class _Strided(Module):
 
 
 class Convolution(_Strided):
-    def forward(self, input, increment=False):
+    def forward(self, input, increment=False, fuse_bn=None):
+        """fuse_bn: as for SubmanifoldConvolution (full frames, fp16 rows in)."""
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn
         out_size = torch.div(input.spatial_size - self.filter_size, self.filter_stride, rounding_mode="floor") + 1
         assert ((out_size - 1) * self.filter_stride + self.filter_size == input.spatial_size).all(), \
             (input.spatial_size, out_size, self.filter_size, self.filter_stride)
         out = input.features.new_empty(0, dtype=torch.float32)
-        op = SCN.Incre_Convolution_updateOutput if _residual(input, increment) else SCN.Convolution_updateOutput
+        residual = _residual(input, increment)
+        fused = None if residual else _fused_bn_args(self, fuse_bn, input.features)
+        op = SCN.Incre_Convolution_updateOutput if residual else SCN.Convolution_updateOutput
+        extra = () if residual else (fused if fused else (_NONE, _NONE, 0.0, _NONE)) + (False,)
         madds = op(input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                   out, self._parameters["weight"], optionalTensor(self, "bias"), _packed_for(self, input.features))
+                   out, self._parameters["weight"], optionalTensor(self, "bias"), _packed_for(self, input.features), *extra)
         _count(madds, out)
-        return input.like(out, out_size)
+        res = input.like(out, out_size)
+        return _finish_fused(res, fuse_bn, fused[3]) if fused else res
 
     def input_spatial_size(self, out_size):
         return (out_size - 1) * self.filter_stride + self.filter_size
@@ -226,6 +273,9 @@ class BatchNormalization(Module):
         assert input.features.nelement() == 0 or input.features.size(1) == self.nPlanes, \
             (self.nPlanes, input.features.shape)
         residual = _residual(input, increment)
+        ready = input.bn_ready
+        if ready is not None and ready[0] is self and not residual and not self.training:
+            return ready[1]  # the convolution in front of this module already wrote this module's result (and state)
         half_rows = half_rows and not self.training and not residual and self.nPlanes % 8 == 0
         feats = input.features
         out = feats.new_empty(0, dtype=torch.float16 if half_rows else torch.float32)
@@ -321,18 +371,15 @@ class InputLayer(Module):
             feats = feats.to(self.device if self.device else "cuda")
         feats = feats.float()
         output = SparseConvNetTensor(metadata=Metadata(self.dimension), spatial_size=self.spatial_size)
-        # What this network asked of its previous frame's metadata beyond the input scale (neighbour maps, stride-2
-        # levels) is built by this frame's input layer right away, before feature kernels are queued (a grid build
-        # ends with a host round trip).  Kept per InputLayer, i.e. per network.
-        last = self.__dict__.get("_last_meta")
+        # The previous frame's metadata hands on what this network asked of it beyond the input scale (neighbour maps,
+        # stride-2 levels: built by this frame's input layer right away, before feature kernels are queued) and the
+        # bounding box it measured (this frame's grid is laid out for it without a round trip to measure its own).
+        # Kept per InputLayer, i.e. per network; full and incremental frames each inherit from their own kind.
+        kind = "_last_meta_inc" if (increment and increment != "exact") else "_last_meta"
+        last = self.__dict__.get(kind)
         if last is not None:
-            used = last.buildUsed()
-            ahead = self.__dict__.get("_ahead", (0, 0))
-            _keep(self, _ahead=(max(ahead[0], used[0]), max(ahead[1], used[1])))
-        ahead = self.__dict__.get("_ahead")
-        if ahead is not None:
-            output.metadata.setBuildAhead(*ahead)
-        _keep(self, _last_meta=output.metadata)
+            output.metadata.inherit(last)
+        self.__dict__[kind] = output.metadata
         out = feats.new_empty(0)
         if increment == "exact":
             assert self.mode == 4, "the exact incremental mode keeps per-voxel means (InputLayer mode 4)"

@@ -11,6 +11,9 @@ class SparseConvNetTensor(object):
         # layers downstream run their full-frame path; new_points = (first, count) of the frame's own points
         self.recompute_all = recompute_all
         self.new_points = new_points
+        # (BatchNormalization module, its result on these features) when the convolution that made the features
+        # also formed that module's output in its epilogue; not carried over by like()
+        self.bn_ready = None
 
     def get_spatial_locations(self, spatial_size=None):
         """LongTensor [nActive, 4]: x, y, z, batch index of every active site, in row order."""

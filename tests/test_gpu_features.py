@@ -274,6 +274,73 @@ def test_f16_wide_layers_on_small_grids(cuda, n_in, n_out):
     assert float((out.cpu() - want).abs().max()) / float(want.abs().max()) < 3e-3
 
 
+@pytest.mark.parametrize("n_in,n_out,scene", [(32, 32, "c1"), (64, 64, "c1"), (32, 64, "c1"), (96, 96, "spheres"), (160, 128, "spheres"),
+                                              (128, 128, "c1"), (96, 160, "tiny"), (224, 224, "tiny")])
+def test_f16_fused_epilogue_residual_sum_and_batchnorm(cuda, n_in, n_out, scene):
+    """scn_ssc/conv_forward_ex: the residual sum and the BatchNorm + ReLU behind a convolution formed in its epilogue, in
+    every fp16 kernel (warp-level 32/64 planes, slab kernel on a few thousand rows, tcgen05 kernel on many rows and --
+    with split reductions -- on a few hundred).  The fp32 result must equal the plain call's plus the addend, the fp16
+    rows must be the BatchNorm of exactly that result, and skip_raw must leave the fp16 rows unchanged."""
+    import ctypes as C
+    if scene == "c1":
+        c = synth.boxes_and_spheres(0)
+    elif scene == "spheres":
+        c = np.concatenate([synth.sphere_surface((30, 30, 30), 11), synth.sphere_surface((60, 50, 40), 8)], 0)
+    else:
+        c = synth.sphere_surface((20, 20, 20), 4)
+    m = cabi.Metadata()
+    n = m.input_layer_build(128, torch.from_numpy(c).to(cuda), mode=4)
+    rng = np.random.RandomState(n_in + 7 * n_out)
+    stream = torch.cuda.current_stream().cuda_stream
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(cuda)
+    h = t(np.maximum(rng.randn(n, n_in), 0)).half()
+    addend = t(rng.randn(n, n_out))
+    scale, shift = t(rng.uniform(0.5, 1.5, n_out)), t(rng.randn(n_out))
+    fl = C.c_double(0)
+
+    def packed(w):
+        dw = t(w)
+        p = torch.empty(cabi.lib().scn_packed_size_f16(w.shape[0], n_in, n_out), dtype=torch.float16, device=cuda)
+        cabi.call("scn_pack_weights_f16", cabi.ptr(dw), w.shape[0], n_in, n_out, cabi.ptr(p), stream)
+        return p
+
+    def run(fn, sizes, rows_in, rows_out, pw, with_addend, leak):
+        plain = torch.empty(rows_out, n_out, dtype=torch.float32, device=cuda)
+        cabi.call(fn, m.h, *sizes, cabi.ptr(rows_in), n_in, cabi.ptr(plain), n_out, cabi.ptr(pw), None, n_in, n_out, cabi.PREC_F16,
+                  stream, C.byref(fl))
+        add = addend[:rows_out].contiguous() if with_addend else None
+        raw = torch.full((rows_out, n_out), float("nan"), dtype=torch.float32, device=cuda)
+        rows = torch.zeros(rows_out, n_out, dtype=torch.float16, device=cuda)
+        e = cabi.Epilogue(cabi.ptr(add), n_out, cabi.ptr(scale), cabi.ptr(shift), leak, cabi.ptr(rows), n_out, 0)
+        cabi.call(fn + "_ex", m.h, *sizes, cabi.ptr(rows_in), n_in, cabi.ptr(raw), n_out, cabi.ptr(pw), None, n_in, n_out,
+                  cabi.PREC_F16, C.byref(e), stream, C.byref(fl))
+        want_raw = plain + add if with_addend else plain
+        assert torch.equal(raw, want_raw) or float((raw - want_raw).abs().max()) <= 1e-6 * float(want_raw.abs().max())
+        y = raw * scale + shift
+        y = torch.where(y > 0, y, y * leak).clamp(-65504, 65504)
+        assert float((rows.float() - y).abs().max()) <= 2e-3 * max(float(y.abs().max()), 1.0)  # half a unit in the last fp16 place
+        rows2 = torch.zeros_like(rows)
+        e2 = cabi.Epilogue(cabi.ptr(add), n_out, cabi.ptr(scale), cabi.ptr(shift), leak, cabi.ptr(rows2), n_out, 1)
+        cabi.call(fn + "_ex", m.h, *sizes, cabi.ptr(rows_in), n_in, None, n_out, cabi.ptr(pw), None, n_in, n_out, cabi.PREC_F16,
+                  C.byref(e2), stream, C.byref(fl))
+        assert torch.equal(rows, rows2)
+
+    run("scn_ssc_forward", (cabi.size3(128),), h, n, packed(synth.kaiming_uniform(rng, 27, n_in, n_out)), True, 0.0)
+    run("scn_ssc_forward", (cabi.size3(128),), h, n, packed(synth.kaiming_uniform(rng, 27, n_in, n_out)), False, 0.333)
+    n_cc = C.c_int64(0)
+    cabi.call("scn_conv_prepare", m.h, cabi.size3(128), cabi.size3(64), stream, C.byref(n_cc))
+    run("scn_conv_forward", (cabi.size3(128), cabi.size3(64)), h, int(n_cc.value), packed(synth.kaiming_uniform(rng, 8, n_in, n_out)),
+        False, 0.0)
+    # refused where no kernel carries the epilogue: fp32 rows
+    e = cabi.Epilogue(None, 0, cabi.ptr(scale), cabi.ptr(shift), 0.0, cabi.ptr(torch.zeros(n, n_out, dtype=torch.float16, device=cuda)),
+                      n_out, 0)
+    with pytest.raises(cabi.ScnError):
+        cabi.call("scn_ssc_forward_ex", m.h, cabi.size3(128), cabi.ptr(h.float()), n_in, cabi.ptr(torch.empty(n, n_out, device=cuda)),
+                  n_out, cabi.ptr(t(synth.kaiming_uniform(rng, 27, n_in, n_out))), None, n_in, n_out, cabi.PREC_TF32, C.byref(e), stream,
+                  C.byref(fl))
+    cabi.check_errors()
+
+
 def test_conv_deconv_nin_tf32(cuda):
     m, g = _scene(cuda, 1)
     rng = np.random.RandomState(17)

@@ -142,10 +142,6 @@ def test_errors_are_reported_not_fatal(cuda):
         m.input_layer_build(64, torch.tensor([[1, 2, 3]], device=cuda), mode=1)
     with pytest.raises(cabi.ScnError):
         m.ssc_rulebook(64)  # no grid
-    # a scene whose bounding box exceeds the build limit is refused with a clear error
-    with pytest.raises(cabi.ScnError) as e:
-        m.input_layer_build(65536, torch.tensor([[0, 0, 0], [60000, 60000, 60000]], device=cuda), mode=4)
-    assert e.value.code == -4
     # the device is still usable afterwards
     n = m.input_layer_build(64, torch.tensor([[1, 2, 3]], device=cuda), mode=4)
     assert n == 1
@@ -192,3 +188,96 @@ def test_build_ahead_changes_when_not_what(cuda):
         assert len(a) == len(b)
         for x, y in zip(a, b):
             assert np.array_equal(x, y)
+
+
+def _distant_clusters(seed, span):
+    """Two clusters of surfaces at opposite corners of a span^3 volume (a bounding box far beyond what a ranking bitmap
+    is laid out for), with duplicates, in two batch entries."""
+    rng = np.random.RandomState(seed)
+    a = synth.boxes_and_spheres(seed, grid=64) + 1
+    b = synth.boxes_and_spheres(seed + 1, grid=64) + (span - 70)
+    c = np.concatenate([a, b, a[rng.randint(0, a.shape[0], 500)]], 0)
+    c = c[rng.permutation(c.shape[0])]
+    batch = np.sort(rng.randint(0, 2, size=(c.shape[0], 1)), 0)
+    return np.concatenate([c, batch], 1)
+
+
+@pytest.mark.parametrize("span", [4096, 65534])
+def test_scene_spanning_the_whole_volume_builds_and_matches_the_oracle(cuda, span):
+    """A scene that spans the 4096^3 volume model.py declares (and one that spans the whole key range): ranked by
+    sorting, looked up through the open-addressing table; sites, input rules, hash contents, 3x3x3 and 2x2x2 rulebooks at
+    the input scale and down the coarse scales, and coordinate queries, all bit-exact."""
+    cb = _distant_clusters(7, span)
+    size = 1 << 16
+    for mode in (3, 4):
+        m, n = _build(cb, size, cuda, mode=mode)
+        g = O.Grid(cb)
+        assert g.n < cb.shape[0]
+        _check_grid(m, n, g, size)
+        _check_rules(m.ssc_rulebook(size), O.ssc_rules(g))
+        fine = g
+        for level in range(1, 5):  # coarse scales: sorted while the box is still too large, bitmaps once it fits
+            coarse, crules = O.conv2_rules(fine)
+            _check_rules(m.conv_rulebook(size >> (level - 1), size >> level), crules)
+            np.testing.assert_array_equal(m.spatial_locations(size >> level), coarse.coords)
+            _check_rules(m.ssc_rulebook(size >> level), O.ssc_rules(coarse))
+            fine = coarse
+    rng = np.random.RandomState(1)
+    q = np.concatenate([cb[rng.randint(0, cb.shape[0], 3000)], np.concatenate([rng.randint(0, span, size=(3000, 3)),
+                                                                              rng.randint(0, 2, size=(3000, 1))], 1)], 0)
+    soa = torch.from_numpy(np.ascontiguousarray(q.T.astype(np.int32))).to(cuda)
+    np.testing.assert_array_equal(m.query(size, soa).cpu().numpy(), g.lookup(q))
+
+
+def test_spread_out_scene_with_build_ahead_and_incremental_maps(cuda):
+    """The same kind of scene through the build-ahead chain (coarse scales built by the input layer) and as the saved
+    frame of an incremental update: pre-exist map and incremental rulebook bit-exact."""
+    cb = _distant_clusters(9, 4096)[:, :3]
+    rng = np.random.RandomState(2)
+    new = np.concatenate([cb[rng.randint(0, cb.shape[0], 400)], cb[rng.randint(0, cb.shape[0], 400)] + rng.randint(-1, 2, size=(400, 3)),
+                          synth.sphere_surface([2000, 2000, 2000], 6)], 0)
+    new = np.clip(new, 0, 65534)
+    try:
+        cabi.call("scn_set_build_ahead", 1, 4)
+        pre, _ = _build(cb, 4096, cuda)
+        m, _ = _build(new, 4096, cuda)
+    finally:
+        cabi.call("scn_set_build_ahead", -1, -1)
+    pg, g = O.Grid(cb), O.Grid(new)
+    np.testing.assert_array_equal(m.spatial_locations(4096), g.coords)
+    np.testing.assert_array_equal(m.pre_exist(pre, 4096), O.pre_exist(g, pg))
+    _check_rules(m.incre_ssc_rulebook(pre, 4096), O.incre_ssc_rules(g, pg))
+    fine, pfine = g, pg
+    for level in range(1, 5):
+        coarse, crules = O.conv2_rules(fine)
+        pcoarse, _ = O.conv2_rules(pfine)
+        _check_rules(m.conv_rulebook(4096 >> (level - 1), 4096 >> level), crules)
+        np.testing.assert_array_equal(m.pre_exist(pre, 4096 >> level), O.pre_exist(coarse, pcoarse))
+        _check_rules(m.incre_ssc_rulebook(pre, 4096 >> level), O.incre_ssc_rules(coarse, pcoarse))
+        fine, pfine = coarse, pcoarse
+
+
+def test_rebuilding_on_one_metadata_with_a_scene_that_leaves_the_previous_box(cuda):
+    """A metadata object that is built on again lays its bitmap out for the previous scene's box (no round trip to
+    measure); a scene that does not fit is built again with its own box.  Same results either way."""
+    a = synth.boxes_and_spheres(1, grid=96) + 20
+    m = cabi.Metadata()
+    for shift in ((0, 0, 0), (3, -2, 5), (60, 0, 0), (-19, -19, -19), (300, 500, 10), (0, 0, 0)):
+        c = a + np.array(shift)
+        rng = np.random.RandomState(abs(shift[0]) + 1)
+        c = np.concatenate([c, c[rng.randint(0, c.shape[0], 300)]], 0)[rng.permutation(c.shape[0] + 300)]
+        n = m.input_layer_build(1024, torch.from_numpy(c).to(cuda), mode=4)
+        g = O.Grid(c)
+        _check_grid(m, n, g, 1024)
+        _check_rules(m.ssc_rulebook(1024), O.ssc_rules(g))
+        coarse, crules = O.conv2_rules(g)
+        _check_rules(m.conv_rulebook(1024, 512), crules)
+        np.testing.assert_array_equal(m.spatial_locations(512), coarse.coords)
+    # an out-of-range coordinate on a hinted build is still an error, and the next build works
+    bad = a.copy()
+    bad[5] = [70000, 1, 1]
+    with pytest.raises(cabi.ScnError) as e:
+        m.input_layer_build(1024, torch.from_numpy(bad).to(cuda), mode=4)
+    assert e.value.code == -3
+    n = m.input_layer_build(1024, torch.from_numpy(a).to(cuda), mode=4)
+    _check_grid(m, n, O.Grid(a), 1024)

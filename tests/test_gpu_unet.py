@@ -226,3 +226,50 @@ def test_config4_sweep_frames(cuda):
         all_c, all_f = np.concatenate([all_c, new_c], 0), np.concatenate([all_f, new_f], 0)
         want = fresh([dev(all_c), dev(all_f)])[-new_c.shape[0]:]
         assert rel_err(exact, want) <= 1e-4
+
+
+def test_fused_epilogues_change_when_things_are_computed_not_what(cuda):
+    """'fp16' precision: with BatchNorm + ReLU and the residual sums folded into the convolutions' epilogues (the default)
+    the network launches far fewer kernels; the full frame, the state it keeps and a reference-style incremental frame
+    computed from that state agree with the unfused run to fp16 rounding, and without kept state the full frame is the
+    same again while an incremental frame is refused."""
+    import sparseconvnet as scn
+    torch.manual_seed(3)
+    model = small_unet(scn, [32, 64, 96, 128]).eval()
+    randomize_bn(model, 5)
+    model = model.to(cuda)
+    c = synth.boxes_and_spheres(0)
+    f = synth.rgb(0, c.shape[0])
+    nf = synth.next_frame(c, f, 0)
+    t = lambda a: torch.from_numpy(a).to(cuda)
+    want, runner = run_oracle(model.cpu(), [torch.from_numpy(c), torch.from_numpy(f)])
+    want_inc, _ = run_oracle(model, [torch.from_numpy(nf["new_coords"]), torch.from_numpy(nf["new_feats"])], True, runner)
+    model = model.to(cuda)
+    scn.set_precision("fp16")
+    try:
+        results = {}
+        for fused in (False, True):
+            scn.set_epilogue_fusion(fused)
+            with torch.no_grad():
+                model([t(c), t(f)])  # first call: weight packs
+                l0 = scn.SCN.launch_count()
+                full = model([t(c), t(f)])
+                launches = scn.SCN.launch_count() - l0
+                inc = model([t(nf["new_coords"]), t(nf["new_feats"])], True)
+            scn.SCN.check_errors()
+            results[fused] = (full, inc, launches)
+        (full0, inc0, l0), (full1, inc1, l1) = results[False], results[True]
+        assert l1 <= l0 - 20, (l0, l1)  # the fused frame runs without most BatchNorm kernels
+        assert rel_err(full1, full0) <= 5e-3 and rel_err(inc1, inc0) <= 5e-3
+        assert rel_err(full1, want) <= 5e-2 and rel_err(inc1, want_inc) <= 5e-2
+        scn.set_incremental_state(False)
+        with torch.no_grad():
+            full2 = model([t(c), t(f)])
+            assert rel_err(full2, full1) <= 1e-6
+            with pytest.raises(RuntimeError):
+                model([t(nf["new_coords"]), t(nf["new_feats"])], True)
+        torch.cuda.synchronize()
+    finally:
+        scn.set_incremental_state(True)
+        scn.set_epilogue_fusion(True)
+        scn.set_precision("fp32")
