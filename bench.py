@@ -370,6 +370,19 @@ def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
         cabi.call("scn_set_build_ahead", 0, 0)  # the hash build alone: input scale, no neighbour map
         t, n = median_build()
         t_table, _ = median_build(True)
+        # coordinate queries through the open-addressing table (teams of four lanes per probe sequence): every site's own
+        # coordinates plus as many shifted by one voxel (about half of which miss)
+        soa = torch.from_numpy(np.ascontiguousarray(np.concatenate([c4, c4 + np.array([1, 0, 0, 0])], 0).T.astype(np.int32))).to(dev)
+        qts = []
+        for i in range(warmup + steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            m.query(size, soa)
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                qts.append(e0.elapsed_time(e1) * 1e-3)
+        t_query = sorted(qts)[len(qts) // 2]
         # the 3x3x3 rulebook (27 lookups per site in the ranking structure) of that grid, built on first request
         counts = np.zeros(27, dtype=np.int64)
         rts = []
@@ -395,6 +408,7 @@ def hash_bench(dev, steps, warmup, sizes=("c1", "room", "building")):
         out.append({"scene": name, "points": int(c4.shape[0]), "sites": int(n), "us": t * 1e6,
                     "points_per_s": c4.shape[0] / t, "GBps": byts / t / 1e9,
                     "with_open_addressing_table": {"us": t_table * 1e6, "GBps": (byts + 8.0 * cap) / t_table / 1e9},
+                    "table_query": {"queries": int(soa.shape[1]), "us": t_query * 1e6, "queries_per_s": soa.shape[1] / t_query},
                     "us_with_6_coarse_scales_and_all_maps": t_all * 1e6,
                     # algorithmic bytes of the rulebook build: coordinates in, occupied bitmap words and their
                     # prefixes read once (12 bytes per site at most), pairs out

@@ -1075,7 +1075,7 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
     // warp is longer than the split reduction plus its second launch (measured on 60- and 230-row levels).  Measured
     // with 96 planes: 4.4k rows 17.8 us against 25.6 us, 16k rows 32.0 against 32.4 (and one launch instead of two).
     const long long slab_rows = 16384;
-    if (n_out >= 512 && n_out <= slab_rows && warp_slab_f16_shape(K, Cin, Cout))
+    if (n_out <= slab_rows && warp_slab_f16_shape(K, Cin, Cout))
       return gather_mma_slab_f16(in, in_stride, map, K, n_out, static_cast<const __half *>(Wp) + K * Cout * padded_planes(Cin), bias,
                                  out, out_stride, Cin, Cout, init, init_stride, s, epi);
   }

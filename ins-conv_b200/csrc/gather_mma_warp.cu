@@ -435,6 +435,95 @@ k_gather_mma_f16_slab(const __half *__restrict__ in, long long in_stride, const 
                      init ? init + 32 * slab : nullptr, init_stride, g, t, epi, 32 * slab);
 }
 
+// The same tile (16 rows x a slab of 32 output planes) with its reduction SHARED by KS warps, for grids of a few
+// thousand rows and fewer: there a warp that runs all offsets of its tile alone spends its time waiting for one gather
+// after the other (27 dependent round trips to L2, 20-25 us per layer whatever the size) while most of the GPU idles.
+// Here a block of 8 warps holds 8 / KS tiles; the KS warps of a tile take every KS-th of the tile's occupied offsets,
+// park their partial accumulators in shared memory, and the first of them adds the parts in a fixed order (warp 1,
+// 2, ... : deterministic) and runs the epilogue.
+constexpr int kSplitWarps = 8;
+template <int C32, int KS>
+__global__ void __launch_bounds__(kSplitWarps * 32)
+k_gather_mma_f16_slab_split(const __half *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
+                            const uint4 *__restrict__ Wp, int Cout, const float *__restrict__ bias, float *out, long long out_stride,
+                            const float *init, long long init_stride, const EpiBn epi) {
+  constexpr int NTR = 2, ROWS = 16, CIN = C32 * 32, TILES = kSplitWarps / KS;
+  __shared__ int s_map[kSplitWarps][kMaxK * ROWS];
+  __shared__ float s_part[kSplitWarps][16][32];  // [warp][accumulator element][lane]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int tile_local = warp / KS, split = warp % KS;
+  const long long row0 = ((long long)blockIdx.x * TILES + tile_local) * ROWS;
+  const bool live = row0 < n_out;
+  const int slab = blockIdx.y, mtc_total = Cout >> 4;
+  float acc[2][NTR][4];
+#pragma unroll
+  for (int m = 0; m < 2; ++m)
+#pragma unroll
+    for (int n = 0; n < NTR; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
+  if (live) {
+    int *mp = s_map[warp];
+    MapRegs<ROWS> regs;
+    load_map<ROWS>(regs, row0, map, K, n_out, lane);
+    const unsigned int all = publish_map<ROWS>(regs, mp, K, lane);
+    // this warp's share: every KS-th occupied offset, counted from its own index
+    unsigned int mask = 0;
+    int ord = 0;
+    for (unsigned int m = all; m; m &= m - 1, ++ord)
+      if (ord % KS == split) mask |= m & (0u - m);
+    const int WK = C32 * mtc_total * 2 * 32;  // uint4 per offset
+    const __half *in_t = in + 8 * t;
+    const uint4 *wl = Wp + lane + (2 * slab) * 2 * 32;
+    if (mask) {
+      FragH<CIN, NTR> f0, f1;
+      int k0 = __ffs(mask) - 1;
+      mask &= mask - 1;
+      load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
+      while (true) {
+        int k1 = -1;
+        if (mask) {
+          k1 = __ffs(mask) - 1;
+          mask &= mask - 1;
+          load_rows_h<CIN, NTR>(f1, mp + k1 * ROWS, in_t, in_stride, g);
+        }
+        mma_rows_slab<C32, NTR>(acc, f0, wl + (long long)k0 * WK, mtc_total);
+        if (k1 < 0) break;
+        k0 = -1;
+        if (mask) {
+          k0 = __ffs(mask) - 1;
+          mask &= mask - 1;
+          load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
+        }
+        mma_rows_slab<C32, NTR>(acc, f1, wl + (long long)k1 * WK, mtc_total);
+        if (k0 < 0) break;
+      }
+    }
+    if (split != 0) {
+#pragma unroll
+      for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int n = 0; n < NTR; ++n)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) s_part[warp][(m * NTR + n) * 4 + i][lane] = acc[m][n][i];
+    }
+  }
+  __syncthreads();
+  if (live && split == 0) {
+#pragma unroll 1
+    for (int o = 1; o < KS; ++o)
+#pragma unroll
+      for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int n = 0; n < NTR; ++n)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[m][n][i] += s_part[warp + o][(m * NTR + n) * 4 + i][lane];
+    store_acc<32, NTR>(acc, row0, n_out, bias ? bias + 32 * slab : nullptr, out + 32 * slab, out_stride,
+                       init ? init + 32 * slab : nullptr, init_stride, g, t, epi, 32 * slab);
+  }
+}
+
 // W [K][n_in][n_out] fp32 -> fp16 fragments [K][n_in/32][n_out/16][2][lane][8]: half e of (k, c, m, j, lane = 4g + t)
 // is W[k][32c + 8t + 4j + 2(e >> 2) + (e & 1)][16m + g + 8((e >> 1) & 1)]
 __global__ void k_pack_weights_f16(const float *__restrict__ W, __half *__restrict__ Wp, int Cin, int Cout, long long total) {
@@ -639,6 +728,29 @@ int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, i
   const __half *inh = static_cast<const __half *>(in);
   const uint4 *W4 = static_cast<const uint4 *>(Wp);
   const long long tiles = (n_out + 15) / 16;
+  // few rows: share a tile's reduction among 2, 4 or 8 warps (so that about as many warps as a large grid has are in
+  // flight); many rows: one warp per tile
+  const int ks = n_out <= 1024 ? 8 : n_out <= 3072 ? 4 : n_out <= 12288 ? 2 : 1;
+  if (ks > 1) {
+    const int tiles_per_block = kSplitWarps / ks;
+    const dim3 grid((unsigned)((tiles + tiles_per_block - 1) / tiles_per_block), (unsigned)(Cout / 32));
+#define SCN_SPLIT_LAUNCH(C32, KS)                                                                                       \
+  k_gather_mma_f16_slab_split<C32, KS><<<grid, kSplitWarps * 32, 0, s>>>(inh, in_stride, map, K, n_out, W4, (int)Cout, bias, out, \
+                                                                         out_stride, init, init_stride, e)
+#define SCN_SPLIT_C32(KS)                     \
+  switch ((int)(Cin / 32)) {                  \
+    case 3: SCN_SPLIT_LAUNCH(3, KS); break;   \
+    case 4: SCN_SPLIT_LAUNCH(4, KS); break;   \
+    case 5: SCN_SPLIT_LAUNCH(5, KS); break;   \
+    case 6: SCN_SPLIT_LAUNCH(6, KS); break;   \
+    default: SCN_SPLIT_LAUNCH(7, KS); break;  \
+  }
+    if (ks == 8) { SCN_SPLIT_C32(8) } else if (ks == 4) { SCN_SPLIT_C32(4) } else { SCN_SPLIT_C32(2) }
+#undef SCN_SPLIT_C32
+#undef SCN_SPLIT_LAUNCH
+    SCN_LAUNCHED();
+    return SCN_OK;
+  }
   const dim3 grid((unsigned)((tiles + kWarps - 1) / kWarps), (unsigned)(Cout / 32));
 #define SCN_SLAB_LAUNCH(C32)                                                                                          \
   k_gather_mma_f16_slab<C32, 2><<<grid, kWarps * 32, 0, s>>>(inh, in_stride, map, K, n_out, W4, (int)Cout, bias, out, \
