@@ -770,7 +770,7 @@ def main():
         pct = lambda v, q: float(sorted(v)[min(len(v) - 1, int(q * len(v)))])
         stats = lambda v: {"mean": sum(v) / len(v), "p50": pct(v, 0.5), "p99": pct(v, 0.99)}
         sweep = {"frames": n_frames,
-                 "scene_points_at_end": int(model.sparseModel[0].scene_coords.shape[0]),
+                 "scene_voxels_at_end": int(model.sparseModel[0].scene_coords.shape[0]),
                  "reference_ms": stats(lat["reference"]),
                  "full_recompute_every_10th_frame_ms": stats(lat["full"]),
                  "exact_ms": stats(lat["exact"]),

@@ -152,6 +152,11 @@ SCN_API int64_t scn_input_layer_n_points(scn_metadata *m);
 /* Number of sites of the input scale (rules[0][3]; Metadata::inputNActive, Metadata/Metadata.h:278), -1 without an
  * input layer. */
 SCN_API int64_t scn_metadata_input_n_active(scn_metadata *m);
+/* States how many points each site of the input scale stands for (device int32 [n_active]) when that is not the number
+ * of input rows that fell into it: a caller that keeps a scene as per-voxel sums hands in one row per voxel.  Only the
+ * incremental input layer reads it, on the saved frame (the weight of the saved mean, CUDA/IOLayers.cu:88-92 takes it
+ * from the saved rulebook's row).  No counterpart in the reference. */
+SCN_API int scn_input_layer_set_site_counts(scn_metadata *m, const int32_t *counts, int64_t n, void *stream);
 /* The InputLayer rulebook in the reference's padded layout (CUDA/IOLayers.cu:7-12):
  * header HOST int32[4] = {mode, maxActive, nIn, nOut}; rows HOST int32 [nOut, 1+maxActive]
  * = {count, point indices ascending..., zero padding}.  Call with rows == NULL to get the header. */

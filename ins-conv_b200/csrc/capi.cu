@@ -432,6 +432,16 @@ int64_t scn_metadata_input_n_active(scn_metadata *m) {
   if (input_grid(m, &g) != SCN_OK) return -1;
   return g->n;
 }
+int scn_input_layer_set_site_counts(scn_metadata *m, const int32_t *counts, int64_t n, void *stream) {
+  Grid *g;
+  SCN_TRY(input_grid(m, &g));
+  if (n != g->n || (n && !counts)) return fail(SCN_E_INVALID, "one count per site of the input scale is expected");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (n == 0) return SCN_OK;
+  if (!g->site_count) SCN_TRY(dev_alloc_t(&g->site_count, (size_t)n, s));
+  SCN_CUDA(cudaMemcpyAsync(g->site_count, counts, (size_t)n * 4, cudaMemcpyDeviceToDevice, s));
+  return SCN_OK;
+}
 int scn_input_layer_rules(scn_metadata *m, int32_t header_host[4], int32_t *rows_host, void *stream) {
   Grid *g;
   SCN_TRY(input_grid(m, &g));

@@ -399,7 +399,7 @@ int bn_forward_train(const float *in, int64_t in_stride, float *out, int64_t out
 __global__ void k_input_fwd(const float *__restrict__ in, float *__restrict__ out, long long n, int planes,
                             const int32_t *__restrict__ off, const int32_t *__restrict__ item, int average,
                             const int32_t *__restrict__ pre_exist, const int32_t *__restrict__ pre_off,
-                            const float *__restrict__ pre_out) {
+                            const float *__restrict__ pre_out, const int32_t *__restrict__ pre_count) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n * planes) return;
   const long long r = i / planes;
@@ -409,7 +409,7 @@ __global__ void k_input_fwd(const float *__restrict__ in, float *__restrict__ ou
   int pe = -1, pre_cnt = 0;
   if (pre_exist) {
     pe = pre_exist[r];
-    if (pe >= 0) pre_cnt = pre_off ? pre_off[pe + 1] - pre_off[pe] : 1;
+    if (pe >= 0) pre_cnt = pre_count ? pre_count[pe] : pre_off ? pre_off[pe + 1] - pre_off[pe] : 1;
   }
   const float mult = (average && cnt > 0) ? 1.0f / (float)(cnt + pre_cnt) : 1.0f;
   float acc = 0.f;
@@ -422,7 +422,8 @@ __global__ void k_input_fwd(const float *__restrict__ in, float *__restrict__ ou
 // writes the site's row; nothing is summed, so the order of the sources does not matter and no source list is needed.
 __global__ void k_input_fwd_unique(const float *__restrict__ in, float *__restrict__ out, long long n_src, int planes,
                                    const int32_t *__restrict__ src_row, int average, const int32_t *__restrict__ pre_exist,
-                                   const int32_t *__restrict__ pre_off, const float *__restrict__ pre_out) {
+                                   const int32_t *__restrict__ pre_off, const float *__restrict__ pre_out,
+                                   const int32_t *__restrict__ pre_count) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_src * planes) return;
   const long long p = i / planes;
@@ -431,7 +432,7 @@ __global__ void k_input_fwd_unique(const float *__restrict__ in, float *__restri
   int pe = -1, pre_cnt = 0;
   if (pre_exist) {
     pe = pre_exist[r];
-    if (pe >= 0) pre_cnt = pre_off ? pre_off[pe + 1] - pre_off[pe] : 1;
+    if (pe >= 0) pre_cnt = pre_count ? pre_count[pe] : pre_off ? pre_off[pe + 1] - pre_off[pe] : 1;
   }
   const float mult = average ? 1.0f / (float)(1 + pre_cnt) : 1.0f;
   float acc = 0.f;
@@ -462,13 +463,15 @@ int input_forward(const Grid &g, const float *in, float *out, int64_t planes, in
   if (!g.csr_off && g.n == g.n_src) {  // one source per site
     if (!g.src_row) return fail(SCN_E_STATE, "grid has no input rules");
     k_input_fwd_unique<<<blocks_for(g.n_src * planes, 256), 256, 0, s>>>(in, out, g.n_src, (int)planes, g.src_row, average, pre_exist,
-                                                                       pre ? pre->csr_off : nullptr, pre_out);
+                                                                       pre ? pre->csr_off : nullptr, pre_out,
+                                                                       pre ? pre->site_count : nullptr);
     SCN_LAUNCHED();
     return SCN_OK;
   }
   if (!g.csr_item) return fail(SCN_E_STATE, "grid has no input rules");
   k_input_fwd<<<blocks_for(g.n * planes, 256), 256, 0, s>>>(in, out, g.n, (int)planes, g.csr_off, g.csr_item, average,
-                                                          pre_exist, pre ? pre->csr_off : nullptr, pre_out);
+                                                          pre_exist, pre ? pre->csr_off : nullptr, pre_out,
+                                                          pre ? pre->site_count : nullptr);
   SCN_LAUNCHED();
   return SCN_OK;
 }

@@ -728,9 +728,12 @@ int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, i
   const __half *inh = static_cast<const __half *>(in);
   const uint4 *W4 = static_cast<const uint4 *>(Wp);
   const long long tiles = (n_out + 15) / 16;
-  // few rows: share a tile's reduction among 2, 4 or 8 warps (so that about as many warps as a large grid has are in
-  // flight); many rows: one warp per tile
-  const int ks = n_out <= 1024 ? 8 : n_out <= 3072 ? 4 : n_out <= 12288 ? 2 : 1;
+  // a few hundred rows (the two deepest levels of the UNet): a tile's reduction is shared by 8 warps, which replaces
+  // the tcgen05 kernel's split reductions and its second launch there (23 us and 18 us per layer against 24-30 us).
+  // From a thousand rows on one warp per tile is faster: sharing by 4 warps at 4k rows / 160 planes measured 46 us
+  // against 28 us, by 2 warps at 7k rows / 128 planes 26 us against 23 us -- what bounds those layers is the weight
+  // traffic from L2 (every 16-row tile reads all of its slab's weights), which more warps in flight only congest.
+  const int ks = n_out <= 1024 ? 8 : 1;
   if (ks > 1) {
     const int tiles_per_block = kSplitWarps / ks;
     const dim3 grid((unsigned)((tiles + tiles_per_block - 1) / tiles_per_block), (unsigned)(Cout / 32));

@@ -848,6 +848,7 @@ int grid_free(Grid &g, cudaStream_t s) {
   release(g.src_row);
   release(g.csr_off);
   release(g.csr_item);
+  release(g.site_count);
   release(g.nbr);
   release(g.bitmap);
   release(g.prefix);

@@ -84,6 +84,9 @@ struct Grid {
   mutable int32_t *csr_item = nullptr;  // [n_src] sources of each site, ascending; when every site has one source it is
                                         // only made on request (grid_ensure_source_lists): row -> its source
   int32_t max_active = 0;
+  // optional: how many points each site stands for, when that is not the length of its source list (a scene kept as
+  // per-voxel sums hands in one entry per voxel that stands for all the points merged into it); owned by the grid
+  int32_t *site_count = nullptr;
   // occupancy bitmap of the box in key order and the exclusive prefix sums of its word popcounts: the ranking
   // structure of the build, kept because "row of the site at (x,y,z)" = prefix[word] + popcount(bits below) answers
   // the neighbour queries of the 3x3x3 map with coherent reads instead of hash probes

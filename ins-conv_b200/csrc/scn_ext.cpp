@@ -195,6 +195,12 @@ class Metadata3 {
   void setBuildAhead(int neighbour_maps, int coarse_levels) {
     check(scn_metadata_set_build_ahead(h_, neighbour_maps, coarse_levels), "Metadata.setBuildAhead");
   }
+  void setSiteCounts(at::Tensor counts) {
+    TORCH_CHECK(counts.is_cuda() && counts.scalar_type() == at::kInt && counts.dim() == 1, "counts must be a CUDA int32 vector");
+    auto c = counts.contiguous();
+    check(scn_input_layer_set_site_counts(h_, c.data_ptr<int>(), c.numel(), (void *)c10::cuda::getCurrentCUDAStream().stream()),
+          "Metadata.setSiteCounts");
+  }
   void inherit(Metadata3 &previous) { check(scn_metadata_inherit(h_, previous.h()), "Metadata.inherit"); }
   std::pair<int, int> buildUsed() {
     int nm = 0, levels = 0;
@@ -588,7 +594,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
       .def("getNActive", &Metadata3::getNActive)
       .def("setBuildAhead", &Metadata3::setBuildAhead)
       .def("buildUsed", &Metadata3::buildUsed)
-      .def("inherit", &Metadata3::inherit);
+      .def("inherit", &Metadata3::inherit)
+      .def("setSiteCounts", &Metadata3::setSiteCounts);
   mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("dilated_rate"), pybind11::arg("packed") = none, pybind11::arg("addend") = none, pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("skip_raw") = false);
   mod.def("Convolution_updateOutput", &Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none, pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("skip_raw") = false);
   mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);

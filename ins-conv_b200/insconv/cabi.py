@@ -53,6 +53,7 @@ PROTOTYPES = {
     "scn_output_layer_forward": (_int, [_p, _p, _p, _i64, _p]),
     "scn_input_layer_n_points": (_i64, [_p]),
     "scn_metadata_input_n_active": (_i64, [_p]),
+    "scn_input_layer_set_site_counts": (_int, [_p, _p, _i64, _p]),
     "scn_input_layer_rules": (_int, [_p, _p, _p, _p]),
     "scn_ssc_rulebook": (_int, [_p, _i64p, _p, _p, _p]),
     "scn_conv_rulebook": (_int, [_p, _i64p, _i64p, _p, _p, _p]),

@@ -383,25 +383,59 @@ class InputLayer(Module):
         out = feats.new_empty(0)
         if increment == "exact":
             assert self.mode == 4, "the exact incremental mode keeps per-voxel means (InputLayer mode 4)"
+            # The kept scene is per-VOXEL state -- coordinates, feature sum, point count -- so its size is the
+            # scene's, however many frames have been merged.  The frame's points are appended to the voxel list and
+            # the input layer sums (mode 3) features and counts per site: sites of the merged scene, their sums and
+            # counts in one pass; the network sees the means.
+            scene_c, scene_s, scene_n = self._scene(feats.device)
             coords = coords.to(feats.device).long()
-            n_old = self.scene_coords.shape[0]
-            all_coords = torch.cat([self.scene_coords, coords], 0)
-            all_feats = torch.cat([self.scene_feats, feats], 0)
-            SCN.InputLayer_updateOutput(output.metadata, self.spatial_size, all_coords, all_feats, out, batch_size,
-                                        self.mode)
-            output.features = out
+            if coords.shape[1] != scene_c.shape[1]:  # batch column on one side only: batch 0
+                pad = lambda c: c if c.shape[1] == 4 else torch.cat([c, c.new_zeros(c.shape[0], 1)], 1)
+                coords, scene_c = pad(coords), pad(scene_c)
+            n_old, n_new, planes = scene_c.shape[0], coords.shape[0], feats.shape[1]
+            merged = torch.empty(n_old + n_new, planes + 1, dtype=torch.float32, device=feats.device)
+            merged[:n_old, :planes] = scene_s
+            merged[:n_old, planes] = scene_n
+            merged[n_old:, :planes] = feats
+            merged[n_old:, planes] = 1.0
+            SCN.InputLayer_updateOutput(output.metadata, self.spatial_size, torch.cat([scene_c, coords], 0), merged, out,
+                                        batch_size, 3)
+            sums, counts = out[:, :planes], out[:, planes]
+            output.features = sums / counts[:, None]
+            output.metadata.setSiteCounts(counts.round().int())  # a later residual frame weights these means correctly
             output.recompute_all = True
-            output.new_points = (n_old, coords.shape[0])
-            _keep(self, save_output=output, scene_coords=all_coords, scene_feats=all_feats)
+            output.new_points = (n_old, n_new)
+            sites = output.metadata.getSpatialLocationsDevice(self.spatial_size).t()[:, :scene_c.shape[1]].long()
+            _keep(self, save_output=output, _scene_state=(sites.contiguous(), sums.contiguous(), counts.contiguous()),
+                  _scene_points=None)
         elif not increment:
             SCN.InputLayer_updateOutput(output.metadata, self.spatial_size, coords, feats, out, batch_size, self.mode)
             output.features = out
-            _keep(self, save_output=output, scene_coords=coords.to(feats.device).long(), scene_feats=feats)
+            # the scene of the exact mode starts as this frame's points (one point each); they are only turned into
+            # voxel state when an exact frame or an edit asks for it
+            _keep(self, save_output=output, _scene_points=(coords, feats), _scene_state=None)
         else:
             SCN.Incre_InputLayer_updateOutput(output.metadata, self.spatial_size, coords, feats, out, batch_size,
                                               self.mode, self.save_output.metadata, self.save_output.features)
             output.features = out
         return output
+
+    def _scene(self, device):
+        """(coordinates [V, 3|4] int64, feature sums [V, planes], point counts [V]) of the kept scene."""
+        state = self.__dict__.get("_scene_state")
+        if state is None:
+            pts = self.__dict__.get("_scene_points")
+            assert pts is not None, "no frame has been run yet"
+            c, f = pts
+            f = f.to(device).float()
+            state = (c.to(device).long(), f, torch.ones(f.shape[0], dtype=torch.float32, device=device))
+            _keep(self, _scene_state=state, _scene_points=None)
+        return state
+
+    @property
+    def scene_coords(self):
+        """Coordinates of the kept scene's entries (voxels once an exact frame has merged them)."""
+        return self._scene(self.save_output.features.device)[0]
 
     @staticmethod
     def _voxel_keys(coords):
@@ -415,17 +449,25 @@ class InputLayer(Module):
         return k
 
     def delete_voxels(self, coords):
-        """Removes every kept point that falls in one of the given voxels (effective at the next exact frame).
-        The reference has no deletion; here a deleted voxel simply is no longer part of the scene."""
-        coords = coords.to(self.scene_coords.device)
-        keep = ~torch.isin(self._voxel_keys(self.scene_coords), self._voxel_keys(coords))
-        _keep(self, scene_coords=self.scene_coords[keep], scene_feats=self.scene_feats[keep])
+        """Removes the given voxels from the kept scene (effective at the next exact frame).  The reference has no
+        deletion; here a deleted voxel simply is no longer part of the scene."""
+        c, s, n = self._scene(self.save_output.features.device)
+        coords = coords.to(c.device).long()
+        if coords.shape[1] != c.shape[1]:
+            coords = coords[:, :3] if c.shape[1] == 3 else torch.cat([coords, coords.new_zeros(coords.shape[0], 1)], 1)
+        keep = ~torch.isin(self._voxel_keys(c), self._voxel_keys(coords))
+        _keep(self, _scene_state=(c[keep], s[keep], n[keep]))
 
     def replace_voxels(self, coords, feats):
         """Replaces the content of the given voxels by one point each carrying `feats` (a re-drawn feature)."""
         self.delete_voxels(coords)
-        _keep(self, scene_coords=torch.cat([self.scene_coords, coords.to(self.scene_coords.device).long()], 0),
-              scene_feats=torch.cat([self.scene_feats, feats.to(self.scene_feats.device).float()], 0))
+        c, s, n = self._scene(self.save_output.features.device)
+        coords = coords.to(c.device).long()
+        if coords.shape[1] != c.shape[1]:
+            coords = coords[:, :3] if c.shape[1] == 3 else torch.cat([coords, coords.new_zeros(coords.shape[0], 1)], 1)
+        feats = feats.to(s.device).float()
+        _keep(self, _scene_state=(torch.cat([c, coords], 0), torch.cat([s, feats], 0),
+                                  torch.cat([n, n.new_ones(coords.shape[0])], 0)))
 
 
 class OutputLayer(Module):
