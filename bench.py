@@ -431,18 +431,27 @@ def slab_bench(args, rank, world, local, dist):
     feats = synth.rgb(0, coords.shape[0])
     align = 2 ** (len(PLANES) - 1)
     cuts = slab.cuts_for(coords[:, 0].min(), coords[:, 0].max(), world, align)
-    ext = slab.extended_mask(coords[:, 0], cuts, rank, align)
+    assert all(b > a for a, b in zip(cuts, cuts[1:])), "more slabs than aligned cells"
+    ext = slab.load_mask(coords, cuts, rank, len(PLANES))
     n_own = int(slab.owned_mask(coords[:, 0], cuts, rank).sum())
-    ex = slab.SlabExchange(dist, rank, world, cuts, 4096)
+    peer = world > 1 and args.halo == "peer"
+    ex = slab.PeerSlabExchange(dist, rank, world, cuts, 4096, dev) if peer else slab.SlabExchange(dist, rank, world, cuts, 4096)
     if world > 1:
-        slab.install(model, ex, (scn.SubmanifoldConvolution, scn.Convolution))
+        slab.install(model, ex)
     dc, df = torch.from_numpy(coords[ext]).to(dev), torch.from_numpy(feats[ext]).to(dev)
 
     def frame():
         return model([dc, df])
 
+    if peer:  # one untimed frame with the pushed bytes summed on the device
+        ex.track_bytes = True
+        frame()
+        ex.track_bytes = False
+        sent_one_frame, ex_one_frame = ex.bytes_sent, ex.exchanges
     for _ in range(args.warmup):
         frame()
+    if peer:
+        ex.check()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
@@ -457,10 +466,17 @@ def slab_bench(args, rank, world, local, dist):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
     launches = scn.SCN.launch_count() - l0
+    if peer:
+        ex.check()  # raises if a neighbour did not answer or a plane did not fit its slot
+        frames = 1
+        sent_total, n_ex = sent_one_frame, ex_one_frame
+    else:
+        frames = max(args.steps + args.warmup, 1)
+        sent_total, n_ex = ex.bytes_sent, ex.exchanges
     ssc_mods = [m for m in model.modules() if isinstance(m, scn.SubmanifoldConvolution)]
     layers_local = sum(int(m.save_input_feats.shape[0]) for m in ssc_mods)
     if dist is not None:
-        t = torch.tensor([ms, float(layers_local), float(ex.bytes_sent)], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms, float(layers_local), float(sent_total)], device=dev, dtype=torch.float64)
         tmax = t.clone()
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
@@ -473,12 +489,14 @@ def slab_bench(args, rank, world, local, dist):
                           "scaling": "strong", "vs_baseline": None,
                           "dtype": {"fp32": "f32", "tf32": "tf32", "fp16": "f16"}[args.precision], "data": "synthetic",
                           "config": {"workload": "configs[4] part 2: one %d-voxel building (5 rooms x 4 floors) in %d x-slabs, "
-                                                 "halo rows exchanged by NCCL after every SSC / strided convolution"
+                                                 "halo rows exchanged after every SSC / strided convolution"
                                                  % (coords.shape[0], world),
-                                     "cuts": cuts, "ghost_zone_voxels": align,
+                                     "cuts": cuts, "ghost_zone": "per level, the plane next to each cut (coarse cells by one point each)",
                                      "voxel_layers_computed_incl_ghost": layers_all,
-                                     "halo_bytes_sent_per_frame": sent / max(args.steps + args.warmup, 1),
-                                     "exchanges_per_frame": ex.exchanges // max(args.steps + args.warmup, 1)},
+                                     "halo": "rows pushed into the neighbour's memory by the library's own kernels (CUDA IPC "
+                                             "over NVLink), no NCCL call in the frame" if peer else "NCCL grouped send/recv",
+                                     "halo_bytes_sent_per_frame": sent / frames,
+                                     "exchanges_per_frame": n_ex // frames},
                           "gpu_launches": int(launches)}))
 
 
@@ -541,6 +559,8 @@ def main():
     ap.add_argument("--hash", action="store_true", help="time the grid build alone and exit")
     ap.add_argument("--workload", default="room", choices=["room", "building"],
                     help="room: one scene per GPU (default); building: one 4M-voxel scene split into x-slabs")
+    ap.add_argument("--halo", default="peer", choices=["peer", "nccl"],
+                    help="building workload: how halo rows travel (own kernels into peer memory, or NCCL send/recv)")
     ap.add_argument("--n-in", type=int, default=32)
     ap.add_argument("--n-out", type=int, default=32)
     ap.add_argument("--profile", action="store_true", help="allow fewer than 3 warm-up steps (numbers are not bench values)")

@@ -359,6 +359,32 @@ SCN_API int scn_incre_bn_forward(scn_metadata *m, scn_metadata *pre, const int64
                          const float *beta, double eps, double leakiness, const float *pre_out,
                          const float *pre_in, void *stream);
 
+/* ---- one scene on several GPUs: halo rows pushed into the neighbours' memory ------------------------------
+ * The reference runs on one GPU; these entry points have no counterpart there.  A scene is cut into slabs along x,
+ * one per GPU (one process each); after every convolution that reads neighbouring sites a rank overwrites the rows
+ * of the plane beyond each of its cuts with the values their owner computed.  An scn_halo owns this rank's inbox
+ * (device memory the two neighbours write into: per side two message slots of slot_bytes and a sequence number);
+ * scn_halo_ipc_handle gives the 64-byte CUDA IPC handle to send to the neighbours, scn_halo_connect maps a
+ * neighbour's inbox (side 0 = left, 1 = right; handle NULL = this rank's own inbox, i.e. the rank is its own
+ * neighbour on that side).  All ranks must issue the same sequence of exchanges.
+ *
+ * scn_halo_exchange queues two kernels on `stream` and returns: rows is a device array [4][cap] of row indices
+ * (send-left, send-right, receive-left, receive-right; both ranks at a cut list the plane's rows in the same order),
+ * counts a device array [4] of how many entries of each list are used.  `a` (and `b`, optional) are row-major device
+ * arrays patched in place, rows of a_row_bytes / b_row_bytes (multiples of 4).  Waiting for a neighbour is bounded
+ * (scn_halo_set_spin_limit polls of 200 ns, default about one second): when it runs out the rows stay untouched and
+ * scn_halo_status (which synchronises the stream) reports timed_out = 1; overflow = 1 says a plane did not fit a
+ * slot and was cut short.  Both are cleared by reading them. */
+typedef struct scn_halo scn_halo;
+SCN_API int scn_halo_create(scn_halo **out, int64_t slot_bytes);
+SCN_API void scn_halo_destroy(scn_halo *h);
+SCN_API int scn_halo_ipc_handle(scn_halo *h, void *handle64);
+SCN_API int scn_halo_connect(scn_halo *h, int side, const void *handle64);
+SCN_API int scn_halo_set_spin_limit(scn_halo *h, int64_t polls);
+SCN_API int scn_halo_exchange(scn_halo *h, const int64_t *rows, const int64_t *counts, int64_t cap, void *a,
+                              int64_t a_row_bytes, void *b, int64_t b_row_bytes, void *stream);
+SCN_API int scn_halo_status(scn_halo *h, int *timed_out, int *overflow, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -101,6 +101,16 @@ PROTOTYPES.update({
                                      C.POINTER(_dbl)]),
 })
 
+PROTOTYPES.update({
+    "scn_halo_create": (_int, [C.POINTER(_p), _i64]),
+    "scn_halo_destroy": (None, [_p]),
+    "scn_halo_ipc_handle": (_int, [_p, _p]),
+    "scn_halo_connect": (_int, [_p, _int, _p]),
+    "scn_halo_set_spin_limit": (_int, [_p, _i64]),
+    "scn_halo_exchange": (_int, [_p, _p, _p, _i64, _p, _i64, _p, _i64, _p]),
+    "scn_halo_status": (_int, [_p, C.POINTER(_int), C.POINTER(_int), _p]),
+})
+
 _STATUS = {n for n, (r, _) in PROTOTYPES.items() if r is _int and n not in ("scn_n_rulebook_bits", "scn_weights_packable")}
 
 

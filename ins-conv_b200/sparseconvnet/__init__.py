@@ -9,6 +9,8 @@ torch extension, which forwards to libinsconv_b200.so.  There is no CPU path.
 forward_pass_multiplyAdd_count = 0
 forward_pass_hidden_states = 0
 
+import torch  # noqa: E402,F401  (the extension creates tensors while it loads: torch has to be initialised first)
+
 from . import SCN  # noqa: E402  (the compiled extension; importing fails loudly when it is not built)
 from .tensor import SparseConvNetTensor  # noqa: E402
 from .metadata import Metadata  # noqa: E402
@@ -26,6 +28,13 @@ def set_epilogue_fusion(on):
     kernel of its own."""
     from . import containers
     containers.fuse_epilogues[0] = bool(on)
+
+
+def set_halo_exchange(fn):
+    """fn(SparseConvNetTensor) is run on the result of every full-frame SubmanifoldConvolution and Convolution, or None
+    to switch it off.  One scene split over several GPUs restores its halo rows here (insconv.slab.SlabExchange)."""
+    from . import layers
+    layers.halo_exchange[0] = fn
 
 
 def set_incremental_state(on):

@@ -25,6 +25,16 @@ from .tensor import SparseConvNetTensor
 from .utils import toLongTensor, optionalTensor, _precision
 
 _NONE = torch.empty(0)
+# [callable or None]: run on the result of every full-frame SubmanifoldConvolution and Convolution (the layers whose
+# rows depend on neighbouring sites); a scene split over several GPUs exchanges its halo rows here
+# (sparseconvnet.set_halo_exchange, insconv.slab)
+halo_exchange = [None]
+
+
+def _halo(t):
+    if halo_exchange[0] is not None:
+        halo_exchange[0](t)
+    return t
 
 
 def _keep(module, **state):
@@ -173,7 +183,7 @@ class SubmanifoldConvolution(Module):
             _keep(self, save_meta=input.metadata, save_input_feats=input.features)
             _count(madds, out)
             res = input.like(out)
-            return _finish_fused(res, fuse_bn, fused[3]) if fused else res
+            return _halo(_finish_fused(res, fuse_bn, fused[3]) if fused else res)
         madds = SCN.Incre_SubmanifoldConvolution_updateOutput(
             input.spatial_size, self.filter_size, input.metadata, input.features, out, self._parameters["weight"],
             optionalTensor(self, "bias"), self.save_meta, _f32(self, self.save_input_feats), _packed(self))
@@ -219,7 +229,8 @@ class Convolution(_Strided):
                    out, self._parameters["weight"], optionalTensor(self, "bias"), _packed_for(self, input.features), *extra)
         _count(madds, out)
         res = input.like(out, out_size)
-        return _finish_fused(res, fuse_bn, fused[3]) if fused else res
+        res = _finish_fused(res, fuse_bn, fused[3]) if fused else res
+        return res if residual else _halo(res)
 
     def input_spatial_size(self, out_size):
         return (out_size - 1) * self.filter_stride + self.filter_size

@@ -37,7 +37,7 @@ def _scene():
     return c, synth.rgb(5, c.shape[0])
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, out, sparse_ghost):
     _paths()
     from insconv import slab
     from oracle.scn_graph import GraphRunner
@@ -46,7 +46,7 @@ def _worker(rank, world, port, out):
     c, f = _scene()
     align = 2 ** (len(PLANES) - 1)
     cuts = slab.cuts_for(c[:, 0].min(), c[:, 0].max(), world, align)
-    ext = slab.extended_mask(c[:, 0], cuts, rank, align)
+    ext = slab.load_mask(c, cuts, rank, len(PLANES)) if sparse_ghost else slab.extended_mask(c[:, 0], cuts, rank, align)
     own = slab.owned_mask(c[ext][:, 0], cuts, rank)
     ex = slab.SlabExchange(dist, rank, world, cuts, 128)
     runner = GraphRunner(model, post=lambda m, t: ex(t))
@@ -56,7 +56,11 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_two_slabs_equal_the_whole_scene():
+import pytest
+
+
+@pytest.mark.parametrize("world,sparse_ghost", [(2, False), (3, True)])
+def test_slabs_equal_the_whole_scene(world, sparse_ghost):
     _paths()
     from oracle.scn_graph import GraphRunner
     with socket.socket() as s:
@@ -64,13 +68,13 @@ def test_two_slabs_equal_the_whole_scene():
         port = s.getsockname()[1]
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(2, port, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(world, port, out, sparse_ghost), nprocs=world, join=True)
     model = _model()
     c, f = _scene()
     runner = GraphRunner(model)
     want = runner._run(model.linear, runner._run(model.sparseModel, [torch.from_numpy(c), torch.from_numpy(f)], False), False).numpy()
     got = np.full_like(want, np.nan)
-    for r in (0, 1):
+    for r in range(world):
         idx, y, n_ex, cuts = out[r]
         got[idx] = y
         assert n_ex > 10  # one exchange per submanifold / strided convolution
@@ -89,3 +93,27 @@ def test_cuts_are_aligned_and_cover():
     x = np.arange(0, 300)
     cuts = slab.cuts_for(0, 299, 2, 64)
     assert (slab.owned_mask(x, cuts, 0) ^ slab.owned_mask(x, cuts, 1)).all()
+
+
+def test_sparse_ghost_zone_keeps_every_cell_next_to_a_cut():
+    """load_mask: at every level the planes next to a rank's cuts hold the same occupied cells as in the whole scene,
+    the level-0 planes hold every point, and far fewer points are loaded than with the full ghost zone."""
+    _paths()
+    from insconv import slab
+    c, _ = _scene()
+    levels = 5
+    align = 2 ** (levels - 1)
+    world = 3
+    cuts = slab.cuts_for(c[:, 0].min(), c[:, 0].max(), world, align)
+    for rank in range(world):
+        keep = slab.load_mask(c, cuts, rank, levels)
+        full = slab.extended_mask(c[:, 0], cuts, rank, align)
+        own = slab.owned_mask(c[:, 0], cuts, rank)
+        assert (keep & own).sum() == own.sum() and not (keep & ~full).any()
+        assert keep.sum() - own.sum() < 0.35 * (full.sum() - own.sum())
+        for lvl in range(levels):
+            for plane in ((cuts[rank] >> lvl) - 1, cuts[rank + 1] >> lvl):
+                cells = lambda pts: {tuple(v) for v in (pts[(pts[:, 0] >> lvl) == plane] >> lvl)}
+                assert cells(c[keep]) == cells(c)
+        for plane in (cuts[rank] - 1, cuts[rank + 1]):
+            assert (keep[c[:, 0] == plane]).all()
