@@ -67,6 +67,10 @@ SCN_API const char *scn_last_error(void);
 SCN_API const char *scn_version(void);
 /* Number of kernel launches issued by this library since load (all threads). */
 SCN_API uint64_t scn_launch_count(void);
+/* Tuning aid for the fp16 kernel of wide layers on small grids (16-row tiles, 32 output planes per warp): how many
+ * warps share the reduction of one tile.  0 (default): chosen per launch from the number of tiles; 1, 2, 4, 8: fixed.
+ * Results do not depend on it beyond the order of fp32 additions.  Process-wide. */
+SCN_API int scn_set_slab_share(int warps);
 /* Synchronises `stream` and reports errors that kernels can only flag asynchronously (a bounded
  * wait inside a tensor-core kernel that ran out).  No counterpart in the reference, whose kernels
  * have no such waits. */

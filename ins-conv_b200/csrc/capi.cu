@@ -240,6 +240,11 @@ extern "C" {
 const char *scn_last_error(void) { return t_error.c_str(); }
 const char *scn_version(void) { return "insconv_b200 0.1 (sm_100a)"; }
 uint64_t scn_launch_count(void) { return g_launches.load(); }
+int scn_set_slab_share(int warps) {
+  if (warps != 0 && warps != 1 && warps != 2 && warps != 4 && warps != 8) return fail(SCN_E_INVALID, "0 (automatic), 1, 2, 4 or 8");
+  g_slab_share = warps;
+  return SCN_OK;
+}
 int scn_n_rulebook_bits(void) { return 32; }
 int scn_check_errors(void *stream) {
   SCN_CUDA(cudaStreamSynchronize((cudaStream_t)stream));

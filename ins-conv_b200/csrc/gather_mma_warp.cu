@@ -303,21 +303,137 @@ __device__ __forceinline__ void mma_rows_h(float (&acc)[COUT / 16][NTR][4], cons
   }
 }
 
+// Row ADDRESSES instead of row numbers in the warp's slice of shared memory: the address of a gathered row is formed once
+// per (offset, row) when the map entries are published, not by every lane of the quad at every use, and an absent
+// neighbour points at a row of zeros, so the loads of the reduction loop are unconditional (no predicate, no zeroing
+// of the destination registers).  In the loop a row costs one 8-byte shared-memory read, one 64-bit add (the lane's
+// 16 bytes inside the row) and the load itself.
+//
+// Order of the offsets: a 3x3x3 filter's offsets are visited with dx innermost (k = 9 (dx+1) + 3 (dy+1) + (dz+1) is
+// visited as ..., k, k + 9, k + 18, ...).  Rows are numbered along x, so the three dx variants of a (dy, dz) pair read
+// the same rows shifted by one: visited back to back the second and third find the lines the first just fetched in L1.
+__device__ __align__(256) unsigned char g_zero_row[512];  // never written: zero-initialised with the module
+
+__device__ __forceinline__ constexpr int visit_pos(int k) { return (k % 9) * 3 + k / 9; }  // position of offset k
+__device__ __forceinline__ int visit_offset(int p, bool permuted) { return permuted ? (p % 3) * 9 + p / 3 : p; }
+
+// Publishes the addresses and returns the set of occupied offsets as a mask over VISIT positions (permuted: K == 27).
+template <int ROWS>
+__device__ __forceinline__ unsigned int publish_addr(const MapRegs<ROWS> &m, unsigned long long *mp, int K, int lane,
+                                                     const char *in_bytes, long long stride_bytes, bool permuted) {
+  constexpr int PER = MapRegs<ROWS>::PER, NL = MapRegs<ROWS>::NL;
+  const int r = lane % ROWS, ksub = lane / ROWS;
+  const unsigned long long zero = reinterpret_cast<unsigned long long>(g_zero_row);
+  const unsigned long long base = reinterpret_cast<unsigned long long>(in_bytes);
+  unsigned int mask = 0;
+#pragma unroll
+  for (int j = 0; j < NL; ++j) {
+    const int k = j * PER + ksub;
+    if (k < K) mp[k * ROWS + r] = m.v[j] >= 0 ? base + (unsigned long long)((long long)m.v[j] * stride_bytes) : zero;
+    const unsigned int b = __ballot_sync(0xffffffffu, m.v[j] >= 0);
+    if (PER == 2) {
+      const int ka = j * PER, kb = j * PER + 1;
+      mask |= ((b & 0xffffu) ? 1u : 0u) << (permuted ? visit_pos(ka) : ka);
+      if (kb < kMaxK) mask |= ((b >> 16) ? 1u : 0u) << (permuted ? visit_pos(kb) : kb);
+    } else {
+      mask |= (b ? 1u : 0u) << (permuted ? visit_pos(j) : j);
+    }
+  }
+  __syncwarp();
+  return mask;
+}
+
+template <int CIN, int NTR>
+__device__ __forceinline__ void load_rows_a(FragH<CIN, NTR> &f, const unsigned long long *mp_k, int g, int lane_bytes) {
+#pragma unroll
+  for (int n = 0; n < NTR; ++n) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(mp_k[n * 8 + g] + (unsigned long long)lane_bytes);
+#pragma unroll
+    for (int c = 0; c < CIN / 32; ++c) f.v[n][c] = __ldg(p + 4 * c);
+  }
+}
+
+// Epilogue of a 32-plane pass through the warp's slice of shared memory: the accumulator fragments hold single floats
+// of rows 2t, 2t + 1 (a lane would store 4 bytes at a time, 16 * NTR stores and as many again for the fp16 rows); staged
+// with a pitch of 36 floats (conflict-free both ways) a lane reads 4 consecutive planes of a row and every store is
+// 16 bytes (8 for the fp16 rows).  Needs 16-byte aligned rows (vec); otherwise the element-wise form is used.
+template <int NTR>
+__device__ __forceinline__ void store_pass(const float (&a0)[NTR][4], const float (&a1)[NTR][4], float *st, long long row0,
+                                           long long n_out, const float *__restrict__ bias, float *out, long long out_stride,
+                                           const float *init, long long init_stride, int lane, const EpiBn &e, int plane0) {
+  constexpr int ROWS = 8 * NTR, PITCH = 36;
+  const int g = lane >> 2, t = lane & 3;
+  __syncwarp();
+#pragma unroll
+  for (int n = 0; n < NTR; ++n)
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        st[(8 * n + 2 * t + j) * PITCH + 8 * h + g] = a0[n][2 * h + j];
+        st[(8 * n + 2 * t + j) * PITCH + 16 + 8 * h + g] = a1[n][2 * h + j];
+      }
+  __syncwarp();
+  const int q = lane & 7, r0 = lane >> 3;
+  float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f), sc = b4, sh = b4;
+  if (!init && bias) b4 = __ldg(reinterpret_cast<const float4 *>(bias) + q);
+  if (e.dst) {
+    sc = __ldg(reinterpret_cast<const float4 *>(e.scale + plane0) + q);
+    sh = __ldg(reinterpret_cast<const float4 *>(e.shift + plane0) + q);
+  }
+#pragma unroll
+  for (int i = 0; i < ROWS / 4; ++i) {
+    const int r = 4 * i + r0;
+    const long long row = row0 + r;
+    if (row < n_out) {
+      float4 v = *reinterpret_cast<const float4 *>(st + r * PITCH + 4 * q);
+      if (init) {
+        const float4 a = *reinterpret_cast<const float4 *>(init + row * init_stride + 4 * q);
+        v.x += a.x, v.y += a.y, v.z += a.z, v.w += a.w;
+      } else {
+        v.x += b4.x, v.y += b4.y, v.z += b4.z, v.w += b4.w;
+      }
+      if (!e.skip_raw) *reinterpret_cast<float4 *>(out + row * out_stride + 4 * q) = v;
+      if (e.dst) {
+        float y0 = fmaf(v.x, sc.x, sh.x), y1 = fmaf(v.y, sc.y, sh.y), y2 = fmaf(v.z, sc.z, sh.z), y3 = fmaf(v.w, sc.w, sh.w);
+        y0 = y0 > 0.f ? y0 : y0 * e.leak, y1 = y1 > 0.f ? y1 : y1 * e.leak;
+        y2 = y2 > 0.f ? y2 : y2 * e.leak, y3 = y3 > 0.f ? y3 : y3 * e.leak;
+        const __half2 lo = __floats2half2_rn(fminf(fmaxf(y0, -65504.f), 65504.f), fminf(fmaxf(y1, -65504.f), 65504.f));
+        const __half2 hi = __floats2half2_rn(fminf(fmaxf(y2, -65504.f), 65504.f), fminf(fmaxf(y3, -65504.f), 65504.f));
+        uint2 pk;
+        pk.x = *reinterpret_cast<const unsigned int *>(&lo);
+        pk.y = *reinterpret_cast<const unsigned int *>(&hi);
+        *reinterpret_cast<uint2 *>(static_cast<__half *>(e.dst) + row * e.stride + plane0 + 4 * q) = pk;
+      }
+    }
+  }
+}
+
+// true when store_pass may be used: 16-byte aligned fp32 rows, 8-byte aligned fp16 rows
+__host__ __device__ __forceinline__ bool rows_vectorisable(const float *out, long long out_stride, const float *init,
+                                                           long long init_stride, const float *bias, const EpiBn &e) {
+  auto al = [](const void *p, unsigned a) { return (reinterpret_cast<unsigned long long>(p) & (a - 1)) == 0; };
+  return al(out, 16) && out_stride % 4 == 0 && (!init || (al(init, 16) && init_stride % 4 == 0)) && (!bias || al(bias, 16)) &&
+         (!e.dst || (al(e.dst, 8) && e.stride % 4 == 0 && al(e.scale, 16) && al(e.shift, 16)));
+}
+
 template <int CIN, int COUT, int NTR, int MINB>
 __global__ void __launch_bounds__(kWarps * 32, MINB)
 k_gather_mma_f16(const __half *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
                  const uint4 *__restrict__ Wp, const float *__restrict__ bias, float *out, long long out_stride,
-                 const float *init, long long init_stride, const EpiBn epi) {
+                 const float *init, long long init_stride, const EpiBn epi, const int vec) {
   constexpr int ROWS = 8 * NTR, MTC = COUT / 16;
-  __shared__ int s_map[kWarps][kMaxK * ROWS];
+  static_assert(kMaxK * ROWS * 8 >= ROWS * 36 * 4, "the epilogue stages a 32-plane pass in the warp's map slice");
+  __shared__ unsigned long long s_map[kWarps][kMaxK * ROWS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const long long row0 = ((long long)blockIdx.x * kWarps + warp) * ROWS;
   if (row0 >= n_out) return;
-  int *mp = s_map[warp];
+  unsigned long long *mp = s_map[warp];
   MapRegs<ROWS> regs;
   load_map<ROWS>(regs, row0, map, K, n_out, lane);
-  unsigned int mask = publish_map<ROWS>(regs, mp, K, lane);
+  const bool perm = K == 27;
+  unsigned int mask = publish_addr<ROWS>(regs, mp, K, lane, reinterpret_cast<const char *>(in), in_stride * 2, perm);
   float acc[MTC][NTR][4];
 #pragma unroll
   for (int m = 0; m < MTC; ++m)
@@ -326,202 +442,188 @@ k_gather_mma_f16(const __half *__restrict__ in, long long in_stride, const int32
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
   constexpr int WK = (CIN / 32) * MTC * 2 * 32;  // uint4 per offset
-  const __half *in_t = in + 8 * t;
   const uint4 *wl = Wp + lane;
   if (mask) {
     FragH<CIN, NTR> f0, f1;
-    int k0 = __ffs(mask) - 1;
+    int k0 = visit_offset(__ffs(mask) - 1, perm);
     mask &= mask - 1;
-    load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
+    load_rows_a<CIN, NTR>(f0, mp + k0 * ROWS, g, 16 * t);
     while (true) {
       int k1 = -1;
       if (mask) {
-        k1 = __ffs(mask) - 1;
+        k1 = visit_offset(__ffs(mask) - 1, perm);
         mask &= mask - 1;
-        load_rows_h<CIN, NTR>(f1, mp + k1 * ROWS, in_t, in_stride, g);
+        load_rows_a<CIN, NTR>(f1, mp + k1 * ROWS, g, 16 * t);
       }
       mma_rows_h<CIN, COUT, NTR>(acc, f0, wl + k0 * WK);
       if (k1 < 0) break;
       k0 = -1;
       if (mask) {
-        k0 = __ffs(mask) - 1;
+        k0 = visit_offset(__ffs(mask) - 1, perm);
         mask &= mask - 1;
-        load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
+        load_rows_a<CIN, NTR>(f0, mp + k0 * ROWS, g, 16 * t);
       }
       mma_rows_h<CIN, COUT, NTR>(acc, f1, wl + k1 * WK);
       if (k0 < 0) break;
     }
   }
-  store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, init, init_stride, g, t, epi);
+  if (vec) {
+    float *st = reinterpret_cast<float *>(mp);
+#pragma unroll
+    for (int pass = 0; pass < MTC / 2; ++pass)
+      store_pass<NTR>(acc[2 * pass], acc[2 * pass + 1], st, row0, n_out, bias ? bias + 32 * pass : nullptr, out + 32 * pass,
+                      out_stride, init ? init + 32 * pass : nullptr, init_stride, lane, epi, 32 * pass);
+  } else {
+    store_acc<COUT, NTR>(acc, row0, n_out, bias, out, out_stride, init, init_stride, g, t, epi);
+  }
 }
 
-// Wide layers on small grids (the deep levels of a UNet: a few hundred to a few thousand rows, 96-224 planes).  There
+// Wide layers on small grids (the deep levels of a UNet: a hundred to sixteen thousand rows, 96-224 planes).  There
 // the tcgen05 kernel has too few 128-row tiles to fill the GPU, shares a tile's reduction among work items and needs a
-// second launch to add the partial tiles; this form gives a warp 16 rows and a slab of 32 output planes
-// (blockIdx.y) and lets it run the whole reduction, so the layer is one launch of rows/16 x n_out/32 independent warps.
-template <int C32, int NTR>
-__device__ __forceinline__ void mma_rows_slab(float (&acc)[2][NTR][4], const FragH<C32 * 32, NTR> &f, const uint4 *__restrict__ wk,
-                                              int mtc_total) {
+// second launch to add the partial tiles.  Here a tile is 16 rows x a slab of 32 output planes (blockIdx.y), its
+// reduction over the occupied offsets is run by KS warps (1, 2, 4 or 8: every KS-th occupied offset each), and the
+// layer is one launch of rows/16 x n_out/32 x KS warps.  With one warp per tile a layer takes as long as its chain
+// of 27 dependent gathers (0.4-0.5 us each: 20-30 us whatever the size) while most of the GPU idles; the launcher
+// picks KS so that the GPU is covered.  The partial accumulators of warps 1 .. KS-1 are parked in shared memory and
+// added by warp 0 in a fixed order (deterministic), which then runs the epilogue.
+//
+// Registers decide how many warps fit, so the gathered rows have ONE buffer (16 rows x n_in: 8 registers per 32 planes):
+// as soon as the MMAs of a 32-plane chunk have been issued, the chunk's registers are reloaded with the same chunk of the
+// warp's next offset, which then has the rest of this offset's MMAs to arrive.  The weight fragments of the next chunk
+// are fetched while the MMAs of the current one are issued (two buffers of 16 registers).
+constexpr int kSlabWarps = 8;
+
+template <int C32> struct SlabRows {
+  uint4 v[2][C32];
+};
+
+// chunk c of the rows at `mp_k` (16 addresses): lane (g, t) takes 16 bytes of rows g and g + 8
+template <int C32>
+__device__ __forceinline__ void slab_load_chunk(SlabRows<C32> &f, const unsigned long long *mp_k, int g, int lane_bytes, int c) {
+#pragma unroll
+  for (int n = 0; n < 2; ++n)
+    f.v[n][c] = __ldg(reinterpret_cast<const uint4 *>(mp_k[n * 8 + g] + (unsigned long long)(lane_bytes + 64 * c)));
+}
+
+__device__ __forceinline__ void slab_load_w(uint4 (&a)[2][2], const uint4 *__restrict__ wk, int c, int mtc_total) {
+#pragma unroll
+  for (int m = 0; m < 2; ++m) {
+    a[m][0] = __ldg(wk + ((c * mtc_total + m) * 2) * 32);
+    a[m][1] = __ldg(wk + ((c * mtc_total + m) * 2 + 1) * 32);
+  }
+}
+
+// One offset: MMAs of all chunks; after a chunk's MMAs its row registers are refilled from the next offset (mp_next,
+// null at the end) and the weight fragments of the following chunk (of this offset, or chunk 0 of the next: wk_next)
+// are already on their way.  P0: which weight buffer holds chunk 0 (alternates from offset to offset when C32 is odd).
+template <int C32, int P0>
+__device__ __forceinline__ void slab_offset(float (&acc)[2][2][4], SlabRows<C32> &f, uint4 (&a)[2][2][2], const uint4 *__restrict__ wk,
+                                            const uint4 *__restrict__ wk_next, const unsigned long long *mp_next, int mtc_total,
+                                            int g, int lane_bytes) {
 #pragma unroll
   for (int c = 0; c < C32; ++c) {
-    uint4 a[2][2];
-#pragma unroll
-    for (int m = 0; m < 2; ++m) {
-      a[m][0] = __ldg(wk + ((c * mtc_total + m) * 2) * 32);
-      a[m][1] = __ldg(wk + ((c * mtc_total + m) * 2 + 1) * 32);
-    }
+    const int cur = (P0 + c) & 1, nxt = cur ^ 1;
+    if (c + 1 < C32) slab_load_w(a[nxt], wk, c + 1, mtc_total);
+    else if (wk_next) slab_load_w(a[nxt], wk_next, 0, mtc_total);
 #pragma unroll
     for (int m = 0; m < 2; ++m)
 #pragma unroll
-      for (int n = 0; n < NTR; ++n) mma_m16n8k16_f16(acc[m][n], a[m][0], f.v[n][c].x, f.v[n][c].y);
+      for (int n = 0; n < 2; ++n) mma_m16n8k16_f16(acc[m][n], a[cur][m][0], f.v[n][c].x, f.v[n][c].y);
 #pragma unroll
     for (int m = 0; m < 2; ++m)
 #pragma unroll
-      for (int n = 0; n < NTR; ++n) mma_m16n8k16_f16(acc[m][n], a[m][1], f.v[n][c].z, f.v[n][c].w);
+      for (int n = 0; n < 2; ++n) mma_m16n8k16_f16(acc[m][n], a[cur][m][1], f.v[n][c].z, f.v[n][c].w);
+    if (mp_next) slab_load_chunk<C32>(f, mp_next, g, lane_bytes, c);
   }
 }
 
-template <int C32, int NTR>
-__global__ void __launch_bounds__(kWarps * 32, 3)
+template <int C32, int KS>
+__global__ void __launch_bounds__(kSlabWarps * 32, 2)
 k_gather_mma_f16_slab(const __half *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
                       const uint4 *__restrict__ Wp, int Cout, const float *__restrict__ bias, float *out, long long out_stride,
-                      const float *init, long long init_stride, const EpiBn epi) {
-  constexpr int ROWS = 8 * NTR, CIN = C32 * 32;
-  __shared__ int s_map[kWarps][kMaxK * ROWS];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
-  const long long row0 = ((long long)blockIdx.x * kWarps + warp) * ROWS;
-  if (row0 >= n_out) return;
-  const int slab = blockIdx.y, mtc_total = Cout >> 4;
-  int *mp = s_map[warp];
-  MapRegs<ROWS> regs;
-  load_map<ROWS>(regs, row0, map, K, n_out, lane);
-  unsigned int mask = publish_map<ROWS>(regs, mp, K, lane);
-  float acc[2][NTR][4];
-#pragma unroll
-  for (int m = 0; m < 2; ++m)
-#pragma unroll
-    for (int n = 0; n < NTR; ++n)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
-  const int WK = C32 * mtc_total * 2 * 32;  // uint4 per offset
-  const __half *in_t = in + 8 * t;
-  const uint4 *wl = Wp + lane + (2 * slab) * 2 * 32;  // this slab's two 16-plane tiles inside a 32-plane block's fragments
-  if (mask) {
-    FragH<CIN, NTR> f0, f1;
-    int k0 = __ffs(mask) - 1;
-    mask &= mask - 1;
-    load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
-    while (true) {
-      int k1 = -1;
-      if (mask) {
-        k1 = __ffs(mask) - 1;
-        mask &= mask - 1;
-        load_rows_h<CIN, NTR>(f1, mp + k1 * ROWS, in_t, in_stride, g);
-      }
-      mma_rows_slab<C32, NTR>(acc, f0, wl + (long long)k0 * WK, mtc_total);
-      if (k1 < 0) break;
-      k0 = -1;
-      if (mask) {
-        k0 = __ffs(mask) - 1;
-        mask &= mask - 1;
-        load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
-      }
-      mma_rows_slab<C32, NTR>(acc, f1, wl + (long long)k1 * WK, mtc_total);
-      if (k0 < 0) break;
-    }
-  }
-  store_acc<32, NTR>(acc, row0, n_out, bias ? bias + 32 * slab : nullptr, out + 32 * slab, out_stride,
-                     init ? init + 32 * slab : nullptr, init_stride, g, t, epi, 32 * slab);
-}
-
-// The same tile (16 rows x a slab of 32 output planes) with its reduction SHARED by KS warps, for grids of a few
-// thousand rows and fewer: there a warp that runs all offsets of its tile alone spends its time waiting for one gather
-// after the other (27 dependent round trips to L2, 20-25 us per layer whatever the size) while most of the GPU idles.
-// Here a block of 8 warps holds 8 / KS tiles; the KS warps of a tile take every KS-th of the tile's occupied offsets,
-// park their partial accumulators in shared memory, and the first of them adds the parts in a fixed order (warp 1,
-// 2, ... : deterministic) and runs the epilogue.
-constexpr int kSplitWarps = 8;
-template <int C32, int KS>
-__global__ void __launch_bounds__(kSplitWarps * 32)
-k_gather_mma_f16_slab_split(const __half *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
-                            const uint4 *__restrict__ Wp, int Cout, const float *__restrict__ bias, float *out, long long out_stride,
-                            const float *init, long long init_stride, const EpiBn epi) {
-  constexpr int NTR = 2, ROWS = 16, CIN = C32 * 32, TILES = kSplitWarps / KS;
-  __shared__ int s_map[kSplitWarps][kMaxK * ROWS];
-  __shared__ float s_part[kSplitWarps][16][32];  // [warp][accumulator element][lane]
+                      const float *init, long long init_stride, const EpiBn epi, const int vec) {
+  constexpr int ROWS = 16, TILES = kSlabWarps / KS;
+  __shared__ unsigned long long s_map[kSlabWarps][kMaxK * ROWS];
+  __shared__ float s_part[KS > 1 ? kSlabWarps : 1][16][32];  // [warp][accumulator element][lane]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int tile_local = warp / KS, split = warp % KS;
   const long long row0 = ((long long)blockIdx.x * TILES + tile_local) * ROWS;
   const bool live = row0 < n_out;
+  if (KS == 1 && !live) return;  // with one warp per tile the warps never meet
   const int slab = blockIdx.y, mtc_total = Cout >> 4;
-  float acc[2][NTR][4];
+  unsigned long long *mp = s_map[warp];
+  float acc[2][2][4];
 #pragma unroll
   for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int n = 0; n < NTR; ++n)
+    for (int n = 0; n < 2; ++n)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
   if (live) {
-    int *mp = s_map[warp];
     MapRegs<ROWS> regs;
     load_map<ROWS>(regs, row0, map, K, n_out, lane);
-    const unsigned int all = publish_map<ROWS>(regs, mp, K, lane);
-    // this warp's share: every KS-th occupied offset, counted from its own index
-    unsigned int mask = 0;
-    int ord = 0;
-    for (unsigned int m = all; m; m &= m - 1, ++ord)
-      if (ord % KS == split) mask |= m & (0u - m);
-    const int WK = C32 * mtc_total * 2 * 32;  // uint4 per offset
-    const __half *in_t = in + 8 * t;
-    const uint4 *wl = Wp + lane + (2 * slab) * 2 * 32;
+    const bool perm = K == 27;
+    const unsigned int all = publish_addr<ROWS>(regs, mp, K, lane, reinterpret_cast<const char *>(in), in_stride * 2, perm);
+    unsigned int mask = all;
+    if (KS > 1) {  // this warp's share: every KS-th occupied offset, counted from its own index
+      mask = 0;
+      int ord = 0;
+      for (unsigned int m = all; m; m &= m - 1, ++ord)
+        if (ord % KS == split) mask |= m & (0u - m);
+    }
+    const long long WK = (long long)C32 * mtc_total * 2 * 32;  // uint4 per offset
+    const uint4 *wl = Wp + lane + (2 * slab) * 2 * 32;  // this slab's two 16-plane tiles inside a 32-plane block's fragments
     if (mask) {
-      FragH<CIN, NTR> f0, f1;
-      int k0 = __ffs(mask) - 1;
+      SlabRows<C32> f;
+      uint4 a[2][2][2];
+      int k = visit_offset(__ffs(mask) - 1, perm);
       mask &= mask - 1;
-      load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
+      const uint4 *wk = wl + k * WK;
+      slab_load_w(a[0], wk, 0, mtc_total);
+#pragma unroll
+      for (int c = 0; c < C32; ++c) slab_load_chunk<C32>(f, mp + k * ROWS, g, 16 * t, c);
       while (true) {
-        int k1 = -1;
-        if (mask) {
-          k1 = __ffs(mask) - 1;
-          mask &= mask - 1;
-          load_rows_h<CIN, NTR>(f1, mp + k1 * ROWS, in_t, in_stride, g);
-        }
-        mma_rows_slab<C32, NTR>(acc, f0, wl + (long long)k0 * WK, mtc_total);
-        if (k1 < 0) break;
-        k0 = -1;
-        if (mask) {
-          k0 = __ffs(mask) - 1;
-          mask &= mask - 1;
-          load_rows_h<CIN, NTR>(f0, mp + k0 * ROWS, in_t, in_stride, g);
-        }
-        mma_rows_slab<C32, NTR>(acc, f1, wl + (long long)k1 * WK, mtc_total);
-        if (k0 < 0) break;
+        int kn = mask ? visit_offset(__ffs(mask) - 1, perm) : -1;
+        mask &= mask - 1;
+        slab_offset<C32, 0>(acc, f, a, wk, kn >= 0 ? wl + kn * WK : nullptr, kn >= 0 ? mp + kn * ROWS : nullptr, mtc_total, g, 16 * t);
+        if (kn < 0) break;
+        wk = wl + kn * WK;
+        kn = mask ? visit_offset(__ffs(mask) - 1, perm) : -1;
+        mask &= mask - 1;
+        slab_offset<C32, (C32 & 1)>(acc, f, a, wk, kn >= 0 ? wl + kn * WK : nullptr, kn >= 0 ? mp + kn * ROWS : nullptr, mtc_total, g,
+                                    16 * t);
+        if (kn < 0) break;
+        wk = wl + kn * WK;
       }
     }
-    if (split != 0) {
+    if (KS > 1 && split != 0) {
 #pragma unroll
       for (int m = 0; m < 2; ++m)
 #pragma unroll
-        for (int n = 0; n < NTR; ++n)
+        for (int n = 0; n < 2; ++n)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) s_part[warp][(m * NTR + n) * 4 + i][lane] = acc[m][n][i];
+          for (int i = 0; i < 4; ++i) s_part[warp][(m * 2 + n) * 4 + i][lane] = acc[m][n][i];
     }
   }
-  __syncthreads();
-  if (live && split == 0) {
+  if (KS > 1) {
+    __syncthreads();
+    if (!live || split != 0) return;
 #pragma unroll 1
     for (int o = 1; o < KS; ++o)
 #pragma unroll
       for (int m = 0; m < 2; ++m)
 #pragma unroll
-        for (int n = 0; n < NTR; ++n)
+        for (int n = 0; n < 2; ++n)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) acc[m][n][i] += s_part[warp + o][(m * NTR + n) * 4 + i][lane];
-    store_acc<32, NTR>(acc, row0, n_out, bias ? bias + 32 * slab : nullptr, out + 32 * slab, out_stride,
-                       init ? init + 32 * slab : nullptr, init_stride, g, t, epi, 32 * slab);
+          for (int i = 0; i < 4; ++i) acc[m][n][i] += s_part[warp + o][(m * 2 + n) * 4 + i][lane];
   }
+  if (vec)
+    store_pass<2>(acc[0], acc[1], reinterpret_cast<float *>(mp), row0, n_out, bias ? bias + 32 * slab : nullptr, out + 32 * slab,
+                  out_stride, init ? init + 32 * slab : nullptr, init_stride, lane, epi, 32 * slab);
+  else
+    store_acc<32, 2>(acc, row0, n_out, bias ? bias + 32 * slab : nullptr, out + 32 * slab, out_stride,
+                     init ? init + 32 * slab : nullptr, init_stride, g, t, epi, 32 * slab);
 }
 
 // W [K][n_in][n_out] fp32 -> fp16 fragments [K][n_in/32][n_out/16][2][lane][8]: half e of (k, c, m, j, lane = 4g + t)
@@ -718,6 +820,9 @@ bool warp_slab_f16_shape(int64_t K, int64_t Cin, int64_t Cout) {
   return K >= 1 && K <= kMaxK && Cin % 32 == 0 && Cin >= 96 && Cin <= 224 && Cout % 32 == 0 && Cout >= 32 && Cout <= 256;
 }
 
+// 0: the launcher chooses how many warps share a tile's reduction; 1, 2, 4, 8: fixed (scn_set_slab_share, a tuning aid)
+int g_slab_share = 0;
+
 int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
                         int64_t init_stride, cudaStream_t s, const EpiBn *epi) {
@@ -728,43 +833,34 @@ int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, i
   const __half *inh = static_cast<const __half *>(in);
   const uint4 *W4 = static_cast<const uint4 *>(Wp);
   const long long tiles = (n_out + 15) / 16;
-  // a few hundred rows (the two deepest levels of the UNet): a tile's reduction is shared by 8 warps, which replaces
-  // the tcgen05 kernel's split reductions and its second launch there (23 us and 18 us per layer against 24-30 us).
-  // From a thousand rows on one warp per tile is faster: sharing by 4 warps at 4k rows / 160 planes measured 46 us
-  // against 28 us, by 2 warps at 7k rows / 128 planes 26 us against 23 us -- what bounds those layers is the weight
-  // traffic from L2 (every 16-row tile reads all of its slab's weights), which more warps in flight only congest.
-  const int ks = n_out <= 1024 ? 8 : 1;
-  if (ks > 1) {
-    const int tiles_per_block = kSplitWarps / ks;
-    const dim3 grid((unsigned)((tiles + tiles_per_block - 1) / tiles_per_block), (unsigned)(Cout / 32));
-#define SCN_SPLIT_LAUNCH(C32, KS)                                                                                       \
-  k_gather_mma_f16_slab_split<C32, KS><<<grid, kSplitWarps * 32, 0, s>>>(inh, in_stride, map, K, n_out, W4, (int)Cout, bias, out, \
-                                                                         out_stride, init, init_stride, e)
-#define SCN_SPLIT_C32(KS)                     \
-  switch ((int)(Cin / 32)) {                  \
-    case 3: SCN_SPLIT_LAUNCH(3, KS); break;   \
-    case 4: SCN_SPLIT_LAUNCH(4, KS); break;   \
-    case 5: SCN_SPLIT_LAUNCH(5, KS); break;   \
-    case 6: SCN_SPLIT_LAUNCH(6, KS); break;   \
-    default: SCN_SPLIT_LAUNCH(7, KS); break;  \
+  const int vec = rows_vectorisable(out, out_stride, init, init_stride, bias, e) ? 1 : 0;
+  // warps that share a tile's reduction: as few as cover the GPU with about two blocks of 8 warps per SM
+  const long long slabs = Cout / 32;
+  int ks = g_slab_share;
+  if (ks != 1 && ks != 2 && ks != 4 && ks != 8) {
+    ks = 1;
+    while (ks < 8 && tiles * slabs * ks < 148 * 16) ks *= 2;
   }
-    if (ks == 8) { SCN_SPLIT_C32(8) } else if (ks == 4) { SCN_SPLIT_C32(4) } else { SCN_SPLIT_C32(2) }
-#undef SCN_SPLIT_C32
-#undef SCN_SPLIT_LAUNCH
-    SCN_LAUNCHED();
-    return SCN_OK;
+  const int tiles_per_block = kSlabWarps / ks;
+  const dim3 grid((unsigned)((tiles + tiles_per_block - 1) / tiles_per_block), (unsigned)slabs);
+#define SCN_SLAB_LAUNCH(C32, KS)                                                                                              \
+  k_gather_mma_f16_slab<C32, KS><<<grid, kSlabWarps * 32, 0, s>>>(inh, in_stride, map, K, n_out, W4, (int)Cout, bias, out, \
+                                                                  out_stride, init, init_stride, e, vec)
+#define SCN_SLAB_KS(C32)                        \
+  switch (ks) {                                 \
+    case 1: SCN_SLAB_LAUNCH(C32, 1); break;     \
+    case 2: SCN_SLAB_LAUNCH(C32, 2); break;     \
+    case 4: SCN_SLAB_LAUNCH(C32, 4); break;     \
+    default: SCN_SLAB_LAUNCH(C32, 8); break;    \
   }
-  const dim3 grid((unsigned)((tiles + kWarps - 1) / kWarps), (unsigned)(Cout / 32));
-#define SCN_SLAB_LAUNCH(C32)                                                                                          \
-  k_gather_mma_f16_slab<C32, 2><<<grid, kWarps * 32, 0, s>>>(inh, in_stride, map, K, n_out, W4, (int)Cout, bias, out, \
-                                                             out_stride, init, init_stride, e)
   switch ((int)(Cin / 32)) {
-    case 3: SCN_SLAB_LAUNCH(3); break;
-    case 4: SCN_SLAB_LAUNCH(4); break;
-    case 5: SCN_SLAB_LAUNCH(5); break;
-    case 6: SCN_SLAB_LAUNCH(6); break;
-    default: SCN_SLAB_LAUNCH(7); break;
+    case 3: SCN_SLAB_KS(3); break;
+    case 4: SCN_SLAB_KS(4); break;
+    case 5: SCN_SLAB_KS(5); break;
+    case 6: SCN_SLAB_KS(6); break;
+    default: SCN_SLAB_KS(7); break;
   }
+#undef SCN_SLAB_KS
 #undef SCN_SLAB_LAUNCH
   SCN_LAUNCHED();
   return SCN_OK;
@@ -780,11 +876,12 @@ int gather_mma_warp_f16(const void *in, int64_t in_stride, const int32_t *map, i
     return fail(SCN_E_INVALID, "fp16 rows must be 16-byte aligned with a stride that is a multiple of 8 elements");
   const __half *inh = static_cast<const __half *>(in);
   const uint4 *W4 = static_cast<const uint4 *>(Wp);
+  const int vec = rows_vectorisable(out, out_stride, init, init_stride, bias, e) ? 1 : 0;
 #define SCN_F16_LAUNCH(CI, CO, NTR, MINB)                                                                         \
   do {                                                                                                            \
     const long long tiles = (n_out + 8 * NTR - 1) / (8 * NTR);                                                    \
     k_gather_mma_f16<CI, CO, NTR, MINB><<<(unsigned)((tiles + kWarps - 1) / kWarps), kWarps * 32, 0, s>>>(        \
-        inh, in_stride, map, K, n_out, W4, bias, out, out_stride, init, init_stride, e);                          \
+        inh, in_stride, map, K, n_out, W4, bias, out, out_stride, init, init_stride, e, vec);                     \
   } while (0)
   if (Cin == 32 && Cout == 32) SCN_F16_LAUNCH(32, 32, 4, 5);
   else if (Cin == 32 && Cout == 64) SCN_F16_LAUNCH(32, 64, 4, 4);

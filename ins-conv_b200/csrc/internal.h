@@ -213,6 +213,7 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
 int warp_mma_pack_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
 // wide layers on small grids: 16 rows x 32 output planes per warp, whole reduction in one launch
 bool warp_slab_f16_shape(int64_t K, int64_t Cin, int64_t Cout);
+extern int g_slab_share;
 int warp_mma_pack_f16_any(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
 int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,

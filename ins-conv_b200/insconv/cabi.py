@@ -38,6 +38,7 @@ PROTOTYPES = {
     "scn_last_error": (C.c_char_p, []),
     "scn_version": (C.c_char_p, []),
     "scn_launch_count": (C.c_uint64, []),
+    "scn_set_slab_share": (_int, [_int]),
     "scn_n_rulebook_bits": (_int, []),
     "scn_check_errors": (_int, [_p]),
     "scn_metadata_create": (_int, [C.POINTER(_p)]),

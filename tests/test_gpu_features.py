@@ -244,6 +244,49 @@ def test_f16_activations_bn_then_convolutions(cuda, n_in, n_out):
     cabi.check_errors()
 
 
+def test_f16_rows_saturate_instead_of_overflowing(cuda):
+    """Activations beyond the fp16 range (|y| > 65504) are written as +-65504, never as infinity, both by the
+    BatchNorm kernel that writes fp16 rows and by the convolution epilogue that applies a BatchNorm; NaN-free
+    downstream.  Leakiness 1 (no activation) keeps the negative side large too."""
+    import ctypes as C
+    stream = torch.cuda.current_stream().cuda_stream
+    rng = np.random.RandomState(4)
+    n, planes = 4096, 32
+    x = (rng.randn(n, planes) * 1e5).astype(np.float32)  # a third of the entries beyond +-65504
+    one, zero = torch.ones(planes, device=cuda), torch.zeros(planes, device=cuda)
+    xd = torch.from_numpy(x).to(cuda)
+    out = torch.empty(n, planes, dtype=torch.float16, device=cuda)
+    cabi.call("scn_bn_forward_f16", cabi.ptr(xd), planes, cabi.ptr(out), planes, n, planes, cabi.ptr(zero), cabi.ptr(one),
+              cabi.ptr(one), cabi.ptr(zero), 0.0, 1.0, stream)
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all() and got.max() == 65504.0 and got.min() == -65504.0
+    inside = np.abs(x) < 6e4
+    assert np.abs(got[inside] - x[inside]).max() <= 1e-3 * 6e4
+    assert (np.abs(got[np.abs(x) > 65504]) == 65504.0).all()
+    # the same through a convolution epilogue: an SSC that only has its centre offset, rows of size ~100 times 1000
+    m, g = _scene(cuda, 1)
+    h = torch.from_numpy((rng.randn(g.n, planes) * 100).astype(np.float32)).to(cuda).half()
+    w = np.zeros((27, planes, planes), np.float32)
+    w[13] = np.eye(planes) * 1000
+    dw = torch.from_numpy(w).to(cuda)
+    pw = torch.empty(cabi.lib().scn_packed_size_f16(27, planes, planes), dtype=torch.float16, device=cuda)
+    cabi.call("scn_pack_weights_f16", cabi.ptr(dw), 27, planes, planes, cabi.ptr(pw), stream)
+    raw = torch.empty(g.n, planes, dtype=torch.float32, device=cuda)
+    rows = torch.empty(g.n, planes, dtype=torch.float16, device=cuda)
+    epi = cabi.Epilogue(None, 0, cabi.ptr(one), cabi.ptr(zero), 1.0, cabi.ptr(rows), planes, 0)
+    fl = C.c_double(0)
+    cabi.call("scn_ssc_forward_ex", m.h, cabi.size3(128), cabi.ptr(h), planes, cabi.ptr(raw), planes, cabi.ptr(pw), None,
+              planes, planes, cabi.PREC_F16, C.byref(epi), stream, C.byref(fl))
+    torch.cuda.synchronize()
+    cabi.check_errors()
+    want = h.float() * 1000
+    assert float((raw - want).abs().max()) <= 1e-3 * float(want.abs().max())  # the fp32 result is not clipped
+    r = rows.float()
+    assert bool(torch.isfinite(r).all()) and float(r.max()) == 65504.0 and float(r.min()) == -65504.0
+    assert bool((r[want.abs() > 65504].abs() == 65504.0).all())
+
+
 @pytest.mark.parametrize("n_in,n_out", [(96, 96), (128, 160), (160, 128), (224, 224), (192, 32)])
 def test_f16_wide_layers_on_small_grids(cuda, n_in, n_out):
     # a few thousand rows and many planes (the deep levels of a UNet): the slab kernel, 16 rows x 32 output planes per
@@ -402,6 +445,35 @@ def test_tf32_tiny_row_counts(cuda, rows):
     got, _ = m.ssc_forward(4096, torch.from_numpy(xs).to(cuda), torch.from_numpy(ws).to(cuda), None, cabi.PREC_TF32)
     cabi.check_errors()
     close(got, O.conv_forward(xs, ws, O.ssc_rules(g), g.n), TF32_TOL)
+
+
+@pytest.mark.parametrize("n_in,n_out,seed,size", [(64, 256, 0, 128), (256, 256, 0, 128), (256, 256, 1, 64), (32, 256, 3, 128)])
+def test_tf32_256_output_planes_per_tile_kernel(cuda, n_in, n_out, seed, size):
+    """256 output planes with 27 offsets leave too little shared memory for the persistent tcgen05 kernel's
+    stages: these shapes run the one-tile-per-CTA tcgen05 kernel -- through the neighbour map, with the
+    reduction of a tile split over several CTAs on the small scenes (partial sums + reduction kernel) and not
+    split on the large one, with a bias, and with the addend read from the output array itself."""
+    import ctypes as C
+    m, g = _scene(cuda, seed, size)
+    rng = np.random.RandomState(n_in + n_out + seed)
+    x = rng.randn(g.n, n_in).astype(np.float32)
+    w = synth.kaiming_uniform(rng, 27, n_in, n_out)
+    b = rng.randn(n_out).astype(np.float32)
+    want = O.conv_forward(x, w, O.ssc_rules(g), g.n, b)
+    dx, dw, db = torch.from_numpy(x).to(cuda), torch.from_numpy(w).to(cuda), torch.from_numpy(b).to(cuda)
+    got, _ = m.ssc_forward(size, dx, dw, db, precision=cabi.PREC_TF32)
+    cabi.check_errors()
+    close(got, want, TF32_TOL)
+    assert float((got.cpu() - want).abs().max()) / float(want.abs().max()) < 5e-3
+    # out = out + convolution: the addend is the output array (read and written by the same thread of the epilogue)
+    plain, _ = m.ssc_forward(size, dx, dw, None, cabi.PREC_TF32)
+    base = torch.from_numpy(rng.randn(g.n, n_out).astype(np.float32)).to(cuda)
+    out = base.clone()
+    fl = C.c_double(0)
+    cabi.call("scn_ssc_forward_add", m.h, cabi.size3(size), cabi.ptr(dx), n_in, cabi.ptr(out), n_out, cabi.ptr(dw),
+              cabi.ptr(out), n_out, n_in, n_out, cabi.PREC_TF32, torch.cuda.current_stream().cuda_stream, C.byref(fl))
+    cabi.check_errors()
+    assert float((out - (plain + base)).abs().max()) <= 1e-5 * float((plain + base).abs().max())
 
 
 @pytest.mark.parametrize("n_in,n_out", [(64, 32), (96, 128)])

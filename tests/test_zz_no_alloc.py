@@ -3,8 +3,10 @@
 Some hosts hand out all device memory at start-up and must not see a library touch an allocator
 afterwards; for them the library keeps the one piece of scratch this op needs (the transposed weights)
 in a fixed buffer of its own.  The test drives the entry point through the C ABI and checks it against the
-ordinary scn_nin_forward on the tensor-core path, with plane counts that entry point also gives to the tcgen05
-kernel (it hands narrower layers to a warp-level kernel): same kernel, so the results must agree to rounding.
+ordinary scn_nin_forward on the tensor-core path, with plane counts that entry point also gives to a tcgen05
+kernel (it hands narrower layers to a warp-level kernel).  The two entry points run different tcgen05 kernels (one
+tile per CTA here, the persistent kernel there) that add the same tf32 products in the same order of 32-plane steps,
+so the results must agree to fp32 rounding.
 Two calls in a row with different shapes and weights make sure nothing stale in the shared buffer leaks
 from one call into the next.  This file is collected last so that a failure here cannot hide others.
 """
@@ -40,6 +42,52 @@ def test_two_calls_match_the_allocating_entry_point(cuda):
         # and both sit within the tensor-core tolerance of an fp32 product
         ref = x @ w + (b if with_bias else 0)
         assert float((got - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
+def _pool_counters():
+    """(reserved now, reserved high-water mark, used now, used high-water mark) of the device's stream-ordered pool,
+    the one the library's temporaries come from."""
+    rt = C.CDLL("libcudart.so.12")
+    pool = C.c_void_p()
+    assert rt.cudaDeviceGetDefaultMemPool(C.byref(pool), C.c_int(torch.cuda.current_device())) == 0
+    vals = []
+    for attr in (5, 6, 7, 8):  # cudaMemPoolAttrReservedMemCurrent, ReservedMemHigh, UsedMemCurrent, UsedMemHigh
+        v = C.c_uint64(0)
+        assert rt.cudaMemPoolGetAttribute(pool, C.c_int(attr), C.byref(v)) == 0
+        vals.append(v.value)
+    return tuple(vals), rt, pool
+
+
+def test_no_allocator_is_touched(cuda):
+    """Neither the stream-ordered pool of the device (high-water marks reset just before, unchanged after) nor
+    torch's allocator sees the call; the ordinary entry point, run the same way, does move the pool's mark."""
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(30000, 128, generator=g).to(cuda)
+    w = (torch.randn(128, 96, generator=g) * 0.1).to(cuda)
+    out = torch.empty(30000, 96, device=cuda)
+    args = (cabi.ptr(x), 128, cabi.ptr(out), 96, 30000, cabi.ptr(w), None, 128, 96, torch.cuda.current_stream().cuda_stream)
+    cabi.call("scn_nin_forward_noalloc", *args)  # first call: module load, function attributes
+    torch.cuda.synchronize()
+    _, rt, pool = _pool_counters()
+    zero = C.c_uint64(0)
+    for attr in (6, 8):  # high-water marks can be reset to zero = to the current value
+        assert rt.cudaMemPoolSetAttribute(pool, C.c_int(attr), C.byref(zero)) == 0
+    before, _, _ = _pool_counters()
+    torch_before = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
+    for _ in range(3):
+        cabi.call("scn_nin_forward_noalloc", *args)
+    torch.cuda.synchronize()
+    after, _, _ = _pool_counters()
+    assert after == before, (before, after)
+    assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == torch_before
+    cabi.check_errors()
+    # the same probe does see the allocating entry point (it takes its transposed weights from the pool)
+    fl = C.c_double(0)
+    cabi.call("scn_nin_forward", cabi.ptr(x), 128, cabi.ptr(out), 96, 30000, cabi.ptr(w), None, 128, 96, cabi.PREC_TF32,
+              torch.cuda.current_stream().cuda_stream, C.byref(fl))
+    torch.cuda.synchronize()
+    moved, _, _ = _pool_counters()
+    assert moved[3] > before[3], (before, moved)
 
 
 def test_sizes_beyond_the_fixed_buffer_are_refused(cuda):
