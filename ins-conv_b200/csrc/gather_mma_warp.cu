@@ -834,13 +834,13 @@ int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, i
   const uint4 *W4 = static_cast<const uint4 *>(Wp);
   const long long tiles = (n_out + 15) / 16;
   const int vec = rows_vectorisable(out, out_stride, init, init_stride, bias, e) ? 1 : 0;
-  // warps that share a tile's reduction: as few as cover the GPU with about two blocks of 8 warps per SM
-  const long long slabs = Cout / 32;
+  // Warps that share a tile's reduction, from the number of tiles x slabs (warps when nothing is shared).  Measured on
+  // the levels of a 255k-voxel room (us per layer with 1 / 2 / 4 / 8 warps): 14.6k rows 96->96 39 / 35 / 39 / 55,
+  // 192->96 70 / 59 / 59 / 75; 3.5k rows 128->128 23 / 23 / 23 / 25; 2k rows 160->160 28 / 25 / 21 / 23;
+  // 502 rows 192->192 33 / 23 / 14 / 14; 116 rows 224->224 35 / 23 / 16 / 12.
+  const long long slabs = Cout / 32, lone = tiles * slabs;
   int ks = g_slab_share;
-  if (ks != 1 && ks != 2 && ks != 4 && ks != 8) {
-    ks = 1;
-    while (ks < 8 && tiles * slabs * ks < 148 * 16) ks *= 2;
-  }
+  if (ks != 1 && ks != 2 && ks != 4 && ks != 8) ks = lone >= 4000 ? 1 : lone >= 1000 ? 2 : lone >= 150 ? 4 : 8;
   const int tiles_per_block = kSlabWarps / ks;
   const dim3 grid((unsigned)((tiles + tiles_per_block - 1) / tiles_per_block), (unsigned)slabs);
 #define SCN_SLAB_LAUNCH(C32, KS)                                                                                              \

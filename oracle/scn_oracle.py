@@ -3,9 +3,16 @@
 Only tests/, __graft_entry__.smoke() and the cpu_baseline / reference legs of bench.py may import
 this module, and only as the checker or the timed CPU baseline.  Nothing the library ships calls it.
 
-PARITY UNPINNED: the reference repository holds no tests, golden vectors or fixtures for this path
-and its own extension cannot be built in this environment (it needs google sparsehash, a CUDA-9 era
-CUDPP and PyTorch 1.1 APIs), so this restatement is anchored on the reference's source text alone.
+PARITY PINNED AGAINST THE REFERENCE ITSELF: the reference repository holds no tests, golden vectors or
+fixtures for this path, so the restatement is checked against the reference's own code run on the host:
+oracle/build_ref.py compiles the reference's Metadata, rulebook builders and cuda_* / cpu_* operators from the
+sources where they lie (its CUDA kernels run through a CUDA-on-host emulation; CUDPP, which its build vendors, is
+stood in for by its documented contract -- unique-key rank, stable value order, scan, compact), and
+tests/test_oracle_vs_reference.py compares every function of this module with it: site numbering, input rules,
+3x3x3 and 2/2 rulebooks, every full-frame and incremental operator.  Outputs of the reference on seeded inputs are
+committed as tests/golden/ref_*.npz (made by tests/golden/make_golden_ref.py) for machines without the reference
+tree.  What the reference has no semantics for -- voxel deletion, an incremental mode that equals a full
+recompute -- stays unpinned: it is checked against the full recompute only.
 Each function cites the reference lines it follows (paths relative to sparseconvnet/SCN/ of
 THU-luvision/INS-Conv).
 
