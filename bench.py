@@ -430,8 +430,7 @@ def slab_bench(args, rank, world, local, dist):
     coords = synth.building(0, target=args.voxels if args.voxels > 1000000 else 4000000)
     feats = synth.rgb(0, coords.shape[0])
     align = 2 ** (len(PLANES) - 1)
-    cuts = slab.cuts_for(coords[:, 0].min(), coords[:, 0].max(), world, align)
-    assert all(b > a for a, b in zip(cuts, cuts[1:])), "more slabs than aligned cells"
+    cuts = slab.cuts_balanced(coords[:, 0], world, align)
     ext = slab.load_mask(coords, cuts, rank, len(PLANES))
     n_own = int(slab.owned_mask(coords[:, 0], cuts, rank).sum())
     peer = world > 1 and args.halo == "peer"
@@ -500,6 +499,56 @@ def slab_bench(args, rank, world, local, dist):
                           "gpu_launches": int(launches)}))
 
 
+def rooms_bench(args, rank, world, local, dist):
+    """configs[4], first part: 64 independent seeded rooms, scene i on rank i % world (insconv.shard), every rank with its
+    own model copy and one Metadata per scene; no data-path collective.  A step runs every room once; strong scaling
+    (the batch is fixed)."""
+    import torch
+    import sparseconvnet as scn
+    from insconv import shard, synth
+    dev = torch.device("cuda", local)
+    scn.set_precision(args.precision)
+    model = build_model(scn, torch).to(dev)
+    n_scenes = 64
+    mine = shard.scenes_for_rank(n_scenes, rank, world)
+    scenes = []
+    for i in mine:
+        c = synth.room(i, target=args.voxels)
+        scenes.append((torch.from_numpy(c).to(dev), torch.from_numpy(synth.rgb(i, c.shape[0])).to(dev)))
+    voxels = sum(int(c.shape[0]) for c, _ in scenes)
+
+    def step():
+        for c, f in scenes:
+            model([c, f])
+
+    for _ in range(args.warmup):
+        step()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = scn.SCN.launch_count()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = scn.SCN.launch_count() - l0
+    total_voxels, ms = shard.aggregate(dist, dev, voxels, ms)
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": total_voxels * 53 / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None,
+                          "dtype": {"fp32": "f32", "tf32": "tf32", "fp16": "f16"}[args.precision], "data": "synthetic",
+                          "config": {"workload": "configs[4] part 1: 64 seeded rooms (~%d voxels each), scene i on rank i %% %d, "
+                                                 "one full UNet frame per room per step" % (args.voxels, world),
+                                     "scenes": n_scenes, "voxels_total": int(total_voxels), "ms_per_room": ms * world / n_scenes},
+                          "gpu_launches": int(launches)}))
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -557,8 +606,9 @@ def main():
     ap.add_argument("--sweep-frames", type=int, default=100)
     ap.add_argument("--layer", action="store_true", help="time one SSC layer alone (rulebook cached) and exit")
     ap.add_argument("--hash", action="store_true", help="time the grid build alone and exit")
-    ap.add_argument("--workload", default="room", choices=["room", "building"],
-                    help="room: one scene per GPU (default); building: one 4M-voxel scene split into x-slabs")
+    ap.add_argument("--workload", default="room", choices=["room", "building", "rooms64"],
+                    help="room: one scene per GPU (default); building: one 4M-voxel scene split into x-slabs; "
+                         "rooms64: 64 rooms shared out over the GPUs")
     ap.add_argument("--halo", default="peer", choices=["peer", "nccl"],
                     help="building workload: how halo rows travel (own kernels into peer memory, or NCCL send/recv)")
     ap.add_argument("--n-in", type=int, default=32)
@@ -608,6 +658,11 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "rooms64":
+        rooms_bench(args, rank, world, local, dist)
+        if dist is not None:
+            dist.destroy_process_group()
+        return 0
     if args.workload == "building":
         slab_bench(args, rank, world, local, dist)
         if dist is not None:
@@ -658,7 +713,7 @@ def main():
 
     REGIONS = 3
 
-    def timed(fn, steps, warmup, before_region=None):
+    def timed(fn, steps, warmup, before_region=None, end_of_region=None):
         """W warm-up steps, then REGIONS timed regions of exactly K steps each (barrier + device synchronisation on
         both sides, CUDA events, maximum over ranks).  The figure returned is the median region: single steps of
         10-100 ms that have nothing to do with the kernels (the whole virtual machine pauses; see step_host_ms) land
@@ -666,6 +721,8 @@ def main():
         is kept in the JSON line (ms_per_step_of_each_region)."""
         for _ in range(warmup):
             fn()
+        if end_of_region is not None:
+            end_of_region()
         regions = []
         for _ in range(REGIONS):
             if before_region is not None:
@@ -678,6 +735,8 @@ def main():
             for _ in range(steps):
                 fn()
                 stamps.append(time.perf_counter())  # host side only: when each step's launches had been queued
+            if end_of_region is not None:
+                end_of_region()  # work the steps left in flight (the e2e leg's last host read) belongs to the region
             e1.record()
             barrier()
             host_ms = [(b - a) * 1e3 for a, b in zip(stamps, stamps[1:])]
@@ -799,14 +858,40 @@ def main():
         model([d_coords, d_feats])
 
     # ---- e2e: pinned host inputs, host read of the result -------------------------------------------
-    h_out = torch.empty(coords.shape[0], 20, dtype=torch.float32).pin_memory()
+    # As a serving loop would run it: one frame in flight.  Step t queues its input copies and its frame, hands the
+    # result to a copy stream (device -> pinned host, double-buffered) and only then waits for the result of step t-1
+    # and reads it; every step's result reaches the host and is read, the last one inside the timed region (timed()
+    # synchronises the device before it stops the clock and drain() reads what is left).
+    h_outs = [torch.empty(coords.shape[0], 20, dtype=torch.float32).pin_memory() for _ in range(2)]
+    copy_stream = torch.cuda.Stream(device=dev)
+    copied = [torch.cuda.Event(), torch.cuda.Event()]
+    e2e_state = {"t": 0, "pending": None, "checksum": 0.0}
+
+    def e2e_read(i):
+        copied[i].synchronize()
+        e2e_state["checksum"] += float(h_outs[i][0, 0]) + float(h_outs[i][-1, -1])  # the host touches the result
 
     def e2e_frame():
+        i = e2e_state["t"] & 1
         y = model([h_coords, h_feats.to(dev, non_blocking=True)])
-        h_out.copy_(y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the host reads the result every step
+        done = torch.cuda.Event()
+        done.record()
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(done)
+            h_outs[i].copy_(y, non_blocking=True)
+            copied[i].record()
+        y.record_stream(copy_stream)
+        if e2e_state["pending"] is not None:
+            e2e_read(e2e_state["pending"])
+        e2e_state["pending"] = i
+        e2e_state["t"] += 1
 
-    ms_e2e, _ = timed(e2e_frame, args.steps, args.warmup) if "e2e" in legs else (float("nan"), 0)
+    def e2e_drain():
+        if e2e_state["pending"] is not None:
+            e2e_read(e2e_state["pending"])
+            e2e_state["pending"] = None
+
+    ms_e2e, _ = timed(e2e_frame, args.steps, args.warmup, end_of_region=e2e_drain) if "e2e" in legs else (float("nan"), 0)
     # the same full frame in the other precisions (fewer steps: these are reported beside the headline, not as it)
     other = {}
     if "precisions" in legs:
@@ -879,7 +964,10 @@ def main():
                                                "equal to a full recompute, kept scene advances"},
             "sweep": sweep,
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": int(h2d),
-                    "d2h_bytes_per_step": int(d2h)},
+                    "d2h_bytes_per_step": int(d2h),
+                    "pipelining": "one frame in flight: the host waits for and reads step t-1's result (pinned, copied on "
+                                  "a second stream) after queueing step t; every step's result is read, the last inside "
+                                  "the timed region"},
             "gpu_launches": int(launches) * args.steps,
             # host time between the ends of consecutive steps of each timed leg (full, incremental, exact, e2e as
             # run): a single step far above the median is a stall of the host or the driver, not of the kernels

@@ -173,8 +173,13 @@ static int need_incre(scn_metadata *m, scn_metadata *pre, const int64_t *size, G
     dev_free(x.up2, s);
     x = IncreMaps();
     x.pre = pre;
-    SCN_TRY(dev_alloc_t(&x.pre_exist, (size_t)(*g)->n, s));
-    SCN_TRY(grid_query(**pg, (*g)->coords, (*g)->n, (*g)->n, x.pre_exist, true, s));
+    int r = dev_alloc_t(&x.pre_exist, (size_t)(*g)->n, s);
+    if (r == SCN_OK) r = grid_query(**pg, (*g)->coords, (*g)->n, (*g)->n, x.pre_exist, true, s);
+    if (r != SCN_OK) {  // no half-made entry: the next call starts over
+      dev_free(x.pre_exist, s);
+      x = IncreMaps();
+      return r;
+    }
   }
   *im = &x;
   return SCN_OK;

@@ -1341,6 +1341,8 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
   const int T = 256;
   LevelRecord *rec_d = nullptr;
   SCN_TRY(dev_alloc_t(&rec_d, (size_t)count, s));
+  Tmp rec_guard(s);  // released on every way out
+  rec_guard.p = rec_d;
   SCN_CUDA(cudaMemsetAsync(rec_d, 0, (size_t)count * sizeof(LevelRecord), s));
   Box box = fine0.box;
   int64_t bound = fine0.n;  // upper bound of the site count of the source level (exact for the first level)
@@ -1393,10 +1395,13 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
     g.fine_up = reinterpret_cast<int32_t *>(g.arena + o_up);
     if (with_ssc) g.nbr = reinterpret_cast<int32_t *>(g.arena + o_nbr);
     // the record was zeroed with the others: no error, and the scan leaves the site count in it
-    SCN_CUDA(cudaMemsetAsync(g.bitmap, 0, (size_t)nwords * 8, s));
+    if (cudaMemsetAsync(g.bitmap, 0, (size_t)nwords * 8, s) != cudaSuccess ||
+        cudaMemsetAsync(g.child, 0xFF, (size_t)n_max * 8 * 4, s) != cudaSuccess) {
+      rc = fail(SCN_E_CUDA, "coarse grid build: memset failed");
+      break;
+    }
     k_mark_soa<<<blocks_for(n_src, T), T, 0, s>>>(src_coords, n_src, 1, bx, g.bitmap, src);
     if ((rc = scan_emit(PopcWords{g.bitmap}, StorePrefix{g.prefix}, nwords, &info_d->n_unique, s)) != SCN_OK) break;
-    SCN_CUDA(cudaMemsetAsync(g.child, 0xFF, (size_t)n_max * 8 * 4, s));
     k_conv_maps<<<blocks_for(n_src, 256), 256, 0, s>>>(src_coords, n_src, nullptr, 0, g.child, g.fine_up, counts_d, info_d, src,
                                                        bx, g.bitmap, g.prefix, g.src_row, g.coords);
     if (with_ssc) {
@@ -1421,7 +1426,6 @@ int grid_build_coarse_chain(Grid *const *levels, int count, const Grid &fine0, b
       rc = fail(SCN_E_CUDA, std::string("coarse grid build: ") + cudaGetErrorString(cudaGetLastError()));
     else if (land != rec.data()) memcpy(rec.data(), land, bytes);
   }
-  dev_free(rec_d, s);
   if (rc != SCN_OK) {
     for (int l = 0; l < count; ++l) grid_free(*levels[l], s);
     return rc;

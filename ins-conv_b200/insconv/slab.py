@@ -33,6 +33,35 @@ def cuts_for(x_lo, x_hi, world, align):
     return cuts
 
 
+def cuts_balanced(x, world, align):
+    """world+1 cut positions, multiples of `align`, that split the points (x: their x coordinates) into slabs whose
+    largest point count is as small as the alignment allows (dynamic programme over the aligned cells); every slab
+    is at least one cell wide."""
+    x = np.asarray(x, dtype=np.int64)
+    a_lo = (int(x.min()) // align) * align
+    a_hi = ((int(x.max()) + align) // align) * align
+    cells = (a_hi - a_lo) // align
+    if cells < world:
+        raise ValueError("more slabs than aligned cells")
+    before = np.concatenate([[0], np.cumsum(np.bincount((x - a_lo) // align, minlength=cells))])  # points left of cell i
+    # best[r][i]: smallest possible maximum over r slabs covering cells [0, i)
+    inf = float("inf")
+    best = [[inf] * (cells + 1) for _ in range(world + 1)]
+    arg = [[0] * (cells + 1) for _ in range(world + 1)]
+    best[0][0] = 0
+    for r in range(1, world + 1):
+        for i in range(r, cells - (world - r) + 1):
+            for j in range(r - 1, i):
+                v = max(best[r - 1][j], before[i] - before[j])
+                if v < best[r][i]:
+                    best[r][i], arg[r][i] = v, j
+    cuts, i = [cells], cells
+    for r in range(world, 0, -1):
+        i = arg[r][i]
+        cuts.append(i)
+    return [a_lo + align * i for i in reversed(cuts)]
+
+
 def extended_mask(x, cuts, rank, align):
     """Points a rank loads, simple variant: its slab plus `align` voxels of ghost zone on each side."""
     return (x >= cuts[rank] - align) & (x < cuts[rank + 1] + align)

@@ -90,6 +90,17 @@ def test_cuts_are_aligned_and_cover():
         cuts = slab.cuts_for(8, 2007, world, 64)
         assert len(cuts) == world + 1 and cuts[0] <= 8 and cuts[-1] > 2007
         assert all(c % 64 == 0 for c in cuts) and all(b >= a for a, b in zip(cuts, cuts[1:]))
+    rng = np.random.RandomState(0)
+    pts = np.concatenate([rng.randint(8, 500, 30000), rng.randint(500, 2008, 10000)])  # three quarters in the first quarter
+    for world in (1, 2, 4, 8):
+        cuts = slab.cuts_balanced(pts, world, 64)
+        assert len(cuts) == world + 1 and cuts[0] <= 8 and cuts[-1] > 2007
+        assert all(c % 64 == 0 for c in cuts) and all(b > a for a, b in zip(cuts, cuts[1:]))
+        own = [int(slab.owned_mask(pts, cuts, r).sum()) for r in range(world)]
+        assert sum(own) == pts.size
+        even = [int(slab.owned_mask(pts, slab.cuts_for(8, 2007, world, 64), r).sum()) for r in range(world)]
+        assert max(own) <= max(even)
+    assert slab.cuts_balanced(np.array([5, 70, 130]), 3, 64) == [0, 64, 128, 192]
     x = np.arange(0, 300)
     cuts = slab.cuts_for(0, 299, 2, 64)
     assert (slab.owned_mask(x, cuts, 0) ^ slab.owned_mask(x, cuts, 1)).all()
