@@ -389,6 +389,37 @@ SCN_API int scn_halo_exchange(scn_halo *h, const int64_t *rows, const int64_t *c
                               int64_t a_row_bytes, void *b, int64_t b_row_bytes, void *stream);
 SCN_API int scn_halo_status(scn_halo *h, int *timed_out, int *overflow, void *stream);
 
+/* ---- label fusion: the per-voxel vote table behind the network --------------------------------------------
+ * Replaces Result<3> (Metadata/resultHash.h:22-138; bound as Result_3, pybind.cpp:36-45) and ResultOfWeight<3>
+ * (resultHash.h:141-218; pybind.cpp:275-282): host hash maps there, a device-resident open-addressing table here.
+ * weight_classes = 0: vote table, an entry is (label, confidence); > 0: weight table, an entry is a vector of that
+ * many scores.  maximum: the cap of the confidence (the reference stores its float argument in an int member, so
+ * its default 0.7 acts as 0; pass what the reference would hold).  points: device int64 [n, ncols], ncols 3 (x,y,z)
+ * or 4 (+ batch index), coordinates in the library's key range; scores: device fp32 [n, classes] with the given row
+ * stride.  Rows of one call that name the same voxel are applied in row order.
+ *   update  vote: new voxel -> (argmax, max score); known voxel, same label -> confidence = min(maximum, confidence +
+ *           score); other label -> confidence -= score, and below zero the label flips and the confidence changes
+ *           sign (resultHash.h:62-98).  weight: new -> the row; known -> 0.5 * old + row (resultHash.h:146-158)
+ *   set     vote table only: (argmax, confidence 0) whatever was there (resultHash.h:37-50)
+ *   query   labels[i] = label (weight table: argmax of the vector) or -1 (multiQuery, resultHash.h:108-117)
+ *   size    number of entries; synchronises the stream and reports coordinates outside the key range
+ *           (SCN_E_RANGE) seen by earlier calls; rows_applied_serially (optional): rows of the last update that were
+ *           not the first of their voxel
+ *   dump    every entry as int64 (x, y, z, label), in no particular order (get_all_points_labels)
+ *   finalize  keeps only the entries named by the points (resultHash.h:128-138) */
+typedef struct scn_labels scn_labels;
+SCN_API int scn_labels_create(scn_labels **out, int weight_classes, double maximum);
+SCN_API void scn_labels_destroy(scn_labels *h);
+SCN_API int scn_labels_clear(scn_labels *h, void *stream);
+SCN_API int scn_labels_update(scn_labels *h, const int64_t *points, int ncols, int64_t n, const float *scores,
+                              int64_t scores_stride, int64_t classes, void *stream);
+SCN_API int scn_labels_set(scn_labels *h, const int64_t *points, int ncols, int64_t n, const float *scores,
+                           int64_t scores_stride, int64_t classes, void *stream);
+SCN_API int scn_labels_query(scn_labels *h, const int64_t *points, int ncols, int64_t n, int64_t *labels, void *stream);
+SCN_API int scn_labels_size(scn_labels *h, int64_t *size, int64_t *rows_applied_serially, void *stream);
+SCN_API int scn_labels_dump(scn_labels *h, int64_t *out, int64_t capacity_rows, int64_t *n_written, void *stream);
+SCN_API int scn_labels_finalize(scn_labels *h, const int64_t *points, int ncols, int64_t n, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

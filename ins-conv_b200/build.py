@@ -17,7 +17,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(ROOT, "include")
 LIB = os.path.join(HERE, "libinsconv_b200.so")
-CU_SOURCES = ["capi.cu", "grid_build.cu", "feature_ops.cu", "gather_gemm_tc.cu", "gather_mma_warp.cu", "halo_exchange.cu"]
+CU_SOURCES = ["capi.cu", "grid_build.cu", "feature_ops.cu", "gather_gemm_tc.cu", "gather_mma_warp.cu", "halo_exchange.cu", "label_fusion.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

@@ -579,6 +579,112 @@ void no_backward(pybind11::args, pybind11::kwargs) {
   throw std::runtime_error("this build of sparseconvnet.SCN is inference only: backward passes are not part of the hot path");
 }
 
+
+// ---- label fusion (Result_3, ResultOfWeight: sparseconvnet/SCN/pybind.cpp:36-45, 275-282) ------------------------
+// Same method names and argument meaning as the reference's classes; points may be CPU or CUDA LongTensors, scores CPU
+// or CUDA float tensors (they are moved to the GPU, where the table lives); query results come back as the reference
+// returns them, CPU LongTensors.
+class LabelTable {
+ public:
+  // weight_classes < 0: a weight table whose vector length is taken from the first update
+  LabelTable(int weight_classes, double maximum) : classes_(weight_classes), maximum_(maximum) {
+    if (weight_classes >= 0) check(scn_labels_create(&h_, weight_classes, maximum), "label table");
+  }
+  ~LabelTable() { scn_labels_destroy(h_); }
+  LabelTable(const LabelTable &) = delete;
+  LabelTable &operator=(const LabelTable &) = delete;
+
+  void update(at::Tensor ps, at::Tensor label) { apply(ps, label, false); }
+  void set(at::Tensor ps, at::Tensor label) {
+    if (ps.dim() == 1) {
+      ps = ps.unsqueeze(0);
+      label = label.unsqueeze(0);
+    }
+    apply(ps, label, true);
+  }
+  at::Tensor multiQuery(at::Tensor ps) {
+    auto p = points(ps);
+    auto out = at::empty({p.size(0)}, p.options());
+    if (!h_) return out.fill_(-1).cpu();
+    check(scn_labels_query(h_, p.data_ptr<int64_t>(), (int)p.size(1), p.size(0), out.data_ptr<int64_t>(), stream_of(p)),
+          "multiQuery");
+    sync_status(p);
+    return out.cpu();
+  }
+  int64_t query(at::Tensor p) {
+    TORCH_CHECK(p.dim() == 1, "query takes one point");
+    return multiQuery(p.unsqueeze(0))[0].item<int64_t>();
+  }
+  at::Tensor get_all_points_labels() {
+    auto opts = at::TensorOptions().dtype(at::kLong).device(at::kCUDA);
+    if (!h_) return at::empty({0, 4}, at::TensorOptions().dtype(at::kLong));
+    auto stream = (void *)c10::cuda::getCurrentCUDAStream().stream();
+    int64_t n = 0;
+    check(scn_labels_size(h_, &n, nullptr, stream), "get_all_points_labels");
+    auto out = at::empty({n, 4}, opts);
+    int64_t written = 0;
+    check(scn_labels_dump(h_, out.data_ptr<int64_t>(), n, &written, stream), "get_all_points_labels");
+    return out.narrow(0, 0, written).cpu();
+  }
+  void finalize(at::Tensor ps) {
+    if (!h_) return;
+    auto p = points(ps);
+    check(scn_labels_finalize(h_, p.data_ptr<int64_t>(), (int)p.size(1), p.size(0), stream_of(p)), "finalize");
+  }
+  void clear() {
+    if (h_) check(scn_labels_clear(h_, (void *)c10::cuda::getCurrentCUDAStream().stream()), "clear");
+  }
+  int64_t size() {
+    if (!h_) return 0;
+    int64_t n = 0;
+    check(scn_labels_size(h_, &n, nullptr, (void *)c10::cuda::getCurrentCUDAStream().stream()), "size");
+    return n;
+  }
+  int64_t rowsAppliedSerially() {
+    if (!h_) return 0;
+    int64_t n = 0, later = 0;
+    check(scn_labels_size(h_, &n, &later, (void *)c10::cuda::getCurrentCUDAStream().stream()), "size");
+    return later;
+  }
+
+ private:
+  static at::Tensor points(const at::Tensor &ps) {
+    TORCH_CHECK(ps.dim() == 2 && (ps.size(1) == 3 || ps.size(1) == 4) && ps.scalar_type() == at::kLong,
+                "points must be a LongTensor [n, 3] or [n, 4]");
+    return ps.to(at::kCUDA).contiguous();
+  }
+  void apply(const at::Tensor &ps, const at::Tensor &label, bool set) {
+    auto p = points(ps);
+    TORCH_CHECK(label.dim() == 2 && label.size(0) == p.size(0) && label.size(1) >= 1, "scores must be [n, classes]");
+    auto sc = label.to(at::kCUDA, at::kFloat).contiguous();
+    if (!h_) {  // weight table: the vector length is that of the first scores seen
+      classes_ = (int)sc.size(1);
+      check(scn_labels_create(&h_, classes_, maximum_), "label table");
+    }
+    auto fn = set ? scn_labels_set : scn_labels_update;
+    check(fn(h_, p.data_ptr<int64_t>(), (int)p.size(1), p.size(0), sc.data_ptr<float>(), sc.stride(0), sc.size(1), stream_of(p)),
+          set ? "set" : "update");
+  }
+  void sync_status(const at::Tensor &p) {
+    int64_t n = 0;
+    check(scn_labels_size(h_, &n, nullptr, stream_of(p)), "label table");
+  }
+  scn_labels *h_ = nullptr;
+  int classes_;
+  double maximum_;
+};
+
+// Result<3>: `int maximum` initialised from a float (resultHash.h:24-29) -- the default 0.7 is held as 0
+class Result3 : public LabelTable {
+ public:
+  Result3() : LabelTable(0, (double)(int)0.7f) {}
+  explicit Result3(float maximum) : LabelTable(0, (double)(int)maximum) {}
+};
+class ResultOfWeight3 : public LabelTable {
+ public:
+  ResultOfWeight3() : LabelTable(-1, 0.0) {}
+};
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
@@ -586,6 +692,27 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
   // default of every optional tensor argument: an empty tensor (the interface's "no bias" convention), so that calls
   // with the reference's own argument lists work as they are
   const at::Tensor none = at::empty({0});
+  pybind11::class_<Result3>(mod, "Result_3")
+      .def(pybind11::init<>())
+      .def(pybind11::init<float>())
+      .def("set", &Result3::set)
+      .def("query", &Result3::query)
+      .def("multiQuery", &Result3::multiQuery)
+      .def("clear", &Result3::clear)
+      .def("update", &Result3::update)
+      .def("get_all_points_labels", &Result3::get_all_points_labels)
+      .def("finalize", &Result3::finalize)
+      .def("size", &Result3::size)
+      .def("rowsAppliedSerially", &Result3::rowsAppliedSerially);
+  pybind11::class_<ResultOfWeight3>(mod, "ResultOfWeight")
+      .def(pybind11::init<>())
+      .def("query", &ResultOfWeight3::query)
+      .def("multiQuery", &ResultOfWeight3::multiQuery)
+      .def("clear", &ResultOfWeight3::clear)
+      .def("update", &ResultOfWeight3::update)
+      .def("get_all_points_labels", &ResultOfWeight3::get_all_points_labels)
+      .def("finalize", &ResultOfWeight3::finalize)
+      .def("size", &ResultOfWeight3::size);
   pybind11::class_<Metadata3>(mod, "Metadata_3")
       .def(pybind11::init<>())
       .def("clear", &Metadata3::clear)

@@ -112,6 +112,18 @@ PROTOTYPES.update({
     "scn_halo_status": (_int, [_p, C.POINTER(_int), C.POINTER(_int), _p]),
 })
 
+PROTOTYPES.update({
+    "scn_labels_create": (_int, [C.POINTER(_p), _int, _dbl]),
+    "scn_labels_destroy": (None, [_p]),
+    "scn_labels_clear": (_int, [_p, _p]),
+    "scn_labels_update": (_int, [_p, _p, _int, _i64, _p, _i64, _i64, _p]),
+    "scn_labels_set": (_int, [_p, _p, _int, _i64, _p, _i64, _i64, _p]),
+    "scn_labels_query": (_int, [_p, _p, _int, _i64, _p, _p]),
+    "scn_labels_size": (_int, [_p, _i64p, _i64p, _p]),
+    "scn_labels_dump": (_int, [_p, _p, _i64, _i64p, _p]),
+    "scn_labels_finalize": (_int, [_p, _p, _int, _i64, _p]),
+})
+
 _STATUS = {n for n, (r, _) in PROTOTYPES.items() if r is _int and n not in ("scn_n_rulebook_bits", "scn_weights_packable")}
 
 

@@ -37,7 +37,7 @@ CU_FILES = ["CUDA/CUDPPWrapper.cu", "CUDA/SubmanifoldRules_cuda.cu", "CUDA/IOLay
 HOST_AFTER = ["CUDA/Convolution.cpp", "CUDA/Deconvolution.cpp", "CUDA/BatchNormalization.cpp", "CUDA/IOLayers.cpp",
               "CUDA/NetworkInNetwork.cpp",
               "CPU/Convolution.cpp", "CPU/Deconvolution.cpp", "CPU/BatchNormalization.cpp", "CPU/IOLayers.cpp",
-              "CPU/NetworkInNetwork.cpp"]
+              "CPU/NetworkInNetwork.cpp", "Metadata/resultHash.h"]
 OWN = ["ref_prelude.h", "ref_emu.h", "ref_cudpp.h", "ref_exports.cpp", "build_ref.py"]
 
 
@@ -160,6 +160,8 @@ def build(reference=DEFAULT_REFERENCE, force=False, verbose=False):
            "-I" + HERE, "-I" + os.path.join(HERE, "ref_shim"), "-I" + ref_scn, "-I" + os.path.join(ref_scn, "CUDA"),
            "-I" + os.path.join(reference, "extra", "cudpp", "include")]
     cmd += ["-I" + p for p in ce.include_paths() if "cuda" not in p.lower().split(os.sep)[-2:]]
+    import sysconfig
+    cmd += ["-I" + sysconfig.get_paths()["include"]]  # resultHash.h includes torch/extension.h, which wants Python.h
     cmd += ["-L" + lib_dir, "-ltorch_cpu", "-ltorch", "-lc10", "-Wl,-rpath," + lib_dir]
     if verbose:
         print(" ".join(cmd), flush=True)

@@ -224,4 +224,46 @@ int ref_cpu_output_forward(void *m, const float *in, long rows, long planes) {
   REF_GUARD(g_out = at::empty({0}, at::kFloat); cpu_OutputLayer_updateOutput<float, 3>(M(m), f32(in, rows, planes), g_out))
 }
 
+
+// ---- label fusion: Result<3> and ResultOfWeight<3> (Metadata/resultHash.h) -------------------------------
+void *ref_result_new(float maximum) { return new Result<3>(maximum); }
+void ref_result_free(void *r) { delete static_cast<Result<3> *>(r); }
+int ref_result_update(void *r, const long *pts, long n, const float *scores, long classes) {
+  REF_GUARD(static_cast<Result<3> *>(r)->update(coords_tensor(pts, n, 3), f32(scores, n, classes)))
+}
+int ref_result_set(void *r, const long *pts, long n, const float *scores, long classes) {
+  REF_GUARD(static_cast<Result<3> *>(r)->set(coords_tensor(pts, n, 3), f32(scores, n, classes)))
+}
+int ref_result_multiquery(void *r, const long *pts, long n, long *out) {
+  REF_GUARD(at::Tensor t = static_cast<Result<3> *>(r)->multiQuery(coords_tensor(pts, n, 3));
+            std::memcpy(out, t.data_ptr<long>(), sizeof(long) * n))
+}
+long ref_result_size(void *r) { return (long)static_cast<Result<3> *>(r)->result.size(); }
+int ref_result_all(void *r, long *out) {
+  REF_GUARD(at::Tensor t = static_cast<Result<3> *>(r)->get_all_points_labels().contiguous();
+            std::memcpy(out, t.data_ptr<long>(), sizeof(long) * t.numel()))
+}
+int ref_result_finalize(void *r, const long *pts, long n) { REF_GUARD(static_cast<Result<3> *>(r)->finalize(coords_tensor(pts, n, 3))) }
+// the confidence of one voxel (not exposed by the reference's binding; read from its map for the comparison)
+float ref_result_confidence(void *r, long x, long y, long z) {
+  Point<3> p;
+  p[0] = x, p[1] = y, p[2] = z;
+  auto &m = static_cast<Result<3> *>(r)->result;
+  auto it = m.find(p);
+  return it == m.end() ? -1.f : it->second.second;
+}
+
+void *ref_weight_new() { return new ResultOfWeight<3>(); }
+void ref_weight_free(void *r) { delete static_cast<ResultOfWeight<3> *>(r); }
+int ref_weight_update(void *r, const long *pts, long n, const float *scores, long classes) {
+  REF_GUARD(static_cast<ResultOfWeight<3> *>(r)->update(coords_tensor(pts, n, 3), f32(scores, n, classes).clone()))
+}
+int ref_weight_multiquery(void *r, const long *pts, long n, long *out) {
+  REF_GUARD(at::Tensor t = static_cast<ResultOfWeight<3> *>(r)->multiQuery(coords_tensor(pts, n, 3));
+            std::memcpy(out, t.data_ptr<long>(), sizeof(long) * n))
+}
+long ref_weight_size(void *r) { return (long)static_cast<ResultOfWeight<3> *>(r)->result.size(); }
+int ref_weight_finalize(void *r, const long *pts, long n) {
+  REF_GUARD(static_cast<ResultOfWeight<3> *>(r)->finalize(coords_tensor(pts, n, 3)))
+}
 }  // extern "C"

@@ -3,6 +3,7 @@
 #pragma once
 #include <ATen/ATen.h>
 #include <torch/types.h>
+#include <torch/extension.h>  // Metadata/resultHash.h includes it; it must be seen before CUDA is redefined below
 #include <cassert>
 #include <iostream>
 #include <memory>

@@ -254,3 +254,87 @@ def cpu_output_forward(m, x):
     x, xp = _f(x)
     _check(lib().ref_cpu_output_forward(m.h, xp, _c(x.shape[0]), _c(x.shape[1])))
     return _result_f32()
+
+
+# ---- label fusion: the reference's Result<3> / ResultOfWeight<3> (Metadata/resultHash.h) ---------------------------
+def _pts(ps):
+    p = np.ascontiguousarray(np.asarray(ps, np.int64)[:, :3])
+    return p, p.ctypes.data_as(_L)
+
+
+class Result(object):
+    def __init__(self, maximum=0.7):
+        L = lib()
+        L.ref_result_new.restype = ctypes.c_void_p
+        L.ref_result_new.argtypes = [ctypes.c_float]
+        L.ref_result_size.restype = ctypes.c_long
+        L.ref_result_confidence.restype = ctypes.c_float
+        self.h = ctypes.c_void_p(L.ref_result_new(ctypes.c_float(maximum)))
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().ref_result_free(self.h)
+            self.h = None
+
+    def _apply(self, fn, ps, label):
+        p, pp = _pts(ps)
+        s = np.ascontiguousarray(label, np.float32)
+        _check(fn(self.h, pp, ctypes.c_long(p.shape[0]), s.ctypes.data_as(_F), ctypes.c_long(s.shape[1])))
+
+    def update(self, ps, label):
+        self._apply(lib().ref_result_update, ps, label)
+
+    def set(self, ps, label):
+        self._apply(lib().ref_result_set, ps, label)
+
+    def multiQuery(self, ps):
+        p, pp = _pts(ps)
+        out = np.empty(p.shape[0], np.int64)
+        _check(lib().ref_result_multiquery(self.h, pp, ctypes.c_long(p.shape[0]), out.ctypes.data_as(_L)))
+        return out
+
+    def size(self):
+        return int(lib().ref_result_size(self.h))
+
+    def get_all_points_labels(self):
+        out = np.empty((self.size(), 4), np.int64)
+        _check(lib().ref_result_all(self.h, out.ctypes.data_as(_L)))
+        return out
+
+    def finalize(self, ps):
+        p, pp = _pts(ps)
+        _check(lib().ref_result_finalize(self.h, pp, ctypes.c_long(p.shape[0])))
+
+    def confidence(self, x, y, z):
+        return float(lib().ref_result_confidence(self.h, ctypes.c_long(x), ctypes.c_long(y), ctypes.c_long(z)))
+
+
+class ResultOfWeight(object):
+    def __init__(self):
+        L = lib()
+        L.ref_weight_new.restype = ctypes.c_void_p
+        L.ref_weight_size.restype = ctypes.c_long
+        self.h = ctypes.c_void_p(L.ref_weight_new())
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().ref_weight_free(self.h)
+            self.h = None
+
+    def update(self, ps, label):
+        p, pp = _pts(ps)
+        s = np.ascontiguousarray(label, np.float32)
+        _check(lib().ref_weight_update(self.h, pp, ctypes.c_long(p.shape[0]), s.ctypes.data_as(_F), ctypes.c_long(s.shape[1])))
+
+    def multiQuery(self, ps):
+        p, pp = _pts(ps)
+        out = np.empty(p.shape[0], np.int64)
+        _check(lib().ref_weight_multiquery(self.h, pp, ctypes.c_long(p.shape[0]), out.ctypes.data_as(_L)))
+        return out
+
+    def size(self):
+        return int(lib().ref_weight_size(self.h))
+
+    def finalize(self, ps):
+        p, pp = _pts(ps)
+        _check(lib().ref_weight_finalize(self.h, pp, ctypes.c_long(p.shape[0])))

@@ -10,6 +10,9 @@ files.  Inputs are not stored: tests regenerate them from the seeds with insconv
                   boxes-and-spheres scene (seed 3: 50,208 voxels in a 128^3 grid), Kaiming-uniform weights
   ref_c2.npz      configs[1], the part the reference has semantics for (insert + re-draw; it has no
                   deletion): frame t+1's new points through Incre_InputLayer and Incre_SubmanifoldConvolution
+  ref_labels.npz  label fusion: Result<3> (default cap and cap 3) and ResultOfWeight<3> after the seeded frames of
+                  tests/labels_cases.py -- labels of every scene voxel after each frame, confidences, after
+                  finalize and after set
   ref_chain.npz   InputLayer -> SSC 16->32 -> BatchNormReLU -> Convolution 32->96 /2 -> SSC 96->96 ->
                   Deconvolution 96->32 -> OutputLayer, full frame then incremental frame, every operator the
                   reference's (the network of __graft_entry__.smoke())
@@ -140,6 +143,32 @@ def main():
         d[name + "_colsum"] = np.asarray(x, np.float64).sum(0)
     np.savez_compressed(os.path.join(HERE, "ref_chain.npz"), **d)
     print("ref_chain: full %s, incremental %s" % (full.shape, inc.shape))
+
+    # ---- label fusion: the reference's Result<3> / ResultOfWeight<3> on seeded frames of scores ----
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from labels_cases import frames
+    d = {}
+    for name, maximum in (("default", 0.7), ("cap3", 3.0)):
+        scene, fr = frames(0)
+        r = R.Result(maximum)
+        per_frame = []
+        for ps, sc in fr:
+            r.update(ps, sc)
+            per_frame.append(r.multiQuery(scene).astype(np.int8))
+        d[name + "_labels_after_each_frame"] = np.stack(per_frame)
+        d[name + "_confidence"] = np.array([r.confidence(*[int(v) for v in p]) for p in scene], np.float32)
+        d[name + "_size"] = np.array(r.size())
+        r.finalize(scene[::3])
+        d[name + "_labels_after_finalize"] = r.multiQuery(scene).astype(np.int8)
+        r.set(scene[:50], fr[0][1][:50])
+        d[name + "_labels_after_set"] = r.multiQuery(scene).astype(np.int8)
+    w = R.ResultOfWeight()
+    for ps, sc in fr:
+        w.update(ps, sc)
+    d["weight_labels"] = w.multiQuery(scene).astype(np.int8)
+    d["scene_digest"] = digest(scene)
+    np.savez_compressed(os.path.join(HERE, "ref_labels.npz"), **d)
+    print("ref_labels: %d voxels, %d frames" % (scene.shape[0], len(fr)))
 
 
 if __name__ == "__main__":

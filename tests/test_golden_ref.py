@@ -179,3 +179,28 @@ def test_committed_model_fixture_is_what_the_reference_builds_today():
     ) % os.path.join(HERE, "golden")], capture_output=True, text=True, check=True)
     with open(os.path.join(HERE, "golden", "ref_model.json")) as f:
         assert json.loads(r.stdout.strip().splitlines()[-1]) == json.load(f)
+
+
+def test_label_fusion_oracle_equals_the_reference_vectors():
+    """oracle/scn_labels.py against what the reference's Result<3> / ResultOfWeight<3> produced (ref_labels.npz)."""
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from labels_cases import frames
+    from oracle import scn_labels as L
+    fx = load("ref_labels.npz")
+    for name, maximum in (("default", 0.7), ("cap3", 3.0)):
+        scene, fr = frames(0)
+        assert np.array_equal(G.digest(scene), fx["scene_digest"]), "the case generator changed: regenerate the fixtures"
+        o = L.Result(maximum)
+        for f, (ps, sc) in enumerate(fr):
+            o.update(ps, sc)
+            assert np.array_equal(o.multiQuery(scene), fx[name + "_labels_after_each_frame"][f])
+        conf = np.array([o.result.get(tuple(int(v) for v in p), (0, -1.0))[1] for p in scene], np.float32)
+        assert np.array_equal(conf, fx[name + "_confidence"]) and len(o.result) == int(fx[name + "_size"])
+        o.finalize(scene[::3])
+        assert np.array_equal(o.multiQuery(scene), fx[name + "_labels_after_finalize"])
+        o.set(scene[:50], fr[0][1][:50])
+        assert np.array_equal(o.multiQuery(scene), fx[name + "_labels_after_set"])
+    w = L.ResultOfWeight()
+    for ps, sc in fr:
+        w.update(ps, sc)
+    assert np.array_equal(w.multiQuery(scene), fx["weight_labels"])

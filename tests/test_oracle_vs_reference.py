@@ -244,3 +244,40 @@ def test_incremental_maps_and_operators(R):
     vox, pvox = rng.randn(g.n, 8).astype(np.float32), rng.randn(pg.n, 8).astype(np.float32)
     want = O.incre_output_forward(vox, g, pg, pvox).numpy()
     assert rel(R.incre_output_layer(m, vox, pre, pvox), want) <= 1e-6
+
+
+def test_label_fusion_equals_the_reference_classes():
+    """Result<3> (votes with a confidence, with the default cap -- held as 0 by the reference's int member -- and with
+    a cap of 3) and ResultOfWeight<3> over six frames of scores that revisit voxels with agreeing and disagreeing
+    labels and name some voxels twice in one call: labels after every frame, every confidence, finalize, set."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from labels_cases import frames
+    from oracle import scn_labels as L
+    for maximum in (0.7, 3.0):
+        scene, fr = frames(1)
+        r, o = R.Result(maximum), L.Result(maximum)
+        for ps, sc in fr:
+            r.update(ps, sc)
+            o.update(ps, sc)
+            assert np.array_equal(r.multiQuery(scene), o.multiQuery(scene))
+        assert r.size() == len(o.result)
+        for k, (lab, conf) in o.result.items():
+            assert r.confidence(*k) == float(conf), k
+        got = r.get_all_points_labels()
+        assert {tuple(v) for v in got.tolist()} == {tuple(v) for v in o.get_all_points_labels().tolist()}
+        r.finalize(scene[::3])
+        o.finalize(scene[::3])
+        assert r.size() == len(o.result) and np.array_equal(r.multiQuery(scene), o.multiQuery(scene))
+        r.set(scene[:40], fr[0][1][:40])
+        o.set(scene[:40], fr[0][1][:40])
+        assert np.array_equal(r.multiQuery(scene), o.multiQuery(scene))
+        assert all(r.confidence(*[int(v) for v in p]) == 0.0 for p in scene[:40])
+    rw, ow = R.ResultOfWeight(), L.ResultOfWeight()
+    for ps, sc in fr:
+        rw.update(ps, sc)
+        ow.update(ps, sc)
+        assert np.array_equal(rw.multiQuery(scene), ow.multiQuery(scene))
+    rw.finalize(scene[:500])
+    ow.finalize(scene[:500])
+    assert rw.size() == len(ow.result) == 500 - int((ow.multiQuery(scene[:500]) < 0).sum())
