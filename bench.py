@@ -258,6 +258,53 @@ def layer_bench(args, dev, hbm_peak, bf16_peak, peak_kind):
                          "peak_kind": peak_kind, "algorithmic_bytes": byts, "algorithmic_flops": flops}}
 
 
+def labels_bench(dev, coords, steps, warmup):
+    """Label fusion behind the network (row f2 of the scope table): one frame's scores for every voxel of the room
+    merged into the device-resident vote table (SCN.Result_3.update), scores and coordinates already on the GPU; beside
+    it the CPU restatement of the reference's Result<3> on a 20,000-point sample (the reference's own comment puts its
+    host loop at about 30 ms for 20,000 points, Metadata/resultHash.h:53-54)."""
+    import numpy as np
+    import torch
+    import sparseconvnet as scn
+    from oracle import scn_labels
+    rng = np.random.RandomState(5)
+    n = coords.shape[0]
+    scores = torch.softmax(torch.from_numpy(rng.randn(n, 20).astype(np.float32)), 1).to(dev)
+    pts = torch.from_numpy(np.ascontiguousarray(coords[:, :3])).to(dev)
+    table = scn.SCN.Result_3(3.0)
+    for _ in range(warmup):
+        table.update(pts, scores)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = scn.SCN.launch_count()
+    e0.record()
+    for _ in range(steps):
+        table.update(pts, scores)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / steps
+    launches = (scn.SCN.launch_count() - l0) // steps
+    q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    q0.record()
+    labels = table.multiQuery(pts)
+    q1.record()
+    torch.cuda.synchronize()
+    sample = 20000
+    cpu = scn_labels.Result(3.0)
+    c_np, s_np = coords[:sample, :3], scores[:sample].cpu().numpy()
+    cpu.update(c_np, s_np)
+    t0 = time.perf_counter()
+    cpu.update(c_np, s_np)
+    cpu_ms = (time.perf_counter() - t0) * 1e3
+    assert np.array_equal(labels[:sample].numpy(), cpu.multiQuery(c_np)), "the GPU table and the CPU restatement disagree"
+    # bytes that have to move: coordinates and scores in, (key, label, confidence) read and written once
+    alg = n * (24 + 80 + 2 * 16)
+    return {"voxels": int(n), "classes": 20, "update_us": us, "voxels_per_s": n / (us * 1e-6), "launches": int(launches),
+            "GBps": alg / (us * 1e-6) / 1e9, "entries": int(table.size()),
+            "multi_query_with_host_copy_us": q0.elapsed_time(q1) * 1e3,
+            "cpu_port": {"points": sample, "ms": cpu_ms, "kind": "port (Python dictionary restatement of the reference's host loop)"}}
+
+
 def configs01_bench(dev, steps, warmup):
     """BASELINE configs[0] and configs[1] as single-layer figures through the C ABI: one SubmanifoldConvolution 16->16,
     fp32, no bias, on the seeded boxes-and-spheres scene (seed 3: 50,208 voxels in 128^3), rulebook cached; then the same
@@ -602,7 +649,7 @@ def main():
     ap.add_argument("--precision", default="fp16", choices=["fp32", "tf32", "fp16"])
     ap.add_argument("--quick", action="store_true", help="skip the 4M-point hash build (profiling aid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--legs", default="full,incre,sweep,e2e,precisions,configs01", help="which timed legs to run (profiling aid)")
+    ap.add_argument("--legs", default="full,incre,sweep,e2e,precisions,configs01,labels", help="which timed legs to run (profiling aid)")
     ap.add_argument("--sweep-frames", type=int, default=100)
     ap.add_argument("--layer", action="store_true", help="time one SSC layer alone (rulebook cached) and exit")
     ap.add_argument("--hash", action="store_true", help="time the grid build alone and exit")
@@ -978,7 +1025,8 @@ def main():
             "hash_build": hashes,
             # the same frame in the other precisions, value and ms per step (median of 3 regions of min(K, 20) steps)
             "other_precisions": other,
-            "single_layer": configs01_bench(dev, 20, 3) if "configs01" in legs else None}
+            "single_layer": configs01_bench(dev, 20, 3) if "configs01" in legs else None,
+            "label_fusion": labels_bench(dev, coords, 20, 3) if "labels" in legs else None}
     if world == 1 and not args.no_cpu_baseline:
         r = cpu_reference(args.voxels, 3, 1)
         line["cpu_baseline"] = {"value": r["value"], "unit": UNIT, "cores": r["cores"], "kind": "port",

@@ -148,11 +148,16 @@ __device__ __forceinline__ void vote(Table &t, int slot, bool is_new, int val, f
 
 // mode 0: update; mode 1: set (resultHash.h:37-50: label = argmax, confidence 0, whatever was there)
 __global__ void k_lab_vote_first(Table t, const int *__restrict__ slot_of, long long n, const float *__restrict__ scores,
-                                 long long stride, int classes, float maximum, int mode) {
+                                 long long stride, int classes, float maximum, int mode, int *__restrict__ list,
+                                 unsigned int *n_later) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int slot = slot_of[i];
-  if (slot < 0 || t.first[slot] != (int)i) return;
+  if (slot < 0) return;
+  if (t.first[slot] != (int)i) {  // not the first row of its voxel in this call: left to the serial pass
+    list[atomicAdd(n_later, 1u)] = (int)i;
+    return;
+  }
   int val;
   float p;
   arg_max(scores + i * stride, classes, &val, &p);
@@ -166,56 +171,85 @@ __global__ void k_lab_vote_first(Table t, const int *__restrict__ slot_of, long 
 
 // ResultOfWeight::update (resultHash.h:146-158): one thread per (row, class)
 __global__ void k_lab_blend_first(Table t, const int *__restrict__ slot_of, long long n, const float *__restrict__ scores,
-                                  long long stride) {
+                                  long long stride, int *__restrict__ list, unsigned int *n_later) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long i = idx / t.classes;
   const int c = (int)(idx - i * t.classes);
   if (i >= n) return;
   const int slot = slot_of[i];
-  if (slot < 0 || t.first[slot] != (int)i) return;
+  if (slot < 0) return;
+  if (t.first[slot] != (int)i) {
+    if (c == 0) list[atomicAdd(n_later, 1u)] = (int)i;
+    return;
+  }
   float *dst = t.probs + (long long)slot * t.classes + c;
   const float x = scores[i * stride + c];
   *dst = t.fresh[slot] ? x : *dst * 0.5f + x;
 }
 
-// Rows that are not the first of their voxel in this call, applied one after the other in row order by one block:
-// every thread scans a contiguous piece of the rows, the pieces' finds are concatenated in order (block scan of the
-// counts), then the votes are applied serially (vote mode: thread 0; weight mode: thread c for class c).
+// Rows that are not the first of their voxel in this call (collected in no particular order by the kernel above),
+// applied one after the other in row order by one block: the list is sorted (in shared memory when it has at most 8192
+// entries, else rebuilt in order by scanning the rows), then the votes are applied serially (vote table: thread 0;
+// weight table: thread c for class c).  Nothing to do in the common case of a call that names every voxel once.
+constexpr int kSortMax = 8192;
 __global__ void __launch_bounds__(1024) k_lab_later_rows(Table t, const int *__restrict__ slot_of, long long n,
                                                          const float *__restrict__ scores, long long stride, int classes,
-                                                         float maximum, int mode, int *__restrict__ list, unsigned int *n_later) {
-  __shared__ unsigned int offs[1024];
-  __shared__ unsigned int total;
-  const int T = blockDim.x, tid = threadIdx.x;
-  const long long per = (n + T - 1) / T, lo = per * tid, hi = lo + per < n ? lo + per : n;
-  unsigned int mine = 0;
-  for (long long i = lo; i < hi; ++i) {
-    const int s = slot_of[i];
-    mine += (s >= 0 && t.first[s] != (int)i) ? 1u : 0u;
-  }
-  offs[tid] = mine;
-  __syncthreads();
-  if (tid == 0) {
-    unsigned int run = 0;
-    for (int k = 0; k < T; ++k) {
-      const unsigned int v = offs[k];
-      offs[k] = run;
-      run += v;
-    }
-    total = run;
-    *n_later = run;
-  }
-  __syncthreads();
+                                                         float maximum, int mode, int *__restrict__ list,
+                                                         const unsigned int *__restrict__ n_later) {
+  const unsigned int total = *n_later;
   if (total == 0) return;
-  unsigned int at = offs[tid];
-  for (long long i = lo; i < hi; ++i) {
-    const int s = slot_of[i];
-    if (s >= 0 && t.first[s] != (int)i) list[at++] = (int)i;
+  __shared__ int sorted[kSortMax];
+  __shared__ unsigned int offs[1024];
+  const int T = blockDim.x, tid = threadIdx.x;
+  const int *order = sorted;
+  if (total <= (unsigned)kSortMax) {
+    unsigned int m = 1;
+    while (m < total) m <<= 1;
+    for (unsigned int j = tid; j < m; j += T) sorted[j] = j < total ? list[j] : INT_MAX;
+    __syncthreads();
+    for (unsigned int k = 2; k <= m; k <<= 1)
+      for (unsigned int j = k >> 1; j > 0; j >>= 1) {
+        for (unsigned int x = tid; x < m; x += T) {
+          const unsigned int y = x ^ j;
+          if (y > x) {
+            const int a = sorted[x], b = sorted[y];
+            const bool up = (x & k) == 0;
+            if ((a > b) == up) {
+              sorted[x] = b;
+              sorted[y] = a;
+            }
+          }
+        }
+        __syncthreads();
+      }
+  } else {
+    const long long per = (n + T - 1) / T, lo = per * tid, hi = lo + per < n ? lo + per : n;
+    unsigned int mine = 0;
+    for (long long i = lo; i < hi; ++i) {
+      const int s = slot_of[i];
+      mine += (s >= 0 && t.first[s] != (int)i) ? 1u : 0u;
+    }
+    offs[tid] = mine;
+    __syncthreads();
+    if (tid == 0) {
+      unsigned int run = 0;
+      for (int k = 0; k < T; ++k) {
+        const unsigned int v = offs[k];
+        offs[k] = run;
+        run += v;
+      }
+    }
+    __syncthreads();
+    unsigned int at = offs[tid];
+    for (long long i = lo; i < hi; ++i) {
+      const int s = slot_of[i];
+      if (s >= 0 && t.first[s] != (int)i) list[at++] = (int)i;
+    }
+    __syncthreads();
+    order = list;
   }
-  __syncthreads();
-  __threadfence_block();
   for (unsigned int j = 0; j < total; ++j) {
-    const int i = list[j], slot = slot_of[i];
+    const int i = order[j], slot = slot_of[i];
     if (t.classes == 0) {
       if (tid == 0) {
         int val;
@@ -442,12 +476,17 @@ int apply(scn_labels *h, const int64_t *points, int ncols, int64_t n, const floa
   SCN_TRY(dev_alloc_t(&slot_of, (size_t)n * 2, s));
   list = slot_of + n;
   const long long *pts = reinterpret_cast<const long long *>(points);
+  if (cudaMemsetAsync(h->counters + 2, 0, sizeof(unsigned int), s) != cudaSuccess) {
+    dev_free(slot_of, s);
+    return fail(SCN_E_CUDA, "label table: memset failed");
+  }
   k_lab_insert<<<blocks(n, 256), 256, 0, s>>>(h->t, pts, ncols, n, slot_of, h->counters, h->counters + 1);
   SCN_LAUNCHED();
   if (h->classes == 0)
-    k_lab_vote_first<<<blocks(n, 256), 256, 0, s>>>(h->t, slot_of, n, scores, stride, (int)classes, h->maximum, mode);
+    k_lab_vote_first<<<blocks(n, 256), 256, 0, s>>>(h->t, slot_of, n, scores, stride, (int)classes, h->maximum, mode, list,
+                                                    h->counters + 2);
   else
-    k_lab_blend_first<<<blocks(n * classes, 256), 256, 0, s>>>(h->t, slot_of, n, scores, stride);
+    k_lab_blend_first<<<blocks(n * classes, 256), 256, 0, s>>>(h->t, slot_of, n, scores, stride, list, h->counters + 2);
   SCN_LAUNCHED();
   k_lab_later_rows<<<1, 1024, 0, s>>>(h->t, slot_of, n, scores, stride, (int)classes, h->maximum, mode, list, h->counters + 2);
   SCN_LAUNCHED();
