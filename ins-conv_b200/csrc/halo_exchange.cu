@@ -50,12 +50,17 @@ struct HaloArgs {
 
 template <typename W> __device__ __forceinline__ int64_t rows_that_fit(const HaloArgs &p, int list) {
   int64_t n = p.counts[list];
-  if (n > p.cap) n = p.cap;
+  bool cut = false;
+  if (n > p.cap) {  // the caller's list is shorter than the plane
+    n = p.cap;
+    cut = true;
+  }
   const int64_t row_bytes = p.a_row_bytes + p.b_row_bytes;
   if (n * row_bytes > p.slot_bytes) {
     n = p.slot_bytes / row_bytes;
-    if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(p.status, 2u);
+    cut = true;
   }
+  if (cut && threadIdx.x == 0 && blockIdx.x == 0) atomicOr(p.status, 2u);
   return n;
 }
 

@@ -85,6 +85,10 @@ def test_plane_larger_than_a_slot_is_reported():
         assert _status(cabi, h) == (0, 1)
         assert _status(cabi, h) == (0, 0)  # reading clears
         assert torch.equal(a[lists[3, :64]], a0[lists[0, :64]]) and torch.equal(a[lists[3, 64:100]], a0[lists[3, 64:100]])
+        # a count beyond the list's capacity (the caller's lists were cut short) is reported the same way
+        short = lists[:, :40].contiguous()
+        _exchange(cabi, h, short, torch.tensor((50, 10, 10, 50)).cuda(), a)
+        assert _status(cabi, h) == (0, 1)
     finally:
         cabi.call("scn_halo_destroy", h)
 
