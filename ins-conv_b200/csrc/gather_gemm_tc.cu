@@ -382,7 +382,8 @@ __device__ __forceinline__ void tma_tile2d(uint32_t dst, const CUtensorMap *tm, 
 //                          warp runs the loop so that the ring position stays a warp-uniform value.
 // Every blocking primitive is a bounded mbarrier wait.  A tile with no neighbour at all still runs one step
 // of zero rows so that all roles see the same sequence of tiles.
-constexpr int kPThreads = 416;  // 4 epilogue warps, 8 producer warps, 1 tensor-core warp
+constexpr int kPThreads = 448;  // 4 epilogue warps, 8 producer warps, 1 tensor-core warp, 1 weight-loading warp
+constexpr int kMaxBStages = 4;
 constexpr int kProdWarps = 8;
 constexpr int kMaxStages = 8;
 constexpr int kMapBufs = 3;
@@ -391,10 +392,12 @@ constexpr uint32_t kInfoDone = 1;  // info word of a step: (steps of the item <<
 struct alignas(16) CtlP {
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
+  unsigned long long bfull[kMaxBStages];
+  unsigned long long bempty[kMaxBStages];
   unsigned long long accfull[2];
   unsigned long long accempty[2];
   unsigned long long mapfull[kMapBufs];
-  unsigned long long pad_;  // keeps kmask_part on a 16-byte boundary (it is read as two uint4)
+  unsigned long long pad_;  // keeps kmask_part on a 16-byte boundary (it is read as two uint4): 8 + 8 + 4 + 4 + 2 + 2 + 3 + 1 words
   uint32_t info[kMaxStages];
   uint32_t kmask_part[kMapBufs][kProdWarps];
   uint32_t tmem_base;
@@ -433,12 +436,16 @@ __global__ void __launch_bounds__(kPThreads, 1)
 k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, const __grid_constant__ CUtensorMap tmB,
                            const int32_t *__restrict__ map, int K, long long n_out, const float *__restrict__ bias,
                            float *out, long long out_stride, int Cin, int Cout, const float *init, long long init_stride,
-                           uint32_t acc_cols, int stages, long long tiles, int Z, float *__restrict__ partial, const EpiBn epi) {
+                           uint32_t acc_cols, int stages, int stages_b, long long tiles, int Z, float *__restrict__ partial,
+                           const EpiBn epi) {
+  // shared memory: `stages` operand tiles (the gathered rows of a step, 16 KB each), `stages_b` weight boxes
+  // (n_out x 128 bytes each), the control block, the map buffers.  The two rings are separate because what bounds the
+  // kernel is the number of gathered bytes in flight: a weight box per operand slot would take half of the room.
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t b_bytes = (uint32_t)Cout * 128u;
-  const uint32_t stage_bytes = kABytes + b_bytes;
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  CtlP *ctl = reinterpret_cast<CtlP *>(smem + (size_t)stages * stage_bytes);
+  const uint32_t b_ring = (uint32_t)stages * kABytes;  // offset of the weight ring
+  CtlP *ctl = reinterpret_cast<CtlP *>(smem + (size_t)b_ring + (size_t)stages_b * b_bytes);
   int *s_map = reinterpret_cast<int *>(ctl + 1);  // [kMapBufs][K][128]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr int kStepPlanes = HALF ? 64 : 32;  // planes per reduction step (128 bytes of a row)
@@ -453,14 +460,20 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
   if (tid == 0) {
     ctl->failed = 0;
     for (int s = 0; s < stages; ++s) {
-      mbar_init(smem_u32(&ctl->full[s]), 2);  // the owning warp's arrival + the weight copy's expect_tx arrival
+      mbar_init(smem_u32(&ctl->full[s]), 1);  // the owning producer warp's arrival
       mbar_init(smem_u32(&ctl->empty[s]), 1);
+    }
+    for (int s = 0; s < stages_b; ++s) {
+      mbar_init(smem_u32(&ctl->bfull[s]), 1);  // the weight copy's expect_tx arrival
+      mbar_init(smem_u32(&ctl->bempty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl->accfull[b]), 1);
       mbar_init(smem_u32(&ctl->accempty[b]), 4);  // one arrival per epilogue warp
     }
-    for (int b = 0; b < kMapBufs; ++b) mbar_init(smem_u32(&ctl->mapfull[b]), kProdWarps);  // one arrival per producer warp
+    // one arrival per producer warp, one of the weight-loading warp (which thereby keeps the producers from reusing a
+    // map buffer whose offset mask it has not read yet)
+    for (int b = 0; b < kMapBufs; ++b) mbar_init(smem_u32(&ctl->mapfull[b]), kProdWarps + 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
   }
@@ -566,13 +579,9 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
             stop = true;
             break;
           }
-          const uint32_t a_base = smem_base + (uint32_t)slot * stage_bytes;
+          const uint32_t a_base = smem_base + (uint32_t)slot * kABytes;
           const uint32_t bar = smem_u32(&ctl->full[slot]);
-          if (lane == 0) {
-            if (it == 0) ctl->info[slot] = (uint32_t)T << 8;  // the item's step count rides on its first step
-            mbar_expect_tx(bar, b_bytes);
-            tma_tile2d(a_base + kABytes, &tmB, bar, kb * kStepPlanes, k * Cout);
-          }
+          if (lane == 0 && it == 0) ctl->info[slot] = (uint32_t)T << 8;  // the item's step count rides on its first step
           const int *mr = mrows + k * kTileM + q;
           const unsigned char *in_kb = in_c + (size_t)kb * 128;
           // fp16 rows: the last block of a row may be half empty (n_in = 96, 160, 224): those chunks are zero-filled
@@ -615,7 +624,6 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
         const uint32_t bar = smem_u32(&ctl->full[slot]);
         ctl->info[slot] = kInfoDone;
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
       }
     }
     __syncwarp();
@@ -627,11 +635,13 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
     // descriptor words: low = start address / 16 | leading offset 16 B; high = stride offset 1024 B, version, 128-byte swizzle
     const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
     const uint32_t a_lo0 = ((smem_base >> 4) & 0x3FFFu) | (1u << 16);
-    const uint32_t stage16 = stage_bytes >> 4, b_off16 = kABytes >> 4;
+    const uint32_t stage16 = kABytes >> 4, bstage16 = b_bytes >> 4;
+    const uint32_t b_lo0 = (((smem_base + b_ring) >> 4) & 0x3FFFu) | (1u << 16);
     const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
+    const uint32_t bfull0 = smem_u32(&ctl->bfull[0]), bempty0 = smem_u32(&ctl->bempty[0]);
     long long tile_i = 0;
-    int slot = 0;
-    uint32_t phase = 0, a_lo = a_lo0;
+    int slot = 0, bslot = 0;
+    uint32_t phase = 0, bphase = 0, a_lo = a_lo0, b_lo = b_lo0;
     bool alive = true;
     while (alive) {
       if (!mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) break;
@@ -644,19 +654,18 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
       if (tile_i >= 2 && !mbar_wait(smem_u32(&ctl->accempty[buf]), (uint32_t)(((tile_i >> 1) - 1) & 1), failed)) break;
       tc_fence_after();  // the epilogue's TMEM reads of this accumulator are ordered before the new MMAs
       for (int t = 0; t < T; ++t) {
-        if (t > 0) {
-          if (!mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) {
-            alive = false;
-            break;
-          }
+        if ((t > 0 && !mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) ||
+            !mbar_wait(bfull0 + 8u * (uint32_t)bslot, bphase, failed)) {
+          alive = false;
+          break;
         }
         if (elect_one()) {
-          const uint32_t b_lo = a_lo + b_off16;
           mma_lohi<HALF>(tmem_d, a_lo, b_lo, desc_hi, idesc, t > 0 ? 1u : 0u);
           mma_lohi<HALF>(tmem_d, a_lo + 2, b_lo + 2, desc_hi, idesc, 1u);
           mma_lohi<HALF>(tmem_d, a_lo + 4, b_lo + 4, desc_hi, idesc, 1u);
           mma_lohi<HALF>(tmem_d, a_lo + 6, b_lo + 6, desc_hi, idesc, 1u);
           mma_commit(empty0 + 8u * (uint32_t)slot);
+          mma_commit(bempty0 + 8u * (uint32_t)bslot);
           if (t == T - 1) mma_commit(smem_u32(&ctl->accfull[buf]));
         }
         a_lo += stage16;
@@ -665,8 +674,74 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
           phase ^= 1u;
           a_lo = a_lo0;
         }
+        b_lo += bstage16;
+        if (++bslot == stages_b) {
+          bslot = 0;
+          bphase ^= 1u;
+          b_lo = b_lo0;
+        }
       }
       ++tile_i;
+    }
+    __syncwarp();
+  } else if (warp == 4 + kProdWarps + 1) {
+    // =========================== weights ==========================================================
+    // One warp walks all steps in order and fetches each step's weight block with one TMA box into the weight ring.
+    // It is the only waiter on the ring's `bempty` barriers, so it sees their phases one after the other (a parity
+    // wait cannot tell phases two apart).  It takes part in the map barriers like a producer warp: its arrival for
+    // tile i + 1 comes after it has read tile i's offset mask, which keeps the producers from reusing that buffer
+    // early; it arrives before it starts the tile's copies, so the producers never wait for the weight ring.
+    const uint32_t bfull0 = smem_u32(&ctl->bfull[0]), bempty0 = smem_u32(&ctl->bempty[0]);
+    int bslot = 0, mbuf = 0;
+    uint32_t bwrapped = 0, mphase = 0;
+    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->mapfull[0])) : "memory");
+    bool stop = false;
+    for (long long i = 0; i < my_tiles && !*failed && !stop; ++i) {
+      const long long item = (long long)blockIdx.x + i * gridDim.x;
+      if (!mbar_wait(smem_u32(&ctl->mapfull[mbuf]), mphase, failed)) break;
+      const uint4 km0 = *reinterpret_cast<const uint4 *>(&ctl->kmask_part[mbuf][0]);
+      const uint4 km1 = *reinterpret_cast<const uint4 *>(&ctl->kmask_part[mbuf][4]);
+      const unsigned int kmask = km0.x | km0.y | km0.z | km0.w | km1.x | km1.y | km1.z | km1.w;
+      if (++mbuf == kMapBufs) {
+        mbuf = 0;
+        mphase ^= 1u;
+      }
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->mapfull[mbuf])) : "memory");
+      // the same enumeration of the item's steps as the producers'
+      const int z = (int)(item % Z);
+      const int nk_all = __popc(kmask);
+      const int Tall = nk_all * KB;
+      const int t0 = (int)(((long long)Tall * z) / Z);
+      const int Tz = (int)(((long long)Tall * (z + 1)) / Z) - t0;
+      const int T = Tz > 0 ? Tz : 1;
+      unsigned int rest = kmask;
+      int kb = 0;
+      if (Tz > 0) {
+        for (int r = t0 / KB; r > 0; --r) rest &= rest - 1;
+        kb = t0 % KB;
+      }
+      int k = (Tz > 0 && rest) ? __ffs(rest) - 1 : 0;
+      for (int it = 0; it < T; ++it) {
+        if (bwrapped > 0 && !mbar_wait(bempty0 + 8u * (uint32_t)bslot, (bwrapped - 1) & 1u, failed)) {
+          stop = true;
+          break;
+        }
+        if (lane == 0) {
+          const uint32_t bar = bfull0 + 8u * (uint32_t)bslot;
+          mbar_expect_tx(bar, b_bytes);
+          tma_tile2d(smem_base + b_ring + (uint32_t)bslot * b_bytes, &tmB, bar, kb * kStepPlanes, k * Cout);
+        }
+        if (++bslot == stages_b) {
+          bslot = 0;
+          ++bwrapped;
+        }
+        if (++kb == KB) {
+          kb = 0;
+          rest &= rest - 1;
+          k = rest ? __ffs(rest) - 1 : 0;
+        }
+      }
     }
     __syncwarp();
   } else {
@@ -902,6 +977,28 @@ int tc_check_errors(cudaStream_t s) {
   return SCN_OK;
 }
 
+// Shared-memory plan of the persistent kernel: operand slots (16 KB each, at most one per producer warp) and weight
+// slots (n_out x 128 bytes each).  Three weight slots when that leaves six operand slots or more, else two.
+struct PersistPlan {
+  int stages, stages_b;
+  size_t smem;
+};
+static PersistPlan persist_plan(int64_t K, int64_t Cout) {
+  const size_t b_bytes = (size_t)Cout * 128;
+  const size_t fixed_p = sizeof(CtlP) + (size_t)kMapBufs * K * kTileM * sizeof(int) + 1024;
+  const long long room = 220ll * 1024 - (long long)fixed_p;
+  PersistPlan p;
+  p.stages_b = 3;
+  p.stages = (int)((room - 3ll * (long long)b_bytes) / kABytes);
+  if (p.stages < 6) {
+    p.stages_b = 2;
+    p.stages = (int)((room - 2ll * (long long)b_bytes) / kABytes);
+  }
+  if (p.stages > kMaxStages) p.stages = kMaxStages;
+  p.smem = (size_t)p.stages * kABytes + (size_t)p.stages_b * b_bytes + fixed_p;
+  return p;
+}
+
 int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out, const float *W,
                      const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
                      int64_t init_stride, bool packed, cudaStream_t s, bool *handled) {
@@ -972,8 +1069,8 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
     CUtensorMap tmB;
     if (packed) SCN_TRY(cached_tensor_map(&tmB, Wt, false, (uint64_t)Cin, (uint64_t)K * Cout, 32, (uint32_t)Cout));
     else SCN_TRY(encode_2d(&tmB, Wt, false, (uint64_t)Cin, (uint64_t)K * Cout, (uint64_t)Cin * 4, 32, (uint32_t)Cout));
-    const int st = st_p;
-    const size_t smem_p = (size_t)st * stage_bytes + fixed_p;
+    const PersistPlan plan = persist_plan(K, Cout);
+    const size_t smem_p = plan.smem;
     {
       // the opt-in shared memory limit is raised once per device, to the most this kernel ever asks for
       static bool raised[64] = {false};
@@ -987,8 +1084,8 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
     }
     const long long n_items = tiles * Z;
     k_gather_gemm_tc_persist<false><<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads, smem_p, s>>>(
-        in, in_stride, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, (int)Cout, init, init_stride, cols, st, tiles, Z,
-        partial, EpiBn());
+        in, in_stride, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, (int)Cout, init, init_stride, cols, plan.stages,
+        plan.stages_b, tiles, Z, partial, EpiBn());
   } else {
 #define SCN_TC_LAUNCH(S, A)                                                                                          \
   do {                                                                                                               \
@@ -1020,6 +1117,8 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
 // ---------------------------------------------------------------------------------------------
 namespace {
 inline int64_t padded_planes(int64_t Cin) { return (Cin + 63) / 64 * 64; }
+// which shapes the fp16 path takes (kept as it was when a ring slot held operand tile and weight box together, so that
+// packed weights and the shapes the interface announces stay what they were)
 inline int persist_stages(int64_t K, int64_t Cout) {
   const size_t stage_bytes = (size_t)kABytes + (size_t)Cout * 128;
   const size_t fixed_p = sizeof(CtlP) + (size_t)kMapBufs * K * kTileM * sizeof(int) + 1024;
@@ -1082,9 +1181,7 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
   if (in_stride % 8 != 0 || out_stride % 4 != 0 || !aligned16(in) || !aligned16(Wp) || !aligned16(out) ||
       (bias && !aligned16(bias)) || (init && (!aligned16(init) || init_stride % 4 != 0)))
     return fail(SCN_E_INVALID, "rows must be 16-byte aligned (fp16 stride a multiple of 8, fp32 strides multiples of 4)");
-  const size_t stage_bytes = (size_t)kABytes + (size_t)Cout * 128;
-  const size_t fixed_p = sizeof(CtlP) + (size_t)kMapBufs * K * kTileM * sizeof(int) + 1024;
-  const int st = persist_stages(K, Cout);
+  const PersistPlan plan = persist_plan(K, Cout);
   uint32_t cols = 32;
   while (cols < (uint32_t)Cout) cols <<= 1;
   const long long tiles = (n_out + kTileM - 1) / kTileM;
@@ -1130,10 +1227,9 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
     return rc;
   }
   const long long n_items = tiles * Z;
-  k_gather_gemm_tc_persist<true><<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads,
-                                   (size_t)st * stage_bytes + fixed_p, s>>>(in, in_stride, tmB, map, K, n_out, bias, out, out_stride,
-                                                                            (int)Cin, (int)Cout, init, init_stride, cols, st,
-                                                                            tiles, Z, partial, Z > 1 ? EpiBn() : e);
+  k_gather_gemm_tc_persist<true><<<(unsigned)(n_items < sm_count ? n_items : sm_count), kPThreads, plan.smem, s>>>(
+      in, in_stride, tmB, map, K, n_out, bias, out, out_stride, (int)Cin, (int)Cout, init, init_stride, cols, plan.stages,
+      plan.stages_b, tiles, Z, partial, Z > 1 ? EpiBn() : e);
   SCN_LAUNCHED();
   if (Z > 1) {
     const long long work = n_out * (Cout / 4);
