@@ -246,7 +246,7 @@ def test_incremental_maps_and_operators(R):
     assert rel(R.incre_output_layer(m, vox, pre, pvox), want) <= 1e-6
 
 
-def test_label_fusion_equals_the_reference_classes():
+def test_label_fusion_equals_the_reference_classes(R):
     """Result<3> (votes with a confidence, with the default cap -- held as 0 by the reference's int member -- and with
     a cap of 3) and ResultOfWeight<3> over six frames of scores that revisit voxels with agreeing and disagreeing
     labels and name some voxels twice in one call: labels after every frame, every confidence, finalize, set."""
