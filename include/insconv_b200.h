@@ -362,6 +362,15 @@ SCN_API int scn_incre_bn_forward(scn_metadata *m, scn_metadata *pre, const int64
                          const float *running_mean, const float *running_var, const float *gamma,
                          const float *beta, double eps, double leakiness, const float *pre_out,
                          const float *pre_in, void *stream);
+/* The incremental BatchNorm of the 'fp16' precision: the residual is written as fp16 rows for the convolution behind it
+ * (out: fp16 [n_active, planes], strides in elements), the saved frame's BatchNorm output is read as the fp16 rows that
+ * frame wrote (pre_out), its input as fp32 rows (pre_in).  With SCN_PREC_F16, scn_incre_ssc_forward and
+ * scn_incre_deconv_forward read both the residual rows and the saved rows as fp16 and take the fp16 weight pack. */
+SCN_API int scn_incre_bn_forward_f16(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const float *in,
+                                     int64_t in_stride, void *out, int64_t out_stride, int64_t planes,
+                                     const float *running_mean, const float *running_var, const float *gamma,
+                                     const float *beta, double eps, double leakiness, const void *pre_out,
+                                     int64_t pre_out_stride, const float *pre_in, int64_t pre_in_stride, void *stream);
 
 /* ---- one scene on several GPUs: halo rows pushed into the neighbours' memory ------------------------------
  * The reference runs on one GPU; these entry points have no counterpart there.  A scene is cut into slabs along x,

@@ -736,10 +736,10 @@ int scn_incre_ssc_forward(scn_metadata *m, scn_metadata *pre, const int64_t size
   if (!pre_in) return fail(SCN_E_INVALID, "null saved features");
   SCN_TRY(ensure_ssc(m, *g, s));
   SCN_TRY(need_nbr2(g, pg, im, s));
-  SCN_TRY(gather_gemm(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0, precision, s));
+  SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0, precision, s));
   if (im->nbr2_total)
-    SCN_TRY(gather_gemm(pre_in, pre_in_stride, pg->n, im->nbr2, 27, g->n, weight, nullptr, out, out_stride, n_in, n_out, out, out_stride,
-                        precision, s));
+    SCN_TRY(run_conv(pre_in, pre_in_stride, pg->n, im->nbr2, 27, g->n, weight, nullptr, out, out_stride, n_in, n_out, out, out_stride,
+                     precision, s));
   if (flops) *flops = (double)(g->nbr_total + im->nbr2_total) * (double)n_in * (double)n_out;
   return SCN_OK;
 }
@@ -774,10 +774,10 @@ int scn_incre_deconv_forward(scn_metadata *m, scn_metadata *pre, const int64_t i
     SCN_TRY(dev_alloc_t(&im_c->up2, (size_t)fine->n * 8, s));
     SCN_TRY(build_incre_up(*coarse, im_c->pre_exist, im_f->pre_exist, im_c->up2, s));
   }
-  SCN_TRY(gather_gemm(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
-                      precision, s));
-  SCN_TRY(gather_gemm(pre_in, pre_in_stride, pg1->n, im_c->up2, 8, fine->n, weight, nullptr, out, out_stride, n_in, n_out, out, out_stride,
-                      precision, s));
+  SCN_TRY(run_conv(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
+                   precision, s));
+  SCN_TRY(run_conv(pre_in, pre_in_stride, pg1->n, im_c->up2, 8, fine->n, weight, nullptr, out, out_stride, n_in, n_out, out, out_stride,
+                   precision, s));
   if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
   return SCN_OK;
 }
@@ -793,6 +793,20 @@ int scn_incre_bn_forward(scn_metadata *m, scn_metadata *pre, const int64_t size[
   if (!in || !out || !running_mean || !running_var || !pre_out || !pre_in) return fail(SCN_E_INVALID, "null pointer");
   return bn_forward(in, in_stride, out, out_stride, g->n, planes, running_mean, running_var, gamma, beta, (float)eps,
                     (float)leakiness, im->pre_exist, pre_out, pre_in, s);
+}
+int scn_incre_bn_forward_f16(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const float *in, int64_t in_stride,
+                             void *out, int64_t out_stride, int64_t planes, const float *running_mean,
+                             const float *running_var, const float *gamma, const float *beta, double eps, double leakiness,
+                             const void *pre_out, int64_t pre_out_stride, const float *pre_in, int64_t pre_in_stride,
+                             void *stream) {
+  Grid *g, *pg;
+  IncreMaps *im;
+  cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(need_incre(m, pre, size, &g, &pg, &im, s));
+  if (g->n == 0) return SCN_OK;
+  if (!in || !out || !running_mean || !running_var || !pre_out || !pre_in) return fail(SCN_E_INVALID, "null pointer");
+  return bn_forward_f16out(in, in_stride, out, out_stride, g->n, planes, running_mean, running_var, gamma, beta, (float)eps,
+                           (float)leakiness, s, im->pre_exist, pre_out, pre_out_stride, pre_in, pre_in_stride);
 }
 
 }  // extern "C"

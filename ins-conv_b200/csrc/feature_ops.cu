@@ -244,9 +244,14 @@ __global__ void k_bn(const float *__restrict__ in, long long in_stride, float *_
 
 // The same BatchNorm + leaky ReLU with the result rounded to fp16: the 16-bit rows are what the fp16 gather-GEMM
 // of the following convolution reads (half the bytes per gathered row).  Eight planes per thread.
+// Incremental form (pre_exist given): for a site that existed in the saved frame the result is the RESIDUAL of the
+// activation, act(w (x + x_saved) + b) - y_saved (CUDA/BatchNormalization.cu:112-150), with y_saved read from the fp16
+// rows the saved frame's BatchNorm wrote and x_saved from the fp32 rows it read.
 __global__ void k_bn_f16out(const float *__restrict__ in, long long in_stride, __half *__restrict__ out, long long out_stride,
                             long long rows, int C, const float *__restrict__ mean, const float *__restrict__ var,
-                            const float *__restrict__ gamma, const float *__restrict__ beta, float eps, float leak) {
+                            const float *__restrict__ gamma, const float *__restrict__ beta, float eps, float leak,
+                            const int32_t *__restrict__ pre_exist, const __half *__restrict__ pre_out, long long pre_out_stride,
+                            const float *__restrict__ pre_in, long long pre_in_stride) {
   extern __shared__ float sm[];  // scale[C], shift[C]
   float *sw = sm, *sb = sm + C;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
@@ -263,13 +268,29 @@ __global__ void k_bn_f16out(const float *__restrict__ in, long long in_stride, _
     const int c = (int)(i % cv) * 8;
     const float4 x0 = *reinterpret_cast<const float4 *>(in + row * in_stride + c);
     const float4 x1 = *reinterpret_cast<const float4 *>(in + row * in_stride + c + 4);
-    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    float ys[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // what the saved frame held at this site (residual form)
+    const int pe = pre_exist ? pre_exist[row] : -1;
+    if (pe >= 0) {
+      const float4 a0 = *reinterpret_cast<const float4 *>(pre_in + (long long)pe * pre_in_stride + c);
+      const float4 a1 = *reinterpret_cast<const float4 *>(pre_in + (long long)pe * pre_in_stride + c + 4);
+      xs[0] += a0.x, xs[1] += a0.y, xs[2] += a0.z, xs[3] += a0.w, xs[4] += a1.x, xs[5] += a1.y, xs[6] += a1.z, xs[7] += a1.w;
+      const uint4 q = *reinterpret_cast<const uint4 *>(pre_out + (long long)pe * pre_out_stride + c);
+      const __half2 *h = reinterpret_cast<const __half2 *>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(h[j]);
+        ys[2 * j] = f.x;
+        ys[2 * j + 1] = f.y;
+      }
+    }
     __align__(16) __half2 y[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       // values beyond fp16's range saturate at +-65504 instead of becoming infinities
-      const float a = fminf(fmaxf(leaky(sw[c + 2 * j] * xs[2 * j] + sb[c + 2 * j], leak), -65504.f), 65504.f);
-      const float b = fminf(fmaxf(leaky(sw[c + 2 * j + 1] * xs[2 * j + 1] + sb[c + 2 * j + 1], leak), -65504.f), 65504.f);
+      const float a = fminf(fmaxf(leaky(sw[c + 2 * j] * xs[2 * j] + sb[c + 2 * j], leak) - ys[2 * j], -65504.f), 65504.f);
+      const float b =
+          fminf(fmaxf(leaky(sw[c + 2 * j + 1] * xs[2 * j + 1] + sb[c + 2 * j + 1], leak) - ys[2 * j + 1], -65504.f), 65504.f);
       y[j] = __floats2half2_rn(a, b);
     }
     *reinterpret_cast<uint4 *>(out + row * out_stride + c) = *reinterpret_cast<const uint4 *>(y);
@@ -278,16 +299,21 @@ __global__ void k_bn_f16out(const float *__restrict__ in, long long in_stride, _
 
 int bn_forward_f16out(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows, int64_t planes,
                       const float *mean, const float *var, const float *gamma, const float *beta, float eps, float leak,
-                      cudaStream_t s) {
+                      cudaStream_t s, const int32_t *pre_exist, const void *pre_out, int64_t pre_out_stride, const float *pre_in,
+                      int64_t pre_in_stride) {
   if (rows == 0 || planes == 0) return SCN_OK;
   if (planes > 4096) return fail(SCN_E_INVALID, "BatchNorm over more than 4096 planes");
   if (planes % 8 != 0 || in_stride % 4 != 0 || out_stride % 8 != 0 || !aligned16(in) || !aligned16(out))
     return fail(SCN_E_INVALID, "fp16 BatchNorm output needs planes and the output stride to be multiples of 8 and 16-byte aligned rows");
+  if (pre_exist && (!pre_out || !pre_in || pre_out_stride % 8 != 0 || pre_in_stride % 4 != 0 || !aligned16(pre_out) || !aligned16(pre_in)))
+    return fail(SCN_E_INVALID, "incremental fp16 BatchNorm: saved rows must be 16-byte aligned (fp16 stride a multiple of 8, fp32 of 4)");
   const long long work = rows * (planes / 8);
   unsigned blocks = blocks_for(work, 256);
   if (blocks > 148u * 16u) blocks = 148u * 16u;
   k_bn_f16out<<<blocks, 256, (size_t)planes * 2 * sizeof(float), s>>>(in, in_stride, static_cast<__half *>(out), out_stride, rows,
-                                                                      (int)planes, mean, var, gamma, beta, eps, leak);
+                                                                      (int)planes, mean, var, gamma, beta, eps, leak, pre_exist,
+                                                                      static_cast<const __half *>(pre_out), pre_out_stride, pre_in,
+                                                                      pre_in_stride);
   SCN_LAUNCHED();
   return SCN_OK;
 }

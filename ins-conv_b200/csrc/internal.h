@@ -198,9 +198,11 @@ int bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_strid
                cudaStream_t s);
 // BatchNorm + leaky ReLU (running statistics) with the result stored as fp16 rows (out: __half [rows, planes],
 // out_stride in fp16 elements)
+// pre_exist (optional, [rows]): incremental form, the residual against the saved frame's rows pre_out (fp16) / pre_in (fp32)
 int bn_forward_f16out(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows, int64_t planes,
                       const float *mean, const float *var, const float *gamma, const float *beta, float eps, float leak,
-                      cudaStream_t s);
+                      cudaStream_t s, const int32_t *pre_exist = nullptr, const void *pre_out = nullptr, int64_t pre_out_stride = 0,
+                      const float *pre_in = nullptr, int64_t pre_in_stride = 0);
 // fp16 form of the warp-level gather-GEMM: in = __half rows, weights packed by warp_mma_pack_f16 (fp16 fragments)
 bool warp_mma_f16_shape(int64_t K, int64_t Cin, int64_t Cout);
 // fp16 rows through the persistent tcgen05 kernel: planes multiples of 32, weights [vol][n_out][n_in padded to 64] fp16

@@ -403,13 +403,13 @@ double Incre_SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tenso
                                                  at::Tensor input_features, at::Tensor output_features,
                                                  at::Tensor weight, at::Tensor bias, Metadata3 &pre_m,
                                                  at::Tensor pre_input_feats, at::Tensor packed) {
-  need_cuda_f32(input_features, "input_features");
-  need_cuda_f32(pre_input_feats, "pre_input_feats");
+  // fp32 residual rows with fp32 saved rows, or ('fp16' precision) both as fp16 rows with the fp16 weight pack
+  FeatArg fin(input_features, "input_features"), fpre(pre_input_feats, "pre_input_feats");
+  TORCH_CHECK(fin.half == fpre.half, "residual rows and saved rows must have the same type (both float32 or both float16)");
   expect_filter(filterSize, 3, "SubmanifoldConvolution");
   c10::cuda::CUDAGuard guard(input_features.device());
   Size3 s(inputSize);
-  auto in = input_features.contiguous();
-  auto pre = pre_input_feats.contiguous();
+  const at::Tensor &in = fin.t, &pre = fpre.t;
   auto w = weight.contiguous();
   const int64_t n = scn_metadata_n_active(m.h(), s.v);
   TORCH_CHECK(n >= 0, "Metadata has no grid at this spatial size");
@@ -420,10 +420,10 @@ double Incre_SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tenso
   need_opt_cuda_f32(bias, w.size(2), "bias");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
-  WeightArg wa(w, packed);
-  check(scn_incre_ssc_forward(m.h(), pre_m.h(), s.v, in.data_ptr<float>(), in.size(1),
+  WeightArg wa(w, packed, fin.half);
+  check(scn_incre_ssc_forward(m.h(), pre_m.h(), s.v, fin.ptr, in.size(1),
                               output_features.data_ptr<float>(), w.size(2), wa.ptr, opt_ptr(bias),
-                              pre.data_ptr<float>(), pre.size(1), w.size(1), w.size(2), wa.precision, stream_of(in),
+                              fpre.ptr, pre.size(1), w.size(1), w.size(2), wa.precision, stream_of(in),
                               &flops),
         "Incre_SubmanifoldConvolution_updateOutput");
   return flops;
@@ -443,12 +443,11 @@ double Incre_Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputS
                                         at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
                                         at::Tensor output_features, at::Tensor weight, at::Tensor bias,
                                         Metadata3 &pre_m, at::Tensor pre_input_feats, at::Tensor packed) {
-  need_cuda_f32(input_features, "input_features");
-  need_cuda_f32(pre_input_feats, "pre_input_feats");
+  FeatArg fin(input_features, "input_features"), fpre(pre_input_feats, "pre_input_feats");
+  TORCH_CHECK(fin.half == fpre.half, "residual rows and saved rows must have the same type (both float32 or both float16)");
   c10::cuda::CUDAGuard guard(input_features.device());
   Size3 si(inputSize), so(outputSize);
-  auto in = input_features.contiguous();
-  auto pre = pre_input_feats.contiguous();
+  const at::Tensor &in = fin.t, &pre = fpre.t;
   auto w = weight.contiguous();
   const int64_t n = scn_metadata_n_active(m.h(), so.v);
   TORCH_CHECK(n >= 0, "Deconvolution: Metadata has no grid at the output spatial size");
@@ -459,10 +458,10 @@ double Incre_Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputS
   need_opt_cuda_f32(bias, w.size(2), "bias");
   output_features.resize_({n, w.size(2)});
   double flops = 0;
-  WeightArg wa(w, packed);
-  check(scn_incre_deconv_forward(m.h(), pre_m.h(), si.v, so.v, in.data_ptr<float>(), in.size(1),
+  WeightArg wa(w, packed, fin.half);
+  check(scn_incre_deconv_forward(m.h(), pre_m.h(), si.v, so.v, fin.ptr, in.size(1),
                                  output_features.data_ptr<float>(), w.size(2), wa.ptr, opt_ptr(bias),
-                                 pre.data_ptr<float>(), pre.size(1), w.size(1), w.size(2), wa.precision, stream_of(in),
+                                 fpre.ptr, pre.size(1), w.size(1), w.size(2), wa.precision, stream_of(in),
                                  &flops),
         "Incre_Deconvolution_updateOutput");
   return flops;
@@ -481,7 +480,14 @@ void Incre_BatchNormalization_updateOutput(at::Tensor input_features, at::Tensor
   auto in = input_features.contiguous();
   auto po = pre_output_feats.contiguous();
   auto pi = pre_input_feats.contiguous();
-  need_cuda_f32(po, "pre_output_feats");
+  // 'fp16' precision: an output tensor of type float16 asks for the residual as fp16 rows; the saved output then is
+  // the fp16 tensor the saved frame's BatchNorm wrote
+  const bool half_out = output_features.scalar_type() == at::kHalf;
+  if (half_out) {
+    TORCH_CHECK(po.is_cuda() && po.scalar_type() == at::kHalf, "pre_output_feats must be the saved float16 rows");
+  } else {
+    need_cuda_f32(po, "pre_output_feats");
+  }
   need_cuda_f32(pi, "pre_input_feats");
   TORCH_CHECK(in.dim() == 2, "input_features must be [rows, planes]");
   need_rows(in, scn_metadata_n_active(m.h(), s.v), in.size(1), "input_features");
@@ -493,8 +499,16 @@ void Incre_BatchNormalization_updateOutput(at::Tensor input_features, at::Tensor
   need_opt_cuda_f32(runningVar, in.size(1), "runningVar");
   need_opt_cuda_f32(weight, in.size(1), "weight");
   need_opt_cuda_f32(bias, in.size(1), "bias");
-  output_features.resize_as_(in);
+  output_features.resize_(in.sizes());
   if (in.numel() == 0) return;
+  if (half_out) {
+    check(scn_incre_bn_forward_f16(m.h(), pre_m.h(), s.v, in.data_ptr<float>(), in.size(1), output_features.data_ptr<at::Half>(),
+                                   in.size(1), in.size(1), runningMean.data_ptr<float>(), runningVar.data_ptr<float>(),
+                                   opt_ptr(weight), opt_ptr(bias), eps, leakiness, po.data_ptr<at::Half>(), po.size(1),
+                                   pi.data_ptr<float>(), pi.size(1), stream_of(in)),
+          "Incre_BatchNormalization_updateOutput");
+    return;
+  }
   check(scn_incre_bn_forward(m.h(), pre_m.h(), s.v, in.data_ptr<float>(), in.size(1),
                              output_features.data_ptr<float>(), in.size(1), in.size(1), runningMean.data_ptr<float>(),
                              runningVar.data_ptr<float>(), opt_ptr(weight), opt_ptr(bias), eps, leakiness,

@@ -84,6 +84,7 @@ PROTOTYPES = {
     "scn_incre_ssc_rulebook": (_int, [_p, _p, _i64p, _p, _p, _p]),
     "scn_incre_deconv_forward": (_int, [_p, _p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _p, _i64, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_incre_bn_forward": (_int, [_p, _p, _i64p, _p, _i64, _p, _i64, _i64, _p, _p, _p, _p, _dbl, _dbl, _p, _p, _p]),
+    "scn_incre_bn_forward_f16": (_int, [_p, _p, _i64p, _p, _i64, _p, _i64, _i64, _p, _p, _p, _p, _dbl, _dbl, _p, _i64, _p, _i64, _p]),
 }
 
 

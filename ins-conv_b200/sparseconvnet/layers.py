@@ -142,6 +142,17 @@ def _f32(module, t):
     return wide
 
 
+def _residual_rows(module, rows, saved):
+    """(residual rows, saved rows, weight pack) for an incremental convolution.  In 'fp16' precision the BatchNorm in
+    front hands over the residual as fp16 rows and the saved frame kept its input as fp16 rows: both go to the fp16
+    kernels as they are.  Mixed types (a saved frame from another precision) are widened to fp32."""
+    if rows.dtype == torch.float16 and saved.dtype == torch.float16:
+        return rows, saved, _packed_for(module, rows)
+    if rows.dtype == torch.float16:
+        rows = rows.float()
+    return rows, _f32(module, saved), _packed(module)
+
+
 def _count(madds, out):
     sparseconvnet.forward_pass_multiplyAdd_count += madds
     sparseconvnet.forward_pass_hidden_states += out.nelement()
@@ -184,9 +195,10 @@ class SubmanifoldConvolution(Module):
             _count(madds, out)
             res = input.like(out)
             return _halo(_finish_fused(res, fuse_bn, fused[3]) if fused else res)
+        rows, saved, packed = _residual_rows(self, input.features, self.save_input_feats)
         madds = SCN.Incre_SubmanifoldConvolution_updateOutput(
-            input.spatial_size, self.filter_size, input.metadata, input.features, out, self._parameters["weight"],
-            optionalTensor(self, "bias"), self.save_meta, _f32(self, self.save_input_feats), _packed(self))
+            input.spatial_size, self.filter_size, input.metadata, rows, out, self._parameters["weight"],
+            optionalTensor(self, "bias"), self.save_meta, saved, packed)
         _count(madds, out)
         return input.like(out)
 
@@ -250,10 +262,10 @@ class Deconvolution(_Strided):
                 out, self._parameters["weight"], optionalTensor(self, "bias"), _packed_for(self, input.features))
             _keep(self, save_meta=input.metadata, save_input_feats=input.features)
         else:
+            rows, saved, packed = _residual_rows(self, input.features, self.save_input_feats)
             madds = SCN.Incre_Deconvolution_updateOutput(
-                input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                out, self._parameters["weight"], optionalTensor(self, "bias"), self.save_meta,
-                _f32(self, self.save_input_feats), _packed(self))
+                input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, rows,
+                out, self._parameters["weight"], optionalTensor(self, "bias"), self.save_meta, saved, packed)
         _count(madds, out)
         return input.like(out, out_size)
 
@@ -287,7 +299,10 @@ class BatchNormalization(Module):
         ready = input.bn_ready
         if ready is not None and ready[0] is self and not residual and not self.training:
             return ready[1]  # the convolution in front of this module already wrote this module's result (and state)
-        half_rows = half_rows and not self.training and not residual and self.nPlanes % 8 == 0
+        half_rows = half_rows and not self.training and self.nPlanes % 8 == 0
+        if residual:  # fp16 residual rows when the saved frame's output was written as fp16 rows and its input was kept
+            half_rows = half_rows and self.save_output.features.dtype == torch.float16 and \
+                self.save_input.features.dtype == torch.float32 and self.save_input.features.numel() > 0
         feats = input.features
         out = feats.new_empty(0, dtype=torch.float16 if half_rows else torch.float32)
         mean, var = self._buffers["running_mean"], self._buffers["running_var"]
@@ -303,7 +318,8 @@ class BatchNormalization(Module):
             SCN.Incre_BatchNormalization_updateOutput(
                 feats, out, _NONE, _NONE, mean, var,
                 optionalTensor(self, "weight"), optionalTensor(self, "bias"), self.eps, self.momentum, self.training,
-                self.leakiness, input.metadata, self.save_output.metadata, _f32(self, self.save_output.features),
+                self.leakiness, input.metadata, self.save_output.metadata,
+                self.save_output.features if half_rows else _f32(self, self.save_output.features),
                 self.save_input.features, input.spatial_size)
         return input.like(out)
 

@@ -141,3 +141,65 @@ def test_incremental_operators_one_by_one(cuda, precision):
     got = m.incre_output_forward(pre, t(vox), t(pvox))
     assert rel(got, O.incre_output_forward(vox, g, pg, pvox)) <= 1e-6
     cabi.check_errors()
+
+
+def test_incremental_operators_on_fp16_rows(cuda):
+    """SCN_PREC_F16 in the incremental operators: residual rows and saved rows are fp16 (as a BatchNorm in front of the
+    layer writes them), weights are the fp16 pack; the incremental BatchNorm writes its residual as fp16 rows and reads
+    the saved frame's output as fp16 rows.  Against the oracle's formulas on the same fp16-rounded inputs."""
+    import ctypes as C
+    stream = torch.cuda.current_stream().cuda_stream
+    coords, new = frames(7)
+    rng = np.random.RandomState(11)
+    pre, m = build(cuda, coords), build(cuda, new)
+    pg, g = O.Grid(coords), O.Grid(new)
+    h = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(cuda).half()
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(cuda)
+
+    def packed(w):
+        p = torch.empty(cabi.lib().scn_packed_size_f16(w.shape[0], w.shape[1], w.shape[2]), dtype=torch.float16, device=cuda)
+        dw = t(w)
+        cabi.call("scn_pack_weights_f16", cabi.ptr(dw), w.shape[0], w.shape[1], w.shape[2], cabi.ptr(p), stream)
+        torch.cuda.synchronize()
+        return p
+
+    fl = C.c_double(0)
+    for n_in, n_out in ((32, 32), (64, 32), (96, 96), (128, 160)):  # warp-level kernels, slab kernel
+        x, px = h(rng.randn(g.n, n_in)), h(rng.randn(pg.n, n_in))
+        w = synth.kaiming_uniform(rng, 27, n_in, n_out)
+        want = O.incre_ssc_forward(x.float().cpu().numpy(), w, g, pg, px.float().cpu().numpy(), None)
+        out = torch.empty(g.n, n_out, dtype=torch.float32, device=cuda)
+        pw = packed(w)
+        cabi.call("scn_incre_ssc_forward", m.h, pre.h, cabi.size3(96), cabi.ptr(x), n_in, cabi.ptr(out), n_out, cabi.ptr(pw), None,
+                  cabi.ptr(px), n_in, n_in, n_out, cabi.PREC_F16, stream, C.byref(fl))
+        assert rel(out, want) <= 2e-2, (n_in, n_out)
+        assert fl.value == O.rule_flops(O.ssc_rules(g), n_in, n_out) + O.rule_flops(O.incre_ssc_rules(g, pg), n_in, n_out)
+    # BatchNorm residual as fp16 rows
+    for planes, leak in ((32, 0.0), (96, 0.333)):
+        x, px = rng.randn(g.n, planes).astype(np.float32), rng.randn(pg.n, planes).astype(np.float32)
+        mean, var = rng.randn(planes).astype(np.float32), rng.uniform(0.5, 2, planes).astype(np.float32)
+        gamma, beta = rng.randn(planes).astype(np.float32), rng.randn(planes).astype(np.float32)
+        py = h(O.bn_forward(px, mean, var, gamma, beta, 1e-4, leak).numpy())  # what the saved frame wrote
+        want = O.incre_bn_forward(x, mean, var, gamma, beta, 1e-4, leak, g, pg, py.float().cpu(), px)
+        out = torch.empty(g.n, planes, dtype=torch.float16, device=cuda)
+        dx, dpx, dm, dv, dg, db = t(x), t(px), t(mean), t(var), t(gamma), t(beta)
+        cabi.call("scn_incre_bn_forward_f16", m.h, pre.h, cabi.size3(96), cabi.ptr(dx), planes, cabi.ptr(out), planes, planes,
+                  cabi.ptr(dm), cabi.ptr(dv), cabi.ptr(dg), cabi.ptr(db), 1e-4, leak, cabi.ptr(py), planes, cabi.ptr(dpx), planes,
+                  stream)
+        torch.cuda.synchronize()
+        assert rel(out.float(), want) <= 2e-3
+    # incremental deconvolution on fp16 rows
+    coarse, rules = O.conv2_rules(g)
+    pcoarse, _ = O.conv2_rules(pg)
+    pre.conv_rulebook(96, 48)
+    m.conv_rulebook(96, 48)
+    for n_in, n_out in ((64, 32), (128, 96)):
+        xc, pxc = h(rng.randn(coarse.n, n_in)), h(rng.randn(pcoarse.n, n_in))
+        wd = synth.kaiming_uniform(rng, 8, n_in, n_out)
+        want = O.incre_deconv_forward(xc.float().cpu().numpy(), wd, g, coarse, rules, pg, pcoarse, pxc.float().cpu().numpy())
+        out = torch.empty(g.n, n_out, dtype=torch.float32, device=cuda)
+        pw = packed(wd)
+        cabi.call("scn_incre_deconv_forward", m.h, pre.h, cabi.size3(48), cabi.size3(96), cabi.ptr(xc), n_in, cabi.ptr(out), n_out,
+                  cabi.ptr(pw), None, cabi.ptr(pxc), n_in, n_in, n_out, cabi.PREC_F16, stream, C.byref(fl))
+        assert rel(out, want) <= 2e-2, (n_in, n_out)
+    cabi.check_errors()

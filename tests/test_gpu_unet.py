@@ -87,6 +87,49 @@ def test_small_unet_incremental_matches_oracle(cuda):
     assert rel_err(got1, want1) <= 1e-4
 
 
+@pytest.mark.parametrize("precision,tol", [("tf32", 2e-2), ("fp16", 2e-2)])
+def test_incremental_frame_in_the_tensor_core_precisions(cuda, monkeypatch, precision, tol):
+    """The reference-style incremental frame with planes that take the tensor-core kernels (32..128: warp-level, slab
+    and tcgen05 kernels) against the oracle's incremental formulas.  In 'fp16' precision the residual travels as fp16
+    rows from every BatchNorm to the convolution behind it and the saved rows are read as the fp16 rows the full frame
+    wrote (no widened copies): checked by the types the modules saw."""
+    import sparseconvnet as scn
+    torch.manual_seed(4)
+    model = small_unet(scn, [32, 64, 96, 128], residual=True, full_scale=128).eval()
+    randomize_bn(model, 4)
+    c = synth.boxes_and_spheres(4)
+    f = synth.rgb(4, c.shape[0])
+    nf = synth.next_frame(c, f, seed=4)
+    want0, runner = run_oracle(model, [torch.from_numpy(c), torch.from_numpy(f)])
+    want1, _ = run_oracle(model, [torch.from_numpy(nf["new_coords"]), torch.from_numpy(nf["new_feats"])], True, runner)
+    model = model.to(cuda)
+    seen = []
+    real_bn = scn.SCN.Incre_BatchNormalization_updateOutput
+
+    def spy_bn(feats, out, *rest):
+        real_bn(feats, out, *rest)
+        seen.append((out.dtype, rest[-3].dtype))  # the residual written, the saved output read
+
+    monkeypatch.setattr(scn.SCN, "Incre_BatchNormalization_updateOutput", spy_bn)
+    scn.set_precision(precision)
+    try:
+        got0 = model([torch.from_numpy(c).to(cuda), torch.from_numpy(f).to(cuda)])
+        del seen[:]
+        got1 = model([torch.from_numpy(nf["new_coords"]).to(cuda), torch.from_numpy(nf["new_feats"]).to(cuda)], True)
+        scn.SCN.check_errors()
+    finally:
+        scn.set_precision("fp32")
+    assert rel_err(got0, want0) <= 5e-2
+    assert got1.shape[0] == nf["new_coords"].shape[0]
+    assert rel_err(got1, want1) <= 5e-2, precision
+    assert float((got1.cpu() - want1).norm() / want1.norm()) <= tol, precision
+    halves = [d for d in seen if d == (torch.float16, torch.float16)]
+    if precision == "fp16":  # all but the BatchNorms that are not in front of a convolution
+        assert len(seen) > 10 and len(halves) >= len(seen) - 2 and all(d[0] == d[1] for d in seen)
+    else:
+        assert len(seen) > 10 and not halves
+
+
 def test_reference_model_py_topology(cuda):
     # the Naive_UNet of the reference's model.py (m=32, planes 32..224, reps 2, residual), reproduced here
     # because the reference tree does not travel with the tests
