@@ -914,16 +914,21 @@ def main():
                 all_c, all_f = torch.cat(acc_c), torch.cat(acc_f)
                 lat["full"].append(clocked(lambda: model([all_c, all_f])))
         scene_points_reference = int(sum(c.shape[0] for c in acc_c))
+        model([d_coords, d_feats])
+        model(list(frames[0]), "exact")  # untimed: first use of the exact mode (one-time set-up, as every timed leg warms up)
         model([d_coords, d_feats])  # reset the kept scene to the base room
-        for dn, dfn in frames:
+        worst = (0.0, -1)
+        for fr, (dn, dfn) in enumerate(frames):
             lat["exact"].append(clocked(lambda: model([dn, dfn], "exact")))
+            if lat["exact"][-1] > worst[0]:
+                worst = (lat["exact"][-1], fr)
         pct = lambda v, q: float(sorted(v)[min(len(v) - 1, int(q * len(v)))])
         stats = lambda v: {"mean": sum(v) / len(v), "p50": pct(v, 0.5), "p99": pct(v, 0.99)}
         sweep = {"frames": n_frames,
                  "scene_voxels_at_end": int(model.sparseModel[0].scene_coords.shape[0]),
                  "reference_ms": stats(lat["reference"]),
                  "full_recompute_every_10th_frame_ms": stats(lat["full"]),
-                 "exact_ms": stats(lat["exact"]),
+                 "exact_ms": stats(lat["exact"]), "exact_slowest_frame": {"ms": worst[0], "frame": worst[1]},
                  "points_fed_in_reference_pass": scene_points_reference,
                  "timing": "host wall clock around each frame, device synchronised on both sides"}
         model([d_coords, d_feats])
