@@ -19,7 +19,7 @@ rulebook builders and Metadata run as written.  Third-party pieces that are NOT 
 stood in for by contract: CUDPP (extra/cudpp: sort-based multivalue hash, compact, scan, reduce), google
 sparsehash, easy_profiler, the CUDA runtime (ref_shim/, ref_emu.h, ref_cudpp.h).
 
-Usage: python oracle/build_ref.py [--force] [--verbose] [--reference /root/reference]
+Usage: python oracle/build_ref.py [--force] [--verbose] [--reference DIR]   (DIR: the reference tree; default below)
 """
 import os
 import re
