@@ -397,6 +397,13 @@ SCN_API int scn_halo_set_spin_limit(scn_halo *h, int64_t polls);
 SCN_API int scn_halo_exchange(scn_halo *h, const int64_t *rows, const int64_t *counts, int64_t cap, void *a,
                               int64_t a_row_bytes, void *b, int64_t b_row_bytes, void *stream);
 SCN_API int scn_halo_status(scn_halo *h, int *timed_out, int *overflow, void *stream);
+/* The row lists scn_halo_exchange takes, for a rank that owns the sites with lo <= x < hi of the scale `size`
+ * (coordinates of that scale): lists [4][cap] int64 on the device = rows with x == lo, x == hi - 1, x == lo - 1,
+ * x == hi, each ascending; counts [4] int64 on the device.  left / right: whether the rank has a neighbour on that side
+ * (the lists of a side without one stay empty).  Two launches, no host round trip; entries beyond cap are dropped
+ * and show as counts[i] > cap (which scn_halo_exchange reports as overflow). */
+SCN_API int scn_halo_plane_lists(scn_metadata *m, const int64_t size[3], int lo, int hi, int left, int right, int64_t cap,
+                                 int64_t *lists, int64_t *counts, void *stream);
 
 /* ---- label fusion: the per-voxel vote table behind the network --------------------------------------------
  * Replaces Result<3> (Metadata/resultHash.h:22-138; bound as Result_3, pybind.cpp:36-45) and ResultOfWeight<3>

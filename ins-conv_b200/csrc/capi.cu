@@ -442,6 +442,18 @@ int64_t scn_metadata_input_n_active(scn_metadata *m) {
   if (input_grid(m, &g) != SCN_OK) return -1;
   return g->n;
 }
+int scn_halo_plane_lists(scn_metadata *m, const int64_t size[3], int lo, int hi, int left, int right, int64_t cap,
+                         int64_t *lists, int64_t *counts, void *stream) {
+  Grid *g;
+  SCN_TRY(need_grid(m, size, &g));
+  if (cap < 0 || !counts || (cap && !lists)) return fail(SCN_E_INVALID, "scn_halo_plane_lists: bad argument");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (g->n == 0) {
+    SCN_CUDA(cudaMemsetAsync(counts, 0, 4 * sizeof(int64_t), s));
+    return SCN_OK;
+  }
+  return halo_plane_lists(g->coords, g->n, lo, hi, left != 0, right != 0, cap, lists, counts, s);
+}
 int scn_input_layer_set_site_counts(scn_metadata *m, const int32_t *counts, int64_t n, void *stream) {
   Grid *g;
   SCN_TRY(input_grid(m, &g));

@@ -20,6 +20,7 @@
 // Inboxes are plain cudaMalloc allocations shared through CUDA IPC handles (the ranks are processes of one box).
 // The reference has no multi-GPU path; there is nothing this replaces.
 #include "internal.h"
+#include <limits.h>
 #include <string.h>
 
 namespace scn {
@@ -136,7 +137,81 @@ template <typename W> __global__ void __launch_bounds__(256) k_halo_unpack(const
   }
 }
 
+// Row lists of the four planes next to a rank's cuts (x == lo: sent left, x == hi - 1: sent right, x == lo - 1:
+// received from the left, x == hi: received from the right), each ascending, from a scale's x coordinates.  Two
+// launches of the same grid: every block counts the hits of its contiguous piece of the rows, then (second launch)
+// adds up the counts of the pieces in front of it and writes its hits in order.  plane[i] = INT_MIN switches list i off.
+constexpr int kListBlocks = 128;
+constexpr int kListThreads = 256;
+
+__global__ void __launch_bounds__(kListThreads) k_plane_lists(const int32_t *__restrict__ x, long long n, int4 plane,
+                                                              unsigned int *__restrict__ piece_counts, int64_t *__restrict__ lists,
+                                                              int64_t *__restrict__ counts, long long cap, int pass) {
+  __shared__ unsigned int s_warp[4][kListThreads / 32];
+  __shared__ unsigned int s_base[4];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const long long per = (n + gridDim.x - 1) / gridDim.x;
+  const long long lo = per * blockIdx.x, hi = lo + per < n ? lo + per : n;
+  const int want[4] = {plane.x, plane.y, plane.z, plane.w};
+  unsigned int run[4] = {0, 0, 0, 0};  // hits of this block so far (second pass: in front of the current chunk)
+  if (pass == 1) {
+    if (tid < 4) {
+      unsigned int before = 0;
+      for (int b = 0; b < (int)blockIdx.x; ++b) before += piece_counts[4 * b + tid];
+      s_base[tid] = before;
+      if (blockIdx.x == gridDim.x - 1) counts[tid] = (int64_t)before + piece_counts[4 * blockIdx.x + tid];
+    }
+    __syncthreads();
+  }
+  for (long long c0 = lo; c0 < hi; c0 += kListThreads) {
+    const long long i = c0 + tid;
+    const int v = i < hi ? x[i] : INT_MIN + 1;
+    unsigned int below[4];
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+      const unsigned int b = __ballot_sync(0xffffffffu, v == want[l]);
+      below[l] = __popc(b & ((1u << lane) - 1u));
+      if (lane == 0) s_warp[l][warp] = __popc(b);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+      unsigned int before = 0, total = 0;
+#pragma unroll
+      for (int w = 0; w < kListThreads / 32; ++w) {
+        const unsigned int c = s_warp[l][w];
+        before += w < warp ? c : 0u;
+        total += c;
+      }
+      if (pass == 1 && v == want[l]) {
+        const long long at = (long long)s_base[l] + run[l] + before + below[l];
+        if (at < cap) lists[(long long)l * cap + at] = i;
+      }
+      run[l] += total;
+    }
+    __syncthreads();
+  }
+  if (pass == 0 && tid < 4) piece_counts[4 * blockIdx.x + tid] = run[tid];
+}
+
 }  // namespace
+
+int halo_plane_lists(const int32_t *x, int64_t n, int lo, int hi, bool left, bool right, int64_t cap, int64_t *lists,
+                     int64_t *counts, cudaStream_t s) {
+  unsigned int *pieces = nullptr;
+  SCN_TRY(dev_alloc_t(&pieces, (size_t)4 * kListBlocks, s));
+  const int off = INT_MIN;
+  const int4 plane = make_int4(left ? lo : off, right ? hi - 1 : off, left ? lo - 1 : off, right ? hi : off);
+  for (int pass = 0; pass < 2; ++pass) {
+    k_plane_lists<<<kListBlocks, kListThreads, 0, s>>>(x, n, plane, pieces, lists, counts, cap, pass);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
+  const cudaError_t e = cudaGetLastError();
+  dev_free(pieces, s);
+  if (e != cudaSuccess) return fail(SCN_E_CUDA, std::string("plane lists: ") + cudaGetErrorString(e));
+  return SCN_OK;
+}
+
 }  // namespace scn
 
 using namespace scn;

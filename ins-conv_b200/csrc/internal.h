@@ -214,6 +214,9 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
                        int64_t init_stride, cudaStream_t s, const EpiBn *epi = nullptr);
 int warp_mma_pack_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
 // wide layers on small grids: 16 rows x 32 output planes per warp, whole reduction in one launch
+// ascending row lists [4][cap] (int64) of the planes x == lo, hi - 1, lo - 1, hi (a side without a neighbour: empty) and their lengths
+int halo_plane_lists(const int32_t *x, int64_t n, int lo, int hi, bool left, bool right, int64_t cap, int64_t *lists,
+                     int64_t *counts, cudaStream_t s);
 bool warp_slab_f16_shape(int64_t K, int64_t Cin, int64_t Cout);
 extern int g_slab_share;
 int warp_mma_pack_f16_any(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);

@@ -195,6 +195,16 @@ class Metadata3 {
   void setBuildAhead(int neighbour_maps, int coarse_levels) {
     check(scn_metadata_set_build_ahead(h_, neighbour_maps, coarse_levels), "Metadata.setBuildAhead");
   }
+  // row lists [4][cap] and their lengths [4] (CUDA int64) of the planes next to a slab's cuts: scn_halo_plane_lists
+  std::pair<at::Tensor, at::Tensor> haloPlaneLists(at::Tensor spatialSize, int64_t lo, int64_t hi, bool left, bool right, int64_t cap) {
+    Size3 s(spatialSize);
+    auto opts = at::TensorOptions().dtype(at::kLong).device(at::kCUDA);
+    auto lists = at::empty({4, cap}, opts), counts = at::empty({4}, opts);
+    check(scn_halo_plane_lists(h_, s.v, (int)lo, (int)hi, left ? 1 : 0, right ? 1 : 0, cap, lists.data_ptr<int64_t>(),
+                               counts.data_ptr<int64_t>(), (void *)c10::cuda::getCurrentCUDAStream().stream()),
+          "Metadata.haloPlaneLists");
+    return {lists, counts};
+  }
   void setSiteCounts(at::Tensor counts) {
     TORCH_CHECK(counts.is_cuda() && counts.scalar_type() == at::kInt && counts.dim() == 1, "counts must be a CUDA int32 vector");
     auto c = counts.contiguous();
@@ -736,7 +746,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
       .def("setBuildAhead", &Metadata3::setBuildAhead)
       .def("buildUsed", &Metadata3::buildUsed)
       .def("inherit", &Metadata3::inherit)
-      .def("setSiteCounts", &Metadata3::setSiteCounts);
+      .def("setSiteCounts", &Metadata3::setSiteCounts)
+      .def("haloPlaneLists", &Metadata3::haloPlaneLists);
   mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("dilated_rate"), pybind11::arg("packed") = none, pybind11::arg("addend") = none, pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("skip_raw") = false);
   mod.def("Convolution_updateOutput", &Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none, pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("skip_raw") = false);
   mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);

@@ -111,6 +111,7 @@ PROTOTYPES.update({
     "scn_halo_set_spin_limit": (_int, [_p, _i64]),
     "scn_halo_exchange": (_int, [_p, _p, _p, _i64, _p, _i64, _p, _i64, _p]),
     "scn_halo_status": (_int, [_p, C.POINTER(_int), C.POINTER(_int), _p]),
+    "scn_halo_plane_lists": (_int, [_p, _i64p, _int, _int, _int, _int, _i64, _p, _p, _p]),
 })
 
 PROTOTYPES.update({

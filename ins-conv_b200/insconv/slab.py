@@ -194,15 +194,12 @@ class PeerSlabExchange(SlabExchange):
         if hit is not None and hit["meta"] is tensor.metadata:
             return hit
         shift = int(round(np.log2(self.full_scale / size)))
-        x = tensor.metadata.getSpatialLocationsDevice(tensor.spatial_size)[0]
         lo, hi = self.cuts[self.rank] >> shift, self.cuts[self.rank + 1] >> shift
-        cap = min(int(x.shape[0]), self.max_rows)
-        none = torch.zeros_like(x, dtype=torch.bool)
-        left, right = self.rank > 0, self.rank + 1 < self.world
-        planes = torch.stack([x == lo if left else none, x == hi - 1 if right else none,
-                              x == lo - 1 if left else none, x == hi if right else none])
-        lists = torch.stack([torch.nonzero_static(m, size=cap, fill_value=0).flatten() for m in planes]).contiguous()
-        hit = {"meta": tensor.metadata, "lists": lists, "counts": planes.sum(1).contiguous(), "cap": cap}
+        n = int(tensor.metadata.getNActive(tensor.spatial_size))
+        cap = max(min(n, self.max_rows), 1)
+        # two launches of the library (no torch ops, no host round trip): ascending rows of the four planes
+        lists, counts = tensor.metadata.haloPlaneLists(tensor.spatial_size, lo, hi, self.rank > 0, self.rank + 1 < self.world, cap)
+        hit = {"meta": tensor.metadata, "lists": lists, "counts": counts, "cap": cap}
         self.cache[size] = hit
         return hit
 

@@ -130,3 +130,28 @@ def test_bad_arguments_are_refused():
             _exchange(cabi, h, lists, torch.zeros(4, dtype=torch.int64).cuda(), a)
     finally:
         cabi.call("scn_halo_destroy", h)
+
+
+def test_plane_row_lists_match_a_direct_search(cuda):
+    """scn_halo_plane_lists (through Metadata.haloPlaneLists): ascending rows of the planes x == lo, hi - 1, lo - 1, hi of a
+    scale, with and without neighbours, at the input scale and at a coarse one, and with a capacity that cuts them short."""
+    import sparseconvnet as scn
+    from insconv import synth
+    c = synth.room(3, target=60000)
+    il = scn.InputLayer(3, 4096, mode=4)
+    t = il([torch.from_numpy(c).to(cuda), torch.ones(c.shape[0], 1, device=cuda)])
+    conv = scn.Convolution(3, 1, 1, 2, 2, False).to(cuda)
+    coarse = conv(t)
+    for tensor, lo, hi in ((t, 100, 228), (t, 8, 9), (coarse, 50, 114)):
+        x = tensor.metadata.getSpatialLocationsDevice(tensor.spatial_size)[0]
+        n = x.shape[0]
+        for left, right in ((True, True), (False, True), (True, False)):
+            lists, counts = tensor.metadata.haloPlaneLists(tensor.spatial_size, lo, hi, left, right, n)
+            want = [torch.nonzero(x == v).flatten() if on else x.new_empty(0, dtype=torch.long)
+                    for v, on in ((lo, left), (hi - 1, right), (lo - 1, left), (hi, right))]
+            assert counts.tolist() == [w.numel() for w in want]
+            for i, w in enumerate(want):
+                assert torch.equal(lists[i, :w.numel()], w)
+        lists, counts = tensor.metadata.haloPlaneLists(tensor.spatial_size, lo, hi, True, True, 5)
+        full = int((x == lo).sum())
+        assert int(counts[0]) == full and torch.equal(lists[0, :min(5, full)], torch.nonzero(x == lo).flatten()[:5])
