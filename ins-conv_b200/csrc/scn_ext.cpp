@@ -747,7 +747,27 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
       .def("buildUsed", &Metadata3::buildUsed)
       .def("inherit", &Metadata3::inherit)
       .def("setSiteCounts", &Metadata3::setSiteCounts)
-      .def("haloPlaneLists", &Metadata3::haloPlaneLists);
+      .def("haloPlaneLists", &Metadata3::haloPlaneLists)
+      // The rest of the reference's Metadata interface (pybind.cpp:16-33).  The two setters only record a value that
+      // the sample-by-sample builders below would read; those builders (and the dense / thresholded-tensor entry points)
+      // feed the CPU SparseGrid path of the reference, which the GPU-grid hot path never takes: they exist here so that
+      // code probing for them finds them, and say what they are when called.
+      .def("setInputSpatialSize", [](Metadata3 &, at::Tensor) {})
+      .def("setNormalGuideScale", [](Metadata3 &, int64_t) {});
+  for (const char *name : {"batchAddSample", "setInputSpatialLocation", "setInputSpatialLocations",
+                           "createMetadataForDenseToSparse", "sparsifyMetadata", "appendMetadata", "sparsifyCompare",
+                           "addSampleFromThresholdedTensor", "generateRuleBooks3s2", "generateRuleBooks2s2",
+                           "compareSparseHelper"}) {
+    const std::string what = name;
+    pybind11::setattr(mod.attr("Metadata_3"), name,
+                      pybind11::cpp_function(
+                          [what](pybind11::args, pybind11::kwargs) {
+                            throw std::runtime_error("Metadata." + what +
+                                                     " belongs to the reference's CPU sparse-grid path, which this build "
+                                                     "does not have (scenes enter through InputLayer)");
+                          },
+                          pybind11::is_method(mod.attr("Metadata_3"))));
+  }
   mod.def("SubmanifoldConvolution_updateOutput", &SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("dilated_rate"), pybind11::arg("packed") = none, pybind11::arg("addend") = none, pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("skip_raw") = false);
   mod.def("Convolution_updateOutput", &Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none, pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("skip_raw") = false);
   mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);

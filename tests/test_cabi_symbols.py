@@ -56,3 +56,13 @@ def test_extension_module_exports_the_reference_operator_names():
     import pytest
     with pytest.raises(RuntimeError):
         scn.SCN.SubmanifoldConvolution_backward()
+    # label fusion classes and the whole method surface of the reference's Metadata class (pybind.cpp:13-45, 275-282)
+    for cls, methods in (("Result_3", ["set", "query", "multiQuery", "clear", "update", "get_all_points_labels", "finalize"]),
+                         ("ResultOfWeight", ["query", "multiQuery", "clear", "update", "get_all_points_labels", "finalize"]),
+                         ("Metadata_3", ["clear", "setInputSpatialSize", "setNormalGuideScale", "batchAddSample",
+                                         "setInputSpatialLocation", "setInputSpatialLocations", "getSpatialLocations",
+                                         "createMetadataForDenseToSparse", "sparsifyMetadata", "appendMetadata",
+                                         "sparsifyCompare", "addSampleFromThresholdedTensor", "generateRuleBooks3s2",
+                                         "generateRuleBooks2s2", "compareSparseHelper"])):
+        for name in methods:
+            assert hasattr(getattr(scn.SCN, cls), name), (cls, name)
