@@ -235,7 +235,8 @@ def test_config3_full_room_tf32_vs_fp32_oracle(cuda):
     halves = [m for m in model.modules() if isinstance(m, scn.BatchNormalization)
               and getattr(m, "save_output", None) is not None and m.save_output.features.dtype == torch.float16]
     assert len(halves) >= 10
-    # a reference-style incremental frame after an fp16 full frame still works (saved fp16 rows are widened)
+    # a reference-style incremental frame after an fp16 full frame on the full-size network (parity of that path: see
+    # test_incremental_frame_in_the_tensor_core_precisions)
     scn.set_precision("fp16")
     try:
         model(x)
