@@ -250,6 +250,14 @@ typedef struct scn_epilogue {
   void *bn_out;
   int64_t bn_out_stride;
   int skip_raw;
+  /* incremental operators only (scn_incre_*_forward_ex; must be NULL / 0 elsewhere): the rows the saved frame's
+   * BatchNorm read (fp32, [saved sites, n_out]) and wrote (fp16).  With them the fused result is the RESIDUAL of the
+   * activation, act((v + saved input) * scale + shift) - saved output, for sites that existed in the saved frame
+   * (CUDA/BatchNormalization.cu:112-150) and act(v * scale + shift) for new ones. */
+  const float *bn_pre_in;
+  int64_t bn_pre_in_stride;
+  const void *bn_pre_out;
+  int64_t bn_pre_out_stride;
 } scn_epilogue;
 /* scn_ssc_forward / scn_conv_forward / scn_deconv_forward with an epilogue (epi == NULL: exactly those). */
 SCN_API int scn_ssc_forward_ex(scn_metadata *m, const int64_t size[3], const float *in, int64_t in_stride, float *out,
@@ -366,6 +374,18 @@ SCN_API int scn_incre_bn_forward(scn_metadata *m, scn_metadata *pre, const int64
  * (out: fp16 [n_active, planes], strides in elements), the saved frame's BatchNorm output is read as the fp16 rows that
  * frame wrote (pre_out), its input as fp32 rows (pre_in).  With SCN_PREC_F16, scn_incre_ssc_forward and
  * scn_incre_deconv_forward read both the residual rows and the saved rows as fp16 and take the fp16 weight pack. */
+/* scn_incre_ssc_forward with an epilogue: addend = residual rows added to the result (the shortcut of a ResNet block);
+ * bn_* = the incremental BatchNorm behind the layer formed in the convolution's epilogue (bn_pre_in / bn_pre_out given,
+ * skip_raw 0).  scn_incre_conv_forward_ex: the stride-2 convolution of the residual (scn_conv_forward on the
+ * incremental grid, CUDA/Convolution.cpp:83-113) with the same epilogue on the coarse scale. */
+SCN_API int scn_incre_ssc_forward_ex(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const float *in,
+                                     int64_t in_stride, float *out, int64_t out_stride, const float *weight,
+                                     const float *bias, const float *pre_in, int64_t pre_in_stride, int64_t n_in,
+                                     int64_t n_out, int precision, const scn_epilogue *epi, void *stream, double *flops);
+SCN_API int scn_incre_conv_forward_ex(scn_metadata *m, scn_metadata *pre, const int64_t in_size[3],
+                                      const int64_t out_size[3], const float *in, int64_t in_stride, float *out,
+                                      int64_t out_stride, const float *weight, const float *bias, int64_t n_in,
+                                      int64_t n_out, int precision, const scn_epilogue *epi, void *stream, double *flops);
 SCN_API int scn_incre_bn_forward_f16(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const float *in,
                                      int64_t in_stride, void *out, int64_t out_stride, int64_t planes,
                                      const float *running_mean, const float *running_var, const float *gamma,

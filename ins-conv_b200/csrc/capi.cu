@@ -207,10 +207,23 @@ static int take_epilogue(const scn_epilogue *epi, const float *bias, int64_t n_o
     e->dst = epi->bn_out;
     e->stride = epi->bn_out_stride;
     e->skip_raw = epi->skip_raw ? 1 : 0;
+    if (epi->bn_pre_in || epi->bn_pre_out) {  // incremental form: the caller of this function adds pre_exist
+      if (!epi->bn_pre_in || !epi->bn_pre_out || epi->skip_raw)
+        return fail(SCN_E_INVALID, "incremental fused BatchNorm needs both saved row sets and a stored fp32 result");
+      e->pre_in = epi->bn_pre_in;
+      e->pre_in_stride = epi->bn_pre_in_stride;
+      e->pre_out = epi->bn_pre_out;
+      e->pre_out_stride = epi->bn_pre_out_stride;
+    }
     *has = true;
   } else if (epi->skip_raw) {
     return fail(SCN_E_INVALID, "skip_raw without a fused BatchNorm output leaves nothing to compute");
   }
+  return SCN_OK;
+}
+
+static int no_saved_rows(const scn_epilogue *epi) {
+  if (epi && (epi->bn_pre_in || epi->bn_pre_out)) return fail(SCN_E_INVALID, "bn_pre_in / bn_pre_out belong to the incremental operators");
   return SCN_OK;
 }
 
@@ -551,6 +564,7 @@ int scn_ssc_forward_ex(scn_metadata *m, const int64_t size[3], const float *in, 
   SCN_TRY(take_epilogue(epi, bias, n_out, &init, &init_stride, &b, &e, &fused));
   SCN_TRY(check_feat(in, (fused && e.skip_raw) ? (const void *)weight : (const void *)out, weight, n_in, n_out));
   cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(no_saved_rows(epi));
   SCN_TRY(ensure_ssc(m, *g, s));
   SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, b, out, out_stride, n_in, n_out, init, init_stride, precision, s,
                    fused ? &e : nullptr));
@@ -579,11 +593,11 @@ int scn_conv_prepare(scn_metadata *m, const int64_t in_size[3], const int64_t ou
   if (n_active_out) *n_active_out = coarse->n;
   return SCN_OK;
 }
-int scn_conv_forward_ex(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
-                        int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias, int64_t n_in,
-                        int64_t n_out, int precision, const scn_epilogue *epi, void *stream, double *flops) {
+static int conv_forward_impl(scn_metadata *m, scn_metadata *pre, const int64_t in_size[3], const int64_t out_size[3],
+                             const float *in, int64_t in_stride, float *out, int64_t out_stride, const float *weight,
+                             const float *bias, int64_t n_in, int64_t n_out, int precision, const scn_epilogue *epi,
+                             cudaStream_t s, double *flops) {
   Grid *fine, *coarse;
-  cudaStream_t s = (cudaStream_t)stream;
   SCN_TRY(need_coarse(m, in_size, out_size, &fine, &coarse, s));
   if (flops) *flops = 0;
   if (coarse->n == 0) return SCN_OK;
@@ -592,11 +606,32 @@ int scn_conv_forward_ex(scn_metadata *m, const int64_t in_size[3], const int64_t
   EpiBn e;
   bool fused;
   SCN_TRY(take_epilogue(epi, bias, n_out, &init, &init_stride, &b, &e, &fused));
+  if (fused && e.pre_in) {  // incremental form: which coarse sites existed in the saved frame
+    Grid *g2, *pg2;
+    IncreMaps *im;
+    SCN_TRY(need_incre(m, pre, out_size, &g2, &pg2, &im, s));
+    e.pre_exist = im->pre_exist;
+  }
   SCN_TRY(check_feat(in, (fused && e.skip_raw) ? (const void *)weight : (const void *)out, weight, n_in, n_out));
   SCN_TRY(run_conv(in, in_stride, fine->n, coarse->child, 8, coarse->n, weight, b, out, out_stride, n_in, n_out, init, init_stride,
                    precision, s, fused ? &e : nullptr));
   if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
   return SCN_OK;
+}
+int scn_conv_forward_ex(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
+                        int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias, int64_t n_in,
+                        int64_t n_out, int precision, const scn_epilogue *epi, void *stream, double *flops) {
+  SCN_TRY(no_saved_rows(epi));
+  return conv_forward_impl(m, nullptr, in_size, out_size, in, in_stride, out, out_stride, weight, bias, n_in, n_out, precision, epi,
+                           (cudaStream_t)stream, flops);
+}
+int scn_incre_conv_forward_ex(scn_metadata *m, scn_metadata *pre, const int64_t in_size[3], const int64_t out_size[3],
+                              const float *in, int64_t in_stride, float *out, int64_t out_stride, const float *weight,
+                              const float *bias, int64_t n_in, int64_t n_out, int precision, const scn_epilogue *epi,
+                              void *stream, double *flops) {
+  if (epi && (epi->bn_pre_in || epi->bn_pre_out) && !pre) return fail(SCN_E_INVALID, "null saved metadata");
+  return conv_forward_impl(m, pre, in_size, out_size, in, in_stride, out, out_stride, weight, bias, n_in, n_out, precision, epi,
+                           (cudaStream_t)stream, flops);
 }
 int scn_conv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t out_size[3], const float *in,
                      int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
@@ -609,6 +644,7 @@ int scn_deconv_forward_ex(scn_metadata *m, const int64_t in_size[3], const int64
                           int64_t n_in, int64_t n_out, int precision, const scn_epilogue *epi, void *stream, double *flops) {
   Grid *fine, *coarse;
   cudaStream_t s = (cudaStream_t)stream;
+  SCN_TRY(no_saved_rows(epi));
   SCN_TRY(need_coarse(m, out_size, in_size, &fine, &coarse, s));
   if (flops) *flops = 0;
   if (fine->n == 0) return SCN_OK;
@@ -734,10 +770,10 @@ static int need_nbr2(Grid *g, Grid *pg, IncreMaps *im, cudaStream_t s) {
   return SCN_OK;
 }
 
-int scn_incre_ssc_forward(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const float *in,
-                          int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
-                          const float *pre_in, int64_t pre_in_stride, int64_t n_in, int64_t n_out, int precision,
-                          void *stream, double *flops) {
+int scn_incre_ssc_forward_ex(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const float *in,
+                             int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
+                             const float *pre_in, int64_t pre_in_stride, int64_t n_in, int64_t n_out, int precision,
+                             const scn_epilogue *epi, void *stream, double *flops) {
   Grid *g, *pg;
   IncreMaps *im;
   cudaStream_t s = (cudaStream_t)stream;
@@ -746,14 +782,30 @@ int scn_incre_ssc_forward(scn_metadata *m, scn_metadata *pre, const int64_t size
   if (g->n == 0) return SCN_OK;
   SCN_TRY(check_feat(in, out, weight, n_in, n_out));
   if (!pre_in) return fail(SCN_E_INVALID, "null saved features");
+  const float *init = nullptr, *bias1 = bias;
+  int64_t init_stride = 0;
+  EpiBn e;
+  bool has = false;
+  SCN_TRY(take_epilogue(epi, bias, n_out, &init, &init_stride, &bias1, &e, &has));
+  if (has && e.pre_in) e.pre_exist = im->pre_exist;
   SCN_TRY(ensure_ssc(m, *g, s));
   SCN_TRY(need_nbr2(g, pg, im, s));
-  SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0, precision, s));
-  if (im->nbr2_total)
+  // the epilogue rides on the last pass: the second one (saved neighbours of new sites) when there is one
+  const bool two = im->nbr2_total != 0;
+  SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias1, out, out_stride, n_in, n_out, init, init_stride, precision, s,
+                   has && !two ? &e : nullptr));
+  if (two)
     SCN_TRY(run_conv(pre_in, pre_in_stride, pg->n, im->nbr2, 27, g->n, weight, nullptr, out, out_stride, n_in, n_out, out, out_stride,
-                     precision, s));
+                     precision, s, has ? &e : nullptr));
   if (flops) *flops = (double)(g->nbr_total + im->nbr2_total) * (double)n_in * (double)n_out;
   return SCN_OK;
+}
+int scn_incre_ssc_forward(scn_metadata *m, scn_metadata *pre, const int64_t size[3], const float *in,
+                          int64_t in_stride, float *out, int64_t out_stride, const float *weight, const float *bias,
+                          const float *pre_in, int64_t pre_in_stride, int64_t n_in, int64_t n_out, int precision,
+                          void *stream, double *flops) {
+  return scn_incre_ssc_forward_ex(m, pre, size, in, in_stride, out, out_stride, weight, bias, pre_in, pre_in_stride, n_in, n_out,
+                                  precision, nullptr, stream, flops);
 }
 int scn_incre_ssc_rulebook(scn_metadata *m, scn_metadata *pre, const int64_t size[3], int64_t counts_host[27],
                            int32_t *pairs_host, void *stream) {

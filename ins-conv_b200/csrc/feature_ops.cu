@@ -251,13 +251,18 @@ __global__ void k_bn_f16out(const float *__restrict__ in, long long in_stride, _
                             long long rows, int C, const float *__restrict__ mean, const float *__restrict__ var,
                             const float *__restrict__ gamma, const float *__restrict__ beta, float eps, float leak,
                             const int32_t *__restrict__ pre_exist, const __half *__restrict__ pre_out, long long pre_out_stride,
-                            const float *__restrict__ pre_in, long long pre_in_stride) {
+                            const float *__restrict__ pre_in, long long pre_in_stride, int affine_given) {
   extern __shared__ float sm[];  // scale[C], shift[C]
   float *sw = sm, *sb = sm + C;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    const float w = (1.0f / sqrtf(var[c] + eps)) * (gamma ? gamma[c] : 1.f);
-    sw[c] = w;
-    sb[c] = (beta ? beta[c] : 0.f) - mean[c] * w;
+    if (affine_given) {  // mean = scale, var = shift
+      sw[c] = mean[c];
+      sb[c] = var[c];
+    } else {
+      const float w = (1.0f / sqrtf(var[c] + eps)) * (gamma ? gamma[c] : 1.f);
+      sw[c] = w;
+      sb[c] = (beta ? beta[c] : 0.f) - mean[c] * w;
+    }
   }
   __syncthreads();
   const int cv = C / 8;
@@ -300,7 +305,7 @@ __global__ void k_bn_f16out(const float *__restrict__ in, long long in_stride, _
 int bn_forward_f16out(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows, int64_t planes,
                       const float *mean, const float *var, const float *gamma, const float *beta, float eps, float leak,
                       cudaStream_t s, const int32_t *pre_exist, const void *pre_out, int64_t pre_out_stride, const float *pre_in,
-                      int64_t pre_in_stride) {
+                      int64_t pre_in_stride, bool affine_given) {
   if (rows == 0 || planes == 0) return SCN_OK;
   if (planes > 4096) return fail(SCN_E_INVALID, "BatchNorm over more than 4096 planes");
   if (planes % 8 != 0 || in_stride % 4 != 0 || out_stride % 8 != 0 || !aligned16(in) || !aligned16(out))
@@ -313,7 +318,7 @@ int bn_forward_f16out(const float *in, int64_t in_stride, void *out, int64_t out
   k_bn_f16out<<<blocks, 256, (size_t)planes * 2 * sizeof(float), s>>>(in, in_stride, static_cast<__half *>(out), out_stride, rows,
                                                                       (int)planes, mean, var, gamma, beta, eps, leak, pre_exist,
                                                                       static_cast<const __half *>(pre_out), pre_out_stride, pre_in,
-                                                                      pre_in_stride);
+                                                                      pre_in_stride, affine_given ? 1 : 0);
   SCN_LAUNCHED();
   return SCN_OK;
 }

@@ -1163,7 +1163,16 @@ int tc_pack_weights_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, vo
 int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                        const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
                        int64_t init_stride, cudaStream_t s, const EpiBn *epi) {
-  const EpiBn e = epi ? *epi : EpiBn();
+  EpiBn e = epi ? *epi : EpiBn();
+  // The incremental form of the fused BatchNorm (residual against the saved frame's rows) lives in the epilogues of the
+  // warp-level and slab kernels; where the tcgen05 kernel takes the layer, the convolution stores its fp32 result and
+  // the BatchNorm kernel follows as a launch of its own.
+  EpiBn later;
+  const bool slab = n_out <= 16384 && warp_slab_f16_shape(K, Cin, Cout);
+  if (e.dst && e.pre_exist && !slab) {
+    later = e;
+    e = EpiBn();
+  }
   if (e.dst && (e.stride % 8 != 0 || !aligned16(e.dst) || !aligned16(e.scale) || !aligned16(e.shift)))
     return fail(SCN_E_INVALID, "the fp16 rows of a fused BatchNorm must be 16-byte aligned with a stride that is a multiple of 8");
   if (!tc_f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "the fp16 tcgen05 gather-GEMM takes planes that are multiples of 32, n_out <= 224");
@@ -1238,6 +1247,10 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
     SCN_LAUNCHED();
   }
   if (partial_pooled) dev_free(partial, s);
+  if (later.dst)
+    SCN_TRY(bn_forward_f16out(out, out_stride, later.dst, later.stride, n_out, Cout, later.scale, later.shift, nullptr, nullptr, 0.f,
+                              later.leak, s, later.pre_exist, later.pre_out, later.pre_out_stride, later.pre_in, later.pre_in_stride,
+                              true));
   return SCN_OK;
 }
 

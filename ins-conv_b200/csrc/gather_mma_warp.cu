@@ -163,6 +163,9 @@ __device__ __forceinline__ void store_acc(const float (&acc)[COUT / 16][NTR][4],
         float *o = out + row * out_stride + g;
         const float *ini = init ? init + row * init_stride + g : nullptr;
         __half *hd = e.dst ? static_cast<__half *>(e.dst) + row * e.stride + plane0 + g : nullptr;
+        const int pe = (hd && e.pre_exist) ? e.pre_exist[row] : -1;
+        const float *xs = pe >= 0 ? e.pre_in + (long long)pe * e.pre_in_stride + plane0 + g : nullptr;
+        const __half *ys = pe >= 0 ? static_cast<const __half *>(e.pre_out) + (long long)pe * e.pre_out_stride + plane0 + g : nullptr;
 #pragma unroll
         for (int m = 0; m < COUT / 16; ++m)
 #pragma unroll
@@ -173,8 +176,9 @@ __device__ __forceinline__ void store_acc(const float (&acc)[COUT / 16][NTR][4],
             else if (bias) v += __ldg(bias + c + g);
             if (!e.skip_raw) o[c] = v;
             if (hd) {
-              float y = fmaf(v, sc[m][h], sh[m][h]);
+              float y = fmaf(xs ? v + xs[c] : v, sc[m][h], sh[m][h]);
               y = y > 0.f ? y : y * e.leak;
+              if (ys) y -= __half2float(ys[c]);
               hd[c] = __float2half_rn(fminf(fmaxf(y, -65504.f), 65504.f));
             }
           }
@@ -395,9 +399,21 @@ __device__ __forceinline__ void store_pass(const float (&a0)[NTR][4], const floa
       }
       if (!e.skip_raw) *reinterpret_cast<float4 *>(out + row * out_stride + 4 * q) = v;
       if (e.dst) {
-        float y0 = fmaf(v.x, sc.x, sh.x), y1 = fmaf(v.y, sc.y, sh.y), y2 = fmaf(v.z, sc.z, sh.z), y3 = fmaf(v.w, sc.w, sh.w);
+        float4 x = v, ysv = make_float4(0.f, 0.f, 0.f, 0.f);
+        const int pe = e.pre_exist ? e.pre_exist[row] : -1;
+        if (pe >= 0) {  // incremental form: add the saved input, subtract the saved activation
+          const float4 a = *reinterpret_cast<const float4 *>(e.pre_in + (long long)pe * e.pre_in_stride + plane0 + 4 * q);
+          x.x += a.x, x.y += a.y, x.z += a.z, x.w += a.w;
+          const uint2 hq = *reinterpret_cast<const uint2 *>(static_cast<const __half *>(e.pre_out) + (long long)pe * e.pre_out_stride +
+                                                            plane0 + 4 * q);
+          const float2 f0 = __half22float2(*reinterpret_cast<const __half2 *>(&hq.x));
+          const float2 f1 = __half22float2(*reinterpret_cast<const __half2 *>(&hq.y));
+          ysv = make_float4(f0.x, f0.y, f1.x, f1.y);
+        }
+        float y0 = fmaf(x.x, sc.x, sh.x), y1 = fmaf(x.y, sc.y, sh.y), y2 = fmaf(x.z, sc.z, sh.z), y3 = fmaf(x.w, sc.w, sh.w);
         y0 = y0 > 0.f ? y0 : y0 * e.leak, y1 = y1 > 0.f ? y1 : y1 * e.leak;
         y2 = y2 > 0.f ? y2 : y2 * e.leak, y3 = y3 > 0.f ? y3 : y3 * e.leak;
+        y0 -= ysv.x, y1 -= ysv.y, y2 -= ysv.z, y3 -= ysv.w;
         const __half2 lo = __floats2half2_rn(fminf(fmaxf(y0, -65504.f), 65504.f), fminf(fmaxf(y1, -65504.f), 65504.f));
         const __half2 hi = __floats2half2_rn(fminf(fmaxf(y2, -65504.f), 65504.f), fminf(fmaxf(y3, -65504.f), 65504.f));
         uint2 pk;
@@ -414,7 +430,8 @@ __host__ __device__ __forceinline__ bool rows_vectorisable(const float *out, lon
                                                            long long init_stride, const float *bias, const EpiBn &e) {
   auto al = [](const void *p, unsigned a) { return (reinterpret_cast<unsigned long long>(p) & (a - 1)) == 0; };
   return al(out, 16) && out_stride % 4 == 0 && (!init || (al(init, 16) && init_stride % 4 == 0)) && (!bias || al(bias, 16)) &&
-         (!e.dst || (al(e.dst, 8) && e.stride % 4 == 0 && al(e.scale, 16) && al(e.shift, 16)));
+         (!e.dst || (al(e.dst, 8) && e.stride % 4 == 0 && al(e.scale, 16) && al(e.shift, 16))) &&
+         (!e.pre_exist || (al(e.pre_in, 16) && e.pre_in_stride % 4 == 0 && al(e.pre_out, 8) && e.pre_out_stride % 4 == 0));
 }
 
 template <int CIN, int COUT, int NTR, int MINB>

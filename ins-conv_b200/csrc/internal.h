@@ -170,6 +170,14 @@ struct EpiBn {
   void *dst = nullptr;           // __half rows [n_out, stride]
   long long stride = 0;
   int skip_raw = 0;
+  // incremental form (pre_exist given): for an output row that existed in the saved frame (pre_exist[row] >= 0) the
+  // fp16 result is the residual act((v + x_saved) * scale + shift) - y_saved, with x_saved the saved frame's fp32 row
+  // and y_saved its BatchNorm's fp16 row (CUDA/BatchNormalization.cu:112-150)
+  const int32_t *pre_exist = nullptr;
+  const float *pre_in = nullptr;
+  long long pre_in_stride = 0;
+  const void *pre_out = nullptr;  // __half rows
+  long long pre_out_stride = 0;
 };
 
 // out[o] = (init ? init[o] : bias) + sum_k in[map[k*n_out + o]] * W[k]   (map == nullptr: identity, K = 1)
@@ -199,10 +207,11 @@ int bn_forward(const float *in, int64_t in_stride, float *out, int64_t out_strid
 // BatchNorm + leaky ReLU (running statistics) with the result stored as fp16 rows (out: __half [rows, planes],
 // out_stride in fp16 elements)
 // pre_exist (optional, [rows]): incremental form, the residual against the saved frame's rows pre_out (fp16) / pre_in (fp32)
+// affine_given: `mean` holds the per-plane scale and `var` the shift (gamma, beta, eps unused)
 int bn_forward_f16out(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows, int64_t planes,
                       const float *mean, const float *var, const float *gamma, const float *beta, float eps, float leak,
                       cudaStream_t s, const int32_t *pre_exist = nullptr, const void *pre_out = nullptr, int64_t pre_out_stride = 0,
-                      const float *pre_in = nullptr, int64_t pre_in_stride = 0);
+                      const float *pre_in = nullptr, int64_t pre_in_stride = 0, bool affine_given = false);
 // fp16 form of the warp-level gather-GEMM: in = __half rows, weights packed by warp_mma_pack_f16 (fp16 fragments)
 bool warp_mma_f16_shape(int64_t K, int64_t Cin, int64_t Cout);
 // fp16 rows through the persistent tcgen05 kernel: planes multiples of 32, weights [vol][n_out][n_in padded to 64] fp16

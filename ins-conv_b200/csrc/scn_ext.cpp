@@ -151,6 +151,20 @@ struct EpiArg {
       TORCH_CHECK(!skip_raw, "skip_raw needs a fused BatchNorm output");
     }
   }
+  // incremental form of the fused BatchNorm: the rows the saved frame's BatchNorm read (fp32) and wrote (fp16)
+  void saved_rows(const at::Tensor &pre_in, const at::Tensor &pre_out, int64_t saved_rows_count, int64_t planes) {
+    if (!e.bn_out) return;
+    TORCH_CHECK(pre_in.defined() && pre_in.is_cuda() && pre_in.scalar_type() == at::kFloat && pre_in.dim() == 2 &&
+                    pre_in.size(0) == saved_rows_count && pre_in.size(1) == planes && pre_in.stride(1) == 1,
+                "bn_pre_in must be the saved float32 rows [saved sites, nOut]");
+    TORCH_CHECK(pre_out.defined() && pre_out.is_cuda() && pre_out.scalar_type() == at::kHalf && pre_out.dim() == 2 &&
+                    pre_out.size(0) == saved_rows_count && pre_out.size(1) == planes && pre_out.stride(1) == 1,
+                "bn_pre_out must be the saved float16 rows [saved sites, nOut]");
+    e.bn_pre_in = pre_in.data_ptr<float>();
+    e.bn_pre_in_stride = pre_in.stride(0);
+    e.bn_pre_out = pre_out.data_ptr<at::Half>();
+    e.bn_pre_out_stride = pre_out.stride(0);
+  }
   const scn_epilogue *get() const { return any ? &e : nullptr; }
 };
 
@@ -251,10 +265,10 @@ double SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filt
   return flops;
 }
 
-double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
-                                at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
-                                at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed,
-                                at::Tensor bn_scale, at::Tensor bn_shift, double bn_leak, at::Tensor bn_out, bool skip_raw) {
+static double convolution_impl(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize, at::Tensor filterStride,
+                               Metadata3 &m, at::Tensor input_features, at::Tensor output_features, at::Tensor weight,
+                               at::Tensor bias, at::Tensor packed, at::Tensor bn_scale, at::Tensor bn_shift, double bn_leak,
+                               at::Tensor bn_out, bool skip_raw, Metadata3 *pre_m, at::Tensor bn_pre_in, at::Tensor bn_pre_out) {
   FeatArg fa(input_features, "input_features");
   need_cuda_f32(weight, "weight");
   expect_filter(filterSize, 2, "Convolution");
@@ -272,11 +286,26 @@ double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at:
   if (!skip_raw) output_features.resize_({n, w.size(2)});
   double flops = 0;
   WeightArg wa(w, packed, fa.half);
+  if (pre_m && bn_pre_in.defined() && bn_pre_in.numel() > 0) {  // incremental form of the fused BatchNorm
+    epi.saved_rows(bn_pre_in, bn_pre_out, scn_metadata_n_active(pre_m->h(), so.v), w.size(2));
+    check(scn_incre_conv_forward_ex(m.h(), pre_m->h(), si.v, so.v, fa.ptr, in.size(1), output_features.data_ptr<float>(), w.size(2),
+                                    wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision, epi.get(), stream_of(in), &flops),
+          "Incre_Convolution_updateOutput");
+    return flops;
+  }
   check(scn_conv_forward_ex(m.h(), si.v, so.v, fa.ptr, in.size(1), skip_raw ? nullptr : output_features.data_ptr<float>(),
                             w.size(2), wa.ptr, opt_ptr(bias), w.size(1), w.size(2), wa.precision, epi.get(),
                             stream_of(in), &flops),
         "Convolution_updateOutput");
   return flops;
+}
+
+double Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
+                                at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
+                                at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed,
+                                at::Tensor bn_scale, at::Tensor bn_shift, double bn_leak, at::Tensor bn_out, bool skip_raw) {
+  return convolution_impl(inputSize, outputSize, filterSize, filterStride, m, input_features, output_features, weight, bias, packed,
+                          bn_scale, bn_shift, bn_leak, bn_out, skip_raw, nullptr, at::Tensor(), at::Tensor());
 }
 
 double Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
@@ -412,7 +441,9 @@ void OutputLayer_updateOutput(Metadata3 &m, at::Tensor input_features, at::Tenso
 double Incre_SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tensor filterSize, Metadata3 &m,
                                                  at::Tensor input_features, at::Tensor output_features,
                                                  at::Tensor weight, at::Tensor bias, Metadata3 &pre_m,
-                                                 at::Tensor pre_input_feats, at::Tensor packed) {
+                                                 at::Tensor pre_input_feats, at::Tensor packed, at::Tensor addend,
+                                                 at::Tensor bn_scale, at::Tensor bn_shift, double bn_leak, at::Tensor bn_out,
+                                                 at::Tensor bn_pre_in, at::Tensor bn_pre_out) {
   // fp32 residual rows with fp32 saved rows, or ('fp16' precision) both as fp16 rows with the fp16 weight pack
   FeatArg fin(input_features, "input_features"), fpre(pre_input_feats, "pre_input_feats");
   TORCH_CHECK(fin.half == fpre.half, "residual rows and saved rows must have the same type (both float32 or both float16)");
@@ -431,22 +462,27 @@ double Incre_SubmanifoldConvolution_updateOutput(at::Tensor inputSize, at::Tenso
   output_features.resize_({n, w.size(2)});
   double flops = 0;
   WeightArg wa(w, packed, fin.half);
-  check(scn_incre_ssc_forward(m.h(), pre_m.h(), s.v, fin.ptr, in.size(1),
-                              output_features.data_ptr<float>(), w.size(2), wa.ptr, opt_ptr(bias),
-                              fpre.ptr, pre.size(1), w.size(1), w.size(2), wa.precision, stream_of(in),
-                              &flops),
+  EpiArg epi(addend, bn_scale, bn_shift, bn_leak, bn_out, false, n, w.size(2), bias);
+  epi.saved_rows(bn_pre_in, bn_pre_out, scn_metadata_n_active(pre_m.h(), s.v), w.size(2));
+  check(scn_incre_ssc_forward_ex(m.h(), pre_m.h(), s.v, fin.ptr, in.size(1),
+                                 output_features.data_ptr<float>(), w.size(2), wa.ptr, opt_ptr(bias),
+                                 fpre.ptr, pre.size(1), w.size(1), w.size(2), wa.precision, epi.get(), stream_of(in),
+                                 &flops),
         "Incre_SubmanifoldConvolution_updateOutput");
   return flops;
 }
 
 double Incre_Convolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
                                       at::Tensor filterStride, Metadata3 &m, at::Tensor input_features,
-                                      at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed) {
+                                      at::Tensor output_features, at::Tensor weight, at::Tensor bias, at::Tensor packed,
+                                      pybind11::object pre_m, at::Tensor bn_scale, at::Tensor bn_shift, double bn_leak,
+                                      at::Tensor bn_out, at::Tensor bn_pre_in, at::Tensor bn_pre_out) {
   // a 2/2 convolution has no overlap between cells: the residual of the output is the convolution of
-  // the residual (reference: CUDA/Convolution.cpp:83-113)
-  at::Tensor none;
-  return Convolution_updateOutput(inputSize, outputSize, filterSize, filterStride, m, input_features, output_features,
-                                  weight, bias, packed, none, none, 0.0, none, false);
+  // the residual (reference: CUDA/Convolution.cpp:83-113).  With pre_m and the saved rows, the incremental BatchNorm
+  // behind the layer is formed in the epilogue.
+  Metadata3 *pm = pre_m.is_none() ? nullptr : pre_m.cast<Metadata3 *>();
+  return convolution_impl(inputSize, outputSize, filterSize, filterStride, m, input_features, output_features, weight, bias, packed,
+                          bn_scale, bn_shift, bn_leak, bn_out, false, pm, bn_pre_in, bn_pre_out);
 }
 
 double Incre_Deconvolution_updateOutput(at::Tensor inputSize, at::Tensor outputSize, at::Tensor filterSize,
@@ -775,8 +811,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
   mod.def("NetworkInNetwork_updateOutput", &NetworkInNetwork_updateOutput, pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);
   mod.def("InputLayer_updateOutput", &InputLayer_updateOutput);
   mod.def("OutputLayer_updateOutput", &OutputLayer_updateOutput);
-  mod.def("Incre_SubmanifoldConvolution_updateOutput", &Incre_SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("pre_metadata"), pybind11::arg("pre_input_feats"), pybind11::arg("packed") = none);
-  mod.def("Incre_Convolution_updateOutput", &Incre_Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);
+  mod.def("Incre_SubmanifoldConvolution_updateOutput", &Incre_SubmanifoldConvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("filterSize"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("pre_metadata"), pybind11::arg("pre_input_feats"), pybind11::arg("packed") = none, pybind11::arg("addend") = none, pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("bn_pre_in") = none, pybind11::arg("bn_pre_out") = none);
+  mod.def("Incre_Convolution_updateOutput", &Incre_Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none, pybind11::arg("pre_metadata") = pybind11::none(), pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("bn_pre_in") = none, pybind11::arg("bn_pre_out") = none);
   mod.def("Incre_Deconvolution_updateOutput", &Incre_Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("pre_metadata"), pybind11::arg("pre_input_feats"), pybind11::arg("packed") = none);
   mod.def("Incre_BatchNormalization_updateOutput", &Incre_BatchNormalization_updateOutput);
   mod.def("Incre_InputLayer_updateOutput", &Incre_InputLayer_updateOutput);

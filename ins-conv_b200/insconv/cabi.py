@@ -92,13 +92,18 @@ PROTOTYPES = {
 class Epilogue(C.Structure):
     """scn_epilogue of include/insconv_b200.h."""
     _fields_ = [("addend", _p), ("addend_stride", _i64), ("bn_scale", _p), ("bn_shift", _p), ("bn_leakiness", _dbl),
-                ("bn_out", _p), ("bn_out_stride", _i64), ("skip_raw", _int)]
+                ("bn_out", _p), ("bn_out_stride", _i64), ("skip_raw", _int), ("bn_pre_in", _p), ("bn_pre_in_stride", _i64),
+                ("bn_pre_out", _p), ("bn_pre_out_stride", _i64)]
 
 
 PROTOTYPES.update({
     "scn_ssc_forward_ex": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, C.POINTER(Epilogue), _p, C.POINTER(_dbl)]),
     "scn_conv_forward_ex": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, C.POINTER(Epilogue), _p,
                                    C.POINTER(_dbl)]),
+    "scn_incre_ssc_forward_ex": (_int, [_p, _p, _i64p, _p, _i64, _p, _i64, _p, _p, _p, _i64, _i64, _i64, _int, C.POINTER(Epilogue), _p,
+                                        C.POINTER(_dbl)]),
+    "scn_incre_conv_forward_ex": (_int, [_p, _p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, C.POINTER(Epilogue), _p,
+                                         C.POINTER(_dbl)]),
     "scn_deconv_forward_ex": (_int, [_p, _i64p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _int, C.POINTER(Epilogue), _p,
                                      C.POINTER(_dbl)]),
 })

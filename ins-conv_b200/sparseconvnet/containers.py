@@ -69,7 +69,10 @@ class Sequential(_Container):
                 input = _run(module, input, increment)
             return input if addend is None else input.like(input.features + addend)
         from .layers import _residual
-        if _residual(input, increment) or self.training or not fuse_epilogues[0]:
+        # The same plan serves residual (reference-style incremental) frames: there the fused BatchNorm is the
+        # incremental one (every convolution checks that the saved frame left what it needs, else it runs unfused)
+        # and the residual of a block's shortcut is added in the branch's last convolution.
+        if self.training or not fuse_epilogues[0] or (_residual(input, increment) and not keep_state[0]):
             return self._forward_half_rows(input, increment, addend)
         # 'fp16' precision, full frame: besides BatchNorms that hand fp16 rows to the convolution behind them, (1) a
         # convolution that reads fp16 rows forms the result of the BatchNorm that consumes its output in its own

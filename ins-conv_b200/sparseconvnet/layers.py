@@ -108,13 +108,24 @@ def bn_affine(bn):
     return bn.__dict__["_affine_cache"][1:]
 
 
-def _fused_bn_args(module, fuse_bn, features):
+def _fused_bn_args(module, fuse_bn, features, residual=False):
     """Arguments for a convolution whose epilogue also applies `fuse_bn` (the BatchNorm + ReLU behind it) and writes
-    the result as fp16 rows: possible when the convolution itself reads fp16 rows (its kernels carry that epilogue)."""
+    the result as fp16 rows: possible when the convolution itself reads fp16 rows (its kernels carry that epilogue).
+    residual: the incremental form, which reads the rows the saved frame's BatchNorm read (fp32) and wrote (fp16)."""
     if fuse_bn is None or features.dtype != torch.float16 or not takes_half_rows(module):
         return None
+    if residual:
+        so, si = fuse_bn.__dict__.get("save_output"), fuse_bn.__dict__.get("save_input")
+        if so is None or si is None or so.features.dtype != torch.float16 or si.features.dtype != torch.float32 or \
+                si.features.numel() == 0 or fuse_bn.training:
+            return None
     scale, shift = bn_affine(fuse_bn)
     return scale, shift, float(fuse_bn.leakiness), features.new_empty(0, dtype=torch.float16)
+
+
+def _saved_bn_rows(fuse_bn):
+    """(rows the saved frame's BatchNorm read, rows it wrote): operands of the incremental fused BatchNorm."""
+    return fuse_bn.save_input.features, fuse_bn.save_output.features
 
 
 def _finish_fused(conv_out, fuse_bn, bn_rows):
@@ -178,10 +189,11 @@ class SubmanifoldConvolution(Module):
             self.bias = Parameter(torch.zeros(nOut))
 
     def forward(self, input, increment=False, addend=None, fuse_bn=None, raw_needed=True):
-        """Full frames only: addend (no bias) = features [nActive, nOut] added to the result in the kernel's epilogue
-        (the residual sum of a ResNet block); fuse_bn = the BatchNormalization module that consumes this output: when
-        this convolution reads fp16 rows, its epilogue also writes fuse_bn's result as fp16 rows (picked up by that
-        module without a kernel of its own); raw_needed = False: nothing else reads the fp32 result, it is not stored."""
+        """addend (no bias) = features [nActive, nOut] added to the result in the kernel's epilogue (the residual sum of
+        a ResNet block); fuse_bn = the BatchNormalization module that consumes this output: when this convolution reads
+        fp16 rows, its epilogue also writes fuse_bn's result as fp16 rows (picked up by that module without a kernel of
+        its own) -- on a residual frame the incremental form of it, against the rows the saved frame's BatchNorm read and
+        wrote; raw_needed = False (full frames): nothing else reads the fp32 result, it is not stored."""
         assert input.features.nelement() == 0 or input.features.size(1) == self.nIn, (self.nIn, self.nOut, input)
         out = input.features.new_empty(0, dtype=torch.float32)
         if not _residual(input, increment):
@@ -196,11 +208,17 @@ class SubmanifoldConvolution(Module):
             res = input.like(out)
             return _halo(_finish_fused(res, fuse_bn, fused[3]) if fused else res)
         rows, saved, packed = _residual_rows(self, input.features, self.save_input_feats)
+        fused = _fused_bn_args(self, fuse_bn, rows, True)
+        fold = addend is not None and "bias" not in self._parameters
         madds = SCN.Incre_SubmanifoldConvolution_updateOutput(
             input.spatial_size, self.filter_size, input.metadata, rows, out, self._parameters["weight"],
-            optionalTensor(self, "bias"), self.save_meta, saved, packed)
+            optionalTensor(self, "bias"), self.save_meta, saved, packed, addend if fold else _NONE,
+            *(fused if fused else (_NONE, _NONE, 0.0, _NONE)), *(_saved_bn_rows(fuse_bn) if fused else (_NONE, _NONE)))
         _count(madds, out)
-        return input.like(out)
+        res = input.like(out if addend is None or fold else out + addend)
+        if fused:  # the incremental BatchNorm's result: picked up by that module, which keeps no state on residual frames
+            res.bn_ready = (fuse_bn, input.like(fused[3]))
+        return res
 
     def input_spatial_size(self, out_size):
         return out_size
@@ -234,15 +252,26 @@ class Convolution(_Strided):
             (input.spatial_size, out_size, self.filter_size, self.filter_stride)
         out = input.features.new_empty(0, dtype=torch.float32)
         residual = _residual(input, increment)
-        fused = None if residual else _fused_bn_args(self, fuse_bn, input.features)
-        op = SCN.Incre_Convolution_updateOutput if residual else SCN.Convolution_updateOutput
-        extra = () if residual else (fused if fused else (_NONE, _NONE, 0.0, _NONE)) + (False,)
-        madds = op(input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features,
-                   out, self._parameters["weight"], optionalTensor(self, "bias"), _packed_for(self, input.features), *extra)
+        fused = _fused_bn_args(self, fuse_bn, input.features, residual)
+        bn_args = fused if fused else (_NONE, _NONE, 0.0, _NONE)
+        if residual:
+            madds = SCN.Incre_Convolution_updateOutput(
+                input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features, out,
+                self._parameters["weight"], optionalTensor(self, "bias"), _packed_for(self, input.features),
+                fuse_bn.save_output.metadata if fused else None, *bn_args,
+                *(_saved_bn_rows(fuse_bn) if fused else (_NONE, _NONE)))
+        else:
+            madds = SCN.Convolution_updateOutput(
+                input.spatial_size, out_size, self.filter_size, self.filter_stride, input.metadata, input.features, out,
+                self._parameters["weight"], optionalTensor(self, "bias"), _packed_for(self, input.features), *bn_args, False)
         _count(madds, out)
         res = input.like(out, out_size)
+        if residual:
+            if fused:
+                res.bn_ready = (fuse_bn, res.like(fused[3]))
+            return res
         res = _finish_fused(res, fuse_bn, fused[3]) if fused else res
-        return res if residual else _halo(res)
+        return _halo(res)
 
     def input_spatial_size(self, out_size):
         return (out_size - 1) * self.filter_stride + self.filter_size
@@ -297,7 +326,7 @@ class BatchNormalization(Module):
             (self.nPlanes, input.features.shape)
         residual = _residual(input, increment)
         ready = input.bn_ready
-        if ready is not None and ready[0] is self and not residual and not self.training:
+        if ready is not None and ready[0] is self and not self.training:
             return ready[1]  # the convolution in front of this module already wrote this module's result (and state)
         half_rows = half_rows and not self.training and self.nPlanes % 8 == 0
         if residual:  # fp16 residual rows when the saved frame's output was written as fp16 rows and its input was kept

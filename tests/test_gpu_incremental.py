@@ -203,3 +203,84 @@ def test_incremental_operators_on_fp16_rows(cuda):
                   cabi.ptr(pw), None, cabi.ptr(pxc), n_in, n_in, n_out, cabi.PREC_F16, stream, C.byref(fl))
         assert rel(out, want) <= 2e-2, (n_in, n_out)
     cabi.check_errors()
+
+
+def test_incremental_batchnorm_in_the_convolution_epilogue(cuda):
+    """scn_incre_ssc_forward_ex / scn_incre_conv_forward_ex with the incremental BatchNorm (and a residual addend) in the
+    epilogue against the same operators followed by scn_incre_bn_forward_f16: equal fp32 results, fp16 rows equal to
+    rounding (the warp-level kernel at 32 planes, the slab kernel at 96, the tcgen05 kernel -- which runs the BatchNorm as
+    a launch of its own inside the library -- for the stride-2 convolution 64 -> 96)."""
+    import ctypes as C
+    stream = torch.cuda.current_stream().cuda_stream
+    coords, new = frames(8)
+    rng = np.random.RandomState(12)
+    pre, m = build(cuda, coords), build(cuda, new)
+    pg, g = O.Grid(coords), O.Grid(new)
+    h = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(cuda).half()
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(cuda)
+
+    def packed(w):
+        p = torch.empty(cabi.lib().scn_packed_size_f16(w.shape[0], w.shape[1], w.shape[2]), dtype=torch.float16, device=cuda)
+        dw = t(w)
+        cabi.call("scn_pack_weights_f16", cabi.ptr(dw), w.shape[0], w.shape[1], w.shape[2], cabi.ptr(p), stream)
+        torch.cuda.synchronize()
+        return p
+
+    fl = C.c_double(0)
+    for n_in, n_out in ((32, 32), (96, 96)):
+        x, px = h(rng.randn(g.n, n_in)), h(rng.randn(pg.n, n_in))
+        pw = packed(synth.kaiming_uniform(rng, 27, n_in, n_out))
+        addend = t(rng.randn(g.n, n_out))
+        scale, shift = t(rng.uniform(0.5, 1.5, n_out)), t(rng.randn(n_out))
+        saved_in, saved_out = t(rng.randn(pg.n, n_out)), h(rng.randn(pg.n, n_out))
+        raw = torch.empty(g.n, n_out, dtype=torch.float32, device=cuda)
+        rows = torch.empty(g.n, n_out, dtype=torch.float16, device=cuda)
+        epi = cabi.Epilogue(cabi.ptr(addend), n_out, cabi.ptr(scale), cabi.ptr(shift), 0.0, cabi.ptr(rows), n_out, 0,
+                            cabi.ptr(saved_in), n_out, cabi.ptr(saved_out), n_out)
+        cabi.call("scn_incre_ssc_forward_ex", m.h, pre.h, cabi.size3(96), cabi.ptr(x), n_in, cabi.ptr(raw), n_out, cabi.ptr(pw), None,
+                  cabi.ptr(px), n_in, n_in, n_out, cabi.PREC_F16, C.byref(epi), stream, C.byref(fl))
+        plain = torch.empty_like(raw)
+        cabi.call("scn_incre_ssc_forward", m.h, pre.h, cabi.size3(96), cabi.ptr(x), n_in, cabi.ptr(plain), n_out, cabi.ptr(pw), None,
+                  cabi.ptr(px), n_in, n_in, n_out, cabi.PREC_F16, stream, C.byref(fl))
+        want_raw = plain + addend
+        assert float((raw - want_raw).abs().max()) <= 1e-5 * float(want_raw.abs().max())
+        # the BatchNorm kernel with scale/shift as gamma/beta on zero mean, unit variance, eps 0
+        want_rows = torch.empty_like(rows)
+        zero, one = torch.zeros(n_out, device=cuda), torch.ones(n_out, device=cuda)
+        cabi.call("scn_incre_bn_forward_f16", m.h, pre.h, cabi.size3(96), cabi.ptr(want_raw), n_out, cabi.ptr(want_rows), n_out, n_out,
+                  cabi.ptr(zero), cabi.ptr(one), cabi.ptr(scale), cabi.ptr(shift), 0.0, 0.0, cabi.ptr(saved_out), n_out,
+                  cabi.ptr(saved_in), n_out, stream)
+        torch.cuda.synchronize()
+        assert float((rows.float() - want_rows.float()).abs().max()) <= 2e-3 * float(want_rows.float().abs().max())
+    # stride-2 convolution of the residual with the incremental BatchNorm of the coarse scale
+    pre.conv_rulebook(96, 48)
+    n_c = C.c_int64(0)
+    cabi.call("scn_conv_prepare", m.h, cabi.size3(96), cabi.size3(48), stream, C.byref(n_c))
+    n_c, n_pc = int(n_c.value), pre.n_active(48)
+    for n_in, n_out in ((32, 64), (64, 96)):
+        x = h(rng.randn(g.n, n_in))
+        pw = packed(synth.kaiming_uniform(rng, 8, n_in, n_out))
+        scale, shift = t(rng.uniform(0.5, 1.5, n_out)), t(rng.randn(n_out))
+        saved_in, saved_out = t(rng.randn(n_pc, n_out)), h(rng.randn(n_pc, n_out))
+        raw = torch.empty(n_c, n_out, dtype=torch.float32, device=cuda)
+        rows = torch.empty(n_c, n_out, dtype=torch.float16, device=cuda)
+        epi = cabi.Epilogue(None, 0, cabi.ptr(scale), cabi.ptr(shift), 0.0, cabi.ptr(rows), n_out, 0, cabi.ptr(saved_in), n_out,
+                            cabi.ptr(saved_out), n_out)
+        cabi.call("scn_incre_conv_forward_ex", m.h, pre.h, cabi.size3(96), cabi.size3(48), cabi.ptr(x), n_in, cabi.ptr(raw), n_out,
+                  cabi.ptr(pw), None, n_in, n_out, cabi.PREC_F16, C.byref(epi), stream, C.byref(fl))
+        plain = torch.empty_like(raw)
+        cabi.call("scn_conv_forward", m.h, cabi.size3(96), cabi.size3(48), cabi.ptr(x), n_in, cabi.ptr(plain), n_out, cabi.ptr(pw),
+                  None, n_in, n_out, cabi.PREC_F16, stream, C.byref(fl))
+        assert float((raw - plain).abs().max()) <= 1e-5 * float(plain.abs().max())
+        want_rows = torch.empty_like(rows)
+        zero, one = torch.zeros(n_out, device=cuda), torch.ones(n_out, device=cuda)
+        cabi.call("scn_incre_bn_forward_f16", m.h, pre.h, cabi.size3(48), cabi.ptr(plain), n_out, cabi.ptr(want_rows), n_out, n_out,
+                  cabi.ptr(zero), cabi.ptr(one), cabi.ptr(scale), cabi.ptr(shift), 0.0, 0.0, cabi.ptr(saved_out), n_out,
+                  cabi.ptr(saved_in), n_out, stream)
+        torch.cuda.synchronize()
+        assert float((rows.float() - want_rows.float()).abs().max()) <= 2e-3 * float(want_rows.float().abs().max())
+    # the saved-row fields belong to the incremental operators
+    with pytest.raises(cabi.ScnError):
+        cabi.call("scn_ssc_forward_ex", m.h, cabi.size3(96), cabi.ptr(x), n_in, cabi.ptr(raw), n_out, cabi.ptr(pw), None, n_in, n_out,
+                  cabi.PREC_F16, C.byref(epi), stream, C.byref(fl))
+    cabi.check_errors()
