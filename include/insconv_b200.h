@@ -71,6 +71,8 @@ SCN_API uint64_t scn_launch_count(void);
  * warps share the reduction of one tile.  0 (default): chosen per launch from the number of tiles; 1, 2, 4, 8: fixed.
  * Results do not depend on it beyond the order of fp32 additions.  Process-wide. */
 SCN_API int scn_set_slab_share(int warps);
+/* Tuning aid: the row count up to which a wide fp16 layer runs that kernel instead of the tcgen05 kernel. */
+SCN_API int scn_set_slab_max_rows(int64_t rows);
 /* Synchronises `stream` and reports errors that kernels can only flag asynchronously (a bounded
  * wait inside a tensor-core kernel that ran out).  No counterpart in the reference, whose kernels
  * have no such waits. */

@@ -263,6 +263,11 @@ int scn_set_slab_share(int warps) {
   g_slab_share = warps;
   return SCN_OK;
 }
+int scn_set_slab_max_rows(int64_t rows) {
+  if (rows < 0) return fail(SCN_E_INVALID, "rows must not be negative");
+  g_slab_max_rows = rows;
+  return SCN_OK;
+}
 int scn_n_rulebook_bits(void) { return 32; }
 int scn_check_errors(void *stream) {
   SCN_CUDA(cudaStreamSynchronize((cudaStream_t)stream));

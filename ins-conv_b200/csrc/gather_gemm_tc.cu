@@ -1160,6 +1160,9 @@ int tc_pack_weights_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, vo
   return SCN_OK;
 }
 
+// rows up to which a wide fp16 layer goes to the slab kernel instead of the tcgen05 kernel (scn_set_slab_max_rows)
+long long g_slab_max_rows = 8192;
+
 int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                        const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
                        int64_t init_stride, cudaStream_t s, const EpiBn *epi) {
@@ -1168,7 +1171,7 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
   // warp-level and slab kernels; where the tcgen05 kernel takes the layer, the convolution stores its fp32 result and
   // the BatchNorm kernel follows as a launch of its own.
   EpiBn later;
-  const bool slab = n_out <= 16384 && warp_slab_f16_shape(K, Cin, Cout);
+  const bool slab = n_out <= g_slab_max_rows && warp_slab_f16_shape(K, Cin, Cout);
   if (e.dst && e.pre_exist && !slab) {
     later = e;
     e = EpiBn();
@@ -1178,12 +1181,12 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
   if (!tc_f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "the fp16 tcgen05 gather-GEMM takes planes that are multiples of 32, n_out <= 224");
   if (!map && K != 1) return fail(SCN_E_INVALID, "no map given for a filter volume above 1");
   {
-    // small grids: too few 128-row tiles for the persistent kernel to fill the GPU without splitting reductions.
-    // Below ~500 rows the slab kernel in turn has too few warps (rows/16 x n_out/32) and its serial reduction per
-    // warp is longer than the split reduction plus its second launch (measured on 60- and 230-row levels).  Measured
-    // with 96 planes: 4.4k rows 17.8 us against 25.6 us, 16k rows 32.0 against 32.4 (and one launch instead of two).
-    const long long slab_rows = 16384;
-    if (n_out <= slab_rows && warp_slab_f16_shape(K, Cin, Cout))
+    // small grids: too few 128-row tiles for the persistent kernel to fill the GPU without splitting reductions; the
+    // slab kernel covers them with rows/16 x n_out/32 tiles whose reductions several warps share.  Measured on the
+    // levels of a 255k-voxel room (slab kernel against this kernel): 14.6k rows 96->96 37 against 29 us, 192->96 62
+    // against 49; 3.5k rows 128->128 24 against 24; 2k rows 160->160 21.5 against 27; 502 rows 192->192 16 against 27;
+    // 116 rows 224->224 12.5 against 31.  The line is drawn at 8192 rows.
+    if (slab)
       return gather_mma_slab_f16(in, in_stride, map, K, n_out, static_cast<const __half *>(Wp) + K * Cout * padded_planes(Cin), bias,
                                  out, out_stride, Cin, Cout, init, init_stride, s, epi);
   }

@@ -228,6 +228,7 @@ int halo_plane_lists(const int32_t *x, int64_t n, int lo, int hi, bool left, boo
                      int64_t *counts, cudaStream_t s);
 bool warp_slab_f16_shape(int64_t K, int64_t Cin, int64_t Cout);
 extern int g_slab_share;
+extern long long g_slab_max_rows;
 int warp_mma_pack_f16_any(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
 int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,

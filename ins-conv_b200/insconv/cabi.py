@@ -39,6 +39,7 @@ PROTOTYPES = {
     "scn_version": (C.c_char_p, []),
     "scn_launch_count": (C.c_uint64, []),
     "scn_set_slab_share": (_int, [_int]),
+    "scn_set_slab_max_rows": (_int, [_i64]),
     "scn_n_rulebook_bits": (_int, []),
     "scn_check_errors": (_int, [_p]),
     "scn_metadata_create": (_int, [C.POINTER(_p)]),
