@@ -383,7 +383,6 @@ __device__ __forceinline__ void tma_tile2d(uint32_t dst, const CUtensorMap *tm, 
 // Every blocking primitive is a bounded mbarrier wait.  A tile with no neighbour at all still runs one step
 // of zero rows so that all roles see the same sequence of tiles.
 constexpr int kPThreads = 448;  // 4 epilogue warps, 8 producer warps, 1 tensor-core warp, 1 weight-loading warp
-constexpr int kMaxBStages = 4;
 constexpr int kProdWarps = 8;
 constexpr int kMaxStages = 8;
 constexpr int kMapBufs = 3;
@@ -392,12 +391,10 @@ constexpr uint32_t kInfoDone = 1;  // info word of a step: (steps of the item <<
 struct alignas(16) CtlP {
   unsigned long long full[kMaxStages];
   unsigned long long empty[kMaxStages];
-  unsigned long long bfull[kMaxBStages];
-  unsigned long long bempty[kMaxBStages];
   unsigned long long accfull[2];
   unsigned long long accempty[2];
   unsigned long long mapfull[kMapBufs];
-  unsigned long long pad_;  // keeps kmask_part on a 16-byte boundary (it is read as two uint4): 8 + 8 + 4 + 4 + 2 + 2 + 3 + 1 words
+  unsigned long long pad_;  // keeps kmask_part on a 16-byte boundary (it is read as two uint4): 8 + 8 + 2 + 2 + 3 + 1 words
   uint32_t info[kMaxStages];
   uint32_t kmask_part[kMapBufs][kProdWarps];
   uint32_t tmem_base;
@@ -460,12 +457,10 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
   if (tid == 0) {
     ctl->failed = 0;
     for (int s = 0; s < stages; ++s) {
-      mbar_init(smem_u32(&ctl->full[s]), 1);  // the owning producer warp's arrival
+      // a step is ready when its gathered rows AND its weight box have landed: the owning producer warp's arrival and
+      // the weight warp's expect_tx arrival complete the same barrier, so the issuing warp waits once per step
+      mbar_init(smem_u32(&ctl->full[s]), 2);
       mbar_init(smem_u32(&ctl->empty[s]), 1);
-    }
-    for (int s = 0; s < stages_b; ++s) {
-      mbar_init(smem_u32(&ctl->bfull[s]), 1);  // the weight copy's expect_tx arrival
-      mbar_init(smem_u32(&ctl->bempty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&ctl->accfull[b]), 1);
@@ -638,10 +633,9 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
     const uint32_t stage16 = kABytes >> 4, bstage16 = b_bytes >> 4;
     const uint32_t b_lo0 = (((smem_base + b_ring) >> 4) & 0x3FFFu) | (1u << 16);
     const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
-    const uint32_t bfull0 = smem_u32(&ctl->bfull[0]), bempty0 = smem_u32(&ctl->bempty[0]);
     long long tile_i = 0;
     int slot = 0, bslot = 0;
-    uint32_t phase = 0, bphase = 0, a_lo = a_lo0, b_lo = b_lo0;
+    uint32_t phase = 0, a_lo = a_lo0, b_lo = b_lo0;
     bool alive = true;
     while (alive) {
       if (!mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) break;
@@ -654,8 +648,7 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
       if (tile_i >= 2 && !mbar_wait(smem_u32(&ctl->accempty[buf]), (uint32_t)(((tile_i >> 1) - 1) & 1), failed)) break;
       tc_fence_after();  // the epilogue's TMEM reads of this accumulator are ordered before the new MMAs
       for (int t = 0; t < T; ++t) {
-        if ((t > 0 && !mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) ||
-            !mbar_wait(bfull0 + 8u * (uint32_t)bslot, bphase, failed)) {
+        if (t > 0 && !mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) {
           alive = false;
           break;
         }
@@ -664,8 +657,7 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
           mma_lohi<HALF>(tmem_d, a_lo + 2, b_lo + 2, desc_hi, idesc, 1u);
           mma_lohi<HALF>(tmem_d, a_lo + 4, b_lo + 4, desc_hi, idesc, 1u);
           mma_lohi<HALF>(tmem_d, a_lo + 6, b_lo + 6, desc_hi, idesc, 1u);
-          mma_commit(empty0 + 8u * (uint32_t)slot);
-          mma_commit(bempty0 + 8u * (uint32_t)bslot);
+          mma_commit(empty0 + 8u * (uint32_t)slot);  // releases the operand slot and, for the weight warp, the weight slot
           if (t == T - 1) mma_commit(smem_u32(&ctl->accfull[buf]));
         }
         a_lo += stage16;
@@ -677,7 +669,6 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
         b_lo += bstage16;
         if (++bslot == stages_b) {
           bslot = 0;
-          bphase ^= 1u;
           b_lo = b_lo0;
         }
       }
@@ -687,13 +678,18 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
   } else if (warp == 4 + kProdWarps + 1) {
     // =========================== weights ==========================================================
     // One warp walks all steps in order and fetches each step's weight block with one TMA box into the weight ring.
-    // It is the only waiter on the ring's `bempty` barriers, so it sees their phases one after the other (a parity
-    // wait cannot tell phases two apart).  It takes part in the map barriers like a producer warp: its arrival for
-    // tile i + 1 comes after it has read tile i's offset mask, which keeps the producers from reusing that buffer
-    // early; it arrives before it starts the tile's copies, so the producers never wait for the weight ring.
-    const uint32_t bfull0 = smem_u32(&ctl->bfull[0]), bempty0 = smem_u32(&ctl->bempty[0]);
-    int bslot = 0, mbuf = 0;
-    uint32_t bwrapped = 0, mphase = 0;
+    // The copy completes the step's `full` barrier (its second arrival, with the box's byte count), so the issuing
+    // warp has one wait per step.  The ring has no barriers of its own: the weight slot of step g was last used by step
+    // g - stages_b, whose tcgen05.commit arrived on that step's operand-slot `empty` barrier; the warp waits for that
+    // phase.  There are more operand slots than weight slots, so that barrier cannot be a phase further (step
+    // g - stages_b + stages has no weights yet), and when the wait has passed, step g - stages has been consumed too:
+    // the arrival on `full` lands in the phase that belongs to step g.  The warp takes part in the map barriers like a
+    // producer warp: its arrival for tile i + 1 comes after it has read tile i's offset mask, which keeps the
+    // producers from reusing that buffer early.
+    const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
+    int bslot = 0, mbuf = 0, aslot = 0, eslot = 0;
+    uint32_t mphase = 0, ephase = 0;
+    long long g = 0;  // steps walked so far
     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&ctl->mapfull[0])) : "memory");
     bool stop = false;
     for (long long i = 0; i < my_tiles && !*failed && !stop; ++i) {
@@ -723,19 +719,24 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
       }
       int k = (Tz > 0 && rest) ? __ffs(rest) - 1 : 0;
       for (int it = 0; it < T; ++it) {
-        if (bwrapped > 0 && !mbar_wait(bempty0 + 8u * (uint32_t)bslot, (bwrapped - 1) & 1u, failed)) {
-          stop = true;
-          break;
+        if (g >= stages_b) {
+          if (!mbar_wait(empty0 + 8u * (uint32_t)eslot, ephase, failed)) {
+            stop = true;
+            break;
+          }
+          if (++eslot == stages) {
+            eslot = 0;
+            ephase ^= 1u;
+          }
         }
         if (lane == 0) {
-          const uint32_t bar = bfull0 + 8u * (uint32_t)bslot;
+          const uint32_t bar = full0 + 8u * (uint32_t)aslot;
           mbar_expect_tx(bar, b_bytes);
           tma_tile2d(smem_base + b_ring + (uint32_t)bslot * b_bytes, &tmB, bar, kb * kStepPlanes, k * Cout);
         }
-        if (++bslot == stages_b) {
-          bslot = 0;
-          ++bwrapped;
-        }
+        ++g;
+        if (++aslot == stages) aslot = 0;
+        if (++bslot == stages_b) bslot = 0;
         if (++kb == KB) {
           kb = 0;
           rest &= rest - 1;
@@ -743,6 +744,9 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
         }
       }
     }
+    // the sentinel step carries no weights: the second arrival its `full` barrier waits for
+    if (!stop && !*failed && lane == 0)
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(full0 + 8u * (uint32_t)aslot) : "memory");
     __syncwarp();
   } else {
     // =========================== epilogue =========================================================
@@ -995,6 +999,7 @@ static PersistPlan persist_plan(int64_t K, int64_t Cout) {
     p.stages = (int)((room - 2ll * (long long)b_bytes) / kABytes);
   }
   if (p.stages > kMaxStages) p.stages = kMaxStages;
+  if (p.stages_b >= p.stages) p.stages_b = p.stages > 1 ? p.stages - 1 : 1;  // the kernel relies on fewer weight slots than operand slots
   p.smem = (size_t)p.stages * kABytes + (size_t)p.stages_b * b_bytes + fixed_p;
   return p;
 }
