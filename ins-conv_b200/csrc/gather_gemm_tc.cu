@@ -386,7 +386,7 @@ constexpr int kPThreads = 448;  // 4 epilogue warps, 8 producer warps, 1 tensor-
 constexpr int kProdWarps = 8;
 constexpr int kMaxStages = 8;
 constexpr int kMapBufs = 3;
-constexpr uint32_t kInfoDone = 1;  // info word of a step: (steps of the item << 8) on an item's first step, or this flag
+constexpr uint32_t kInfoDone = 1;  // info word of a step: (steps of the item << 8 | its first plane block << 1) on an item's first step, or this flag
 
 struct alignas(16) CtlP {
   unsigned long long full[kMaxStages];
@@ -576,21 +576,25 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
           }
           const uint32_t a_base = smem_base + (uint32_t)slot * kABytes;
           const uint32_t bar = smem_u32(&ctl->full[slot]);
-          if (lane == 0 && it == 0) ctl->info[slot] = (uint32_t)T << 8;  // the item's step count rides on its first step
+          if (lane == 0 && it == 0) ctl->info[slot] = ((uint32_t)T << 8) | ((uint32_t)kb << 1);  // the item's step count and first plane block ride on its first step
           const int *mr = mrows + k * kTileM + q;
           const unsigned char *in_kb = in_c + (size_t)kb * 128;
-          // fp16 rows: the last block of a row may be half empty (n_in = 96, 160, 224): those chunks are zero-filled
+          // fp16 rows: the last block of a row may be half empty (n_in = 32, 96, 160, 224).  The tensor-core warp then
+          // issues only the two K = 16 MMAs that cover the first 32 planes, so the other chunks of the slot are never
+          // read and their lanes copy nothing.
           const bool chunk_ok = !HALF || kb * kStepPlanes + c * kChunkPlanes < Cin;
+          if (chunk_ok) {
 #pragma unroll
-          for (int j0 = 0; j0 < 32; j0 += 8) {
-            int src[8];
+            for (int j0 = 0; j0 < 32; j0 += 8) {
+              int src[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) src[j] = (nk && chunk_ok) ? mr[4 * (j0 + j)] : -1;
+              for (int j = 0; j < 8; ++j) src[j] = nk ? mr[4 * (j0 + j)] : -1;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const unsigned char *p = src[j] >= 0 ? in_kb + (long long)src[j] * in_stride * kElem : in;
-              const uint32_t dst = a_base + (uint32_t)(((j0 + j) >> 1) << 10) + (((j0 + j) & 1) ? dst_odd : dst_even);
-              cp_async16(dst, p, src[j] >= 0 ? 16u : 0u);
+              for (int j = 0; j < 8; ++j) {
+                const unsigned char *p = src[j] >= 0 ? in_kb + (long long)src[j] * in_stride * kElem : in;
+                const uint32_t dst = a_base + (uint32_t)(((j0 + j) >> 1) << 10) + (((j0 + j) & 1) ? dst_odd : dst_even);
+                cp_async16(dst, p, src[j] >= 0 ? 16u : 0u);
+              }
             }
           }
           cp_async_commit();
@@ -636,12 +640,14 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
     long long tile_i = 0;
     int slot = 0, bslot = 0;
     uint32_t phase = 0, a_lo = a_lo0, b_lo = b_lo0;
+    const bool half_block = HALF && Cin - (KB - 1) * kStepPlanes <= 32;  // the last plane block of a row holds 32 planes
     bool alive = true;
     while (alive) {
       if (!mbar_wait(full0 + 8u * (uint32_t)slot, phase, failed)) break;
       const uint32_t info = __shfl_sync(0xffffffffu, ctl->info[slot], 0);
       if (info & kInfoDone) break;
       const int T = (int)(info >> 8);
+      int kb = (int)((info >> 1) & 7u);
       const int buf = (int)(tile_i & 1);
       const uint32_t tmem_d = tmem_base + (uint32_t)buf * acc_cols;
       // the epilogue must have drained this accumulator (used by tile tile_i - 2)
@@ -655,11 +661,14 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
         if (elect_one()) {
           mma_lohi<HALF>(tmem_d, a_lo, b_lo, desc_hi, idesc, t > 0 ? 1u : 0u);
           mma_lohi<HALF>(tmem_d, a_lo + 2, b_lo + 2, desc_hi, idesc, 1u);
-          mma_lohi<HALF>(tmem_d, a_lo + 4, b_lo + 4, desc_hi, idesc, 1u);
-          mma_lohi<HALF>(tmem_d, a_lo + 6, b_lo + 6, desc_hi, idesc, 1u);
+          if (kb != KB - 1 || !half_block) {
+            mma_lohi<HALF>(tmem_d, a_lo + 4, b_lo + 4, desc_hi, idesc, 1u);
+            mma_lohi<HALF>(tmem_d, a_lo + 6, b_lo + 6, desc_hi, idesc, 1u);
+          }
           mma_commit(empty0 + 8u * (uint32_t)slot);  // releases the operand slot and, for the weight warp, the weight slot
           if (t == T - 1) mma_commit(smem_u32(&ctl->accfull[buf]));
         }
+        if (++kb == KB) kb = 0;
         a_lo += stage16;
         if (++slot == stages) {
           slot = 0;
