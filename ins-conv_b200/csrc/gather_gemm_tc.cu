@@ -534,6 +534,7 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
     const uint32_t dst_even = (uint32_t)(q << 7) + (uint32_t)((c ^ q) << 4);
     const uint32_t dst_odd = (uint32_t)((q + 4) << 7) + (uint32_t)((c ^ (q + 4)) << 4);
     const unsigned char *in_c = in + (size_t)c * 16;  // this lane's 16-byte chunk of a row block
+    const uint32_t row_bytes = (uint32_t)(in_stride * kElem);  // the launcher keeps rows below 4 GB
     int mbuf = 0;
     uint32_t mphase = 0;
     for (long long i = 0; i < my_tiles && !*failed; ++i) {
@@ -591,7 +592,9 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
               for (int j = 0; j < 8; ++j) src[j] = nk ? mr[4 * (j0 + j)] : -1;
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                const unsigned char *p = src[j] >= 0 ? in_kb + (long long)src[j] * in_stride * kElem : in;
+                // an absent neighbour copies zero bytes (the chunk is zero-filled) from row 0, so that the address is
+                // one 32 x 32 -> 64-bit multiply-add for every lane
+                const unsigned char *p = in_kb + (unsigned long long)(uint32_t)max(src[j], 0) * row_bytes;
                 const uint32_t dst = a_base + (uint32_t)(((j0 + j) >> 1) << 10) + (((j0 + j) & 1) ? dst_odd : dst_even);
                 cp_async16(dst, p, src[j] >= 0 ? 16u : 0u);
               }
@@ -1019,6 +1022,7 @@ int gather_gemm_tf32(const float *in, int64_t in_stride, int64_t in_rows, const 
   *handled = false;
   if (Cin % 32 != 0 || Cout % 32 != 0 || Cout > 256 || K > 27) return SCN_OK;
   if (in_stride % 4 != 0 || out_stride % 4 != 0 || !aligned16(in) || !aligned16(W) || !aligned16(out)) return SCN_OK;
+  if (in_stride > (1ll << 29)) return SCN_OK;  // the kernel multiplies row numbers by a 32-bit row size
   if (bias && !aligned16(bias)) return SCN_OK;
   if (init && (!aligned16(init) || init_stride % 4 != 0)) return SCN_OK;
   const size_t stage_bytes = (size_t)kABytes + (size_t)Cout * 128;
@@ -1207,6 +1211,7 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
   if (in_stride % 8 != 0 || out_stride % 4 != 0 || !aligned16(in) || !aligned16(Wp) || !aligned16(out) ||
       (bias && !aligned16(bias)) || (init && (!aligned16(init) || init_stride % 4 != 0)))
     return fail(SCN_E_INVALID, "rows must be 16-byte aligned (fp16 stride a multiple of 8, fp32 strides multiples of 4)");
+  if (in_stride > (1ll << 30)) return fail(SCN_E_INVALID, "input row stride above 2^30 elements");
   const PersistPlan plan = persist_plan(K, Cout);
   uint32_t cols = 32;
   while (cols < (uint32_t)Cout) cols <<= 1;
