@@ -490,6 +490,9 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
     const int tp = tid - 128, pw = warp - 4;
     // map staging: thread tp and thread tp + 128 share row (tp & 127) of a tile: one takes the even offsets, the other the odd
     const int prow = tp & 127, par = tp >> 7;
+    // where row prow's entry sits among an offset's 128: the copying lanes take rows q, q + 4, q + 8, ... and read their
+    // 32 entries as eight 16-byte words, so the entries of rows with the same (row & 3) are stored next to each other
+    const int pslot = ((prow & 3) << 5) | (prow >> 2);
     int nxt[14];  // map entries of this thread's row, offsets par, par + 2, ..., of the tile after the current one
     auto load_map = [&](long long item) {
       const long long tile = item / Z;
@@ -509,7 +512,7 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
       for (int j = 0; j < 14; ++j) {
         const int k = 2 * j + par;
         if (k < K) {
-          mrows[k * kTileM + prow] = nxt[j];
+          mrows[k * kTileM + pslot] = nxt[j];
           mine |= (nxt[j] >= 0 ? 1u : 0u) << k;
         }
       }
@@ -578,7 +581,7 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
           const uint32_t a_base = smem_base + (uint32_t)slot * kABytes;
           const uint32_t bar = smem_u32(&ctl->full[slot]);
           if (lane == 0 && it == 0) ctl->info[slot] = ((uint32_t)T << 8) | ((uint32_t)kb << 1);  // the item's step count and first plane block ride on its first step
-          const int *mr = mrows + k * kTileM + q;
+          const int4 *mr = reinterpret_cast<const int4 *>(mrows + k * kTileM + (q << 5));
           const unsigned char *in_kb = in_c + (size_t)kb * 128;
           // fp16 rows: the last block of a row may be half empty (n_in = 32, 96, 160, 224).  The tensor-core warp then
           // issues only the two K = 16 MMAs that cover the first 32 planes, so the other chunks of the slot are never
@@ -588,8 +591,15 @@ k_gather_gemm_tc_persist(const void *__restrict__ in_v, long long in_stride, con
 #pragma unroll
             for (int j0 = 0; j0 < 32; j0 += 8) {
               int src[8];
+              {
+                const int4 lo = mr[j0 >> 2], hi = mr[(j0 >> 2) + 1];
+                src[0] = lo.x; src[1] = lo.y; src[2] = lo.z; src[3] = lo.w;
+                src[4] = hi.x; src[5] = hi.y; src[6] = hi.z; src[7] = hi.w;
+              }
+              if (!nk) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) src[j] = nk ? mr[4 * (j0 + j)] : -1;
+                for (int j = 0; j < 8; ++j) src[j] = -1;
+              }
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 // an absent neighbour copies zero bytes (the chunk is zero-filled) from row 0, so that the address is
