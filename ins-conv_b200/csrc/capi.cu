@@ -236,14 +236,16 @@ static int check_feat(const void *in, const void *out, const void *w, int64_t n_
 // One convolution through the gather-GEMM; SCN_PREC_F16: `in` holds fp16 rows and `weight` fp16 fragments
 static int run_conv(const float *in, int64_t in_stride, int64_t in_rows, const int32_t *map, int K, int64_t n_out,
                     const float *weight, const float *bias, float *out, int64_t out_stride, int64_t n_in, int64_t n_planes_out,
-                    const float *init, int64_t init_stride, int precision, cudaStream_t s, const EpiBn *epi = nullptr) {
+                    const float *init, int64_t init_stride, int precision, cudaStream_t s, const EpiBn *epi = nullptr,
+                    const SecondRows *second = nullptr) {
   if (precision == SCN_PREC_F16) {  // narrow layers: warp-level kernel; wide layers: tcgen05 kernel
     if (warp_mma_f16_shape(K, n_in, n_planes_out))
       return gather_mma_warp_f16(in, in_stride, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
-                                 init_stride, s, epi);
+                                 init_stride, s, epi, second);
     return gather_gemm_tc_f16(in, in_stride, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
-                              init_stride, s, epi);
+                              init_stride, s, epi, second);
   }
+  if (second) return fail(SCN_E_UNSUPPORTED, "a second set of gathered rows needs fp16 rows (SCN_PREC_F16)");
   if (epi && epi->dst) return fail(SCN_E_UNSUPPORTED, "a fused BatchNorm output needs a convolution that reads fp16 rows (SCN_PREC_F16)");
   return gather_gemm(in, in_stride, in_rows, map, K, n_out, weight, bias, out, out_stride, n_in, n_planes_out, init,
                      init_stride, precision, s);
@@ -797,6 +799,17 @@ int scn_incre_ssc_forward_ex(scn_metadata *m, scn_metadata *pre, const int64_t s
   SCN_TRY(need_nbr2(g, pg, im, s));
   // the epilogue rides on the last pass: the second one (saved neighbours of new sites) when there is one
   const bool two = im->nbr2_total != 0;
+  if (two && precision == SCN_PREC_F16 && f16_second_rows_ok(27, n_in, n_out, g->n)) {
+    // both gathers in one launch: the kernel walks the second map through the same accumulators
+    SecondRows second;
+    second.in = pre_in;
+    second.stride = pre_in_stride;
+    second.map = im->nbr2;
+    SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias1, out, out_stride, n_in, n_out, init, init_stride, precision,
+                     s, has ? &e : nullptr, &second));
+    if (flops) *flops = (double)(g->nbr_total + im->nbr2_total) * (double)n_in * (double)n_out;
+    return SCN_OK;
+  }
   SCN_TRY(run_conv(in, in_stride, g->n, g->nbr, 27, g->n, weight, bias1, out, out_stride, n_in, n_out, init, init_stride, precision, s,
                    has && !two ? &e : nullptr));
   if (two)
@@ -843,10 +856,19 @@ int scn_incre_deconv_forward(scn_metadata *m, scn_metadata *pre, const int64_t i
     SCN_TRY(dev_alloc_t(&im_c->up2, (size_t)fine->n * 8, s));
     SCN_TRY(build_incre_up(*coarse, im_c->pre_exist, im_f->pre_exist, im_c->up2, s));
   }
-  SCN_TRY(run_conv(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
-                   precision, s));
-  SCN_TRY(run_conv(pre_in, pre_in_stride, pg1->n, im_c->up2, 8, fine->n, weight, nullptr, out, out_stride, n_in, n_out, out, out_stride,
-                   precision, s));
+  if (precision == SCN_PREC_F16 && f16_second_rows_ok(8, n_in, n_out, fine->n)) {  // both gathers in one launch
+    SecondRows second;
+    second.in = pre_in;
+    second.stride = pre_in_stride;
+    second.map = im_c->up2;
+    SCN_TRY(run_conv(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
+                     precision, s, nullptr, &second));
+  } else {
+    SCN_TRY(run_conv(in, in_stride, coarse->n, coarse->fine_up, 8, fine->n, weight, bias, out, out_stride, n_in, n_out, nullptr, 0,
+                     precision, s));
+    SCN_TRY(run_conv(pre_in, pre_in_stride, pg1->n, im_c->up2, 8, fine->n, weight, nullptr, out, out_stride, n_in, n_out, out,
+                     out_stride, precision, s));
+  }
   if (flops) *flops = (double)fine->n * (double)n_in * (double)n_out;
   return SCN_OK;
 }

@@ -1193,7 +1193,7 @@ long long g_slab_max_rows = 8192;
 
 int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                        const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                       int64_t init_stride, cudaStream_t s, const EpiBn *epi) {
+                       int64_t init_stride, cudaStream_t s, const EpiBn *epi, const SecondRows *second) {
   EpiBn e = epi ? *epi : EpiBn();
   // The incremental form of the fused BatchNorm (residual against the saved frame's rows) lives in the epilogues of the
   // warp-level and slab kernels; where the tcgen05 kernel takes the layer, the convolution stores its fp32 result and
@@ -1216,8 +1216,9 @@ int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, in
     // 116 rows 224->224 12.5 against 31.  The line is drawn at 8192 rows.
     if (slab)
       return gather_mma_slab_f16(in, in_stride, map, K, n_out, static_cast<const __half *>(Wp) + K * Cout * padded_planes(Cin), bias,
-                                 out, out_stride, Cin, Cout, init, init_stride, s, epi);
+                                 out, out_stride, Cin, Cout, init, init_stride, s, epi, second);
   }
+  if (second) return fail(SCN_E_UNSUPPORTED, "the tcgen05 kernel gathers one set of rows (f16_second_rows_ok says which layers take two)");
   if (in_stride % 8 != 0 || out_stride % 4 != 0 || !aligned16(in) || !aligned16(Wp) || !aligned16(out) ||
       (bias && !aligned16(bias)) || (init && (!aligned16(init) || init_stride % 4 != 0)))
     return fail(SCN_E_INVALID, "rows must be 16-byte aligned (fp16 stride a multiple of 8, fp32 strides multiples of 4)");

@@ -434,11 +434,13 @@ __host__ __device__ __forceinline__ bool rows_vectorisable(const float *out, lon
          (!e.pre_exist || (al(e.pre_in, 16) && e.pre_in_stride % 4 == 0 && al(e.pre_out, 8) && e.pre_out_stride % 4 == 0));
 }
 
-template <int CIN, int COUT, int NTR, int MINB>
+// TWO: a second set of gathered rows (SecondRows) follows the first through the same accumulators: the warp's slice of
+// shared memory is refilled with the second map's addresses once the first reduction is done.
+template <int CIN, int COUT, int NTR, int MINB, bool TWO>
 __global__ void __launch_bounds__(kWarps * 32, MINB)
 k_gather_mma_f16(const __half *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
                  const uint4 *__restrict__ Wp, const float *__restrict__ bias, float *out, long long out_stride,
-                 const float *init, long long init_stride, const EpiBn epi, const int vec) {
+                 const float *init, long long init_stride, const EpiBn epi, const int vec, const SecondRows second) {
   constexpr int ROWS = 8 * NTR, MTC = COUT / 16;
   static_assert(kMaxK * ROWS * 8 >= ROWS * 36 * 4, "the epilogue stages a 32-plane pass in the warp's map slice");
   __shared__ unsigned long long s_map[kWarps][kMaxK * ROWS];
@@ -447,10 +449,7 @@ k_gather_mma_f16(const __half *__restrict__ in, long long in_stride, const int32
   const long long row0 = ((long long)blockIdx.x * kWarps + warp) * ROWS;
   if (row0 >= n_out) return;
   unsigned long long *mp = s_map[warp];
-  MapRegs<ROWS> regs;
-  load_map<ROWS>(regs, row0, map, K, n_out, lane);
   const bool perm = K == 27;
-  unsigned int mask = publish_addr<ROWS>(regs, mp, K, lane, reinterpret_cast<const char *>(in), in_stride * 2, perm);
   float acc[MTC][NTR][4];
 #pragma unroll
   for (int m = 0; m < MTC; ++m)
@@ -460,6 +459,14 @@ k_gather_mma_f16(const __half *__restrict__ in, long long in_stride, const int32
       for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
   constexpr int WK = (CIN / 32) * MTC * 2 * 32;  // uint4 per offset
   const uint4 *wl = Wp + lane;
+#pragma unroll 1
+  for (int src = 0; src < (TWO ? 2 : 1); ++src) {
+  if (TWO && src == 1) __syncwarp();  // every lane has read the first map's addresses
+  MapRegs<ROWS> regs;
+  load_map<ROWS>(regs, row0, (TWO && src == 1) ? second.map : map, K, n_out, lane);
+  unsigned int mask = publish_addr<ROWS>(regs, mp, K, lane,
+                                         (TWO && src == 1) ? static_cast<const char *>(second.in) : reinterpret_cast<const char *>(in),
+                                         ((TWO && src == 1) ? second.stride : in_stride) * 2, perm);
   if (mask) {
     FragH<CIN, NTR> f0, f1;
     int k0 = visit_offset(__ffs(mask) - 1, perm);
@@ -484,6 +491,8 @@ k_gather_mma_f16(const __half *__restrict__ in, long long in_stride, const int32
       if (k0 < 0) break;
     }
   }
+  }
+  if (TWO) __syncwarp();  // the slice becomes the epilogue's staging area
   if (vec) {
     float *st = reinterpret_cast<float *>(mp);
 #pragma unroll
@@ -554,11 +563,11 @@ __device__ __forceinline__ void slab_offset(float (&acc)[2][2][4], SlabRows<C32>
   }
 }
 
-template <int C32, int KS>
+template <int C32, int KS, bool TWO>
 __global__ void __launch_bounds__(kSlabWarps * 32, 2)
 k_gather_mma_f16_slab(const __half *__restrict__ in, long long in_stride, const int32_t *__restrict__ map, int K, long long n_out,
                       const uint4 *__restrict__ Wp, int Cout, const float *__restrict__ bias, float *out, long long out_stride,
-                      const float *init, long long init_stride, const EpiBn epi, const int vec) {
+                      const float *init, long long init_stride, const EpiBn epi, const int vec, const SecondRows second) {
   constexpr int ROWS = 16, TILES = kSlabWarps / KS;
   __shared__ unsigned long long s_map[kSlabWarps][kMaxK * ROWS];
   __shared__ float s_part[KS > 1 ? kSlabWarps : 1][16][32];  // [warp][accumulator element][lane]
@@ -578,10 +587,15 @@ k_gather_mma_f16_slab(const __half *__restrict__ in, long long in_stride, const 
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
   if (live) {
-    MapRegs<ROWS> regs;
-    load_map<ROWS>(regs, row0, map, K, n_out, lane);
     const bool perm = K == 27;
-    const unsigned int all = publish_addr<ROWS>(regs, mp, K, lane, reinterpret_cast<const char *>(in), in_stride * 2, perm);
+#pragma unroll 1
+    for (int src = 0; src < (TWO ? 2 : 1); ++src) {  // TWO: the second set of rows follows through the same accumulators
+    if (TWO && src == 1) __syncwarp();  // every lane has read the first map's addresses
+    MapRegs<ROWS> regs;
+    load_map<ROWS>(regs, row0, (TWO && src == 1) ? second.map : map, K, n_out, lane);
+    const unsigned int all = publish_addr<ROWS>(
+        regs, mp, K, lane, (TWO && src == 1) ? static_cast<const char *>(second.in) : reinterpret_cast<const char *>(in),
+        ((TWO && src == 1) ? second.stride : in_stride) * 2, perm);
     unsigned int mask = all;
     if (KS > 1) {  // this warp's share: every KS-th occupied offset, counted from its own index
       mask = 0;
@@ -614,6 +628,8 @@ k_gather_mma_f16_slab(const __half *__restrict__ in, long long in_stride, const 
         wk = wl + kn * WK;
       }
     }
+    }
+    if (TWO) __syncwarp();  // the slice becomes the epilogue's staging area
     if (KS > 1 && split != 0) {
 #pragma unroll
       for (int m = 0; m < 2; ++m)
@@ -833,6 +849,10 @@ int warp_mma_pack_f16_any(const float *W, int64_t K, int64_t Cin, int64_t Cout, 
   return SCN_OK;
 }
 
+bool f16_second_rows_ok(int64_t K, int64_t Cin, int64_t Cout, int64_t n_out) {
+  return K > 1 && (warp_mma_f16_shape(K, Cin, Cout) || (n_out <= g_slab_max_rows && warp_slab_f16_shape(K, Cin, Cout)));
+}
+
 bool warp_slab_f16_shape(int64_t K, int64_t Cin, int64_t Cout) {
   return K >= 1 && K <= kMaxK && Cin % 32 == 0 && Cin >= 96 && Cin <= 224 && Cout % 32 == 0 && Cout >= 32 && Cout <= 256;
 }
@@ -840,13 +860,23 @@ bool warp_slab_f16_shape(int64_t K, int64_t Cin, int64_t Cout) {
 // 0: the launcher chooses how many warps share a tile's reduction; 1, 2, 4, 8: fixed (scn_set_slab_share, a tuning aid)
 int g_slab_share = 0;
 
+static int check_second(const SecondRows *second, int K) {
+  if (!second) return SCN_OK;
+  if (!second->in || !second->map || K == 1) return fail(SCN_E_INVALID, "a second set of rows needs rows, a map and a filter volume above 1");
+  if (second->stride % 8 != 0 || !aligned16(second->in))
+    return fail(SCN_E_INVALID, "fp16 rows must be 16-byte aligned with a stride that is a multiple of 8 elements");
+  return SCN_OK;
+}
+
 int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                        int64_t init_stride, cudaStream_t s, const EpiBn *epi) {
+                        int64_t init_stride, cudaStream_t s, const EpiBn *epi, const SecondRows *second) {
   const EpiBn e = epi ? *epi : EpiBn();
   if (!warp_slab_f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "shape not covered by the slab kernel");
   if (in_stride % 8 != 0 || !aligned16(in) || !aligned16(Wp))
     return fail(SCN_E_INVALID, "fp16 rows must be 16-byte aligned with a stride that is a multiple of 8 elements");
+  SCN_TRY(check_second(second, K));
+  const SecondRows two = second ? *second : SecondRows();
   const __half *inh = static_cast<const __half *>(in);
   const uint4 *W4 = static_cast<const uint4 *>(Wp);
   const long long tiles = (n_out + 15) / 16;
@@ -860,9 +890,15 @@ int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, i
   if (ks != 1 && ks != 2 && ks != 4 && ks != 8) ks = lone >= 4000 ? 1 : lone >= 1000 ? 2 : lone >= 150 ? 4 : 8;
   const int tiles_per_block = kSlabWarps / ks;
   const dim3 grid((unsigned)((tiles + tiles_per_block - 1) / tiles_per_block), (unsigned)slabs);
-#define SCN_SLAB_LAUNCH(C32, KS)                                                                                              \
-  k_gather_mma_f16_slab<C32, KS><<<grid, kSlabWarps * 32, 0, s>>>(inh, in_stride, map, K, n_out, W4, (int)Cout, bias, out, \
-                                                                  out_stride, init, init_stride, e, vec)
+#define SCN_SLAB_LAUNCH(C32, KS)                                                                                                    \
+  do {                                                                                                                             \
+    if (second)                                                                                                                    \
+      k_gather_mma_f16_slab<C32, KS, true><<<grid, kSlabWarps * 32, 0, s>>>(inh, in_stride, map, K, n_out, W4, (int)Cout, bias, out, \
+                                                                            out_stride, init, init_stride, e, vec, two);            \
+    else                                                                                                                           \
+      k_gather_mma_f16_slab<C32, KS, false><<<grid, kSlabWarps * 32, 0, s>>>(inh, in_stride, map, K, n_out, W4, (int)Cout, bias,    \
+                                                                             out, out_stride, init, init_stride, e, vec, two);     \
+  } while (0)
 #define SCN_SLAB_KS(C32)                        \
   switch (ks) {                                 \
     case 1: SCN_SLAB_LAUNCH(C32, 1); break;     \
@@ -885,8 +921,10 @@ int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, i
 
 int gather_mma_warp_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                        int64_t init_stride, cudaStream_t s, const EpiBn *epi) {
+                        int64_t init_stride, cudaStream_t s, const EpiBn *epi, const SecondRows *second) {
   const EpiBn e = epi ? *epi : EpiBn();
+  SCN_TRY(check_second(second, K));
+  const SecondRows two = second ? *second : SecondRows();
   if (!f16_shape(K, Cin, Cout)) return fail(SCN_E_INVALID, "the fp16 gather-GEMM takes 32 or 64 planes on either side");
   if (!map && K != 1) return fail(SCN_E_INVALID, "no map given for a filter volume above 1");
   if (in_stride % 8 != 0 || !aligned16(in) || !aligned16(Wp))
@@ -897,8 +935,12 @@ int gather_mma_warp_f16(const void *in, int64_t in_stride, const int32_t *map, i
 #define SCN_F16_LAUNCH(CI, CO, NTR, MINB)                                                                         \
   do {                                                                                                            \
     const long long tiles = (n_out + 8 * NTR - 1) / (8 * NTR);                                                    \
-    k_gather_mma_f16<CI, CO, NTR, MINB><<<(unsigned)((tiles + kWarps - 1) / kWarps), kWarps * 32, 0, s>>>(        \
-        inh, in_stride, map, K, n_out, W4, bias, out, out_stride, init, init_stride, e, vec);                     \
+    if (second)                                                                                                   \
+      k_gather_mma_f16<CI, CO, NTR, MINB, true><<<(unsigned)((tiles + kWarps - 1) / kWarps), kWarps * 32, 0, s>>>( \
+          inh, in_stride, map, K, n_out, W4, bias, out, out_stride, init, init_stride, e, vec, two);              \
+    else                                                                                                          \
+      k_gather_mma_f16<CI, CO, NTR, MINB, false><<<(unsigned)((tiles + kWarps - 1) / kWarps), kWarps * 32, 0, s>>>( \
+          inh, in_stride, map, K, n_out, W4, bias, out, out_stride, init, init_stride, e, vec, two);              \
   } while (0)
   if (Cin == 32 && Cout == 32) SCN_F16_LAUNCH(32, 32, 4, 5);
   else if (Cin == 32 && Cout == 64) SCN_F16_LAUNCH(32, 64, 4, 4);

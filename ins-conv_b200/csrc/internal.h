@@ -212,6 +212,16 @@ int bn_forward_f16out(const float *in, int64_t in_stride, void *out, int64_t out
                       const float *mean, const float *var, const float *gamma, const float *beta, float eps, float leak,
                       cudaStream_t s, const int32_t *pre_exist = nullptr, const void *pre_out = nullptr, int64_t pre_out_stride = 0,
                       const float *pre_in = nullptr, int64_t pre_in_stride = 0, bool affine_given = false);
+// A second set of gathered rows for the same weights and the same output rows: out = init + sum_k in[map[k]] W[k] +
+// sum_k in2[map2[k]] W[k] in one launch (the incremental submanifold convolution: residual rows of the changed
+// neighbours and saved rows of the old neighbours of new sites).  Carried by the warp-level and slab fp16 kernels.
+struct SecondRows {
+  const void *in = nullptr;  // __half rows
+  long long stride = 0;      // in fp16 elements
+  const int32_t *map = nullptr;  // [K][n_out]
+};
+// true when an fp16 layer of this shape on this many rows runs on a kernel that takes SecondRows
+bool f16_second_rows_ok(int64_t K, int64_t Cin, int64_t Cout, int64_t n_out);
 // fp16 form of the warp-level gather-GEMM: in = __half rows, weights packed by warp_mma_pack_f16 (fp16 fragments)
 bool warp_mma_f16_shape(int64_t K, int64_t Cin, int64_t Cout);
 // fp16 rows through the persistent tcgen05 kernel: planes multiples of 32, weights [vol][n_out][n_in padded to 64] fp16
@@ -220,7 +230,7 @@ int64_t tc_f16_packed_size(int64_t K, int64_t Cin, int64_t Cout);
 int tc_pack_weights_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
 int gather_gemm_tc_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                        const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                       int64_t init_stride, cudaStream_t s, const EpiBn *epi = nullptr);
+                       int64_t init_stride, cudaStream_t s, const EpiBn *epi = nullptr, const SecondRows *second = nullptr);
 int warp_mma_pack_f16(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
 // wide layers on small grids: 16 rows x 32 output planes per warp, whole reduction in one launch
 // ascending row lists [4][cap] (int64) of the planes x == lo, hi - 1, lo - 1, hi (a side without a neighbour: empty) and their lengths
@@ -232,10 +242,10 @@ extern long long g_slab_max_rows;
 int warp_mma_pack_f16_any(const float *W, int64_t K, int64_t Cin, int64_t Cout, void *packed, cudaStream_t s);
 int gather_mma_slab_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                        int64_t init_stride, cudaStream_t s, const EpiBn *epi = nullptr);
+                        int64_t init_stride, cudaStream_t s, const EpiBn *epi = nullptr, const SecondRows *second = nullptr);
 int gather_mma_warp_f16(const void *in, int64_t in_stride, const int32_t *map, int K, int64_t n_out, const void *Wp,
                         const float *bias, float *out, int64_t out_stride, int64_t Cin, int64_t Cout, const float *init,
-                        int64_t init_stride, cudaStream_t s, const EpiBn *epi = nullptr);
+                        int64_t init_stride, cudaStream_t s, const EpiBn *epi = nullptr, const SecondRows *second = nullptr);
 int bn_forward_train(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows, int64_t planes,
                      float *running_mean, float *running_var, float *save_mean, float *save_invstd, const float *gamma,
                      const float *beta, float eps, float momentum, float leak, cudaStream_t s);

@@ -174,6 +174,13 @@ def test_incremental_operators_on_fp16_rows(cuda):
                   cabi.ptr(px), n_in, n_in, n_out, cabi.PREC_F16, stream, C.byref(fl))
         assert rel(out, want) <= 2e-2, (n_in, n_out)
         assert fl.value == O.rule_flops(O.ssc_rules(g), n_in, n_out) + O.rule_flops(O.incre_ssc_rules(g, pg), n_in, n_out)
+        # with the maps cached, both gathers (changed neighbours, saved neighbours of new sites) are ONE launch
+        assert sum(len(r) for r in O.incre_ssc_rules(g, pg)) > 0
+        l0 = cabi.lib().scn_launch_count()
+        cabi.call("scn_incre_ssc_forward", m.h, pre.h, cabi.size3(96), cabi.ptr(x), n_in, cabi.ptr(out), n_out, cabi.ptr(pw), None,
+                  cabi.ptr(px), n_in, n_in, n_out, cabi.PREC_F16, stream, C.byref(fl))
+        assert cabi.lib().scn_launch_count() - l0 == 1, (n_in, n_out)
+        assert rel(out, want) <= 2e-2, (n_in, n_out)
     # BatchNorm residual as fp16 rows
     for planes, leak in ((32, 0.0), (96, 0.333)):
         x, px = rng.randn(g.n, planes).astype(np.float32), rng.randn(pg.n, planes).astype(np.float32)
