@@ -215,6 +215,16 @@ SCN_API int64_t scn_packed_size_f16(int64_t volume, int64_t n_in, int64_t n_out)
 SCN_API int scn_weights_packable_f16(int64_t volume, int64_t n_in, int64_t n_out);
 SCN_API int scn_pack_weights_f16(const float *weight, int64_t volume, int64_t n_in, int64_t n_out, void *packed,
                                  void *stream);
+/* JoinTable (sparseconvnet/tables.py:44-55: torch.cat of the feature planes of two tensors on the same sites) followed
+ * by the BatchNorm + leaky ReLU that consumes it (a UNet decoder: JoinTable, then a block whose branch starts with
+ * BatchNormReLU), in one pass: joined = [a | b] as fp32 rows [rows, a_planes + b_planes] and
+ * rows_f16 = activation(joined * scale + shift) as fp16 rows for the convolution behind the BatchNorm (scale, shift:
+ * [a_planes + b_planes], gamma / sqrt(var + eps) and beta - mean * scale).  Plane counts multiples of 4; strides in
+ * elements. */
+SCN_API int scn_join_bn_forward_f16(const float *a, int64_t a_stride, int64_t a_planes, const float *b, int64_t b_stride,
+                                    int64_t b_planes, int64_t rows, float *joined, int64_t joined_stride,
+                                    const float *scale, const float *shift, double leakiness, void *rows_f16,
+                                    int64_t rows_f16_stride, void *stream);
 SCN_API int scn_bn_forward_f16(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows,
                                int64_t planes, const float *running_mean, const float *running_var, const float *gamma,
                                const float *beta, double eps, double leakiness, void *stream);

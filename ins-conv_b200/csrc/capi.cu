@@ -672,6 +672,15 @@ int scn_deconv_forward(scn_metadata *m, const int64_t in_size[3], const int64_t 
   return scn_deconv_forward_ex(m, in_size, out_size, in, in_stride, out, out_stride, weight, bias, n_in, n_out, precision, nullptr,
                                stream, flops);
 }
+int scn_join_bn_forward_f16(const float *a, int64_t a_stride, int64_t a_planes, const float *b, int64_t b_stride, int64_t b_planes,
+                            int64_t rows, float *joined, int64_t joined_stride, const float *scale, const float *shift,
+                            double leakiness, void *rows_f16, int64_t rows_f16_stride, void *stream) {
+  if (rows < 0) return fail(SCN_E_INVALID, "negative size");
+  if (rows && (!a || !b || !joined || !scale || !shift || !rows_f16)) return fail(SCN_E_INVALID, "null pointer");
+  return join_bn_forward_f16(a, a_stride, a_planes, b, b_stride, b_planes, rows, joined, joined_stride, scale, shift, (float)leakiness,
+                             rows_f16, rows_f16_stride, (cudaStream_t)stream);
+}
+
 int scn_bn_forward_f16(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows, int64_t planes,
                        const float *running_mean, const float *running_var, const float *gamma, const float *beta,
                        double eps, double leakiness, void *stream) {

@@ -302,6 +302,51 @@ __global__ void k_bn_f16out(const float *__restrict__ in, long long in_stride, _
   }
 }
 
+// JoinTable followed by BatchNorm + leaky ReLU in one pass: joined[r] = [a[r] | b[r]] as fp32 rows (the shortcut of the
+// block behind reads them) and rows16[r] = activation(joined[r] * scale + shift) as fp16 rows (the convolution behind the
+// BatchNorm gathers them).  One thread per four planes of a row.
+__global__ void k_join_bn_f16(const float *__restrict__ a, long long a_stride, int a_planes, const float *__restrict__ b,
+                              long long b_stride, int b_planes, long long rows, float *__restrict__ joined, long long joined_stride,
+                              const float *__restrict__ scale, const float *__restrict__ shift, float leak,
+                              __half *__restrict__ rows16, long long rows16_stride) {
+  const int groups = (a_planes + b_planes) >> 2;
+  const long long total = rows * groups;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / groups;
+    const int c = (int)(i - r * groups) << 2;
+    const float4 v = c < a_planes ? __ldg(reinterpret_cast<const float4 *>(a + r * a_stride + c))
+                                  : __ldg(reinterpret_cast<const float4 *>(b + r * b_stride + (c - a_planes)));
+    *reinterpret_cast<float4 *>(joined + r * joined_stride + c) = v;
+    const float4 sc = __ldg(reinterpret_cast<const float4 *>(scale + c)), sh = __ldg(reinterpret_cast<const float4 *>(shift + c));
+    float y[4] = {fmaf(v.x, sc.x, sh.x), fmaf(v.y, sc.y, sh.y), fmaf(v.z, sc.z, sh.z), fmaf(v.w, sc.w, sh.w)};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) y[j] = fminf(fmaxf(y[j] > 0.f ? y[j] : y[j] * leak, -65504.f), 65504.f);  // saturates like k_bn_f16out
+    const __half2 lo = __floats2half2_rn(y[0], y[1]), hi = __floats2half2_rn(y[2], y[3]);
+    uint2 packed;
+    packed.x = *reinterpret_cast<const unsigned int *>(&lo);
+    packed.y = *reinterpret_cast<const unsigned int *>(&hi);
+    *reinterpret_cast<uint2 *>(rows16 + r * rows16_stride + c) = packed;
+  }
+}
+
+int join_bn_forward_f16(const float *a, int64_t a_stride, int64_t a_planes, const float *b, int64_t b_stride, int64_t b_planes,
+                        int64_t rows, float *joined, int64_t joined_stride, const float *scale, const float *shift, float leak,
+                        void *rows16, int64_t rows16_stride, cudaStream_t s) {
+  if (rows == 0) return SCN_OK;
+  if (a_planes <= 0 || b_planes <= 0 || a_planes % 4 != 0 || b_planes % 4 != 0 || a_planes + b_planes > 4096)
+    return fail(SCN_E_INVALID, "joined BatchNorm: plane counts must be positive multiples of 4, at most 4096 together");
+  if (a_stride % 4 != 0 || b_stride % 4 != 0 || joined_stride % 4 != 0 || rows16_stride % 4 != 0 || !aligned16(a) || !aligned16(b) ||
+      !aligned16(joined) || !aligned16(scale) || !aligned16(shift) || (reinterpret_cast<uintptr_t>(rows16) & 7))
+    return fail(SCN_E_INVALID, "joined BatchNorm: rows must be 16-byte aligned with strides that are multiples of 4 elements");
+  const long long work = rows * ((a_planes + b_planes) / 4);
+  unsigned blocks = blocks_for(work, 256);
+  if (blocks > 148u * 16u) blocks = 148u * 16u;
+  k_join_bn_f16<<<blocks, 256, 0, s>>>(a, a_stride, (int)a_planes, b, b_stride, (int)b_planes, rows, joined, joined_stride, scale,
+                                       shift, leak, static_cast<__half *>(rows16), rows16_stride);
+  SCN_LAUNCHED();
+  return SCN_OK;
+}
+
 int bn_forward_f16out(const float *in, int64_t in_stride, void *out, int64_t out_stride, int64_t rows, int64_t planes,
                       const float *mean, const float *var, const float *gamma, const float *beta, float eps, float leak,
                       cudaStream_t s, const int32_t *pre_exist, const void *pre_out, int64_t pre_out_stride, const float *pre_in,

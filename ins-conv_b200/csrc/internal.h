@@ -222,6 +222,10 @@ struct SecondRows {
 };
 // true when an fp16 layer of this shape on this many rows runs on a kernel that takes SecondRows
 bool f16_second_rows_ok(int64_t K, int64_t Cin, int64_t Cout, int64_t n_out);
+// JoinTable + BatchNorm + leaky ReLU in one pass: joined = [a | b] (fp32 rows), rows16 = activation(joined * scale + shift) (fp16 rows)
+int join_bn_forward_f16(const float *a, int64_t a_stride, int64_t a_planes, const float *b, int64_t b_stride, int64_t b_planes,
+                        int64_t rows, float *joined, int64_t joined_stride, const float *scale, const float *shift, float leak,
+                        void *rows16, int64_t rows16_stride, cudaStream_t s);
 // fp16 form of the warp-level gather-GEMM: in = __half rows, weights packed by warp_mma_pack_f16 (fp16 fragments)
 bool warp_mma_f16_shape(int64_t K, int64_t Cin, int64_t Cout);
 // fp16 rows through the persistent tcgen05 kernel: planes multiples of 32, weights [vol][n_out][n_in padded to 64] fp16

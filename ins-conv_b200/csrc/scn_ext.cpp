@@ -376,6 +376,29 @@ void BatchNormalization_updateOutput(at::Tensor input_features, at::Tensor outpu
         "BatchNormalization_updateOutput");
 }
 
+// JoinTable of two tensors followed by the inference BatchNorm + leaky ReLU that consumes it, in one pass ('fp16'
+// precision): joined <- [a | b] (float32), rows <- activation(joined * scale + shift) (float16)
+void JoinTable_BatchNormalization_updateOutput(at::Tensor a, at::Tensor b, at::Tensor joined, at::Tensor scale, at::Tensor shift,
+                                               double leakiness, at::Tensor rows) {
+  need_cuda_f32(a, "a");
+  need_cuda_f32(b, "b");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(0) == b.size(0), "a and b must be [rows, planes] on the same rows");
+  const int64_t planes = a.size(1) + b.size(1);
+  need_opt_cuda_f32(scale, planes, "scale");
+  need_opt_cuda_f32(shift, planes, "shift");
+  TORCH_CHECK(scale.numel() == planes && shift.numel() == planes, "scale and shift must have one entry per joined plane");
+  TORCH_CHECK(joined.scalar_type() == at::kFloat && rows.scalar_type() == at::kHalf, "joined must be float32 and rows float16");
+  c10::cuda::CUDAGuard guard(a.device());
+  auto ac = a.contiguous(), bc = b.contiguous();
+  joined.resize_({a.size(0), planes});
+  rows.resize_({a.size(0), planes});
+  if (a.size(0) == 0) return;
+  check(scn_join_bn_forward_f16(ac.data_ptr<float>(), ac.size(1), ac.size(1), bc.data_ptr<float>(), bc.size(1), bc.size(1), ac.size(0),
+                                joined.data_ptr<float>(), planes, scale.data_ptr<float>(), shift.data_ptr<float>(), leakiness,
+                                rows.data_ptr<at::Half>(), planes, stream_of(ac)),
+        "JoinTable_BatchNormalization_updateOutput");
+}
+
 double NetworkInNetwork_updateOutput(at::Tensor input_features, at::Tensor output_features, at::Tensor weight,
                                      at::Tensor bias, at::Tensor packed) {
   need_cuda_f32(input_features, "input_features");
@@ -808,6 +831,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
   mod.def("Convolution_updateOutput", &Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none, pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("skip_raw") = false);
   mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);
   mod.def("BatchNormalization_updateOutput", &BatchNormalization_updateOutput);
+  mod.def("JoinTable_BatchNormalization_updateOutput", &JoinTable_BatchNormalization_updateOutput);
   mod.def("NetworkInNetwork_updateOutput", &NetworkInNetwork_updateOutput, pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);
   mod.def("InputLayer_updateOutput", &InputLayer_updateOutput);
   mod.def("OutputLayer_updateOutput", &OutputLayer_updateOutput);

@@ -69,6 +69,7 @@ PROTOTYPES = {
     "scn_packed_size_f16": (_i64, [_i64, _i64, _i64]),
     "scn_weights_packable_f16": (_int, [_i64, _i64, _i64]),
     "scn_pack_weights_f16": (_int, [_p, _i64, _i64, _i64, _p, _p]),
+    "scn_join_bn_forward_f16": (_int, [_p, _i64, _i64, _p, _i64, _i64, _i64, _p, _i64, _p, _p, _dbl, _p, _i64, _p]),
     "scn_bn_forward_f16": (_int, [_p, _i64, _p, _i64, _i64, _i64, _p, _p, _p, _p, _dbl, _dbl, _p]),
     "scn_ssc_forward_add": (_int, [_p, _i64p, _p, _i64, _p, _i64, _p, _p, _i64, _i64, _i64, _int, _p, C.POINTER(_dbl)]),
     "scn_conv_prepare": (_int, [_p, _i64p, _i64p, _p, _i64p]),

@@ -111,6 +111,8 @@ class Sequential(_Container):
                 extra_add = None
             elif kind == "bn_half":
                 input = module.forward(input, increment, True)
+            elif kind == "join":
+                input = module.forward(input, increment, consumer)
             else:
                 input = _run(module, input, increment)
             if extra_add is not None:
@@ -136,6 +138,8 @@ class Sequential(_Container):
             elif isinstance(m, BatchNormalization) and after is not None and takes_half_rows(after) and \
                     not (_hooked(m) or after._forward_pre_hooks):
                 steps.append(("bn_half", None))
+            elif isinstance(m, JoinTable) and not _hooked(m):  # its BatchNorm consumer is applied while the planes are joined
+                steps.append(("join", _bn_consumer(after, after2) if after is not None else None))
             else:
                 steps.append(("plain", None))
         return mods, steps
@@ -191,7 +195,19 @@ class AddTable(_Container):
 class JoinTable(_Container):
     """Concatenates the feature planes of a list of tensors living on the same sites."""
 
-    def forward(self, input, increment=False):
+    def forward(self, input, increment=False, fuse_bn=None):
+        """fuse_bn ('fp16' precision, full frames): the BatchNormalization that consumes the joined tensor in front of a
+        convolution that reads fp16 rows; its result is then written in the same pass as the concatenation."""
+        if fuse_bn is not None and len(input) == 2:
+            from .layers import SCN, _finish_fused, _residual, bn_affine
+            a, b = input[0].features, input[1].features
+            if not _residual(input, increment) and not fuse_bn.training and a.is_cuda and a.dtype == torch.float32 and \
+                    b.dtype == torch.float32 and a.dim() == 2 and b.dim() == 2 and a.size(0) == b.size(0) and a.size(0) > 0 and \
+                    a.size(1) % 4 == 0 and b.size(1) % 4 == 0 and a.size(1) + b.size(1) == fuse_bn.nPlanes:
+                scale, shift = bn_affine(fuse_bn)
+                joined, rows = a.new_empty(0), a.new_empty(0, dtype=torch.float16)
+                SCN.JoinTable_BatchNormalization_updateOutput(a, b, joined, scale, shift, float(fuse_bn.leakiness), rows)
+                return _finish_fused(input[0].like(joined), fuse_bn, rows)
         return input[0].like(torch.cat([t.features for t in input], 1))
 
     def input_spatial_size(self, out_size):

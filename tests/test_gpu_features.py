@@ -88,6 +88,32 @@ def test_bn_forward(cuda, planes, leak):
     close(got, O.bn_forward(x, mean, var, None, None, 1e-4, leak), 1e-5)
 
 
+@pytest.mark.parametrize("pa,pb,leak", [(32, 32, 0.0), (224, 224, 0.0), (64, 96, 0.333), (4, 8, 1.0)])
+def test_join_then_batchnorm_in_one_pass(cuda, pa, pb, leak):
+    """scn_join_bn_forward_f16: the joined fp32 rows bit for bit, the BatchNorm of the joined rows (the oracle's formula
+    on the concatenation, scale / shift as the modules derive them) as fp16 rows to fp16 rounding."""
+    rng = np.random.RandomState(pa + pb)
+    rows = 5003
+    a, b = rng.randn(rows, pa).astype(np.float32), rng.randn(rows, pb).astype(np.float32)
+    planes = pa + pb
+    mean, var = rng.randn(planes).astype(np.float32), rng.uniform(0.5, 2.0, planes).astype(np.float32)
+    gamma, beta = rng.randn(planes).astype(np.float32), rng.randn(planes).astype(np.float32)
+    scale = (gamma / np.sqrt(var + 1e-4)).astype(np.float32)
+    shift = (beta - mean * scale).astype(np.float32)
+    t = lambda x: torch.from_numpy(x).to(cuda)
+    da, db, dsc, dsh = t(a), t(b), t(scale), t(shift)
+    joined = torch.empty(rows, planes, dtype=torch.float32, device=cuda)
+    half = torch.empty(rows, planes, dtype=torch.float16, device=cuda)
+    cabi.call("scn_join_bn_forward_f16", cabi.ptr(da), pa, pa, cabi.ptr(db), pb, pb, rows, cabi.ptr(joined), planes, cabi.ptr(dsc),
+              cabi.ptr(dsh), leak, cabi.ptr(half), planes, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    cat = np.concatenate([a, b], 1)
+    assert np.array_equal(joined.cpu().numpy(), cat)
+    want = O.bn_forward(cat, mean, var, gamma, beta, 1e-4, leak).numpy()
+    got = half.float().cpu().numpy()
+    assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max() + 1e-6
+
+
 @pytest.mark.parametrize("n_in,n_out,bias", [(64, 32, False), (6, 3, True), (448, 224, False)])
 def test_nin_forward(cuda, n_in, n_out, bias):
     rng = np.random.RandomState(n_in)
