@@ -552,9 +552,42 @@ int input_forward(const Grid &g, const float *in, float *out, int64_t planes, in
   return SCN_OK;
 }
 
+// the same, four planes per thread (planes a multiple of 4, 16-byte aligned rows): 16-byte loads and stores, one
+// division per four values
+__global__ void k_output_fwd4(const float4 *__restrict__ in, float4 *__restrict__ out, long long n_pts, int groups,
+                              const int32_t *__restrict__ src_row, const int32_t *__restrict__ pre_exist,
+                              const float4 *__restrict__ pre_in) {
+  const long long total = n_pts * groups;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long p = i / groups;
+    const int c = (int)(i - p * groups);
+    const int r = __ldg(src_row + p);
+    float4 v = __ldg(in + (long long)r * groups + c);
+    if (pre_exist) {
+      const int pe = __ldg(pre_exist + r);
+      if (pe >= 0) {
+        const float4 w = __ldg(pre_in + (long long)pe * groups + c);
+        v.x += w.x;
+        v.y += w.y;
+        v.z += w.z;
+        v.w += w.w;
+      }
+    }
+    out[i] = v;
+  }
+}
 int output_forward(const Grid &g, const float *in, float *out, int64_t planes, const int32_t *pre_exist,
                    const float *pre_in, cudaStream_t s) {
   if (g.n_src == 0 || planes == 0) return SCN_OK;
+  if (planes % 4 == 0 && aligned16(in) && aligned16(out) && (!pre_exist || aligned16(pre_in))) {
+    const long long work = g.n_src * (planes / 4);
+    unsigned blocks = blocks_for(work, 256);
+    if (blocks > 148u * 32u) blocks = 148u * 32u;
+    k_output_fwd4<<<blocks, 256, 0, s>>>(reinterpret_cast<const float4 *>(in), reinterpret_cast<float4 *>(out), g.n_src,
+                                         (int)(planes / 4), g.src_row, pre_exist, reinterpret_cast<const float4 *>(pre_in));
+    SCN_LAUNCHED();
+    return SCN_OK;
+  }
   k_output_fwd<<<blocks_for(g.n_src * planes, 256), 256, 0, s>>>(in, out, g.n_src, (int)planes, g.src_row, pre_exist,
                                                                pre_in);
   SCN_LAUNCHED();

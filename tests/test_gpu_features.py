@@ -139,6 +139,8 @@ def test_input_output_layers(cuda, mode):
     h = rng.randn(g.n, 32).astype(np.float32)
     pts = m.output_forward(torch.from_numpy(h).to(cuda))
     assert torch.equal(pts.cpu(), O.output_forward(h, g))
+    h3 = rng.randn(g.n, 3).astype(np.float32)  # a plane count that is not a multiple of 4: the scalar kernel
+    assert torch.equal(m.output_forward(torch.from_numpy(h3).to(cuda)).cpu(), O.output_forward(h3, g))
 
 
 def test_linearity_at_full_size(cuda):
