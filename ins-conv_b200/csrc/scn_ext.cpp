@@ -420,14 +420,64 @@ double NetworkInNetwork_updateOutput(at::Tensor input_features, at::Tensor outpu
 
 // coords may be a CPU or a CUDA LongTensor [N,3] or [N,4]; a CUDA tensor is used in place (no bounce
 // through the host).
+// Grid builds on a stream of their own (overlap_grid_build): the site ranking and the coarse scales of frame t + 1 depend
+// on that frame's coordinates only, so they can run while the last layers of frame t are still on the GPU, instead of
+// behind them; the host, which waits for the site counts, is then not held up by frame t either.
+struct BuildOverlap {
+  bool on = false;
+  int device = -1;
+  cudaStream_t side = nullptr;
+  cudaEvent_t inputs_ready = nullptr, built = nullptr;
+};
+BuildOverlap g_build_overlap;
+
+// on: records "the inputs of the frames that follow are ready" on the current stream (the builds wait for that event,
+// not for the stream's later work) and moves the builds of InputLayer_updateOutput to a side stream; off: back to the
+// current stream.  The caller promises that coordinates handed over while this is on are complete at that event (inputs
+// resident in device memory, or call again after queueing their copies).
+void overlap_grid_build(bool on) {
+  BuildOverlap &o = g_build_overlap;
+  if (!on) {
+    o.on = false;
+    return;
+  }
+  int dev = 0;
+  TORCH_CHECK(cudaGetDevice(&dev) == cudaSuccess, "overlap_grid_build: no CUDA device");
+  if (o.device != dev) {
+    TORCH_CHECK(o.device < 0, "overlap_grid_build serves one device per process");
+    TORCH_CHECK(cudaStreamCreateWithFlags(&o.side, cudaStreamNonBlocking) == cudaSuccess &&
+                    cudaEventCreateWithFlags(&o.inputs_ready, cudaEventDisableTiming) == cudaSuccess &&
+                    cudaEventCreateWithFlags(&o.built, cudaEventDisableTiming) == cudaSuccess,
+                "overlap_grid_build: could not create the side stream");
+    o.device = dev;
+  }
+  TORCH_CHECK(cudaEventRecord(o.inputs_ready, c10::cuda::getCurrentCUDAStream(dev).stream()) == cudaSuccess,
+              "overlap_grid_build: could not record the event");
+  o.on = true;
+}
+
 void build_input(Metadata3 &m, at::Tensor spatialSize, at::Tensor input_coords, const at::Tensor &feats,
-                 long batchSize, long mode) {
+                 long batchSize, long mode, bool may_overlap = false) {
   TORCH_CHECK(input_coords.dim() == 2 && (input_coords.size(1) == 3 || input_coords.size(1) == 4),
               "coords must be N x 3 or N x 4");
   Size3 s(spatialSize);
   auto c = input_coords.to(at::kLong).contiguous();
   TORCH_CHECK(c.size(0) == feats.size(0), "coords and features disagree on the number of points");
   int64_t n = 0;
+  const BuildOverlap &o = g_build_overlap;
+  // only coordinates that are used as they are (no conversion queued on the current stream just now)
+  const bool overlap = may_overlap && o.on && c.is_cuda() && c.is_same(input_coords) && c.device().index() == o.device;
+  if (overlap) {
+    cudaStream_t main = c10::cuda::getCurrentCUDAStream(o.device).stream();
+    TORCH_CHECK(cudaStreamWaitEvent(o.side, o.inputs_ready, 0) == cudaSuccess, "InputLayer_updateOutput: stream wait failed");
+    check(scn_input_layer_build(m.h(), s.v, c.data_ptr<int64_t>(), 0, c.size(0), (int)c.size(1), batchSize, (int)mode,
+                                (void *)o.side, &n),
+          "InputLayer_updateOutput");
+    // the layers run on the current stream: behind the build
+    TORCH_CHECK(cudaEventRecord(o.built, o.side) == cudaSuccess && cudaStreamWaitEvent(main, o.built, 0) == cudaSuccess,
+                "InputLayer_updateOutput: stream wait failed");
+    return;
+  }
   check(scn_input_layer_build(m.h(), s.v, c.data_ptr<int64_t>(), c.is_cuda() ? 0 : 1, c.size(0), (int)c.size(1),
                               batchSize, (int)mode, stream_of(feats), &n),
         "InputLayer_updateOutput");
@@ -438,7 +488,7 @@ void InputLayer_updateOutput(Metadata3 &m, at::Tensor spatialSize, at::Tensor in
   need_cuda_f32(input_features, "input_features");
   c10::cuda::CUDAGuard guard(input_features.device());
   auto in = input_features.contiguous();
-  build_input(m, spatialSize, input_coords, in, batchSize, mode);
+  build_input(m, spatialSize, input_coords, in, batchSize, mode, true);
   Size3 s(spatialSize);
   output_features.resize_({scn_metadata_n_active(m.h(), s.v), in.size(1)});
   check(scn_input_layer_forward(m.h(), in.data_ptr<float>(), output_features.data_ptr<float>(), in.size(1),
@@ -831,6 +881,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, mod) {
   mod.def("Convolution_updateOutput", &Convolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none, pybind11::arg("bn_scale") = none, pybind11::arg("bn_shift") = none, pybind11::arg("bn_leak") = 0.0, pybind11::arg("bn_out") = none, pybind11::arg("skip_raw") = false);
   mod.def("Deconvolution_updateOutput", &Deconvolution_updateOutput, pybind11::arg("inputSize"), pybind11::arg("outputSize"), pybind11::arg("filterSize"), pybind11::arg("filterStride"), pybind11::arg("metadata"), pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);
   mod.def("BatchNormalization_updateOutput", &BatchNormalization_updateOutput);
+  mod.def("overlap_grid_build", &overlap_grid_build, pybind11::arg("on"));
   mod.def("JoinTable_BatchNormalization_updateOutput", &JoinTable_BatchNormalization_updateOutput);
   mod.def("NetworkInNetwork_updateOutput", &NetworkInNetwork_updateOutput, pybind11::arg("input_features"), pybind11::arg("output_features"), pybind11::arg("weight"), pybind11::arg("bias"), pybind11::arg("packed") = none);
   mod.def("InputLayer_updateOutput", &InputLayer_updateOutput);

@@ -37,6 +37,16 @@ def set_halo_exchange(fn):
     layers.halo_exchange[0] = fn
 
 
+def overlap_grid_build(on):
+    """on: the grid builds of the following full frames (InputLayer: site ranking, coarse scales, rulebook maps) run on a
+    stream of their own, so that the build of frame t + 1 overlaps the last layers of frame t and the host, which waits
+    for the site counts, is not held up by frame t.  The call records "inputs ready" on the current stream: the builds
+    wait for the work queued on it so far and for nothing later, so the coordinates of the frames that follow must be
+    complete at that point (resident in device memory; call again after queueing new copies).  off (default): builds run
+    on the current stream like everything else."""
+    SCN.overlap_grid_build(bool(on))
+
+
 def set_incremental_state(on):
     """Full frames keep the state that reference-style incremental frames (increment=True) read later (default on).
     Off is for pure full-frame inference: a convolution whose output only feeds a BatchNorm fused into its epilogue then

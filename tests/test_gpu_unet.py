@@ -324,3 +324,34 @@ def test_fused_epilogues_change_when_things_are_computed_not_what(cuda):
         scn.set_incremental_state(True)
         scn.set_epilogue_fusion(True)
         scn.set_precision("fp32")
+
+
+def test_grid_builds_on_a_stream_of_their_own_change_nothing(cuda):
+    """sparseconvnet.overlap_grid_build: frames of two different scenes queued back to back, with the builds on the side
+    stream, give bit for bit what the same frames give with everything on one stream."""
+    import sparseconvnet as scn
+    torch.manual_seed(5)
+    model = small_unet(scn, [32, 64, 96, 128]).eval()
+    randomize_bn(model, 6)
+    model = model.to(cuda)
+    scenes = []
+    for seed in (1, 2):
+        c = synth.boxes_and_spheres(seed)
+        scenes.append((torch.from_numpy(c).to(cuda), torch.from_numpy(synth.rgb(seed, c.shape[0])).to(cuda)))
+    scn.set_precision("fp16")
+    try:
+        with torch.no_grad():
+            want = [model([c, f]).clone() for c, f in scenes]
+            torch.cuda.synchronize()
+            scn.overlap_grid_build(True)
+            got = []
+            for _ in range(3):  # no synchronisation between the frames
+                for c, f in scenes:
+                    got.append(model([c, f]))
+            torch.cuda.synchronize()
+        scn.SCN.check_errors()
+        for i, y in enumerate(got):
+            assert torch.equal(y, want[i % 2]), i
+    finally:
+        scn.overlap_grid_build(False)
+        scn.set_precision("fp32")
