@@ -73,6 +73,8 @@ struct scn_metadata {
   bool has_input = false;
   int mode = 0;
   int64_t batch_size = 0;
+  // the stream of the latest call that read this object's grids: what clear() releases them on, so that the release is
+  // ordered behind every kernel that reads them (a build may have run on another stream than the layers)
   cudaStream_t last_stream = nullptr;
   // what the next scn_input_layer_build on this object builds beyond the input scale (-1: the process default), and
   // what the network that ran on it went on to ask for (the caller's record for its next frame)
@@ -443,12 +445,14 @@ static int input_grid(scn_metadata *m, Grid **g) {
 int scn_input_layer_forward(scn_metadata *m, const float *in, float *out, int64_t planes, void *stream) {
   Grid *g;
   SCN_TRY(input_grid(m, &g));
+  m->last_stream = (cudaStream_t)stream;
   if (g->n && (!in || !out)) return fail(SCN_E_INVALID, "null features");
   return input_forward(*g, in, out, planes, m->mode == 4, nullptr, nullptr, nullptr, (cudaStream_t)stream);
 }
 int scn_output_layer_forward(scn_metadata *m, const float *in, float *out, int64_t planes, void *stream) {
   Grid *g;
   SCN_TRY(input_grid(m, &g));
+  m->last_stream = (cudaStream_t)stream;
   if (g->n && (!in || !out)) return fail(SCN_E_INVALID, "null features");
   return output_forward(*g, in, out, planes, nullptr, nullptr, (cudaStream_t)stream);
 }
@@ -562,6 +566,7 @@ int scn_ssc_forward_ex(scn_metadata *m, const int64_t size[3], const float *in, 
                        const scn_epilogue *epi, void *stream, double *flops) {
   Grid *g;
   SCN_TRY(need_grid(m, size, &g));
+  m->last_stream = (cudaStream_t)stream;
   if (flops) *flops = 0;
   if (g->n == 0) return SCN_OK;
   const float *init, *b;
@@ -606,6 +611,7 @@ static int conv_forward_impl(scn_metadata *m, scn_metadata *pre, const int64_t i
                              cudaStream_t s, double *flops) {
   Grid *fine, *coarse;
   SCN_TRY(need_coarse(m, in_size, out_size, &fine, &coarse, s));
+  m->last_stream = s;
   if (flops) *flops = 0;
   if (coarse->n == 0) return SCN_OK;
   const float *init, *b;
@@ -653,6 +659,7 @@ int scn_deconv_forward_ex(scn_metadata *m, const int64_t in_size[3], const int64
   cudaStream_t s = (cudaStream_t)stream;
   SCN_TRY(no_saved_rows(epi));
   SCN_TRY(need_coarse(m, out_size, in_size, &fine, &coarse, s));
+  m->last_stream = s;
   if (flops) *flops = 0;
   if (fine->n == 0) return SCN_OK;
   const float *init, *b;
