@@ -328,8 +328,8 @@ SCN_API int scn_nin_forward(const float *in, int64_t in_stride, float *out, int6
  *   n_in * n_out <= 131072, n_in and n_out multiples of 32, n_out <= 256;
  * anything else is refused with SCN_E_CAPACITY or SCN_E_INVALID and a message.  Pointers must be
  * 16-byte aligned and strides multiples of 4 elements.
- * The first call on each device looks up the buffer's device address; make that call before starting
- * a stream capture on that device.  All calls share the one buffer: it is rewritten at the start of
+ * The first call on each device looks up the buffer's device address (a runtime query, made once per
+ * device).  All calls share the one buffer: it is rewritten at the start of
  * every call (nothing in it has to be cleared), so two calls whose GPU work can overlap -- different
  * streams, or different threads -- race on it; keep them on one stream or serialise them. */
 SCN_API int scn_nin_forward_noalloc(const float *in, int64_t in_stride, float *out, int64_t out_stride, int64_t rows,
